@@ -1,0 +1,221 @@
+/*
+ * vxb200_w8a8.h - C ABI of the B200 (sm_100a) W8A8 linear route.
+ *
+ * The op: fp32 activations -> per-token symmetric int8 (scale = absmax/127)
+ * -> int8 x int8 -> int32 GEMM against pre-packed per-output-channel int8
+ * weights -> fused epilogue: dequant (act-scale x weight-scale) + bias to fp32,
+ * or bit-exact requantization to int8 for a following W8A8 layer.
+ *
+ * Two layers of entry points:
+ *   1. device-pointer entries (vxb_linear_*, vxb_quantize_rows): inputs and
+ *      outputs already live in GPU memory; the caller owns them.
+ *   2. reference-facing entries (vxb_qlinear_i8u8, vxb_cuda_graph_llm_f32,
+ *      vxb_cuda_graph_packed_linear_decode_f32): HOST pointers in, HOST results
+ *      out, signatures and return convention of the reference's own CUDA
+ *      backend hooks so that its C host code can bind them unchanged.
+ *
+ * Return convention of every int-returning entry (the reference's tri-state,
+ * native/src/backends/cuda_engine.h:13-19):
+ *      1  handled - result is in the output buffer
+ *      0  declined before touching the output (unsupported dtype/shape/...);
+ *         the caller may use another route
+ *     -1  failed after work was submitted; do not fall back
+ * vxb_last_error() describes the most recent 0 / -1 on the calling thread.
+ * There is no CPU fallback anywhere in this library.
+ *
+ * Plain C types only; all pointers are raw addresses.
+ */
+#ifndef VXB200_W8A8_H
+#define VXB200_W8A8_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define VXB_ABI_VERSION 1u
+
+#if defined(__GNUC__)
+#define VXB_API __attribute__((visibility("default")))
+#else
+#define VXB_API
+#endif
+
+/* Byte dtypes, numerically equal to the reference's VX_DTYPE_U8 / VX_DTYPE_I8
+ * (native/include/volvoxai_enums.h:479-480). */
+#define VXB_DTYPE_U8 5u
+#define VXB_DTYPE_I8 6u
+/* Operator id of PackedLinear (native/src/generated/operator_vocabulary.h:127). */
+#define VXB_OP_PACKED_LINEAR 1036
+
+typedef struct VxbContext VxbContext; /* device + stream + reusable scratch */
+typedef struct VxbWeight VxbWeight;   /* one linear's weights, repacked once */
+
+/* Kernel route selection for vxb_linear_* (VXB_ROUTE_AUTO in production). */
+enum {
+    VXB_ROUTE_AUTO = 0,
+    VXB_ROUTE_GEMV = 1,     /* bandwidth-bound small-M path (rows <= 32) */
+    VXB_ROUTE_TCGEN05 = 2,  /* TMA-fed tcgen05 kind::i8 GEMM, TMEM accumulators */
+    VXB_ROUTE_SIMT = 3      /* one-thread-per-output dp4a kernel (verification) */
+};
+
+VXB_API uint32_t vxb_abi_version(void);
+VXB_API const char* vxb_last_error(void);
+/* Name of the kernel route the calling thread's last handled call took,
+ * e.g. "k1+tcgen05-i8+e1"; the counterpart of the reference's per-node route
+ * labels (native/src/runtime/engine_runtime_dispatch.inc:2118). */
+VXB_API const char* vxb_last_route(void);
+/* Number of kernels this library launched since load (all threads). */
+VXB_API uint64_t vxb_launch_count(void);
+
+/* ---- context ---------------------------------------------------------- */
+/* `stream` is a cudaStream_t (NULL = the legacy default stream). Scratch
+ * (quantized activations, row scales, split-K partials) grows on demand and is
+ * reused; one context must not be used from two threads at once.  Mirrors the
+ * reference's rule that contexts never share mutable scratch
+ * (docs/backend-sdk.md:75-95). */
+VXB_API int vxb_context_create(int device, void* stream, VxbContext** out);
+VXB_API void vxb_context_destroy(VxbContext* ctx);
+VXB_API int vxb_context_set_stream(VxbContext* ctx, void* stream);
+VXB_API int vxb_context_synchronize(VxbContext* ctx);
+
+/* ---- weight loader ("repack once at compile time") -------------------- */
+/* Replaces the reference's per-model one-time packing of QLinear weights,
+ * qlinear_metadata_build -> vx_pack_q8_weight
+ * (native/src/runtime/engine_runtime_model.inc:2125-2218,
+ *  native/src/kernels/packed_quant_gemm.c:237-392).
+ * Source layout = the canonical W8A8 SafeTensors tensors
+ * (docs/w8a8-safetensors.md:13-121): int8 weight [d_out,d_in] row-major,
+ * fp32 per-output-channel scale [d_out] (all > 0, finite).  bias_f32 (E1) and
+ * bias_i32 (E2, accumulator domain) are optional.  HOST pointers; the data is
+ * copied, laid out for TMA (rows padded to a multiple of 128 bytes with zeros)
+ * and the per-channel code sums needed for activation zero points are
+ * computed on the device. */
+VXB_API int vxb_weight_create_i8(VxbContext* ctx, const int8_t* weight, const float* weight_scales,
+                         const float* bias_f32, const int32_t* bias_i32,
+                         uint32_t d_out, uint32_t d_in, VxbWeight** out);
+/* Same, from PackedLinear W8 storage (docs/packed-linear-design.md:24-41;
+ * native/src/kernels/llm_ops.h:22-32): I32 words [d_out, ceil(d_in/4)] in
+ * offset-binary (int8 = byte ^ 0x80, padding bytes 0x80) and fp32 group scales
+ * [d_out, ceil(d_in/group_size)].  Declines (0) unless every group scale of a
+ * row is identical (per-channel mode) and group_size is 32/64/128/256. */
+VXB_API int vxb_weight_create_w8_words(VxbContext* ctx, const int32_t* words, const float* group_scales,
+                               const float* bias_f32, uint32_t d_out, uint32_t d_in,
+                               uint32_t group_size, VxbWeight** out);
+VXB_API void vxb_weight_destroy(VxbWeight* w);
+VXB_API uint32_t vxb_weight_d_in(const VxbWeight* w);
+VXB_API uint32_t vxb_weight_d_out(const VxbWeight* w);
+/* Bytes of device memory the repacked weight occupies. */
+VXB_API uint64_t vxb_weight_device_bytes(const VxbWeight* w);
+
+/* ---- device-pointer entries ------------------------------------------- */
+/* Per-token quantizer alone. Device twin of vx_packed_prepare_i8_*
+ * (native/src/kernels/packed_linear_ops.inc:97-217) and of the scalar branch
+ * at :1574-1597.  x: fp32 [rows,k] (device).  q: int8 [rows,ldq], ldq >= k,
+ * bytes k..ldq-1 of every row are zeroed.  row_scales: fp32 [rows]; a row that
+ * holds NaN/Inf gets scale NaN, all-zero codes and valid 0.  valid may be NULL. */
+VXB_API int vxb_quantize_rows(VxbContext* ctx, const float* x, uint32_t rows, uint32_t k,
+                      int8_t* q, uint32_t ldq, float* row_scales, int32_t* valid);
+
+/* Whole op, fp32 out (epilogue E1): y[m,n] = f32(f32(acc)*f32(as[m]*ws[n])) + bias[n].
+ * Device twin of vx_packed_linear_forward in dynamic-I8 mode with one scale
+ * group per channel (native/src/kernels/packed_linear_ops.inc:1545-1621).
+ * x: fp32 [rows,d_in]; y: fp32, row stride ldy elements (>= d_out). */
+VXB_API int vxb_linear_f32(VxbContext* ctx, const VxbWeight* w, const float* x, uint32_t rows,
+                   float* y, uint32_t ldy, int route);
+
+/* Whole op, int8 out (epilogue E2), bit-exact:
+ *   mult = f32(f32(as[m]*ws[n]) / out_scale)
+ *   q    = sat_i8(rte(f32(f32(f32(acc + bias_i32[n]) * mult) + out_zero)))
+ * The arithmetic of vx_w8a8_requantize_accumulator / vx_w8a8_multiplier
+ * (native/src/kernels/w8a8_affine.h:125-181) with the dynamic per-token
+ * activation scale in place of the static input scale. Rows holding NaN/Inf
+ * produce out_zero. y: int8, row stride ldy bytes. */
+VXB_API int vxb_linear_i8(VxbContext* ctx, const VxbWeight* w, const float* x, uint32_t rows,
+                  float out_scale, int32_t out_zero, int8_t* y, uint32_t ldy, int route);
+
+/* Whole op up to the exact accumulator (no epilogue), for parity checks:
+ * acc int32 [rows,d_out]; q_out (int8 [rows,d_in]) and scales_out (fp32 [rows])
+ * may be NULL. Exposes what vx_packed_dot_i8 returns per (row, channel)
+ * (native/src/kernels/packed_linear_ops.inc:483-493). */
+VXB_API int vxb_linear_acc_i32(VxbContext* ctx, const VxbWeight* w, const float* x, uint32_t rows,
+                       int32_t* acc, int8_t* q_out, float* scales_out, int route);
+
+/* Static-activation QLinear on device buffers: int8/uint8 input with one
+ * per-tensor scale and zero point, int8/uint8 output.  Device twin of
+ * vx_qlinear_i8u8_packed (native/src/kernels/packed_quant_gemm.c:2633-2763);
+ * uses the weight's bias_i32.  input: [rows,d_in] bytes; output [rows,ldy]. */
+VXB_API int vxb_qlinear_device(VxbContext* ctx, const VxbWeight* w, const void* input, uint32_t rows,
+                       float input_scale, int32_t input_zero_point, float output_scale,
+                       int32_t output_zero_point, uint32_t input_dtype, uint32_t output_dtype,
+                       void* output, uint32_t ldy, int route);
+
+/* Measurement utility (no counterpart in the reference): every SM issues
+ * `iters` x 256 back-to-back M128xN256xK32 kind::i8 MMAs on operands resident
+ * in shared memory; *tops receives the dense int8 rate in tera-ops/s (2 ops per
+ * multiply-accumulate), timed with CUDA events.  The measured denominator for
+ * the tensor-bound roofline. */
+VXB_API int vxb_measure_i8_tensor_peak(VxbContext* ctx, uint32_t iters, double* tops);
+
+/* ---- reference-facing entries (HOST pointers) ------------------------- */
+/* Drop-in for the VxW8A8Ops.qlinear_i8u8 slot
+ * (native/src/backends/w8a8_device_ops.h:15-17,89-124; CUDA implementation
+ * cuda_graph_qlinear_i8u8, native/src/backends/cuda/host/
+ * cuda_graph_quantized_linear_conv_host.inc:19-106).  Same argument order.
+ * Weights are keyed by host address and repacked on first use (immutable, as
+ * the reference marks them is_weight). Declines non-zero weight zero points,
+ * U8 weights, overlapping output, non-finite or non-positive scales. */
+VXB_API int vxb_qlinear_i8u8(const void* input, const void* weight, const float* weight_scales,
+                     const int32_t* weight_zero_points, const int32_t* bias, void* output,
+                     uint32_t rows, uint32_t d_in, uint32_t d_out, float input_scale,
+                     int32_t input_zero_point, float output_scale, int32_t output_zero_point,
+                     uint32_t input_dtype, uint32_t weight_dtype, uint32_t output_dtype);
+
+/* Layout-compatible with the reference's VxLLMOpArgs
+ * (native/src/kernels/llm_ops.h:38-53); only the PackedLinear fields are read:
+ * x[0]=input fp32 [rows,K], x[1]=W8 words, x[2]=group scales, x[3]=bias or NULL,
+ * y[0]=out fp32 [rows,N]; key_dim=K, value_dim=N, rate=group size,
+ * groups=weight bits, normalize=activation bits, batch*sequence=rows,
+ * first_unit/unit_count = flat output window (0 = everything). */
+typedef struct VxbLLMOpArgs {
+    int32_t kind, batch, sequence, keys, heads, kv_heads, key_dim, value_dim;
+    int32_t streams, groups, rate, window, top_k, iterations;
+    int32_t index_heads, index_dim, rotary_dim, rotary_offset;
+    int32_t normalize, causal, interleaved, mask_mode;
+    float eps, hc_eps, scale;
+    const float* x[8];
+    float* y[3];
+    const int32_t* mask;
+    const int32_t* positions;
+    uint64_t x_elements[8], y_elements[3], mask_elements, position_elements;
+    int32_t query_offset;
+    uint64_t first_unit, unit_count;
+} VxbLLMOpArgs;
+
+/* Drop-in for cuda_graph_llm_f32 with kind == PackedLinear
+ * (native/src/backends/cuda_engine.h:13-15; native/src/backends/cuda/host/
+ * cuda_graph_llm_host.inc:714-783).  Admits weight bits 8 + activation bits 8
+ * with per-channel-constant group scales; declines (0) everything else so the
+ * reference's own routes keep serving W2/3/4 and A16/F32.  A window must cover
+ * whole rows. */
+VXB_API int vxb_cuda_graph_llm_f32(const VxbLLMOpArgs* args);
+
+/* Drop-in for the scalar decode entry cuda_graph_packed_linear_decode_f32
+ * (native/src/backends/cuda_engine.h:16-19; impl cuda_graph_llm_host.inc:111-186):
+ * one row, group size 128. */
+VXB_API int vxb_cuda_graph_packed_linear_decode_f32(const float* input, const int32_t* packed_weights,
+                                            const float* weight_scales, const float* bias,
+                                            float* output, uint32_t input_width,
+                                            uint32_t output_width, uint32_t weight_bits,
+                                            uint32_t activation_bits);
+
+/* Drops every cached weight / context the reference-facing entries created
+ * (the counterpart of freeing a compiled model). */
+VXB_API void vxb_host_cache_clear(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VXB200_W8A8_H */

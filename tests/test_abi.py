@@ -1,0 +1,69 @@
+"""CPU-only checks of the drop-in boundary: the shared library loads, exports every
+symbol the public header declares, mirrors the reference descriptor layout, and its
+admission rules decline (return 0) without touching a device."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+
+from volvoxai_b200 import _lib, w8a8
+from volvoxai_b200 import workloads as wl
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "vxb200_w8a8.h")).read()
+    return sorted(set(re.findall(r"VXB_API[^;(]*?\b(vxb_\w+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    L = _lib.load()
+    names = declared_symbols()
+    assert len(names) >= 20
+    for n in names:
+        assert hasattr(L, n), n
+    assert sorted(_lib.EXPORTS) == names
+    assert L.vxb_abi_version() == 1
+
+
+def test_descriptor_layout_matches_reference_struct():
+    # sizeof(VxLLMOpArgs) == 336, x at 104, first_unit at 320 on LP64
+    # (native/src/kernels/llm_ops.h:38-53)
+    assert C.sizeof(_lib.LLMOpArgs) == 336
+    assert _lib.LLMOpArgs.x.offset == 104
+    assert _lib.LLMOpArgs.first_unit.offset == 320
+    assert _lib.LLMOpArgs.unit_count.offset == 328
+
+
+def test_packed_linear_admission_declines_on_host():
+    x = np.zeros((2, 64), np.float32)
+    w = np.zeros((4, 64), np.int8)
+    words = wl.pack_w8_words(w)
+    scales = np.ones((4, 1), np.float32)
+    y = np.full((2, 4), 7.0, np.float32)
+    # W4 / A16 / F32 arithmetic stay with the reference's own routes
+    assert w8a8.packed_linear(x, words, scales, None, y, weight_bits=4, group_size=64) == 0
+    assert w8a8.packed_linear(x, words, scales, None, y, activation_bits=16, group_size=64) == 0
+    assert w8a8.packed_linear(x, words, scales, None, y, activation_bits=32, group_size=64) == 0
+    # ragged window, window past the end, first_unit without a count
+    assert w8a8.packed_linear(x, words, scales, None, y, group_size=64, first_unit=1, unit_count=4) == 0
+    assert w8a8.packed_linear(x, words, scales, None, y, group_size=64, first_unit=4, unit_count=8) == 0
+    assert w8a8.packed_linear(x, words, scales, None, y, group_size=64, first_unit=4, unit_count=0) == 0
+    assert (y == 7.0).all()  # declined before touching the output
+    assert "admitted" in w8a8.last_error() or "window" in w8a8.last_error() or "first_unit" in w8a8.last_error()
+
+
+def test_qlinear_admission_declines_on_host():
+    x = np.zeros((2, 8), np.int8)
+    w = np.zeros((3, 8), np.int8)
+    ws = np.ones(3, np.float32)
+    z = np.zeros(3, np.int32)
+    out = np.full((2, 3), 9, np.int8)
+    assert w8a8.qlinear_i8u8(x, w.view(np.uint8), ws, z, z, out, 1.0, 0, 1.0, 0) == 0  # U8 weights
+    assert w8a8.qlinear_i8u8(x, w, ws, np.array([0, 1, 0], np.int32), z, out, 1.0, 0, 1.0, 0) == 0
+    both = np.zeros(2 * 8 + 2 * 3, np.int8)
+    xin, alias = both[:16].reshape(2, 8), both[12:18].reshape(2, 3)
+    assert w8a8.qlinear_i8u8(xin, w, ws, z, z, alias, 1.0, 0, 1.0, 0) == 0  # output overlaps input
+    assert (out == 9).all()

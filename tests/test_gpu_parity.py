@@ -1,0 +1,355 @@
+"""Parity of the CUDA path (through the C ABI) against the CPU oracle and the golden
+fixtures. Bit-exact for int8 codes, row scales, int32 accumulators and requantized
+int8 outputs; fp32 outputs within 1e-5 (max-abs error normalised by output RMS)."""
+import numpy as np
+import pytest
+
+from volvoxai_b200 import workloads as wl
+
+pytestmark = pytest.mark.gpu
+
+F32_TOL = 1e-5  # max|y - y_ref| / rms(y_ref)
+
+
+@pytest.fixture(scope="module")
+def torch():
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    return torch
+
+
+@pytest.fixture(scope="module")
+def ctx(torch):
+    from volvoxai_b200 import w8a8
+    c = w8a8.Context(0)
+    yield c
+    c.synchronize()
+    c.close()
+
+
+def dev(torch, a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def rel_err(y, ref):
+    ok = np.isfinite(ref)
+    rms = np.sqrt(np.mean(ref[ok].astype(np.float64) ** 2)) if ok.any() else 1.0
+    return float(np.abs(y[ok].astype(np.float64) - ref[ok]).max() / max(rms, 1e-30)) if ok.any() else 0.0
+
+
+ROUTES = {"gemv": 1, "tcgen05": 2, "simt": 3}
+
+
+def run_case(torch, ctx, oracle, case, routes, bias_i32=None, out_zero=0):
+    from volvoxai_b200 import w8a8
+    x, w, ws, bias = case["x"], case["w"], case["ws"], case.get("bias")
+    ref = oracle.w8a8_linear(x, w, ws, bias=bias)
+    finite_rows = ref["valid"] != 0
+    os_ = float(wl.static_out_scale(ref["out"]))
+    ref_i8 = oracle.requant_rows(ref["acc"], ref["row_scales"], ref["valid"], ws, bias_i32, os_, out_zero)
+    assert ref_i8 is not None
+    weight = w8a8.Weight.from_i8(ctx, w, ws, bias_f32=bias, bias_i32=bias_i32)
+    xd = dev(torch, x)
+    for name in routes:
+        r = ROUTES[name]
+        acc, q, s = ctx.linear_acc_i32(weight, xd, route=r, want_q=True)
+        y = ctx.linear_f32(weight, xd, route=r)
+        y8 = ctx.linear_i8(weight, xd, os_, out_zero, route=r)
+        ctx.synchronize()
+        acc, q, s, y, y8 = (t.cpu().numpy() for t in (acc, q, s, y, y8))
+        assert np.array_equal(q, ref["q"]), name
+        assert np.array_equal(s[finite_rows].view(np.uint32), ref["row_scales"][finite_rows].view(np.uint32)), name
+        assert np.isnan(s[~finite_rows]).all(), name
+        assert np.array_equal(acc, ref["acc"]), name
+        assert np.array_equal(np.isnan(y), np.isnan(ref["out"])), name
+        assert rel_err(y, ref["out"]) <= F32_TOL, name
+        assert np.array_equal(y8, ref_i8), name
+    weight.close()
+
+
+# ---- K1 alone ------------------------------------------------------------------------
+
+@pytest.mark.parametrize("k", [5, 33, 257])
+def test_quantizer_golden_adversarial(torch, ctx, golden, k):
+    x = golden[f"quant_k{k}_x"]
+    for ldq in (k, (k + 127) // 128 * 128):
+        q, s, v = ctx.quantize_rows(dev(torch, x), ldq=ldq)
+        ctx.synchronize()
+        q, s, v = q.cpu().numpy(), s.cpu().numpy(), v.cpu().numpy()
+        assert v.all()
+        assert np.array_equal(s.view(np.uint32), golden[f"quant_k{k}_scale"].view(np.uint32))
+        assert np.array_equal(q[:, :k], golden[f"quant_k{k}_q"])
+        assert (q[:, k:] == 0).all()
+
+
+def test_quantizer_special_rows(torch, ctx, golden):
+    x = golden["quant_special_x"]
+    q, s, v = ctx.quantize_rows(dev(torch, x), ldq=128)
+    ctx.synchronize()
+    q, s, v = q.cpu().numpy(), s.cpu().numpy(), v.cpu().numpy()
+    ok = golden["quant_special_valid"] != 0
+    assert np.array_equal(v != 0, ok)
+    assert np.array_equal(q[:, :40], golden["quant_special_q"])
+    assert np.array_equal(s[ok].view(np.uint32), golden["quant_special_scale"][ok].view(np.uint32))
+    assert np.isnan(s[~ok]).all()
+
+
+@pytest.mark.parametrize("k", [1, 2, 3, 7, 8, 9, 31, 32, 33, 63, 64, 65, 255, 256, 257, 320, 576,
+                               1280, 1283, 2048, 4096, 5000, 14336, 20000])
+def test_quantizer_widths_vs_oracle(torch, ctx, oracle, k):
+    rng = np.random.default_rng(k)
+    x = (rng.standard_normal((9, k)) * rng.choice([1e-30, 1e-3, 1.0, 50.0, 1e20], size=(9, 1))).astype(np.float32)
+    x[3] = 0
+    if k > 4:
+        x[5, k // 2] = np.nan
+        x[6, k - 1] = -np.inf
+    qo, so, vo = oracle.quantize_rows(x)
+    kpad = (k + 127) // 128 * 128
+    q, s, v = ctx.quantize_rows(dev(torch, x), ldq=kpad)
+    ctx.synchronize()
+    q, s, v = q.cpu().numpy(), s.cpu().numpy(), v.cpu().numpy()
+    ok = vo != 0
+    assert np.array_equal(v != 0, ok)
+    assert np.array_equal(q[:, :k], qo) and (q[:, k:] == 0).all()
+    assert np.array_equal(s[ok].view(np.uint32), so[ok].view(np.uint32))
+
+
+# ---- whole op ---------------------------------------------------------------------------
+
+def test_config1_all_routes_and_golden(torch, ctx, oracle, golden):
+    """M64 K576 N1536, the reference's CPU-runnable case."""
+    from volvoxai_b200 import w8a8
+    c1 = wl.single_linear()
+    run_case(torch, ctx, oracle, c1, ["simt", "tcgen05"])
+    weight = w8a8.Weight.from_i8(ctx, c1["w"], c1["ws"], bias_f32=c1["bias"])
+    xd = dev(torch, c1["x"])
+    acc, q, s = ctx.linear_acc_i32(weight, xd, want_q=True)
+    y = ctx.linear_f32(weight, xd)
+    y8 = ctx.linear_i8(weight, xd, float(golden["c1_out_scale"]), 0)
+    ctx.synchronize()
+    cols = golden["c1_cols"]
+    assert np.array_equal(q.cpu().numpy(), golden["c1_q"])
+    assert np.array_equal(s.cpu().numpy().view(np.uint32), golden["c1_scale"].view(np.uint32))
+    assert np.array_equal(acc.cpu().numpy()[:, cols], golden["c1_acc_cols"])
+    assert rel_err(y.cpu().numpy()[:, cols], golden["c1_y_cols"]) <= F32_TOL
+    assert np.array_equal(y8.cpu().numpy()[:8], golden["c1_e2_rows8"])
+
+
+@pytest.mark.parametrize("rows", [1, 2, 3, 4, 5, 8, 9, 16, 17, 31, 32])
+@pytest.mark.parametrize("k,n", [(64, 19), (257, 7), (576, 192), (1283, 13), (4096, 520)])
+def test_small_m_routes(torch, ctx, oracle, rows, k, n):
+    rng = np.random.default_rng(rows * 1000 + k + n)
+    case = {"x": rng.standard_normal((rows, k)).astype(np.float32),
+            "w": rng.integers(-128, 128, size=(n, k), dtype=np.int8),
+            "ws": rng.uniform(0.001, 0.02, size=n).astype(np.float32),
+            "bias": rng.standard_normal(n).astype(np.float32)}
+    if rows > 2:
+        case["x"][1] = 0
+    if rows > 4:
+        case["x"][3, k // 3] = np.inf
+    bias_i32 = rng.integers(-300, 300, size=n).astype(np.int32)
+    run_case(torch, ctx, oracle, case, ["gemv", "tcgen05", "simt"], bias_i32=bias_i32, out_zero=-3)
+
+
+@pytest.mark.parametrize("rows,k,n", [
+    (33, 32, 4), (63, 65, 5), (64, 128, 256), (65, 129, 257), (127, 255, 255), (128, 256, 512),
+    (129, 320, 300), (130, 1280, 19), (402, 96, 320), (256, 576, 1536), (300, 1536, 576),
+    (513, 1024, 3072), (1000, 4096, 1000)])
+def test_tile_boundaries_tcgen05(torch, ctx, oracle, rows, k, n):
+    """Shapes straddling the 128x256x128 tile in every dimension."""
+    rng = np.random.default_rng(rows + k * 7 + n * 13)
+    case = {"x": (rng.standard_normal((rows, k)) * rng.uniform(0.01, 30, size=(rows, 1))).astype(np.float32),
+            "w": rng.integers(-128, 128, size=(n, k), dtype=np.int8),
+            "ws": rng.uniform(0.001, 0.02, size=n).astype(np.float32),
+            "bias": rng.standard_normal(n).astype(np.float32)}
+    case["x"][rows // 2] = 0
+    case["x"][rows - 1, 0] = np.nan
+    run_case(torch, ctx, oracle, case, ["tcgen05", "simt"] if rows * k * n < 5e8 else ["tcgen05"],
+             bias_i32=rng.integers(-1000, 1000, size=n).astype(np.int32), out_zero=5)
+
+
+def test_extreme_codes_do_not_overflow(torch, ctx, oracle):
+    """All-(-128) weights against +-127 activations: the largest accumulators K can produce."""
+    k, n, rows = 8192, 264, 40
+    x = np.full((rows, k), 3.0, np.float32)
+    x[::2] *= -1
+    case = {"x": x, "w": np.full((n, k), -128, np.int8), "ws": np.full(n, 0.01, np.float32), "bias": None}
+    run_case(torch, ctx, oracle, case, ["tcgen05"])
+    case["x"] = x[:8]
+    run_case(torch, ctx, oracle, case, ["gemv"])
+
+
+def test_output_row_stride(torch, ctx, oracle):
+    """ldy > d_out: the op writes a column slab of a wider buffer and nothing else."""
+    from volvoxai_b200 import w8a8
+    c = wl.single_linear(rows=70, k=192, n=96, seed=3)
+    ref = oracle.w8a8_linear(c["x"], c["w"], c["ws"], bias=c["bias"])
+    weight = w8a8.Weight.from_i8(ctx, c["w"], c["ws"], bias_f32=c["bias"])
+    wide = torch.full((70, 300), 12345.0, dtype=torch.float32, device="cuda")
+    for route in (2, 3):
+        wide.fill_(12345.0)
+        ctx.linear_f32(weight, dev(torch, c["x"]), out=wide[:, 100:196], route=route)
+        ctx.synchronize()
+        got = wide.cpu().numpy()
+        assert rel_err(got[:, 100:196], ref["out"]) <= F32_TOL
+        assert (got[:, :100] == 12345.0).all() and (got[:, 196:] == 12345.0).all()
+
+
+def test_w8_words_loader_matches_i8_loader(torch, ctx, oracle, golden):
+    """PackedLinear storage (offset-binary words + constant group scales) -> same results;
+    differing group scales are declined."""
+    from volvoxai_b200 import w8a8
+    c = wl.single_linear(rows=37, k=300, n=50, seed=9)
+    words = wl.pack_w8_words(c["w"])
+    gs = wl.group_scales(c["ws"], 300, 128)
+    wa = w8a8.Weight.from_w8_words(ctx, words, gs, 300, 128, bias_f32=c["bias"])
+    ref = oracle.w8a8_linear(c["x"], c["w"], c["ws"], bias=c["bias"])
+    acc = ctx.linear_acc_i32(wa, dev(torch, c["x"]))
+    ctx.synchronize()
+    assert np.array_equal(acc.cpu().numpy(), ref["acc"])
+    gs[3, 1] *= 1.5
+    with pytest.raises(w8a8.W8A8Error) as e:
+        w8a8.Weight.from_w8_words(ctx, words, gs, 300, 128)
+    assert e.value.code == 0
+    wa.close()
+
+
+# ---- static-activation QLinear (R2) ---------------------------------------------------------
+
+@pytest.mark.parametrize("izp", [0, 11])
+def test_static_qlinear_golden(torch, ctx, golden, izp):
+    from volvoxai_b200 import w8a8
+    weight = w8a8.Weight.from_i8(ctx, golden["r2_sym_w"], golden["r2_sym_ws"], bias_i32=golden["r2_sym_bias"])
+    for route in (1, 2, 3):
+        if route == 1:
+            continue  # 37 rows: above the decode path's limit
+        out = ctx.qlinear_device(weight, dev(torch, golden["r2_sym_x"]), 0.037, izp, 0.9, -7, route=route)
+        ctx.synchronize()
+        assert np.array_equal(out.cpu().numpy(), golden[f"r2_sym_z{izp}_y"])
+    weight.close()
+
+
+@pytest.mark.parametrize("in_u8,out_u8", [(False, False), (True, False), (False, True), (True, True)])
+def test_static_qlinear_dtypes_vs_oracle(torch, ctx, oracle, in_u8, out_u8):
+    from volvoxai_b200 import w8a8
+    rng = np.random.default_rng(5 + in_u8 * 2 + out_u8)
+    rows, k, n = 45, 200, 70
+    x = rng.integers(0, 256, size=(rows, k)).astype(np.uint8) if in_u8 else rng.integers(-128, 128, size=(rows, k)).astype(np.int8)
+    w = rng.integers(-127, 128, size=(n, k), dtype=np.int8)
+    ws = rng.uniform(0.001, 0.02, size=n).astype(np.float32)
+    b = rng.integers(-500, 500, size=n).astype(np.int32)
+    izp, ozp = (131, 120) if in_u8 else (-4, 9)
+    if not out_u8:
+        ozp = -ozp // 10
+    want = oracle.qlinear_i8u8(x, w, b, ws, np.zeros(n, np.int32), 0.05, izp, 0.6, ozp, out_unsigned=out_u8)
+    weight = w8a8.Weight.from_i8(ctx, w, ws, bias_i32=b)
+    for rws, route in ((rows, 2), (rows, 3), (8, 1)):
+        out = ctx.qlinear_device(weight, dev(torch, x[:rws]), 0.05, izp, 0.6, ozp, out_unsigned=out_u8, route=route)
+        ctx.synchronize()
+        assert np.array_equal(out.cpu().numpy(), want[:rws])
+    weight.close()
+
+
+# ---- reference-facing host entries -------------------------------------------------------------
+
+def test_host_qlinear_entry(torch, oracle, golden):
+    from volvoxai_b200 import w8a8
+    x, w = golden["r2_sym_x"], golden["r2_sym_w"]
+    ws, b = golden["r2_sym_ws"], golden["r2_sym_bias"]
+    z = np.zeros(257, np.int32)
+    out = np.zeros((37, 257), np.int8)
+    for izp in (0, 11, 0):  # third call re-uses the cached repacked weight
+        assert w8a8.qlinear_i8u8(x, w, ws, z, b, out, 0.037, izp, 0.9, -7) == 1
+        assert np.array_equal(out, golden[f"r2_sym_z{izp}_y"])
+    # the FMA half-way case of the reference's contract test (expects byte 0 everywhere)
+    xin = np.full((5, 18), 255, np.uint8)
+    xin[:, 17] = 40
+    ones = np.ones((17, 18), np.int8)
+    o2 = np.full((5, 17), 99, np.int8)
+    assert w8a8.qlinear_i8u8(xin, ones, np.full(17, 0.008, np.float32), np.zeros(17, np.int32),
+                             np.zeros(17, np.int32), o2, 0.015, 0, 0.03, -17) == 1
+    assert (o2 == 0).all()
+    w8a8.host_cache_clear()
+
+
+@pytest.mark.parametrize("tag,group", [("r1_5x257x7_g128", 128), ("r1_4x64x19_g64", 64)])
+def test_host_packed_linear_entry_declines_grouped_scales(torch, golden, tag, group):
+    """The golden R1 packages carry genuinely different group scales: declined (0),
+    output untouched, so the reference's own route keeps serving them."""
+    from volvoxai_b200 import w8a8
+    x = golden[tag + "_x"]
+    y = np.full((x.shape[0], golden[tag + "_words"].shape[0]), 4.5, np.float32)
+    rc = w8a8.packed_linear(x, golden[tag + "_words"], golden[tag + "_scales"], golden[tag + "_bias"], y,
+                            group_size=group)
+    if golden[tag + "_scales"].shape[1] > 1:
+        assert rc == 0 and (y == 4.5).all()
+    else:
+        assert rc == 1
+        want = golden[tag + "_y_c"]
+        assert np.array_equal(np.isnan(y), np.isnan(want))
+        assert np.array_equal(y[~np.isnan(want)].view(np.uint32), want[~np.isnan(want)].view(np.uint32))
+    w8a8.host_cache_clear()
+
+
+def test_host_packed_linear_entry(torch, oracle):
+    """Per-channel-constant group scales through the cuda_graph_llm_f32 drop-in, against the
+    oracle's grouped forward (itself pinned bit-for-bit to the reference's CPU forward)."""
+    from volvoxai_b200 import w8a8
+    c = wl.single_linear(rows=11, k=576, n=160, seed=21)
+    c["x"][2] = 0
+    c["x"][7, 5] = np.nan
+    words = wl.pack_w8_words(c["w"])
+    gs = wl.group_scales(c["ws"], 576, 128)
+    want = oracle.packed_linear_w8_grouped(c["x"], words, gs, 128, c["bias"])
+    y = np.full((11, 160), 12345.0, np.float32)
+    assert w8a8.packed_linear(c["x"], words, gs, c["bias"], y, group_size=128) == 1
+    assert "k1+" in w8a8.last_route()
+    assert np.array_equal(np.isnan(y), np.isnan(want))
+    assert rel_err(y, want) <= F32_TOL
+    # window = rows 3..5 only; everything else keeps its bytes
+    y2 = np.full((11, 160), 12345.0, np.float32)
+    assert w8a8.packed_linear(c["x"], words, gs, c["bias"], y2, group_size=128, first_unit=3 * 160, unit_count=3 * 160) == 1
+    assert np.array_equal(y2[3:6], y[3:6])
+    assert (y2[:3] == 12345.0).all() and (y2[6:] == 12345.0).all()
+    # single-row decode entry
+    y3 = np.zeros((1, 160), np.float32)
+    assert w8a8.packed_linear_decode(c["x"][:1], words, gs, c["bias"], y3) == 1
+    assert np.array_equal(y3[0], y[0])
+    w8a8.host_cache_clear()
+
+
+# ---- size-independent properties at benchmark sizes ---------------------------------------------
+
+def test_full_size_properties(torch, ctx, oracle):
+    """M2048 K4096 N14336 (too large for the scalar oracle in seconds): (a) a random sample of
+    512 outputs against exact NumPy int64 dots, (b) row permutation invariance - row r of a
+    permuted input equals the permuted row of the output, bit for bit, (c) checksum of the int32
+    accumulators equals sum_k (sum_m q[m,k]) * (sum_n w[n,k])."""
+    from volvoxai_b200 import w8a8
+    rows, k, n = 2048, 4096, 14336
+    c = wl.gemm_case(rows, k, n, seed=1, weights_fast=True)
+    weight = w8a8.Weight.from_i8(ctx, c["w"], c["ws"])
+    xd = dev(torch, c["x"])
+    acc, q, s = ctx.linear_acc_i32(weight, xd, want_q=True)
+    ctx.synchronize()
+    acc, q = acc.cpu().numpy(), q.cpu().numpy()
+    qo, so, _ = oracle.quantize_rows(c["x"][:64])
+    assert np.array_equal(q[:64], qo) and np.array_equal(s.cpu().numpy()[:64].view(np.uint32), so.view(np.uint32))
+    rng = np.random.default_rng(0)
+    for _ in range(512):
+        m, j = int(rng.integers(rows)), int(rng.integers(n))
+        assert acc[m, j] == int(q[m].astype(np.int64) @ c["w"][j].astype(np.int64))
+    colsum_q = q.astype(np.int64).sum(axis=0)
+    colsum_w = c["w"].astype(np.int64).sum(axis=0)
+    assert int(acc.astype(np.int64).sum()) == int((colsum_q * colsum_w).sum())
+    perm = rng.permutation(rows)
+    os_ = 0.05
+    y8 = ctx.linear_i8(weight, xd, os_, 0)
+    y8p = ctx.linear_i8(weight, dev(torch, c["x"][perm]), os_, 0)
+    ctx.synchronize()
+    assert torch.equal(y8p, y8[torch.from_numpy(perm).cuda()])
+    # spot-check E2 bytes of 8 rows against the oracle's requantizer on the exact accumulators
+    want = oracle.requant_rows(acc[:8], s.cpu().numpy()[:8], None, c["ws"], None, os_, 0)
+    assert np.array_equal(y8.cpu().numpy()[:8], want)
+    weight.close()

@@ -1,0 +1,102 @@
+"""ctypes binding of libvxb200.so (the C ABI declared in include/vxb200_w8a8.h).
+
+Loading fails loudly: there is no CPU or PyTorch fallback for any entry point.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(PKG, "libvxb200.so")
+
+DT_U8, DT_I8 = 5, 6
+OP_PACKED_LINEAR = 1036
+ROUTE_AUTO, ROUTE_GEMV, ROUTE_TCGEN05, ROUTE_SIMT = 0, 1, 2, 3
+
+# Every symbol include/vxb200_w8a8.h declares.
+EXPORTS = [
+    "vxb_abi_version", "vxb_last_error", "vxb_last_route", "vxb_launch_count",
+    "vxb_context_create", "vxb_context_destroy", "vxb_context_set_stream",
+    "vxb_context_synchronize", "vxb_weight_create_i8", "vxb_weight_create_w8_words",
+    "vxb_weight_destroy", "vxb_weight_d_in", "vxb_weight_d_out", "vxb_weight_device_bytes",
+    "vxb_quantize_rows", "vxb_linear_f32", "vxb_linear_i8", "vxb_linear_acc_i32",
+    "vxb_qlinear_device", "vxb_measure_i8_tensor_peak", "vxb_qlinear_i8u8",
+    "vxb_cuda_graph_llm_f32", "vxb_cuda_graph_packed_linear_decode_f32", "vxb_host_cache_clear",
+]
+
+
+class LLMOpArgs(C.Structure):
+    """Field-for-field mirror of the reference's VxLLMOpArgs
+    (native/src/kernels/llm_ops.h:38-53)."""
+    _fields_ = [(n, C.c_int32) for n in (
+        "kind", "batch", "sequence", "keys", "heads", "kv_heads", "key_dim", "value_dim",
+        "streams", "groups", "rate", "window", "top_k", "iterations",
+        "index_heads", "index_dim", "rotary_dim", "rotary_offset",
+        "normalize", "causal", "interleaved", "mask_mode")] + [
+        ("eps", C.c_float), ("hc_eps", C.c_float), ("scale", C.c_float),
+        ("x", C.c_void_p * 8), ("y", C.c_void_p * 3),
+        ("mask", C.c_void_p), ("positions", C.c_void_p),
+        ("x_elements", C.c_uint64 * 8), ("y_elements", C.c_uint64 * 3),
+        ("mask_elements", C.c_uint64), ("position_elements", C.c_uint64),
+        ("query_offset", C.c_int32), ("first_unit", C.c_uint64), ("unit_count", C.c_uint64)]
+
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m volvoxai_b200.build` "
+            "(nvcc, sm_100a). There is no fallback path.")
+    L = C.CDLL(LIB_PATH)
+    vp, u32, i32, f32 = C.c_void_p, C.c_uint32, C.c_int32, C.c_float
+    L.vxb_abi_version.restype = u32
+    L.vxb_last_error.restype = C.c_char_p
+    L.vxb_last_route.restype = C.c_char_p
+    L.vxb_launch_count.restype = C.c_uint64
+    L.vxb_context_create.argtypes = [C.c_int, vp, C.POINTER(vp)]
+    L.vxb_context_destroy.argtypes = [vp]
+    L.vxb_context_destroy.restype = None
+    L.vxb_context_set_stream.argtypes = [vp, vp]
+    L.vxb_context_synchronize.argtypes = [vp]
+    L.vxb_weight_create_i8.argtypes = [vp, vp, vp, vp, vp, u32, u32, C.POINTER(vp)]
+    L.vxb_weight_create_w8_words.argtypes = [vp, vp, vp, vp, u32, u32, u32, C.POINTER(vp)]
+    L.vxb_weight_destroy.argtypes = [vp]
+    L.vxb_weight_destroy.restype = None
+    L.vxb_weight_d_in.argtypes = [vp]
+    L.vxb_weight_d_in.restype = u32
+    L.vxb_weight_d_out.argtypes = [vp]
+    L.vxb_weight_d_out.restype = u32
+    L.vxb_weight_device_bytes.argtypes = [vp]
+    L.vxb_weight_device_bytes.restype = C.c_uint64
+    L.vxb_quantize_rows.argtypes = [vp, vp, u32, u32, vp, u32, vp, vp]
+    L.vxb_linear_f32.argtypes = [vp, vp, vp, u32, vp, u32, C.c_int]
+    L.vxb_linear_i8.argtypes = [vp, vp, vp, u32, f32, i32, vp, u32, C.c_int]
+    L.vxb_linear_acc_i32.argtypes = [vp, vp, vp, u32, vp, vp, vp, C.c_int]
+    L.vxb_qlinear_device.argtypes = [vp, vp, vp, u32, f32, i32, f32, i32, u32, u32, vp, u32, C.c_int]
+    L.vxb_measure_i8_tensor_peak.argtypes = [vp, u32, C.POINTER(C.c_double)]
+    L.vxb_qlinear_i8u8.argtypes = [vp, vp, vp, vp, vp, vp, u32, u32, u32, f32, i32, f32, i32,
+                                   u32, u32, u32]
+    L.vxb_cuda_graph_llm_f32.argtypes = [C.POINTER(LLMOpArgs)]
+    L.vxb_cuda_graph_packed_linear_decode_f32.argtypes = [vp, vp, vp, vp, vp, u32, u32, u32, u32]
+    L.vxb_host_cache_clear.restype = None
+    for name in EXPORTS:
+        fn = getattr(L, name)
+        if fn.restype is C.c_int and name.startswith("vxb_") and name not in (
+                "vxb_last_error", "vxb_last_route"):
+            fn.restype = C.c_int
+    _lib = L
+    return L
+
+
+def last_error() -> str:
+    return load().vxb_last_error().decode(errors="replace")
+
+
+def last_route() -> str:
+    return load().vxb_last_route().decode(errors="replace")

@@ -1,0 +1,615 @@
+// C ABI of the W8A8 linear route (declarations and contracts: include/vxb200_w8a8.h).
+// Host-side orchestration only: validation, scratch, route choice, tensor maps.
+#include "../../include/vxb200_w8a8.h"
+#include "common.cuh"
+
+#include <atomic>
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <unordered_map>
+#include <vector>
+
+using namespace vxb;
+
+namespace {
+
+thread_local char g_error[512] = "";
+thread_local char g_route[96] = "";
+std::atomic<uint64_t> g_launches{0};
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap; va_start(ap, fmt);
+    vsnprintf(g_error, sizeof g_error, fmt, ap);
+    va_end(ap);
+    return code;
+}
+#define CUDA_TRY(expr, code)                                                              \
+    do { cudaError_t e__ = (expr);                                                        \
+         if (e__ != cudaSuccess) return fail((code), "%s: %s", #expr, cudaGetErrorString(e__)); \
+    } while (0)
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+std::once_flag g_encode_once;
+
+EncodeTiledFn encode_fn() {
+    std::call_once(g_encode_once, [] {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            g_encode = (EncodeTiledFn)fn;
+    });
+    return g_encode;
+}
+
+// int8 matrix [rows, kpad] row-major -> 2-D tensor map with a (128 B x box_rows) box, 128B swizzle
+bool encode_i8_rows(CUtensorMap* map, const void* base, uint32_t rows, uint32_t kpad, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {kpad, rows};
+    cuuint64_t strides[1] = {kpad};
+    cuuint32_t box[2] = {kKAlign, box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+struct Buffer {
+    void* ptr = nullptr; size_t bytes = 0;
+    cudaError_t reserve(size_t need) {
+        if (need <= bytes) return cudaSuccess;
+        if (ptr) cudaFree(ptr);
+        ptr = nullptr; bytes = 0;
+        size_t grow = need + need / 4;
+        cudaError_t e = cudaMalloc(&ptr, grow);
+        if (e == cudaSuccess) bytes = grow;
+        return e;
+    }
+    void release() { if (ptr) cudaFree(ptr); ptr = nullptr; bytes = 0; }
+};
+
+}  // namespace
+
+struct VxbContext {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    int sm_count = 0;
+    Buffer q, row_scales, bias_eff, stage_in, stage_out;
+    int* status = nullptr;        // device word raised by bounded waits
+    int* status_host = nullptr;   // pinned mirror
+    bool tcgen05_ready = false;
+};
+
+struct VxbWeight {
+    int device = 0;
+    uint32_t d_in = 0, d_out = 0, kpad = 0;
+    int8_t* w = nullptr;       // [d_out, kpad]
+    float* ws = nullptr;       // [d_out]
+    float* bias_f32 = nullptr; // [d_out] or null
+    int32_t* bias_i32 = nullptr;
+    int32_t* wsum = nullptr;   // [d_out] sum of codes per channel
+    CUtensorMap tmap_b;        // box 256 rows
+    bool has_tmap = false;
+    uint64_t bytes = 0;
+};
+
+namespace {
+
+int ensure_device(const VxbContext* ctx) {
+    int cur = -1;
+    CUDA_TRY(cudaGetDevice(&cur), -1);
+    if (cur != ctx->device) CUDA_TRY(cudaSetDevice(ctx->device), -1);
+    return 1;
+}
+
+void count_launch(int n = 1) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+
+bool valid_scale(float v) { return std::isfinite(v) && v > 0.0f; }
+
+// Finish building a weight whose int8 rows already sit (unpadded) in `staging` on the device.
+int finish_weight(VxbContext* ctx, VxbWeight* w, const uint8_t* staging, uint32_t src_ld,
+                  uint32_t xor_mask, const float* ws_host, const float* bias_f32,
+                  const int32_t* bias_i32) {
+    const uint32_t n = w->d_out, k = w->d_in;
+    w->kpad = round_up(k, kKAlign);
+    CUDA_TRY(cudaMalloc(&w->w, (size_t)n * w->kpad), 0);
+    CUDA_TRY(cudaMalloc(&w->ws, (size_t)n * 4), 0);
+    CUDA_TRY(cudaMalloc(&w->wsum, (size_t)n * 4), 0);
+    w->bytes = (uint64_t)n * w->kpad + 8ull * n;
+    CUDA_TRY(launch_repack_weight(staging, src_ld, n, k, xor_mask, w->w, w->kpad, w->wsum, ctx->stream), -1);
+    count_launch();
+    CUDA_TRY(cudaMemcpyAsync(w->ws, ws_host, (size_t)n * 4, cudaMemcpyHostToDevice, ctx->stream), -1);
+    if (bias_f32) {
+        CUDA_TRY(cudaMalloc(&w->bias_f32, (size_t)n * 4), 0);
+        CUDA_TRY(cudaMemcpyAsync(w->bias_f32, bias_f32, (size_t)n * 4, cudaMemcpyHostToDevice, ctx->stream), -1);
+        w->bytes += 4ull * n;
+    }
+    if (bias_i32) {
+        CUDA_TRY(cudaMalloc(&w->bias_i32, (size_t)n * 4), 0);
+        CUDA_TRY(cudaMemcpyAsync(w->bias_i32, bias_i32, (size_t)n * 4, cudaMemcpyHostToDevice, ctx->stream), -1);
+        w->bytes += 4ull * n;
+    }
+    w->has_tmap = encode_i8_rows(&w->tmap_b, w->w, n, w->kpad, 256);
+    CUDA_TRY(cudaStreamSynchronize(ctx->stream), -1);
+    return 1;
+}
+
+struct Plan {
+    int route;
+    const char* name;
+};
+
+Plan choose_route(const VxbContext* ctx, const VxbWeight* w, uint32_t rows, int requested) {
+    if (requested == VXB_ROUTE_GEMV) return {VXB_ROUTE_GEMV, "gemv-dp4a"};
+    if (requested == VXB_ROUTE_SIMT) return {VXB_ROUTE_SIMT, "simt-dp4a"};
+    if (requested == VXB_ROUTE_TCGEN05) return {VXB_ROUTE_TCGEN05, "tcgen05-i8"};
+    (void)ctx; (void)w;
+    if (rows <= 32) return {VXB_ROUTE_GEMV, "gemv-dp4a"};
+    return {VXB_ROUTE_TCGEN05, "tcgen05-i8"};
+}
+
+// int32 GEMM + epilogue over already-quantized activations q [rows, kpad].
+int run_gemm(VxbContext* ctx, const VxbWeight* w, const int8_t* q, uint32_t rows,
+             const EpilogueParams& epi, int requested, const char* prefix) {
+    const Plan plan = choose_route(ctx, w, rows, requested);
+    if (plan.route == VXB_ROUTE_GEMV) {
+        if (rows > 32) return fail(0, "gemv route needs rows <= 32 (got %u)", rows);
+        CUDA_TRY(launch_gemv(q, rows, w->w, w->d_out, w->kpad, epi, ctx->sm_count, ctx->stream), -1);
+    } else if (plan.route == VXB_ROUTE_SIMT) {
+        CUDA_TRY(launch_gemm_simt(q, rows, w->w, w->d_out, w->kpad, epi, ctx->stream), -1);
+    } else {
+        if (!w->has_tmap) return fail(0, "no tensor map for this weight (driver entry point missing)");
+        if (!ctx->tcgen05_ready) {
+            CUDA_TRY(gemm_tcgen05_prepare(), 0);
+            ctx->tcgen05_ready = true;
+        }
+        GemmTcgen05Args a;
+        if (!encode_i8_rows(&a.tmap_a, q, rows, w->kpad, 128)) return fail(0, "cuTensorMapEncodeTiled failed for activations");
+        a.tmap_b = w->tmap_b;
+        a.rows = rows; a.n = w->d_out; a.kpad = w->kpad; a.epi = epi; a.status = ctx->status;
+        CUDA_TRY(launch_gemm_tcgen05(a, ctx->sm_count, ctx->stream), -1);
+    }
+    count_launch();
+    const char* tail = epi.mode == kEpiAcc ? "acc" : epi.mode == kEpiF32 ? "e1" : "e2";
+    snprintf(g_route, sizeof g_route, "%s%s+%s", prefix, plan.name, tail);
+    return 1;
+}
+
+int check_common(const VxbContext* ctx, const VxbWeight* w, const void* x, const void* y, uint32_t ldy) {
+    if (!ctx || !w || !x || !y) return fail(0, "null argument");
+    if (w->device != ctx->device) return fail(0, "weight lives on device %d, context on %d", w->device, ctx->device);
+    if (ldy < w->d_out) return fail(0, "output row stride %u < d_out %u", ldy, w->d_out);
+    return 1;
+}
+
+int quantize_into_scratch(VxbContext* ctx, const VxbWeight* w, const float* x, uint32_t rows) {
+    CUDA_TRY(ctx->q.reserve((size_t)rows * w->kpad), 0);
+    CUDA_TRY(ctx->row_scales.reserve((size_t)rows * 4), 0);
+    CUDA_TRY(launch_quantize_rows(x, rows, w->d_in, (int8_t*)ctx->q.ptr, w->kpad,
+                                  (float*)ctx->row_scales.ptr, nullptr, ctx->stream), -1);
+    count_launch();
+    return 1;
+}
+
+}  // namespace
+
+extern "C" {
+
+uint32_t vxb_abi_version(void) { return VXB_ABI_VERSION; }
+const char* vxb_last_error(void) { return g_error; }
+const char* vxb_last_route(void) { return g_route; }
+uint64_t vxb_launch_count(void) { return g_launches.load(); }
+
+int vxb_context_create(int device, void* stream, VxbContext** out) {
+    if (!out) return fail(0, "null out");
+    *out = nullptr;
+    int count = 0;
+    CUDA_TRY(cudaGetDeviceCount(&count), 0);
+    if (device < 0 || device >= count) return fail(0, "device %d out of range (%d present)", device, count);
+    CUDA_TRY(cudaSetDevice(device), 0);
+    cudaDeviceProp prop;
+    CUDA_TRY(cudaGetDeviceProperties(&prop, device), 0);
+    if (prop.major != 10) return fail(0, "device %d is sm_%d%d; this library is sm_100a only", device, prop.major, prop.minor);
+    VxbContext* ctx = new VxbContext();
+    ctx->device = device; ctx->stream = (cudaStream_t)stream; ctx->sm_count = prop.multiProcessorCount;
+    if (cudaMalloc(&ctx->status, sizeof(int)) != cudaSuccess ||
+        cudaMemset(ctx->status, 0, sizeof(int)) != cudaSuccess ||
+        cudaMallocHost(&ctx->status_host, sizeof(int)) != cudaSuccess) {
+        delete ctx;
+        return fail(0, "context allocation failed: %s", cudaGetErrorString(cudaGetLastError()));
+    }
+    *out = ctx;
+    return 1;
+}
+
+void vxb_context_destroy(VxbContext* ctx) {
+    if (!ctx) return;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    ctx->q.release(); ctx->row_scales.release(); ctx->bias_eff.release();
+    ctx->stage_in.release(); ctx->stage_out.release();
+    if (ctx->status) cudaFree(ctx->status);
+    if (ctx->status_host) cudaFreeHost(ctx->status_host);
+    delete ctx;
+}
+
+int vxb_context_set_stream(VxbContext* ctx, void* stream) {
+    if (!ctx) return fail(0, "null context");
+    ctx->stream = (cudaStream_t)stream;
+    return 1;
+}
+
+int vxb_context_synchronize(VxbContext* ctx) {
+    if (!ctx) return fail(0, "null context");
+    if (ensure_device(ctx) != 1) return -1;
+    CUDA_TRY(cudaMemcpyAsync(ctx->status_host, ctx->status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream), -1);
+    CUDA_TRY(cudaStreamSynchronize(ctx->stream), -1);
+    if (*ctx->status_host != 0) {
+        const int code = *ctx->status_host;
+        cudaMemsetAsync(ctx->status, 0, sizeof(int), ctx->stream);
+        return fail(-1, "a bounded device wait expired (status %d); results of this batch are invalid", code);
+    }
+    return 1;
+}
+
+int vxb_weight_create_i8(VxbContext* ctx, const int8_t* weight, const float* weight_scales,
+                         const float* bias_f32, const int32_t* bias_i32, uint32_t d_out,
+                         uint32_t d_in, VxbWeight** out) {
+    if (!ctx || !weight || !weight_scales || !out) return fail(0, "null argument");
+    *out = nullptr;
+    if (!d_out || !d_in) return fail(0, "empty weight");
+    // K*127*128 must stay inside int32 (the reference's overflow proof,
+    // native/src/kernels/packed_quant_gemm.c:741-755)
+    if ((uint64_t)d_in * 127u * 128u > 2147483647ull) return fail(0, "d_in %u can overflow the int32 accumulator", d_in);
+    for (uint32_t i = 0; i < d_out; i++)
+        if (!valid_scale(weight_scales[i])) return fail(0, "weight scale %u is not positive and finite", i);
+    if (ensure_device(ctx) != 1) return -1;
+    VxbWeight* w = new VxbWeight();
+    w->device = ctx->device; w->d_in = d_in; w->d_out = d_out;
+    Buffer staging;
+    int rc;
+    if (staging.reserve((size_t)d_out * d_in) != cudaSuccess) { rc = fail(0, "staging allocation failed"); }
+    else if (cudaMemcpyAsync(staging.ptr, weight, (size_t)d_out * d_in, cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess) {
+        rc = fail(-1, "weight upload failed");
+    } else {
+        rc = finish_weight(ctx, w, (const uint8_t*)staging.ptr, d_in, 0u, weight_scales, bias_f32, bias_i32);
+    }
+    cudaStreamSynchronize(ctx->stream);
+    staging.release();
+    if (rc != 1) { vxb_weight_destroy(w); return rc; }
+    *out = w;
+    return 1;
+}
+
+int vxb_weight_create_w8_words(VxbContext* ctx, const int32_t* words, const float* group_scales,
+                               const float* bias_f32, uint32_t d_out, uint32_t d_in,
+                               uint32_t group_size, VxbWeight** out) {
+    if (!ctx || !words || !group_scales || !out) return fail(0, "null argument");
+    *out = nullptr;
+    if (!d_out || !d_in) return fail(0, "empty weight");
+    if (group_size != 32 && group_size != 64 && group_size != 128 && group_size != 256)
+        return fail(0, "group size %u is not 32/64/128/256", group_size);
+    if ((uint64_t)d_in * 127u * 128u > 2147483647ull) return fail(0, "d_in %u can overflow the int32 accumulator", d_in);
+    const uint32_t groups = (d_in + group_size - 1) / group_size, row_words = (d_in + 3) / 4;
+    std::vector<float> ws(d_out);
+    for (uint32_t n = 0; n < d_out; n++) {
+        const float s = group_scales[(size_t)n * groups];
+        if (!valid_scale(s)) return fail(0, "group scale of channel %u is not positive and finite", n);
+        for (uint32_t g = 1; g < groups; g++)
+            if (memcmp(&group_scales[(size_t)n * groups + g], &s, 4) != 0)
+                return fail(0, "channel %u has differing group scales; only per-channel-constant scales are admitted", n);
+        ws[n] = s;
+        // canonical padding: unused bytes of the final word hold the encoded zero 0x80
+        const uint8_t* bytes = (const uint8_t*)(words + (size_t)n * row_words);
+        for (uint32_t j = d_in; j < row_words * 4; j++)
+            if (bytes[j] != 0x80u) return fail(0, "channel %u: padding byte %u is not the encoded zero", n, j);
+    }
+    if (ensure_device(ctx) != 1) return -1;
+    VxbWeight* w = new VxbWeight();
+    w->device = ctx->device; w->d_in = d_in; w->d_out = d_out;
+    Buffer staging;
+    int rc;
+    const size_t src_bytes = (size_t)d_out * row_words * 4;
+    if (staging.reserve(src_bytes) != cudaSuccess) rc = fail(0, "staging allocation failed");
+    else if (cudaMemcpyAsync(staging.ptr, words, src_bytes, cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess)
+        rc = fail(-1, "weight upload failed");
+    else rc = finish_weight(ctx, w, (const uint8_t*)staging.ptr, row_words * 4, 0x80u, ws.data(), bias_f32, nullptr);
+    cudaStreamSynchronize(ctx->stream);
+    staging.release();
+    if (rc != 1) { vxb_weight_destroy(w); return rc; }
+    *out = w;
+    return 1;
+}
+
+void vxb_weight_destroy(VxbWeight* w) {
+    if (!w) return;
+    cudaSetDevice(w->device);
+    if (w->w) cudaFree(w->w);
+    if (w->ws) cudaFree(w->ws);
+    if (w->bias_f32) cudaFree(w->bias_f32);
+    if (w->bias_i32) cudaFree(w->bias_i32);
+    if (w->wsum) cudaFree(w->wsum);
+    delete w;
+}
+uint32_t vxb_weight_d_in(const VxbWeight* w) { return w ? w->d_in : 0; }
+uint32_t vxb_weight_d_out(const VxbWeight* w) { return w ? w->d_out : 0; }
+uint64_t vxb_weight_device_bytes(const VxbWeight* w) { return w ? w->bytes : 0; }
+
+int vxb_quantize_rows(VxbContext* ctx, const float* x, uint32_t rows, uint32_t k, int8_t* q,
+                      uint32_t ldq, float* row_scales, int32_t* valid) {
+    if (!ctx || !x || !q || !row_scales) return fail(0, "null argument");
+    if (!k || ldq < k) return fail(0, "bad widths k=%u ldq=%u", k, ldq);
+    if (!rows) return 1;
+    if (ensure_device(ctx) != 1) return -1;
+    CUDA_TRY(launch_quantize_rows(x, rows, k, q, ldq, row_scales, valid, ctx->stream), -1);
+    count_launch();
+    snprintf(g_route, sizeof g_route, "k1");
+    return 1;
+}
+
+int vxb_linear_f32(VxbContext* ctx, const VxbWeight* w, const float* x, uint32_t rows, float* y,
+                   uint32_t ldy, int route) {
+    int rc = check_common(ctx, w, x, y, ldy);
+    if (rc != 1) return rc;
+    if (!rows) return 1;
+    if (ensure_device(ctx) != 1) return -1;
+    if ((rc = quantize_into_scratch(ctx, w, x, rows)) != 1) return rc;
+    EpilogueParams epi{};
+    epi.mode = kEpiF32; epi.row_scales = (const float*)ctx->row_scales.ptr; epi.ws = w->ws;
+    epi.bias_f32 = w->bias_f32; epi.out = y; epi.ld = ldy;
+    return run_gemm(ctx, w, (const int8_t*)ctx->q.ptr, rows, epi, route, "k1+");
+}
+
+int vxb_linear_i8(VxbContext* ctx, const VxbWeight* w, const float* x, uint32_t rows,
+                  float out_scale, int32_t out_zero, int8_t* y, uint32_t ldy, int route) {
+    int rc = check_common(ctx, w, x, y, ldy);
+    if (rc != 1) return rc;
+    if (!valid_scale(out_scale)) return fail(0, "output scale is not positive and finite");
+    if (out_zero < -128 || out_zero > 127) return fail(0, "output zero point %d outside int8", out_zero);
+    if (!rows) return 1;
+    if (ensure_device(ctx) != 1) return -1;
+    if ((rc = quantize_into_scratch(ctx, w, x, rows)) != 1) return rc;
+    EpilogueParams epi{};
+    epi.mode = kEpiI8; epi.row_scales = (const float*)ctx->row_scales.ptr; epi.ws = w->ws;
+    epi.bias_i32 = w->bias_i32; epi.out_scale = out_scale; epi.out_zero = out_zero;
+    epi.out_lo = -128; epi.out_hi = 127; epi.out = y; epi.ld = ldy;
+    return run_gemm(ctx, w, (const int8_t*)ctx->q.ptr, rows, epi, route, "k1+");
+}
+
+int vxb_linear_acc_i32(VxbContext* ctx, const VxbWeight* w, const float* x, uint32_t rows,
+                       int32_t* acc, int8_t* q_out, float* scales_out, int route) {
+    int rc = check_common(ctx, w, x, acc, w ? w->d_out : 0);
+    if (rc != 1) return rc;
+    if (!rows) return 1;
+    if (ensure_device(ctx) != 1) return -1;
+    if ((rc = quantize_into_scratch(ctx, w, x, rows)) != 1) return rc;
+    if (q_out)
+        CUDA_TRY(cudaMemcpy2DAsync(q_out, w->d_in, ctx->q.ptr, w->kpad, w->d_in, rows,
+                                   cudaMemcpyDeviceToDevice, ctx->stream), -1);
+    if (scales_out)
+        CUDA_TRY(cudaMemcpyAsync(scales_out, ctx->row_scales.ptr, (size_t)rows * 4,
+                                 cudaMemcpyDeviceToDevice, ctx->stream), -1);
+    EpilogueParams epi{};
+    epi.mode = kEpiAcc; epi.out = acc; epi.ld = w->d_out;
+    return run_gemm(ctx, w, (const int8_t*)ctx->q.ptr, rows, epi, route, "k1+");
+}
+
+int vxb_qlinear_device(VxbContext* ctx, const VxbWeight* w, const void* input, uint32_t rows,
+                       float input_scale, int32_t input_zero_point, float output_scale,
+                       int32_t output_zero_point, uint32_t input_dtype, uint32_t output_dtype,
+                       void* output, uint32_t ldy, int route) {
+    int rc = check_common(ctx, w, input, output, ldy);
+    if (rc != 1) return rc;
+    const bool in_u8 = input_dtype == VXB_DTYPE_U8, out_u8 = output_dtype == VXB_DTYPE_U8;
+    if ((!in_u8 && input_dtype != VXB_DTYPE_I8) || (!out_u8 && output_dtype != VXB_DTYPE_I8))
+        return fail(0, "activation dtypes must be I8 or U8");
+    if (!valid_scale(input_scale) || !valid_scale(output_scale)) return fail(0, "scales must be positive and finite");
+    if (input_zero_point < (in_u8 ? 0 : -128) || input_zero_point > (in_u8 ? 255 : 127) ||
+        output_zero_point < (out_u8 ? 0 : -128) || output_zero_point > (out_u8 ? 255 : 127))
+        return fail(0, "zero point outside its dtype");
+    if (!rows) return 1;
+    if (ensure_device(ctx) != 1) return -1;
+    // activations into the padded signed layout (U8 -> subtract 128 from codes and zero point)
+    CUDA_TRY(ctx->q.reserve((size_t)rows * w->kpad), 0);
+    CUDA_TRY(ctx->row_scales.reserve((size_t)rows * 4), 0);
+    CUDA_TRY(ctx->bias_eff.reserve((size_t)w->d_out * 4), 0);
+    CUDA_TRY(launch_copy_bytes_padded((const uint8_t*)input, rows, w->d_in, (uint8_t*)ctx->q.ptr, w->kpad,
+                                      in_u8 ? 0x80u : 0u, ctx->stream), -1);
+    CUDA_TRY(launch_fill_f32((float*)ctx->row_scales.ptr, rows, input_scale, ctx->stream), -1);
+    const int32_t signed_zero = in_u8 ? input_zero_point - 128 : input_zero_point;
+    CUDA_TRY(launch_fold_zero_point(w->bias_i32, w->wsum, signed_zero, (int32_t*)ctx->bias_eff.ptr,
+                                    w->d_out, ctx->stream), -1);
+    count_launch(3);
+    EpilogueParams epi{};
+    epi.mode = kEpiI8; epi.row_scales = (const float*)ctx->row_scales.ptr; epi.ws = w->ws;
+    epi.bias_i32 = (const int32_t*)ctx->bias_eff.ptr; epi.out_scale = output_scale;
+    epi.out_zero = output_zero_point; epi.out_lo = out_u8 ? 0 : -128; epi.out_hi = out_u8 ? 255 : 127;
+    epi.out = output; epi.ld = ldy;
+    return run_gemm(ctx, w, (const int8_t*)ctx->q.ptr, rows, epi, route, "static+");
+}
+
+int vxb_measure_i8_tensor_peak(VxbContext* ctx, uint32_t iters, double* tops) {
+    if (!ctx || !tops || !iters) return fail(0, "bad argument");
+    if (ensure_device(ctx) != 1) return -1;
+    if (!ctx->tcgen05_ready) { CUDA_TRY(gemm_tcgen05_prepare(), 0); ctx->tcgen05_ready = true; }
+    long long* cycles = nullptr;
+    CUDA_TRY(cudaMalloc(&cycles, sizeof(long long) * ctx->sm_count), 0);
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0); cudaEventCreate(&e1);
+    cudaError_t err = launch_i8_peak_probe(4, cycles, ctx->status, ctx->sm_count, ctx->stream);  // warm-up
+    cudaEventRecord(e0, ctx->stream);
+    if (err == cudaSuccess) err = launch_i8_peak_probe(iters, cycles, ctx->status, ctx->sm_count, ctx->stream);
+    cudaEventRecord(e1, ctx->stream);
+    count_launch(2);
+    if (err == cudaSuccess) err = cudaEventSynchronize(e1);
+    float ms = 0.0f;
+    cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0); cudaEventDestroy(e1);
+    cudaFree(cycles);
+    if (err != cudaSuccess) return fail(-1, "peak probe failed: %s", cudaGetErrorString(err));
+    const double ops = (double)ctx->sm_count * iters * 256.0 * 2.0 * 128.0 * 256.0 * 32.0;
+    *tops = ops / (ms * 1e-3) / 1e12;
+    return vxb_context_synchronize(ctx) == 1 ? 1 : -1;
+}
+
+}  // extern "C"
+
+// ---- reference-facing host-pointer entries ------------------------------------------
+namespace {
+
+struct HostKey {
+    const void* weight; const void* scales; const void* bias; uint32_t d_in, d_out, kind;
+    bool operator==(const HostKey& o) const {
+        return weight == o.weight && scales == o.scales && bias == o.bias && d_in == o.d_in &&
+               d_out == o.d_out && kind == o.kind;
+    }
+};
+struct HostKeyHash {
+    size_t operator()(const HostKey& k) const {
+        size_t h = (size_t)k.weight * 1315423911u;
+        h ^= (size_t)k.scales + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2);
+        h ^= (size_t)k.bias + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2);
+        h ^= ((size_t)k.d_in << 32) ^ k.d_out ^ ((size_t)k.kind << 60);
+        return h;
+    }
+};
+
+std::mutex g_host_mutex;
+VxbContext* g_host_ctx = nullptr;
+std::unordered_map<HostKey, VxbWeight*, HostKeyHash> g_host_weights;
+
+// One process-wide context on the device named by VOLVOXAI_CUDA_DEVICE (the
+// reference's own selector), default 0. Calls are serialised by g_host_mutex,
+// matching the reference's single-stream synchronous backend.
+int host_context(VxbContext** out) {
+    if (!g_host_ctx) {
+        int device = 0;
+        if (const char* env = getenv("VOLVOXAI_CUDA_DEVICE")) device = atoi(env);
+        int rc = vxb_context_create(device, nullptr, &g_host_ctx);
+        if (rc != 1) return rc;
+    }
+    *out = g_host_ctx;
+    return 1;
+}
+
+bool overlap(const void* a, size_t an, const void* b, size_t bn) {
+    if (!an || !bn) return false;
+    const uintptr_t x = (uintptr_t)a, y = (uintptr_t)b;
+    return x < y + bn && y < x + an;
+}
+
+}  // namespace
+
+extern "C" {
+
+int vxb_qlinear_i8u8(const void* input, const void* weight, const float* weight_scales,
+                     const int32_t* weight_zero_points, const int32_t* bias, void* output,
+                     uint32_t rows, uint32_t d_in, uint32_t d_out, float input_scale,
+                     int32_t input_zero_point, float output_scale, int32_t output_zero_point,
+                     uint32_t input_dtype, uint32_t weight_dtype, uint32_t output_dtype) {
+    if (!input || !weight || !weight_scales || !weight_zero_points || !bias || !output)
+        return fail(0, "null argument");
+    if (!rows || !d_in || !d_out) return fail(0, "empty shape");
+    if (weight_dtype != VXB_DTYPE_I8) return fail(0, "only I8 weights are admitted");
+    for (uint32_t i = 0; i < d_out; i++)
+        if (weight_zero_points[i] != 0) return fail(0, "non-zero weight zero point at channel %u", i);
+    const size_t in_bytes = (size_t)rows * d_in, out_bytes = (size_t)rows * d_out;
+    if (overlap(output, out_bytes, input, in_bytes) || overlap(output, out_bytes, weight, (size_t)d_out * d_in) ||
+        overlap(output, out_bytes, bias, (size_t)d_out * 4) || overlap(output, out_bytes, weight_scales, (size_t)d_out * 4))
+        return fail(0, "output overlaps an input");
+    std::lock_guard<std::mutex> lock(g_host_mutex);
+    VxbContext* ctx = nullptr;
+    int rc = host_context(&ctx);
+    if (rc != 1) return rc;
+    const HostKey key{weight, weight_scales, bias, d_in, d_out, 1u};
+    VxbWeight* w = nullptr;
+    auto it = g_host_weights.find(key);
+    if (it != g_host_weights.end()) w = it->second;
+    else {
+        rc = vxb_weight_create_i8(ctx, (const int8_t*)weight, weight_scales, nullptr, bias, d_out, d_in, &w);
+        if (rc != 1) return rc;
+        g_host_weights.emplace(key, w);
+    }
+    CUDA_TRY(ctx->stage_in.reserve(in_bytes), 0);
+    CUDA_TRY(ctx->stage_out.reserve(out_bytes), 0);
+    CUDA_TRY(cudaMemcpyAsync(ctx->stage_in.ptr, input, in_bytes, cudaMemcpyHostToDevice, ctx->stream), -1);
+    rc = vxb_qlinear_device(ctx, w, ctx->stage_in.ptr, rows, input_scale, input_zero_point, output_scale,
+                            output_zero_point, input_dtype, output_dtype, ctx->stage_out.ptr, d_out,
+                            VXB_ROUTE_AUTO);
+    if (rc != 1) return rc;
+    CUDA_TRY(cudaMemcpyAsync(output, ctx->stage_out.ptr, out_bytes, cudaMemcpyDeviceToHost, ctx->stream), -1);
+    return vxb_context_synchronize(ctx) == 1 ? 1 : -1;
+}
+
+int vxb_cuda_graph_llm_f32(const VxbLLMOpArgs* a) {
+    if (!a) return fail(0, "null descriptor");
+    if (a->kind != VXB_OP_PACKED_LINEAR) return fail(0, "operator %d is not PackedLinear", a->kind);
+    if (a->groups != 8 || a->normalize != 8) return fail(0, "only weight bits 8 / activation bits 8 are admitted");
+    if (a->key_dim <= 0 || a->value_dim <= 0 || a->batch <= 0 || a->sequence <= 0) return fail(0, "bad shape");
+    if (!a->x[0] || !a->x[1] || !a->x[2] || !a->y[0]) return fail(0, "null tensor");
+    const uint32_t k = (uint32_t)a->key_dim, n = (uint32_t)a->value_dim;
+    const uint64_t rows64 = (uint64_t)a->batch * (uint64_t)a->sequence;
+    if (rows64 > 0xffffffffull) return fail(0, "too many rows");
+    // window: whole rows only (the generation path asks for exactly the last row)
+    uint64_t first = a->first_unit, units = a->unit_count ? a->unit_count : rows64 * n;
+    if (first > rows64 * n || units > rows64 * n - first) return fail(0, "window outside the output");
+    if (first % n != 0 || units % n != 0) return fail(0, "ragged output windows are not admitted");
+    if (a->first_unit != 0 && a->unit_count == 0) return fail(0, "first_unit without unit_count");
+    const uint32_t row0 = (uint32_t)(first / n), rows = (uint32_t)(units / n);
+    if (!rows) return 1;
+
+    std::lock_guard<std::mutex> lock(g_host_mutex);
+    VxbContext* ctx = nullptr;
+    int rc = host_context(&ctx);
+    if (rc != 1) return rc;
+    const HostKey key{a->x[1], a->x[2], a->x[3], k, n, 2u};
+    VxbWeight* w = nullptr;
+    auto it = g_host_weights.find(key);
+    if (it != g_host_weights.end()) w = it->second;
+    else {
+        rc = vxb_weight_create_w8_words(ctx, (const int32_t*)a->x[1], a->x[2], a->x[3], n, k,
+                                        (uint32_t)a->rate, &w);
+        if (rc != 1) return rc;
+        g_host_weights.emplace(key, w);
+    }
+    const size_t in_bytes = (size_t)rows * k * 4, out_bytes = (size_t)rows * n * 4;
+    CUDA_TRY(ctx->stage_in.reserve(in_bytes), 0);
+    CUDA_TRY(ctx->stage_out.reserve(out_bytes), 0);
+    CUDA_TRY(cudaMemcpyAsync(ctx->stage_in.ptr, a->x[0] + (size_t)row0 * k, in_bytes, cudaMemcpyHostToDevice, ctx->stream), -1);
+    rc = vxb_linear_f32(ctx, w, (const float*)ctx->stage_in.ptr, rows, (float*)ctx->stage_out.ptr, n, VXB_ROUTE_AUTO);
+    if (rc != 1) return rc == 0 ? 0 : -1;
+    CUDA_TRY(cudaMemcpyAsync(a->y[0] + (size_t)row0 * n, ctx->stage_out.ptr, out_bytes, cudaMemcpyDeviceToHost, ctx->stream), -1);
+    return vxb_context_synchronize(ctx) == 1 ? 1 : -1;
+}
+
+int vxb_cuda_graph_packed_linear_decode_f32(const float* input, const int32_t* packed_weights,
+                                            const float* weight_scales, const float* bias,
+                                            float* output, uint32_t input_width,
+                                            uint32_t output_width, uint32_t weight_bits,
+                                            uint32_t activation_bits) {
+    VxbLLMOpArgs a;
+    memset(&a, 0, sizeof a);
+    a.kind = VXB_OP_PACKED_LINEAR; a.batch = 1; a.sequence = 1;
+    a.key_dim = (int32_t)input_width; a.value_dim = (int32_t)output_width;
+    a.groups = (int32_t)weight_bits; a.normalize = (int32_t)activation_bits; a.rate = 128;
+    a.x[0] = input; a.x[1] = (const float*)packed_weights; a.x[2] = weight_scales; a.x[3] = bias;
+    a.y[0] = output;
+    return vxb_cuda_graph_llm_f32(&a);
+}
+
+void vxb_host_cache_clear(void) {
+    std::lock_guard<std::mutex> lock(g_host_mutex);
+    for (auto& kv : g_host_weights) vxb_weight_destroy(kv.second);
+    g_host_weights.clear();
+    if (g_host_ctx) { vxb_context_destroy(g_host_ctx); g_host_ctx = nullptr; }
+}
+
+}  // extern "C"

@@ -1,0 +1,123 @@
+// Shared declarations for the W8A8 kernels (sm_100a only).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda.h>
+#include <stdint.h>
+
+namespace vxb {
+
+// Weight rows and quantized activation rows are padded to this many bytes
+// (one 128-byte TMA swizzle span) and zero-filled, so every kernel walks K in
+// whole 128-byte steps without a tail.
+constexpr uint32_t kKAlign = 128;
+
+__host__ __device__ inline uint32_t round_up(uint32_t v, uint32_t m) { return (v + m - 1) / m * m; }
+
+// Epilogue selection shared by all GEMM-shaped kernels.
+enum Epilogue : int { kEpiAcc = 0, kEpiF32 = 1, kEpiI8 = 2 };
+
+struct EpilogueParams {
+    int mode;                 // Epilogue
+    const float* row_scales;  // [rows]   activation scale per token (NaN = invalid row)
+    const float* ws;          // [N]      weight scale per output channel
+    const float* bias_f32;    // [N] or nullptr (E1)
+    const int32_t* bias_i32;  // [N] or nullptr (E2, accumulator domain, zero-point folded)
+    float out_scale;          // E2
+    int32_t out_zero;         // E2
+    int32_t out_lo, out_hi;   // E2 saturation range (I8: -128..127, U8: 0..255)
+    void* out;                // int32 / float / int8 [rows, ld]
+    uint32_t ld;              // output row stride in elements
+};
+
+// ---- epilogue arithmetic (every operation separately rounded; no FMA) ----
+
+// E1: y = f32(f32(acc) * f32(as*ws)) + bias
+__device__ __forceinline__ float epi_f32(int32_t acc, float as, float ws, float bias) {
+    const float combined = __fmul_rn(as, ws);
+    const float product = __fmul_rn(__int2float_rn(acc), combined);
+    return __fadd_rn(product, bias);
+}
+
+// E2: multiplier association f32(f32(as*ws)/os) is part of the contract.
+__device__ __forceinline__ int32_t epi_i8(int32_t acc, float as, float ws, float out_scale,
+                                          int32_t out_zero, int32_t lo, int32_t hi) {
+    const float product = __fmul_rn(as, ws);
+    const float mult = __fdiv_rn(product, out_scale);
+    const float scaled = __fmul_rn(__int2float_rn(acc), mult);
+    const float moved = __fadd_rn(scaled, __int2float_rn(out_zero));
+    if (moved != moved) return out_zero;
+    if (moved <= (float)lo) return lo;
+    if (moved >= (float)hi) return hi;
+    return __float2int_rn(moved);
+}
+
+// One output element through the selected epilogue (scalar path).
+__device__ __forceinline__ void epi_store(const EpilogueParams& p, uint32_t row, uint32_t col,
+                                          int32_t acc) {
+    const size_t at = (size_t)row * p.ld + col;
+    if (p.mode == kEpiAcc) {
+        ((int32_t*)p.out)[at] = acc;
+    } else if (p.mode == kEpiF32) {
+        ((float*)p.out)[at] = epi_f32(acc, p.row_scales[row], p.ws[col],
+                                      p.bias_f32 ? p.bias_f32[col] : 0.0f);
+    } else {
+        const int32_t a = acc + (p.bias_i32 ? p.bias_i32[col] : 0);
+        ((int8_t*)p.out)[at] = (int8_t)epi_i8(a, p.row_scales[row], p.ws[col], p.out_scale,
+                                              p.out_zero, p.out_lo, p.out_hi);
+    }
+}
+
+// ---- launchers implemented in the .cu files -------------------------------
+
+// K1: per-token absmax + quantize. q rows have stride ldq (multiple of 16 when
+// the vector path is to be used); bytes [k, ldq) are zeroed.
+cudaError_t launch_quantize_rows(const float* x, uint32_t rows, uint32_t k, int8_t* q,
+                                 uint32_t ldq, float* row_scales, int32_t* valid,
+                                 cudaStream_t stream);
+
+// Fill a float array with one value (static-activation QLinear row scales).
+cudaError_t launch_fill_f32(float* dst, uint32_t count, float value, cudaStream_t stream);
+
+// bias_eff[n] = bias[n] - input_zero * wsum[n]  (activation zero-point folding)
+cudaError_t launch_fold_zero_point(const int32_t* bias, const int32_t* wsum, int32_t input_zero,
+                                   int32_t* out, uint32_t n, cudaStream_t stream);
+
+// Convert U8 activations to the signed domain (x ^ 0x80) with row padding.
+cudaError_t launch_copy_bytes_padded(const uint8_t* src, uint32_t rows, uint32_t k, uint8_t* dst,
+                                     uint32_t ld, uint32_t xor_mask, cudaStream_t stream);
+
+// Weight repack: int8 [N,K] (or W8 offset-binary bytes with xor 0x80, source row
+// stride src_ld bytes) -> [N, kpad] zero padded + per-channel code sums.
+cudaError_t launch_repack_weight(const uint8_t* src, uint32_t src_ld, uint32_t n, uint32_t k,
+                                 uint32_t xor_mask, int8_t* dst, uint32_t kpad, int32_t* wsum,
+                                 cudaStream_t stream);
+
+// K3: small-M (rows <= 32) bandwidth-bound GEMV, dp4a + warp-shuffle reduction.
+cudaError_t launch_gemv(const int8_t* q, uint32_t rows, const int8_t* w, uint32_t n,
+                        uint32_t kpad, const EpilogueParams& epi, int sm_count,
+                        cudaStream_t stream);
+
+// Verification kernel: one thread per output, dp4a over K.
+cudaError_t launch_gemm_simt(const int8_t* q, uint32_t rows, const int8_t* w, uint32_t n,
+                             uint32_t kpad, const EpilogueParams& epi, cudaStream_t stream);
+
+// K2: TMA-fed tcgen05 kind::i8 GEMM. `status` is a device int the kernel sets
+// non-zero when a bounded wait expired; tmap_* are encoded by the caller.
+struct GemmTcgen05Args {
+    CUtensorMap tmap_a;  // activations int8 [rows, kpad], box 128 x 128B, swizzle 128B
+    CUtensorMap tmap_b;  // weights     int8 [n, kpad],    box 256 x 128B, swizzle 128B
+    uint32_t rows, n, kpad;
+    EpilogueParams epi;
+    int* status;
+};
+cudaError_t launch_gemm_tcgen05(const GemmTcgen05Args& args, int sm_count, cudaStream_t stream);
+cudaError_t gemm_tcgen05_prepare();  // one-time func attribute set-up
+
+// tensor-pipe peak probe: issues `iters` rounds of kind::i8 MMAs on resident
+// shared-memory operands in every CTA; returns through `cycles` the SM clocks
+// spent per CTA.
+cudaError_t launch_i8_peak_probe(uint32_t iters, long long* cycles, int* status, int sm_count,
+                                 cudaStream_t stream);
+
+}  // namespace vxb

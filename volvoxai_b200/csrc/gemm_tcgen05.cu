@@ -1,0 +1,461 @@
+// K2: int8 x int8 -> int32 GEMM on the 5th-generation tensor cores.
+//
+//   acc[m,n] = sum_k q[m,k] * w[n,k]      q: [rows,kpad] int8, w: [n,kpad] int8
+//
+// Persistent, warp-specialised kernel, one CTA per SM:
+//   warp 0      TMA producer: 128x128B activation tile + 256x128B weight tile
+//               per stage into 128B-swizzled shared memory (4-stage ring,
+//               mbarrier transaction counts)
+//   warp 1      allocates TMEM; one lane issues tcgen05.mma.cta_group::1
+//               .kind::i8 (M128 x N256 x K32 per instruction, 4 per stage);
+//               tcgen05.commit releases smem stages and publishes accumulators
+//   warps 2-5   epilogue: tcgen05.ld the int32 accumulators (each warp owns the
+//               32 TMEM lanes of its quarter), apply the fused epilogue
+//               (raw int32 / dequant+bias fp32 / requant int8) and store.
+// Two 256-column accumulators fill the 512-column TMEM, so the epilogue of
+// tile i overlaps the MMAs of tile i+1.
+//
+// It replaces the reference's mma.sync tile kernels for the same arithmetic
+// (vx_packed_cuda_a8_tile, vx_cuda_packed_a8_m16/_m64:
+//  native/src/backends/cuda/kernels/cuda_forward_llm_kernels.inc:693-883,
+//  :1249-1511) and its thread/warp dp4a QLinear kernels
+// (cuda_forward_quantized_basic_kernels.inc:1-104).
+//
+// Every wait on an mbarrier is bounded (~2 s of SM clocks); on expiry the
+// kernel raises a status word, drains, frees its TMEM and returns.
+#include "common.cuh"
+
+namespace vxb {
+
+namespace {
+
+constexpr uint32_t kBM = 128;           // activation rows per tile (UMMA M)
+constexpr uint32_t kBN = 256;           // output channels per tile (UMMA N)
+constexpr uint32_t kBK = 128;           // K bytes per stage (one swizzle span)
+constexpr uint32_t kUmmaK = 32;         // K per kind::i8 instruction
+constexpr uint32_t kStages = 4;
+constexpr uint32_t kABytes = kBM * kBK;            // 16 KiB
+constexpr uint32_t kBBytes = kBN * kBK;            // 32 KiB
+constexpr uint32_t kStageBytes = kABytes + kBBytes;
+constexpr uint32_t kAccCols = kBN;                 // int32 columns per accumulator
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kThreads = 192;
+constexpr uint32_t kEpiThreads = 128;
+constexpr long long kWaitLimitCycles = 4000000000LL;  // ~2 s at 1.9 GHz
+
+// dynamic shared memory layout (offsets from a 1024-byte aligned base)
+constexpr uint32_t kOffStages = 0;
+constexpr uint32_t kOffWs = kStages * kStageBytes;           // float[4 warps][256]
+constexpr uint32_t kOffBias = kOffWs + 4 * kBN * 4;          // float/int32[4 warps][256]
+constexpr uint32_t kOffBars = kOffBias + 4 * kBN * 4;        // 8-byte barriers
+constexpr uint32_t kNumBars = 2 * kStages + 4;
+constexpr uint32_t kOffTmemPtr = kOffBars + kNumBars * 8;
+constexpr uint32_t kOffAbort = kOffTmemPtr + 4;
+constexpr uint32_t kSmemBytes = kOffAbort + 4 + 1024;        // + alignment slack
+
+// ---- PTX wrappers -----------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: false when the limit expired or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    uint32_t spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if ((++spins & 63u) == 0u) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > kWaitLimitCycles) { *abort_flag = 1; return false; }
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ void fence_barrier_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int32_t c0, int32_t c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem], int8 x int8 -> int32
+__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                        uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// mbarrier arrives once every previously issued MMA of this thread has finished.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                 ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+          "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor for a K-major tile whose rows are 128 bytes,
+// 128B-swizzled (what TMA writes with CU_TENSOR_MAP_SWIZZLE_128B): 8-row groups
+// are 1024 bytes apart (stride byte offset), descriptor version 1 (sm_100),
+// layout type 2 = SWIZZLE_128B. The leading byte offset is unused for
+// swizzled K-major operands. Fields are in units of 16 bytes.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3fffu);
+    d |= (uint64_t)1u << 16;
+    d |= (uint64_t)(1024u >> 4) << 32;
+    d |= (uint64_t)1u << 46;
+    d |= (uint64_t)2u << 61;
+    return d;
+}
+
+// Instruction descriptor, kind::i8: D = S32 (bits 4-5 = 2), A and B signed
+// 8-bit (bits 7-9 and 10-12 = 1), both K-major (bits 15, 16 = 0), N>>3 at
+// bits 17-22, M>>4 at bits 24-28, dense, no saturation.
+__host__ __device__ constexpr uint32_t make_idesc(uint32_t m, uint32_t n) {
+    return (2u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+
+struct Smem {
+    uint8_t* base;
+    __device__ uint32_t a(uint32_t s) const { return smem_u32(base + kOffStages + s * kStageBytes); }
+    __device__ uint32_t b(uint32_t s) const { return a(s) + kABytes; }
+    __device__ uint32_t full(uint32_t s) const { return smem_u32(base + kOffBars + s * 8); }
+    __device__ uint32_t empty(uint32_t s) const { return smem_u32(base + kOffBars + (kStages + s) * 8); }
+    __device__ uint32_t tmem_full(uint32_t b) const { return smem_u32(base + kOffBars + (2 * kStages + b) * 8); }
+    __device__ uint32_t tmem_empty(uint32_t b) const { return smem_u32(base + kOffBars + (2 * kStages + 2 + b) * 8); }
+    __device__ uint32_t* tmem_ptr() const { return reinterpret_cast<uint32_t*>(base + kOffTmemPtr); }
+    __device__ volatile int* abort_flag() const { return reinterpret_cast<volatile int*>(base + kOffAbort); }
+    __device__ float* ws() const { return reinterpret_cast<float*>(base + kOffWs); }
+    __device__ float* bias() const { return reinterpret_cast<float*>(base + kOffBias); }
+};
+
+__device__ __forceinline__ void nap(uint32_t rounds) {
+    for (uint32_t i = 0; i < rounds; i++) __nanosleep(1000);
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_i8_tcgen05_kernel(const __grid_constant__ GemmTcgen05Args args) {
+    extern __shared__ uint8_t smem_raw[];
+    Smem sm;
+    sm.base = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    const uint32_t tiles_m = (args.rows + kBM - 1) / kBM;
+    const uint32_t tiles_n = (args.n + kBN - 1) / kBN;
+    const uint32_t total_tiles = tiles_m * tiles_n;
+    const uint32_t num_kb = args.kpad / kBK;
+    volatile int* abort_flag = sm.abort_flag();
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < kStages; s++) { mbar_init(sm.full(s), 1); mbar_init(sm.empty(s), 1); }
+        for (uint32_t b = 0; b < 2; b++) { mbar_init(sm.tmem_full(b), 1); mbar_init(sm.tmem_empty(b), kEpiThreads); }
+        *abort_flag = 0;
+        fence_barrier_init();
+        prefetch_tmap(&args.tmap_a);
+        prefetch_tmap(&args.tmap_b);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(sm.tmem_ptr()), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *sm.tmem_ptr();
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0, armed = 0, armed_parity = 0;
+            bool ok = true;
+            for (uint32_t t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+                const int32_t m0 = (int32_t)((t % tiles_m) * kBM);
+                const int32_t n0 = (int32_t)((t / tiles_m) * kBN);
+                for (uint32_t kb = 0; kb < num_kb; kb++) {
+                    if (!mbar_wait(sm.empty(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
+                    mbar_expect_tx(sm.full(stage), kStageBytes);
+                    tma_load_2d(sm.a(stage), &args.tmap_a, sm.full(stage), (int32_t)(kb * kBK), m0);
+                    tma_load_2d(sm.b(stage), &args.tmap_b, sm.full(stage), (int32_t)(kb * kBK), n0);
+                    armed |= 1u << stage;
+                    armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                }
+            }
+            if (!ok) {
+                // drain: give this CTA's own copies in flight a bounded time to land
+                for (uint32_t s = 0; s < kStages; s++) {
+                    if (!(armed & (1u << s))) continue;
+                    for (uint32_t i = 0; i < 2000; i++) {
+                        if (mbar_try_wait(sm.full(s), (armed_parity >> s) & 1u)) break;
+                        __nanosleep(500);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(kBM, kBN);
+            uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+            bool ok = true;
+            for (uint32_t t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+                if (!mbar_wait(sm.tmem_empty(acc), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * kAccCols;
+                for (uint32_t kb = 0; kb < num_kb; kb++) {
+                    if (!mbar_wait(sm.full(stage), phase, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = sm.a(stage), b_addr = sm.b(stage);
+#pragma unroll
+                    for (uint32_t k = 0; k < kBK / kUmmaK; k++) {
+                        umma_i8(d_tmem, make_smem_desc(a_addr + k * kUmmaK),
+                                make_smem_desc(b_addr + k * kUmmaK), idesc, (kb | k) != 0u);
+                    }
+                    umma_commit(sm.empty(stage));
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                umma_commit(sm.tmem_full(acc));
+                acc ^= 1u;
+                if (acc == 0) acc_phase ^= 1u;
+            }
+        }
+    } else {
+        // ---------------- epilogue (warps 2..5) ----------------
+        const uint32_t quarter = warp & 3u;              // TMEM lanes [32*quarter, +32)
+        const EpilogueParams& ep = args.epi;
+        // each epilogue warp stages its own copy of the tile's per-channel vectors, so the
+        // four warps never wait on one another
+        float* s_ws = sm.ws() + quarter * kBN;
+        float* s_bias = sm.bias() + quarter * kBN;
+        uint32_t acc = 0, acc_phase = 0;
+        bool ok = true;
+        for (uint32_t t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+            const uint32_t m0 = (t % tiles_m) * kBM, n0 = (t / tiles_m) * kBN;
+            // stage this tile's per-channel vectors
+            __syncwarp();
+            for (uint32_t i = lane; i < kBN; i += 32) {
+                const uint32_t n = n0 + i;
+                float wsv = 0.0f, bv = 0.0f;
+                if (n < args.n && ep.mode != kEpiAcc) {
+                    wsv = __ldg(ep.ws + n);
+                    if (ep.mode == kEpiF32) bv = ep.bias_f32 ? __ldg(ep.bias_f32 + n) : 0.0f;
+                    else bv = __int_as_float(ep.bias_i32 ? __ldg(ep.bias_i32 + n) : 0);
+                }
+                s_ws[i] = wsv; s_bias[i] = bv;
+            }
+            __syncwarp();
+            ok = __all_sync(0xffffffffu, mbar_wait(sm.tmem_full(acc), acc_phase, abort_flag));
+            if (!ok) break;
+            tc_fence_after();
+
+            const uint32_t row = m0 + quarter * 32 + lane;
+            const bool row_ok = row < args.rows;
+            const float as = (row_ok && ep.mode != kEpiAcc) ? __ldg(ep.row_scales + row) : 0.0f;
+            const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + acc * kAccCols;
+#pragma unroll 1
+            for (uint32_t c = 0; c < kBN; c += 32) {
+                uint32_t r[32];
+                tmem_ld32(taddr + c, r);
+                tmem_ld_wait();
+                const uint32_t col = n0 + c;
+                if (!row_ok || col >= args.n) continue;
+                const bool full = col + 32 <= args.n;
+                if (ep.mode == kEpiI8) {
+                    int8_t* dst = (int8_t*)ep.out + (size_t)row * ep.ld + col;
+                    uint32_t packed[8];
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        uint32_t word = 0;
+#pragma unroll
+                        for (int b = 0; b < 4; b++) {
+                            const int i = j * 4 + b;
+                            const int32_t a = (int32_t)r[i] + __float_as_int(s_bias[c + i]);
+                            const int32_t qv = epi_i8(a, as, s_ws[c + i], ep.out_scale, ep.out_zero,
+                                                      ep.out_lo, ep.out_hi);
+                            word |= ((uint32_t)qv & 0xffu) << (8 * b);
+                        }
+                        packed[j] = word;
+                    }
+                    if (full && (((uintptr_t)dst) & 15u) == 0) {
+                        reinterpret_cast<uint4*>(dst)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                        reinterpret_cast<uint4*>(dst)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; i++)
+                            if (col + i < args.n) dst[i] = (int8_t)((packed[i >> 2] >> (8 * (i & 3))) & 0xffu);
+                    }
+                } else {
+                    uint32_t o[32];
+                    if (ep.mode == kEpiF32) {
+#pragma unroll
+                        for (int i = 0; i < 32; i++)
+                            o[i] = __float_as_uint(epi_f32((int32_t)r[i], as, s_ws[c + i], s_bias[c + i]));
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; i++) o[i] = r[i];
+                    }
+                    uint32_t* dst = (uint32_t*)ep.out + (size_t)row * ep.ld + col;
+                    if (full && (((uintptr_t)dst) & 15u) == 0) {
+#pragma unroll
+                        for (int j = 0; j < 8; j++)
+                            reinterpret_cast<uint4*>(dst)[j] = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; i++)
+                            if (col + i < args.n) dst[i] = o[i];
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(sm.tmem_empty(acc));
+            acc ^= 1u;
+            if (acc == 0) acc_phase ^= 1u;
+        }
+    }
+
+    // ---------------- teardown ----------------
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        // a bounded wait expired somewhere: let asynchronous work in flight settle
+        nap(200);
+        if (threadIdx.x == 0 && args.status) atomicExch(args.status, 1);
+        __syncthreads();
+    }
+    tc_fence_after();
+    if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+// ---- tensor-pipe peak probe --------------------------------------------------
+// Every CTA issues back-to-back M128xN256xK32 kind::i8 MMAs on operands that
+// stay resident in shared memory (no TMA, no epilogue): the dense int8 rate the
+// tensor pipe sustains, used as the measured roofline denominator for K2.
+__global__ void __launch_bounds__(128, 1)
+i8_peak_probe_kernel(uint32_t iters, long long* cycles, int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* base = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    __shared__ uint64_t bar;
+    __shared__ uint32_t tmem_ptr;
+    __shared__ int abort_flag;
+    const uint32_t warp = threadIdx.x >> 5;
+    for (uint32_t i = threadIdx.x; i < kStageBytes / 4; i += blockDim.x)
+        reinterpret_cast<uint32_t*>(base)[i] = 0x01010101u;
+    if (threadIdx.x == 0) { mbar_init(smem_u32(&bar), 1); abort_flag = 0; fence_barrier_init(); }
+    fence_proxy_async();
+    if (warp == 0) { tmem_alloc(smem_u32(&tmem_ptr), kTmemCols); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_ptr;
+    if (threadIdx.x == 0) {
+        constexpr uint32_t idesc = make_idesc(kBM, kBN);
+        const uint32_t a_addr = smem_u32(base), b_addr = a_addr + kABytes;
+        const long long t0 = clock64();
+        uint32_t parity = 0;
+        bool ok = true;
+        // commit every 256 instructions so the issue queue never holds an unbounded backlog
+        for (uint32_t it = 0; ok && it < iters; it++) {
+            for (uint32_t j = 0; j < 64; j++) {
+#pragma unroll
+                for (uint32_t k = 0; k < 4; k++)
+                    umma_i8(tmem_base + (j & 1u) * kAccCols, make_smem_desc(a_addr + k * kUmmaK),
+                            make_smem_desc(b_addr + k * kUmmaK), idesc, 1u);
+            }
+            umma_commit(smem_u32(&bar));
+            ok = mbar_wait(smem_u32(&bar), parity, &abort_flag);
+            parity ^= 1u;
+        }
+        cycles[blockIdx.x] = clock64() - t0;
+        if (!ok && status) atomicExch(status, 2);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 0) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+}  // namespace
+
+cudaError_t gemm_tcgen05_prepare() {
+    cudaError_t e = cudaFuncSetAttribute(gemm_i8_tcgen05_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(i8_peak_probe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                (int)(kStageBytes + 1024));
+}
+
+cudaError_t launch_gemm_tcgen05(const GemmTcgen05Args& args, int sm_count, cudaStream_t stream) {
+    if (args.rows == 0 || args.n == 0) return cudaSuccess;
+    const uint32_t tiles = ((args.rows + kBM - 1) / kBM) * ((args.n + kBN - 1) / kBN);
+    const uint32_t grid = tiles < (uint32_t)sm_count ? tiles : (uint32_t)sm_count;
+    gemm_i8_tcgen05_kernel<<<grid, kThreads, kSmemBytes, stream>>>(args);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_i8_peak_probe(uint32_t iters, long long* cycles, int* status, int sm_count,
+                                 cudaStream_t stream) {
+    i8_peak_probe_kernel<<<sm_count, 128, kStageBytes + 1024, stream>>>(iters, cycles, status);
+    return cudaGetLastError();
+}
+
+}  // namespace vxb

@@ -1,0 +1,177 @@
+// K3: decode GEMV for rows <= 32 (HBM-bound: the int8 weights are streamed
+// exactly once), and the one-thread-per-output verification kernel.
+//
+// Reference counterparts: the single-row route of vx_packed_linear_forward
+// (native/src/kernels/packed_linear_ops.inc:1471-1535) and the CUDA decode
+// kernels vx_packed_cuda_a8_columns / vx_cuda_qlinear_warp_dp4a_i8u8
+// (native/src/backends/cuda/kernels/cuda_forward_llm_kernels.inc:254-459,
+//  cuda_forward_quantized_basic_kernels.inc:49-104), which assign one warp (or
+// eight lanes) per output and re-quantize the activation row per column tile.
+// Here the activations are quantized once (K1), staged in shared memory, and
+// every warp streams CH weight rows with 128-bit loads, reusing each
+// activation register across the CH rows; integer partials are reduced with
+// warp shuffles (integer addition is associative, so any order is bit-exact).
+#include "common.cuh"
+
+namespace vxb {
+
+namespace {
+
+constexpr int kGemvThreads = 256;
+constexpr int kGemvWarps = kGemvThreads / 32;
+constexpr uint32_t kGemvSmemBytes = 96 * 1024;  // activation chunk budget
+
+__device__ __forceinline__ int dp4a_s8(uint32_t a, uint32_t b, int c) {
+    return __dp4a((int)a, (int)b, c);
+}
+
+// MR activation rows (compile time), CH weight rows (output channels) per warp.
+template <int MR, int CH>
+__global__ void __launch_bounds__(kGemvThreads)
+gemv_dp4a_kernel(const int8_t* __restrict__ q, uint32_t rows, const int8_t* __restrict__ w,
+                 uint32_t n, uint32_t kpad, uint32_t kchunk, EpilogueParams epi) {
+    extern __shared__ __align__(16) uint8_t smem[];  // [MR][kchunk] activations
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr uint32_t kChannelsPerCta = kGemvWarps * CH;
+    const uint32_t blocks = (n + kChannelsPerCta - 1) / kChannelsPerCta;
+    const bool single_chunk = kchunk >= kpad;
+
+    for (uint32_t blk = blockIdx.x; blk < blocks; blk += gridDim.x) {
+        const uint32_t c0 = blk * kChannelsPerCta + warp * CH;
+        int acc[MR][CH];
+#pragma unroll
+        for (int m = 0; m < MR; m++)
+#pragma unroll
+            for (int c = 0; c < CH; c++) acc[m][c] = 0;
+
+        for (uint32_t kb = 0; kb < kpad; kb += kchunk) {
+            const uint32_t klen = kpad - kb < kchunk ? kpad - kb : kchunk;
+            if (!(single_chunk && blk != blockIdx.x)) {
+                // stage the activation chunk (zero rows beyond `rows`)
+                __syncthreads();
+                const uint32_t vec_per_row = klen / 16;
+                for (uint32_t i = threadIdx.x; i < MR * vec_per_row; i += kGemvThreads) {
+                    const uint32_t m = i / vec_per_row, v = i % vec_per_row;
+                    uint4 val = make_uint4(0, 0, 0, 0);
+                    if (m < rows) val = *reinterpret_cast<const uint4*>(q + (size_t)m * kpad + kb + v * 16);
+                    *reinterpret_cast<uint4*>(smem + (size_t)m * kchunk + v * 16) = val;
+                }
+                __syncthreads();
+            }
+            // each lane owns 16 bytes of every 512-byte step
+            for (uint32_t k0 = lane * 16; k0 < klen; k0 += 512) {
+                uint4 wv[CH];
+#pragma unroll
+                for (int c = 0; c < CH; c++) {
+                    const uint32_t ch = c0 + c;
+                    wv[c] = ch < n ? __ldcs(reinterpret_cast<const uint4*>(w + (size_t)ch * kpad + kb + k0))
+                                   : make_uint4(0, 0, 0, 0);
+                }
+#pragma unroll
+                for (int m = 0; m < MR; m++) {
+                    const uint4 a = *reinterpret_cast<const uint4*>(smem + (size_t)m * kchunk + k0);
+#pragma unroll
+                    for (int c = 0; c < CH; c++) {
+                        int s = acc[m][c];
+                        s = dp4a_s8(a.x, wv[c].x, s);
+                        s = dp4a_s8(a.y, wv[c].y, s);
+                        s = dp4a_s8(a.z, wv[c].z, s);
+                        s = dp4a_s8(a.w, wv[c].w, s);
+                        acc[m][c] = s;
+                    }
+                }
+            }
+        }
+        // warp-shuffle reduction of the integer partials, then the fused epilogue
+#pragma unroll
+        for (int m = 0; m < MR; m++)
+#pragma unroll
+            for (int c = 0; c < CH; c++) {
+                int s = acc[m][c];
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+                acc[m][c] = s;
+            }
+        // lane (m*CH + c) % 32 writes element (m, c)
+#pragma unroll
+        for (int m = 0; m < MR; m++)
+#pragma unroll
+            for (int c = 0; c < CH; c++) {
+                if (lane == ((m * CH + c) & 31) && (uint32_t)m < rows && c0 + c < n)
+                    epi_store(epi, m, c0 + c, acc[m][c]);
+            }
+    }
+}
+
+template <int MR, int CH>
+cudaError_t launch_gemv_t(const int8_t* q, uint32_t rows, const int8_t* w, uint32_t n,
+                          uint32_t kpad, const EpilogueParams& epi, int sm_count,
+                          cudaStream_t stream) {
+    // K chunk: whole K when MR*kpad fits the budget, else the largest multiple of 512 that does.
+    uint32_t kchunk = kpad;
+    if ((uint64_t)MR * kpad > kGemvSmemBytes) kchunk = (kGemvSmemBytes / MR) / 512 * 512;
+    const uint32_t smem = MR * kchunk;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemv_dp4a_kernel<MR, CH>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)kGemvSmemBytes);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    constexpr uint32_t kChannelsPerCta = kGemvWarps * CH;
+    const uint32_t blocks = (n + kChannelsPerCta - 1) / kChannelsPerCta;
+    uint32_t per_sm = smem ? (200u * 1024u) / (smem + 1024u) : 8u;
+    if (per_sm > 8) per_sm = 8;
+    if (per_sm < 1) per_sm = 1;
+    uint32_t grid = (uint32_t)sm_count * per_sm;
+    if (grid > blocks) grid = blocks;
+    gemv_dp4a_kernel<MR, CH><<<grid, kGemvThreads, smem, stream>>>(q, rows, w, n, kpad, kchunk, epi);
+    return cudaGetLastError();
+}
+
+// ---- verification kernel: one thread per output element -------------------
+__global__ void gemm_simt_kernel(const int8_t* __restrict__ q, uint32_t rows,
+                                 const int8_t* __restrict__ w, uint32_t n, uint32_t kpad,
+                                 EpilogueParams epi) {
+    const uint32_t col = blockIdx.x * blockDim.x + threadIdx.x;
+    const uint32_t row = blockIdx.y;
+    if (col >= n || row >= rows) return;
+    const uint32_t* a = reinterpret_cast<const uint32_t*>(q + (size_t)row * kpad);
+    const uint32_t* b = reinterpret_cast<const uint32_t*>(w + (size_t)col * kpad);
+    int acc = 0;
+    for (uint32_t j = 0; j < kpad / 4; j++) acc = dp4a_s8(a[j], b[j], acc);
+    epi_store(epi, row, col, acc);
+}
+
+}  // namespace
+
+cudaError_t launch_gemv(const int8_t* q, uint32_t rows, const int8_t* w, uint32_t n, uint32_t kpad,
+                        const EpilogueParams& epi, int sm_count, cudaStream_t stream) {
+    if (rows == 0 || n == 0) return cudaSuccess;
+    if (rows > 32) return cudaErrorInvalidValue;
+    if (rows <= 1) return launch_gemv_t<1, 4>(q, rows, w, n, kpad, epi, sm_count, stream);
+    if (rows <= 2) return launch_gemv_t<2, 4>(q, rows, w, n, kpad, epi, sm_count, stream);
+    if (rows <= 4) return launch_gemv_t<4, 4>(q, rows, w, n, kpad, epi, sm_count, stream);
+    if (rows <= 8) return launch_gemv_t<8, 2>(q, rows, w, n, kpad, epi, sm_count, stream);
+    if (rows <= 16) return launch_gemv_t<16, 2>(q, rows, w, n, kpad, epi, sm_count, stream);
+    return launch_gemv_t<32, 1>(q, rows, w, n, kpad, epi, sm_count, stream);
+}
+
+cudaError_t launch_gemm_simt(const int8_t* q, uint32_t rows, const int8_t* w, uint32_t n,
+                             uint32_t kpad, const EpilogueParams& epi, cudaStream_t stream) {
+    if (rows == 0 || n == 0) return cudaSuccess;
+    for (uint32_t r0 = 0; r0 < rows; r0 += 65535u) {
+        const uint32_t cnt = rows - r0 < 65535u ? rows - r0 : 65535u;
+        EpilogueParams e = epi;
+        // shift row-indexed pointers for the slab
+        e.row_scales = epi.row_scales ? epi.row_scales + r0 : nullptr;
+        const size_t elem = epi.mode == kEpiI8 ? 1 : 4;
+        e.out = (uint8_t*)epi.out + (size_t)r0 * epi.ld * elem;
+        dim3 grid((n + 127) / 128, cnt);
+        gemm_simt_kernel<<<grid, 128, 0, stream>>>(q + (size_t)r0 * kpad, cnt, w, n, kpad, e);
+    }
+    return cudaGetLastError();
+}
+
+}  // namespace vxb

@@ -1,0 +1,262 @@
+// K1: per-token symmetric int8 quantizer, plus the small layout helpers
+// (weight repack, zero-point folding, byte copies).  HBM-bound byte work:
+// 128-bit loads, 128-bit stores, one pass over the fp32 activations.
+//
+// Arithmetic contract (reference: native/src/kernels/packed_linear_ops.inc
+// :97-153 AVX2, :1574-1597 scalar; CUDA twin cuda_forward_llm_kernels.inc
+// :195-247):
+//   row invalid if any element has an all-ones exponent (NaN/Inf)
+//   amax  = max |x|;  scale = amax == 0 ? 1 : amax / 127  (IEEE divide)
+//   scale = max(scale, 2^-126)
+//   q     = cvt.rni(clamp(x / scale, -127, 127))            (IEEE divide, ties to even)
+// A reciprocal-multiply would move half-way values across a rounding
+// boundary, so the divide is __fdiv_rn on every element.
+#include "common.cuh"
+
+namespace vxb {
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kMaxVecPerThread = 16;  // float4 per thread kept in registers (K <= 16384)
+
+__device__ __forceinline__ bool nonfinite_bits(float v) {
+    return (__float_as_uint(v) & 0x7f800000u) == 0x7f800000u;
+}
+
+__device__ __forceinline__ int32_t quant1(float v, float scale) {
+    float r = __fdiv_rn(v, scale);
+    r = fminf(fmaxf(r, -127.0f), 127.0f);
+    return __float2int_rn(r);
+}
+
+__device__ __forceinline__ uint32_t pack4(float4 v, float scale) {
+    const uint32_t a = (uint32_t)quant1(v.x, scale) & 0xffu;
+    const uint32_t b = (uint32_t)quant1(v.y, scale) & 0xffu;
+    const uint32_t c = (uint32_t)quant1(v.z, scale) & 0xffu;
+    const uint32_t d = (uint32_t)quant1(v.w, scale) & 0xffu;
+    return a | (b << 8) | (c << 16) | (d << 24);
+}
+
+// Reduce (max, or-flag) over THREADS_PER_ROW consecutive threads (power of two).
+template <int THREADS_PER_ROW>
+__device__ __forceinline__ void row_reduce(float& amax, int& bad, float* smem_max, int* smem_bad) {
+    constexpr int kWarpSpan = THREADS_PER_ROW < 32 ? THREADS_PER_ROW : 32;
+#pragma unroll
+    for (int off = kWarpSpan / 2; off > 0; off >>= 1) {
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+        bad |= __shfl_xor_sync(0xffffffffu, bad, off);
+    }
+    if constexpr (THREADS_PER_ROW > 32) {
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        if (lane == 0) { smem_max[warp] = amax; smem_bad[warp] = bad; }
+        __syncthreads();
+        constexpr int kWarps = THREADS_PER_ROW / 32;
+        const int first = (threadIdx.x / THREADS_PER_ROW) * kWarps;  // this row's first warp
+        float m = 0.0f; int b = 0;
+#pragma unroll
+        for (int i = 0; i < kWarps; i++) { m = fmaxf(m, smem_max[first + i]); b |= smem_bad[first + i]; }
+        amax = m; bad = b;
+    }
+}
+
+// THREADS_PER_ROW threads cooperate on one row; kThreads/THREADS_PER_ROW rows per CTA.
+// VEC: row addressed as float4 (k % 4 == 0, 16-byte aligned base and ldq % 16 == 0).
+// CACHE: the row's float4s stay in registers between the two passes.
+template <int THREADS_PER_ROW, bool CACHE>
+__global__ void __launch_bounds__(kThreads)
+quantize_rows_vec(const float* __restrict__ x, uint32_t rows, uint32_t k, int8_t* __restrict__ q,
+                  uint32_t ldq, float* __restrict__ row_scales, int32_t* __restrict__ valid) {
+    __shared__ float smem_max[kThreads / 32];
+    __shared__ int smem_bad[kThreads / 32];
+    constexpr int kRowsPerCta = kThreads / THREADS_PER_ROW;
+    const uint32_t row = blockIdx.x * kRowsPerCta + threadIdx.x / THREADS_PER_ROW;
+    const int t = threadIdx.x % THREADS_PER_ROW;
+    const bool active = row < rows;
+    const uint32_t nvec = k / 4;
+    const float4* in = reinterpret_cast<const float4*>(x + (size_t)(active ? row : 0) * k);
+
+    float4 cache[CACHE ? kMaxVecPerThread : 1];
+    float amax = 0.0f; int bad = 0;
+    if (active) {
+        if constexpr (CACHE) {
+#pragma unroll
+            for (int i = 0; i < kMaxVecPerThread; i++) {
+                const uint32_t v = t + i * THREADS_PER_ROW;
+                cache[i] = v < nvec ? __ldg(in + v) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int i = 0; i < kMaxVecPerThread; i++) {
+                const float4 c = cache[i];
+                bad |= nonfinite_bits(c.x) | nonfinite_bits(c.y) | nonfinite_bits(c.z) | nonfinite_bits(c.w);
+                amax = fmaxf(amax, fmaxf(fmaxf(fabsf(c.x), fabsf(c.y)), fmaxf(fabsf(c.z), fabsf(c.w))));
+            }
+        } else {
+            for (uint32_t v = t; v < nvec; v += THREADS_PER_ROW) {
+                const float4 c = __ldg(in + v);
+                bad |= nonfinite_bits(c.x) | nonfinite_bits(c.y) | nonfinite_bits(c.z) | nonfinite_bits(c.w);
+                amax = fmaxf(amax, fmaxf(fmaxf(fabsf(c.x), fabsf(c.y)), fmaxf(fabsf(c.z), fabsf(c.w))));
+            }
+        }
+    }
+    row_reduce<THREADS_PER_ROW>(amax, bad, smem_max, smem_bad);
+    if (!active) return;
+
+    float scale = amax == 0.0f ? 1.0f : __fdiv_rn(amax, 127.0f);
+    scale = fmaxf(scale, 1.1754943508222875e-38f);
+    if (t == 0) {
+        row_scales[row] = bad ? __int_as_float(0x7fc00000) : scale;
+        if (valid) valid[row] = bad ? 0 : 1;
+    }
+    uint32_t* out = reinterpret_cast<uint32_t*>(q + (size_t)row * ldq);
+    const uint32_t nwords = ldq / 4;
+    if constexpr (CACHE) {
+#pragma unroll
+        for (int i = 0; i < kMaxVecPerThread; i++) {
+            const uint32_t v = t + i * THREADS_PER_ROW;
+            if (v < nwords) out[v] = (v < nvec && !bad) ? pack4(cache[i], scale) : 0u;
+        }
+        for (uint32_t v = t + kMaxVecPerThread * THREADS_PER_ROW; v < nwords; v += THREADS_PER_ROW) out[v] = 0u;
+    } else {
+        for (uint32_t v = t; v < nwords; v += THREADS_PER_ROW)
+            out[v] = (v < nvec && !bad) ? pack4(__ldg(in + v), scale) : 0u;
+    }
+}
+
+// Any k / alignment: one warp per row, scalar accesses.
+__global__ void __launch_bounds__(kThreads)
+quantize_rows_scalar(const float* __restrict__ x, uint32_t rows, uint32_t k, int8_t* __restrict__ q,
+                     uint32_t ldq, float* __restrict__ row_scales, int32_t* __restrict__ valid) {
+    const uint32_t row = blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const float* in = x + (size_t)row * k;
+    float amax = 0.0f; int bad = 0;
+    for (uint32_t j = lane; j < k; j += 32) {
+        const float v = in[j];
+        bad |= nonfinite_bits(v);
+        amax = fmaxf(amax, fabsf(v));
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+        bad |= __shfl_xor_sync(0xffffffffu, bad, off);
+    }
+    float scale = amax == 0.0f ? 1.0f : __fdiv_rn(amax, 127.0f);
+    scale = fmaxf(scale, 1.1754943508222875e-38f);
+    if (lane == 0) {
+        row_scales[row] = bad ? __int_as_float(0x7fc00000) : scale;
+        if (valid) valid[row] = bad ? 0 : 1;
+    }
+    int8_t* out = q + (size_t)row * ldq;
+    for (uint32_t j = lane; j < ldq; j += 32)
+        out[j] = (j < k && !bad) ? (int8_t)quant1(in[j], scale) : (int8_t)0;
+}
+
+__global__ void fill_f32_kernel(float* dst, uint32_t count, float value) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < count) dst[i] = value;
+}
+
+__global__ void fold_zero_point_kernel(const int32_t* bias, const int32_t* wsum, int32_t zero,
+                                       int32_t* out, uint32_t n) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = (bias ? bias[i] : 0) - zero * wsum[i];
+}
+
+__global__ void copy_bytes_padded_kernel(const uint8_t* __restrict__ src, uint32_t rows, uint32_t k,
+                                         uint8_t* __restrict__ dst, uint32_t ld, uint32_t xor_mask) {
+    const uint32_t row = blockIdx.y;
+    for (uint32_t j = blockIdx.x * blockDim.x + threadIdx.x; j < ld; j += gridDim.x * blockDim.x)
+        dst[(size_t)row * ld + j] = j < k ? (uint8_t)(src[(size_t)row * k + j] ^ xor_mask) : (uint8_t)0;
+}
+
+// One warp per weight row: copy (with optional ^0x80), zero the padding, sum the codes.
+__global__ void __launch_bounds__(kThreads)
+repack_weight_kernel(const uint8_t* __restrict__ src, uint32_t src_ld, uint32_t n, uint32_t k,
+                     uint32_t xor_mask, int8_t* __restrict__ dst, uint32_t kpad,
+                     int32_t* __restrict__ wsum) {
+    const uint32_t row = blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= n) return;
+    const uint8_t* in = src + (size_t)row * src_ld;
+    int8_t* out = dst + (size_t)row * kpad;
+    int32_t sum = 0;
+    for (uint32_t j = lane; j < kpad; j += 32) {
+        const int8_t v = j < k ? (int8_t)(in[j] ^ xor_mask) : (int8_t)0;
+        out[j] = v;
+        sum += v;
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+    if (lane == 0) wsum[row] = sum;
+}
+
+template <int TPR>
+cudaError_t launch_vec(const float* x, uint32_t rows, uint32_t k, int8_t* q, uint32_t ldq,
+                       float* row_scales, int32_t* valid, cudaStream_t stream) {
+    constexpr int kRowsPerCta = kThreads / TPR;
+    const uint32_t grid = (rows + kRowsPerCta - 1) / kRowsPerCta;
+    if (k / 4 <= (uint32_t)TPR * kMaxVecPerThread)
+        quantize_rows_vec<TPR, true><<<grid, kThreads, 0, stream>>>(x, rows, k, q, ldq, row_scales, valid);
+    else
+        quantize_rows_vec<TPR, false><<<grid, kThreads, 0, stream>>>(x, rows, k, q, ldq, row_scales, valid);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_quantize_rows(const float* x, uint32_t rows, uint32_t k, int8_t* q, uint32_t ldq,
+                                 float* row_scales, int32_t* valid, cudaStream_t stream) {
+    if (rows == 0) return cudaSuccess;
+    const bool vec = (k % 4 == 0) && (ldq % 4 == 0) && ((uintptr_t)x % 16 == 0) && ((uintptr_t)q % 4 == 0);
+    if (!vec) {
+        const uint32_t grid = (rows + kThreads / 32 - 1) / (kThreads / 32);
+        quantize_rows_scalar<<<grid, kThreads, 0, stream>>>(x, rows, k, q, ldq, row_scales, valid);
+        return cudaGetLastError();
+    }
+    // Threads per row grow with K so each thread keeps at most 16 float4 in registers.
+    if (k <= 512) return launch_vec<8>(x, rows, k, q, ldq, row_scales, valid, stream);
+    if (k <= 2048) return launch_vec<32>(x, rows, k, q, ldq, row_scales, valid, stream);
+    if (k <= 4096) return launch_vec<64>(x, rows, k, q, ldq, row_scales, valid, stream);
+    if (k <= 8192) return launch_vec<128>(x, rows, k, q, ldq, row_scales, valid, stream);
+    return launch_vec<256>(x, rows, k, q, ldq, row_scales, valid, stream);
+}
+
+cudaError_t launch_fill_f32(float* dst, uint32_t count, float value, cudaStream_t stream) {
+    if (!count) return cudaSuccess;
+    fill_f32_kernel<<<(count + 255) / 256, 256, 0, stream>>>(dst, count, value);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_fold_zero_point(const int32_t* bias, const int32_t* wsum, int32_t input_zero,
+                                   int32_t* out, uint32_t n, cudaStream_t stream) {
+    if (!n) return cudaSuccess;
+    fold_zero_point_kernel<<<(n + 255) / 256, 256, 0, stream>>>(bias, wsum, input_zero, out, n);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_copy_bytes_padded(const uint8_t* src, uint32_t rows, uint32_t k, uint8_t* dst,
+                                     uint32_t ld, uint32_t xor_mask, cudaStream_t stream) {
+    if (!rows) return cudaSuccess;
+    dim3 grid((ld + 1023) / 1024 < 8 ? (ld + 1023) / 1024 : 8, rows);
+    // grid.y is limited to 65535: larger row counts go in slabs
+    for (uint32_t r0 = 0; r0 < rows; r0 += 65535u) {
+        const uint32_t cnt = rows - r0 < 65535u ? rows - r0 : 65535u;
+        grid.y = cnt;
+        copy_bytes_padded_kernel<<<grid, 256, 0, stream>>>(src + (size_t)r0 * k, cnt, k,
+                                                            dst + (size_t)r0 * ld, ld, xor_mask);
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t launch_repack_weight(const uint8_t* src, uint32_t src_ld, uint32_t n, uint32_t k,
+                                 uint32_t xor_mask, int8_t* dst, uint32_t kpad, int32_t* wsum,
+                                 cudaStream_t stream) {
+    if (!n) return cudaSuccess;
+    const uint32_t grid = (n + kThreads / 32 - 1) / (kThreads / 32);
+    repack_weight_kernel<<<grid, kThreads, 0, stream>>>(src, src_ld, n, k, xor_mask, dst, kpad, wsum);
+    return cudaGetLastError();
+}
+
+}  // namespace vxb

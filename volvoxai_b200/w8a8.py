@@ -1,0 +1,257 @@
+"""Host-side mirror of the reference's operator interface for the W8A8 linear,
+on top of the C ABI (include/vxb200_w8a8.h).
+
+Two levels, as in the C header:
+
+* ``Context`` / ``Weight`` / ``linear_*``: device-resident tensors (torch is
+  used for device memory and streams only; every kernel is in libvxb200.so).
+* ``qlinear_i8u8`` / ``packed_linear`` / ``packed_linear_decode``: NumPy host
+  arrays in and out, the argument order, admission rules and tri-state return
+  (1 handled / 0 declined / -1 failed) of the reference's CUDA backend hooks
+  ``VxW8A8Ops.qlinear_i8u8`` (native/src/backends/w8a8_device_ops.h:15-17) and
+  ``cuda_graph_llm_f32`` / ``cuda_graph_packed_linear_decode_f32``
+  (native/src/backends/cuda_engine.h:13-19).
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+from ._lib import (DT_I8, DT_U8, OP_PACKED_LINEAR, ROUTE_AUTO, ROUTE_GEMV, ROUTE_SIMT,
+                   ROUTE_TCGEN05, LLMOpArgs, last_error, last_route)
+
+__all__ = ["Context", "Weight", "W8A8Error", "qlinear_i8u8", "packed_linear",
+           "packed_linear_decode", "host_cache_clear", "launch_count", "last_error",
+           "last_route", "ROUTE_AUTO", "ROUTE_GEMV", "ROUTE_TCGEN05", "ROUTE_SIMT",
+           "DT_I8", "DT_U8"]
+
+
+class W8A8Error(RuntimeError):
+    """Raised by the device-level wrappers when the library declines (0) or fails (-1)."""
+
+    def __init__(self, code: int):
+        self.code = code
+        super().__init__(f"libvxb200 returned {code}: {last_error()}")
+
+
+def _check(code: int) -> None:
+    if code != 1:
+        raise W8A8Error(code)
+
+
+def _ptr(a) -> C.c_void_p:
+    if a is None:
+        return C.c_void_p(0)
+    if isinstance(a, np.ndarray):
+        return C.c_void_p(a.ctypes.data)
+    return C.c_void_p(a.data_ptr())  # torch tensor
+
+
+def launch_count() -> int:
+    return int(_lib.load().vxb_launch_count())
+
+
+class Context:
+    """Device + stream + reusable scratch (one per thread of use)."""
+
+    def __init__(self, device: int = 0, stream: int | None = None):
+        self._L = _lib.load()
+        self.device = device
+        h = C.c_void_p(0)
+        _check(self._L.vxb_context_create(device, C.c_void_p(stream or 0), C.byref(h)))
+        self.handle = h
+
+    def set_stream(self, stream: int | None) -> None:
+        _check(self._L.vxb_context_set_stream(self.handle, C.c_void_p(stream or 0)))
+
+    def use_torch_stream(self) -> None:
+        import torch
+        self.set_stream(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def synchronize(self) -> None:
+        _check(self._L.vxb_context_synchronize(self.handle))
+
+    def measure_i8_tensor_peak(self, iters: int = 200) -> float:
+        out = C.c_double(0.0)
+        _check(self._L.vxb_measure_i8_tensor_peak(self.handle, iters, C.byref(out)))
+        return out.value
+
+    def close(self) -> None:
+        if getattr(self, "handle", None):
+            self._L.vxb_context_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ---- device-pointer entries (torch tensors on this device) ----
+    def quantize_rows(self, x, ldq: int | None = None):
+        """fp32 [rows,k] -> (int8 [rows,ldq], fp32 scales [rows], int32 valid [rows])."""
+        import torch
+        rows, k = x.shape
+        ldq = ldq or k
+        q = torch.empty((rows, ldq), dtype=torch.int8, device=x.device)
+        s = torch.empty(rows, dtype=torch.float32, device=x.device)
+        v = torch.empty(rows, dtype=torch.int32, device=x.device)
+        _check(self._L.vxb_quantize_rows(self.handle, _ptr(x), rows, k, _ptr(q), ldq, _ptr(s), _ptr(v)))
+        return q, s, v
+
+    def linear_f32(self, w: "Weight", x, out=None, route: int = ROUTE_AUTO):
+        import torch
+        rows = x.shape[0]
+        if out is None:
+            out = torch.empty((rows, w.d_out), dtype=torch.float32, device=x.device)
+        _check(self._L.vxb_linear_f32(self.handle, w.handle, _ptr(x), rows, _ptr(out),
+                                      out.stride(0), route))
+        return out
+
+    def linear_i8(self, w: "Weight", x, out_scale: float, out_zero: int = 0, out=None,
+                  route: int = ROUTE_AUTO):
+        import torch
+        rows = x.shape[0]
+        if out is None:
+            out = torch.empty((rows, w.d_out), dtype=torch.int8, device=x.device)
+        _check(self._L.vxb_linear_i8(self.handle, w.handle, _ptr(x), rows, float(out_scale),
+                                     int(out_zero), _ptr(out), out.stride(0), route))
+        return out
+
+    def linear_acc_i32(self, w: "Weight", x, route: int = ROUTE_AUTO, want_q: bool = False):
+        import torch
+        rows = x.shape[0]
+        acc = torch.empty((rows, w.d_out), dtype=torch.int32, device=x.device)
+        q = torch.empty((rows, w.d_in), dtype=torch.int8, device=x.device) if want_q else None
+        s = torch.empty(rows, dtype=torch.float32, device=x.device) if want_q else None
+        _check(self._L.vxb_linear_acc_i32(self.handle, w.handle, _ptr(x), rows, _ptr(acc),
+                                          _ptr(q), _ptr(s), route))
+        return (acc, q, s) if want_q else acc
+
+    def qlinear_device(self, w: "Weight", x, input_scale, input_zero, output_scale, output_zero,
+                       out_unsigned: bool = False, route: int = ROUTE_AUTO):
+        import torch
+        rows = x.shape[0]
+        in_dt = DT_U8 if x.dtype == torch.uint8 else DT_I8
+        out = torch.empty((rows, w.d_out), dtype=torch.uint8 if out_unsigned else torch.int8,
+                          device=x.device)
+        _check(self._L.vxb_qlinear_device(self.handle, w.handle, _ptr(x), rows, float(input_scale),
+                                          int(input_zero), float(output_scale), int(output_zero),
+                                          in_dt, DT_U8 if out_unsigned else DT_I8, _ptr(out),
+                                          out.stride(0), route))
+        return out
+
+
+class Weight:
+    """One linear's weights on the device, repacked once (the compile-time step)."""
+
+    def __init__(self, ctx: Context, handle):
+        self._L = ctx._L
+        self.ctx = ctx
+        self.handle = handle
+        self.d_in = int(self._L.vxb_weight_d_in(handle))
+        self.d_out = int(self._L.vxb_weight_d_out(handle))
+
+    @classmethod
+    def from_i8(cls, ctx: Context, w: np.ndarray, ws: np.ndarray, bias_f32=None, bias_i32=None):
+        """int8 [d_out,d_in] + fp32 scale [d_out] (the W8A8 SafeTensors layout)."""
+        w = np.ascontiguousarray(w, np.int8)
+        ws = np.ascontiguousarray(ws, np.float32)
+        bf = None if bias_f32 is None else np.ascontiguousarray(bias_f32, np.float32)
+        bi = None if bias_i32 is None else np.ascontiguousarray(bias_i32, np.int32)
+        h = C.c_void_p(0)
+        _check(ctx._L.vxb_weight_create_i8(ctx.handle, _ptr(w), _ptr(ws), _ptr(bf), _ptr(bi),
+                                           w.shape[0], w.shape[1], C.byref(h)))
+        return cls(ctx, h)
+
+    @classmethod
+    def from_w8_words(cls, ctx: Context, words: np.ndarray, group_scales: np.ndarray, d_in: int,
+                      group_size: int, bias_f32=None):
+        """PackedLinear W8 storage: I32 words [d_out,ceil(d_in/4)] + group scales."""
+        words = np.ascontiguousarray(words).view(np.int32)
+        gs = np.ascontiguousarray(group_scales, np.float32)
+        bf = None if bias_f32 is None else np.ascontiguousarray(bias_f32, np.float32)
+        h = C.c_void_p(0)
+        _check(ctx._L.vxb_weight_create_w8_words(ctx.handle, _ptr(words), _ptr(gs), _ptr(bf),
+                                                 words.shape[0], d_in, group_size, C.byref(h)))
+        return cls(ctx, h)
+
+    @property
+    def device_bytes(self) -> int:
+        return int(self._L.vxb_weight_device_bytes(self.handle))
+
+    def close(self) -> None:
+        if getattr(self, "handle", None):
+            self._L.vxb_weight_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+# ---- reference-facing host entries (NumPy in / out, tri-state int return) ----
+
+def qlinear_i8u8(input, weight, weight_scales, weight_zero_points, bias, output,
+                 input_scale, input_zero_point, output_scale, output_zero_point) -> int:
+    """Same argument meaning and order as ``VxW8A8Ops.qlinear_i8u8``; dtypes are taken from
+    the arrays (int8 / uint8). Writes ``output`` in place. Returns 1 / 0 / -1."""
+    L = _lib.load()
+    rows, d_in = input.shape
+    d_out = weight.shape[0]
+
+    def dt(a):
+        return DT_U8 if a.dtype == np.uint8 else DT_I8
+    for a in (input, weight, output):
+        if a.dtype not in (np.int8, np.uint8) or not a.flags.c_contiguous:
+            raise TypeError("byte tensors must be contiguous int8/uint8 arrays")
+    ws = np.ascontiguousarray(weight_scales, np.float32)
+    wz = np.ascontiguousarray(weight_zero_points, np.int32)
+    b = np.ascontiguousarray(bias, np.int32)
+    return int(L.vxb_qlinear_i8u8(_ptr(input), _ptr(weight), _ptr(ws), _ptr(wz), _ptr(b),
+                                  _ptr(output), rows, d_in, d_out, float(input_scale),
+                                  int(input_zero_point), float(output_scale),
+                                  int(output_zero_point), dt(input), dt(weight), dt(output)))
+
+
+def packed_linear(x, words, scales, bias, y, *, weight_bits=8, group_size=128,
+                  activation_bits=8, first_unit=0, unit_count=0) -> int:
+    """PackedLinear through the ``cuda_graph_llm_f32`` drop-in: builds the reference's
+    VxLLMOpArgs descriptor (kind=1036, key_dim=K, value_dim=N, rate=group size,
+    groups=weight bits, normalize=activation bits, batch*sequence=rows) and calls the C
+    entry. ``y`` (fp32 [rows,N]) is written in place inside the window. Returns 1/0/-1."""
+    L = _lib.load()
+    for a, t in ((x, np.float32), (scales, np.float32), (y, np.float32)):
+        if a.dtype != t or not a.flags.c_contiguous:
+            raise TypeError("x, scales and y must be contiguous float32 arrays")
+    words = np.ascontiguousarray(words).view(np.int32)
+    rows, k = x.shape
+    a = LLMOpArgs()
+    a.kind, a.batch, a.sequence = OP_PACKED_LINEAR, 1, rows
+    a.key_dim, a.value_dim = k, words.shape[0]
+    a.groups, a.rate, a.normalize = weight_bits, group_size, activation_bits
+    a.x[0], a.x[1], a.x[2] = x.ctypes.data, words.ctypes.data, scales.ctypes.data
+    a.x[3] = bias.ctypes.data if bias is not None else None
+    a.y[0] = y.ctypes.data
+    a.x_elements[0], a.x_elements[1], a.x_elements[2] = x.size, words.size, scales.size
+    a.y_elements[0] = y.size
+    a.first_unit, a.unit_count = first_unit, unit_count
+    keep = (x, words, scales, bias, y)  # noqa: F841  (alive across the call)
+    return int(L.vxb_cuda_graph_llm_f32(C.byref(a)))
+
+
+def packed_linear_decode(x, words, scales, bias, y, *, weight_bits=8, activation_bits=8) -> int:
+    """One-row decode entry (``cuda_graph_packed_linear_decode_f32``), group size 128."""
+    L = _lib.load()
+    words = np.ascontiguousarray(words).view(np.int32)
+    return int(L.vxb_cuda_graph_packed_linear_decode_f32(
+        _ptr(x), _ptr(words), _ptr(scales), _ptr(bias), _ptr(y), x.shape[-1], words.shape[0],
+        weight_bits, activation_bits))
+
+
+def host_cache_clear() -> None:
+    _lib.load().vxb_host_cache_clear()
