@@ -1,0 +1,441 @@
+#!/usr/bin/env python3
+"""Benchmark of the W8A8 linear hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W]            # this repository's CUDA route
+    python bench.py --impl reference [--gpus N] [--steps K] [--warmup W]   # reference CPU route
+
+A step is one pass of the hot path (per-token quantize -> int8 GEMM -> fused epilogue) over
+one batch of synthetic input.  Default workload: the compute-bound GEMM of the benchmark
+configurations, M=8192 tokens, K=4096, N=14336, requantizing (int8) epilogue, with the
+output channels N sharded across the GPUs of one node and an NCCL all-gather of the int8
+output slabs when N > 1 GPU.  Rank 0 prints ONE JSON line.
+
+  value      2*M*K*N / step time, inputs resident in HBM, CUDA events on the launching
+             stream, max over ranks (includes the all-gather when n_gpus > 1)
+  e2e        the same metric through the host-pointer entry vxb_linear_host: pinned host
+             buffers, host->device and device->host copies inside the timed region
+  roofline   the tcgen05 GEMM kernel alone, timed live by event pairs inside the timed loop
+  cpu_baseline  the reference's own CPU kernels (oracle/_ref) on this box's host cores, on a
+             bounded row sample of the same workload (rank 0, N=1 only)
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from volvoxai_b200 import workloads as wl  # noqa: E402
+
+NOMINAL_I8_TOPS = 4500.0
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        d["_source"] = "measured"
+        return d
+    d = dict(FALLBACK_PEAKS)
+    d["_source"] = "fallback"
+    return d
+
+
+# ---------------------------------------------------------------------------------------------
+# clocks: NVML sampling thread (read-only) during the timed region
+# ---------------------------------------------------------------------------------------------
+class ClockSampler:
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
+               0x4: "sw_power_cap", 0x80: "hw_power_brake", 0x2: "applications_clocks_setting"}
+
+    def __init__(self, device_index: int, period_s: float = 0.005):
+        self.samples, self.reasons, self.power = [], set(), []
+        self.period = period_s
+        self._stop = threading.Event()
+        self._thread = None
+        self.max_mhz = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = device_index
+            if visible:
+                ids = [v.strip() for v in visible.split(",") if v.strip()]
+                if device_index < len(ids) and ids[device_index].isdigit():
+                    phys = int(ids[device_index])
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _once(self):
+        try:
+            self.samples.append(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM))
+            mask = self.nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+            for bit, name in self.REASONS.items():
+                if mask & bit:
+                    self.reasons.add(name)
+            self.power.append(self.nv.nvmlDeviceGetPowerUsage(self.h) / 1000.0)
+        except Exception:
+            pass
+
+    def _run(self):
+        while not self._stop.is_set():
+            self._once()
+            self._stop.wait(self.period)
+
+    def start(self):
+        if self.nv is None:
+            return
+        self._stop.clear()
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+
+    def sample_now(self):
+        if self.nv is not None:
+            self._once()
+
+    def stop(self):
+        if self._thread is not None:
+            self._stop.set()
+            self._thread.join()
+            self._thread = None
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["unavailable"]}
+        return {"sm_mhz": float(np.median(self.samples)), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples),
+                "power_w_max": max(self.power) if self.power else None}
+
+
+# ---------------------------------------------------------------------------------------------
+# reference / CPU legs
+# ---------------------------------------------------------------------------------------------
+def cpu_reference_run(rows, k, n, steps, warmup, budget_s=None, seed=0):
+    """Times the reference's own CPU kernels on a row sample of the workload: per-row int8
+    preparation (vx_packed_prepare_i8_*) + packed int8 GEMM with requantization
+    (vx_qlinear_i8u8_packed), all host threads through the reference's thread pool.
+    Falls back to the scalar oracle port when oracle/_ref was not built."""
+    from oracle.bindings import Oracle, Ref
+    cores = os.cpu_count() or 1
+    x = wl.gemm_activations(rows, k, seed)
+    w, ws = wl.gemm_weights(n, k, seed)
+    zeros = np.zeros(n, np.int32)
+    ops = 2.0 * rows * k * n
+    if Ref.available():
+        ref = Ref()
+        got = ref.threads_enter(cores)
+        threads = got if got > 0 else 1
+        packed = ref.pack_q8(w)
+        q = np.zeros((rows, k), np.int8)
+        scales = np.zeros(rows, np.float32)
+        out = np.zeros((rows, n), np.int8)
+
+        def step():
+            ref.prepare_rows(x, q, scales)
+            # R2's activation scale is per tensor; the arithmetic cost does not depend on it
+            ok = ref.qlinear_packed(q, packed, np.int8, n, zeros, ws, zeros, float(scales.mean()), 0,
+                                    0.05, 0, out=out)
+            assert ok is not None
+        kind, isa = "reference", ref.isa()
+        label = (f"vx_packed_prepare_i8 + vx_qlinear_i8u8_packed (isa {isa}) on rows 0..{rows - 1} "
+                 f"of the workload, K={k}, N={n}")
+    else:
+        orc = Oracle()
+        threads = 1
+
+        def step():
+            orc.w8a8_linear(x, w, ws, requant=True, out_scale=0.05)
+        kind = "port"
+        label = f"scalar oracle port on rows 0..{rows - 1}, K={k}, N={n}"
+    for _ in range(warmup):
+        step()
+    times = []
+    t_begin = time.perf_counter()
+    for i in range(steps):
+        t0 = time.perf_counter()
+        step()
+        times.append(time.perf_counter() - t0)
+        if budget_s is not None and time.perf_counter() - t_begin > budget_s and i >= 2:
+            break
+    if kind == "reference":
+        ref.threads_leave()
+    total = float(np.sum(times))
+    return {"tops": ops * len(times) / total / 1e12, "ms_per_step": 1e3 * total / len(times),
+            "steps": len(times), "cores": threads, "kind": kind, "sample": label}
+
+
+def reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    m, k, n = args.rows, args.k, args.n
+    rows = min(m, args.cpu_rows)
+    r = cpu_reference_run(rows, k, n, args.steps, args.warmup)
+    line = {
+        "impl": "reference", "metric": "w8a8_linear_int8_tops", "value": r["tops"], "unit": "TOPS",
+        "n_gpus": args.gpus, "steps": r["steps"], "warmup": args.warmup,
+        "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+        "config": workload_config(args, 1),
+        "cpu_baseline": {"value": r["tops"], "unit": "TOPS", "cores": r["cores"], "kind": r["kind"],
+                         "sample": r["sample"]},
+        "e2e": {"value": r["tops"], "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, world):
+    return {"workload": f"w8a8_linear_gemm_M{args.rows}_K{args.k}_N{args.n}_requant_int8",
+            "rows": args.rows, "k": args.k, "n": args.n, "epilogue": "requant_int8",
+            "activations": "fp32 N(0,1), 1% outlier channels x20, per-token int8",
+            "weights": "int8 per-output-channel, N(0,0.02)-shaped codes",
+            "parallelism": f"n_shard{world}" + ("+allgather_int8" if world > 1 else ""),
+            "l2": "inputs larger than L2 (x 134 MB + W 59 MB + out 117 MB per step at N=1)"}
+
+
+# ---------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------
+def gemv_sweep(torch, ctx, w8a8, peaks, steps=40):
+    """Decode GEMV sweep (M in 1..32 x three (K,N) shapes): achieved HBM GB/s of the
+    GEMV kernel and of the whole step (quantizer + GEMV), weights rotated so that every
+    launch streams from HBM, not L2."""
+    out = []
+    for (k, n) in wl.GEMV_SHAPES:
+        copies = max(2, int(np.ceil(300e6 / (k * n))))  # > 2x L2 of distinct weights
+        rng = np.random.default_rng(k + n)
+        base_w = rng.integers(-127, 128, size=(n, k), dtype=np.int8)
+        ws = rng.uniform(0.001, 0.02, size=n).astype(np.float32)
+        weights = []
+        for c in range(copies):
+            weights.append(w8a8.Weight.from_i8(ctx, np.roll(base_w, c, axis=0), ws))
+        for rows in wl.GEMV_ROWS:
+            x = torch.from_numpy(rng.standard_normal((rows, k)).astype(np.float32)).cuda()
+            y = torch.empty((rows, n), dtype=torch.float32, device="cuda")
+            for i in range(3):
+                ctx.linear_f32(weights[i % copies], x, out=y)
+            ctx.profile(True)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(steps):
+                ctx.linear_f32(weights[i % copies], x, out=y)
+            e1.record()
+            e1.synchronize()
+            prof = ctx.profile_read()
+            ctx.profile(False)
+            algo_bytes = k * n + 4 * n + 4 * rows * k + 4 * rows * n
+            kern_s = prof["gemm_ms"] / max(1, prof["gemm_launches"]) * 1e-3
+            step_s = e0.elapsed_time(e1) / steps * 1e-3
+            out.append({"rows": rows, "k": k, "n": n,
+                        "kernel_gbs": algo_bytes / kern_s / 1e9,
+                        "kernel_frac_of_measured": algo_bytes / kern_s / 1e9 / peaks["hbm_gbs"],
+                        "kernel_frac_of_nominal_8000": algo_bytes / kern_s / 1e9 / NOMINAL_HBM_GBS,
+                        "step_gbs": algo_bytes / step_s / 1e9,
+                        "kernel_us": kern_s * 1e6, "step_us": step_s * 1e6})
+        for wt in weights:
+            wt.close()
+    return out
+
+
+def gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+    from volvoxai_b200 import w8a8
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device; there is no CPU fallback")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    peaks = measured_peaks()
+    m, k, n = args.rows, args.k, args.n
+    if n % world:
+        raise SystemExit(f"N={n} does not shard over {world} GPUs")
+    n_local = n // world
+
+    ctx = w8a8.Context(local)
+    ctx.use_torch_stream()
+
+    # weights of this rank's output-channel shard (contiguous channel range), activations replicated
+    w_local, ws_local = wl.gemm_weights(n_local, k, seed=1000 + rank)
+    weight = w8a8.Weight.from_i8(ctx, w_local, ws_local)
+    x_host_np = wl.gemm_activations(m, k, seed=0)
+    x_dev = torch.from_numpy(x_host_np).cuda()
+
+    # static output scale: 99.9th percentile |y| / 127 of the ORACLE's fp32 output on a sample
+    # (rows 0..15 x first 256 channels of rank 0's shard), broadcast to all ranks
+    out_scale_t = torch.zeros(1, dtype=torch.float32, device="cuda")
+    if rank == 0:
+        from oracle.bindings import Oracle
+        smp = Oracle().w8a8_linear(x_host_np[:16], w_local[:256], ws_local[:256])
+        out_scale_t[0] = float(wl.static_out_scale(smp["out"]))
+    if world > 1:
+        dist.broadcast(out_scale_t, 0)
+    out_scale = float(out_scale_t.item())
+
+    y_local = torch.empty((m, n_local), dtype=torch.int8, device="cuda")
+    y_all = torch.empty((world, m, n_local), dtype=torch.int8, device="cuda") if world > 1 else None
+
+    def step(gather=True):
+        ctx.linear_i8(weight, x_dev, out_scale, 0, out=y_local)
+        if world > 1 and gather:
+            dist.all_gather_into_tensor(y_all, y_local)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, count):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for _ in range(count):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+
+    sampler = ClockSampler(local)
+    launches0 = w8a8.launch_count()
+    ctx.profile(True)
+    sampler.start()
+    total_ms = timed(step, args.steps)
+    sampler.sample_now()
+    sampler.stop()
+    prof = ctx.profile_read()
+    ctx.profile(False)
+    launches = w8a8.launch_count() - launches0
+    ctx.synchronize()
+
+    ops = 2.0 * m * k * n
+    ms_per_step = total_ms / args.steps
+    value = ops / (ms_per_step * 1e-3) / 1e12
+
+    # kernel-only view (outputs left N-sharded): the same loop without the all-gather
+    nogather_ms = timed(lambda: step(False), args.steps) / args.steps if world > 1 else ms_per_step
+
+    # roofline of the dominant kernel (the tcgen05 GEMM of this rank's shard)
+    gemm_ms = prof["gemm_ms"] / max(1, prof["gemm_launches"])
+    quant_ms = prof["quantize_ms"] / max(1, prof["quantize_launches"])
+    ops_local = 2.0 * m * k * n_local
+    achieved = ops_local / (gemm_ms * 1e-3) / 1e12
+    peak = 2.0 * peaks["bf16_tflops"]
+    i8_probe = ctx.measure_i8_tensor_peak(200)
+    roofline = {
+        "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+        "frac": achieved / peak, "traffic": None,
+        "kernel": "gemm_i8_tcgen05_kernel", "kernel_ms": gemm_ms,
+        "peak_source": f"2 x bf16_tflops (cuBLAS bf16 burst, {peaks['_source']}) as the dense int8 rate",
+        "i8_probe_tops": i8_probe, "frac_of_i8_probe": achieved / i8_probe,
+        "frac_of_nominal_4500": achieved / NOMINAL_I8_TOPS,
+        "quantize_kernel_ms": quant_ms,
+        "quantize_gbs": (5.0 * m * k + 4.0 * m) / (quant_ms * 1e-3) / 1e9 if quant_ms > 0 else None,
+        "quantize_frac_of_hbm": ((5.0 * m * k + 4.0 * m) / (quant_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]
+                                 if quant_ms > 0 else None),
+    }
+    traffic_file = os.path.join(ROOT, "profiles", "gemm_tcgen05_traffic.json")
+    if os.path.exists(traffic_file):
+        with open(traffic_file) as f:
+            t = json.load(f)
+        # ncu capture of a smaller launch, scaled by tiles processed (traffic grows with tiles)
+        roofline["traffic"] = t["dram_bytes_per_tile_k4096"] * (m / 128.0) * (n_local / 256.0) * (k / 4096.0)
+        roofline["traffic_source"] = t["source"]
+
+    # end to end through the host-pointer entry: pinned host buffers, copies inside the region
+    x_pin = torch.from_numpy(x_host_np).pin_memory()
+    y_pin = torch.empty((m, n_local), dtype=torch.int8).pin_memory()
+    e2e_steps = max(3, min(args.steps, 20))
+    for _ in range(2):
+        ctx.linear_host(weight, x_pin, y_pin, requant=True, out_scale=out_scale)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        ctx.linear_host(weight, x_pin, y_pin, requant=True, out_scale=out_scale)
+    barrier()
+    e2e_s = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
+    e2e_ms = float(e2e_s.item()) * 1e3 / e2e_steps
+    # the host result must equal the device-resident result
+    same = bool(torch.equal(y_pin.cuda(), y_local))
+    e2e = {"value": ops / (e2e_ms * 1e-3) / 1e12, "unit": "TOPS", "ms_per_step": e2e_ms,
+           "steps": e2e_steps, "h2d_bytes_per_step": int(x_pin.numel() * 4) * world,
+           "d2h_bytes_per_step": int(y_pin.numel()) * world, "api": "vxb_linear_host",
+           "matches_device_result": same}
+
+    line = {
+        "metric": "w8a8_linear_int8_tops", "value": value, "unit": "TOPS", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8",
+        "data": "synthetic", "config": workload_config(args, world),
+        "clocks": sampler.summary(), "e2e": e2e, "gpu_launches": int(launches),
+        "roofline": roofline,
+        "kernel_only": {"value": ops / (nogather_ms * 1e-3) / 1e12, "unit": "TOPS",
+                        "ms_per_step": nogather_ms, "note": "outputs left N-sharded (no all-gather)"},
+    }
+
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        r = cpu_reference_run(min(m, args.cpu_rows), k, n, steps=1000, warmup=1, budget_s=args.cpu_seconds)
+        line["cpu_baseline"] = {"value": r["tops"], "unit": "TOPS", "cores": r["cores"],
+                                "kind": r["kind"], "sample": r["sample"] + f", {r['steps']} repeats"}
+    elif rank == 0:
+        line["cpu_baseline"] = None
+    if rank == 0 and world == 1 and not args.no_extras:
+        line["extras"] = {"gemv_sweep": gemv_sweep(torch, ctx, w8a8, peaks)}
+
+    weight.close()
+    ctx.close()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--rows", type=int, default=8192)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--n", type=int, default=14336)
+    ap.add_argument("--cpu-rows", type=int, default=512, help="row sample for the CPU legs")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+    else:
+        gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -152,6 +152,26 @@ VXB_API int vxb_qlinear_device(VxbContext* ctx, const VxbWeight* w, const void* 
                        int32_t output_zero_point, uint32_t input_dtype, uint32_t output_dtype,
                        void* output, uint32_t ldy, int route);
 
+/* Whole op with HOST buffers (what an application holding host tensors calls):
+ * copies x (fp32 [rows,d_in]) to the device, runs vxb_linear_i8 (requant != 0;
+ * y_host int8 [rows,d_out]) or vxb_linear_f32 (requant == 0; y_host fp32
+ * [rows,d_out]), copies the result back and waits for it.  The host-pointer
+ * convention of the reference's backend hooks
+ * (native/src/backends/cuda/host/cuda_graph_llm_host.inc:714-783) applied to the
+ * new op; pinned host memory makes the copies asynchronous DMA. */
+VXB_API int vxb_linear_host(VxbContext* ctx, const VxbWeight* w, const float* x_host, uint32_t rows,
+                    int requant, float out_scale, int32_t out_zero, void* y_host);
+
+/* Per-kernel device timing, the counterpart of the reference's instrumented
+ * replay plan (docs/cuda.md:537-556): while enabled, every quantizer launch and
+ * every GEMM/GEMV launch of this context is bracketed by CUDA events on the
+ * context's stream (at most 8192 launches of each kind are recorded).
+ * vxb_context_profile(ctx, 1) clears and starts, (ctx, 0) clears and stops;
+ * _read waits for the stream and returns summed milliseconds and launch counts. */
+VXB_API int vxb_context_profile(VxbContext* ctx, int enable);
+VXB_API int vxb_context_profile_read(VxbContext* ctx, double* quantize_ms, uint64_t* quantize_launches,
+                             double* gemm_ms, uint64_t* gemm_launches);
+
 /* Measurement utility (no counterpart in the reference): every SM issues
  * `iters` x 256 back-to-back M128xN256xK32 kind::i8 MMAs on operands resident
  * in shared memory; *tops receives the dense int8 rate in tera-ops/s (2 ops per

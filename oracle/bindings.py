@@ -241,6 +241,16 @@ class Ref:
             q[r], s[r], v[r] = self.prepare_i8(x[r])
         return q, s, v
 
+    def prepare_rows(self, x, q=None, scales=None):
+        """Quantize every row (threaded through the reference's pool when a scope is open)."""
+        x = _f32(x)
+        rows, k = x.shape
+        q = np.zeros((rows, k), np.int8) if q is None else q
+        scales = np.zeros(rows, np.float32) if scales is None else scales
+        self.lib.ref_prepare_rows(_p(x, C.c_float), C.c_uint32(rows), C.c_uint32(k),
+                                  _p(q, C.c_int8), _p(scales, C.c_float))
+        return q, scales
+
     def dot_i8(self, q, words, count, bits=8):
         q = np.ascontiguousarray(q, np.int8)
         words = np.ascontiguousarray(words).view(np.uint32)

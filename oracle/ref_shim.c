@@ -38,6 +38,19 @@ REF_API int ref_prepare_i8(const float* x, uint32_t k, int8_t* q, float* scale) 
 #endif
 }
 
+/* All rows, spread over the reference's thread pool when a scope is entered. */
+typedef struct { const float* x; uint32_t k; int8_t* q; float* scales; } RefPrepareJob;
+static void ref_prepare_range(void* opaque, int begin, int end) {
+    RefPrepareJob* job = (RefPrepareJob*)opaque;
+    for (int r = begin; r < end; r++)
+        ref_prepare_i8(job->x + (size_t)r * job->k, job->k, job->q + (size_t)r * job->k,
+                       job->scales + r);
+}
+REF_API void ref_prepare_rows(const float* x, uint32_t rows, uint32_t k, int8_t* q, float* scales) {
+    RefPrepareJob job = {x, k, q, scales};
+    vx_kernels_parallel_for((int)rows, 8, ref_prepare_range, &job);
+}
+
 REF_API int32_t ref_dot_i8(const int8_t* q, const uint32_t* words, uint32_t count, uint32_t bits) {
     return vx_packed_dot_i8(q, words, count, bits);
 }

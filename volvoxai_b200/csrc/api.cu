@@ -86,6 +86,9 @@ struct VxbContext {
     int* status = nullptr;        // device word raised by bounded waits
     int* status_host = nullptr;   // pinned mirror
     bool tcgen05_ready = false;
+    // optional per-kernel timing (event pairs on the launching stream)
+    bool profiling = false;
+    std::vector<cudaEvent_t> prof_events[2];   // [0] = K1 quantizer, [1] = GEMM / GEMV
 };
 
 struct VxbWeight {
@@ -111,6 +114,17 @@ int ensure_device(const VxbContext* ctx) {
 }
 
 void count_launch(int n = 1) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+
+constexpr size_t kMaxProfiledLaunches = 8192;
+struct ProfileScope {
+    VxbContext* ctx; int kind; bool on;
+    ProfileScope(VxbContext* c, int k) : ctx(c), kind(k), on(c->profiling && c->prof_events[k].size() < 2 * kMaxProfiledLaunches) {
+        if (on) { cudaEvent_t e; cudaEventCreate(&e); cudaEventRecord(e, ctx->stream); ctx->prof_events[kind].push_back(e); }
+    }
+    ~ProfileScope() {
+        if (on) { cudaEvent_t e; cudaEventCreate(&e); cudaEventRecord(e, ctx->stream); ctx->prof_events[kind].push_back(e); }
+    }
+};
 
 bool valid_scale(float v) { return std::isfinite(v) && v > 0.0f; }
 
@@ -160,6 +174,7 @@ Plan choose_route(const VxbContext* ctx, const VxbWeight* w, uint32_t rows, int 
 int run_gemm(VxbContext* ctx, const VxbWeight* w, const int8_t* q, uint32_t rows,
              const EpilogueParams& epi, int requested, const char* prefix) {
     const Plan plan = choose_route(ctx, w, rows, requested);
+    ProfileScope scope(ctx, 1);
     if (plan.route == VXB_ROUTE_GEMV) {
         if (rows > 32) return fail(0, "gemv route needs rows <= 32 (got %u)", rows);
         CUDA_TRY(launch_gemv(q, rows, w->w, w->d_out, w->kpad, epi, ctx->sm_count, ctx->stream), -1);
@@ -193,8 +208,11 @@ int check_common(const VxbContext* ctx, const VxbWeight* w, const void* x, const
 int quantize_into_scratch(VxbContext* ctx, const VxbWeight* w, const float* x, uint32_t rows) {
     CUDA_TRY(ctx->q.reserve((size_t)rows * w->kpad), 0);
     CUDA_TRY(ctx->row_scales.reserve((size_t)rows * 4), 0);
-    CUDA_TRY(launch_quantize_rows(x, rows, w->d_in, (int8_t*)ctx->q.ptr, w->kpad,
-                                  (float*)ctx->row_scales.ptr, nullptr, ctx->stream), -1);
+    {
+        ProfileScope scope(ctx, 0);
+        CUDA_TRY(launch_quantize_rows(x, rows, w->d_in, (int8_t*)ctx->q.ptr, w->kpad,
+                                      (float*)ctx->row_scales.ptr, nullptr, ctx->stream), -1);
+    }
     count_launch();
     return 1;
 }
@@ -234,6 +252,7 @@ void vxb_context_destroy(VxbContext* ctx) {
     if (!ctx) return;
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
+    for (auto& v : ctx->prof_events) { for (cudaEvent_t e : v) cudaEventDestroy(e); v.clear(); }
     ctx->q.release(); ctx->row_scales.release(); ctx->bias_eff.release();
     ctx->stage_in.release(); ctx->stage_out.release();
     if (ctx->status) cudaFree(ctx->status);
@@ -434,6 +453,54 @@ int vxb_qlinear_device(VxbContext* ctx, const VxbWeight* w, const void* input, u
     epi.out_zero = output_zero_point; epi.out_lo = out_u8 ? 0 : -128; epi.out_hi = out_u8 ? 255 : 127;
     epi.out = output; epi.ld = ldy;
     return run_gemm(ctx, w, (const int8_t*)ctx->q.ptr, rows, epi, route, "static+");
+}
+
+int vxb_context_profile(VxbContext* ctx, int enable) {
+    if (!ctx) return fail(0, "null context");
+    if (ensure_device(ctx) != 1) return -1;
+    for (auto& v : ctx->prof_events) { for (cudaEvent_t e : v) cudaEventDestroy(e); v.clear(); }
+    ctx->profiling = enable != 0;
+    return 1;
+}
+
+int vxb_context_profile_read(VxbContext* ctx, double* quantize_ms, uint64_t* quantize_launches,
+                             double* gemm_ms, uint64_t* gemm_launches) {
+    if (!ctx) return fail(0, "null context");
+    if (ensure_device(ctx) != 1) return -1;
+    CUDA_TRY(cudaStreamSynchronize(ctx->stream), -1);
+    double ms[2] = {0.0, 0.0}; uint64_t n[2] = {0, 0};
+    for (int k = 0; k < 2; k++) {
+        auto& v = ctx->prof_events[k];
+        for (size_t i = 0; i + 1 < v.size(); i += 2) {
+            float t = 0.0f;
+            if (cudaEventElapsedTime(&t, v[i], v[i + 1]) == cudaSuccess) { ms[k] += t; n[k]++; }
+        }
+    }
+    if (quantize_ms) *quantize_ms = ms[0];
+    if (quantize_launches) *quantize_launches = n[0];
+    if (gemm_ms) *gemm_ms = ms[1];
+    if (gemm_launches) *gemm_launches = n[1];
+    return 1;
+}
+
+int vxb_linear_host(VxbContext* ctx, const VxbWeight* w, const float* x_host, uint32_t rows,
+                    int requant, float out_scale, int32_t out_zero, void* y_host) {
+    if (!ctx || !w || !x_host || !y_host) return fail(0, "null argument");
+    if (!rows) return 1;
+    if (ensure_device(ctx) != 1) return -1;
+    const size_t in_bytes = (size_t)rows * w->d_in * 4;
+    const size_t out_bytes = (size_t)rows * w->d_out * (requant ? 1 : 4);
+    CUDA_TRY(ctx->stage_in.reserve(in_bytes), 0);
+    CUDA_TRY(ctx->stage_out.reserve(out_bytes), 0);
+    CUDA_TRY(cudaMemcpyAsync(ctx->stage_in.ptr, x_host, in_bytes, cudaMemcpyHostToDevice, ctx->stream), -1);
+    int rc = requant
+        ? vxb_linear_i8(ctx, w, (const float*)ctx->stage_in.ptr, rows, out_scale, out_zero,
+                        (int8_t*)ctx->stage_out.ptr, w->d_out, VXB_ROUTE_AUTO)
+        : vxb_linear_f32(ctx, w, (const float*)ctx->stage_in.ptr, rows, (float*)ctx->stage_out.ptr,
+                         w->d_out, VXB_ROUTE_AUTO);
+    if (rc != 1) return rc;
+    CUDA_TRY(cudaMemcpyAsync(y_host, ctx->stage_out.ptr, out_bytes, cudaMemcpyDeviceToHost, ctx->stream), -1);
+    return vxb_context_synchronize(ctx) == 1 ? 1 : -1;
 }
 
 int vxb_measure_i8_tensor_peak(VxbContext* ctx, uint32_t iters, double* tops) {

@@ -78,6 +78,26 @@ class Context:
         _check(self._L.vxb_measure_i8_tensor_peak(self.handle, iters, C.byref(out)))
         return out.value
 
+    def profile(self, enable: bool) -> None:
+        """Start (True) or stop (False) per-kernel event timing; both clear the record."""
+        _check(self._L.vxb_context_profile(self.handle, 1 if enable else 0))
+
+    def profile_read(self) -> dict:
+        qms, qn, gms, gn = C.c_double(0), C.c_uint64(0), C.c_double(0), C.c_uint64(0)
+        _check(self._L.vxb_context_profile_read(self.handle, C.byref(qms), C.byref(qn),
+                                                C.byref(gms), C.byref(gn)))
+        return {"quantize_ms": qms.value, "quantize_launches": qn.value,
+                "gemm_ms": gms.value, "gemm_launches": gn.value}
+
+    def linear_host(self, w: "Weight", x_host, y_host, requant: bool = False,
+                    out_scale: float = 1.0, out_zero: int = 0) -> None:
+        """Whole op on HOST buffers (NumPy arrays or pinned torch CPU tensors):
+        h2d copy, kernels, d2h copy, wait."""
+        rows = x_host.shape[0]
+        _check(self._L.vxb_linear_host(self.handle, w.handle, _ptr(x_host), rows,
+                                       1 if requant else 0, float(out_scale), int(out_zero),
+                                       _ptr(y_host)))
+
     def close(self) -> None:
         if getattr(self, "handle", None):
             self._L.vxb_context_destroy(self.handle)

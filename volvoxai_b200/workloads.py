@@ -80,34 +80,45 @@ def gemv_case(rows, k, n, seed=0):
     return {"x": x, "w": w, "ws": ws, "bias": None}
 
 
-def gemm_case(rows, k, n, seed=0, weights_fast=False):
-    """Configuration 5: x~N(0,1) with 1% outlier channels x20; W~N(0,0.02) per channel.
-
-    ``weights_fast`` draws the int8 codes directly (|N(0,1)|-shaped codes with the
-    per-channel maximum pinned at 127) instead of authoring from fp32, for the
-    multi-GB shapes where materialising an fp32 master is wasteful; the value
-    distribution of codes and scales is the same.
-    """
-    rng = np.random.default_rng(seed)
+def gemm_activations(rows, k, seed=0):
+    """Configuration 5 activations: N(0,1) with a fixed random 1% of the K channels x20."""
+    rng = np.random.default_rng([seed, 0xA])
     x = rng.standard_normal((rows, k), dtype=np.float32)
     outliers = rng.choice(k, size=max(1, k // 100), replace=False)
     x[:, outliers] *= np.float32(20.0)
+    return x
+
+
+def gemm_weights(n, k, seed=0):
+    """Configuration 5 weights for n output channels, drawn directly as int8 codes with the
+    distribution per-channel quantization of N(0,0.02) produces (|code| max pinned at 127,
+    scale = channel absmax/127 with absmax ~ 4.2 sigma), without an fp32 master."""
+    rng = np.random.default_rng([seed, 0xB])
+    w = np.empty((n, k), np.int8)
+    step = max(1, (1 << 25) // k)
+    for lo in range(0, n, step):
+        hi = min(n, lo + step)
+        z = rng.standard_normal((hi - lo, k), dtype=np.float32)
+        z *= np.float32(127.0 / 4.2)
+        np.clip(np.rint(z, out=z), -127, 127, out=z)
+        w[lo:hi] = z.astype(np.int8)
+    w[:, 0] = 127
+    ws = (np.float32(0.02 * 4.2 / 127.0) * rng.uniform(0.9, 1.1, size=n)).astype(np.float32)
+    return w, ws
+
+
+def gemm_case(rows, k, n, seed=0, weights_fast=False):
+    """Configuration 5: x~N(0,1) with 1% outlier channels x20; W~N(0,0.02) per channel.
+    ``weights_fast`` draws the int8 codes directly (gemm_weights) instead of authoring from
+    an fp32 master, for the multi-GB shapes."""
+    x = gemm_activations(rows, k, seed)
     if weights_fast:
-        w = np.empty((n, k), np.int8)
-        step = max(1, (1 << 26) // k)
-        for lo in range(0, n, step):
-            hi = min(n, lo + step)
-            z = rng.standard_normal((hi - lo, k), dtype=np.float32)
-            z *= np.float32(127.0 / 4.2)
-            np.clip(np.rint(z, out=z), -127, 127, out=z)
-            w[lo:hi] = z.astype(np.int8)
-        w[:, 0] = 127
-        ws = np.full(n, np.float32(0.02 * 4.2 / 127.0), np.float32)
-        ws *= rng.uniform(0.9, 1.1, size=n).astype(np.float32)
+        w, ws = gemm_weights(n, k, seed)
     else:
-        wf = rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02)
+        wf = (np.random.default_rng([seed, 0xC]).standard_normal((n, k), dtype=np.float32)
+              * np.float32(0.02))
         w, ws = quantize_weight_per_channel(wf)
-    return {"x": x, "w": w, "ws": ws, "bias": None, "outliers": outliers}
+    return {"x": x, "w": w, "ws": ws, "bias": None}
 
 
 def static_out_scale(y: np.ndarray) -> np.float32:
