@@ -210,42 +210,59 @@ def workload_config(args, world):
 # ---------------------------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------------------------
-def gemv_sweep(torch, ctx, w8a8, peaks, steps=40):
-    """Decode GEMV sweep (M in 1..32 x three (K,N) shapes): achieved HBM GB/s of the
-    GEMV kernel and of the whole step (quantizer + GEMV), weights rotated so that every
-    launch streams from HBM, not L2."""
+def gemv_sweep(torch, ctx, w8a8, peaks, launches=24, replays=5):
+    """Decode sweep (M in 1..32 x three (K,N) shapes).  Per case: the skinny kernel alone
+    (prepared activations) for both small-M routes, and the whole step (quantizer + kernel).
+    Each measurement replays a CUDA graph of `launches` back-to-back launches between two
+    events, so host launch cost is not in the number.  Weights rotate through more than 2x L2
+    of distinct copies, so every launch streams from HBM."""
     out = []
+    routes = {"decode_tcgen05": w8a8.ROUTE_DECODE, "gemv_dp4a": w8a8.ROUTE_GEMV}
+    side = torch.cuda.Stream()
+
+    def graph_ms(fn):
+        """ms per launch of fn(i), i = 0..launches-1, replayed from a CUDA graph."""
+        for i in range(3):
+            fn(i)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            ctx.use_torch_stream()
+            for i in range(launches):
+                fn(i)
+        ctx.use_torch_stream()
+        g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(replays):
+            g.replay()
+        e1.record()
+        e1.synchronize()
+        return e0.elapsed_time(e1) / (launches * replays)
+
     for (k, n) in wl.GEMV_SHAPES:
-        copies = max(2, int(np.ceil(300e6 / (k * n))))  # > 2x L2 of distinct weights
+        copies = max(2, int(np.ceil(300e6 / (k * n))))
         rng = np.random.default_rng(k + n)
         base_w = rng.integers(-127, 128, size=(n, k), dtype=np.int8)
         ws = rng.uniform(0.001, 0.02, size=n).astype(np.float32)
-        weights = []
-        for c in range(copies):
-            weights.append(w8a8.Weight.from_i8(ctx, np.roll(base_w, c, axis=0), ws))
+        weights = [w8a8.Weight.from_i8(ctx, np.roll(base_w, c, axis=0), ws) for c in range(copies)]
         for rows in wl.GEMV_ROWS:
             x = torch.from_numpy(rng.standard_normal((rows, k)).astype(np.float32)).cuda()
             y = torch.empty((rows, n), dtype=torch.float32, device="cuda")
-            for i in range(3):
-                ctx.linear_f32(weights[i % copies], x, out=y)
-            ctx.profile(True)
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for i in range(steps):
-                ctx.linear_f32(weights[i % copies], x, out=y)
-            e1.record()
-            e1.synchronize()
-            prof = ctx.profile_read()
-            ctx.profile(False)
+            q, sc = ctx.prepare(weights[0], x)
             algo_bytes = k * n + 4 * n + 4 * rows * k + 4 * rows * n
-            kern_s = prof["gemm_ms"] / max(1, prof["gemm_launches"]) * 1e-3
-            step_s = e0.elapsed_time(e1) / steps * 1e-3
-            out.append({"rows": rows, "k": k, "n": n,
-                        "kernel_gbs": algo_bytes / kern_s / 1e9,
-                        "kernel_frac_of_measured": algo_bytes / kern_s / 1e9 / peaks["hbm_gbs"],
-                        "kernel_frac_of_nominal_8000": algo_bytes / kern_s / 1e9 / NOMINAL_HBM_GBS,
-                        "step_gbs": algo_bytes / step_s / 1e9,
-                        "kernel_us": kern_s * 1e6, "step_us": step_s * 1e6})
+            rec = {"rows": rows, "k": k, "n": n, "algorithmic_bytes": algo_bytes}
+            for name, route in routes.items():
+                ms = graph_ms(lambda i, route=route: ctx.linear_prepared(
+                    weights[i % copies], q, sc, y, mode=1, route=route))
+                rec[name] = {"kernel_us": ms * 1e3, "gbs": algo_bytes / (ms * 1e-3) / 1e9,
+                             "frac_of_measured": algo_bytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                             "frac_of_nominal_8000": algo_bytes / (ms * 1e-3) / 1e9 / NOMINAL_HBM_GBS}
+            ms = graph_ms(lambda i: ctx.linear_f32(weights[i % copies], x, out=y))
+            rec["step_auto"] = {"route": w8a8.last_route(), "step_us": ms * 1e3,
+                                "gbs": algo_bytes / (ms * 1e-3) / 1e9}
+            out.append(rec)
         for wt in weights:
             wt.close()
     return out

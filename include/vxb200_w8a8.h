@@ -56,9 +56,10 @@ typedef struct VxbWeight VxbWeight;   /* one linear's weights, repacked once */
 /* Kernel route selection for vxb_linear_* (VXB_ROUTE_AUTO in production). */
 enum {
     VXB_ROUTE_AUTO = 0,
-    VXB_ROUTE_GEMV = 1,     /* bandwidth-bound small-M path (rows <= 32) */
+    VXB_ROUTE_GEMV = 1,     /* dp4a + warp-shuffle GEMV (rows <= 32) */
     VXB_ROUTE_TCGEN05 = 2,  /* TMA-fed tcgen05 kind::i8 GEMM, TMEM accumulators */
-    VXB_ROUTE_SIMT = 3      /* one-thread-per-output dp4a kernel (verification) */
+    VXB_ROUTE_SIMT = 3,     /* one-thread-per-output dp4a kernel (verification) */
+    VXB_ROUTE_DECODE = 4    /* weight-streaming stream-K tcgen05 kernel (rows <= 128) */
 };
 
 VXB_API uint32_t vxb_abi_version(void);
@@ -142,6 +143,17 @@ VXB_API int vxb_linear_i8(VxbContext* ctx, const VxbWeight* w, const float* x, u
  * (native/src/kernels/packed_linear_ops.inc:483-493). */
 VXB_API int vxb_linear_acc_i32(VxbContext* ctx, const VxbWeight* w, const float* x, uint32_t rows,
                        int32_t* acc, int8_t* q_out, float* scales_out, int route);
+
+/* Prepared-activation form, the counterpart of the reference's prepared path
+ * (x[4] prepared words / x[5] row scales, native/src/backends/cuda/host/
+ * cuda_graph_llm_host.inc:15-107): the caller quantized the rows itself with
+ * vxb_quantize_rows into q with row stride vxb_weight_row_bytes(w) (bytes past
+ * d_in zero) and passes the row scales.  mode 0: int32 accumulators, 1: fp32
+ * (E1), 2: int8 (E2, uses out_scale / out_zero).  ldy in elements of `out`. */
+VXB_API uint32_t vxb_weight_row_bytes(const VxbWeight* w);
+VXB_API int vxb_linear_prepared(VxbContext* ctx, const VxbWeight* w, const int8_t* q,
+                        const float* row_scales, uint32_t rows, int mode, float out_scale,
+                        int32_t out_zero, void* out, uint32_t ldy, int route);
 
 /* Static-activation QLinear on device buffers: int8/uint8 input with one
  * per-tensor scale and zero point, int8/uint8 output.  Device twin of

@@ -53,6 +53,11 @@ class Oracle:
         L.vxo_qlinear_i8u8.restype = C.c_int
         L.vxo_packed_linear_w8_grouped.restype = C.c_int
         L.vxo_w8a8_linear.restype = C.c_int
+        L.vxo_div_const_mismatches.restype = C.c_uint64
+        L.vxo_div_const_mismatches.argtypes = [C.c_float, C.c_uint64, C.c_uint64, C.c_int, C.c_int]
+
+    def div_const_mismatches(self, d, count, seed=1, lo_exp=-60, hi_exp=60):
+        return int(self.lib.vxo_div_const_mismatches(float(np.float32(d)), count, seed, lo_exp, hi_exp))
 
     def round_i8(self, v):
         return int(self.lib.vxo_round_i8(float(np.float32(v))))

@@ -263,3 +263,32 @@ VXO_API int vxo_w8a8_linear(const float* x, uint64_t rows, uint32_t k, uint32_t 
     return vxo_requant_rows(scratch_acc, rows, n, row_scales, valid, ws, bias_i32,
                             out_scale, out_zero, 0, (uint8_t*)out);
 }
+
+/* Checker for the constant-divisor division the CUDA epilogues use (no
+ * counterpart in the reference, which divides with the IEEE operator): computes
+ * a/d through rcp = RN(1/d) and two FMA corrections and counts disagreements
+ * with the correctly rounded quotient over `count` pseudo-random positive a
+ * whose exponents are uniform in [lo_exp, hi_exp]. */
+#include <math.h>
+VXO_API uint64_t vxo_div_const_mismatches(float d, uint64_t count, uint64_t seed,
+                                          int lo_exp, int hi_exp) {
+    const float rcp = (float)(1.0 / (double)d);
+    uint64_t bad = 0, state = seed * 6364136223846793005ull + 1442695040888963407ull;
+    for (uint64_t i = 0; i < count; i++) {
+        state = state * 6364136223846793005ull + 1442695040888963407ull;
+        const uint32_t mant = (uint32_t)(state >> 41);                 /* 23 bits */
+        const int span = hi_exp - lo_exp + 1;
+        const int e = lo_exp + (int)((state >> 20) % (uint64_t)span);
+        union { uint32_t u; float f; } a;
+        a.u = ((uint32_t)(e + 127) << 23) | mant;
+        volatile float want = a.f / d;
+        const float q0 = a.f * rcp;
+        const float r0 = fmaf(-d, q0, a.f);
+        const float q1 = fmaf(r0, rcp, q0);
+        const float r1 = fmaf(-d, q1, a.f);
+        const float q2 = fmaf(r1, rcp, q1);
+        union { float f; uint32_t u; } x, y; x.f = q2; y.f = want;
+        bad += x.u != y.u;
+    }
+    return bad;
+}

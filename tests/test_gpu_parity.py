@@ -38,7 +38,7 @@ def rel_err(y, ref):
     return float(np.abs(y[ok].astype(np.float64) - ref[ok]).max() / max(rms, 1e-30)) if ok.any() else 0.0
 
 
-ROUTES = {"gemv": 1, "tcgen05": 2, "simt": 3}
+ROUTES = {"gemv": 1, "tcgen05": 2, "simt": 3, "decode": 4}
 
 
 def run_case(torch, ctx, oracle, case, routes, bias_i32=None, out_zero=0):
@@ -149,7 +149,40 @@ def test_small_m_routes(torch, ctx, oracle, rows, k, n):
     if rows > 4:
         case["x"][3, k // 3] = np.inf
     bias_i32 = rng.integers(-300, 300, size=n).astype(np.int32)
-    run_case(torch, ctx, oracle, case, ["gemv", "tcgen05", "simt"], bias_i32=bias_i32, out_zero=-3)
+    run_case(torch, ctx, oracle, case, ["gemv", "decode", "tcgen05", "simt"], bias_i32=bias_i32, out_zero=-3)
+
+
+@pytest.mark.parametrize("rows", [33, 48, 64, 65, 100, 127, 128])
+@pytest.mark.parametrize("k,n", [(64, 19), (576, 192), (1024, 3072), (3072, 1024), (4096, 520)])
+def test_decode_route_up_to_128_rows(torch, ctx, oracle, rows, k, n):
+    """The weight-streaming stream-K kernel with 64 and 128 token slots, split over every SM
+    (partial tiles meet in the integer workspace) - bit-exact for any split."""
+    rng = np.random.default_rng(rows * 31 + k + n)
+    case = {"x": (rng.standard_normal((rows, k)) * rng.uniform(0.01, 30, size=(rows, 1))).astype(np.float32),
+            "w": rng.integers(-128, 128, size=(n, k), dtype=np.int8),
+            "ws": rng.uniform(0.001, 0.02, size=n).astype(np.float32),
+            "bias": rng.standard_normal(n).astype(np.float32)}
+    case["x"][1] = 0
+    case["x"][rows - 2, k // 3] = np.inf
+    run_case(torch, ctx, oracle, case, ["decode", "tcgen05"],
+             bias_i32=rng.integers(-300, 300, size=n).astype(np.int32), out_zero=7)
+
+
+def test_decode_route_leaves_its_workspace_clean(torch, ctx, oracle):
+    """Back-to-back calls of different shapes share the split-K workspace; every call must
+    find it zero (the finishing CTA clears what it consumed)."""
+    from volvoxai_b200 import w8a8
+    rng = np.random.default_rng(77)
+    shapes = [(8, 4096, 4096), (32, 4096, 1024), (1, 14336, 512), (64, 1024, 3072), (8, 4096, 4096)]
+    for (rows, k, n) in shapes:
+        c = wl.gemv_case(rows, k, n, seed=int(rng.integers(1 << 30)))
+        want = oracle.w8a8_linear(c["x"], c["w"], c["ws"])
+        weight = w8a8.Weight.from_i8(ctx, c["w"], c["ws"])
+        for _ in range(3):
+            acc = ctx.linear_acc_i32(weight, dev(torch, c["x"]), route=4)
+            ctx.synchronize()
+            assert np.array_equal(acc.cpu().numpy(), want["acc"])
+        weight.close()
 
 
 @pytest.mark.parametrize("rows,k,n", [
@@ -177,7 +210,7 @@ def test_extreme_codes_do_not_overflow(torch, ctx, oracle):
     case = {"x": x, "w": np.full((n, k), -128, np.int8), "ws": np.full(n, 0.01, np.float32), "bias": None}
     run_case(torch, ctx, oracle, case, ["tcgen05"])
     case["x"] = x[:8]
-    run_case(torch, ctx, oracle, case, ["gemv"])
+    run_case(torch, ctx, oracle, case, ["gemv", "decode"])
 
 
 def test_output_row_stride(torch, ctx, oracle):
@@ -244,7 +277,7 @@ def test_static_qlinear_dtypes_vs_oracle(torch, ctx, oracle, in_u8, out_u8):
         ozp = -ozp // 10
     want = oracle.qlinear_i8u8(x, w, b, ws, np.zeros(n, np.int32), 0.05, izp, 0.6, ozp, out_unsigned=out_u8)
     weight = w8a8.Weight.from_i8(ctx, w, ws, bias_i32=b)
-    for rws, route in ((rows, 2), (rows, 3), (8, 1)):
+    for rws, route in ((rows, 2), (rows, 3), (rows, 4), (8, 1)):
         out = ctx.qlinear_device(weight, dev(torch, x[:rws]), 0.05, izp, 0.6, ozp, out_unsigned=out_u8, route=route)
         ctx.synchronize()
         assert np.array_equal(out.cpu().numpy(), want[:rws])

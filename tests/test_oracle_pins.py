@@ -191,3 +191,33 @@ def test_requant_rows_equals_per_row_qlinear(oracle, ref):
         want = ref.qlinear_portable(res["q"][m:m + 1], c["w"], bias_i32, c["ws"], z,
                                     float(res["row_scales"][m]), 0, float(os_), 3)
         assert np.array_equal(got[m], want[0])
+
+
+def test_constant_divisor_division_is_correctly_rounded(oracle):
+    """The CUDA requantizing epilogue divides f32(as*ws) by the constant out_scale through a
+    precomputed reciprocal and two FMA corrections when as, ws and out_scale all lie in
+    [2^-30, 2^30] and out_scale's significand is not all ones. Inside that guard the result
+    must equal the IEEE quotient the reference computes, bit for bit."""
+    rng = np.random.default_rng(3)
+    divisors = [0.05, 0.0745, 1.0, 3.0, 0.75, 2.0 ** -30, 2.0 ** 30, 1.9999998, 1.0000001,
+                0.33333334, 7.0, 1e-3]
+    divisors += list(np.exp2(rng.uniform(-30, 30, size=40)).astype(np.float32))
+    for d in divisors:
+        bits = np.float32(d).view(np.uint32)
+        if (bits & 0x7fffff) == 0x7fffff:
+            continue  # the host routes such divisors to the IEEE divide
+        assert oracle.div_const_mismatches(d, 400000, seed=int(bits) | 1) == 0, d
+
+
+def test_constant_divisor_division_for_the_quantizer(oracle):
+    """The CUDA quantizer divides a whole row by its scale the same way (guard: scale in
+    [2^-60, 2^60], significand not all ones). Quotients that can round to a non-zero code
+    (|x| >= scale * 2^-20) must match the IEEE divide bit for bit."""
+    rng = np.random.default_rng(4)
+    for e in list(range(-60, 61, 6)):
+        for _ in range(3):
+            d = np.float32(np.exp2(e) * rng.uniform(1.0, 1.9999))
+            if (d.view(np.uint32) & 0x7fffff) == 0x7fffff:
+                continue
+            lo = int(np.floor(np.log2(float(d)))) - 20
+            assert oracle.div_const_mismatches(d, 200000, seed=e * 7 + 1000, lo_exp=lo, hi_exp=lo + 28) == 0, d

@@ -17,8 +17,8 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 ROOT = os.path.dirname(PKG)
 LIB = os.path.join(PKG, "libvxb200.so")
-SOURCES = ["api.cu", "quantize.cu", "gemv.cu", "gemm_tcgen05.cu"]
-HEADERS = [os.path.join(CSRC, "common.cuh"), os.path.join(ROOT, "include", "vxb200_w8a8.h")]
+SOURCES = ["api.cu", "quantize.cu", "gemv.cu", "gemm_tcgen05.cu", "decode_tcgen05.cu"]
+HEADERS = [os.path.join(CSRC, "common.cuh"), os.path.join(CSRC, "tcgen05.cuh"), os.path.join(ROOT, "include", "vxb200_w8a8.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -83,6 +83,7 @@ struct VxbContext {
     cudaStream_t stream = nullptr;
     int sm_count = 0;
     Buffer q, row_scales, bias_eff, stage_in, stage_out;
+    Buffer splitk_ws, splitk_counters;   // zero between calls (the decode kernel cleans up)
     int* status = nullptr;        // device word raised by bounded waits
     int* status_host = nullptr;   // pinned mirror
     bool tcgen05_ready = false;
@@ -99,9 +100,11 @@ struct VxbWeight {
     float* bias_f32 = nullptr; // [d_out] or null
     int32_t* bias_i32 = nullptr;
     int32_t* wsum = nullptr;   // [d_out] sum of codes per channel
-    CUtensorMap tmap_b;        // box 256 rows
+    CUtensorMap tmap_b;        // box 256 rows (large-M kernel)
+    CUtensorMap tmap_w128;     // box 128 rows (decode kernel)
     bool has_tmap = false;
     uint64_t bytes = 0;
+    float ws_min = 0.0f, ws_max = 0.0f;  // range of the per-channel scales
 };
 
 namespace {
@@ -128,12 +131,22 @@ struct ProfileScope {
 
 bool valid_scale(float v) { return std::isfinite(v) && v > 0.0f; }
 
+// The requantizing epilogue may divide by out_scale through its precomputed reciprocal
+// (div_const) when every operand stays far from the exponent limits and out_scale's
+// significand is not all ones; otherwise the kernels use the IEEE divide.
+void set_requant_divisor(EpilogueParams& epi, const VxbWeight* w, float out_scale);
+
 // Finish building a weight whose int8 rows already sit (unpadded) in `staging` on the device.
 int finish_weight(VxbContext* ctx, VxbWeight* w, const uint8_t* staging, uint32_t src_ld,
                   uint32_t xor_mask, const float* ws_host, const float* bias_f32,
                   const int32_t* bias_i32) {
     const uint32_t n = w->d_out, k = w->d_in;
     w->kpad = round_up(k, kKAlign);
+    w->ws_min = w->ws_max = ws_host[0];
+    for (uint32_t i = 1; i < n; i++) {
+        w->ws_min = ws_host[i] < w->ws_min ? ws_host[i] : w->ws_min;
+        w->ws_max = ws_host[i] > w->ws_max ? ws_host[i] : w->ws_max;
+    }
     CUDA_TRY(cudaMalloc(&w->w, (size_t)n * w->kpad), 0);
     CUDA_TRY(cudaMalloc(&w->ws, (size_t)n * 4), 0);
     CUDA_TRY(cudaMalloc(&w->wsum, (size_t)n * 4), 0);
@@ -151,9 +164,19 @@ int finish_weight(VxbContext* ctx, VxbWeight* w, const uint8_t* staging, uint32_
         CUDA_TRY(cudaMemcpyAsync(w->bias_i32, bias_i32, (size_t)n * 4, cudaMemcpyHostToDevice, ctx->stream), -1);
         w->bytes += 4ull * n;
     }
-    w->has_tmap = encode_i8_rows(&w->tmap_b, w->w, n, w->kpad, 256);
+    w->has_tmap = encode_i8_rows(&w->tmap_b, w->w, n, w->kpad, 256) &&
+                  encode_i8_rows(&w->tmap_w128, w->w, n, w->kpad, 128);
     CUDA_TRY(cudaStreamSynchronize(ctx->stream), -1);
     return 1;
+}
+
+void set_requant_divisor(EpilogueParams& epi, const VxbWeight* w, float out_scale) {
+    uint32_t bits; memcpy(&bits, &out_scale, 4);
+    const bool all_ones = (bits & 0x007fffffu) == 0x007fffffu;
+    const float lo = 9.31322574615478515625e-10f, hi = 1073741824.0f;  // 2^-30 .. 2^30
+    epi.out_scale = out_scale;
+    epi.out_rcp = (float)(1.0 / (double)out_scale);
+    epi.fast_div = (!all_ones && out_scale >= lo && out_scale <= hi && w->ws_min >= lo && w->ws_max <= hi) ? 1 : 0;
 }
 
 struct Plan {
@@ -165,8 +188,9 @@ Plan choose_route(const VxbContext* ctx, const VxbWeight* w, uint32_t rows, int 
     if (requested == VXB_ROUTE_GEMV) return {VXB_ROUTE_GEMV, "gemv-dp4a"};
     if (requested == VXB_ROUTE_SIMT) return {VXB_ROUTE_SIMT, "simt-dp4a"};
     if (requested == VXB_ROUTE_TCGEN05) return {VXB_ROUTE_TCGEN05, "tcgen05-i8"};
+    if (requested == VXB_ROUTE_DECODE) return {VXB_ROUTE_DECODE, "decode-tcgen05-i8"};
     (void)ctx; (void)w;
-    if (rows <= 32) return {VXB_ROUTE_GEMV, "gemv-dp4a"};
+    if (rows <= 128) return {VXB_ROUTE_DECODE, "decode-tcgen05-i8"};
     return {VXB_ROUTE_TCGEN05, "tcgen05-i8"};
 }
 
@@ -180,6 +204,27 @@ int run_gemm(VxbContext* ctx, const VxbWeight* w, const int8_t* q, uint32_t rows
         CUDA_TRY(launch_gemv(q, rows, w->w, w->d_out, w->kpad, epi, ctx->sm_count, ctx->stream), -1);
     } else if (plan.route == VXB_ROUTE_SIMT) {
         CUDA_TRY(launch_gemm_simt(q, rows, w->w, w->d_out, w->kpad, epi, ctx->stream), -1);
+    } else if (plan.route == VXB_ROUTE_DECODE) {
+        if (rows > 128) return fail(0, "decode route needs rows <= 128 (got %u)", rows);
+        if (!w->has_tmap) return fail(0, "no tensor map for this weight (driver entry point missing)");
+        // split-K scratch: int32 [rows, d_out] + one counter per 128-channel tile, kept zero
+        const size_t ws_bytes = (size_t)128 * w->d_out * 4, cnt_bytes = (size_t)((w->d_out + 127) / 128) * 4;
+        if (ctx->splitk_ws.bytes < ws_bytes) {
+            CUDA_TRY(ctx->splitk_ws.reserve(ws_bytes), 0);
+            CUDA_TRY(cudaMemsetAsync(ctx->splitk_ws.ptr, 0, ctx->splitk_ws.bytes, ctx->stream), -1);
+        }
+        if (ctx->splitk_counters.bytes < cnt_bytes) {
+            CUDA_TRY(ctx->splitk_counters.reserve(cnt_bytes), 0);
+            CUDA_TRY(cudaMemsetAsync(ctx->splitk_counters.ptr, 0, ctx->splitk_counters.bytes, ctx->stream), -1);
+        }
+        DecodeTcgen05Args a;
+        if (!encode_i8_rows(&a.tmap_x, q, rows, w->kpad, decode_token_slots(rows)))
+            return fail(0, "cuTensorMapEncodeTiled failed for activations");
+        a.tmap_w = w->tmap_w128;
+        a.rows = rows; a.n = w->d_out; a.kpad = w->kpad; a.epi = epi;
+        a.workspace = (int32_t*)ctx->splitk_ws.ptr; a.counters = (uint32_t*)ctx->splitk_counters.ptr;
+        a.status = ctx->status;
+        CUDA_TRY(launch_decode_tcgen05(a, ctx->sm_count, ctx->stream), -1);
     } else {
         if (!w->has_tmap) return fail(0, "no tensor map for this weight (driver entry point missing)");
         if (!ctx->tcgen05_ready) {
@@ -255,6 +300,7 @@ void vxb_context_destroy(VxbContext* ctx) {
     for (auto& v : ctx->prof_events) { for (cudaEvent_t e : v) cudaEventDestroy(e); v.clear(); }
     ctx->q.release(); ctx->row_scales.release(); ctx->bias_eff.release();
     ctx->stage_in.release(); ctx->stage_out.release();
+    ctx->splitk_ws.release(); ctx->splitk_counters.release();
     if (ctx->status) cudaFree(ctx->status);
     if (ctx->status_host) cudaFreeHost(ctx->status_host);
     delete ctx;
@@ -274,6 +320,8 @@ int vxb_context_synchronize(VxbContext* ctx) {
     if (*ctx->status_host != 0) {
         const int code = *ctx->status_host;
         cudaMemsetAsync(ctx->status, 0, sizeof(int), ctx->stream);
+        if (ctx->splitk_ws.ptr) cudaMemsetAsync(ctx->splitk_ws.ptr, 0, ctx->splitk_ws.bytes, ctx->stream);
+        if (ctx->splitk_counters.ptr) cudaMemsetAsync(ctx->splitk_counters.ptr, 0, ctx->splitk_counters.bytes, ctx->stream);
         return fail(-1, "a bounded device wait expired (status %d); results of this batch are invalid", code);
     }
     return 1;
@@ -398,7 +446,7 @@ int vxb_linear_i8(VxbContext* ctx, const VxbWeight* w, const float* x, uint32_t 
     if ((rc = quantize_into_scratch(ctx, w, x, rows)) != 1) return rc;
     EpilogueParams epi{};
     epi.mode = kEpiI8; epi.row_scales = (const float*)ctx->row_scales.ptr; epi.ws = w->ws;
-    epi.bias_i32 = w->bias_i32; epi.out_scale = out_scale; epi.out_zero = out_zero;
+    epi.bias_i32 = w->bias_i32; set_requant_divisor(epi, w, out_scale); epi.out_zero = out_zero;
     epi.out_lo = -128; epi.out_hi = 127; epi.out = y; epi.ld = ldy;
     return run_gemm(ctx, w, (const int8_t*)ctx->q.ptr, rows, epi, route, "k1+");
 }
@@ -419,6 +467,29 @@ int vxb_linear_acc_i32(VxbContext* ctx, const VxbWeight* w, const float* x, uint
     EpilogueParams epi{};
     epi.mode = kEpiAcc; epi.out = acc; epi.ld = w->d_out;
     return run_gemm(ctx, w, (const int8_t*)ctx->q.ptr, rows, epi, route, "k1+");
+}
+
+uint32_t vxb_weight_row_bytes(const VxbWeight* w) { return w ? w->kpad : 0; }
+
+int vxb_linear_prepared(VxbContext* ctx, const VxbWeight* w, const int8_t* q, const float* row_scales,
+                        uint32_t rows, int mode, float out_scale, int32_t out_zero, void* out,
+                        uint32_t ldy, int route) {
+    int rc = check_common(ctx, w, q, out, ldy);
+    if (rc != 1) return rc;
+    if (mode < 0 || mode > 2) return fail(0, "mode must be 0, 1 or 2");
+    if (mode != 0 && !row_scales) return fail(0, "row scales are required for modes 1 and 2");
+    if (!rows) return 1;
+    if (ensure_device(ctx) != 1) return -1;
+    EpilogueParams epi{};
+    epi.mode = mode; epi.row_scales = row_scales; epi.ws = w->ws; epi.out = out; epi.ld = ldy;
+    if (mode == kEpiF32) epi.bias_f32 = w->bias_f32;
+    if (mode == kEpiI8) {
+        if (!valid_scale(out_scale)) return fail(0, "output scale is not positive and finite");
+        if (out_zero < -128 || out_zero > 127) return fail(0, "output zero point %d outside int8", out_zero);
+        epi.bias_i32 = w->bias_i32; set_requant_divisor(epi, w, out_scale); epi.out_zero = out_zero;
+        epi.out_lo = -128; epi.out_hi = 127;
+    }
+    return run_gemm(ctx, w, q, rows, epi, route, "prepared+");
 }
 
 int vxb_qlinear_device(VxbContext* ctx, const VxbWeight* w, const void* input, uint32_t rows,
@@ -449,7 +520,7 @@ int vxb_qlinear_device(VxbContext* ctx, const VxbWeight* w, const void* input, u
     count_launch(3);
     EpilogueParams epi{};
     epi.mode = kEpiI8; epi.row_scales = (const float*)ctx->row_scales.ptr; epi.ws = w->ws;
-    epi.bias_i32 = (const int32_t*)ctx->bias_eff.ptr; epi.out_scale = output_scale;
+    epi.bias_i32 = (const int32_t*)ctx->bias_eff.ptr; set_requant_divisor(epi, w, output_scale);
     epi.out_zero = output_zero_point; epi.out_lo = out_u8 ? 0 : -128; epi.out_hi = out_u8 ? 255 : 127;
     epi.out = output; epi.ld = ldy;
     return run_gemm(ctx, w, (const int8_t*)ctx->q.ptr, rows, epi, route, "static+");

@@ -24,6 +24,8 @@ struct EpilogueParams {
     const float* bias_f32;    // [N] or nullptr (E1)
     const int32_t* bias_i32;  // [N] or nullptr (E2, accumulator domain, zero-point folded)
     float out_scale;          // E2
+    float out_rcp;            // E2: RN(1/out_scale), used when fast_div != 0
+    int32_t fast_div;         // E2: host verified that division by out_scale may use div_const()
     int32_t out_zero;         // E2
     int32_t out_lo, out_hi;   // E2 saturation range (I8: -128..127, U8: 0..255)
     void* out;                // int32 / float / int8 [rows, ld]
@@ -50,6 +52,38 @@ __device__ __forceinline__ int32_t epi_i8(int32_t acc, float as, float ws, float
     if (moved <= (float)lo) return lo;
     if (moved >= (float)hi) return hi;
     return __float2int_rn(moved);
+}
+
+// Correctly rounded a / d for a constant divisor whose reciprocal rcp = RN(1/d) was
+// computed once: two Newton corrections with exact FMA residuals (the tail of the
+// IEEE division sequence, without the per-element reciprocal approximation and range
+// check). Valid - bit-identical to __fdiv_rn - when d's significand is not all ones and
+// a, d and a/d stay far from the fp32 exponent limits; the caller guards both.
+__device__ __forceinline__ float div_const(float a, float d, float rcp) {
+    const float q0 = __fmul_rn(a, rcp);
+    const float r0 = __fmaf_rn(-d, q0, a);
+    const float q1 = __fmaf_rn(r0, rcp, q0);
+    const float r1 = __fmaf_rn(-d, q1, a);
+    return __fmaf_rn(r1, rcp, q1);
+}
+// Range guard for div_const on the activation scale of one row (the host checked the
+// weight scales and out_scale): 2^-30 <= as <= 2^30. NaN fails the guard.
+__device__ __forceinline__ bool div_const_row_ok(float as) {
+    return as >= 9.31322574615478515625e-10f && as <= 1073741824.0f;
+}
+
+// E2 with the saturation done by min/max and the division by div_const (FAST) or
+// __fdiv_rn; same result as epi_i8 bit for bit.
+template <bool FAST>
+__device__ __forceinline__ int32_t epi_i8_v2(int32_t acc, float as, float ws, float out_scale,
+                                             float out_rcp, float zero_f, float lo_f, float hi_f,
+                                             int32_t out_zero) {
+    const float product = __fmul_rn(as, ws);
+    const float mult = FAST ? div_const(product, out_scale, out_rcp) : __fdiv_rn(product, out_scale);
+    const float scaled = __fmul_rn(__int2float_rn(acc), mult);
+    const float moved = __fadd_rn(scaled, zero_f);
+    const int32_t q = __float2int_rn(fminf(fmaxf(moved, lo_f), hi_f));
+    return moved != moved ? out_zero : q;
 }
 
 // One output element through the selected epilogue (scalar path).
@@ -113,6 +147,21 @@ struct GemmTcgen05Args {
 };
 cudaError_t launch_gemm_tcgen05(const GemmTcgen05Args& args, int sm_count, cudaStream_t stream);
 cudaError_t gemm_tcgen05_prepare();  // one-time func attribute set-up
+
+// K3b: skinny stream-K tcgen05 kernel for rows <= 128 (weights are the UMMA M operand).
+// workspace: int32 [rows, n] zero on entry and zero again on exit; counters: uint32
+// [ceil(n/128)] likewise.
+struct DecodeTcgen05Args {
+    CUtensorMap tmap_w;  // weights     int8 [n, kpad],    box 128 x 128B, swizzle 128B
+    CUtensorMap tmap_x;  // activations int8 [rows, kpad], box MT x 128B (MT = token slots)
+    uint32_t rows, n, kpad;
+    EpilogueParams epi;
+    int32_t* workspace;
+    uint32_t* counters;
+    int* status;
+};
+uint32_t decode_token_slots(uint32_t rows);  // 32 / 64 / 128
+cudaError_t launch_decode_tcgen05(const DecodeTcgen05Args& args, int sm_count, cudaStream_t stream);
 
 // tensor-pipe peak probe: issues `iters` rounds of kind::i8 MMAs on resident
 // shared-memory operands in every CTA; returns through `cycles` the SM clocks

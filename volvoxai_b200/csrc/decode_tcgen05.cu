@@ -1,0 +1,312 @@
+// K3b: skinny (decode-shaped) W8A8 GEMM for rows <= 128: HBM-bound, the int8 weights are
+// streamed exactly once and every SM streams the same number of bytes.
+//
+//   acc[m,n] = sum_k q[m,k] * w[n,k]
+//
+// The operands are swapped relative to the large-M kernel: the WEIGHT tile is the UMMA
+// M operand (128 output channels x 128 K bytes per stage) and the few activation rows are
+// the UMMA N operand (MT = 32/64/128 token slots, zero-filled by TMA beyond `rows`), so the
+// tensor pipe only does the work the tokens need while TMA keeps ~160 KB of weight bytes in
+// flight per SM.  Work is split stream-K style: the (channel tile, K block) units are dealt
+// out in equal contiguous ranges to one persistent CTA per SM, so a CTA may finish one tile,
+// compute whole tiles, and start another.  A CTA that holds only part of a tile's K range
+// adds its int32 partials into a zero-initialised workspace with red.global.add and bumps the
+// tile's counter; the CTA that completes the count applies the epilogue and clears workspace
+// and counter again.  Integer addition is associative, so the result is bit-identical for
+// every split.
+//
+// Reference counterparts: the decode kernels vx_packed_cuda_a8_columns and the fused
+// GEMV family (native/src/backends/cuda/kernels/cuda_forward_llm_kernels.inc:254-459,
+// cuda_forward_gemv_pair_kernels.inc:155-1711), which give each CTA one row x 32 columns and
+// re-quantize the activation row per column tile; and the CPU single-row route
+// (native/src/kernels/packed_linear_ops.inc:1471-1535).
+//
+// All mbarrier waits are bounded; on expiry the kernel raises the status word, drains and
+// frees its TMEM.  No CTA ever waits for another CTA.
+#include "tcgen05.cuh"
+
+namespace vxb {
+
+namespace {
+
+using namespace tc;
+
+constexpr uint32_t kDM = 128;            // output channels per tile (UMMA M)
+constexpr uint32_t kDK = 128;            // K bytes per stage
+constexpr uint32_t kWBytes = kDM * kDK;  // 16 KiB weight tile
+constexpr uint32_t kThreads = 192;       // producer warp, MMA warp, 4 epilogue warps
+
+template <uint32_t MT> struct DecodeCfg {
+    static constexpr uint32_t kXBytes = MT * kDK;
+    static constexpr uint32_t kStageBytes = kWBytes + kXBytes;
+    static constexpr uint32_t kStages = MT <= 64 ? 8 : 6;
+    static constexpr uint32_t kTmemCols = 2 * MT < 32 ? 32 : 2 * MT;
+    static constexpr uint32_t kOffBars = kStages * kStageBytes;
+    static constexpr uint32_t kNumBars = 2 * kStages + 4;
+    static constexpr uint32_t kOffTmemPtr = kOffBars + kNumBars * 8;
+    static constexpr uint32_t kOffAbort = kOffTmemPtr + 4;
+    static constexpr uint32_t kOffFlag = kOffAbort + 4;       // epilogue-uniform decisions
+    static constexpr uint32_t kOffScales = kOffFlag + 8;      // float[MT] activation scales
+    static constexpr uint32_t kSmemBytes = kOffScales + MT * 4 + 1024;
+};
+
+__device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+struct Segment { uint32_t tile, kb_begin, kb_end; };
+
+// The s-th segment of this CTA's unit range [u0, u1): consecutive K blocks of one tile.
+__device__ __forceinline__ bool next_segment(uint64_t& u, uint64_t u1, uint32_t num_kb, Segment& seg) {
+    if (u >= u1) return false;
+    seg.tile = (uint32_t)(u / num_kb);
+    seg.kb_begin = (uint32_t)(u % num_kb);
+    const uint64_t left = u1 - u;
+    const uint32_t room = num_kb - seg.kb_begin;
+    const uint32_t take = left < room ? (uint32_t)left : room;
+    seg.kb_end = seg.kb_begin + take;
+    u += take;
+    return true;
+}
+
+template <uint32_t MT>
+__global__ void __launch_bounds__(kThreads, 1)
+decode_i8_tcgen05_kernel(const __grid_constant__ DecodeTcgen05Args args) {
+    using Cfg = DecodeCfg<MT>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* base = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    auto w_addr = [&](uint32_t s) { return smem_u32(base + s * Cfg::kStageBytes); };
+    auto x_addr = [&](uint32_t s) { return smem_u32(base + s * Cfg::kStageBytes + kWBytes); };
+    auto full = [&](uint32_t s) { return smem_u32(base + Cfg::kOffBars + s * 8); };
+    auto empty = [&](uint32_t s) { return smem_u32(base + Cfg::kOffBars + (Cfg::kStages + s) * 8); };
+    auto tmem_full = [&](uint32_t b) { return smem_u32(base + Cfg::kOffBars + (2 * Cfg::kStages + b) * 8); };
+    auto tmem_empty = [&](uint32_t b) { return smem_u32(base + Cfg::kOffBars + (2 * Cfg::kStages + 2 + b) * 8); };
+    uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(base + Cfg::kOffTmemPtr);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(base + Cfg::kOffAbort);
+    volatile int* epi_flag = reinterpret_cast<volatile int*>(base + Cfg::kOffFlag);
+    float* s_as = reinterpret_cast<float*>(base + Cfg::kOffScales);
+
+    const uint32_t tiles_n = (args.n + kDM - 1) / kDM;
+    const uint32_t num_kb = args.kpad / kDK;
+    const uint64_t units = (uint64_t)tiles_n * num_kb;
+    const uint64_t u0 = units * blockIdx.x / gridDim.x;
+    const uint64_t u1 = units * (blockIdx.x + 1) / gridDim.x;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < Cfg::kStages; s++) { mbar_init(full(s), 1); mbar_init(empty(s), 1); }
+        for (uint32_t b = 0; b < 2; b++) { mbar_init(tmem_full(b), 1); mbar_init(tmem_empty(b), 128); }
+        *abort_flag = 0;
+        fence_barrier_init();
+        prefetch_tmap(&args.tmap_w);
+        prefetch_tmap(&args.tmap_x);
+    }
+    if (warp == 1) { tmem_alloc(smem_u32(tmem_ptr), Cfg::kTmemCols); tmem_relinquish(); }
+    if (threadIdx.x >= 64) {
+        const uint32_t e = threadIdx.x - 64;
+        if (e < MT) s_as[e] = (e < args.rows && args.epi.mode != kEpiAcc) ? __ldg(args.epi.row_scales + e) : 0.0f;
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_ptr;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0, armed = 0, armed_parity = 0;
+            bool ok = true;
+            uint64_t u = u0; Segment seg;
+            while (ok && next_segment(u, u1, num_kb, seg)) {
+                for (uint32_t kb = seg.kb_begin; kb < seg.kb_end; kb++) {
+                    if (!mbar_wait(empty(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
+                    mbar_expect_tx(full(stage), Cfg::kStageBytes);
+                    tma_load_2d(w_addr(stage), &args.tmap_w, full(stage), (int32_t)(kb * kDK), (int32_t)(seg.tile * kDM));
+                    tma_load_2d(x_addr(stage), &args.tmap_x, full(stage), (int32_t)(kb * kDK), 0);
+                    armed |= 1u << stage;
+                    armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
+                    if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
+                }
+            }
+            if (!ok) {
+                for (uint32_t s = 0; s < Cfg::kStages; s++) {
+                    if (!(armed & (1u << s))) continue;
+                    for (uint32_t i = 0; i < 2000; i++) {
+                        if (mbar_try_wait(full(s), (armed_parity >> s) & 1u)) break;
+                        __nanosleep(500);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(kDM, MT);
+            uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+            bool ok = true;
+            uint64_t u = u0; Segment seg;
+            while (ok && next_segment(u, u1, num_kb, seg)) {
+                if (!mbar_wait(tmem_empty(acc), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * MT;
+                for (uint32_t kb = seg.kb_begin; kb < seg.kb_end; kb++) {
+                    if (!mbar_wait(full(stage), phase, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t wa = w_addr(stage), xa = x_addr(stage);
+#pragma unroll
+                    for (uint32_t k = 0; k < kDK / kUmmaK; k++)
+                        umma_i8(d_tmem, make_smem_desc(wa + k * kUmmaK), make_smem_desc(xa + k * kUmmaK),
+                                idesc, (kb != seg.kb_begin || k != 0u) ? 1u : 0u);
+                    umma_commit(empty(stage));
+                    if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                umma_commit(tmem_full(acc));
+                acc ^= 1u;
+                if (acc == 0) acc_phase ^= 1u;
+            }
+        }
+    } else {
+        // ---------------- epilogue (warps 2..5): thread = one output channel ----------------
+        const uint32_t quarter = warp & 3u;
+        const EpilogueParams& ep = args.epi;
+        const float zero_f = __int2float_rn(ep.out_zero);
+        const float lo_f = __int2float_rn(ep.out_lo), hi_f = __int2float_rn(ep.out_hi);
+        uint32_t acc = 0, acc_phase = 0;
+        uint64_t u = u0; Segment seg;
+        while (next_segment(u, u1, num_kb, seg)) {
+            const bool waited = mbar_wait(tmem_full(acc), acc_phase, abort_flag);
+            // make the give-up decision uniform across the four epilogue warps
+            epi_bar();
+            if (threadIdx.x == 64) epi_flag[0] = (*abort_flag != 0 || !waited) ? 1 : 0;
+            epi_bar();
+            if (epi_flag[0]) break;
+            tc_fence_after();
+
+            const uint32_t n = seg.tile * kDM + quarter * 32 + lane;
+            const bool n_ok = n < args.n;
+            const bool whole = seg.kb_begin == 0 && seg.kb_end == num_kb;
+            const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + acc * MT;
+            const float wsv = (n_ok && ep.mode != kEpiAcc) ? __ldg(ep.ws + n) : 0.0f;
+            float bias_f = 0.0f; int32_t bias_i = 0;
+            if (n_ok && ep.mode == kEpiF32 && ep.bias_f32) bias_f = __ldg(ep.bias_f32 + n);
+            if (n_ok && ep.mode == kEpiI8 && ep.bias_i32) bias_i = __ldg(ep.bias_i32 + n);
+
+            // One 32-token chunk of this thread's channel through the selected epilogue.
+            auto finish_chunk = [&](uint32_t c, const int32_t (&v)[32]) {
+                if (!n_ok) return;
+#pragma unroll
+                for (uint32_t i = 0; i < 32; i++) {
+                    const uint32_t m = c + i;
+                    if (m >= args.rows) continue;
+                    const size_t at = (size_t)m * ep.ld + n;
+                    if (ep.mode == kEpiAcc) {
+                        ((int32_t*)ep.out)[at] = v[i];
+                    } else if (ep.mode == kEpiF32) {
+                        ((float*)ep.out)[at] = epi_f32(v[i], s_as[m], wsv, bias_f);
+                    } else {
+                        const float as = s_as[m];
+                        const int32_t qv = (ep.fast_div != 0 && div_const_row_ok(as))
+                            ? epi_i8_v2<true>(v[i] + bias_i, as, wsv, ep.out_scale, ep.out_rcp, zero_f, lo_f, hi_f, ep.out_zero)
+                            : epi_i8_v2<false>(v[i] + bias_i, as, wsv, ep.out_scale, ep.out_rcp, zero_f, lo_f, hi_f, ep.out_zero);
+                        ((int8_t*)ep.out)[at] = (int8_t)qv;
+                    }
+                }
+            };
+
+#pragma unroll 1
+            for (uint32_t c = 0; c < MT; c += 32) {
+                uint32_t r[32];
+                tmem_ld32(taddr + c, r);
+                tmem_ld_wait();
+                if (c >= args.rows) continue;
+                int32_t v[32];
+#pragma unroll
+                for (int i = 0; i < 32; i++) v[i] = (int32_t)r[i];
+                if (whole) {
+                    finish_chunk(c, v);
+                } else if (n_ok) {
+                    // partial K range: add into the zero-initialised workspace
+#pragma unroll
+                    for (uint32_t i = 0; i < 32; i++)
+                        if (c + i < args.rows) atomicAdd(args.workspace + (size_t)(c + i) * args.n + n, v[i]);
+                }
+            }
+            // the accumulator has been consumed: hand the TMEM buffer back to the MMA warp
+            tc_fence_before();
+            mbar_arrive(tmem_empty(acc));
+            acc ^= 1u;
+            if (acc == 0) acc_phase ^= 1u;
+
+            if (!whole) {
+                // count the K blocks delivered; whoever completes the tile finishes it
+                __threadfence();
+                epi_bar();
+                if (threadIdx.x == 64) {
+                    const uint32_t mine = seg.kb_end - seg.kb_begin;
+                    const uint32_t before = atomicAdd(args.counters + seg.tile, mine);
+                    epi_flag[1] = (before + mine == num_kb) ? 1 : 0;
+                }
+                epi_bar();
+                if (epi_flag[1] != 0) {
+                    __threadfence();
+#pragma unroll 1
+                    for (uint32_t c = 0; c < MT && c < args.rows; c += 32) {
+                        int32_t v[32];
+#pragma unroll
+                        for (uint32_t i = 0; i < 32; i++) {
+                            v[i] = 0;
+                            if (n_ok && c + i < args.rows) {
+                                int32_t* slot = args.workspace + (size_t)(c + i) * args.n + n;
+                                v[i] = __ldcg(slot);
+                                __stcg(slot, 0);   // leave the workspace clean for the next call
+                            }
+                        }
+                        finish_chunk(c, v);
+                    }
+                    if (threadIdx.x == 64) args.counters[seg.tile] = 0u;
+                }
+            }
+        }
+    }
+
+    // ---------------- teardown ----------------
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        nap(200);
+        if (threadIdx.x == 0 && args.status) atomicExch(args.status, 3);
+        __syncthreads();
+    }
+    tc_fence_after();
+    if (warp == 1) tmem_dealloc(tmem_base, Cfg::kTmemCols);
+}
+
+template <uint32_t MT>
+cudaError_t launch_t(const DecodeTcgen05Args& args, int sm_count, cudaStream_t stream) {
+    using Cfg = DecodeCfg<MT>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(decode_i8_tcgen05_kernel<MT>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::kSmemBytes);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    const uint64_t units = (uint64_t)((args.n + kDM - 1) / kDM) * (args.kpad / kDK);
+    const uint32_t grid = units < (uint64_t)sm_count ? (uint32_t)units : (uint32_t)sm_count;
+    decode_i8_tcgen05_kernel<MT><<<grid, kThreads, Cfg::kSmemBytes, stream>>>(args);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+uint32_t decode_token_slots(uint32_t rows) { return rows <= 32 ? 32u : rows <= 64 ? 64u : 128u; }
+
+cudaError_t launch_decode_tcgen05(const DecodeTcgen05Args& args, int sm_count, cudaStream_t stream) {
+    if (args.rows == 0 || args.n == 0) return cudaSuccess;
+    if (args.rows > 128) return cudaErrorInvalidValue;
+    if (args.rows <= 32) return launch_t<32>(args, sm_count, stream);
+    if (args.rows <= 64) return launch_t<64>(args, sm_count, stream);
+    return launch_t<128>(args, sm_count, stream);
+}
+
+}  // namespace vxb

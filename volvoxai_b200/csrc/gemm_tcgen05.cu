@@ -9,8 +9,8 @@
 //   warp 1      allocates TMEM; one lane issues tcgen05.mma.cta_group::1
 //               .kind::i8 (M128 x N256 x K32 per instruction, 4 per stage);
 //               tcgen05.commit releases smem stages and publishes accumulators
-//   warps 2-5   epilogue: tcgen05.ld the int32 accumulators (each warp owns the
-//               32 TMEM lanes of its quarter), apply the fused epilogue
+//   warps 2-9   epilogue: tcgen05.ld the int32 accumulators (two warps per 32-lane
+//               TMEM quarter, one per 128-column half), apply the fused epilogue
 //               (raw int32 / dequant+bias fp32 / requant int8) and store.
 // Two 256-column accumulators fill the 512-column TMEM, so the epilogue of
 // tile i overlaps the MMAs of tile i+1.
@@ -23,155 +23,37 @@
 //
 // Every wait on an mbarrier is bounded (~2 s of SM clocks); on expiry the
 // kernel raises a status word, drains, frees its TMEM and returns.
-#include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace vxb {
 
 namespace {
 
+using namespace tc;
+
 constexpr uint32_t kBM = 128;           // activation rows per tile (UMMA M)
 constexpr uint32_t kBN = 256;           // output channels per tile (UMMA N)
 constexpr uint32_t kBK = 128;           // K bytes per stage (one swizzle span)
-constexpr uint32_t kUmmaK = 32;         // K per kind::i8 instruction
 constexpr uint32_t kStages = 4;
 constexpr uint32_t kABytes = kBM * kBK;            // 16 KiB
 constexpr uint32_t kBBytes = kBN * kBK;            // 32 KiB
 constexpr uint32_t kStageBytes = kABytes + kBBytes;
 constexpr uint32_t kAccCols = kBN;                 // int32 columns per accumulator
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kThreads = 192;
-constexpr uint32_t kEpiThreads = 128;
-constexpr long long kWaitLimitCycles = 4000000000LL;  // ~2 s at 1.9 GHz
+constexpr uint32_t kEpiWarps = 8;
+constexpr uint32_t kThreads = 64 + 32 * kEpiWarps;  // producer warp + MMA warp + epilogue warps
+constexpr uint32_t kEpiThreads = 32 * kEpiWarps;
+constexpr uint32_t kEpiCols = kBN / 2;              // columns per epilogue warp
 
 // dynamic shared memory layout (offsets from a 1024-byte aligned base)
 constexpr uint32_t kOffStages = 0;
-constexpr uint32_t kOffWs = kStages * kStageBytes;           // float[4 warps][256]
-constexpr uint32_t kOffBias = kOffWs + 4 * kBN * 4;          // float/int32[4 warps][256]
-constexpr uint32_t kOffBars = kOffBias + 4 * kBN * 4;        // 8-byte barriers
+constexpr uint32_t kOffWs = kStages * kStageBytes;                   // float[8 warps][128]
+constexpr uint32_t kOffBias = kOffWs + kEpiWarps * kEpiCols * 4;     // float/int32[8 warps][128]
+constexpr uint32_t kOffBars = kOffBias + kEpiWarps * kEpiCols * 4;   // 8-byte barriers
 constexpr uint32_t kNumBars = 2 * kStages + 4;
 constexpr uint32_t kOffTmemPtr = kOffBars + kNumBars * 8;
 constexpr uint32_t kOffAbort = kOffTmemPtr + 4;
 constexpr uint32_t kSmemBytes = kOffAbort + 4 + 1024;        // + alignment slack
-
-// ---- PTX wrappers -----------------------------------------------------------
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-    return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait: false when the limit expired or another role already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    uint32_t spins = 0;
-    while (!mbar_try_wait(bar, parity)) {
-        if ((++spins & 63u) == 0u) {
-            if (*abort_flag) return false;
-            if (clock64() - t0 > kWaitLimitCycles) { *abort_flag = 1; return false; }
-        }
-    }
-    return true;
-}
-__device__ __forceinline__ void fence_barrier_init() {
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-}
-__device__ __forceinline__ void fence_proxy_async() {
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
-                                            int32_t c0, int32_t c1) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
-        "[%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
-}
-__device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {
-    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
-}
-__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                 ::"r"(dst_smem), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() {
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_after() {
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-// D[tmem] (+)= A[smem] * B[smem], int8 x int8 -> int32
-__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                        uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-// mbarrier arrives once every previously issued MMA of this thread has finished.
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
-                 ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
-          "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() {
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// Shared-memory matrix descriptor for a K-major tile whose rows are 128 bytes,
-// 128B-swizzled (what TMA writes with CU_TENSOR_MAP_SWIZZLE_128B): 8-row groups
-// are 1024 bytes apart (stride byte offset), descriptor version 1 (sm_100),
-// layout type 2 = SWIZZLE_128B. The leading byte offset is unused for
-// swizzled K-major operands. Fields are in units of 16 bytes.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr >> 4) & 0x3fffu);
-    d |= (uint64_t)1u << 16;
-    d |= (uint64_t)(1024u >> 4) << 32;
-    d |= (uint64_t)1u << 46;
-    d |= (uint64_t)2u << 61;
-    return d;
-}
-
-// Instruction descriptor, kind::i8: D = S32 (bits 4-5 = 2), A and B signed
-// 8-bit (bits 7-9 and 10-12 = 1), both K-major (bits 15, 16 = 0), N>>3 at
-// bits 17-22, M>>4 at bits 24-28, dense, no saturation.
-__host__ __device__ constexpr uint32_t make_idesc(uint32_t m, uint32_t n) {
-    return (2u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
-}
 
 struct Smem {
     uint8_t* base;
@@ -186,10 +68,6 @@ struct Smem {
     __device__ float* ws() const { return reinterpret_cast<float*>(base + kOffWs); }
     __device__ float* bias() const { return reinterpret_cast<float*>(base + kOffBias); }
 };
-
-__device__ __forceinline__ void nap(uint32_t rounds) {
-    for (uint32_t i = 0; i < rounds; i++) __nanosleep(1000);
-}
 
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_i8_tcgen05_kernel(const __grid_constant__ GemmTcgen05Args args) {
@@ -279,20 +157,27 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ GemmTcgen05Args args) {
             }
         }
     } else {
-        // ---------------- epilogue (warps 2..5) ----------------
+        // ---------------- epilogue (warps 2..9) ----------------
+        // Two warps per TMEM lane quarter (one per SM sub-partition pair), each owning one
+        // half of the tile's 256 columns, so every scheduler has two epilogue warps to
+        // interleave.
         const uint32_t quarter = warp & 3u;              // TMEM lanes [32*quarter, +32)
+        const uint32_t half = (warp - 2u) >> 2;          // columns [128*half, +128) of the tile
+        const uint32_t cbase = half * kEpiCols;
         const EpilogueParams& ep = args.epi;
-        // each epilogue warp stages its own copy of the tile's per-channel vectors, so the
-        // four warps never wait on one another
-        float* s_ws = sm.ws() + quarter * kBN;
-        float* s_bias = sm.bias() + quarter * kBN;
+        // each epilogue warp stages its own slice of the per-channel vectors, so the warps
+        // never wait on one another
+        float* s_ws = sm.ws() + (warp - 2u) * kEpiCols;
+        float* s_bias = sm.bias() + (warp - 2u) * kEpiCols;
+        const float zero_f = __int2float_rn(ep.out_zero);
+        const float lo_f = __int2float_rn(ep.out_lo), hi_f = __int2float_rn(ep.out_hi);
         uint32_t acc = 0, acc_phase = 0;
         bool ok = true;
         for (uint32_t t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
-            const uint32_t m0 = (t % tiles_m) * kBM, n0 = (t / tiles_m) * kBN;
-            // stage this tile's per-channel vectors
+            const uint32_t m0 = (t % tiles_m) * kBM, n0 = (t / tiles_m) * kBN + cbase;
+            // stage this warp's per-channel vectors for the tile
             __syncwarp();
-            for (uint32_t i = lane; i < kBN; i += 32) {
+            for (uint32_t i = lane; i < kEpiCols; i += 32) {
                 const uint32_t n = n0 + i;
                 float wsv = 0.0f, bv = 0.0f;
                 if (n < args.n && ep.mode != kEpiAcc) {
@@ -310,30 +195,41 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ GemmTcgen05Args args) {
             const uint32_t row = m0 + quarter * 32 + lane;
             const bool row_ok = row < args.rows;
             const float as = (row_ok && ep.mode != kEpiAcc) ? __ldg(ep.row_scales + row) : 0.0f;
-            const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + acc * kAccCols;
+            const bool fast = ep.fast_div != 0 && div_const_row_ok(as);
+            const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + acc * kAccCols + cbase;
 #pragma unroll 1
-            for (uint32_t c = 0; c < kBN; c += 32) {
+            for (uint32_t c = 0; c < kEpiCols; c += 32) {
                 uint32_t r[32];
                 tmem_ld32(taddr + c, r);
                 tmem_ld_wait();
                 const uint32_t col = n0 + c;
                 if (!row_ok || col >= args.n) continue;
                 const bool full = col + 32 <= args.n;
+                const float4* w4 = reinterpret_cast<const float4*>(s_ws + c);
+                const float4* b4 = reinterpret_cast<const float4*>(s_bias + c);
                 if (ep.mode == kEpiI8) {
                     int8_t* dst = (int8_t*)ep.out + (size_t)row * ep.ld + col;
                     uint32_t packed[8];
+                    if (fast) {
 #pragma unroll
-                    for (int j = 0; j < 8; j++) {
-                        uint32_t word = 0;
-#pragma unroll
-                        for (int b = 0; b < 4; b++) {
-                            const int i = j * 4 + b;
-                            const int32_t a = (int32_t)r[i] + __float_as_int(s_bias[c + i]);
-                            const int32_t qv = epi_i8(a, as, s_ws[c + i], ep.out_scale, ep.out_zero,
-                                                      ep.out_lo, ep.out_hi);
-                            word |= ((uint32_t)qv & 0xffu) << (8 * b);
+                        for (int j = 0; j < 8; j++) {
+                            const float4 wv = w4[j], bv = b4[j];
+                            const int32_t q0 = epi_i8_v2<true>((int32_t)r[4 * j + 0] + __float_as_int(bv.x), as, wv.x, ep.out_scale, ep.out_rcp, zero_f, lo_f, hi_f, ep.out_zero);
+                            const int32_t q1 = epi_i8_v2<true>((int32_t)r[4 * j + 1] + __float_as_int(bv.y), as, wv.y, ep.out_scale, ep.out_rcp, zero_f, lo_f, hi_f, ep.out_zero);
+                            const int32_t q2 = epi_i8_v2<true>((int32_t)r[4 * j + 2] + __float_as_int(bv.z), as, wv.z, ep.out_scale, ep.out_rcp, zero_f, lo_f, hi_f, ep.out_zero);
+                            const int32_t q3 = epi_i8_v2<true>((int32_t)r[4 * j + 3] + __float_as_int(bv.w), as, wv.w, ep.out_scale, ep.out_rcp, zero_f, lo_f, hi_f, ep.out_zero);
+                            packed[j] = __byte_perm(__byte_perm(q0, q1, 0x0040), __byte_perm(q2, q3, 0x0040), 0x5410);
                         }
-                        packed[j] = word;
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 8; j++) {
+                            const float4 wv = w4[j], bv = b4[j];
+                            const int32_t q0 = epi_i8_v2<false>((int32_t)r[4 * j + 0] + __float_as_int(bv.x), as, wv.x, ep.out_scale, ep.out_rcp, zero_f, lo_f, hi_f, ep.out_zero);
+                            const int32_t q1 = epi_i8_v2<false>((int32_t)r[4 * j + 1] + __float_as_int(bv.y), as, wv.y, ep.out_scale, ep.out_rcp, zero_f, lo_f, hi_f, ep.out_zero);
+                            const int32_t q2 = epi_i8_v2<false>((int32_t)r[4 * j + 2] + __float_as_int(bv.z), as, wv.z, ep.out_scale, ep.out_rcp, zero_f, lo_f, hi_f, ep.out_zero);
+                            const int32_t q3 = epi_i8_v2<false>((int32_t)r[4 * j + 3] + __float_as_int(bv.w), as, wv.w, ep.out_scale, ep.out_rcp, zero_f, lo_f, hi_f, ep.out_zero);
+                            packed[j] = __byte_perm(__byte_perm(q0, q1, 0x0040), __byte_perm(q2, q3, 0x0040), 0x5410);
+                        }
                     }
                     if (full && (((uintptr_t)dst) & 15u) == 0) {
                         reinterpret_cast<uint4*>(dst)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
@@ -347,8 +243,13 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ GemmTcgen05Args args) {
                     uint32_t o[32];
                     if (ep.mode == kEpiF32) {
 #pragma unroll
-                        for (int i = 0; i < 32; i++)
-                            o[i] = __float_as_uint(epi_f32((int32_t)r[i], as, s_ws[c + i], s_bias[c + i]));
+                        for (int j = 0; j < 8; j++) {
+                            const float4 wv = w4[j], bv = b4[j];
+                            o[4 * j + 0] = __float_as_uint(epi_f32((int32_t)r[4 * j + 0], as, wv.x, bv.x));
+                            o[4 * j + 1] = __float_as_uint(epi_f32((int32_t)r[4 * j + 1], as, wv.y, bv.y));
+                            o[4 * j + 2] = __float_as_uint(epi_f32((int32_t)r[4 * j + 2], as, wv.z, bv.z));
+                            o[4 * j + 3] = __float_as_uint(epi_f32((int32_t)r[4 * j + 3], as, wv.w, bv.w));
+                        }
                     } else {
 #pragma unroll
                         for (int i = 0; i < 32; i++) o[i] = r[i];

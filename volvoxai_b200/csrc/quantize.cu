@@ -18,24 +18,44 @@ namespace vxb {
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int kMaxVecPerThread = 16;  // float4 per thread kept in registers (K <= 16384)
+constexpr int kMaxVecPerThread = 8;   // float4 per thread kept in registers (K <= 8192)
 
 __device__ __forceinline__ bool nonfinite_bits(float v) {
     return (__float_as_uint(v) & 0x7f800000u) == 0x7f800000u;
 }
 
-__device__ __forceinline__ int32_t quant1(float v, float scale) {
-    float r = __fdiv_rn(v, scale);
+// The row's scale is a constant divisor for the whole row: when it is well inside the
+// exponent range and its significand is not all ones, x / scale is computed through the
+// correctly rounded reciprocal and two FMA corrections (div_const), which yields the IEEE
+// quotient bit for bit wherever the quotient can round to a non-zero code; otherwise
+// the IEEE divide is used.
+struct RowDivisor {
+    float scale, rcp;
+    bool fast;
+    __device__ __forceinline__ explicit RowDivisor(float s) {
+        scale = s;
+        rcp = __frcp_rn(s);
+        const uint32_t bits = __float_as_uint(s);
+        fast = s >= 8.67361737988403547206e-19f && s <= 1152921504606846976.0f &&  // 2^-60 .. 2^60
+               (bits & 0x007fffffu) != 0x007fffffu;
+    }
+};
+
+template <bool FAST>
+__device__ __forceinline__ int32_t quant1(float v, const RowDivisor& d) {
+    float r = FAST ? div_const(v, d.scale, d.rcp) : __fdiv_rn(v, d.scale);
     r = fminf(fmaxf(r, -127.0f), 127.0f);
     return __float2int_rn(r);
 }
 
-__device__ __forceinline__ uint32_t pack4(float4 v, float scale) {
-    const uint32_t a = (uint32_t)quant1(v.x, scale) & 0xffu;
-    const uint32_t b = (uint32_t)quant1(v.y, scale) & 0xffu;
-    const uint32_t c = (uint32_t)quant1(v.z, scale) & 0xffu;
-    const uint32_t d = (uint32_t)quant1(v.w, scale) & 0xffu;
-    return a | (b << 8) | (c << 16) | (d << 24);
+template <bool FAST>
+__device__ __forceinline__ uint32_t pack4t(float4 v, const RowDivisor& d) {
+    const int32_t a = quant1<FAST>(v.x, d), b = quant1<FAST>(v.y, d);
+    const int32_t c = quant1<FAST>(v.z, d), e = quant1<FAST>(v.w, d);
+    return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, e, 0x0040), 0x5410);
+}
+__device__ __forceinline__ uint32_t pack4(float4 v, const RowDivisor& d) {
+    return d.fast ? pack4t<true>(v, d) : pack4t<false>(v, d);
 }
 
 // Reduce (max, or-flag) over THREADS_PER_ROW consecutive threads (power of two).
@@ -110,16 +130,25 @@ quantize_rows_vec(const float* __restrict__ x, uint32_t rows, uint32_t k, int8_t
     }
     uint32_t* out = reinterpret_cast<uint32_t*>(q + (size_t)row * ldq);
     const uint32_t nwords = ldq / 4;
+    const RowDivisor div(scale);
     if constexpr (CACHE) {
+        if (div.fast && !bad) {
 #pragma unroll
-        for (int i = 0; i < kMaxVecPerThread; i++) {
-            const uint32_t v = t + i * THREADS_PER_ROW;
-            if (v < nwords) out[v] = (v < nvec && !bad) ? pack4(cache[i], scale) : 0u;
+            for (int i = 0; i < kMaxVecPerThread; i++) {
+                const uint32_t v = t + i * THREADS_PER_ROW;
+                if (v < nwords) out[v] = v < nvec ? pack4t<true>(cache[i], div) : 0u;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < kMaxVecPerThread; i++) {
+                const uint32_t v = t + i * THREADS_PER_ROW;
+                if (v < nwords) out[v] = (v < nvec && !bad) ? pack4t<false>(cache[i], div) : 0u;
+            }
         }
         for (uint32_t v = t + kMaxVecPerThread * THREADS_PER_ROW; v < nwords; v += THREADS_PER_ROW) out[v] = 0u;
     } else {
         for (uint32_t v = t; v < nwords; v += THREADS_PER_ROW)
-            out[v] = (v < nvec && !bad) ? pack4(__ldg(in + v), scale) : 0u;
+            out[v] = (v < nvec && !bad) ? pack4(__ldg(in + v), div) : 0u;
     }
 }
 
@@ -149,8 +178,9 @@ quantize_rows_scalar(const float* __restrict__ x, uint32_t rows, uint32_t k, int
         if (valid) valid[row] = bad ? 0 : 1;
     }
     int8_t* out = q + (size_t)row * ldq;
+    const RowDivisor div(scale);
     for (uint32_t j = lane; j < ldq; j += 32)
-        out[j] = (j < k && !bad) ? (int8_t)quant1(in[j], scale) : (int8_t)0;
+        out[j] = (j < k && !bad) ? (int8_t)quant1<false>(in[j], div) : (int8_t)0;
 }
 
 __global__ void fill_f32_kernel(float* dst, uint32_t count, float value) {
@@ -215,11 +245,11 @@ cudaError_t launch_quantize_rows(const float* x, uint32_t rows, uint32_t k, int8
         quantize_rows_scalar<<<grid, kThreads, 0, stream>>>(x, rows, k, q, ldq, row_scales, valid);
         return cudaGetLastError();
     }
-    // Threads per row grow with K so each thread keeps at most 16 float4 in registers.
-    if (k <= 512) return launch_vec<8>(x, rows, k, q, ldq, row_scales, valid, stream);
-    if (k <= 2048) return launch_vec<32>(x, rows, k, q, ldq, row_scales, valid, stream);
-    if (k <= 4096) return launch_vec<64>(x, rows, k, q, ldq, row_scales, valid, stream);
-    if (k <= 8192) return launch_vec<128>(x, rows, k, q, ldq, row_scales, valid, stream);
+    // Threads per row grow with K so each thread keeps at most 8 float4 in registers.
+    if (k <= 256) return launch_vec<8>(x, rows, k, q, ldq, row_scales, valid, stream);
+    if (k <= 1024) return launch_vec<32>(x, rows, k, q, ldq, row_scales, valid, stream);
+    if (k <= 2048) return launch_vec<64>(x, rows, k, q, ldq, row_scales, valid, stream);
+    if (k <= 4096) return launch_vec<128>(x, rows, k, q, ldq, row_scales, valid, stream);
     return launch_vec<256>(x, rows, k, q, ldq, row_scales, valid, stream);
 }
 

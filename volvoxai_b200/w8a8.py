@@ -19,12 +19,12 @@ import ctypes as C
 import numpy as np
 
 from . import _lib
-from ._lib import (DT_I8, DT_U8, OP_PACKED_LINEAR, ROUTE_AUTO, ROUTE_GEMV, ROUTE_SIMT,
+from ._lib import (DT_I8, DT_U8, OP_PACKED_LINEAR, ROUTE_AUTO, ROUTE_DECODE, ROUTE_GEMV, ROUTE_SIMT,
                    ROUTE_TCGEN05, LLMOpArgs, last_error, last_route)
 
 __all__ = ["Context", "Weight", "W8A8Error", "qlinear_i8u8", "packed_linear",
            "packed_linear_decode", "host_cache_clear", "launch_count", "last_error",
-           "last_route", "ROUTE_AUTO", "ROUTE_GEMV", "ROUTE_TCGEN05", "ROUTE_SIMT",
+           "last_route", "ROUTE_AUTO", "ROUTE_GEMV", "ROUTE_TCGEN05", "ROUTE_SIMT", "ROUTE_DECODE",
            "DT_I8", "DT_U8"]
 
 
@@ -150,6 +150,19 @@ class Context:
                                           _ptr(q), _ptr(s), route))
         return (acc, q, s) if want_q else acc
 
+    def prepare(self, w: "Weight", x):
+        """Quantize rows into the weight's padded row layout: (int8 [rows,row_bytes], scales)."""
+        q, s, _ = self.quantize_rows(x, ldq=w.row_bytes)
+        return q, s
+
+    def linear_prepared(self, w: "Weight", q, row_scales, out, mode: int = 1, out_scale: float = 1.0,
+                        out_zero: int = 0, route: int = ROUTE_AUTO):
+        """GEMM + epilogue over already-quantized rows (mode 0 int32 / 1 fp32 / 2 int8)."""
+        _check(self._L.vxb_linear_prepared(self.handle, w.handle, _ptr(q), _ptr(row_scales),
+                                           q.shape[0], mode, float(out_scale), int(out_zero),
+                                           _ptr(out), out.stride(0), route))
+        return out
+
     def qlinear_device(self, w: "Weight", x, input_scale, input_zero, output_scale, output_zero,
                        out_unsigned: bool = False, route: int = ROUTE_AUTO):
         import torch
@@ -173,6 +186,7 @@ class Weight:
         self.handle = handle
         self.d_in = int(self._L.vxb_weight_d_in(handle))
         self.d_out = int(self._L.vxb_weight_d_out(handle))
+        self.row_bytes = int(self._L.vxb_weight_row_bytes(handle))
 
     @classmethod
     def from_i8(cls, ctx: Context, w: np.ndarray, ws: np.ndarray, bias_f32=None, bias_i32=None):
