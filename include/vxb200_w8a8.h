@@ -191,6 +191,42 @@ VXB_API int vxb_context_profile_read(VxbContext* ctx, double* quantize_ms, uint6
  * the tensor-bound roofline. */
 VXB_API int vxb_measure_i8_tensor_peak(VxbContext* ctx, uint32_t iters, double* tops);
 
+/* Decode linear that allocates nothing.  It has no counterpart in the reference.
+ *
+ * Who needs it: a host that must not allocate device memory at run time - for
+ * example one that reports a fixed memory inventory for a compiled model and
+ * is held to it, or code that runs while its stream is being captured, where
+ * cudaMalloc is not permitted.  The ordinary entries above grow scratch inside
+ * a VxbContext with cudaMalloc; this one takes the split-K scratch of the decode
+ * kernel (partial sums, tile counters, status word) from a fixed array that is
+ * part of the library image.  Every GPU that loads the library holds that array
+ * (about 2 MiB) until the process exits.
+ *
+ * It runs y = dequant(q * W^T) + bias for rows <= VXB_NOALLOC_MAX_ROWS and
+ * d_out <= VXB_NOALLOC_MAX_CHANNELS, fp32 out, on DEVICE buffers that the caller
+ * owns: q int8 [rows,row_bytes] and row_scales fp32 [rows] as vxb_quantize_rows
+ * writes them (ldq = row_bytes, a multiple of 128, padding zero), weight int8
+ * [d_out,row_bytes] row-major with zero padding, weight_scales fp32 [d_out], bias
+ * fp32 [d_out] or NULL, y fp32 with row stride ldy.  Larger sizes are refused
+ * (return 0) with the limit named in `error`; nothing has been written then.
+ *
+ * The call makes no cudaMalloc / cudaFree and calls no allocating routine.  The
+ * first call on each device looks up the array's address on that device and sets
+ * a kernel attribute; make that first call before any stream capture begins.
+ * All calls share the one array: each call clears the part it uses, so results
+ * do not depend on earlier calls, but two calls whose GPU work overlaps (different
+ * streams, or graphs replayed concurrently) race on it - keep them ordered.
+ * The work is enqueued on `stream` (a cudaStream_t); with wait != 0 the call also
+ * waits for it and returns -1 if a bounded device wait expired.  error/error_bytes
+ * name an optional buffer for a message. */
+#define VXB_NOALLOC_MAX_ROWS 32u
+#define VXB_NOALLOC_MAX_CHANNELS 16384u
+VXB_API int vxb_decode_linear_f32_noalloc(const int8_t* q, const float* row_scales, uint32_t rows,
+                                  const int8_t* weight, const float* weight_scales,
+                                  const float* bias, uint32_t d_out, uint32_t row_bytes,
+                                  float* y, uint32_t ldy, void* stream, int wait,
+                                  char* error, size_t error_bytes);
+
 /* ---- reference-facing entries (HOST pointers) ------------------------- */
 /* Drop-in for the VxW8A8Ops.qlinear_i8u8 slot
  * (native/src/backends/w8a8_device_ops.h:15-17,89-124; CUDA implementation

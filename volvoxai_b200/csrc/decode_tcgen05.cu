@@ -310,3 +310,157 @@ cudaError_t launch_decode_tcgen05(const DecodeTcgen05Args& args, int sm_count, c
 }
 
 }  // namespace vxb
+
+// ---------------------------------------------------------------------------------------
+// Allocation-free entry point (declared in include/vxb200_w8a8.h).
+//
+// The stream-K decode kernel needs scratch in global memory: an int32 [rows, d_out]
+// workspace where CTAs that hold part of a tile's K range meet, one counter per 128-channel
+// tile and a status word.  The library's ordinary entries take that scratch from buffers a
+// VxbContext allocates with cudaMalloc.  This variant instead keeps it in a fixed array that
+// is part of the loaded module, so a caller that is not allowed to allocate (a host with a
+// sealed device-memory inventory, or code running while its stream is being captured) can
+// still run the decode linear.  Every GPU that loads the library holds the array until exit.
+// ---------------------------------------------------------------------------------------
+#include "../../include/vxb200_w8a8.h"
+
+#include <cstdio>
+#include <mutex>
+
+namespace {
+
+constexpr uint32_t kNoAllocMaxRows = VXB_NOALLOC_MAX_ROWS;
+constexpr uint32_t kNoAllocMaxChannels = VXB_NOALLOC_MAX_CHANNELS;
+constexpr size_t kNoAllocStatusBytes = 256;
+constexpr size_t kNoAllocCounterBytes = (size_t)(kNoAllocMaxChannels / 128) * 4;
+constexpr size_t kNoAllocWorkspaceBytes = (size_t)kNoAllocMaxRows * kNoAllocMaxChannels * 4;
+constexpr size_t kNoAllocBytes = kNoAllocStatusBytes + kNoAllocCounterBytes + kNoAllocWorkspaceBytes;
+
+// In host code this name is only a stand-in for the symbol, not a device address: the
+// address a kernel can use comes from cudaGetSymbolAddress on the device in question.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_noalloc_mutex;
+unsigned char* g_noalloc_ptr[kMaxDevices] = {};   // per device: address of its copy of the array
+int g_noalloc_sms[kMaxDevices] = {};
+
+typedef CUresult (*NoAllocEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                    const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                    const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// Writes the reason into the caller's buffer (if any) and returns `code`.
+struct NoAllocError {
+    char* text; size_t bytes;
+    int operator()(int code, const char* what, cudaError_t e = cudaSuccess) const {
+        if (text && bytes) {
+            if (e != cudaSuccess) snprintf(text, bytes, "%s: %s", what, cudaGetErrorString(e));
+            else snprintf(text, bytes, "%s", what);
+        }
+        return code;
+    }
+};
+
+bool noalloc_encode(CUtensorMap* map, const void* base, uint32_t rows, uint32_t row_bytes, uint32_t box_rows) {
+    static NoAllocEncodeFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess) return false;
+        fn = (NoAllocEncodeFn)p;
+    }
+    cuuint64_t dims[2] = {row_bytes, rows};
+    cuuint64_t strides[1] = {row_bytes};
+    cuuint32_t box[2] = {128, box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+extern "C" int vxb_decode_linear_f32_noalloc(const int8_t* q, const float* row_scales, uint32_t rows,
+                                             const int8_t* weight, const float* weight_scales,
+                                             const float* bias, uint32_t d_out, uint32_t row_bytes,
+                                             float* y, uint32_t ldy, void* stream, int wait,
+                                             char* error, size_t error_bytes) {
+    const NoAllocError noalloc_fail{error, error_bytes};
+    if (error && error_bytes) error[0] = 0;
+    if (!q || !row_scales || !weight || !weight_scales || !y)
+        return noalloc_fail(0, "null argument");
+    if (rows == 0 || d_out == 0) return 1;
+    if (rows > kNoAllocMaxRows) {
+        if (error && error_bytes)
+            snprintf(error, error_bytes, "rows %u exceeds the fixed scratch (at most %u rows)", rows, kNoAllocMaxRows);
+        return 0;
+    }
+    if (d_out > kNoAllocMaxChannels) {
+        if (error && error_bytes)
+            snprintf(error, error_bytes, "d_out %u exceeds the fixed scratch (at most %u output channels)",
+                     d_out, kNoAllocMaxChannels);
+        return 0;
+    }
+    if (row_bytes == 0 || row_bytes % 128 != 0) return noalloc_fail(0, "row_bytes must be a positive multiple of 128");
+    if (ldy < d_out) return noalloc_fail(0, "output row stride smaller than d_out");
+    if (((uintptr_t)q | (uintptr_t)weight) & 15u) return noalloc_fail(0, "q and weight must be 16-byte aligned");
+
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return noalloc_fail(0, "cudaGetDevice", e);
+    if (device < 0 || device >= kMaxDevices) return noalloc_fail(0, "device index out of range");
+    {
+        // One-time set-up for this device, with this device current: find where ITS copy of the
+        // array lives and let the kernel use its shared-memory budget. Nothing is allocated.
+        std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+        if (!g_noalloc_ptr[device]) {
+            unsigned char* ptr = nullptr;
+            e = cudaGetSymbolAddress((void**)&ptr, g_noalloc_scratch);
+            if (e != cudaSuccess || !ptr) return noalloc_fail(0, "cudaGetSymbolAddress(scratch)", e);
+            int sms = 0;
+            e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+            if (e != cudaSuccess || sms <= 0) return noalloc_fail(0, "cudaDeviceGetAttribute", e);
+            e = cudaFuncSetAttribute(vxb::decode_i8_tcgen05_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)vxb::DecodeCfg<32>::kSmemBytes);
+            if (e != cudaSuccess) return noalloc_fail(0, "cudaFuncSetAttribute", e);
+            g_noalloc_sms[device] = sms;
+            g_noalloc_ptr[device] = ptr;
+        }
+    }
+    unsigned char* scratch = g_noalloc_ptr[device];
+    int* status = reinterpret_cast<int*>(scratch);
+    uint32_t* counters = reinterpret_cast<uint32_t*>(scratch + kNoAllocStatusBytes);
+    int32_t* workspace = reinterpret_cast<int32_t*>(scratch + kNoAllocStatusBytes + kNoAllocCounterBytes);
+    cudaStream_t s = (cudaStream_t)stream;
+
+    // The array keeps whatever the previous call left: counters and the part of the workspace
+    // this call will use must start at zero (a memset node, not an allocation).
+    const size_t used = kNoAllocStatusBytes + kNoAllocCounterBytes + (size_t)rows * d_out * 4;
+    e = cudaMemsetAsync(scratch, 0, used, s);
+    if (e != cudaSuccess) return noalloc_fail(-1, "cudaMemsetAsync(scratch)", e);
+
+    vxb::DecodeTcgen05Args a;
+    if (!noalloc_encode(&a.tmap_w, weight, d_out, row_bytes, 128) ||
+        !noalloc_encode(&a.tmap_x, q, rows, row_bytes, 32))
+        return noalloc_fail(0, "cuTensorMapEncodeTiled failed");
+    a.rows = rows; a.n = d_out; a.kpad = row_bytes;
+    a.epi = vxb::EpilogueParams{};
+    a.epi.mode = vxb::kEpiF32; a.epi.row_scales = row_scales; a.epi.ws = weight_scales;
+    a.epi.bias_f32 = bias; a.epi.out = y; a.epi.ld = ldy;
+    a.workspace = workspace; a.counters = counters; a.status = status;
+    const uint64_t units = (uint64_t)((d_out + 127) / 128) * (row_bytes / 128);
+    const uint32_t grid = units < (uint64_t)g_noalloc_sms[device] ? (uint32_t)units : (uint32_t)g_noalloc_sms[device];
+    vxb::decode_i8_tcgen05_kernel<32><<<grid, vxb::kThreads, vxb::DecodeCfg<32>::kSmemBytes, s>>>(a);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return noalloc_fail(-1, "kernel launch", e);
+    if (wait) {
+        int host_status = 0;
+        e = cudaMemcpyAsync(&host_status, status, sizeof(int), cudaMemcpyDeviceToHost, s);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+        if (e != cudaSuccess) return noalloc_fail(-1, "waiting for the result", e);
+        if (host_status != 0) return noalloc_fail(-1, "a bounded device wait expired; the output is invalid");
+    }
+    return 1;
+}
