@@ -282,10 +282,10 @@ def gpu_arm(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     peaks = measured_peaks()
+    from volvoxai_b200 import sharded
     m, k, n = args.rows, args.k, args.n
-    if n % world:
-        raise SystemExit(f"N={n} does not shard over {world} GPUs")
-    n_local = n // world
+    lo, hi = sharded.shard_bounds(n, world, rank)
+    n_local = hi - lo
 
     ctx = w8a8.Context(local)
     ctx.use_torch_stream()
@@ -307,13 +307,15 @@ def gpu_arm(args):
         dist.broadcast(out_scale_t, 0)
     out_scale = float(out_scale_t.item())
 
-    y_local = torch.empty((m, n_local), dtype=torch.int8, device="cuda")
-    y_all = torch.empty((world, m, n_local), dtype=torch.int8, device="cuda") if world > 1 else None
+    lin = sharded.NShardedLinear(
+        n, world, rank, lambda x, out: ctx.linear_i8(weight, x, out_scale, 0, out=out), torch.int8, "cuda")
+    y_local = lin.forward_sharded(x_dev)
 
     def step(gather=True):
-        ctx.linear_i8(weight, x_dev, out_scale, 0, out=y_local)
         if world > 1 and gather:
-            dist.all_gather_into_tensor(y_all, y_local)
+            lin.forward_gathered(x_dev)   # local slab + NCCL all-gather of the int8 slabs
+        else:
+            lin.forward_sharded(x_dev)
 
     def barrier():
         if world > 1:

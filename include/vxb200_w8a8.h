@@ -59,7 +59,8 @@ enum {
     VXB_ROUTE_GEMV = 1,     /* dp4a + warp-shuffle GEMV (rows <= 32) */
     VXB_ROUTE_TCGEN05 = 2,  /* TMA-fed tcgen05 kind::i8 GEMM, TMEM accumulators */
     VXB_ROUTE_SIMT = 3,     /* one-thread-per-output dp4a kernel (verification) */
-    VXB_ROUTE_DECODE = 4    /* weight-streaming stream-K tcgen05 kernel (rows <= 128) */
+    VXB_ROUTE_DECODE = 4,   /* weight-streaming tcgen05 kernel, whole channels per CTA (rows <= 128) */
+    VXB_ROUTE_DECODE_STREAMK = 5 /* weight-streaming stream-K tcgen05 kernel (rows <= 128) */
 };
 
 VXB_API uint32_t vxb_abi_version(void);

@@ -38,7 +38,7 @@ def rel_err(y, ref):
     return float(np.abs(y[ok].astype(np.float64) - ref[ok]).max() / max(rms, 1e-30)) if ok.any() else 0.0
 
 
-ROUTES = {"gemv": 1, "tcgen05": 2, "simt": 3, "decode": 4}
+ROUTES = {"gemv": 1, "tcgen05": 2, "simt": 3, "decode": 4, "streamk": 5}
 
 
 def run_case(torch, ctx, oracle, case, routes, bias_i32=None, out_zero=0):
@@ -149,14 +149,15 @@ def test_small_m_routes(torch, ctx, oracle, rows, k, n):
     if rows > 4:
         case["x"][3, k // 3] = np.inf
     bias_i32 = rng.integers(-300, 300, size=n).astype(np.int32)
-    run_case(torch, ctx, oracle, case, ["gemv", "decode", "tcgen05", "simt"], bias_i32=bias_i32, out_zero=-3)
+    run_case(torch, ctx, oracle, case, ["gemv", "decode", "streamk", "tcgen05", "simt"], bias_i32=bias_i32, out_zero=-3)
 
 
 @pytest.mark.parametrize("rows", [33, 48, 64, 65, 100, 127, 128])
 @pytest.mark.parametrize("k,n", [(64, 19), (576, 192), (1024, 3072), (3072, 1024), (4096, 520)])
 def test_decode_route_up_to_128_rows(torch, ctx, oracle, rows, k, n):
-    """The weight-streaming stream-K kernel with 64 and 128 token slots, split over every SM
-    (partial tiles meet in the integer workspace) - bit-exact for any split."""
+    """Both weight-streaming kernels with 64 and 128 token slots: channel ownership per CTA,
+    and stream-K over every SM (partial tiles meet in the integer workspace) - bit-exact for
+    any split."""
     rng = np.random.default_rng(rows * 31 + k + n)
     case = {"x": (rng.standard_normal((rows, k)) * rng.uniform(0.01, 30, size=(rows, 1))).astype(np.float32),
             "w": rng.integers(-128, 128, size=(n, k), dtype=np.int8),
@@ -164,7 +165,7 @@ def test_decode_route_up_to_128_rows(torch, ctx, oracle, rows, k, n):
             "bias": rng.standard_normal(n).astype(np.float32)}
     case["x"][1] = 0
     case["x"][rows - 2, k // 3] = np.inf
-    run_case(torch, ctx, oracle, case, ["decode", "tcgen05"],
+    run_case(torch, ctx, oracle, case, ["decode", "streamk", "tcgen05"],
              bias_i32=rng.integers(-300, 300, size=n).astype(np.int32), out_zero=7)
 
 
@@ -179,7 +180,7 @@ def test_decode_route_leaves_its_workspace_clean(torch, ctx, oracle):
         want = oracle.w8a8_linear(c["x"], c["w"], c["ws"])
         weight = w8a8.Weight.from_i8(ctx, c["w"], c["ws"])
         for _ in range(3):
-            acc = ctx.linear_acc_i32(weight, dev(torch, c["x"]), route=4)
+            acc = ctx.linear_acc_i32(weight, dev(torch, c["x"]), route=5)
             ctx.synchronize()
             assert np.array_equal(acc.cpu().numpy(), want["acc"])
         weight.close()
@@ -210,7 +211,7 @@ def test_extreme_codes_do_not_overflow(torch, ctx, oracle):
     case = {"x": x, "w": np.full((n, k), -128, np.int8), "ws": np.full(n, 0.01, np.float32), "bias": None}
     run_case(torch, ctx, oracle, case, ["tcgen05"])
     case["x"] = x[:8]
-    run_case(torch, ctx, oracle, case, ["gemv", "decode"])
+    run_case(torch, ctx, oracle, case, ["gemv", "decode", "streamk"])
 
 
 def test_output_row_stride(torch, ctx, oracle):
@@ -277,7 +278,7 @@ def test_static_qlinear_dtypes_vs_oracle(torch, ctx, oracle, in_u8, out_u8):
         ozp = -ozp // 10
     want = oracle.qlinear_i8u8(x, w, b, ws, np.zeros(n, np.int32), 0.05, izp, 0.6, ozp, out_unsigned=out_u8)
     weight = w8a8.Weight.from_i8(ctx, w, ws, bias_i32=b)
-    for rws, route in ((rows, 2), (rows, 3), (rows, 4), (8, 1)):
+    for rws, route in ((rows, 2), (rows, 3), (rows, 4), (rows, 5), (8, 1)):
         out = ctx.qlinear_device(weight, dev(torch, x[:rws]), 0.05, izp, 0.6, ozp, out_unsigned=out_u8, route=route)
         ctx.synchronize()
         assert np.array_equal(out.cpu().numpy(), want[:rws])

@@ -65,7 +65,7 @@ def test_noalloc_matches_ordinary_entry_twice(torch, rows, k, n):
         x = torch.from_numpy((rng.standard_normal((rows, k)) * (1 + 9 * attempt)).astype(np.float32)).cuda()
         q, scales = ctx.prepare(weight, x)
         want = torch.empty((rows, n), dtype=torch.float32, device="cuda")
-        ctx.linear_prepared(weight, q, scales, want, mode=1, route=w8a8.ROUTE_DECODE)
+        ctx.linear_prepared(weight, q, scales, want, mode=1, route=w8a8.ROUTE_DECODE_STREAMK)
         ctx.synchronize()
         got = torch.full((rows, n), -7.0, dtype=torch.float32, device="cuda")
         rc, msg = call_noalloc(torch, q, scales, w_dev, ws_dev, bias_dev, n, row_bytes, got)

@@ -101,7 +101,9 @@ struct VxbWeight {
     int32_t* bias_i32 = nullptr;
     int32_t* wsum = nullptr;   // [d_out] sum of codes per channel
     CUtensorMap tmap_b;        // box 256 rows (large-M kernel)
-    CUtensorMap tmap_w128;     // box 128 rows (decode kernel)
+    CUtensorMap tmap_w128;     // box 128 rows (stream-K decode kernel)
+    CUtensorMap tmap_rows;     // box tile_rows rows (channel-owning decode kernel)
+    uint32_t tile_rows = 0, tiles_per_cta = 0;
     bool has_tmap = false;
     uint64_t bytes = 0;
     float ws_min = 0.0f, ws_max = 0.0f;  // range of the per-channel scales
@@ -166,6 +168,8 @@ int finish_weight(VxbContext* ctx, VxbWeight* w, const uint8_t* staging, uint32_
     }
     w->has_tmap = encode_i8_rows(&w->tmap_b, w->w, n, w->kpad, 256) &&
                   encode_i8_rows(&w->tmap_w128, w->w, n, w->kpad, 128);
+    decode_rows_plan(n, ctx->sm_count, &w->tile_rows, &w->tiles_per_cta);
+    w->has_tmap = w->has_tmap && encode_i8_rows(&w->tmap_rows, w->w, n, w->kpad, w->tile_rows);
     CUDA_TRY(cudaStreamSynchronize(ctx->stream), -1);
     return 1;
 }
@@ -188,9 +192,10 @@ Plan choose_route(const VxbContext* ctx, const VxbWeight* w, uint32_t rows, int 
     if (requested == VXB_ROUTE_GEMV) return {VXB_ROUTE_GEMV, "gemv-dp4a"};
     if (requested == VXB_ROUTE_SIMT) return {VXB_ROUTE_SIMT, "simt-dp4a"};
     if (requested == VXB_ROUTE_TCGEN05) return {VXB_ROUTE_TCGEN05, "tcgen05-i8"};
-    if (requested == VXB_ROUTE_DECODE) return {VXB_ROUTE_DECODE, "decode-tcgen05-i8"};
+    if (requested == VXB_ROUTE_DECODE) return {VXB_ROUTE_DECODE, "decode-rows-tcgen05-i8"};
+    if (requested == VXB_ROUTE_DECODE_STREAMK) return {VXB_ROUTE_DECODE_STREAMK, "decode-streamk-tcgen05-i8"};
     (void)ctx; (void)w;
-    if (rows <= 128) return {VXB_ROUTE_DECODE, "decode-tcgen05-i8"};
+    if (rows <= 128) return {VXB_ROUTE_DECODE, "decode-rows-tcgen05-i8"};
     return {VXB_ROUTE_TCGEN05, "tcgen05-i8"};
 }
 
@@ -205,6 +210,18 @@ int run_gemm(VxbContext* ctx, const VxbWeight* w, const int8_t* q, uint32_t rows
     } else if (plan.route == VXB_ROUTE_SIMT) {
         CUDA_TRY(launch_gemm_simt(q, rows, w->w, w->d_out, w->kpad, epi, ctx->stream), -1);
     } else if (plan.route == VXB_ROUTE_DECODE) {
+        if (rows > 128) return fail(0, "decode route needs rows <= 128 (got %u)", rows);
+        if (!w->has_tmap) return fail(0, "no tensor map for this weight (driver entry point missing)");
+        DecodeRowsArgs a;
+        if (!encode_i8_rows(&a.tmap_x, q, rows, w->kpad, decode_rows_token_slots(rows)))
+            return fail(0, "cuTensorMapEncodeTiled failed for activations");
+        a.tmap_w = w->tmap_rows;
+        a.rows = rows; a.n = w->d_out; a.kpad = w->kpad;
+        a.tile_rows = w->tile_rows; a.tiles_per_cta = w->tiles_per_cta; a.stages = 0;
+        a.w_stage_bytes = round_up(w->tile_rows * kKAlign, 1024u);
+        a.epi = epi; a.status = ctx->status;
+        CUDA_TRY(launch_decode_rows(a, ctx->stream), -1);
+    } else if (plan.route == VXB_ROUTE_DECODE_STREAMK) {
         if (rows > 128) return fail(0, "decode route needs rows <= 128 (got %u)", rows);
         if (!w->has_tmap) return fail(0, "no tensor map for this weight (driver entry point missing)");
         // split-K scratch: int32 [rows, d_out] + one counter per 128-channel tile, kept zero

@@ -32,6 +32,27 @@ struct EpilogueParams {
     uint32_t ld;              // output row stride in elements
 };
 
+// ---- programmatic dependent launch ------------------------------------------------------
+// A kernel launched with launch_pdl() may start while the kernel before it in the stream is
+// still running. pdl_wait() returns once every kernel this launch depends on has completed
+// and its writes are visible (at once when the launch carries no such dependency);
+// pdl_release() lets the NEXT launch in the stream begin. Only kernels that call pdl_wait()
+// before touching a predecessor's data may be launched this way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 // ---- epilogue arithmetic (every operation separately rounded; no FMA) ----
 
 // E1: y = f32(f32(acc) * f32(as*ws)) + bias
@@ -147,6 +168,23 @@ struct GemmTcgen05Args {
 };
 cudaError_t launch_gemm_tcgen05(const GemmTcgen05Args& args, int sm_count, cudaStream_t stream);
 cudaError_t gemm_tcgen05_prepare();  // one-time func attribute set-up
+
+// K3: decode kernel in which every CTA owns whole output channels (rows <= 128).
+// tile_rows / tiles_per_cta come from decode_rows_plan(); tmap_w has a box of tile_rows rows,
+// tmap_x a box of decode_rows_token_slots(rows) rows.
+struct DecodeRowsArgs {
+    CUtensorMap tmap_w;
+    CUtensorMap tmap_x;
+    uint32_t rows, n, kpad;
+    uint32_t tile_rows, tiles_per_cta;
+    uint32_t stages;          // filled in by the launcher
+    uint32_t w_stage_bytes;   // round_up(tile_rows * 128, 1024)
+    EpilogueParams epi;
+    int* status;
+};
+uint32_t decode_rows_token_slots(uint32_t rows);  // 8 / 16 / 32 / 64 / 128
+void decode_rows_plan(uint32_t n, int sm_count, uint32_t* tile_rows, uint32_t* tiles_per_cta);
+cudaError_t launch_decode_rows(const DecodeRowsArgs& args, cudaStream_t stream);
 
 // K3b: skinny stream-K tcgen05 kernel for rows <= 128 (weights are the UMMA M operand).
 // workspace: int32 [rows, n] zero on entry and zero again on exit; counters: uint32

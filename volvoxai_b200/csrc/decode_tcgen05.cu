@@ -12,8 +12,9 @@
 // compute whole tiles, and start another.  A CTA that holds only part of a tile's K range
 // adds its int32 partials into a zero-initialised workspace with red.global.add and bumps the
 // tile's counter; the CTA that completes the count applies the epilogue and clears workspace
-// and counter again.  Integer addition is associative, so the result is bit-identical for
-// every split.
+// and counter again (a contiguous range has at most two partial segments; their counting and
+// finishing is batched after the main loop).  Integer addition is associative, so the result
+// is bit-identical for every split.
 //
 // Reference counterparts: the decode kernels vx_packed_cuda_a8_columns and the fused
 // GEMV family (native/src/backends/cuda/kernels/cuda_forward_llm_kernels.inc:254-459,
@@ -39,14 +40,16 @@ constexpr uint32_t kThreads = 192;       // producer warp, MMA warp, 4 epilogue 
 template <uint32_t MT> struct DecodeCfg {
     static constexpr uint32_t kXBytes = MT * kDK;
     static constexpr uint32_t kStageBytes = kWBytes + kXBytes;
-    static constexpr uint32_t kStages = MT <= 64 ? 8 : 6;
+    // about 100 KB of stages per CTA: two CTAs fit one SM, so the next launch's CTA can move
+    // in (and prefetch its weights) while the previous launch's CTA is still finishing
+    static constexpr uint32_t kStages = MT <= 32 ? 5 : MT <= 64 ? 4 : 3;
     static constexpr uint32_t kTmemCols = 2 * MT < 32 ? 32 : 2 * MT;
     static constexpr uint32_t kOffBars = kStages * kStageBytes;
     static constexpr uint32_t kNumBars = 2 * kStages + 4;
     static constexpr uint32_t kOffTmemPtr = kOffBars + kNumBars * 8;
     static constexpr uint32_t kOffAbort = kOffTmemPtr + 4;
-    static constexpr uint32_t kOffFlag = kOffAbort + 4;       // epilogue-uniform decisions
-    static constexpr uint32_t kOffScales = kOffFlag + 8;      // float[MT] activation scales
+    static constexpr uint32_t kOffFlag = kOffAbort + 4;       // epilogue-uniform decisions (4 ints)
+    static constexpr uint32_t kOffScales = kOffFlag + 16;     // float[MT] activation scales
     static constexpr uint32_t kSmemBytes = kOffScales + MT * 4 + 1024;
 };
 
@@ -54,7 +57,7 @@ __device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, 128;" ::: 
 
 struct Segment { uint32_t tile, kb_begin, kb_end; };
 
-// The s-th segment of this CTA's unit range [u0, u1): consecutive K blocks of one tile.
+// Next segment of this CTA's unit range [u, u1): consecutive K blocks of one tile.
 __device__ __forceinline__ bool next_segment(uint64_t& u, uint64_t u1, uint32_t num_kb, Segment& seg) {
     if (u >= u1) return false;
     seg.tile = (uint32_t)(u / num_kb);
@@ -68,7 +71,7 @@ __device__ __forceinline__ bool next_segment(uint64_t& u, uint64_t u1, uint32_t 
 }
 
 template <uint32_t MT>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, 2)
 decode_i8_tcgen05_kernel(const __grid_constant__ DecodeTcgen05Args args) {
     using Cfg = DecodeCfg<MT>;
     extern __shared__ uint8_t smem_raw[];
@@ -100,26 +103,37 @@ decode_i8_tcgen05_kernel(const __grid_constant__ DecodeTcgen05Args args) {
         prefetch_tmap(&args.tmap_x);
     }
     if (warp == 1) { tmem_alloc(smem_u32(tmem_ptr), Cfg::kTmemCols); tmem_relinquish(); }
-    if (threadIdx.x >= 64) {
-        const uint32_t e = threadIdx.x - 64;
-        if (e < MT) s_as[e] = (e < args.rows && args.epi.mode != kEpiAcc) ? __ldg(args.epi.row_scales + e) : 0.0f;
-    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_ptr;
+    if (threadIdx.x == 0) pdl_release();
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
             uint32_t stage = 0, phase = 0, armed = 0, armed_parity = 0;
             bool ok = true;
-            uint64_t u = u0; Segment seg;
+            // Weights never depend on the preceding kernel: fill the ring with weight tiles
+            // first, then wait for the dependency and add the activation tiles.
+            {
+                uint64_t u = u0; Segment seg; uint32_t s = 0;
+                while (s < Cfg::kStages && next_segment(u, u1, num_kb, seg))
+                    for (uint32_t kb = seg.kb_begin; kb < seg.kb_end && s < Cfg::kStages; kb++, s++) {
+                        mbar_expect_tx(full(s), Cfg::kStageBytes);
+                        tma_load_2d(w_addr(s), &args.tmap_w, full(s), (int32_t)(kb * kDK), (int32_t)(seg.tile * kDM));
+                        armed |= 1u << s;
+                    }
+            }
+            pdl_wait();
+            uint64_t u = u0; Segment seg; uint32_t issued = 0;
             while (ok && next_segment(u, u1, num_kb, seg)) {
-                for (uint32_t kb = seg.kb_begin; kb < seg.kb_end; kb++) {
-                    if (!mbar_wait(empty(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
-                    mbar_expect_tx(full(stage), Cfg::kStageBytes);
-                    tma_load_2d(w_addr(stage), &args.tmap_w, full(stage), (int32_t)(kb * kDK), (int32_t)(seg.tile * kDM));
+                for (uint32_t kb = seg.kb_begin; kb < seg.kb_end; kb++, issued++) {
+                    if (issued >= Cfg::kStages) {
+                        if (!mbar_wait(empty(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
+                        mbar_expect_tx(full(stage), Cfg::kStageBytes);
+                        tma_load_2d(w_addr(stage), &args.tmap_w, full(stage), (int32_t)(kb * kDK), (int32_t)(seg.tile * kDM));
+                    }
                     tma_load_2d(x_addr(stage), &args.tmap_x, full(stage), (int32_t)(kb * kDK), 0);
                     armed |= 1u << stage;
                     armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
@@ -167,63 +181,77 @@ decode_i8_tcgen05_kernel(const __grid_constant__ DecodeTcgen05Args args) {
     } else {
         // ---------------- epilogue (warps 2..5): thread = one output channel ----------------
         const uint32_t quarter = warp & 3u;
+        const uint32_t e = threadIdx.x - 64;
         const EpilogueParams& ep = args.epi;
         const float zero_f = __int2float_rn(ep.out_zero);
         const float lo_f = __int2float_rn(ep.out_lo), hi_f = __int2float_rn(ep.out_hi);
+        // everything below reads what the preceding kernel wrote, or writes what it may read
+        pdl_wait();
+        if (e < MT) s_as[e] = (e < args.rows && ep.mode != kEpiAcc) ? __ldg(ep.row_scales + e) : 0.0f;
+        epi_bar();
+
+        // One 32-token chunk of channel n through the selected epilogue.
+        auto finish_chunk = [&](uint32_t n, uint32_t c, const int32_t (&v)[32], float wsv, float bias_f,
+                                int32_t bias_i) {
+#pragma unroll
+            for (uint32_t i = 0; i < 32; i++) {
+                const uint32_t m = c + i;
+                if (m >= args.rows) continue;
+                const size_t at = (size_t)m * ep.ld + n;
+                if (ep.mode == kEpiAcc) {
+                    ((int32_t*)ep.out)[at] = v[i];
+                } else if (ep.mode == kEpiF32) {
+                    ((float*)ep.out)[at] = epi_f32(v[i], s_as[m], wsv, bias_f);
+                } else {
+                    const float as = s_as[m];
+                    const int32_t qv = (ep.fast_div != 0 && div_const_row_ok(as))
+                        ? epi_i8_v2<true>(v[i] + bias_i, as, wsv, ep.out_scale, ep.out_rcp, zero_f, lo_f, hi_f, ep.out_zero)
+                        : epi_i8_v2<false>(v[i] + bias_i, as, wsv, ep.out_scale, ep.out_rcp, zero_f, lo_f, hi_f, ep.out_zero);
+                    ((int8_t*)ep.out)[at] = (int8_t)qv;
+                }
+            }
+        };
+        auto channel_consts = [&](uint32_t n, float& wsv, float& bias_f, int32_t& bias_i) {
+            const bool n_ok = n < args.n;
+            wsv = (n_ok && ep.mode != kEpiAcc) ? __ldg(ep.ws + n) : 0.0f;
+            bias_f = (n_ok && ep.mode == kEpiF32 && ep.bias_f32) ? __ldg(ep.bias_f32 + n) : 0.0f;
+            bias_i = (n_ok && ep.mode == kEpiI8 && ep.bias_i32) ? __ldg(ep.bias_i32 + n) : 0;
+        };
+
+        // A contiguous unit range holds at most two partial segments (its first and its last);
+        // their counting and finishing is deferred and done together after the loop.
+        uint32_t part_tile[2] = {0, 0}, part_blocks[2] = {0, 0}, parts = 0;
         uint32_t acc = 0, acc_phase = 0;
+        bool gave_up = false;
         uint64_t u = u0; Segment seg;
         while (next_segment(u, u1, num_kb, seg)) {
+            const uint32_t n = seg.tile * kDM + quarter * 32 + lane;
+            const bool n_ok = n < args.n;
+            const bool whole = seg.kb_begin == 0 && seg.kb_end == num_kb;
+            float wsv, bias_f; int32_t bias_i;
+            channel_consts(n, wsv, bias_f, bias_i);   // in flight while the MMAs run
+
             const bool waited = mbar_wait(tmem_full(acc), acc_phase, abort_flag);
             // make the give-up decision uniform across the four epilogue warps
             epi_bar();
             if (threadIdx.x == 64) epi_flag[0] = (*abort_flag != 0 || !waited) ? 1 : 0;
             epi_bar();
-            if (epi_flag[0]) break;
+            if (epi_flag[0]) { gave_up = true; break; }
             tc_fence_after();
 
-            const uint32_t n = seg.tile * kDM + quarter * 32 + lane;
-            const bool n_ok = n < args.n;
-            const bool whole = seg.kb_begin == 0 && seg.kb_end == num_kb;
             const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + acc * MT;
-            const float wsv = (n_ok && ep.mode != kEpiAcc) ? __ldg(ep.ws + n) : 0.0f;
-            float bias_f = 0.0f; int32_t bias_i = 0;
-            if (n_ok && ep.mode == kEpiF32 && ep.bias_f32) bias_f = __ldg(ep.bias_f32 + n);
-            if (n_ok && ep.mode == kEpiI8 && ep.bias_i32) bias_i = __ldg(ep.bias_i32 + n);
-
-            // One 32-token chunk of this thread's channel through the selected epilogue.
-            auto finish_chunk = [&](uint32_t c, const int32_t (&v)[32]) {
-                if (!n_ok) return;
-#pragma unroll
-                for (uint32_t i = 0; i < 32; i++) {
-                    const uint32_t m = c + i;
-                    if (m >= args.rows) continue;
-                    const size_t at = (size_t)m * ep.ld + n;
-                    if (ep.mode == kEpiAcc) {
-                        ((int32_t*)ep.out)[at] = v[i];
-                    } else if (ep.mode == kEpiF32) {
-                        ((float*)ep.out)[at] = epi_f32(v[i], s_as[m], wsv, bias_f);
-                    } else {
-                        const float as = s_as[m];
-                        const int32_t qv = (ep.fast_div != 0 && div_const_row_ok(as))
-                            ? epi_i8_v2<true>(v[i] + bias_i, as, wsv, ep.out_scale, ep.out_rcp, zero_f, lo_f, hi_f, ep.out_zero)
-                            : epi_i8_v2<false>(v[i] + bias_i, as, wsv, ep.out_scale, ep.out_rcp, zero_f, lo_f, hi_f, ep.out_zero);
-                        ((int8_t*)ep.out)[at] = (int8_t)qv;
-                    }
-                }
-            };
-
 #pragma unroll 1
             for (uint32_t c = 0; c < MT; c += 32) {
                 uint32_t r[32];
                 tmem_ld32(taddr + c, r);
                 tmem_ld_wait();
-                if (c >= args.rows) continue;
+                if (c >= args.rows || !n_ok) continue;
                 int32_t v[32];
 #pragma unroll
                 for (int i = 0; i < 32; i++) v[i] = (int32_t)r[i];
                 if (whole) {
-                    finish_chunk(c, v);
-                } else if (n_ok) {
+                    finish_chunk(n, c, v, wsv, bias_f, bias_i);
+                } else {
                     // partial K range: add into the zero-initialised workspace
 #pragma unroll
                     for (uint32_t i = 0; i < 32; i++)
@@ -235,35 +263,49 @@ decode_i8_tcgen05_kernel(const __grid_constant__ DecodeTcgen05Args args) {
             mbar_arrive(tmem_empty(acc));
             acc ^= 1u;
             if (acc == 0) acc_phase ^= 1u;
+            if (!whole && parts < 2) {
+                part_tile[parts] = seg.tile;
+                part_blocks[parts] = seg.kb_end - seg.kb_begin;
+                parts++;
+            }
+        }
 
-            if (!whole) {
-                // count the K blocks delivered; whoever completes the tile finishes it
-                __threadfence();
-                epi_bar();
-                if (threadIdx.x == 64) {
-                    const uint32_t mine = seg.kb_end - seg.kb_begin;
-                    const uint32_t before = atomicAdd(args.counters + seg.tile, mine);
-                    epi_flag[1] = (before + mine == num_kb) ? 1 : 0;
-                }
-                epi_bar();
-                if (epi_flag[1] != 0) {
-                    __threadfence();
+        if (!gave_up && parts > 0) {
+            // count the K blocks delivered to each partial tile; whoever completes a tile finishes it
+            __threadfence();
+            epi_bar();
+            if (threadIdx.x == 64) {
+                uint32_t before[2] = {0, 0};
+                for (uint32_t p = 0; p < parts; p++) before[p] = atomicAdd(args.counters + part_tile[p], part_blocks[p]);
+                for (uint32_t p = 0; p < parts; p++) epi_flag[1 + p] = (before[p] + part_blocks[p] == num_kb) ? 1 : 0;
+            }
+            epi_bar();
+            bool any = false;
+            for (uint32_t p = 0; p < parts; p++) any |= epi_flag[1 + p] != 0;
+            if (any) __threadfence();
+            for (uint32_t p = 0; p < parts; p++) {
+                if (epi_flag[1 + p] == 0) continue;
+                const uint32_t tile = part_tile[p];
+                const uint32_t n = tile * kDM + quarter * 32 + lane;
+                if (n < args.n) {
+                    float wsv, bias_f; int32_t bias_i;
+                    channel_consts(n, wsv, bias_f, bias_i);
 #pragma unroll 1
                     for (uint32_t c = 0; c < MT && c < args.rows; c += 32) {
                         int32_t v[32];
 #pragma unroll
                         for (uint32_t i = 0; i < 32; i++) {
                             v[i] = 0;
-                            if (n_ok && c + i < args.rows) {
+                            if (c + i < args.rows) {
                                 int32_t* slot = args.workspace + (size_t)(c + i) * args.n + n;
                                 v[i] = __ldcg(slot);
                                 __stcg(slot, 0);   // leave the workspace clean for the next call
                             }
                         }
-                        finish_chunk(c, v);
+                        finish_chunk(n, c, v, wsv, bias_f, bias_i);
                     }
-                    if (threadIdx.x == 64) args.counters[seg.tile] = 0u;
                 }
+                if (threadIdx.x == 64) args.counters[tile] = 0u;
             }
         }
     }
@@ -293,8 +335,9 @@ cudaError_t launch_t(const DecodeTcgen05Args& args, int sm_count, cudaStream_t s
     }
     const uint64_t units = (uint64_t)((args.n + kDM - 1) / kDM) * (args.kpad / kDK);
     const uint32_t grid = units < (uint64_t)sm_count ? (uint32_t)units : (uint32_t)sm_count;
-    decode_i8_tcgen05_kernel<MT><<<grid, kThreads, Cfg::kSmemBytes, stream>>>(args);
-    return cudaGetLastError();
+    // This launch may begin (prologue, weight prefetch) while the kernel before it in the
+    // stream is still finishing; the kernel waits before it touches the predecessor's data.
+    return launch_pdl(decode_i8_tcgen05_kernel<MT>, dim3(grid), dim3(kThreads), Cfg::kSmemBytes, stream, args);
 }
 
 }  // namespace

@@ -89,6 +89,10 @@ quantize_rows_vec(const float* __restrict__ x, uint32_t rows, uint32_t k, int8_t
                   uint32_t ldq, float* __restrict__ row_scales, int32_t* __restrict__ valid) {
     __shared__ float smem_max[kThreads / 32];
     __shared__ int smem_bad[kThreads / 32];
+    // let the consumer kernel start its prologue and weight prefetch now; then wait until the
+    // kernel before this one has finished with the activations and the q scratch
+    pdl_release();
+    pdl_wait();
     constexpr int kRowsPerCta = kThreads / THREADS_PER_ROW;
     const uint32_t row = blockIdx.x * kRowsPerCta + threadIdx.x / THREADS_PER_ROW;
     const int t = threadIdx.x % THREADS_PER_ROW;
@@ -156,6 +160,8 @@ quantize_rows_vec(const float* __restrict__ x, uint32_t rows, uint32_t k, int8_t
 __global__ void __launch_bounds__(kThreads)
 quantize_rows_scalar(const float* __restrict__ x, uint32_t rows, uint32_t k, int8_t* __restrict__ q,
                      uint32_t ldq, float* __restrict__ row_scales, int32_t* __restrict__ valid) {
+    pdl_release();
+    pdl_wait();
     const uint32_t row = blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (row >= rows) return;
@@ -228,10 +234,10 @@ cudaError_t launch_vec(const float* x, uint32_t rows, uint32_t k, int8_t* q, uin
     constexpr int kRowsPerCta = kThreads / TPR;
     const uint32_t grid = (rows + kRowsPerCta - 1) / kRowsPerCta;
     if (k / 4 <= (uint32_t)TPR * kMaxVecPerThread)
-        quantize_rows_vec<TPR, true><<<grid, kThreads, 0, stream>>>(x, rows, k, q, ldq, row_scales, valid);
-    else
-        quantize_rows_vec<TPR, false><<<grid, kThreads, 0, stream>>>(x, rows, k, q, ldq, row_scales, valid);
-    return cudaGetLastError();
+        return launch_pdl(quantize_rows_vec<TPR, true>, dim3(grid), dim3(kThreads), 0, stream,
+                          x, rows, k, q, ldq, row_scales, valid);
+    return launch_pdl(quantize_rows_vec<TPR, false>, dim3(grid), dim3(kThreads), 0, stream,
+                      x, rows, k, q, ldq, row_scales, valid);
 }
 
 }  // namespace
@@ -242,8 +248,8 @@ cudaError_t launch_quantize_rows(const float* x, uint32_t rows, uint32_t k, int8
     const bool vec = (k % 4 == 0) && (ldq % 4 == 0) && ((uintptr_t)x % 16 == 0) && ((uintptr_t)q % 4 == 0);
     if (!vec) {
         const uint32_t grid = (rows + kThreads / 32 - 1) / (kThreads / 32);
-        quantize_rows_scalar<<<grid, kThreads, 0, stream>>>(x, rows, k, q, ldq, row_scales, valid);
-        return cudaGetLastError();
+        return launch_pdl(quantize_rows_scalar, dim3(grid), dim3(kThreads), 0, stream,
+                          x, rows, k, q, ldq, row_scales, valid);
     }
     // Threads per row grow with K so each thread keeps at most 8 float4 in registers.
     if (k <= 256) return launch_vec<8>(x, rows, k, q, ldq, row_scales, valid, stream);
