@@ -228,6 +228,14 @@ VXB_API int vxb_decode_linear_f32_noalloc(const int8_t* q, const float* row_scal
                                   float* y, uint32_t ldy, void* stream, int wait,
                                   char* error, size_t error_bytes);
 
+/* Measurement utility (no counterpart in the reference): on one SM, `iters` rounds of
+ * `per_commit` kind::i8 MMAs of shape m x n x 32 cycling through `accs` TMEM accumulators,
+ * one commit + wait per round; returns SM clocks per MMA.  Used to size the decode kernels
+ * (how the tensor pipe's time per instruction depends on m and n, and whether MMAs into
+ * one accumulator serialise). */
+VXB_API int vxb_measure_mma_issue(VxbContext* ctx, uint32_t m, uint32_t n, uint32_t accs, uint32_t per_commit,
+                          uint32_t iters, double* cycles_per_mma);
+
 /* ---- reference-facing entries (HOST pointers) ------------------------- */
 /* Drop-in for the VxW8A8Ops.qlinear_i8u8 slot
  * (native/src/backends/w8a8_device_ops.h:15-17,89-124; CUDA implementation

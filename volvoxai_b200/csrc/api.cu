@@ -591,6 +591,24 @@ int vxb_linear_host(VxbContext* ctx, const VxbWeight* w, const float* x_host, ui
     return vxb_context_synchronize(ctx) == 1 ? 1 : -1;
 }
 
+int vxb_measure_mma_issue(VxbContext* ctx, uint32_t m, uint32_t n, uint32_t accs, uint32_t per_commit,
+                          uint32_t iters, double* cycles_per_mma) {
+    if (!ctx || !cycles_per_mma || !iters || !per_commit || !accs) return fail(0, "bad argument");
+    if (ensure_device(ctx) != 1) return -1;
+    if (!ctx->tcgen05_ready) { CUDA_TRY(gemm_tcgen05_prepare(), 0); ctx->tcgen05_ready = true; }
+    long long* cycles = nullptr;
+    CUDA_TRY(cudaMalloc(&cycles, sizeof(long long)), 0);
+    cudaError_t err = launch_mma_probe(m, n, accs, per_commit, iters, cycles, ctx->status, ctx->stream);
+    long long host = 0;
+    if (err == cudaSuccess) err = cudaMemcpyAsync(&host, cycles, sizeof host, cudaMemcpyDeviceToHost, ctx->stream);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(ctx->stream);
+    cudaFree(cycles);
+    count_launch();
+    if (err != cudaSuccess) return fail(-1, "mma probe failed: %s", cudaGetErrorString(err));
+    *cycles_per_mma = (double)host / ((double)iters * per_commit);
+    return vxb_context_synchronize(ctx) == 1 ? 1 : -1;
+}
+
 int vxb_measure_i8_tensor_peak(VxbContext* ctx, uint32_t iters, double* tops) {
     if (!ctx || !tops || !iters) return fail(0, "bad argument");
     if (ensure_device(ctx) != 1) return -1;

@@ -177,7 +177,7 @@ struct DecodeRowsArgs {
     CUtensorMap tmap_x;
     uint32_t rows, n, kpad;
     uint32_t tile_rows, tiles_per_cta;
-    uint32_t stages;          // filled in by the launcher
+    uint32_t stages, umma_n, tmem_cols, acc_cols, issuers;   // filled in by the launcher
     uint32_t w_stage_bytes;   // round_up(tile_rows * 128, 1024)
     EpilogueParams epi;
     int* status;
@@ -206,5 +206,10 @@ cudaError_t launch_decode_tcgen05(const DecodeTcgen05Args& args, int sm_count, c
 // spent per CTA.
 cudaError_t launch_i8_peak_probe(uint32_t iters, long long* cycles, int* status, int sm_count,
                                  cudaStream_t stream);
+
+// Issue-pattern probe on one SM: `iters` rounds of `per_commit` MMAs of shape m x n x 32 cycling
+// through `accs` accumulators, one commit + wait per round; cycles[0] = SM clocks spent.
+cudaError_t launch_mma_probe(uint32_t m, uint32_t n, uint32_t accs, uint32_t per_commit, uint32_t iters,
+                             long long* cycles, int* status, cudaStream_t stream);
 
 }  // namespace vxb

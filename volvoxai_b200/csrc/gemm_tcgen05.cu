@@ -292,7 +292,8 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ GemmTcgen05Args args) {
 // stay resident in shared memory (no TMA, no epilogue): the dense int8 rate the
 // tensor pipe sustains, used as the measured roofline denominator for K2.
 __global__ void __launch_bounds__(128, 1)
-i8_peak_probe_kernel(uint32_t iters, long long* cycles, int* status) {
+i8_peak_probe_kernel(uint32_t iters, long long* cycles, int* status, uint32_t idesc, uint32_t accs,
+                     uint32_t acc_stride, uint32_t per_commit) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     __shared__ uint64_t bar;
@@ -308,25 +309,29 @@ i8_peak_probe_kernel(uint32_t iters, long long* cycles, int* status) {
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_ptr;
-    if (threadIdx.x == 0) {
-        constexpr uint32_t idesc = make_idesc(kBM, kBN);
+    // `issuers` (high 16 bits of accs) warps issue concurrently, each with its own barrier and
+    // accumulator set; issuer 0 reports its clocks
+    const uint32_t issuers = (accs >> 16) ? (accs >> 16) : 1u;
+    accs &= 0xffffu;
+    __shared__ uint64_t bars[4];
+    if (threadIdx.x == 0) { for (int i = 0; i < 4; i++) mbar_init(smem_u32(&bars[i]), 1); fence_barrier_init(); }
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0 && warp < issuers) {
         const uint32_t a_addr = smem_u32(base), b_addr = a_addr + kABytes;
+        const uint32_t my_bar = smem_u32(&bars[warp]);
+        const uint32_t my_tmem = tmem_base + warp * accs * acc_stride;
         const long long t0 = clock64();
         uint32_t parity = 0;
         bool ok = true;
-        // commit every 256 instructions so the issue queue never holds an unbounded backlog
         for (uint32_t it = 0; ok && it < iters; it++) {
-            for (uint32_t j = 0; j < 64; j++) {
-#pragma unroll
-                for (uint32_t k = 0; k < 4; k++)
-                    umma_i8(tmem_base + (j & 1u) * kAccCols, make_smem_desc(a_addr + k * kUmmaK),
-                            make_smem_desc(b_addr + k * kUmmaK), idesc, 1u);
-            }
-            umma_commit(smem_u32(&bar));
-            ok = mbar_wait(smem_u32(&bar), parity, &abort_flag);
+            for (uint32_t j = 0; j < per_commit; j++)
+                umma_i8(my_tmem + (j & (accs - 1u)) * acc_stride, make_smem_desc(a_addr + (j & 3u) * kUmmaK),
+                        make_smem_desc(b_addr + (j & 3u) * kUmmaK), idesc, 1u);
+            umma_commit(my_bar);
+            ok = mbar_wait(my_bar, parity, &abort_flag);
             parity ^= 1u;
         }
-        cycles[blockIdx.x] = clock64() - t0;
+        if (warp == 0) cycles[blockIdx.x] = clock64() - t0;
         if (!ok && status) atomicExch(status, 2);
     }
     tc_fence_before();
@@ -355,7 +360,18 @@ cudaError_t launch_gemm_tcgen05(const GemmTcgen05Args& args, int sm_count, cudaS
 
 cudaError_t launch_i8_peak_probe(uint32_t iters, long long* cycles, int* status, int sm_count,
                                  cudaStream_t stream) {
-    i8_peak_probe_kernel<<<sm_count, 128, kStageBytes + 1024, stream>>>(iters, cycles, status);
+    i8_peak_probe_kernel<<<sm_count, 128, kStageBytes + 1024, stream>>>(
+        iters, cycles, status, make_idesc(kBM, kBN), 2u, kAccCols, 256u);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_mma_probe(uint32_t m, uint32_t n, uint32_t accs, uint32_t per_commit, uint32_t iters,
+                             long long* cycles, int* status, cudaStream_t stream) {
+    uint32_t stride = n < 32 ? 32 : n;
+    const uint32_t issuers = (accs >> 16) ? (accs >> 16) : 1u;
+    if ((accs & 0xffffu) * stride * issuers > kTmemCols || issuers > 4) return cudaErrorInvalidValue;
+    i8_peak_probe_kernel<<<1, 128, kStageBytes + 1024, stream>>>(iters, cycles, status, make_idesc(m, n), accs,
+                                                                 stride, per_commit);
     return cudaGetLastError();
 }
 
