@@ -377,13 +377,14 @@ def gpu_arm(args):
         "quantize_frac_of_hbm": ((5.0 * m * k + 4.0 * m) / (quant_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]
                                  if quant_ms > 0 else None),
     }
-    traffic_file = os.path.join(ROOT, "profiles", "gemm_tcgen05_traffic.json")
-    if os.path.exists(traffic_file):
-        with open(traffic_file) as f:
-            t = json.load(f)
-        # ncu capture of a smaller launch, scaled by tiles processed (traffic grows with tiles)
-        roofline["traffic"] = t["dram_bytes_per_tile_k4096"] * (m / 128.0) * (n_local / 256.0) * (k / 4096.0)
-        roofline["traffic_source"] = t["source"]
+    # DRAM traffic per launch, scaled from the ncu capture of a smaller launch of the same kernel
+    # (M 4096, K 4096, N 14336: dram read 75.64 MB = 1.002 x (M + N_local) x Kpad, dram write 27.3 MB =
+    # 0.466 x M x N_local; see profiles/gemm_i8_tcgen05_M4096_K4096_N14336.md). Reads grow with
+    # (M + N) x K, writes with M x N.
+    kpad = (k + 127) // 128 * 128
+    roofline["traffic"] = 1.002 * (m + n_local) * kpad + 0.466 * m * n_local
+    roofline["traffic_source"] = "ncu dram__bytes_read+write of the M4096 launch, scaled by (M+N)K and MN"
+    roofline["algorithmic_bytes"] = (m + n_local) * kpad + m * n_local
 
     # end to end through the host-pointer entry: pinned host buffers, copies inside the region
     x_pin = torch.from_numpy(x_host_np).pin_memory()
@@ -436,13 +437,83 @@ def gpu_arm(args):
         dist.destroy_process_group()
 
 
+def decode_arm(args):
+    """--workload decode: one decode-shaped linear (rows <= 128) on one GPU. A step is the
+    quantizer + the weight-streaming kernel on device-resident fp32 activations; weights rotate
+    through more than 2x L2 of distinct copies. Prints one JSON line with the HBM roofline of the
+    decode kernel (prepared activations, CUDA-graph replay of back-to-back launches)."""
+    import torch
+    from volvoxai_b200 import w8a8
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device; there is no CPU fallback")
+    peaks = measured_peaks()
+    rows, k, n = args.rows, args.k, args.n
+    ctx = w8a8.Context(0)
+    ctx.use_torch_stream()
+    rng = np.random.default_rng(7)
+    copies = max(2, int(np.ceil(300e6 / (k * n))))
+    base_w = rng.integers(-127, 128, size=(n, k), dtype=np.int8)
+    ws = rng.uniform(0.001, 0.02, size=n).astype(np.float32)
+    weights = [w8a8.Weight.from_i8(ctx, np.roll(base_w, c, axis=0), ws) for c in range(copies)]
+    x = torch.from_numpy(rng.standard_normal((rows, k)).astype(np.float32)).cuda()
+    y = torch.empty((rows, n), dtype=torch.float32, device="cuda")
+    q, sc = ctx.prepare(weights[0], x)
+    algo_bytes = k * n + 4 * n + 4 * rows * k + 4 * rows * n
+    side = torch.cuda.Stream()
+
+    def replay_ms(fn, launches):
+        for i in range(max(3, args.warmup)):
+            fn(i)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            ctx.use_torch_stream()
+            for i in range(launches):
+                fn(i)
+        ctx.use_torch_stream()
+        g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        e1.synchronize()
+        return e0.elapsed_time(e1) / launches
+
+    launches0 = w8a8.launch_count()
+    step_ms = replay_ms(lambda i: ctx.linear_f32(weights[i % copies], x, out=y), args.steps)
+    launches = w8a8.launch_count() - launches0
+    route = w8a8.last_route()
+    kern_ms = replay_ms(lambda i: ctx.linear_prepared(weights[i % copies], q, sc, y, mode=1), args.steps)
+    gbs = algo_bytes / (kern_ms * 1e-3) / 1e9
+    line = {
+        "metric": "w8a8_decode_linear_hbm_gbs", "value": algo_bytes / (step_ms * 1e-3) / 1e9, "unit": "GB/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": step_ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
+        "data": "synthetic",
+        "config": {"workload": f"w8a8_linear_decode_M{rows}_K{k}_N{n}_f32", "rows": rows, "k": k, "n": n,
+                   "route": route, "l2": f"{copies} distinct weight copies rotate (> 2x L2)",
+                   "timing": "CUDA-graph replay of back-to-back launches between two events"},
+        "gpu_launches": int(launches),
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": gbs / peaks["hbm_gbs"], "traffic": None, "kernel": "decode_rows_kernel",
+                     "kernel_us": kern_ms * 1e3, "algorithmic_bytes": algo_bytes,
+                     "frac_of_nominal_8000": gbs / NOMINAL_HBM_GBS, "peak_source": peaks["_source"]},
+    }
+    for wt in weights:
+        wt.close()
+    ctx.close()
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--workload", default="gemm", choices=["gemm", "decode"])
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--rows", type=int, default=8192)
+    ap.add_argument("--rows", type=int, default=None)
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--n", type=int, default=14336)
     ap.add_argument("--cpu-rows", type=int, default=512, help="row sample for the CPU legs")
@@ -450,8 +521,12 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true")
     args = ap.parse_args()
+    if args.rows is None:
+        args.rows = 8 if args.workload == "decode" else 8192
     if args.impl == "reference":
         reference_arm(args)
+    elif args.workload == "decode":
+        decode_arm(args)
     else:
         gpu_arm(args)
 

@@ -3,9 +3,11 @@
 //   acc[m,n] = sum_k q[m,k] * w[n,k]      q: [rows,kpad] int8, w: [n,kpad] int8
 //
 // Persistent, warp-specialised kernel, one CTA per SM:
-//   warp 0      TMA producer: 128x128B activation tile + 256x128B weight tile
-//               per stage into 128B-swizzled shared memory (4-stage ring,
-//               mbarrier transaction counts)
+//   warp 0      TMA producer of the 128x128B activation tile of each stage (128B-swizzled
+//               shared memory, 4-stage ring, mbarrier transaction counts)
+//   warp 10     TMA producer of the 256x128B weight tile of each stage (starting a TMA copy
+//               costs the issuing thread ~200 ns, more than half of the time the tensor pipe
+//               needs for a stage, so the two copies of a stage come from two threads)
 //   warp 1      allocates TMEM; one lane issues tcgen05.mma.cta_group::1
 //               .kind::i8 (M128 x N256 x K32 per instruction, 4 per stage);
 //               tcgen05.commit releases smem stages and publishes accumulators
@@ -41,7 +43,8 @@ constexpr uint32_t kStageBytes = kABytes + kBBytes;
 constexpr uint32_t kAccCols = kBN;                 // int32 columns per accumulator
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kEpiWarps = 8;
-constexpr uint32_t kThreads = 64 + 32 * kEpiWarps;  // producer warp + MMA warp + epilogue warps
+constexpr uint32_t kThreads = 64 + 32 * kEpiWarps + 32;  // A producer + MMA warp + epilogue warps + B producer
+constexpr uint32_t kBWarp = 2 + kEpiWarps;
 constexpr uint32_t kEpiThreads = 32 * kEpiWarps;
 constexpr uint32_t kEpiCols = kBN / 2;              // columns per epilogue warp
 
@@ -106,12 +109,10 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ GemmTcgen05Args args) {
             bool ok = true;
             for (uint32_t t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
                 const int32_t m0 = (int32_t)((t % tiles_m) * kBM);
-                const int32_t n0 = (int32_t)((t / tiles_m) * kBN);
                 for (uint32_t kb = 0; kb < num_kb; kb++) {
                     if (!mbar_wait(sm.empty(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
                     mbar_expect_tx(sm.full(stage), kStageBytes);
                     tma_load_2d(sm.a(stage), &args.tmap_a, sm.full(stage), (int32_t)(kb * kBK), m0);
-                    tma_load_2d(sm.b(stage), &args.tmap_b, sm.full(stage), (int32_t)(kb * kBK), n0);
                     armed |= 1u << stage;
                     armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
@@ -125,6 +126,20 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ GemmTcgen05Args args) {
                         if (mbar_try_wait(sm.full(s), (armed_parity >> s) & 1u)) break;
                         __nanosleep(500);
                     }
+                }
+            }
+        }
+    } else if (warp == kBWarp) {
+        // ---------------- TMA producer, weight tiles ----------------
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (uint32_t t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+                const int32_t n0 = (int32_t)((t / tiles_m) * kBN);
+                for (uint32_t kb = 0; kb < num_kb; kb++) {
+                    if (!mbar_wait(sm.empty(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
+                    tma_load_2d(sm.b(stage), &args.tmap_b, sm.full(stage), (int32_t)(kb * kBK), n0);
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
             }
         }
@@ -156,7 +171,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ GemmTcgen05Args args) {
                 if (acc == 0) acc_phase ^= 1u;
             }
         }
-    } else {
+    } else if (warp < kBWarp) {
         // ---------------- epilogue (warps 2..9) ----------------
         // Two warps per TMEM lane quarter (one per SM sub-partition pair), each owning one
         // half of the tile's 256 columns, so every scheduler has two epilogue warps to
