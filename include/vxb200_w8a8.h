@@ -171,7 +171,9 @@ VXB_API int vxb_qlinear_device(VxbContext* ctx, const VxbWeight* w, const void* 
  * [rows,d_out]), copies the result back and waits for it.  The host-pointer
  * convention of the reference's backend hooks
  * (native/src/backends/cuda/host/cuda_graph_llm_host.inc:714-783) applied to the
- * new op; pinned host memory makes the copies asynchronous DMA. */
+ * new op.  Batches of 1024 rows or more are cut into row chunks whose upload, kernels and
+ * download overlap on three streams (with pinned host memory the copies are asynchronous DMA
+ * in both directions at once); the call returns when the whole result is in y_host. */
 VXB_API int vxb_linear_host(VxbContext* ctx, const VxbWeight* w, const float* x_host, uint32_t rows,
                     int requant, float out_scale, int32_t out_zero, void* y_host);
 

@@ -353,6 +353,28 @@ def test_host_packed_linear_entry(torch, oracle):
     w8a8.host_cache_clear()
 
 
+@pytest.mark.parametrize("rows", [7, 1024, 3001])
+def test_host_whole_op_entry_matches_device_entries(torch, ctx, rows):
+    """vxb_linear_host (chunked, three-stream pipeline for large batches) returns the same bytes
+    as the device-pointer entries, for both epilogues and a ragged last chunk."""
+    from volvoxai_b200 import w8a8
+    c = wl.gemm_case(rows, 512, 384, seed=rows)
+    weight = w8a8.Weight.from_i8(ctx, c["w"], c["ws"], bias_f32=np.linspace(-1, 1, 384).astype(np.float32))
+    xd = dev(torch, c["x"])
+    want_f = ctx.linear_f32(weight, xd)
+    want_q = ctx.linear_i8(weight, xd, 0.05, 3)
+    ctx.synchronize()
+    x_pin = torch.from_numpy(c["x"]).pin_memory()
+    got_f = torch.empty((rows, 384), dtype=torch.float32).pin_memory()
+    got_q = torch.empty((rows, 384), dtype=torch.int8).pin_memory()
+    for _ in range(2):
+        ctx.linear_host(weight, x_pin, got_f, requant=False)
+        ctx.linear_host(weight, x_pin, got_q, requant=True, out_scale=0.05, out_zero=3)
+        assert torch.equal(got_f.view(torch.int32), want_f.cpu().view(torch.int32))
+        assert torch.equal(got_q, want_q.cpu())
+    weight.close()
+
+
 # ---- size-independent properties at benchmark sizes ---------------------------------------------
 
 def test_full_size_properties(torch, ctx, oracle):

@@ -88,6 +88,9 @@ struct VxbContext {
     int* status_host = nullptr;   // pinned mirror
     bool tcgen05_ready = false;
     // optional per-kernel timing (event pairs on the launching stream)
+    // vxb_linear_host: upload / download streams and their events
+    cudaStream_t copy_in = nullptr, copy_out = nullptr;
+    cudaEvent_t ev_in[2] = {}, ev_done[2] = {}, ev_out[2] = {}, ev_start = nullptr;
     bool profiling = false;
     std::vector<cudaEvent_t> prof_events[2];   // [0] = K1 quantizer, [1] = GEMM / GEMV
 };
@@ -318,6 +321,11 @@ void vxb_context_destroy(VxbContext* ctx) {
     ctx->q.release(); ctx->row_scales.release(); ctx->bias_eff.release();
     ctx->stage_in.release(); ctx->stage_out.release();
     ctx->splitk_ws.release(); ctx->splitk_counters.release();
+    if (ctx->copy_in) {
+        cudaStreamDestroy(ctx->copy_in); cudaStreamDestroy(ctx->copy_out);
+        for (int b = 0; b < 2; b++) { cudaEventDestroy(ctx->ev_in[b]); cudaEventDestroy(ctx->ev_done[b]); cudaEventDestroy(ctx->ev_out[b]); }
+        cudaEventDestroy(ctx->ev_start);
+    }
     if (ctx->status) cudaFree(ctx->status);
     if (ctx->status_host) cudaFreeHost(ctx->status_host);
     delete ctx;
@@ -576,18 +584,60 @@ int vxb_linear_host(VxbContext* ctx, const VxbWeight* w, const float* x_host, ui
     if (!ctx || !w || !x_host || !y_host) return fail(0, "null argument");
     if (!rows) return 1;
     if (ensure_device(ctx) != 1) return -1;
-    const size_t in_bytes = (size_t)rows * w->d_in * 4;
-    const size_t out_bytes = (size_t)rows * w->d_out * (requant ? 1 : 4);
-    CUDA_TRY(ctx->stage_in.reserve(in_bytes), 0);
-    CUDA_TRY(ctx->stage_out.reserve(out_bytes), 0);
-    CUDA_TRY(cudaMemcpyAsync(ctx->stage_in.ptr, x_host, in_bytes, cudaMemcpyHostToDevice, ctx->stream), -1);
-    int rc = requant
-        ? vxb_linear_i8(ctx, w, (const float*)ctx->stage_in.ptr, rows, out_scale, out_zero,
-                        (int8_t*)ctx->stage_out.ptr, w->d_out, VXB_ROUTE_AUTO)
-        : vxb_linear_f32(ctx, w, (const float*)ctx->stage_in.ptr, rows, (float*)ctx->stage_out.ptr,
-                         w->d_out, VXB_ROUTE_AUTO);
-    if (rc != 1) return rc;
-    CUDA_TRY(cudaMemcpyAsync(y_host, ctx->stage_out.ptr, out_bytes, cudaMemcpyDeviceToHost, ctx->stream), -1);
+    const size_t in_row = (size_t)w->d_in * 4, out_row = (size_t)w->d_out * (requant ? 1 : 4);
+    // Large batches go through in row chunks on three streams, so that the upload of chunk c+1,
+    // the kernels of chunk c and the download of chunk c-1 overlap (PCIe is full duplex and is
+    // what bounds this entry). Two staging buffers each way.
+    uint32_t chunk = rows;
+    if (rows >= 1024) {
+        chunk = (rows + 7) / 8;
+        chunk = (chunk + 127) / 128 * 128;
+        if (chunk < 256) chunk = 256;
+    }
+    const uint32_t chunks = (rows + chunk - 1) / chunk;
+    CUDA_TRY(ctx->stage_in.reserve(2 * (size_t)chunk * in_row), 0);
+    CUDA_TRY(ctx->stage_out.reserve(2 * (size_t)chunk * out_row), 0);
+    if (!ctx->copy_in) {
+        CUDA_TRY(cudaStreamCreateWithFlags(&ctx->copy_in, cudaStreamNonBlocking), 0);
+        CUDA_TRY(cudaStreamCreateWithFlags(&ctx->copy_out, cudaStreamNonBlocking), 0);
+        for (int b = 0; b < 2; b++) {
+            CUDA_TRY(cudaEventCreateWithFlags(&ctx->ev_in[b], cudaEventDisableTiming), 0);
+            CUDA_TRY(cudaEventCreateWithFlags(&ctx->ev_done[b], cudaEventDisableTiming), 0);
+            CUDA_TRY(cudaEventCreateWithFlags(&ctx->ev_out[b], cudaEventDisableTiming), 0);
+        }
+        CUDA_TRY(cudaEventCreateWithFlags(&ctx->ev_start, cudaEventDisableTiming), 0);
+    }
+    // the copy streams start after whatever is already queued on the context's stream
+    CUDA_TRY(cudaEventRecord(ctx->ev_start, ctx->stream), -1);
+    CUDA_TRY(cudaStreamWaitEvent(ctx->copy_in, ctx->ev_start, 0), -1);
+    CUDA_TRY(cudaStreamWaitEvent(ctx->copy_out, ctx->ev_start, 0), -1);
+    for (uint32_t c = 0; c < chunks; c++) {
+        const int b = (int)(c & 1u);
+        const uint32_t r0 = c * chunk, cnt = rows - r0 < chunk ? rows - r0 : chunk;
+        uint8_t* din = (uint8_t*)ctx->stage_in.ptr + (size_t)b * chunk * in_row;
+        uint8_t* dout = (uint8_t*)ctx->stage_out.ptr + (size_t)b * chunk * out_row;
+        // upload: the buffer is free once the kernels of chunk c-2 are done with it
+        if (c >= 2) CUDA_TRY(cudaStreamWaitEvent(ctx->copy_in, ctx->ev_done[b], 0), -1);
+        CUDA_TRY(cudaMemcpyAsync(din, (const uint8_t*)x_host + (size_t)r0 * in_row, (size_t)cnt * in_row,
+                                 cudaMemcpyHostToDevice, ctx->copy_in), -1);
+        CUDA_TRY(cudaEventRecord(ctx->ev_in[b], ctx->copy_in), -1);
+        // kernels: need the upload, and the output buffer once chunk c-2 has been downloaded
+        CUDA_TRY(cudaStreamWaitEvent(ctx->stream, ctx->ev_in[b], 0), -1);
+        if (c >= 2) CUDA_TRY(cudaStreamWaitEvent(ctx->stream, ctx->ev_out[b], 0), -1);
+        const int rc = requant
+            ? vxb_linear_i8(ctx, w, (const float*)din, cnt, out_scale, out_zero, (int8_t*)dout, w->d_out, VXB_ROUTE_AUTO)
+            : vxb_linear_f32(ctx, w, (const float*)din, cnt, (float*)dout, w->d_out, VXB_ROUTE_AUTO);
+        if (rc != 1) { cudaDeviceSynchronize(); return rc == 0 && c == 0 ? 0 : -1; }
+        CUDA_TRY(cudaEventRecord(ctx->ev_done[b], ctx->stream), -1);
+        // download
+        CUDA_TRY(cudaStreamWaitEvent(ctx->copy_out, ctx->ev_done[b], 0), -1);
+        CUDA_TRY(cudaMemcpyAsync((uint8_t*)y_host + (size_t)r0 * out_row, dout, (size_t)cnt * out_row,
+                                 cudaMemcpyDeviceToHost, ctx->copy_out), -1);
+        CUDA_TRY(cudaEventRecord(ctx->ev_out[b], ctx->copy_out), -1);
+    }
+    // the context's stream joins the last download(s), then the caller waits on it
+    for (int b = 0; b < 2; b++)
+        if (chunks > (uint32_t)b) CUDA_TRY(cudaStreamWaitEvent(ctx->stream, ctx->ev_out[b], 0), -1);
     return vxb_context_synchronize(ctx) == 1 ? 1 : -1;
 }
 
