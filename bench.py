@@ -7,11 +7,13 @@
 A step is one pass of the hot path (per-token quantize -> int8 GEMM -> fused epilogue) over
 one batch of synthetic input.  Default workload: the compute-bound GEMM of the benchmark
 configurations, M=8192 tokens, K=4096, N=14336, requantizing (int8) epilogue, with the
-output channels N sharded across the GPUs of one node and an NCCL all-gather of the int8
-output slabs when N > 1 GPU.  Rank 0 prints ONE JSON line.
+output channels N sharded across the GPUs of one node when N > 1 GPU and the int8 output
+replicated on every GPU by peer stores from the GEMM epilogue (the all-gather fused into the
+kernel; the NCCL all-gather of the slabs is timed beside it under "exchange").
+Rank 0 prints ONE JSON line.
 
   value      2*M*K*N / step time, inputs resident in HBM, CUDA events on the launching
-             stream, max over ranks (includes the all-gather when n_gpus > 1)
+             stream, max over ranks (includes the output exchange when n_gpus > 1)
   e2e        the same metric through the host-pointer entry vxb_linear_host: pinned host
              buffers, host->device and device->host copies inside the timed region
   roofline   the tcgen05 GEMM kernel alone, timed live by event pairs inside the timed loop
@@ -203,7 +205,7 @@ def workload_config(args, world):
             "rows": args.rows, "k": args.k, "n": args.n, "epilogue": "requant_int8",
             "activations": "fp32 N(0,1), 1% outlier channels x20, per-token int8",
             "weights": "int8 per-output-channel, N(0,0.02)-shaped codes",
-            "parallelism": f"n_shard{world}" + ("+allgather_int8" if world > 1 else ""),
+            "parallelism": f"n_shard{world}" + ("+fused_peer_store_allgather_int8" if world > 1 else ""),
             "l2": "inputs larger than L2 (x 134 MB + W 59 MB + out 117 MB per step at N=1)"}
 
 
@@ -280,6 +282,8 @@ def gpu_arm(args):
         raise RuntimeError("bench.py needs a CUDA device; there is no CPU fallback")
     torch.cuda.set_device(local)
     if world > 1:
+        # NCCL's own banner goes to stderr: stdout carries the one JSON line only
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     peaks = measured_peaks()
     from volvoxai_b200 import sharded
@@ -311,11 +315,18 @@ def gpu_arm(args):
         n, world, rank, lambda x, out: ctx.linear_i8(weight, x, out_scale, 0, out=out), torch.int8, "cuda")
     y_local = lin.forward_sharded(x_dev)
 
+    # N > 1: the all-gather is fused into the GEMM epilogue (peer stores over NVLink into every
+    # rank's replicated output buffer); the NCCL all-gather of the slabs is timed beside it
+    fused = sharded.FusedGatherLinear(ctx, weight, n, world, rank, rows=m) if world > 1 else None
+
     def step(gather=True):
         if world > 1 and gather:
-            lin.forward_gathered(x_dev)   # local slab + NCCL all-gather of the int8 slabs
+            fused.forward(x_dev, out_scale)
         else:
             lin.forward_sharded(x_dev)
+
+    def step_nccl():
+        lin.forward_gathered(x_dev)   # local slab + NCCL all-gather of the int8 slabs
 
     def barrier():
         if world > 1:
@@ -357,6 +368,21 @@ def gpu_arm(args):
 
     # kernel-only view (outputs left N-sharded): the same loop without the all-gather
     nogather_ms = timed(lambda: step(False), args.steps) / args.steps if world > 1 else ms_per_step
+    exchange = None
+    if world > 1:
+        for _ in range(3):
+            step_nccl()
+        nccl_ms = timed(step_nccl, args.steps) / args.steps
+        y_rep = fused.forward(x_dev, out_scale)
+        same_as_nccl = bool(torch.equal(y_rep, lin.forward(x_dev)))
+        # lower bound of any exchange that replicates the int8 output: the bytes each GPU must
+        # receive over NVLink at the measured peer-copy rate (770 GB/s per direction)
+        recv_bytes = m * (n - n_local)
+        exchange = {"fused_peer_store_ms": ms_per_step, "nccl_allgather_ms": nccl_ms,
+                    "sharded_no_exchange_ms": nogather_ms,
+                    "nvlink_recv_bytes_per_gpu": int(recv_bytes),
+                    "nvlink_floor_ms": recv_bytes / 770e9 * 1e3,
+                    "fused_matches_nccl_path": same_as_nccl}
 
     # roofline of the dominant kernel (the tcgen05 GEMM of this rank's shard)
     gemm_ms = prof["gemm_ms"] / max(1, prof["gemm_launches"])
@@ -385,6 +411,15 @@ def gpu_arm(args):
     roofline["traffic"] = 1.002 * (m + n_local) * kpad + 0.466 * m * n_local
     roofline["traffic_source"] = "ncu dram__bytes_read+write of the M4096 launch, scaled by (M+N)K and MN"
     roofline["algorithmic_bytes"] = (m + n_local) * kpad + m * n_local
+    if world > 1:
+        # fused GEMM + all-gather kernel: the target time is the slower of the MMAs at the measured
+        # tensor peak and the bytes this GPU must send over NVLink at the measured peer-copy rate
+        send_bytes = m * n_local * (world - 1)
+        t_mma, t_link = ops_local / (peak * 1e12) * 1e3, send_bytes / 770e9 * 1e3
+        roofline["fused"] = {"bound": "nvlink" if t_link > t_mma else "tensor", "mma_ms": t_mma,
+                             "nvlink_ms": t_link, "nvlink_send_bytes": int(send_bytes),
+                             "nvlink_gbs_peak": 770.0, "target_ms": max(t_mma, t_link),
+                             "kernel_ms": gemm_ms, "frac": max(t_mma, t_link) / gemm_ms}
 
     # end to end through the host-pointer entry: pinned host buffers, copies inside the region
     x_pin = torch.from_numpy(x_host_np).pin_memory()
@@ -418,6 +453,8 @@ def gpu_arm(args):
         "kernel_only": {"value": ops / (nogather_ms * 1e-3) / 1e12, "unit": "TOPS",
                         "ms_per_step": nogather_ms, "note": "outputs left N-sharded (no all-gather)"},
     }
+    if exchange is not None:
+        line["exchange"] = exchange
 
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         r = cpu_reference_run(min(m, args.cpu_rows), k, n, steps=1000, warmup=1, budget_s=args.cpu_seconds)

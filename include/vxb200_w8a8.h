@@ -145,6 +145,28 @@ VXB_API int vxb_linear_i8(VxbContext* ctx, const VxbWeight* w, const float* x, u
 VXB_API int vxb_linear_acc_i32(VxbContext* ctx, const VxbWeight* w, const float* x, uint32_t rows,
                        int32_t* acc, int8_t* q_out, float* scales_out, int route);
 
+/* ---- N-sharded multi-GPU form (no counterpart in the reference, which is single-GPU:
+ * docs/cuda.md:26,45-52) -------------------------------------------------------------
+ * Each GPU holds a contiguous range of the output channels (one VxbWeight per shard) and a
+ * full-width replicated output buffer [rows, ldy]. vxb_linear_i8_gather computes this GPU's
+ * channel slab and stores every finished tile both at y (this GPU's buffer, already offset to
+ * the shard's first channel) and at the same position of up to 7 peers' buffers, with plain
+ * stores over NVLink from the GEMM epilogue: the all-gather is fused into the kernel and
+ * overlaps the MMAs. peer_y[p] must be peer-mapped addresses (vxb_peer_open) offset like y.
+ * The call only orders this GPU's work; callers synchronise the GPUs (any barrier) before
+ * reading a buffer that peers write, and before the next call overwrites it.
+ *
+ * vxb_peer_alloc allocates such a buffer (cudaMalloc) and returns its 64-byte inter-process
+ * handle; the other ranks (one process per GPU) map it with vxb_peer_open and unmap it with
+ * vxb_peer_close before the owner calls vxb_peer_free. */
+VXB_API int vxb_peer_alloc(size_t bytes, void** ptr, unsigned char handle[64]);
+VXB_API int vxb_peer_open(const unsigned char handle[64], void** ptr);
+VXB_API int vxb_peer_close(void* ptr);
+VXB_API int vxb_peer_free(void* ptr);
+VXB_API int vxb_linear_i8_gather(VxbContext* ctx, const VxbWeight* w, const float* x, uint32_t rows,
+                         float out_scale, int32_t out_zero, int8_t* y, uint32_t ldy,
+                         void* const* peer_y, uint32_t n_peers);
+
 /* Prepared-activation form, the counterpart of the reference's prepared path
  * (x[4] prepared words / x[5] row scales, native/src/backends/cuda/host/
  * cuda_graph_llm_host.inc:15-107): the caller quantized the rows itself with

@@ -1,0 +1,121 @@
+"""The N-sharded linear with the all-gather fused into the GEMM epilogue (peer stores).
+
+One GPU is enough for the store loop itself (extra destinations on the same GPU are plain
+device addresses) and for the inter-process allocation path with world 1; the two-process
+case needs two GPUs and is skipped otherwise. Results are bit-exact against the CPU oracle."""
+import ctypes as C
+import os
+import socket
+
+import numpy as np
+import pytest
+
+from volvoxai_b200 import workloads as wl
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def torch():
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    return torch
+
+
+def _case(oracle, rows, k, n, seed):
+    case = wl.single_linear(rows=rows, k=k, n=n, seed=seed)
+    ref = oracle.w8a8_linear(case["x"], case["w"], case["ws"])
+    os_ = float(wl.static_out_scale(ref["out"]))
+    want = oracle.requant_rows(ref["acc"], ref["row_scales"], ref["valid"], case["ws"], None, os_, 0)
+    return case, os_, want
+
+
+@pytest.mark.parametrize("rows,k,n,ld", [(300, 256, 200, 208), (129, 384, 257, 259)])
+def test_extra_destinations_receive_every_tile(torch, oracle, rows, k, n, ld):
+    """Three destinations on one GPU: the local buffer and two more. Row pitch 208 takes the
+    vector stores, 259 the unaligned scalar tail; columns beyond n stay untouched."""
+    from volvoxai_b200 import _lib, w8a8
+    L = _lib.load()
+    ctx = w8a8.Context(0)
+    case, os_, want = _case(oracle, rows, k, n, seed=11)
+    weight = w8a8.Weight.from_i8(ctx, case["w"], case["ws"])
+    x = torch.from_numpy(case["x"]).cuda()
+    bufs = [torch.full((rows, ld), 77, dtype=torch.int8, device="cuda") for _ in range(3)]
+    peers = (C.c_void_p * 2)(bufs[1].data_ptr(), bufs[2].data_ptr())
+    rc = L.vxb_linear_i8_gather(ctx.handle, weight.handle, C.c_void_p(x.data_ptr()), rows, os_, 0,
+                                C.c_void_p(bufs[0].data_ptr()), ld, peers, 2)
+    assert rc == 1, _lib.last_error()
+    ctx.synchronize()
+    for b in bufs:
+        got = b.cpu().numpy()
+        assert np.array_equal(got[:, :n], want)
+        assert (got[:, n:] == 77).all()
+    # more than seven peers is declined before any launch
+    many = (C.c_void_p * 8)(*[bufs[1].data_ptr()] * 8)
+    assert L.vxb_linear_i8_gather(ctx.handle, weight.handle, C.c_void_p(x.data_ptr()), rows, os_, 0,
+                                  C.c_void_p(bufs[0].data_ptr()), ld, many, 8) == 0
+    weight.close()
+    ctx.close()
+
+
+def test_world_of_one_uses_the_shared_allocation(torch, oracle):
+    from volvoxai_b200 import sharded, w8a8
+    ctx = w8a8.Context(0)
+    ctx.use_torch_stream()
+    case, os_, want = _case(oracle, 200, 128, 384, seed=12)
+    weight = w8a8.Weight.from_i8(ctx, case["w"], case["ws"])
+    lin = sharded.FusedGatherLinear(ctx, weight, 384, 1, 0, rows=200)
+    x = torch.from_numpy(case["x"]).cuda()
+    for _ in range(3):                      # both buffers of the rotation
+        y = lin.forward(x, os_)
+        assert np.array_equal(y.cpu().numpy(), want)
+    lin.close()
+    weight.close()
+    ctx.close()
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, rows, k, n, ret):
+    import torch
+    import torch.distributed as dist
+    from oracle.bindings import Oracle
+    from volvoxai_b200 import sharded, w8a8
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        case, os_, want = _case(Oracle(), rows, k, n, seed=13)
+        lo, hi = sharded.shard_bounds(n, world, rank)
+        ctx = w8a8.Context(rank)
+        ctx.use_torch_stream()
+        weight = w8a8.Weight.from_i8(ctx, case["w"][lo:hi], case["ws"][lo:hi]) if hi > lo else None
+        lin = sharded.FusedGatherLinear(ctx, weight, n, world, rank, rows=rows)
+        x = torch.from_numpy(case["x"]).cuda()
+        ok = True
+        for _ in range(4):
+            y = lin.forward(x, os_)
+            ok = ok and np.array_equal(y.cpu().numpy(), want)
+            dist.barrier()
+        lin.close()
+        if weight is not None:
+            weight.close()
+        ctx.close()
+        ret[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,rows,k,n", [(2, 1000, 512, 1300), (2, 64, 128, 100)])
+def test_two_gpus_every_rank_holds_the_whole_output(torch, world, rows, k, n):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+    ret = mp.get_context("spawn").Manager().dict()
+    mp.spawn(_worker, args=(world, _free_port(), rows, k, n, ret), nprocs=world, join=True)
+    assert all(ret.get(r) for r in range(world)), dict(ret)

@@ -22,7 +22,8 @@ EXPORTS = [
     "vxb_weight_destroy", "vxb_weight_d_in", "vxb_weight_d_out", "vxb_weight_device_bytes",
     "vxb_quantize_rows", "vxb_linear_f32", "vxb_linear_i8", "vxb_linear_acc_i32",
     "vxb_qlinear_device", "vxb_weight_row_bytes", "vxb_linear_prepared", "vxb_linear_host", "vxb_context_profile", "vxb_context_profile_read",
-    "vxb_measure_i8_tensor_peak", "vxb_measure_mma_issue", "vxb_decode_linear_f32_noalloc", "vxb_qlinear_i8u8",
+    "vxb_measure_i8_tensor_peak", "vxb_measure_mma_issue", "vxb_peer_alloc", "vxb_peer_open",
+    "vxb_peer_close", "vxb_peer_free", "vxb_linear_i8_gather", "vxb_decode_linear_f32_noalloc", "vxb_qlinear_i8u8",
     "vxb_cuda_graph_llm_f32", "vxb_cuda_graph_packed_linear_decode_f32", "vxb_host_cache_clear",
 ]
 
@@ -87,6 +88,11 @@ def load() -> C.CDLL:
     L.vxb_context_profile.argtypes = [vp, C.c_int]
     L.vxb_context_profile_read.argtypes = [vp, C.POINTER(C.c_double), C.POINTER(C.c_uint64),
                                            C.POINTER(C.c_double), C.POINTER(C.c_uint64)]
+    L.vxb_peer_alloc.argtypes = [C.c_size_t, C.POINTER(vp), C.c_char_p]
+    L.vxb_peer_open.argtypes = [C.c_char_p, C.POINTER(vp)]
+    L.vxb_peer_close.argtypes = [vp]
+    L.vxb_peer_free.argtypes = [vp]
+    L.vxb_linear_i8_gather.argtypes = [vp, vp, vp, u32, f32, i32, vp, u32, C.POINTER(vp), u32]
     L.vxb_measure_mma_issue.argtypes = [vp, u32, u32, u32, u32, u32, C.POINTER(C.c_double)]
     L.vxb_measure_i8_tensor_peak.argtypes = [vp, u32, C.POINTER(C.c_double)]
     L.vxb_decode_linear_f32_noalloc.argtypes = [vp, vp, u32, vp, vp, vp, u32, u32, vp, u32, vp,

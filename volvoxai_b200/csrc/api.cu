@@ -494,6 +494,62 @@ int vxb_linear_acc_i32(VxbContext* ctx, const VxbWeight* w, const float* x, uint
     return run_gemm(ctx, w, (const int8_t*)ctx->q.ptr, rows, epi, route, "k1+");
 }
 
+int vxb_peer_alloc(size_t bytes, void** ptr, unsigned char handle[64]) {
+    if (!bytes || !ptr || !handle) return fail(0, "bad argument");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    void* p = nullptr;
+    CUDA_TRY(cudaMalloc(&p, bytes), 0);
+    cudaIpcMemHandle_t h;
+    cudaError_t e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) { cudaFree(p); return fail(0, "cudaIpcGetMemHandle: %s", cudaGetErrorString(e)); }
+    memcpy(handle, &h, 64);
+    *ptr = p;
+    return 1;
+}
+
+int vxb_peer_open(const unsigned char handle[64], void** ptr) {
+    if (!handle || !ptr) return fail(0, "bad argument");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, 64);
+    CUDA_TRY(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess), 0);
+    return 1;
+}
+
+int vxb_peer_close(void* ptr) {
+    if (!ptr) return 1;
+    CUDA_TRY(cudaIpcCloseMemHandle(ptr), -1);
+    return 1;
+}
+
+int vxb_peer_free(void* ptr) {
+    if (!ptr) return 1;
+    CUDA_TRY(cudaFree(ptr), -1);
+    return 1;
+}
+
+int vxb_linear_i8_gather(VxbContext* ctx, const VxbWeight* w, const float* x, uint32_t rows,
+                         float out_scale, int32_t out_zero, int8_t* y, uint32_t ldy,
+                         void* const* peer_y, uint32_t n_peers) {
+    int rc = check_common(ctx, w, x, y, ldy);
+    if (rc != 1) return rc;
+    if (n_peers > 7 || (n_peers && !peer_y)) return fail(0, "at most 7 peers");
+    for (uint32_t p = 0; p < n_peers; p++)
+        if (!peer_y[p]) return fail(0, "null peer pointer");
+    if (!valid_scale(out_scale)) return fail(0, "output scale is not positive and finite");
+    if (out_zero < -128 || out_zero > 127) return fail(0, "output zero point %d outside int8", out_zero);
+    if (!rows) return 1;
+    if (ensure_device(ctx) != 1) return -1;
+    if ((rc = quantize_into_scratch(ctx, w, x, rows)) != 1) return rc;
+    EpilogueParams epi{};
+    epi.mode = kEpiI8; epi.row_scales = (const float*)ctx->row_scales.ptr; epi.ws = w->ws;
+    epi.bias_i32 = w->bias_i32; set_requant_divisor(epi, w, out_scale); epi.out_zero = out_zero;
+    epi.out_lo = -128; epi.out_hi = 127; epi.out = y; epi.ld = ldy;
+    epi.n_peers = n_peers;
+    for (uint32_t p = 0; p < n_peers; p++) epi.peer_out[p] = peer_y[p];
+    // the peer stores live in the large-M kernel's epilogue
+    return run_gemm(ctx, w, (const int8_t*)ctx->q.ptr, rows, epi, VXB_ROUTE_TCGEN05, "k1+");
+}
+
 uint32_t vxb_weight_row_bytes(const VxbWeight* w) { return w ? w->kpad : 0; }
 
 int vxb_linear_prepared(VxbContext* ctx, const VxbWeight* w, const int8_t* q, const float* row_scales,

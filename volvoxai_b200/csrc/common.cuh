@@ -30,6 +30,10 @@ struct EpilogueParams {
     int32_t out_lo, out_hi;   // E2 saturation range (I8: -128..127, U8: 0..255)
     void* out;                // int32 / float / int8 [rows, ld]
     uint32_t ld;              // output row stride in elements
+    // fused all-gather (large-M kernel only): the same [rows, ld] window in up to 7 peer GPUs'
+    // buffers (peer-mapped addresses); every output tile is also stored there
+    uint32_t n_peers;
+    void* peer_out[7];
 };
 
 // ---- programmatic dependent launch ------------------------------------------------------

@@ -84,6 +84,10 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ GemmTcgen05Args args) {
     const uint32_t total_tiles = tiles_m * tiles_n;
     const uint32_t num_kb = args.kpad / kBK;
     volatile int* abort_flag = sm.abort_flag();
+    // with peer destinations the last pipeline stage becomes the epilogue warps' staging area
+    // for coalesced stores (the exchange, not the MMA pipeline, bounds that launch)
+    const bool gather = args.epi.n_peers != 0;
+    const uint32_t nstages = gather ? kStages - 1 : kStages;
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < kStages; s++) { mbar_init(sm.full(s), 1); mbar_init(sm.empty(s), 1); }
@@ -115,7 +119,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ GemmTcgen05Args args) {
                     tma_load_2d(sm.a(stage), &args.tmap_a, sm.full(stage), (int32_t)(kb * kBK), m0);
                     armed |= 1u << stage;
                     armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
-                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                    if (++stage == nstages) { stage = 0; phase ^= 1u; }
                 }
             }
             if (!ok) {
@@ -139,7 +143,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ GemmTcgen05Args args) {
                 for (uint32_t kb = 0; kb < num_kb; kb++) {
                     if (!mbar_wait(sm.empty(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
                     tma_load_2d(sm.b(stage), &args.tmap_b, sm.full(stage), (int32_t)(kb * kBK), n0);
-                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                    if (++stage == nstages) { stage = 0; phase ^= 1u; }
                 }
             }
         }
@@ -163,7 +167,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ GemmTcgen05Args args) {
                                 make_smem_desc(b_addr + k * kUmmaK), idesc, (kb | k) != 0u);
                     }
                     umma_commit(sm.empty(stage));
-                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                    if (++stage == nstages) { stage = 0; phase ^= 1u; }
                 }
                 if (!ok) break;
                 umma_commit(sm.tmem_full(acc));
@@ -184,6 +188,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ GemmTcgen05Args args) {
         // never wait on one another
         float* s_ws = sm.ws() + (warp - 2u) * kEpiCols;
         float* s_bias = sm.bias() + (warp - 2u) * kEpiCols;
+        uint8_t* stage_tile = sm.base + kOffStages + (kStages - 1) * kStageBytes + (warp - 2u) * (32u * kEpiCols);
         const float zero_f = __int2float_rn(ep.out_zero);
         const float lo_f = __int2float_rn(ep.out_lo), hi_f = __int2float_rn(ep.out_hi);
         uint32_t acc = 0, acc_phase = 0;
@@ -246,7 +251,15 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ GemmTcgen05Args args) {
                             packed[j] = __byte_perm(__byte_perm(q0, q1, 0x0040), __byte_perm(q2, q3, 0x0040), 0x5410);
                         }
                     }
-                    if (full && (((uintptr_t)dst) & 15u) == 0) {
+                    if (gather) {
+                        // row `lane` of this warp's [32 rows x 128 B] staging tile; 16-byte pieces
+                        // XOR-swizzled by row so that both the row-wise writes here and the
+                        // piece-wise reads of the flush are free of bank conflicts
+                        uint8_t* st = stage_tile + lane * kEpiCols;
+                        const uint32_t p0 = c >> 4;
+                        *reinterpret_cast<uint4*>(st + (((p0) ^ (lane & 7u)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                        *reinterpret_cast<uint4*>(st + (((p0 + 1u) ^ (lane & 7u)) << 4)) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                    } else if (full && (((uintptr_t)dst) & 15u) == 0) {
                         reinterpret_cast<uint4*>(dst)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
                         reinterpret_cast<uint4*>(dst)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
                     } else {
@@ -285,6 +298,35 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ GemmTcgen05Args args) {
             mbar_arrive(sm.tmem_empty(acc));
             acc ^= 1u;
             if (acc == 0) acc_phase ^= 1u;
+            if (gather) {
+                // flush the staged int8 tile: 8 lanes cover the 128 bytes of one row, 4 rows per
+                // pass, the same 16 bytes going to this GPU's buffer (destination 0) and to the
+                // same rows and columns of every peer's buffer - plain stores over NVLink, so the
+                // all-gather of the output is part of the epilogue and overlaps the next tile's MMAs
+                __syncwarp();
+                const uint32_t piece = lane & 7u;
+#pragma unroll 1
+                for (uint32_t i = 0; i < 8; i++) {
+                    const uint32_t rl = 4u * i + (lane >> 3);
+                    const uint4 v = *reinterpret_cast<const uint4*>(stage_tile + rl * kEpiCols + ((piece ^ (rl & 7u)) << 4));
+                    const uint32_t grow = m0 + quarter * 32 + rl, gcol = n0 + piece * 16;
+                    if (grow >= args.rows || gcol >= args.n) continue;
+                    const bool whole = gcol + 16 <= args.n;
+                    const size_t off = (size_t)grow * ep.ld + gcol;
+                    for (uint32_t d = 0; d <= ep.n_peers; d++) {
+                        int8_t* dst = (int8_t*)(d ? ep.peer_out[d - 1] : ep.out) + off;
+                        if (whole && (((uintptr_t)dst) & 15u) == 0) {
+                            *reinterpret_cast<uint4*>(dst) = v;
+                        } else {
+                            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                            for (int b = 0; b < 16; b++)
+                                if (gcol + b < args.n) dst[b] = (int8_t)((w[b >> 2] >> (8 * (b & 3))) & 0xffu);
+                        }
+                    }
+                }
+                __syncwarp();
+            }
         }
     }
 

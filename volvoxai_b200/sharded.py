@@ -100,3 +100,104 @@ class NShardedLinear:
     def forward(self, x) -> torch.Tensor:
         """Replicated [M, n] output in channel order."""
         return interleave(self.forward_gathered(x), self.n)
+
+
+class _RawCuda:
+    """A raw device allocation exposed through __cuda_array_interface__ (uint8, 1-D)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {
+            "shape": (nbytes,), "typestr": "|i1", "data": (ptr, False), "version": 3, "strides": None}
+
+
+class FusedGatherLinear:
+    """The N-sharded linear with the all-gather fused into the GEMM epilogue.
+
+    Every rank owns a replicated int8 output buffer [M, n] allocated through vxb_peer_alloc
+    and maps the other ranks' buffers (CUDA IPC, one process per GPU).  One call of
+    vxb_linear_i8_gather quantizes the replicated activations, runs the tcgen05 GEMM of the
+    rank's channel range and stores every finished tile at the same [row, lo + col] position
+    of all `world` buffers, with plain stores over NVLink while the MMAs of later tiles run.
+    No NCCL collective moves data; a one-element all-reduce after the kernel is the only
+    cross-GPU synchronisation (stream-ordered: when it has completed on a rank, every rank's
+    kernel, and with it every store into this rank's buffer, has completed).
+
+    Two buffers alternate between steps, so that a rank that is still reading step k's
+    output is never overwritten by a faster peer's step k+1: a peer reaches step k+2, which
+    reuses the buffer, only after the barrier of step k+1, which this rank enters after its
+    own reads of step k (same stream) have been queued ahead of it.
+    """
+
+    DEPTH = 2
+
+    def __init__(self, ctx, weight, n: int, world: int, rank: int, rows: int, group=None):
+        """`weight` holds channels shard_bounds(n, world, rank) (None for an empty shard)."""
+        from . import _lib
+        self._L = _lib.load()
+        self.ctx, self.weight, self.n, self.world, self.rank, self.group = ctx, weight, n, world, rank, group
+        self.rows = rows
+        self.lo, self.hi = shard_bounds(n, world, rank)
+        if (weight.d_out if weight is not None else 0) != self.hi - self.lo:
+            raise ValueError(f"the weight does not hold the shard's {self.hi - self.lo} channels")
+        self.ld = (n + 15) // 16 * 16            # 16-byte row pitch: vector stores on every rank
+        nbytes = rows * self.ld
+        self._own, self._peers, self.buffers = [], [], []
+        self._flag = torch.zeros(1, dtype=torch.int32, device=f"cuda:{ctx.device}")
+        self._step = 0
+        import ctypes as C
+        for _ in range(self.DEPTH):
+            ptr, handle = C.c_void_p(), C.create_string_buffer(64)
+            if self._L.vxb_peer_alloc(nbytes, C.byref(ptr), handle) != 1:
+                raise RuntimeError(_lib.last_error())
+            self._own.append(ptr.value)
+            handles = [None] * world
+            if world > 1:
+                dist.all_gather_object(handles, handle.raw, group=group)
+            mapped = []
+            for r in range(world):
+                if r == rank:
+                    continue
+                p = C.c_void_p()
+                if self._L.vxb_peer_open(handles[r], C.byref(p)) != 1:
+                    raise RuntimeError(_lib.last_error())
+                mapped.append(p.value)
+            self._peers.append(mapped)
+            t = torch.as_tensor(_RawCuda(ptr.value, nbytes), device=f"cuda:{ctx.device}")
+            self.buffers.append(t.view(rows, self.ld))
+
+    def forward(self, x, out_scale: float, out_zero: int = 0, sync: bool = True) -> torch.Tensor:
+        """Returns this rank's replicated [rows, n] int8 output (a view of the step's buffer).
+        With sync=False the caller must order the GPUs itself before reading it."""
+        import ctypes as C
+        if x.shape[0] != self.rows:
+            raise ValueError("row count differs from the mapped buffers")
+        b = self._step % self.DEPTH
+        self._step += 1
+        if self.hi > self.lo:
+            off = self.lo
+            peers = (C.c_void_p * max(1, len(self._peers[b])))(*[p + off for p in self._peers[b]])
+            rc = self._L.vxb_linear_i8_gather(
+                self.ctx.handle, self.weight.handle, C.c_void_p(x.data_ptr()), self.rows,
+                float(out_scale), int(out_zero), C.c_void_p(self._own[b] + off), self.ld,
+                peers, len(self._peers[b]))
+            if rc != 1:
+                from . import _lib
+                raise RuntimeError(f"vxb_linear_i8_gather returned {rc}: {_lib.last_error()}")
+        if sync and self.world > 1:
+            dist.all_reduce(self._flag, group=self.group)
+        return self.buffers[b][:, : self.n]
+
+    def close(self) -> None:
+        """Collective: every rank unmaps its peers' buffers before any owner frees one."""
+        import ctypes as C
+        torch.cuda.synchronize()
+        for mapped in self._peers:
+            for p in mapped:
+                self._L.vxb_peer_close(C.c_void_p(p))
+        self._peers = []
+        self.buffers = []
+        if self.world > 1:
+            dist.barrier(group=self.group)
+        for p in self._own:
+            self._L.vxb_peer_free(C.c_void_p(p))
+        self._own = []
