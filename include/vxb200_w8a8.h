@@ -206,6 +206,14 @@ VXB_API int vxb_linear_host(VxbContext* ctx, const VxbWeight* w, const float* x_
  * vxb_context_profile(ctx, 1) clears and starts, (ctx, 0) clears and stops;
  * _read waits for the stream and returns summed milliseconds and launch counts. */
 VXB_API int vxb_context_profile(VxbContext* ctx, int enable);
+/* Diagnostic: while device_stamps is not NULL, every launch of the decode kernel (route
+ * DECODE) writes 8 %globaltimer values (ns) per CTA into device_stamps[cta*8 + slot]:
+ * 0 entry, 1 prologue done, 2 first weight tile landed, 3 last MMA issued, 4 accumulator
+ * ready, 5 last output stored, 6 preceding kernel finished (programmatic dependency), 7 exit.
+ * The buffer must hold 8 * ceil(d_out / channels-per-CTA) <= 8 * d_out values. The pointer is
+ * read at launch (a captured launch keeps the pointer it was captured with). Counterpart of
+ * the instrumented replay plan of the reference (docs/cuda.md:537-556). */
+VXB_API int vxb_context_trace(VxbContext* ctx, unsigned long long* device_stamps);
 VXB_API int vxb_context_profile_read(VxbContext* ctx, double* quantize_ms, uint64_t* quantize_launches,
                              double* gemm_ms, uint64_t* gemm_launches);
 

@@ -21,7 +21,7 @@ EXPORTS = [
     "vxb_context_synchronize", "vxb_weight_create_i8", "vxb_weight_create_w8_words",
     "vxb_weight_destroy", "vxb_weight_d_in", "vxb_weight_d_out", "vxb_weight_device_bytes",
     "vxb_quantize_rows", "vxb_linear_f32", "vxb_linear_i8", "vxb_linear_acc_i32",
-    "vxb_qlinear_device", "vxb_weight_row_bytes", "vxb_linear_prepared", "vxb_linear_host", "vxb_context_profile", "vxb_context_profile_read",
+    "vxb_qlinear_device", "vxb_weight_row_bytes", "vxb_linear_prepared", "vxb_linear_host", "vxb_context_profile", "vxb_context_profile_read", "vxb_context_trace",
     "vxb_measure_i8_tensor_peak", "vxb_measure_mma_issue", "vxb_peer_alloc", "vxb_peer_open",
     "vxb_peer_close", "vxb_peer_free", "vxb_linear_i8_gather", "vxb_decode_linear_f32_noalloc", "vxb_qlinear_i8u8",
     "vxb_cuda_graph_llm_f32", "vxb_cuda_graph_packed_linear_decode_f32", "vxb_host_cache_clear",
@@ -85,6 +85,7 @@ def load() -> C.CDLL:
     L.vxb_weight_row_bytes.restype = u32
     L.vxb_linear_prepared.argtypes = [vp, vp, vp, vp, u32, C.c_int, f32, i32, vp, u32, C.c_int]
     L.vxb_linear_host.argtypes = [vp, vp, vp, u32, C.c_int, f32, i32, vp]
+    L.vxb_context_trace.argtypes = [vp, vp]
     L.vxb_context_profile.argtypes = [vp, C.c_int]
     L.vxb_context_profile_read.argtypes = [vp, C.POINTER(C.c_double), C.POINTER(C.c_uint64),
                                            C.POINTER(C.c_double), C.POINTER(C.c_uint64)]

@@ -85,6 +85,7 @@ struct VxbContext {
     Buffer q, row_scales, bias_eff, stage_in, stage_out;
     Buffer splitk_ws, splitk_counters;   // zero between calls (the decode kernel cleans up)
     int* status = nullptr;        // device word raised by bounded waits
+    unsigned long long* trace = nullptr;   // caller's device buffer for decode-kernel time stamps, or null
     int* status_host = nullptr;   // pinned mirror
     bool tcgen05_ready = false;
     // optional per-kernel timing (event pairs on the launching stream)
@@ -222,7 +223,7 @@ int run_gemm(VxbContext* ctx, const VxbWeight* w, const int8_t* q, uint32_t rows
         a.rows = rows; a.n = w->d_out; a.kpad = w->kpad;
         a.tile_rows = w->tile_rows; a.tiles_per_cta = w->tiles_per_cta; a.stages = 0;
         a.w_stage_bytes = round_up(w->tile_rows * kKAlign, 1024u);
-        a.epi = epi; a.status = ctx->status;
+        a.epi = epi; a.status = ctx->status; a.trace = ctx->trace;
         CUDA_TRY(launch_decode_rows(a, ctx->stream), -1);
     } else if (plan.route == VXB_ROUTE_DECODE_STREAMK) {
         if (rows > 128) return fail(0, "decode route needs rows <= 128 (got %u)", rows);
@@ -605,6 +606,12 @@ int vxb_qlinear_device(VxbContext* ctx, const VxbWeight* w, const void* input, u
     epi.out_zero = output_zero_point; epi.out_lo = out_u8 ? 0 : -128; epi.out_hi = out_u8 ? 255 : 127;
     epi.out = output; epi.ld = ldy;
     return run_gemm(ctx, w, (const int8_t*)ctx->q.ptr, rows, epi, route, "static+");
+}
+
+int vxb_context_trace(VxbContext* ctx, unsigned long long* device_stamps) {
+    if (!ctx) return fail(0, "null context");
+    ctx->trace = device_stamps;
+    return 1;
 }
 
 int vxb_context_profile(VxbContext* ctx, int enable) {

@@ -181,11 +181,14 @@ struct DecodeRowsArgs {
     CUtensorMap tmap_x;
     uint32_t rows, n, kpad;
     uint32_t tile_rows, tiles_per_cta;
-    uint32_t stages, umma_n, tmem_cols, acc_cols, issuers;   // filled in by the launcher
+    uint32_t stages, umma_n, tmem_cols, acc_cols, issuers, producers;   // filled in by the launcher
     uint32_t w_stage_bytes;   // round_up(tile_rows * 128, 1024)
     EpilogueParams epi;
     int* status;
+    unsigned long long* trace;   // optional [grid][kTraceSlots] of %globaltimer stamps, or null
 };
+constexpr uint32_t kTraceSlots = 8;   // 0 entry, 1 prologue done, 2 first weights landed, 3 last MMA issued,
+                                      // 4 accumulator ready, 5 last store, 6 predecessor finished, 7 exit
 uint32_t decode_rows_token_slots(uint32_t rows);  // 8 / 16 / 32 / 64 / 128
 void decode_rows_plan(uint32_t n, int sm_count, uint32_t* tile_rows, uint32_t* tiles_per_cta);
 cudaError_t launch_decode_rows(const DecodeRowsArgs& args, cudaStream_t stream);

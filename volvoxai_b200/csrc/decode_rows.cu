@@ -37,22 +37,48 @@ namespace {
 using namespace tc;
 
 constexpr uint32_t kRK = 128;              // K bytes per stage
-constexpr uint32_t kIssuerWarps = 4;        // warps 1..4 may issue MMAs
-constexpr uint32_t kXWarp = 1 + kIssuerWarps + 4;             // first activation-producer warp
-constexpr uint32_t kThreads = 32 * (kXWarp + kIssuerWarps);   // weight producer, issuers, 4 epilogue warps, activation producers
-constexpr uint32_t kEpiBase = 32 * (1 + kIssuerWarps);
+constexpr uint32_t kProducerWarps = 4;      // warps that may issue TMA copies
 constexpr uint32_t kMaxStages = 32;
 constexpr uint32_t kMaxTile = 256;         // channels per tile (UMMA N limit)
-constexpr uint32_t kRingBudgetDeep = 150 * 1024;  // one CTA per SM; the ring takes most of its shared memory
+// Two CTAs fit an SM (shared memory, registers and TMEM columns are all held to half of it), so
+// that the CTAs of the NEXT launch in the stream become resident while this launch still runs:
+// their prologue and the first ring-full of their weights overlap this launch's tail, and the
+// weight stream from HBM does not stop between back-to-back decode kernels.
+//
+// That only pays while a CTA's whole weight share is not much larger than the ring it can hold
+// in half an SM: then most of it is already in shared memory when the preceding kernel ends.
+// CTAs with more to stream run alone on their SM (kPair = false) with a ring twice as deep -
+// the stream rate follows the bytes in flight - and with up to eight MMA issuers.
+constexpr uint32_t kPairSmemBytes = (233472 - 2 * 1024) / 2;   // 228 KB per SM, 1 KB reserved per CTA
+constexpr uint32_t kSoloSmemBytes = 200 * 1024;
+constexpr uint32_t kPairShareBytes = 160 * 1024;               // largest weight share per CTA run in pairs
+
+template <bool PAIR> struct ModeCfg {
+    static constexpr uint32_t kIssuerWarps = PAIR ? 4 : 8;     // warps 0.. may issue MMAs
+    static constexpr uint32_t kXWarp = kIssuerWarps + 4;       // first producer warp (4 epilogue warps before it)
+    static constexpr uint32_t kThreads = 32 * (kXWarp + kProducerWarps);
+    static constexpr uint32_t kEpiBase = 32 * kIssuerWarps;
+    static constexpr uint32_t kSmemBytes = PAIR ? kPairSmemBytes : kSoloSmemBytes;
+    static constexpr uint32_t kTmemCols = PAIR ? 256 : 512;
+    static constexpr uint32_t kCtasPerSm = PAIR ? 2 : 1;
+};
 constexpr uint32_t kXposePitch = 33;       // ints per row of the epilogue transpose buffer
 
 template <uint32_t MT> struct RowsCfg {
     static constexpr uint32_t kXBytes = MT * kRK < 1024 ? 1024 : MT * kRK;  // activation stage
     static constexpr uint32_t kUmmaM = MT <= 64 ? 64 : 128;                  // rows the MMA spans
+    static constexpr bool kParkAll = MT <= 32;   // few token rows: the epilogue parks the whole tile at once
+    // parking area of the epilogue: the whole [rows, umma_n] tile (pitch umma_n + 4 ints) for few
+    // token rows, else two [MT][33] buffers for 32-channel chunks
+    // whole 32-channel chunks per row, + 4 ints (pitch = 4 mod 32: 16-byte row stores hit distinct banks)
+    static __host__ __device__ uint32_t park_pitch(uint32_t umma_n) { return round_up(umma_n, 32u) + 4u; }
+    static __host__ __device__ uint32_t xpose_bytes(uint32_t rows, uint32_t umma_n) {
+        return kParkAll ? round_up(rows, 8u) * park_pitch(umma_n) * 4u : 2u * MT * kXposePitch * 4u;
+    }
 };
 
 struct RowsLayout {       // dynamic shared memory, offsets from a 1024-byte aligned base
-    uint32_t stages, w_bytes, x_bytes, umma_m, umma_n;
+    uint32_t stages, w_bytes, x_bytes, umma_m, umma_n, xpose_bytes;
     __host__ __device__ uint32_t w_off(uint32_t s) const { return s * w_bytes; }
     __host__ __device__ uint32_t w_end() const {
         // the MMA reads umma_n x 128 bytes from a weight stage
@@ -67,21 +93,31 @@ struct RowsLayout {       // dynamic shared memory, offsets from a 1024-byte ali
         return ring > reach ? ring : reach;
     }
     __host__ __device__ uint32_t consts_off() const { return x_end(); }   // float ws[256], bias[256]
-    __host__ __device__ uint32_t xpose_off() const { return consts_off() + 2 * kMaxTile * 4; }  // int32 [128][33]
-    __host__ __device__ uint32_t bars_off() const { return xpose_off() + 128 * kXposePitch * 4; }
+    __host__ __device__ uint32_t xpose_off() const { return consts_off() + 2 * kMaxTile * 4; }  // the epilogue's parking area
+    __host__ __device__ uint32_t bars_off() const { return xpose_off() + xpose_bytes; }
     __host__ __device__ uint32_t misc_off() const { return bars_off() + (2 * kMaxStages + 4) * 8; }
     __host__ __device__ uint32_t total() const { return misc_off() + 32 + 128 * 4 + 1024; }
 };
 
+__device__ __forceinline__ void stamp(unsigned long long* trace, uint32_t slot) {
+    if (trace) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        trace[(size_t)blockIdx.x * kTraceSlots + slot] = t;
+    }
+}
+
 __device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
-template <uint32_t MT>
-__global__ void __launch_bounds__(kThreads, 1)
+template <uint32_t MT, bool PAIR>
+__global__ void __launch_bounds__(ModeCfg<PAIR>::kThreads, ModeCfg<PAIR>::kCtasPerSm)
 decode_rows_kernel(const __grid_constant__ DecodeRowsArgs args) {
     using Cfg = RowsCfg<MT>;
+    constexpr uint32_t kIssuerWarps = ModeCfg<PAIR>::kIssuerWarps, kXWarp = ModeCfg<PAIR>::kXWarp;
+    constexpr uint32_t kEpiBase = ModeCfg<PAIR>::kEpiBase;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    const RowsLayout lay{args.stages, args.w_stage_bytes, Cfg::kXBytes, Cfg::kUmmaM, args.umma_n};
+    const RowsLayout lay{args.stages, args.w_stage_bytes, Cfg::kXBytes, Cfg::kUmmaM, args.umma_n, Cfg::xpose_bytes(args.rows, args.umma_n)};
     const uint32_t stages = args.stages;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     auto w_addr = [&](uint32_t s) { return smem_u32(base + lay.w_off(s)); };
@@ -97,6 +133,9 @@ decode_rows_kernel(const __grid_constant__ DecodeRowsArgs args) {
     float* s_ws = reinterpret_cast<float*>(base + lay.consts_off());
     float* s_bias = s_ws + kMaxTile;
     int32_t* s_xpose = reinterpret_cast<int32_t*>(base + lay.xpose_off());
+
+    // let the next launch in the stream become resident as early as possible (see kPairSmemBytes)
+    if (threadIdx.x == 0) { pdl_release(); stamp(args.trace, 0); }
 
     const uint32_t num_kb = args.kpad / kRK;
     const uint32_t tiles = args.tiles_per_cta;
@@ -114,96 +153,84 @@ decode_rows_kernel(const __grid_constant__ DecodeRowsArgs args) {
         prefetch_tmap(&args.tmap_w);
         prefetch_tmap(&args.tmap_x);
     }
-    if (warp == 1) { tmem_alloc(smem_u32(tmem_ptr), args.tmem_cols); tmem_relinquish(); }
+    if (warp == 0) { tmem_alloc(smem_u32(tmem_ptr), args.tmem_cols); tmem_relinquish(); }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_ptr;
-    if (threadIdx.x == 0) pdl_release();
+    if (threadIdx.x == 0) stamp(args.trace, 1);
 
-    if (warp == 0) {
-        // ---------------- weight producer ----------------
-        // One thread, and every clock of it counts: with few channels per CTA a K block is only
-        // a few KB, so the loop below is kept to address increments (no divisions, no layout
-        // arithmetic). Weights depend on nothing that runs before this kernel, so this thread
-        // never waits for the preceding kernel; the activation tiles come from their own thread.
-        if (lane == 0 && args.issuers == 1) {   // with several issuers, each loads its own weight tiles
-            const uint32_t total = tiles * num_kb;
-            const uint32_t w0 = w_addr(0), f0 = full(0), e0 = empty(0), wstep = lay.w_bytes;
-            uint32_t w_sm = w0, fb = f0, eb = e0, stage = 0, phase = 0, kb = 0, armed = 0;
-            int32_t kcoord = 0, channel = (int32_t)first_channel;
+    if (warp >= kXWarp) {
+        // ---------------- producers ----------------
+        // Starting a TMA copy costs the issuing thread some 200 ns whatever the box size, so one
+        // thread cannot feed small K blocks fast enough: producer p of P loads the weight and the
+        // activation tiles of the blocks p, p+P, ... (block = tile * num_kb + kb) into its own
+        // stages p, p+P, ... (the ring depth is a multiple of P), re-arming a stage as soon as the
+        // MMAs that read it have completed. Only increments in the loop, no divisions.
+        // Weights depend on nothing that runs before this kernel: the first ring-full of them is
+        // requested before the wait for the preceding kernel, the activations after it.
+        const uint32_t p = warp - kXWarp, P = args.producers;
+        if (lane == 0 && p < P) {
+            const uint32_t total = tiles * num_kb, own = stages / P;
+            const uint32_t w0 = w_addr(p), x0 = x_addr(p), f0 = full(p), e0 = empty(p);
+            const uint32_t wstep = lay.w_bytes * P, xstep = lay.x_bytes * P;
+            // block cursor (K coordinate and channel of the next block of this producer)
+            uint32_t kb = p; int32_t channel = (int32_t)first_channel;
+            while (kb >= num_kb) { kb -= num_kb; channel += (int32_t)args.tile_rows; }
+            uint32_t i = p, pre = 0;
+            {   // first ring-full of weights
+                uint32_t w_sm = w0, fb = f0, kb2 = kb; int32_t ch2 = channel;
+                for (uint32_t b = p; pre < own && b < total; b += P, pre++) {
+                    mbar_expect_tx(fb, stage_tx);
+                    tma_load_2d(w_sm, &args.tmap_w, fb, (int32_t)(kb2 * kRK), ch2);
+                    kb2 += P; while (kb2 >= num_kb) { kb2 -= num_kb; ch2 += (int32_t)args.tile_rows; }
+                    w_sm += wstep; fb += 8 * P;
+                }
+            }
+            pdl_wait();   // the activations are the preceding kernel's output
+            if (p == 0) stamp(args.trace, 6);
+            uint32_t w_sm = w0, x_sm = x0, fb = f0, eb = e0, stage = 0, phase = 0;
             bool ok = true;
-            for (uint32_t i = 0; i < total; i++) {
-                if (i >= stages && !mbar_wait(eb, phase ^ 1u, abort_flag)) { ok = false; break; }
-                mbar_expect_tx(fb, stage_tx);
-                tma_load_2d(w_sm, &args.tmap_w, fb, kcoord, channel);
-                armed |= 1u << stage;
-                kcoord += (int32_t)kRK;
-                if (++kb == num_kb) { kb = 0; kcoord = 0; channel += (int32_t)args.tile_rows; }
-                w_sm += wstep; fb += 8; eb += 8;
-                if (++stage == stages) { stage = 0; phase ^= 1u; w_sm = w0; fb = f0; eb = e0; }
+            for (uint32_t u = 0; i < total; i += P, u++) {
+                if (u >= pre) {
+                    if (!mbar_wait(eb, phase ^ 1u, abort_flag)) { ok = false; break; }
+                    mbar_expect_tx(fb, stage_tx);
+                    tma_load_2d(w_sm, &args.tmap_w, fb, (int32_t)(kb * kRK), channel);
+                }
+                tma_load_2d(x_sm, &args.tmap_x, fb, (int32_t)(kb * kRK), 0);
+                kb += P; while (kb >= num_kb) { kb -= num_kb; channel += (int32_t)args.tile_rows; }
+                w_sm += wstep; x_sm += xstep; fb += 8 * P; eb += 8 * P;
+                if (++stage == own) { stage = 0; phase ^= 1u; w_sm = w0; x_sm = x0; fb = f0; eb = e0; }
             }
             if (!ok) {
-                // drain: give this CTA's own copies in flight a bounded time to land
-                for (uint32_t s = 0; s < stages; s++) {
-                    if (!(armed & (1u << s))) continue;
+                // drain: give this thread's own copies in flight a bounded time to land
+                for (uint32_t st = p; st < stages; st += P) {
                     for (uint32_t n = 0; n < 2000; n++) {
-                        if (mbar_try_wait(full(s), 0u) || mbar_try_wait(full(s), 1u)) break;
+                        if (mbar_try_wait(full(st), 0u) || mbar_try_wait(full(st), 1u)) break;
                         __nanosleep(500);
                     }
                 }
             }
         }
-    } else if (warp >= kXWarp) {
-        // ---------------- activation producers ----------------
-        // Starting a TMA copy costs the issuing thread some 200 ns whatever the box size, so one
-        // thread cannot feed small K blocks fast enough: producer p of P (= the issuer count)
-        // loads the activation tiles of the K blocks p, p+P, ... into its own stages p, p+P, ...
-        const uint32_t p = warp - kXWarp, P = args.issuers;
-        if (lane == 0 && p < P) {
-            const uint32_t total = tiles * num_kb, own = stages / P;
-            const uint32_t x0 = x_addr(p), f0 = full(p), e0 = empty(p), xstep = lay.x_bytes * P;
-            uint32_t x_sm = x0, fb = f0, eb = e0, stage = 0, phase = 0, kb = p % num_kb, uses = 0;
-            pdl_wait();   // the activations are the preceding kernel's output
-            for (uint32_t i = p; i < total; i += P, uses++) {
-                if (uses >= own && !mbar_wait(eb, phase ^ 1u, abort_flag)) break;
-                tma_load_2d(x_sm, &args.tmap_x, fb, (int32_t)(kb * kRK), 0);
-                kb += P; while (kb >= num_kb) kb -= num_kb;
-                x_sm += xstep; fb += 8 * P; eb += 8 * P;
-                if (++stage == own) { stage = 0; phase ^= 1u; x_sm = x0; fb = f0; eb = e0; }
-            }
-        }
-    } else if (warp <= kIssuerWarps && args.issuers > 1) {
+    } else if (warp < kIssuerWarps && args.issuers > 1) {
         // ---------------- MMA issuers, several: issuer ii takes K blocks ii, ii+I, ... into its own
         // accumulator (one thread can start an MMA only every ~70 clocks, far slower than the tensor
         // pipe finishes a narrow one; the epilogue adds the accumulators up, integers: exact) ------
-        const uint32_t ii = warp - 1u;
+        const uint32_t ii = warp;
         if (lane == 0 && ii < args.issuers) {
             const uint32_t idesc = make_idesc(Cfg::kUmmaM, args.umma_n);
             const uint32_t d_tmem = tmem_base + ii * args.acc_cols;
             bool ok = true;
             // Stage index = kb mod stages and stages is a multiple of the issuer count, so this
-            // issuer owns the stages ii, ii+I, ... (its j-th own stage is ii + I*j). It also loads
-            // the WEIGHT tiles of its own K blocks (weights depend on nothing before this kernel, so
-            // there is no wait for the preceding kernel here): first it fills its stages, then after
-            // each K block it re-arms the stage it consumed `lag` blocks earlier, whose MMAs have
-            // finished by then. Increments only, no divisions.
-            const uint32_t I = args.issuers, own = stages / I, lag = own > 2 ? 2u : own - 1u;
+            // issuer owns the stages ii, ii+I, ... and sees each of their phases in order.
+            const uint32_t I = args.issuers, own = stages / I;
             const uint32_t wstep = lay.w_bytes * I, xstep = lay.x_bytes * I;
             const uint32_t w0 = w_addr(ii), x0 = x_addr(ii), f0 = full(ii), e0 = empty(ii);
-            const int32_t channel = (int32_t)first_channel;
-            uint32_t load_kb = ii, lw = w0, lf = f0;               // next K block to load and its stage
-            for (uint32_t j = 0; j < own && load_kb < num_kb; j++) {
-                mbar_expect_tx(lf, stage_tx);
-                tma_load_2d(lw, &args.tmap_w, lf, (int32_t)(load_kb * kRK), channel);
-                load_kb += I; lw += wstep; lf += 8 * I;
-            }
-            // refill cursor: the stage consumed `lag` blocks ago
-            uint32_t rw = w0, rf = f0, re = e0, rstage = 0, rphase = 0;
-            uint32_t wa = w0, xa = x0, fb = f0, eb = e0, cstage = 0, cphase = 0, first = 1, done = 0;
-            for (uint32_t i = ii; i < num_kb; i += I, done++) {
+            uint32_t wa = w0, xa = x0, fb = f0, eb = e0, cstage = 0, cphase = 0, first = 1;
+            for (uint32_t i = ii; i < num_kb; i += I) {
                 if (!mbar_wait(fb, cphase, abort_flag)) { ok = false; break; }
                 tc_fence_after();
+                if (i == 0) stamp(args.trace, 2);
                 const uint64_t da = make_smem_desc(xa), db = make_smem_desc(wa);
 #pragma unroll
                 for (uint32_t k = 0; k < kRK / kUmmaK; k++)   // +32 bytes of K = +2 in the descriptor's address field
@@ -212,18 +239,11 @@ decode_rows_kernel(const __grid_constant__ DecodeRowsArgs args) {
                 umma_commit(eb);
                 wa += wstep; xa += xstep; fb += 8 * I; eb += 8 * I;
                 if (++cstage == own) { cstage = 0; cphase ^= 1u; wa = w0; xa = x0; fb = f0; eb = e0; }
-                if (done >= lag && load_kb < num_kb) {
-                    if (!mbar_wait(re, rphase, abort_flag)) { ok = false; break; }
-                    mbar_expect_tx(rf, stage_tx);
-                    tma_load_2d(rw, &args.tmap_w, rf, (int32_t)(load_kb * kRK), channel);
-                    load_kb += I;
-                    rw += wstep; rf += 8 * I; re += 8 * I;
-                    if (++rstage == own) { rstage = 0; rphase ^= 1u; rw = w0; rf = f0; re = e0; }
-                }
             }
             if (ok) umma_commit(tmem_full(0));
+            if (ii == 0) stamp(args.trace, 3);
         }
-    } else if (warp == 1) {
+    } else if (warp == 0) {
         // ---------------- MMA issuer, single ----------------
         if (lane == 0) {
             const uint32_t idesc = make_idesc(Cfg::kUmmaM, args.umma_n);
@@ -236,6 +256,7 @@ decode_rows_kernel(const __grid_constant__ DecodeRowsArgs args) {
                 for (uint32_t kb = 0; kb < num_kb; kb++) {
                     if (!mbar_wait(full(stage), phase, abort_flag)) { ok = false; break; }
                     tc_fence_after();
+                    if ((t | kb) == 0) stamp(args.trace, 2);
                     const uint32_t wa = w_addr(stage), xa = x_addr(stage);
 #pragma unroll
                     for (uint32_t k = 0; k < kRK / kUmmaK; k++)   // A = activations, B = weights
@@ -249,8 +270,9 @@ decode_rows_kernel(const __grid_constant__ DecodeRowsArgs args) {
                 if (double_buffered) { acc ^= 1u; if (acc == 0) acc_phase ^= 1u; }
                 else acc_phase ^= 1u;
             }
+            stamp(args.trace, 3);
         }
-    } else if (warp > kIssuerWarps && warp < kXWarp) {
+    } else if (warp >= kIssuerWarps && warp < kXWarp) {
         // ---------------- epilogue (last four warps): thread = one token row ----------------
         const uint32_t quarter = warp & 3u;
         const uint32_t e = threadIdx.x - kEpiBase;
@@ -290,19 +312,82 @@ decode_rows_kernel(const __grid_constant__ DecodeRowsArgs args) {
             epi_bar();
             if (epi_flag[0]) break;
             tc_fence_after();
+            if (e == 0 && t + 1 == tiles) stamp(args.trace, 4);
 
             const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + acc * acc_stride;
             const uint32_t left = args.n > c0 ? args.n - c0 : 0u;
             const uint32_t valid = left < args.tile_rows ? left : args.tile_rows;
+            if constexpr (Cfg::kParkAll) {
+                // Few token rows (M = 64: row r sits in lane r % 16 of warp r / 16). The warps that
+                // hold rows move the whole tile into shared memory, one barrier, then thread =
+                // channel finishes every row of its channel: each store instruction covers
+                // consecutive channels of one row.
+                const uint32_t pitch = Cfg::park_pitch(args.umma_n);
+                if (quarter * 16u < args.rows) {
+                    const uint32_t nchunks = (valid + 31u) >> 5;
+#pragma unroll 1
+                    for (uint32_t ci = 0; ci < nchunks; ci++) {
+                        const uint32_t c = ci << 5;
+                        uint32_t r[32];
+                        tmem_ld32(taddr + c, r);
+                        if (args.issuers > 1) {
+                            uint32_t more[32];
+                            tmem_ld32(taddr + args.acc_cols + c, more);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int i = 0; i < 32; i++) r[i] += more[i];
+                            for (uint32_t a = 2; a < args.issuers; a++) {
+                                tmem_ld32(taddr + a * args.acc_cols + c, more);
+                                tmem_ld_wait();
+#pragma unroll
+                                for (int i = 0; i < 32; i++) r[i] += more[i];
+                            }
+                        } else {
+                            tmem_ld_wait();
+                        }
+                        if (m_ok) {
+                            uint4* dst = reinterpret_cast<uint4*>(s_xpose + m * pitch + c);
+#pragma unroll
+                            for (int j = 0; j < 8; j++) dst[j] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+                        }
+                    }
+                }
+                epi_bar();
+                for (uint32_t col = e; col < valid; col += 128) {
+                    const float wsv = s_ws[col];
+                    const float bf = s_bias[col];
+                    const int32_t bi = __float_as_int(bf);
+                    const size_t at = (size_t)c0 + col;
+#pragma unroll 4
+                    for (uint32_t mm = 0; mm < args.rows; mm++) {
+                        const int32_t v = s_xpose[mm * pitch + col];
+                        const float asv = s_as[mm];
+                        if (ep.mode == kEpiF32) {
+                            ((float*)ep.out)[(size_t)mm * ep.ld + at] = epi_f32(v, asv, wsv, bf);
+                        } else if (ep.mode == kEpiI8) {
+                            const int32_t qv = (ep.fast_div != 0 && div_const_row_ok(asv))
+                                ? epi_i8_v2<true>(v + bi, asv, wsv, ep.out_scale, ep.out_rcp, zero_f, lo_f, hi_f, ep.out_zero)
+                                : epi_i8_v2<false>(v + bi, asv, wsv, ep.out_scale, ep.out_rcp, zero_f, lo_f, hi_f, ep.out_zero);
+                            ((int8_t*)ep.out)[(size_t)mm * ep.ld + at] = (int8_t)qv;
+                        } else {
+                            ((int32_t*)ep.out)[(size_t)mm * ep.ld + at] = v;
+                        }
+                    }
+                }
+            } else {
             // TMEM hands each thread one token row; the stores want one channel per lane. Each
             // 32-channel chunk is therefore transposed through shared memory: row threads park
             // their 32 values, then thread (lane = channel, warp = row group) finishes rows
             // warp, warp+4, ... so that every store instruction covers 32 consecutive channels.
+            // Two parking buffers alternate, so one barrier per chunk is enough, and the TMEM
+            // load of the next chunk is in flight while this one is finished.
             const uint32_t row_group = e >> 5;
+            const uint32_t nchunks = (valid + 31u) >> 5;
+            uint32_t r[32];
+            if (nchunks) tmem_ld32(taddr, r);
 #pragma unroll 1
-            for (uint32_t c = 0; c < args.umma_n; c += 32) {
-                uint32_t r[32];
-                tmem_ld32(taddr + c, r);
+            for (uint32_t ci = 0; ci < nchunks; ci++) {
+                const uint32_t c = ci << 5;
                 tmem_ld_wait();
                 for (uint32_t a = 1; a < args.issuers; a++) {   // add the other issuers' accumulators
                     uint32_t more[32];
@@ -311,12 +396,12 @@ decode_rows_kernel(const __grid_constant__ DecodeRowsArgs args) {
 #pragma unroll
                     for (int i = 0; i < 32; i++) r[i] += more[i];
                 }
-                if (c >= valid) continue;          // uniform: nothing of this chunk is stored
-                epi_bar();                           // the previous chunk has been read
+                int32_t* park = s_xpose + (ci & 1u) * (MT * kXposePitch);
                 if (m_ok) {
 #pragma unroll
-                    for (uint32_t i = 0; i < 32; i++) s_xpose[m * kXposePitch + i] = (int32_t)r[i];
+                    for (uint32_t i = 0; i < 32; i++) park[m * kXposePitch + i] = (int32_t)r[i];
                 }
+                if (ci + 1 < nchunks) tmem_ld32(taddr + c + 32, r);
                 epi_bar();
                 const uint32_t col = c + lane;
                 if (col < valid) {
@@ -325,7 +410,7 @@ decode_rows_kernel(const __grid_constant__ DecodeRowsArgs args) {
                     const int32_t bi = __float_as_int(bf);
                     const size_t at = (size_t)c0 + col;
                     for (uint32_t mm = row_group; mm < args.rows; mm += 4) {
-                        const int32_t v = s_xpose[mm * kXposePitch + lane];
+                        const int32_t v = park[mm * kXposePitch + lane];
                         const float asv = s_as[mm];
                         if (ep.mode == kEpiF32) {
                             ((float*)ep.out)[(size_t)mm * ep.ld + at] = epi_f32(v, asv, wsv, bf);
@@ -340,7 +425,9 @@ decode_rows_kernel(const __grid_constant__ DecodeRowsArgs args) {
                     }
                 }
             }
+            }
             // the accumulator has been consumed: hand the TMEM buffer back to the MMA warp
+            if (e == 0 && t + 1 == tiles) stamp(args.trace, 5);
             tc_fence_before();
             mbar_arrive(tmem_empty(acc));
             if (double_buffered) { acc ^= 1u; if (acc == 0) acc_phase ^= 1u; }
@@ -358,52 +445,71 @@ decode_rows_kernel(const __grid_constant__ DecodeRowsArgs args) {
         __syncthreads();
     }
     tc_fence_after();
-    if (warp == 1) tmem_dealloc(tmem_base, args.tmem_cols);
+    if (warp == 0) tmem_dealloc(tmem_base, args.tmem_cols);
+    if (threadIdx.x == 0) stamp(args.trace, 7);
 }
 
-template <uint32_t MT>
+template <uint32_t MT, bool PAIR>
 cudaError_t launch_t(DecodeRowsArgs args, cudaStream_t stream) {
     using Cfg = RowsCfg<MT>;
+    using Mode = ModeCfg<PAIR>;
     args.umma_n = round_up(args.tile_rows, 16u);
-    // TMEM: a power-of-two number of columns >= umma_n per accumulator; a CTA with one tile
-    // allocates twice that too (the second half stays unused) so acc_stride is uniform, except
-    // that 256-column tiles with a single tile allocate exactly 256 so two CTAs still fit an SM.
+    // TMEM: a power-of-two number of columns >= umma_n per accumulator
     uint32_t cols = 32;
     while (cols < args.umma_n) cols *= 2;
     args.acc_cols = cols;
-    // ring depth: as many stages as fit the budget
-    const uint32_t per_stage = args.w_stage_bytes + Cfg::kXBytes;
-    uint32_t stages = kRingBudgetDeep / per_stage;
-    if (stages < 2) stages = 2;
-    if (stages > kMaxStages) stages = kMaxStages;
-    // several issuers (each with its own accumulator) while they fit the 512 TMEM columns.
-    // Issuer ii takes the K blocks
-    // kb = ii (mod issuers); the ring depth is made a multiple of the issuer count so that each
-    // stage (kb mod stages) is only ever waited on by one issuer, in order - a parity wait on an
-    // mbarrier is only meaningful for a waiter that saw the previous phase complete.
-    uint32_t issuers = 1;
+    // Several issuers (each with its own accumulator) while they fit this CTA's TMEM columns, and
+    // several producers. Issuer ii takes the K blocks ii (mod I), producer p the blocks p (mod P),
+    // and block b lives in stage b mod stages: the ring depth is made a multiple of both counts,
+    // so that each stage's barriers are only ever waited on by one issuer and one producer, in
+    // order - a parity wait on an mbarrier is only meaningful for a waiter that saw the previous
+    // phase complete.
+    const uint32_t num_kb = args.kpad / kRK;
+    uint32_t max_issuers = 1;
     if (args.tiles_per_cta == 1) {
-        issuers = 512 / cols;
-        if (issuers > kIssuerWarps) issuers = kIssuerWarps;
-        const uint32_t num_kb = args.kpad / kRK;
-        while (issuers > 1 && (issuers > num_kb || issuers > stages)) issuers /= 2;
+        max_issuers = Mode::kTmemCols / cols;
+        if (max_issuers > Mode::kIssuerWarps) max_issuers = Mode::kIssuerWarps;
+        if (max_issuers > num_kb) max_issuers = num_kb;
+        if (max_issuers < 1) max_issuers = 1;
     }
-    stages -= stages % issuers;
+    uint32_t max_producers = kProducerWarps;
+    if (max_producers > num_kb) max_producers = num_kb;
+    // ring depth: as many stages as fit half an SM's shared memory, minus up to three to reach a
+    // depth that more than one producer and issuer divide
+    auto fits = [&](uint32_t st) {
+        const RowsLayout f{st, args.w_stage_bytes, Cfg::kXBytes, Cfg::kUmmaM, args.umma_n, Cfg::xpose_bytes(args.rows, args.umma_n)};
+        return f.total() <= Mode::kSmemBytes;
+    };
+    auto divisor = [](uint32_t st, uint32_t cap) { uint32_t d = cap; while (st % d) d--; return d; };
+    // issuers: a power of two (one accumulator each, and TMEM is allocated in powers of two)
+    auto divisor2 = [](uint32_t st, uint32_t cap) { uint32_t d = 1; while (2 * d <= cap && st % (2 * d) == 0) d *= 2; return d; };
+    uint32_t deepest = kMaxStages;
+    while (deepest > 2 && !fits(deepest)) deepest--;
+    uint32_t stages = deepest, producers = divisor(deepest, max_producers), issuers = divisor2(deepest, max_issuers);
+    for (uint32_t st = deepest; st + 3 >= deepest && st >= 2; st--) {
+        const uint32_t pp = divisor(st, max_producers), ii = divisor2(st, max_issuers);
+        // prefer: two or more producers, then two or more issuers (where allowed), then depth
+        const bool good = pp >= (max_producers > 1 ? 2u : 1u) && ii >= (max_issuers > 1 ? 2u : 1u);
+        if (good) { stages = st; producers = pp; issuers = ii; break; }
+    }
+    args.producers = producers;
     args.stages = stages;
     args.issuers = issuers;
-    args.tmem_cols = issuers > 1 ? issuers * cols : ((args.tiles_per_cta == 1 && cols == 256) ? 256u : 2 * cols);
+    // one accumulator per issuer; a CTA with several tiles double-buffers one issuer's accumulator
+    args.tmem_cols = issuers > 1 ? issuers * cols : (args.tiles_per_cta == 1 ? cols : 2 * cols);
     if (args.tmem_cols < 32) args.tmem_cols = 32;
-    const RowsLayout lay{stages, args.w_stage_bytes, Cfg::kXBytes, Cfg::kUmmaM, args.umma_n};
+    if (args.tmem_cols & (args.tmem_cols - 1)) return cudaErrorInvalidValue;   // tcgen05.alloc takes powers of two only
+    const RowsLayout lay{stages, args.w_stage_bytes, Cfg::kXBytes, Cfg::kUmmaM, args.umma_n, Cfg::xpose_bytes(args.rows, args.umma_n)};
     const uint32_t smem = lay.total();
     static uint32_t configured = 0;
     if (smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(decode_rows_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(decode_rows_kernel<MT, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
         configured = smem;
     }
     const uint32_t per_cta = args.tiles_per_cta * args.tile_rows;
     const uint32_t grid = (args.n + per_cta - 1) / per_cta;
-    return launch_pdl(decode_rows_kernel<MT>, dim3(grid), dim3(kThreads), smem, stream, args);
+    return launch_pdl(decode_rows_kernel<MT, PAIR>, dim3(grid), dim3(Mode::kThreads), smem, stream, args);
 }
 
 }  // namespace
@@ -424,11 +530,20 @@ cudaError_t launch_decode_rows(const DecodeRowsArgs& args, cudaStream_t stream) 
     if (args.rows == 0 || args.n == 0) return cudaSuccess;
     if (args.rows > 128 || args.tile_rows == 0 || args.tile_rows > kMaxTile) return cudaErrorInvalidValue;
     const uint32_t mt = decode_rows_token_slots(args.rows);
-    if (mt == 8) return launch_t<8>(args, stream);
-    if (mt == 16) return launch_t<16>(args, stream);
-    if (mt == 32) return launch_t<32>(args, stream);
-    if (mt == 64) return launch_t<64>(args, stream);
-    return launch_t<128>(args, stream);
+    // small weight shares: two CTAs per SM, so that successive launches overlap (see kPairSmemBytes)
+    const bool pair = (size_t)args.tiles_per_cta * args.tile_rows * args.kpad <= kPairShareBytes;
+    if (pair) {
+        if (mt == 8) return launch_t<8, true>(args, stream);
+        if (mt == 16) return launch_t<16, true>(args, stream);
+        if (mt == 32) return launch_t<32, true>(args, stream);
+        if (mt == 64) return launch_t<64, true>(args, stream);
+        return launch_t<128, true>(args, stream);
+    }
+    if (mt == 8) return launch_t<8, false>(args, stream);
+    if (mt == 16) return launch_t<16, false>(args, stream);
+    if (mt == 32) return launch_t<32, false>(args, stream);
+    if (mt == 64) return launch_t<64, false>(args, stream);
+    return launch_t<128, false>(args, stream);
 }
 
 }  // namespace vxb

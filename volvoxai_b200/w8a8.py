@@ -79,6 +79,10 @@ class Context:
         _check(self._L.vxb_measure_i8_tensor_peak(self.handle, iters, C.byref(out)))
         return out.value
 
+    def trace(self, stamps) -> None:
+        """Decode-kernel time stamps into the int64 CUDA tensor `stamps` ([ctas, 8]); None stops."""
+        _check(self._L.vxb_context_trace(self.handle, _ptr(stamps) if stamps is not None else None))
+
     def profile(self, enable: bool) -> None:
         """Start (True) or stop (False) per-kernel event timing; both clear the record."""
         _check(self._L.vxb_context_profile(self.handle, 1 if enable else 0))
