@@ -62,6 +62,21 @@ bool encode_i8_rows(CUtensorMap* map, const void* base, uint32_t rows, uint32_t 
               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// The same matrix seen as {128 B, rows, kpad / 128}: a box of (128 B x box_rows x box_blocks) lands as
+// box_blocks consecutive [box_rows x 128 B] swizzled tiles, one per 128-byte K block.
+bool encode_i8_kblocks(CUtensorMap* map, const void* base, uint32_t rows, uint32_t kpad, uint32_t box_rows,
+                       uint32_t box_blocks) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[3] = {kKAlign, rows, kpad / kKAlign};
+    cuuint64_t strides[2] = {kpad, kKAlign};
+    cuuint32_t box[3] = {kKAlign, box_rows, box_blocks};
+    cuuint32_t elem[3] = {1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 struct Buffer {
     void* ptr = nullptr; size_t bytes = 0;
     cudaError_t reserve(size_t need) {
@@ -217,13 +232,14 @@ int run_gemm(VxbContext* ctx, const VxbWeight* w, const int8_t* q, uint32_t rows
         if (rows > 128) return fail(0, "decode route needs rows <= 128 (got %u)", rows);
         if (!w->has_tmap) return fail(0, "no tensor map for this weight (driver entry point missing)");
         DecodeRowsArgs a;
-        if (!encode_i8_rows(&a.tmap_x, q, rows, w->kpad, decode_rows_token_slots(rows)))
-            return fail(0, "cuTensorMapEncodeTiled failed for activations");
         a.tmap_w = w->tmap_rows;
         a.rows = rows; a.n = w->d_out; a.kpad = w->kpad;
-        a.tile_rows = w->tile_rows; a.tiles_per_cta = w->tiles_per_cta; a.stages = 0;
+        a.tile_rows = w->tile_rows; a.tiles_per_cta = w->tiles_per_cta;
         a.w_stage_bytes = round_up(w->tile_rows * kKAlign, 1024u);
         a.epi = epi; a.status = ctx->status; a.trace = ctx->trace;
+        if (!decode_rows_configure(a)) return fail(0, "no launch shape for the decode kernel (rows %u, d_out %u)", rows, w->d_out);
+        if (!encode_i8_kblocks(&a.tmap_x, q, rows, w->kpad, decode_rows_token_slots(rows), a.x_chunk_blocks))
+            return fail(0, "cuTensorMapEncodeTiled failed for activations");
         CUDA_TRY(launch_decode_rows(a, ctx->stream), -1);
     } else if (plan.route == VXB_ROUTE_DECODE_STREAMK) {
         if (rows > 128) return fail(0, "decode route needs rows <= 128 (got %u)", rows);

@@ -177,11 +177,12 @@ cudaError_t gemm_tcgen05_prepare();  // one-time func attribute set-up
 // tile_rows / tiles_per_cta come from decode_rows_plan(); tmap_w has a box of tile_rows rows,
 // tmap_x a box of decode_rows_token_slots(rows) rows.
 struct DecodeRowsArgs {
-    CUtensorMap tmap_w;
-    CUtensorMap tmap_x;
+    CUtensorMap tmap_w;       // weights [n, kpad], box tile_rows x 128 B
+    CUtensorMap tmap_x;       // activations [rows, kpad] seen as {128 B, rows, kpad/128}, box 128 B x token slots x x_chunk_blocks
     uint32_t rows, n, kpad;
     uint32_t tile_rows, tiles_per_cta;
-    uint32_t stages, umma_n, tmem_cols, acc_cols, issuers, producers;   // filled in by the launcher
+    // filled in by decode_rows_configure
+    uint32_t stages, umma_n, tmem_cols, acc_cols, issuers, producers, x_chunk_blocks, x_slots, pair;
     uint32_t w_stage_bytes;   // round_up(tile_rows * 128, 1024)
     EpilogueParams epi;
     int* status;
@@ -191,6 +192,7 @@ constexpr uint32_t kTraceSlots = 8;   // 0 entry, 1 prologue done, 2 first weigh
                                       // 4 accumulator ready, 5 last store, 6 predecessor finished, 7 exit
 uint32_t decode_rows_token_slots(uint32_t rows);  // 8 / 16 / 32 / 64 / 128
 void decode_rows_plan(uint32_t n, int sm_count, uint32_t* tile_rows, uint32_t* tiles_per_cta);
+bool decode_rows_configure(DecodeRowsArgs& args);   // before the activation tensor map is encoded
 cudaError_t launch_decode_rows(const DecodeRowsArgs& args, cudaStream_t stream);
 
 // K3b: skinny stream-K tcgen05 kernel for rows <= 128 (weights are the UMMA M operand).

@@ -37,8 +37,7 @@ namespace {
 using namespace tc;
 
 constexpr uint32_t kRK = 128;              // K bytes per stage
-constexpr uint32_t kProducerWarps = 4;      // warps that may issue TMA copies
-constexpr uint32_t kMaxStages = 32;
+constexpr uint32_t kMaxStages = 48;
 constexpr uint32_t kMaxTile = 256;         // channels per tile (UMMA N limit)
 // Two CTAs fit an SM (shared memory, registers and TMEM columns are all held to half of it), so
 // that the CTAs of the NEXT launch in the stream become resident while this launch still runs:
@@ -55,6 +54,7 @@ constexpr uint32_t kPairShareBytes = 160 * 1024;               // largest weight
 
 template <bool PAIR> struct ModeCfg {
     static constexpr uint32_t kIssuerWarps = PAIR ? 4 : 8;     // warps 0.. may issue MMAs
+    static constexpr uint32_t kProducerWarps = PAIR ? 4 : 5;   // TMA warps: weight producers, then one for the activations
     static constexpr uint32_t kXWarp = kIssuerWarps + 4;       // first producer warp (4 epilogue warps before it)
     static constexpr uint32_t kThreads = 32 * (kXWarp + kProducerWarps);
     static constexpr uint32_t kEpiBase = 32 * kIssuerWarps;
@@ -65,7 +65,7 @@ template <bool PAIR> struct ModeCfg {
 constexpr uint32_t kXposePitch = 33;       // ints per row of the epilogue transpose buffer
 
 template <uint32_t MT> struct RowsCfg {
-    static constexpr uint32_t kXBytes = MT * kRK < 1024 ? 1024 : MT * kRK;  // activation stage
+    static constexpr uint32_t kXAtom = MT * kRK;   // one [MT x 128 B] activation tile (MT >= 8: whole swizzle atoms)
     static constexpr uint32_t kUmmaM = MT <= 64 ? 64 : 128;                  // rows the MMA spans
     static constexpr bool kParkAll = MT <= 32;   // few token rows: the epilogue parks the whole tile at once
     // parking area of the epilogue: the whole [rows, umma_n] tile (pitch umma_n + 4 ints) for few
@@ -77,25 +77,25 @@ template <uint32_t MT> struct RowsCfg {
     }
 };
 
+constexpr uint32_t kMaxXSlots = 8;
+
 struct RowsLayout {       // dynamic shared memory, offsets from a 1024-byte aligned base
-    uint32_t stages, w_bytes, x_bytes, umma_m, umma_n, xpose_bytes;
+    uint32_t stages, w_bytes;           // weight ring: one [tile_rows x 128 B] tile per stage
+    uint32_t x_slots, x_chunk_bytes;    // activation ring: x_chunk_blocks atoms of [MT x 128 B] per slot
+    uint32_t umma_m, umma_n, xpose_bytes;
     __host__ __device__ uint32_t w_off(uint32_t s) const { return s * w_bytes; }
     __host__ __device__ uint32_t w_end() const {
         // the MMA reads umma_n x 128 bytes from a weight stage
         const uint32_t reach = (stages - 1) * w_bytes + umma_n * kRK;
         return stages * w_bytes > reach ? stages * w_bytes : reach;
     }
-    __host__ __device__ uint32_t x_off(uint32_t s) const { return round_up(w_end(), 1024u) + s * x_bytes; }
-    __host__ __device__ uint32_t x_end() const {
-        // ... and umma_m x 128 bytes from an activation stage
-        const uint32_t ring = x_off(0) + stages * x_bytes;
-        const uint32_t reach = x_off(stages - 1) + umma_m * kRK;
-        return ring > reach ? ring : reach;
-    }
+    __host__ __device__ uint32_t x_off(uint32_t slot) const { return round_up(w_end(), 1024u) + slot * x_chunk_bytes; }
+    // ... and umma_m x 128 bytes from an activation atom (the last atom's reach goes past the ring)
+    __host__ __device__ uint32_t x_end() const { return x_off(x_slots) + umma_m * kRK; }
     __host__ __device__ uint32_t consts_off() const { return x_end(); }   // float ws[256], bias[256]
     __host__ __device__ uint32_t xpose_off() const { return consts_off() + 2 * kMaxTile * 4; }  // the epilogue's parking area
     __host__ __device__ uint32_t bars_off() const { return xpose_off() + xpose_bytes; }
-    __host__ __device__ uint32_t misc_off() const { return bars_off() + (2 * kMaxStages + 4) * 8; }
+    __host__ __device__ uint32_t misc_off() const { return bars_off() + (2 * kMaxStages + 2 * kMaxXSlots + 4) * 8; }
     __host__ __device__ uint32_t total() const { return misc_off() + 32 + 128 * 4 + 1024; }
 };
 
@@ -114,18 +114,21 @@ __global__ void __launch_bounds__(ModeCfg<PAIR>::kThreads, ModeCfg<PAIR>::kCtasP
 decode_rows_kernel(const __grid_constant__ DecodeRowsArgs args) {
     using Cfg = RowsCfg<MT>;
     constexpr uint32_t kIssuerWarps = ModeCfg<PAIR>::kIssuerWarps, kXWarp = ModeCfg<PAIR>::kXWarp;
-    constexpr uint32_t kEpiBase = ModeCfg<PAIR>::kEpiBase;
+    constexpr uint32_t kEpiBase = ModeCfg<PAIR>::kEpiBase, kProducerWarps = ModeCfg<PAIR>::kProducerWarps;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    const RowsLayout lay{args.stages, args.w_stage_bytes, Cfg::kXBytes, Cfg::kUmmaM, args.umma_n, Cfg::xpose_bytes(args.rows, args.umma_n)};
+    const RowsLayout lay{args.stages, args.w_stage_bytes, args.x_slots, args.x_chunk_blocks * Cfg::kXAtom,
+                         Cfg::kUmmaM, args.umma_n, Cfg::xpose_bytes(args.rows, args.umma_n)};
     const uint32_t stages = args.stages;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     auto w_addr = [&](uint32_t s) { return smem_u32(base + lay.w_off(s)); };
     auto x_addr = [&](uint32_t s) { return smem_u32(base + lay.x_off(s)); };
     auto full = [&](uint32_t s) { return smem_u32(base + lay.bars_off() + s * 8); };
     auto empty = [&](uint32_t s) { return smem_u32(base + lay.bars_off() + (kMaxStages + s) * 8); };
-    auto tmem_full = [&](uint32_t b) { return smem_u32(base + lay.bars_off() + (2 * kMaxStages + b) * 8); };
-    auto tmem_empty = [&](uint32_t b) { return smem_u32(base + lay.bars_off() + (2 * kMaxStages + 2 + b) * 8); };
+    auto xfull = [&](uint32_t s) { return smem_u32(base + lay.bars_off() + (2 * kMaxStages + s) * 8); };
+    auto xempty = [&](uint32_t s) { return smem_u32(base + lay.bars_off() + (2 * kMaxStages + kMaxXSlots + s) * 8); };
+    auto tmem_full = [&](uint32_t b) { return smem_u32(base + lay.bars_off() + (2 * kMaxStages + 2 * kMaxXSlots + b) * 8); };
+    auto tmem_empty = [&](uint32_t b) { return smem_u32(base + lay.bars_off() + (2 * kMaxStages + 2 * kMaxXSlots + 2 + b) * 8); };
     uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(base + lay.misc_off());
     volatile int* abort_flag = reinterpret_cast<volatile int*>(base + lay.misc_off() + 4);
     volatile int* epi_flag = reinterpret_cast<volatile int*>(base + lay.misc_off() + 8);
@@ -140,18 +143,22 @@ decode_rows_kernel(const __grid_constant__ DecodeRowsArgs args) {
     const uint32_t num_kb = args.kpad / kRK;
     const uint32_t tiles = args.tiles_per_cta;
     const uint32_t first_channel = blockIdx.x * tiles * args.tile_rows;
-    const uint32_t stage_tx = args.tile_rows * kRK + MT * kRK;   // bytes one stage receives
+    const uint32_t stage_tx = args.tile_rows * kRK;              // bytes one weight stage receives
+    const uint32_t KC = args.x_chunk_blocks, x_slots = args.x_slots;
     const bool double_buffered = tiles > 1;                       // else one accumulator, reused
     const uint32_t acc_stride = args.tmem_cols / 2;              // columns between the two accumulators
 
-    if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < stages; s++) { mbar_init(full(s), 1); mbar_init(empty(s), 1); }
-        mbar_init(tmem_full(0), args.issuers); mbar_init(tmem_full(1), 1);
-        for (uint32_t b = 0; b < 2; b++) mbar_init(tmem_empty(b), 128);
-        *abort_flag = 0;
+    if (warp == 1) {
+        for (uint32_t s = lane; s < stages; s += 32) { mbar_init(full(s), 1); mbar_init(empty(s), 1); }
+        if (lane < x_slots) { mbar_init(xfull(lane), 1); mbar_init(xempty(lane), args.issuers); }
+        if (lane == 0) {
+            mbar_init(tmem_full(0), args.issuers); mbar_init(tmem_full(1), 1);
+            for (uint32_t b = 0; b < 2; b++) mbar_init(tmem_empty(b), 128);
+            *abort_flag = 0;
+            prefetch_tmap(&args.tmap_w);
+            prefetch_tmap(&args.tmap_x);
+        }
         fence_barrier_init();
-        prefetch_tmap(&args.tmap_w);
-        prefetch_tmap(&args.tmap_x);
     }
     if (warp == 0) { tmem_alloc(smem_u32(tmem_ptr), args.tmem_cols); tmem_relinquish(); }
     tc_fence_before();
@@ -160,47 +167,49 @@ decode_rows_kernel(const __grid_constant__ DecodeRowsArgs args) {
     const uint32_t tmem_base = *tmem_ptr;
     if (threadIdx.x == 0) stamp(args.trace, 1);
 
-    if (warp >= kXWarp) {
-        // ---------------- producers ----------------
-        // Starting a TMA copy costs the issuing thread some 200 ns whatever the box size, so one
-        // thread cannot feed small K blocks fast enough: producer p of P loads the weight and the
-        // activation tiles of the blocks p, p+P, ... (block = tile * num_kb + kb) into its own
-        // stages p, p+P, ... (the ring depth is a multiple of P), re-arming a stage as soon as the
-        // MMAs that read it have completed. Only increments in the loop, no divisions.
-        // Weights depend on nothing that runs before this kernel: the first ring-full of them is
-        // requested before the wait for the preceding kernel, the activations after it.
+    if (warp == kXWarp + kProducerWarps - 1) {
+        // ---------------- activation producer ----------------
+        // The activations are shared by every K block's MMAs and small: one copy brings KC
+        // consecutive K blocks ([KC][MT x 128 B] atoms, a 3-D box) into one slot of a short ring of
+        // their own, so a TMA start (some 200 ns of the issuing thread whatever the box size) is
+        // paid once per KC blocks. Every issuer owns the same number of blocks in each chunk and
+        // hands the slot back (tcgen05.commit -> xempty) after its last one.
+        if (lane == 0) {
+            const uint32_t nch = (num_kb + KC - 1) / KC, total = tiles * nch;
+            const uint32_t chunk_tx = KC * Cfg::kXAtom;    // the whole box, zero-filled past the edges
+            pdl_wait();   // the activations are the preceding kernel's output
+            stamp(args.trace, 6);
+            uint32_t slot = 0, phase = 0, kc = 0;
+            for (uint32_t c = 0; c < total; c++) {
+                if (c >= x_slots && !mbar_wait(xempty(slot), phase ^ 1u, abort_flag)) break;
+                mbar_expect_tx(xfull(slot), chunk_tx);
+                tma_load_3d(x_addr(slot), &args.tmap_x, xfull(slot), 0, 0, (int32_t)(kc * KC));
+                if (++kc == nch) kc = 0;
+                if (++slot == x_slots) { slot = 0; phase ^= 1u; }
+            }
+        }
+    } else if (warp >= kXWarp) {
+        // ---------------- weight producers ----------------
+        // Producer p of P loads the weight tiles of the blocks p, p+P, ... (block = tile * num_kb +
+        // kb) into its own stages p, p+P, ... (the ring depth is a multiple of P), re-arming a
+        // stage as soon as the MMAs that read it have completed. Only increments in the loop.
+        // Weights depend on nothing that runs before this kernel, so these threads never wait
+        // for the preceding kernel: the ring is full before the activations may be read.
         const uint32_t p = warp - kXWarp, P = args.producers;
         if (lane == 0 && p < P) {
             const uint32_t total = tiles * num_kb, own = stages / P;
-            const uint32_t w0 = w_addr(p), x0 = x_addr(p), f0 = full(p), e0 = empty(p);
-            const uint32_t wstep = lay.w_bytes * P, xstep = lay.x_bytes * P;
-            // block cursor (K coordinate and channel of the next block of this producer)
+            const uint32_t w0 = w_addr(p), f0 = full(p), e0 = empty(p), wstep = lay.w_bytes * P;
             uint32_t kb = p; int32_t channel = (int32_t)first_channel;
             while (kb >= num_kb) { kb -= num_kb; channel += (int32_t)args.tile_rows; }
-            uint32_t i = p, pre = 0;
-            {   // first ring-full of weights
-                uint32_t w_sm = w0, fb = f0, kb2 = kb; int32_t ch2 = channel;
-                for (uint32_t b = p; pre < own && b < total; b += P, pre++) {
-                    mbar_expect_tx(fb, stage_tx);
-                    tma_load_2d(w_sm, &args.tmap_w, fb, (int32_t)(kb2 * kRK), ch2);
-                    kb2 += P; while (kb2 >= num_kb) { kb2 -= num_kb; ch2 += (int32_t)args.tile_rows; }
-                    w_sm += wstep; fb += 8 * P;
-                }
-            }
-            pdl_wait();   // the activations are the preceding kernel's output
-            if (p == 0) stamp(args.trace, 6);
-            uint32_t w_sm = w0, x_sm = x0, fb = f0, eb = e0, stage = 0, phase = 0;
+            uint32_t w_sm = w0, fb = f0, eb = e0, stage = 0, phase = 0;
             bool ok = true;
-            for (uint32_t u = 0; i < total; i += P, u++) {
-                if (u >= pre) {
-                    if (!mbar_wait(eb, phase ^ 1u, abort_flag)) { ok = false; break; }
-                    mbar_expect_tx(fb, stage_tx);
-                    tma_load_2d(w_sm, &args.tmap_w, fb, (int32_t)(kb * kRK), channel);
-                }
-                tma_load_2d(x_sm, &args.tmap_x, fb, (int32_t)(kb * kRK), 0);
+            for (uint32_t i = p, u = 0; i < total; i += P, u++) {
+                if (u >= own && !mbar_wait(eb, phase ^ 1u, abort_flag)) { ok = false; break; }
+                mbar_expect_tx(fb, stage_tx);
+                tma_load_2d(w_sm, &args.tmap_w, fb, (int32_t)(kb * kRK), channel);
                 kb += P; while (kb >= num_kb) { kb -= num_kb; channel += (int32_t)args.tile_rows; }
-                w_sm += wstep; x_sm += xstep; fb += 8 * P; eb += 8 * P;
-                if (++stage == own) { stage = 0; phase ^= 1u; w_sm = w0; x_sm = x0; fb = f0; eb = e0; }
+                w_sm += wstep; fb += 8 * P; eb += 8 * P;
+                if (++stage == own) { stage = 0; phase ^= 1u; w_sm = w0; fb = f0; eb = e0; }
             }
             if (!ok) {
                 // drain: give this thread's own copies in flight a bounded time to land
@@ -212,65 +221,64 @@ decode_rows_kernel(const __grid_constant__ DecodeRowsArgs args) {
                 }
             }
         }
-    } else if (warp < kIssuerWarps && args.issuers > 1) {
-        // ---------------- MMA issuers, several: issuer ii takes K blocks ii, ii+I, ... into its own
-        // accumulator (one thread can start an MMA only every ~70 clocks, far slower than the tensor
-        // pipe finishes a narrow one; the epilogue adds the accumulators up, integers: exact) ------
-        const uint32_t ii = warp;
-        if (lane == 0 && ii < args.issuers) {
+    } else if (warp < kIssuerWarps) {
+        // ---------------- MMA issuers ----------------
+        // One thread can start an MMA only every ~100 clocks, far slower than the tensor pipe
+        // finishes a narrow one, so up to eight threads issue: issuer ii of I takes the K blocks
+        // ii, ii+I, ... into an accumulator of its own (the epilogue adds them up; integers:
+        // exact). Block b lives in weight stage b mod stages and stages is a multiple of I, so
+        // this thread owns the stages ii, ii+I, ... and sees each of their phases in order; of
+        // every activation chunk (KC = I * m blocks) it owns the atoms ii, ii+I, ...
+        // A CTA with several tiles has one issuer, which alternates between two accumulators.
+        const uint32_t ii = warp, I = args.issuers;
+        if (lane == 0 && ii < I) {
             const uint32_t idesc = make_idesc(Cfg::kUmmaM, args.umma_n);
-            const uint32_t d_tmem = tmem_base + ii * args.acc_cols;
-            bool ok = true;
-            // Stage index = kb mod stages and stages is a multiple of the issuer count, so this
-            // issuer owns the stages ii, ii+I, ... and sees each of their phases in order.
-            const uint32_t I = args.issuers, own = stages / I;
-            const uint32_t wstep = lay.w_bytes * I, xstep = lay.x_bytes * I;
-            const uint32_t w0 = w_addr(ii), x0 = x_addr(ii), f0 = full(ii), e0 = empty(ii);
-            uint32_t wa = w0, xa = x0, fb = f0, eb = e0, cstage = 0, cphase = 0, first = 1;
-            for (uint32_t i = ii; i < num_kb; i += I) {
-                if (!mbar_wait(fb, cphase, abort_flag)) { ok = false; break; }
-                tc_fence_after();
-                if (i == 0) stamp(args.trace, 2);
-                const uint64_t da = make_smem_desc(xa), db = make_smem_desc(wa);
-#pragma unroll
-                for (uint32_t k = 0; k < kRK / kUmmaK; k++)   // +32 bytes of K = +2 in the descriptor's address field
-                    umma_i8(d_tmem, da + 2u * k, db + 2u * k, idesc, (first && k == 0u) ? 0u : 1u);
-                first = 0;
-                umma_commit(eb);
-                wa += wstep; xa += xstep; fb += 8 * I; eb += 8 * I;
-                if (++cstage == own) { cstage = 0; cphase ^= 1u; wa = w0; xa = x0; fb = f0; eb = e0; }
-            }
-            if (ok) umma_commit(tmem_full(0));
-            if (ii == 0) stamp(args.trace, 3);
-        }
-    } else if (warp == 0) {
-        // ---------------- MMA issuer, single ----------------
-        if (lane == 0) {
-            const uint32_t idesc = make_idesc(Cfg::kUmmaM, args.umma_n);
-            uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+            const uint32_t own = stages / I, per_chunk = KC / I;
+            const uint32_t wstep = lay.w_bytes * I, xstep = Cfg::kXAtom * I;
+            const uint32_t w0 = w_addr(ii), f0 = full(ii), e0 = empty(ii);
+            uint32_t wa = w0, fb = f0, eb = e0, cstage = 0, cphase = 0;
+            uint32_t xslot = 0, xphase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
             for (uint32_t t = 0; ok && t < tiles; t++) {
-                if (!mbar_wait(tmem_empty(acc), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
-                tc_fence_after();
-                const uint32_t d_tmem = tmem_base + acc * acc_stride;
-                for (uint32_t kb = 0; kb < num_kb; kb++) {
-                    if (!mbar_wait(full(stage), phase, abort_flag)) { ok = false; break; }
+                uint32_t d_tmem = tmem_base + ii * args.acc_cols;
+                if (I == 1) {
+                    if (!mbar_wait(tmem_empty(acc), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    d_tmem = tmem_base + acc * acc_stride;
+                }
+                uint32_t first = 1, in_chunk = 0, xa = 0;
+                for (uint32_t kb = ii; kb < num_kb; kb += I) {
+                    if (in_chunk == 0) {
+                        if (!mbar_wait(xfull(xslot), xphase, abort_flag)) { ok = false; break; }
+                        xa = x_addr(xslot) + ii * Cfg::kXAtom;
+                    }
+                    if (!mbar_wait(fb, cphase, abort_flag)) { ok = false; break; }
                     tc_fence_after();
                     if ((t | kb) == 0) stamp(args.trace, 2);
-                    const uint32_t wa = w_addr(stage), xa = x_addr(stage);
+                    const uint64_t da = make_smem_desc(xa), db = make_smem_desc(wa);
 #pragma unroll
-                    for (uint32_t k = 0; k < kRK / kUmmaK; k++)   // A = activations, B = weights
-                        umma_i8(d_tmem, make_smem_desc(xa + k * kUmmaK), make_smem_desc(wa + k * kUmmaK),
-                                idesc, (kb | k) != 0u ? 1u : 0u);
-                    umma_commit(empty(stage));
-                    if (++stage == stages) { stage = 0; phase ^= 1u; }
+                    for (uint32_t k = 0; k < kRK / kUmmaK; k++)   // +32 bytes of K = +2 in the descriptor's address field
+                        umma_i8(d_tmem, da + 2u * k, db + 2u * k, idesc, (first && k == 0u) ? 0u : 1u);
+                    first = 0;
+                    umma_commit(eb);
+                    wa += wstep; fb += 8 * I; eb += 8 * I; xa += xstep;
+                    if (++cstage == own) { cstage = 0; cphase ^= 1u; wa = w0; fb = f0; eb = e0; }
+                    if (++in_chunk == per_chunk || kb + I >= num_kb) {
+                        umma_commit(xempty(xslot));
+                        in_chunk = 0;
+                        if (++xslot == x_slots) { xslot = 0; xphase ^= 1u; }
+                    }
                 }
                 if (!ok) break;
-                umma_commit(tmem_full(acc));
-                if (double_buffered) { acc ^= 1u; if (acc == 0) acc_phase ^= 1u; }
-                else acc_phase ^= 1u;
+                if (I == 1) {
+                    umma_commit(tmem_full(acc));
+                    if (double_buffered) { acc ^= 1u; if (acc == 0) acc_phase ^= 1u; }
+                    else acc_phase ^= 1u;
+                } else {
+                    umma_commit(tmem_full(0));
+                }
             }
-            stamp(args.trace, 3);
+            if (ii == 0) stamp(args.trace, 3);
         }
     } else if (warp >= kIssuerWarps && warp < kXWarp) {
         // ---------------- epilogue (last four warps): thread = one token row ----------------
@@ -449,21 +457,17 @@ decode_rows_kernel(const __grid_constant__ DecodeRowsArgs args) {
     if (threadIdx.x == 0) stamp(args.trace, 7);
 }
 
+// Fills in the launch shape: issuers, producers, ring depths, TMEM columns.
 template <uint32_t MT, bool PAIR>
-cudaError_t launch_t(DecodeRowsArgs args, cudaStream_t stream) {
+bool configure_t(DecodeRowsArgs& args) {
     using Cfg = RowsCfg<MT>;
     using Mode = ModeCfg<PAIR>;
+    args.pair = PAIR ? 1u : 0u;
     args.umma_n = round_up(args.tile_rows, 16u);
     // TMEM: a power-of-two number of columns >= umma_n per accumulator
     uint32_t cols = 32;
     while (cols < args.umma_n) cols *= 2;
     args.acc_cols = cols;
-    // Several issuers (each with its own accumulator) while they fit this CTA's TMEM columns, and
-    // several producers. Issuer ii takes the K blocks ii (mod I), producer p the blocks p (mod P),
-    // and block b lives in stage b mod stages: the ring depth is made a multiple of both counts,
-    // so that each stage's barriers are only ever waited on by one issuer and one producer, in
-    // order - a parity wait on an mbarrier is only meaningful for a waiter that saw the previous
-    // phase complete.
     const uint32_t num_kb = args.kpad / kRK;
     uint32_t max_issuers = 1;
     if (args.tiles_per_cta == 1) {
@@ -472,34 +476,60 @@ cudaError_t launch_t(DecodeRowsArgs args, cudaStream_t stream) {
         if (max_issuers > num_kb) max_issuers = num_kb;
         if (max_issuers < 1) max_issuers = 1;
     }
-    uint32_t max_producers = kProducerWarps;
+    uint32_t max_producers = Mode::kProducerWarps - 1;   // the last producer warp loads the activations
     if (max_producers > num_kb) max_producers = num_kb;
-    // ring depth: as many stages as fit half an SM's shared memory, minus up to three to reach a
-    // depth that more than one producer and issuer divide
-    auto fits = [&](uint32_t st) {
-        const RowsLayout f{st, args.w_stage_bytes, Cfg::kXBytes, Cfg::kUmmaM, args.umma_n, Cfg::xpose_bytes(args.rows, args.umma_n)};
-        return f.total() <= Mode::kSmemBytes;
-    };
     auto divisor = [](uint32_t st, uint32_t cap) { uint32_t d = cap; while (st % d) d--; return d; };
-    // issuers: a power of two (one accumulator each, and TMEM is allocated in powers of two)
-    auto divisor2 = [](uint32_t st, uint32_t cap) { uint32_t d = 1; while (2 * d <= cap && st % (2 * d) == 0) d *= 2; return d; };
-    uint32_t deepest = kMaxStages;
-    while (deepest > 2 && !fits(deepest)) deepest--;
-    uint32_t stages = deepest, producers = divisor(deepest, max_producers), issuers = divisor2(deepest, max_issuers);
-    for (uint32_t st = deepest; st + 3 >= deepest && st >= 2; st--) {
-        const uint32_t pp = divisor(st, max_producers), ii = divisor2(st, max_issuers);
-        // prefer: two or more producers, then two or more issuers (where allowed), then depth
-        const bool good = pp >= (max_producers > 1 ? 2u : 1u) && ii >= (max_issuers > 1 ? 2u : 1u);
-        if (good) { stages = st; producers = pp; issuers = ii; break; }
+    // Issuers: a power of two (one accumulator each; TMEM is allocated in powers of two), as many
+    // as leave every issuer two weight stages of its own. Block b lives in stage b mod stages:
+    // the ring depth is a multiple of the issuer and of the producer count, so that each stage's
+    // barriers are only ever waited on by one issuer and one producer, in order - a parity wait
+    // on an mbarrier is only meaningful for a waiter that saw the previous phase complete.
+    uint32_t issuers = 1;
+    while (2 * issuers <= max_issuers) issuers *= 2;
+    for (;; issuers /= 2) {
+        // activation chunk: a multiple of the issuer count, about 8 KB, at most the row's blocks
+        uint32_t per = 8192u / (issuers * Cfg::kXAtom);
+        if (per < 1) per = 1;
+        const uint32_t most = (num_kb + issuers - 1) / issuers;
+        if (per > most) per = most;
+        const uint32_t kc = issuers * per;
+        const uint32_t nch = ((num_kb + kc - 1) / kc) * args.tiles_per_cta;
+        uint32_t slots = kc * Cfg::kXAtom > 8192u ? 2u : 4u;
+        if (slots > nch) slots = nch;
+        auto fits = [&](uint32_t st) {
+            const RowsLayout f{st, args.w_stage_bytes, slots, kc * Cfg::kXAtom, Cfg::kUmmaM, args.umma_n,
+                               Cfg::xpose_bytes(args.rows, args.umma_n)};
+            return f.total() <= Mode::kSmemBytes;
+        };
+        uint32_t deepest = kMaxStages;
+        while (deepest > 1 && !fits(deepest)) deepest--;
+        // among the deepest few depths that the issuers divide: most producers first, then depth
+        uint32_t best = 0, best_p = 0;
+        for (uint32_t st = deepest; st >= 1 && st + 8 > deepest; st--) {
+            if (st % issuers) continue;
+            const uint32_t pp = divisor(st, max_producers);
+            if (pp > best_p) { best = st; best_p = pp; }
+        }
+        if (best >= 2 * issuers || (issuers == 1 && best >= 1)) {
+            if (!fits(best)) return false;   // not even the shallowest ring fits
+            args.stages = best; args.producers = best_p; args.issuers = issuers;
+            args.x_chunk_blocks = kc; args.x_slots = slots;
+            break;
+        }
+        if (issuers == 1) return false;
     }
-    args.producers = producers;
-    args.stages = stages;
-    args.issuers = issuers;
     // one accumulator per issuer; a CTA with several tiles double-buffers one issuer's accumulator
-    args.tmem_cols = issuers > 1 ? issuers * cols : (args.tiles_per_cta == 1 ? cols : 2 * cols);
+    args.tmem_cols = args.issuers > 1 ? args.issuers * cols : (args.tiles_per_cta == 1 ? cols : 2 * cols);
     if (args.tmem_cols < 32) args.tmem_cols = 32;
-    if (args.tmem_cols & (args.tmem_cols - 1)) return cudaErrorInvalidValue;   // tcgen05.alloc takes powers of two only
-    const RowsLayout lay{stages, args.w_stage_bytes, Cfg::kXBytes, Cfg::kUmmaM, args.umma_n, Cfg::xpose_bytes(args.rows, args.umma_n)};
+    return (args.tmem_cols & (args.tmem_cols - 1)) == 0 && args.tmem_cols <= 512;   // tcgen05.alloc: powers of two
+}
+
+template <uint32_t MT, bool PAIR>
+cudaError_t launch_t(const DecodeRowsArgs& args, cudaStream_t stream) {
+    using Cfg = RowsCfg<MT>;
+    using Mode = ModeCfg<PAIR>;
+    const RowsLayout lay{args.stages, args.w_stage_bytes, args.x_slots, args.x_chunk_blocks * Cfg::kXAtom,
+                         Cfg::kUmmaM, args.umma_n, Cfg::xpose_bytes(args.rows, args.umma_n)};
     const uint32_t smem = lay.total();
     static uint32_t configured = 0;
     if (smem > configured) {
@@ -526,24 +556,35 @@ void decode_rows_plan(uint32_t n, int sm_count, uint32_t* tile_rows, uint32_t* t
     *tile_rows = (per_cta + tiles - 1) / tiles;
 }
 
-cudaError_t launch_decode_rows(const DecodeRowsArgs& args, cudaStream_t stream) {
-    if (args.rows == 0 || args.n == 0) return cudaSuccess;
-    if (args.rows > 128 || args.tile_rows == 0 || args.tile_rows > kMaxTile) return cudaErrorInvalidValue;
-    const uint32_t mt = decode_rows_token_slots(args.rows);
+#define VXB_DECODE_DISPATCH(fn, ...)                                                          \
+    do {                                                                                      \
+        const uint32_t mt = decode_rows_token_slots(args.rows);                               \
+        if (pair) {                                                                           \
+            if (mt == 8) return fn<8, true>(__VA_ARGS__);                                     \
+            if (mt == 16) return fn<16, true>(__VA_ARGS__);                                   \
+            if (mt == 32) return fn<32, true>(__VA_ARGS__);                                   \
+            if (mt == 64) return fn<64, true>(__VA_ARGS__);                                   \
+            return fn<128, true>(__VA_ARGS__);                                                \
+        }                                                                                     \
+        if (mt == 8) return fn<8, false>(__VA_ARGS__);                                        \
+        if (mt == 16) return fn<16, false>(__VA_ARGS__);                                      \
+        if (mt == 32) return fn<32, false>(__VA_ARGS__);                                      \
+        if (mt == 64) return fn<64, false>(__VA_ARGS__);                                      \
+        return fn<128, false>(__VA_ARGS__);                                                   \
+    } while (0)
+
+bool decode_rows_configure(DecodeRowsArgs& args) {
+    if (args.rows == 0 || args.rows > 128 || args.n == 0 || args.tile_rows == 0 || args.tile_rows > kMaxTile) return false;
     // small weight shares: two CTAs per SM, so that successive launches overlap (see kPairSmemBytes)
     const bool pair = (size_t)args.tiles_per_cta * args.tile_rows * args.kpad <= kPairShareBytes;
-    if (pair) {
-        if (mt == 8) return launch_t<8, true>(args, stream);
-        if (mt == 16) return launch_t<16, true>(args, stream);
-        if (mt == 32) return launch_t<32, true>(args, stream);
-        if (mt == 64) return launch_t<64, true>(args, stream);
-        return launch_t<128, true>(args, stream);
-    }
-    if (mt == 8) return launch_t<8, false>(args, stream);
-    if (mt == 16) return launch_t<16, false>(args, stream);
-    if (mt == 32) return launch_t<32, false>(args, stream);
-    if (mt == 64) return launch_t<64, false>(args, stream);
-    return launch_t<128, false>(args, stream);
+    VXB_DECODE_DISPATCH(configure_t, args);
+}
+
+cudaError_t launch_decode_rows(const DecodeRowsArgs& args, cudaStream_t stream) {
+    if (args.rows == 0 || args.n == 0) return cudaSuccess;
+    if (args.rows > 128 || args.stages == 0 || args.x_chunk_blocks == 0) return cudaErrorInvalidValue;
+    const bool pair = args.pair != 0;
+    VXB_DECODE_DISPATCH(launch_t, args, stream);
 }
 
 }  // namespace vxb
