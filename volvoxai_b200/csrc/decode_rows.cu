@@ -109,6 +109,39 @@ __device__ __forceinline__ void stamp(unsigned long long* trace, uint32_t slot) 
 
 __device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
+// Finishes a tile parked in shared memory as int32 [rows][pitch]: thread `col_thread` of 128 takes
+// the channels col_thread, col_thread + 128, ... and of each the token rows first_row,
+// first_row + row_step, ..., so that a store instruction covers consecutive channels of one row.
+__device__ __forceinline__ void finish_parked(const DecodeRowsArgs& args, const int32_t* parked, uint32_t pitch,
+                                              const float* s_ws, const float* s_bias, const float* s_as,
+                                              uint32_t c0, uint32_t valid, uint32_t col_thread,
+                                              uint32_t first_row, uint32_t row_step) {
+    const EpilogueParams& ep = args.epi;
+    const float zero_f = __int2float_rn(ep.out_zero);
+    const float lo_f = __int2float_rn(ep.out_lo), hi_f = __int2float_rn(ep.out_hi);
+    for (uint32_t col = col_thread; col < valid; col += 128) {
+        const float wsv = s_ws[col];
+        const float bf = s_bias[col];
+        const int32_t bi = __float_as_int(bf);
+        const size_t at = (size_t)c0 + col;
+#pragma unroll 4
+        for (uint32_t mm = first_row; mm < args.rows; mm += row_step) {
+            const int32_t v = parked[mm * pitch + col];
+            const float asv = s_as[mm];
+            if (ep.mode == kEpiF32) {
+                ((float*)ep.out)[(size_t)mm * ep.ld + at] = epi_f32(v, asv, wsv, bf);
+            } else if (ep.mode == kEpiI8) {
+                const int32_t qv = (ep.fast_div != 0 && div_const_row_ok(asv))
+                    ? epi_i8_v2<true>(v + bi, asv, wsv, ep.out_scale, ep.out_rcp, zero_f, lo_f, hi_f, ep.out_zero)
+                    : epi_i8_v2<false>(v + bi, asv, wsv, ep.out_scale, ep.out_rcp, zero_f, lo_f, hi_f, ep.out_zero);
+                ((int8_t*)ep.out)[(size_t)mm * ep.ld + at] = (int8_t)qv;
+            } else {
+                ((int32_t*)ep.out)[(size_t)mm * ep.ld + at] = v;
+            }
+        }
+    }
+}
+
 template <uint32_t MT, bool PAIR>
 __global__ void __launch_bounds__(ModeCfg<PAIR>::kThreads, ModeCfg<PAIR>::kCtasPerSm)
 decode_rows_kernel(const __grid_constant__ DecodeRowsArgs args) {
@@ -360,28 +393,9 @@ decode_rows_kernel(const __grid_constant__ DecodeRowsArgs args) {
                         }
                     }
                 }
+                if (tiles == 1) break;   // every thread of the CTA finishes the parked tile below
                 epi_bar();
-                for (uint32_t col = e; col < valid; col += 128) {
-                    const float wsv = s_ws[col];
-                    const float bf = s_bias[col];
-                    const int32_t bi = __float_as_int(bf);
-                    const size_t at = (size_t)c0 + col;
-#pragma unroll 4
-                    for (uint32_t mm = 0; mm < args.rows; mm++) {
-                        const int32_t v = s_xpose[mm * pitch + col];
-                        const float asv = s_as[mm];
-                        if (ep.mode == kEpiF32) {
-                            ((float*)ep.out)[(size_t)mm * ep.ld + at] = epi_f32(v, asv, wsv, bf);
-                        } else if (ep.mode == kEpiI8) {
-                            const int32_t qv = (ep.fast_div != 0 && div_const_row_ok(asv))
-                                ? epi_i8_v2<true>(v + bi, asv, wsv, ep.out_scale, ep.out_rcp, zero_f, lo_f, hi_f, ep.out_zero)
-                                : epi_i8_v2<false>(v + bi, asv, wsv, ep.out_scale, ep.out_rcp, zero_f, lo_f, hi_f, ep.out_zero);
-                            ((int8_t*)ep.out)[(size_t)mm * ep.ld + at] = (int8_t)qv;
-                        } else {
-                            ((int32_t*)ep.out)[(size_t)mm * ep.ld + at] = v;
-                        }
-                    }
-                }
+                finish_parked(args, s_xpose, pitch, s_ws, s_bias, s_as, c0, valid, e, 0u, 1u);
             } else {
             // TMEM hands each thread one token row; the stores want one channel per lane. Each
             // 32-channel chunk is therefore transposed through shared memory: row threads park
@@ -443,6 +457,27 @@ decode_rows_kernel(const __grid_constant__ DecodeRowsArgs args) {
         }
     }
 
+    if constexpr (Cfg::kParkAll) {
+        if (tiles == 1) {
+            // The single tile is parked (or a wait gave up, and everybody skips). The loops above
+            // are over for every role, so the whole CTA finishes the tile: four times the threads
+            // of the epilogue warps alone, on what is pure latency at the end of the kernel.
+            __syncwarp();
+            __syncthreads();
+            if (!*abort_flag) {
+                pdl_wait();
+                constexpr uint32_t kGroups = ModeCfg<PAIR>::kThreads / 128;
+                const uint32_t g = threadIdx.x >> 7;
+                const uint32_t left = args.n > first_channel ? args.n - first_channel : 0u;
+                const uint32_t valid = left < args.tile_rows ? left : args.tile_rows;
+                if (g < kGroups)
+                    finish_parked(args, s_xpose, Cfg::park_pitch(args.umma_n), s_ws, s_bias, s_as, first_channel, valid,
+                                  threadIdx.x & 127u, g, kGroups);
+                if (threadIdx.x == kEpiBase) stamp(args.trace, 5);
+            }
+        }
+    }
+
     // ---------------- teardown ----------------
     __syncwarp();
     tc_fence_before();
@@ -484,8 +519,12 @@ bool configure_t(DecodeRowsArgs& args) {
     // the ring depth is a multiple of the issuer and of the producer count, so that each stage's
     // barriers are only ever waited on by one issuer and one producer, in order - a parity wait
     // on an mbarrier is only meaningful for a waiter that saw the previous phase complete.
+    // How many are wanted: a thread starts the four MMAs of a K block in some 0.4 us, and the block
+    // (tile_rows x 128 B) is due every tile_rows x 2.9 ns at this SM's share of the HBM stream; more
+    // issuers than that only lengthen the epilogue, which adds their accumulators up.
+    const uint32_t wanted = (190u + args.tile_rows - 1) / args.tile_rows;
     uint32_t issuers = 1;
-    while (2 * issuers <= max_issuers) issuers *= 2;
+    while (issuers < wanted && 2 * issuers <= max_issuers) issuers *= 2;
     for (;; issuers /= 2) {
         // activation chunk: a multiple of the issuer count, about 8 KB, at most the row's blocks
         uint32_t per = 8192u / (issuers * Cfg::kXAtom);
