@@ -97,9 +97,10 @@ def test_quantizer_special_rows(torch, ctx, golden):
 
 @pytest.mark.parametrize("k", [1, 2, 3, 7, 8, 9, 31, 32, 33, 63, 64, 65, 255, 256, 257, 320, 576,
                                1280, 1283, 2048, 4096, 5000, 14336, 20000])
-def test_quantizer_widths_vs_oracle(torch, ctx, oracle, k):
-    rng = np.random.default_rng(k)
-    x = (rng.standard_normal((9, k)) * rng.choice([1e-30, 1e-3, 1.0, 50.0, 1e20], size=(9, 1))).astype(np.float32)
+@pytest.mark.parametrize("rows", [9, 40])   # up to 32 long rows are shared by clusters of CTAs
+def test_quantizer_widths_vs_oracle(torch, ctx, oracle, k, rows):
+    rng = np.random.default_rng(k + rows)
+    x = (rng.standard_normal((rows, k)) * rng.choice([1e-30, 1e-3, 1.0, 50.0, 1e20], size=(rows, 1))).astype(np.float32)
     x[3] = 0
     if k > 4:
         x[5, k // 2] = np.nan

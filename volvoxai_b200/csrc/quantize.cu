@@ -12,6 +12,7 @@
 // A reciprocal-multiply would move half-way values across a rounding
 // boundary, so the divide is __fdiv_rn on every element.
 #include "common.cuh"
+#include <cooperative_groups.h>
 
 namespace vxb {
 
@@ -19,6 +20,7 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kMaxVecPerThread = 8;   // float4 per thread kept in registers (K <= 8192)
+constexpr uint32_t kClusterMaxRows = 32;   // up to this many rows a cluster of CTAs shares each row
 
 __device__ __forceinline__ bool nonfinite_bits(float v) {
     return (__float_as_uint(v) & 0x7f800000u) == 0x7f800000u;
@@ -156,6 +158,86 @@ quantize_rows_vec(const float* __restrict__ x, uint32_t rows, uint32_t k, int8_t
     }
 }
 
+// Few rows (decode): one row per CTA leaves most of the GPU idle and makes the kernel a chain of
+// dependent loads. Here a thread-block cluster of S CTAs shares a row: each CTA keeps its K/S
+// slice in registers (at most 8 float4 per thread), the S partial (absmax, non-finite) pairs
+// are exchanged through distributed shared memory, and every CTA quantizes its own slice.
+// grid = (S, rows), cluster = (S, 1, 1). max and OR are exact in any order, so the result is
+// bit-identical to the one-CTA kernel.
+template <int S>
+__global__ void __launch_bounds__(kThreads)
+quantize_rows_cluster(const float* __restrict__ x, uint32_t rows, uint32_t k, int8_t* __restrict__ q,
+                      uint32_t ldq, float* __restrict__ row_scales, int32_t* __restrict__ valid) {
+    namespace cg = cooperative_groups;
+    __shared__ float smem_max[kThreads / 32];
+    __shared__ int smem_bad[kThreads / 32];
+    __shared__ float peer_max[S];
+    __shared__ int peer_bad[S];
+    pdl_release();
+    pdl_wait();
+    cg::cluster_group cluster = cg::this_cluster();
+    const uint32_t rank = cluster.block_rank();
+    const uint32_t row = blockIdx.y;
+    const uint32_t nvec = k / 4, nwords = ldq / 4;
+    const uint32_t seg = (nwords + S - 1) / S;                 // words (= float4s) of this CTA's slice
+    const uint32_t w0 = rank * seg;
+    const float4* in = reinterpret_cast<const float4*>(x + (size_t)row * k);
+
+    float4 cache[kMaxVecPerThread];
+    float amax = 0.0f; int bad = 0;
+#pragma unroll
+    for (int i = 0; i < kMaxVecPerThread; i++) {
+        const uint32_t o = threadIdx.x + i * kThreads, v = w0 + o;
+        cache[i] = (o < seg && v < nvec) ? __ldg(in + v) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int i = 0; i < kMaxVecPerThread; i++) {
+        const float4 c = cache[i];
+        bad |= nonfinite_bits(c.x) | nonfinite_bits(c.y) | nonfinite_bits(c.z) | nonfinite_bits(c.w);
+        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(c.x), fabsf(c.y)), fmaxf(fabsf(c.z), fabsf(c.w))));
+    }
+    row_reduce<kThreads>(amax, bad, smem_max, smem_bad);
+    if (threadIdx.x < S) {
+        // thread p publishes this CTA's pair in CTA p's table
+        *cluster.map_shared_rank(&peer_max[rank], threadIdx.x) = amax;
+        *cluster.map_shared_rank(&peer_bad[rank], threadIdx.x) = bad;
+    }
+    cluster.sync();
+    amax = 0.0f; bad = 0;
+#pragma unroll
+    for (int p = 0; p < S; p++) { amax = fmaxf(amax, peer_max[p]); bad |= peer_bad[p]; }
+
+    float scale = amax == 0.0f ? 1.0f : __fdiv_rn(amax, 127.0f);
+    scale = fmaxf(scale, 1.1754943508222875e-38f);
+    if (rank == 0 && threadIdx.x == 0) {
+        row_scales[row] = bad ? __int_as_float(0x7fc00000) : scale;
+        if (valid) valid[row] = bad ? 0 : 1;
+    }
+    uint32_t* out = reinterpret_cast<uint32_t*>(q + (size_t)row * ldq);
+    const RowDivisor div(scale);
+    const bool fast = div.fast && !bad;
+#pragma unroll
+    for (int i = 0; i < kMaxVecPerThread; i++) {
+        const uint32_t o = threadIdx.x + i * kThreads, v = w0 + o;
+        if (o < seg && v < nwords)
+            out[v] = (v < nvec && !bad) ? (fast ? pack4t<true>(cache[i], div) : pack4t<false>(cache[i], div)) : 0u;
+    }
+}
+
+template <int S>
+cudaError_t launch_cluster(const float* x, uint32_t rows, uint32_t k, int8_t* q, uint32_t ldq,
+                           float* row_scales, int32_t* valid, cudaStream_t stream) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(S, rows); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = 0; cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = S; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 2;
+    return cudaLaunchKernelEx(&cfg, quantize_rows_cluster<S>, x, rows, k, q, ldq, row_scales, valid);
+}
+
 // Any k / alignment: one warp per row, scalar accesses.
 __global__ void __launch_bounds__(kThreads)
 quantize_rows_scalar(const float* __restrict__ x, uint32_t rows, uint32_t k, int8_t* __restrict__ q,
@@ -250,6 +332,13 @@ cudaError_t launch_quantize_rows(const float* x, uint32_t rows, uint32_t k, int8
         const uint32_t grid = (rows + kThreads / 32 - 1) / (kThreads / 32);
         return launch_pdl(quantize_rows_scalar, dim3(grid), dim3(kThreads), 0, stream,
                           x, rows, k, q, ldq, row_scales, valid);
+    }
+    // Few long rows: a cluster of 2..8 CTAs per row (each thread then holds one or two float4)
+    if (rows <= kClusterMaxRows && ldq / 4 >= 2u * kThreads && ldq / 4 <= 8u * kThreads * kMaxVecPerThread) {
+        const uint32_t per = (ldq / 4 + kThreads - 1) / kThreads;   // float4 per thread with one CTA
+        if (per >= 8) return launch_cluster<8>(x, rows, k, q, ldq, row_scales, valid, stream);
+        if (per >= 4) return launch_cluster<4>(x, rows, k, q, ldq, row_scales, valid, stream);
+        return launch_cluster<2>(x, rows, k, q, ldq, row_scales, valid, stream);
     }
     // Threads per row grow with K so each thread keeps at most 8 float4 in registers.
     if (k <= 256) return launch_vec<8>(x, rows, k, q, ldq, row_scales, valid, stream);
