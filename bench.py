@@ -179,6 +179,48 @@ def cpu_reference_run(rows, k, n, steps, warmup, budget_s=None, seed=0):
             "steps": len(times), "cores": threads, "kind": kind, "sample": label}
 
 
+def cpu_reference_variants(k, n, seed=0, rows=64, budget_s=2.5):
+    """The other CPU figures beside the headline baseline, each on a `rows`-row sample and a
+    bounded time: the reference's two routes (R1 = vx_packed_linear_forward on W8/G128 words
+    whose group scales repeat the channel scale, fp32 output; R2 = prepare +
+    vx_qlinear_i8u8_packed, int8 output) at one thread and at every host thread."""
+    from oracle.bindings import Ref
+    if not Ref.available():
+        return None
+    ref = Ref()
+    cores = os.cpu_count() or 1
+    x = wl.gemm_activations(rows, k, seed)
+    w, ws = wl.gemm_weights(n, k, seed)
+    words = wl.pack_w8_words(w)
+    gsc = wl.group_scales(ws, k, 128)
+    packed = ref.pack_q8(w)
+    zeros = np.zeros(n, np.int32)
+    q = np.zeros((rows, k), np.int8); scales = np.zeros(rows, np.float32)
+    out8 = np.zeros((rows, n), np.int8); y = np.zeros((rows, n), np.float32)
+    ops = 2.0 * rows * k * n
+
+    def r1():
+        ref.packed_linear(x, words, gsc, 128, None, y=y)
+
+    def r2():
+        ref.prepare_rows(x, q, scales)
+        ref.qlinear_packed(q, packed, np.int8, n, zeros, ws, zeros, float(scales.mean()), 0, 0.05, 0, out=out8)
+
+    res = {"rows": rows, "isa": ref.isa()}
+    for threads in (1, cores):
+        got = ref.threads_enter(threads)
+        for name, fn in (("r1_packed_linear_forward", r1), ("r2_prepare_qlinear_packed", r2)):
+            fn()
+            t0 = time.perf_counter(); cnt = 0
+            while True:
+                fn(); cnt += 1
+                if time.perf_counter() - t0 > budget_s or cnt >= 200:
+                    break
+            res[f"{name}_tops_t{got if got > 0 else 1}"] = ops * cnt / (time.perf_counter() - t0) / 1e12
+        ref.threads_leave()
+    return res
+
+
 def reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -460,6 +502,8 @@ def gpu_arm(args):
         r = cpu_reference_run(min(m, args.cpu_rows), k, n, steps=1000, warmup=1, budget_s=args.cpu_seconds)
         line["cpu_baseline"] = {"value": r["tops"], "unit": "TOPS", "cores": r["cores"],
                                 "kind": r["kind"], "sample": r["sample"] + f", {r['steps']} repeats"}
+        if not args.no_extras:
+            line["cpu_baseline"]["routes"] = cpu_reference_variants(k, n)
     elif rank == 0:
         line["cpu_baseline"] = None
     if rank == 0 and world == 1 and not args.no_extras:
