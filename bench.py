@@ -404,6 +404,7 @@ def gpu_arm(args):
     launches = w8a8.launch_count() - launches0
     ctx.synchronize()
 
+    step_route = w8a8.last_route()
     ops = 2.0 * m * k * n
     ms_per_step = total_ms / args.steps
     value = ops / (ms_per_step * 1e-3) / 1e12
@@ -436,7 +437,7 @@ def gpu_arm(args):
     roofline = {
         "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
         "frac": achieved / peak, "traffic": None,
-        "kernel": "gemm_i8_tcgen05_kernel", "kernel_ms": gemm_ms,
+        "kernel": "gemm_i8_pair_kernel" if "pair" in step_route else "gemm_i8_tcgen05_kernel", "kernel_ms": gemm_ms,
         "peak_source": f"2 x bf16_tflops (cuBLAS bf16 burst, {peaks['_source']}) as the dense int8 rate",
         "i8_probe_tops": i8_probe, "frac_of_i8_probe": achieved / i8_probe,
         "frac_of_nominal_4500": achieved / NOMINAL_I8_TOPS,

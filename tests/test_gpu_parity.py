@@ -38,7 +38,7 @@ def rel_err(y, ref):
     return float(np.abs(y[ok].astype(np.float64) - ref[ok]).max() / max(rms, 1e-30)) if ok.any() else 0.0
 
 
-ROUTES = {"gemv": 1, "tcgen05": 2, "simt": 3, "decode": 4, "streamk": 5}
+ROUTES = {"gemv": 1, "tcgen05": 2, "simt": 3, "decode": 4, "streamk": 5, "pair": 6}
 
 
 def run_case(torch, ctx, oracle, case, routes, bias_i32=None, out_zero=0):
@@ -122,7 +122,7 @@ def test_config1_all_routes_and_golden(torch, ctx, oracle, golden):
     """M64 K576 N1536, the reference's CPU-runnable case."""
     from volvoxai_b200 import w8a8
     c1 = wl.single_linear()
-    run_case(torch, ctx, oracle, c1, ["simt", "tcgen05"])
+    run_case(torch, ctx, oracle, c1, ["simt", "tcgen05", "pair"])
     weight = w8a8.Weight.from_i8(ctx, c1["w"], c1["ws"], bias_f32=c1["bias"])
     xd = dev(torch, c1["x"])
     acc, q, s = ctx.linear_acc_i32(weight, xd, want_q=True)
@@ -166,7 +166,7 @@ def test_decode_route_up_to_128_rows(torch, ctx, oracle, rows, k, n):
             "bias": rng.standard_normal(n).astype(np.float32)}
     case["x"][1] = 0
     case["x"][rows - 2, k // 3] = np.inf
-    run_case(torch, ctx, oracle, case, ["decode", "streamk", "tcgen05"],
+    run_case(torch, ctx, oracle, case, ["decode", "streamk", "tcgen05", "pair"],
              bias_i32=rng.integers(-300, 300, size=n).astype(np.int32), out_zero=7)
 
 
@@ -200,7 +200,7 @@ def test_tile_boundaries_tcgen05(torch, ctx, oracle, rows, k, n):
             "bias": rng.standard_normal(n).astype(np.float32)}
     case["x"][rows // 2] = 0
     case["x"][rows - 1, 0] = np.nan
-    run_case(torch, ctx, oracle, case, ["tcgen05", "simt"] if rows * k * n < 5e8 else ["tcgen05"],
+    run_case(torch, ctx, oracle, case, ["tcgen05", "pair", "simt"] if rows * k * n < 5e8 else ["tcgen05", "pair"],
              bias_i32=rng.integers(-1000, 1000, size=n).astype(np.int32), out_zero=5)
 
 
@@ -210,7 +210,7 @@ def test_extreme_codes_do_not_overflow(torch, ctx, oracle):
     x = np.full((rows, k), 3.0, np.float32)
     x[::2] *= -1
     case = {"x": x, "w": np.full((n, k), -128, np.int8), "ws": np.full(n, 0.01, np.float32), "bias": None}
-    run_case(torch, ctx, oracle, case, ["tcgen05"])
+    run_case(torch, ctx, oracle, case, ["tcgen05", "pair"])
     case["x"] = x[:8]
     run_case(torch, ctx, oracle, case, ["gemv", "decode", "streamk"])
 

@@ -13,6 +13,7 @@ LIB_PATH = os.path.join(PKG, "libvxb200.so")
 DT_U8, DT_I8 = 5, 6
 OP_PACKED_LINEAR = 1036
 ROUTE_AUTO, ROUTE_GEMV, ROUTE_TCGEN05, ROUTE_SIMT, ROUTE_DECODE, ROUTE_DECODE_STREAMK = 0, 1, 2, 3, 4, 5
+ROUTE_TCGEN05_PAIR = 6
 
 # Every symbol include/vxb200_w8a8.h declares.
 EXPORTS = [

@@ -103,6 +103,7 @@ struct VxbContext {
     unsigned long long* trace = nullptr;   // caller's device buffer for decode-kernel time stamps, or null
     int* status_host = nullptr;   // pinned mirror
     bool tcgen05_ready = false;
+    bool pair_ready = false;
     // optional per-kernel timing (event pairs on the launching stream)
     // vxb_linear_host: upload / download streams and their events
     cudaStream_t copy_in = nullptr, copy_out = nullptr;
@@ -211,6 +212,7 @@ Plan choose_route(const VxbContext* ctx, const VxbWeight* w, uint32_t rows, int 
     if (requested == VXB_ROUTE_GEMV) return {VXB_ROUTE_GEMV, "gemv-dp4a"};
     if (requested == VXB_ROUTE_SIMT) return {VXB_ROUTE_SIMT, "simt-dp4a"};
     if (requested == VXB_ROUTE_TCGEN05) return {VXB_ROUTE_TCGEN05, "tcgen05-i8"};
+    if (requested == VXB_ROUTE_TCGEN05_PAIR) return {VXB_ROUTE_TCGEN05_PAIR, "tcgen05-pair-i8"};
     if (requested == VXB_ROUTE_DECODE) return {VXB_ROUTE_DECODE, "decode-rows-tcgen05-i8"};
     if (requested == VXB_ROUTE_DECODE_STREAMK) return {VXB_ROUTE_DECODE_STREAMK, "decode-streamk-tcgen05-i8"};
     (void)ctx; (void)w;
@@ -221,7 +223,8 @@ Plan choose_route(const VxbContext* ctx, const VxbWeight* w, uint32_t rows, int 
 // int32 GEMM + epilogue over already-quantized activations q [rows, kpad].
 int run_gemm(VxbContext* ctx, const VxbWeight* w, const int8_t* q, uint32_t rows,
              const EpilogueParams& epi, int requested, const char* prefix) {
-    const Plan plan = choose_route(ctx, w, rows, requested);
+    Plan plan = choose_route(ctx, w, rows, requested);
+    const bool requested_auto = requested == VXB_ROUTE_AUTO;
     ProfileScope scope(ctx, 1);
     if (plan.route == VXB_ROUTE_GEMV) {
         if (rows > 32) return fail(0, "gemv route needs rows <= 32 (got %u)", rows);
@@ -268,11 +271,27 @@ int run_gemm(VxbContext* ctx, const VxbWeight* w, const int8_t* q, uint32_t rows
             CUDA_TRY(gemm_tcgen05_prepare(), 0);
             ctx->tcgen05_ready = true;
         }
+        if (!ctx->pair_ready) {
+            CUDA_TRY(gemm_pair_prepare(), 0);
+            ctx->pair_ready = true;
+        }
         GemmTcgen05Args a;
         if (!encode_i8_rows(&a.tmap_a, q, rows, w->kpad, 128)) return fail(0, "cuTensorMapEncodeTiled failed for activations");
-        a.tmap_b = w->tmap_b;
         a.rows = rows; a.n = w->d_out; a.kpad = w->kpad; a.epi = epi; a.status = ctx->status;
-        CUDA_TRY(launch_gemm_tcgen05(a, ctx->sm_count, ctx->stream), -1);
+        // pairs of CTAs on 256 x 256 tiles once there are at least two waves of 128 x 256 tiles
+        const uint32_t tiles = ((rows + 127) / 128) * ((w->d_out + 255) / 256);
+        const bool pair = gemm_pair_clusters() > 0 && epi.n_peers == 0 &&
+                          (plan.route == VXB_ROUTE_TCGEN05_PAIR ||
+                           (requested_auto && tiles >= 2u * (uint32_t)ctx->sm_count));
+        if (plan.route == VXB_ROUTE_TCGEN05_PAIR && !pair) return fail(0, "no co-resident CTA pairs on this device");
+        if (pair) {
+            a.tmap_b = w->tmap_w128;   // each CTA of a pair loads half of the tile's weight rows
+            CUDA_TRY(launch_gemm_pair(a, ctx->stream), -1);
+            plan.name = "tcgen05-pair-i8";
+        } else {
+            a.tmap_b = w->tmap_b;
+            CUDA_TRY(launch_gemm_tcgen05(a, ctx->sm_count, ctx->stream), -1);
+        }
     }
     count_launch();
     const char* tail = epi.mode == kEpiAcc ? "acc" : epi.mode == kEpiF32 ? "e1" : "e2";

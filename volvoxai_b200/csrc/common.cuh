@@ -172,6 +172,10 @@ struct GemmTcgen05Args {
 };
 cudaError_t launch_gemm_tcgen05(const GemmTcgen05Args& args, int sm_count, cudaStream_t stream);
 cudaError_t gemm_tcgen05_prepare();  // one-time func attribute set-up
+// The same GEMM by pairs of CTAs (cta_group::2) on 256 x 256 tiles; tmap_b has a box of 128 rows.
+cudaError_t gemm_pair_prepare();    // func attribute + how many pairs can be resident
+int gemm_pair_clusters();           // 0: pairs cannot run on this device
+cudaError_t launch_gemm_pair(const GemmTcgen05Args& args, cudaStream_t stream);
 
 // K3: decode kernel in which every CTA owns whole output channels (rows <= 128).
 // tile_rows / tiles_per_cta come from decode_rows_plan(); tmap_w has a box of tile_rows rows,
