@@ -102,8 +102,14 @@ VXB_API int vxb_weight_create_i8(VxbContext* ctx, const int8_t* weight, const fl
 /* Same, from PackedLinear W8 storage (docs/packed-linear-design.md:24-41;
  * native/src/kernels/llm_ops.h:22-32): I32 words [d_out, ceil(d_in/4)] in
  * offset-binary (int8 = byte ^ 0x80, padding bytes 0x80) and fp32 group scales
- * [d_out, ceil(d_in/group_size)].  Declines (0) unless every group scale of a
- * row is identical (per-channel mode) and group_size is 32/64/128/256. */
+ * [d_out, ceil(d_in/group_size)], group_size 32/64/128/256, all scales positive and
+ * finite (else declined, 0).  When every group scale of a row is identical the weight is
+ * a per-channel weight like the above.  Otherwise it keeps its group scales and is served
+ * by the grouped-scale kernel, which follows the reference's arithmetic group by group
+ * (an exact integer dot per group, fp32 accumulation in ascending group order,
+ * native/src/kernels/packed_linear_ops.inc:1493-1531): such a weight gives fp32 output
+ * (vxb_linear_f32 and the PackedLinear host entries) on the automatic route only; the
+ * int8, int32 and explicit-route entries decline it. */
 VXB_API int vxb_weight_create_w8_words(VxbContext* ctx, const int32_t* words, const float* group_scales,
                                const float* bias_f32, uint32_t d_out, uint32_t d_in,
                                uint32_t group_size, VxbWeight** out);

@@ -233,7 +233,7 @@ def test_output_row_stride(torch, ctx, oracle):
 
 def test_w8_words_loader_matches_i8_loader(torch, ctx, oracle, golden):
     """PackedLinear storage (offset-binary words + constant group scales) -> same results;
-    differing group scales are declined."""
+    differing group scales select the grouped-scale kernel (fp32 output only)."""
     from volvoxai_b200 import w8a8
     c = wl.single_linear(rows=37, k=300, n=50, seed=9)
     words = wl.pack_w8_words(c["w"])
@@ -244,10 +244,47 @@ def test_w8_words_loader_matches_i8_loader(torch, ctx, oracle, golden):
     ctx.synchronize()
     assert np.array_equal(acc.cpu().numpy(), ref["acc"])
     gs[3, 1] *= 1.5
+    wg = w8a8.Weight.from_w8_words(ctx, words, gs, 300, 128, bias_f32=c["bias"])
+    y = ctx.linear_f32(wg, dev(torch, c["x"]))
+    ctx.synchronize()
+    assert "grouped" in w8a8.last_route()
+    want = oracle.packed_linear_w8_grouped(c["x"], words, gs, 128, c["bias"])
+    assert np.array_equal(y.cpu().numpy().view(np.uint32), want.view(np.uint32))
+    for call in (lambda: ctx.linear_acc_i32(wg, dev(torch, c["x"])),
+                 lambda: ctx.linear_i8(wg, dev(torch, c["x"]), 0.05),
+                 lambda: ctx.linear_f32(wg, dev(torch, c["x"]), route=ROUTES["tcgen05"])):
+        with pytest.raises(w8a8.W8A8Error) as e:
+            call()
+        assert e.value.code == 0
+    gs[5, 0] = 0.0
     with pytest.raises(w8a8.W8A8Error) as e:
         w8a8.Weight.from_w8_words(ctx, words, gs, 300, 128)
     assert e.value.code == 0
     wa.close()
+    wg.close()
+
+
+@pytest.mark.parametrize("group", [32, 64, 128, 256])
+@pytest.mark.parametrize("rows,k,n", [(1, 300, 50), (3, 576, 192), (70, 1283, 130), (9, 4096, 520)])
+def test_grouped_scales_vs_oracle(torch, ctx, oracle, group, rows, k, n):
+    """The reference's storage groups with genuinely different scales: bit-equal to the oracle's
+    grouped forward (pinned to the reference's CPU forward), NaN rows included."""
+    from volvoxai_b200 import w8a8
+    rng = np.random.default_rng(group + rows + k + n)
+    c = wl.single_linear(rows=rows, k=k, n=n, seed=group + rows)
+    words = wl.pack_w8_words(c["w"])
+    groups = (k + group - 1) // group
+    gs = (c["ws"][:, None] * rng.uniform(0.5, 2.0, size=(n, groups))).astype(np.float32)
+    x = c["x"].copy()
+    if rows > 2:
+        x[1] = 0
+        x[2, k // 2] = np.nan
+    wg = w8a8.Weight.from_w8_words(ctx, words, gs, k, group, bias_f32=c["bias"])
+    y = ctx.linear_f32(wg, dev(torch, x)).cpu().numpy()
+    want = oracle.packed_linear_w8_grouped(x, words, gs, group, c["bias"])
+    assert np.array_equal(np.isnan(y), np.isnan(want))
+    assert np.array_equal(y[~np.isnan(want)].view(np.uint32), want[~np.isnan(want)].view(np.uint32))
+    wg.close()
 
 
 # ---- static-activation QLinear (R2) ---------------------------------------------------------
@@ -309,21 +346,18 @@ def test_host_qlinear_entry(torch, oracle, golden):
 
 
 @pytest.mark.parametrize("tag,group", [("r1_5x257x7_g128", 128), ("r1_4x64x19_g64", 64)])
-def test_host_packed_linear_entry_declines_grouped_scales(torch, golden, tag, group):
-    """The golden R1 packages carry genuinely different group scales: declined (0),
-    output untouched, so the reference's own route keeps serving them."""
+def test_host_packed_linear_entry_grouped_scales(torch, golden, tag, group):
+    """The golden R1 packages carry genuinely different group scales: served by the
+    grouped-scale kernel, bit-equal to the reference's own forward."""
     from volvoxai_b200 import w8a8
     x = golden[tag + "_x"]
     y = np.full((x.shape[0], golden[tag + "_words"].shape[0]), 4.5, np.float32)
     rc = w8a8.packed_linear(x, golden[tag + "_words"], golden[tag + "_scales"], golden[tag + "_bias"], y,
                             group_size=group)
-    if golden[tag + "_scales"].shape[1] > 1:
-        assert rc == 0 and (y == 4.5).all()
-    else:
-        assert rc == 1
-        want = golden[tag + "_y_c"]
-        assert np.array_equal(np.isnan(y), np.isnan(want))
-        assert np.array_equal(y[~np.isnan(want)].view(np.uint32), want[~np.isnan(want)].view(np.uint32))
+    assert rc == 1
+    want = golden[tag + "_y_c"]
+    assert np.array_equal(np.isnan(y), np.isnan(want))
+    assert np.array_equal(y[~np.isnan(want)].view(np.uint32), want[~np.isnan(want)].view(np.uint32))
     w8a8.host_cache_clear()
 
 

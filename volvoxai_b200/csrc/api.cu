@@ -127,6 +127,9 @@ struct VxbWeight {
     bool has_tmap = false;
     uint64_t bytes = 0;
     float ws_min = 0.0f, ws_max = 0.0f;  // range of the per-channel scales
+    // grouped scales (storage groups of the reference's PackedLinear): 0 = per-channel
+    uint32_t group = 0, groups = 0;
+    float* gscales = nullptr;  // [d_out, groups]
 };
 
 namespace {
@@ -226,7 +229,15 @@ int run_gemm(VxbContext* ctx, const VxbWeight* w, const int8_t* q, uint32_t rows
     Plan plan = choose_route(ctx, w, rows, requested);
     const bool requested_auto = requested == VXB_ROUTE_AUTO;
     ProfileScope scope(ctx, 1);
-    if (plan.route == VXB_ROUTE_GEMV) {
+    if (w->group) {
+        // differing group scales: exact per-group arithmetic, fp32 output only
+        if (!requested_auto && requested != VXB_ROUTE_SIMT) return fail(0, "weights with grouped scales take the automatic route only");
+        if (epi.mode != kEpiF32) return fail(0, "weights with grouped scales produce fp32 output only");
+        EpilogueParams ge = epi;
+        ge.gscales = w->gscales; ge.group = w->group; ge.groups = w->groups;
+        CUDA_TRY(launch_gemm_grouped(q, rows, w->w, w->d_out, w->kpad, ge, ctx->stream), -1);
+        plan.name = "dp4a-grouped";
+    } else if (plan.route == VXB_ROUTE_GEMV) {
         if (rows > 32) return fail(0, "gemv route needs rows <= 32 (got %u)", rows);
         CUDA_TRY(launch_gemv(q, rows, w->w, w->d_out, w->kpad, epi, ctx->sm_count, ctx->stream), -1);
     } else if (plan.route == VXB_ROUTE_SIMT) {
@@ -428,12 +439,14 @@ int vxb_weight_create_w8_words(VxbContext* ctx, const int32_t* words, const floa
     if ((uint64_t)d_in * 127u * 128u > 2147483647ull) return fail(0, "d_in %u can overflow the int32 accumulator", d_in);
     const uint32_t groups = (d_in + group_size - 1) / group_size, row_words = (d_in + 3) / 4;
     std::vector<float> ws(d_out);
+    bool grouped = false;   // some channel's groups differ: the grouped-scale kernel serves this weight
     for (uint32_t n = 0; n < d_out; n++) {
         const float s = group_scales[(size_t)n * groups];
-        if (!valid_scale(s)) return fail(0, "group scale of channel %u is not positive and finite", n);
-        for (uint32_t g = 1; g < groups; g++)
-            if (memcmp(&group_scales[(size_t)n * groups + g], &s, 4) != 0)
-                return fail(0, "channel %u has differing group scales; only per-channel-constant scales are admitted", n);
+        for (uint32_t g = 0; g < groups; g++) {
+            const float sg = group_scales[(size_t)n * groups + g];
+            if (!valid_scale(sg)) return fail(0, "scale of channel %u, group %u is not positive and finite", n, g);
+            if (memcmp(&sg, &s, 4) != 0) grouped = true;
+        }
         ws[n] = s;
         // canonical padding: unused bytes of the final word hold the encoded zero 0x80
         const uint8_t* bytes = (const uint8_t*)(words + (size_t)n * row_words);
@@ -450,6 +463,13 @@ int vxb_weight_create_w8_words(VxbContext* ctx, const int32_t* words, const floa
     else if (cudaMemcpyAsync(staging.ptr, words, src_bytes, cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess)
         rc = fail(-1, "weight upload failed");
     else rc = finish_weight(ctx, w, (const uint8_t*)staging.ptr, row_words * 4, 0x80u, ws.data(), bias_f32, nullptr);
+    if (rc == 1 && grouped) {
+        const size_t gbytes = (size_t)d_out * groups * 4;
+        if (cudaMalloc(&w->gscales, gbytes) != cudaSuccess) rc = fail(0, "group scale allocation failed");
+        else if (cudaMemcpyAsync(w->gscales, group_scales, gbytes, cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess)
+            rc = fail(-1, "group scale upload failed");
+        else { w->group = group_size; w->groups = groups; w->bytes += gbytes; }
+    }
     cudaStreamSynchronize(ctx->stream);
     staging.release();
     if (rc != 1) { vxb_weight_destroy(w); return rc; }
@@ -465,6 +485,7 @@ void vxb_weight_destroy(VxbWeight* w) {
     if (w->bias_f32) cudaFree(w->bias_f32);
     if (w->bias_i32) cudaFree(w->bias_i32);
     if (w->wsum) cudaFree(w->wsum);
+    if (w->gscales) cudaFree(w->gscales);
     delete w;
 }
 uint32_t vxb_weight_d_in(const VxbWeight* w) { return w ? w->d_in : 0; }

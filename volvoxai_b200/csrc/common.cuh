@@ -32,6 +32,8 @@ struct EpilogueParams {
     uint32_t ld;              // output row stride in elements
     // fused all-gather (large-M kernel only): the same [rows, ld] window in up to 7 peer GPUs'
     // buffers (peer-mapped addresses); every output tile is also stored there
+    const float* gscales;   // grouped weight scales [n, groups] (R1 storage groups), or null
+    uint32_t group, groups;  // K bytes per group (32/64/128/256), groups per channel; 0 = per-channel scales
     uint32_t n_peers;
     void* peer_out[7];
 };
@@ -128,6 +130,11 @@ __device__ __forceinline__ void epi_store(const EpilogueParams& p, uint32_t row,
 }
 
 // ---- launchers implemented in the .cu files -------------------------------
+
+// Grouped weight scales (the reference's PackedLinear storage groups): one thread per output,
+// an exact integer dot per group, fp32 accumulation in ascending group order. fp32 output only.
+cudaError_t launch_gemm_grouped(const int8_t* q, uint32_t rows, const int8_t* w, uint32_t n, uint32_t kpad,
+                                const EpilogueParams& epi, cudaStream_t stream);
 
 // K1: per-token absmax + quantize. q rows have stride ldq (multiple of 16 when
 // the vector path is to be used); bytes [k, ldq) are zeroed.

@@ -144,7 +144,75 @@ __global__ void gemm_simt_kernel(const int8_t* __restrict__ q, uint32_t rows,
     epi_store(epi, row, col, acc);
 }
 
+// ---- grouped weight scales ---------------------------------------------------------------
+// y[m,n] = (sum over groups g, ascending, of f32(dot_g) * f32(as[m] * ws[n,g])) + bias[n], every
+// product and sum rounded on its own: the arithmetic of the reference's packed-linear column
+// loop (native/src/kernels/packed_linear_ops.inc:1493-1531), which the tensor-core kernels
+// cannot reproduce from one int32 accumulator per output. One thread per channel and MR
+// token rows (each weight word is loaded once for the MR rows).
+template <int MR>
+__global__ void __launch_bounds__(128)
+gemm_grouped_kernel(const int8_t* __restrict__ q, uint32_t rows, const int8_t* __restrict__ w,
+                    uint32_t n, uint32_t kpad, EpilogueParams epi) {
+    const uint32_t col = blockIdx.x * blockDim.x + threadIdx.x;
+    const uint32_t row0 = blockIdx.y * MR;
+    if (col >= n) return;
+    const uint4* b = reinterpret_cast<const uint4*>(w + (size_t)col * kpad);
+    const uint4* a[MR];
+    float as[MR], sum[MR];
+#pragma unroll
+    for (int m = 0; m < MR; m++) {
+        const uint32_t r = row0 + m < rows ? row0 + m : rows - 1;
+        a[m] = reinterpret_cast<const uint4*>(q + (size_t)r * kpad);
+        as[m] = epi.row_scales[r];
+        sum[m] = 0.0f;
+    }
+    const uint32_t gvec = epi.group / 16, kvec = kpad / 16;
+    for (uint32_t g = 0, v0 = 0; g < epi.groups; g++, v0 += gvec) {
+        const uint32_t v1 = v0 + gvec < kvec ? v0 + gvec : kvec;
+        int dot[MR];
+#pragma unroll
+        for (int m = 0; m < MR; m++) dot[m] = 0;
+        for (uint32_t v = v0; v < v1; v++) {
+            const uint4 wv = __ldg(b + v);
+#pragma unroll
+            for (int m = 0; m < MR; m++) {
+                const uint4 av = __ldg(a[m] + v);
+                int s = dot[m];
+                s = dp4a_s8(av.x, wv.x, s); s = dp4a_s8(av.y, wv.y, s);
+                s = dp4a_s8(av.z, wv.z, s); s = dp4a_s8(av.w, wv.w, s);
+                dot[m] = s;
+            }
+        }
+        const float gs = __ldg(epi.gscales + (size_t)col * epi.groups + g);
+#pragma unroll
+        for (int m = 0; m < MR; m++)
+            sum[m] = __fadd_rn(sum[m], __fmul_rn(__int2float_rn(dot[m]), __fmul_rn(as[m], gs)));
+    }
+    const float bias = epi.bias_f32 ? __ldg(epi.bias_f32 + col) : 0.0f;
+#pragma unroll
+    for (int m = 0; m < MR; m++)
+        if (row0 + m < rows) ((float*)epi.out)[(size_t)(row0 + m) * epi.ld + col] = __fadd_rn(sum[m], bias);
+}
+
 }  // namespace
+
+cudaError_t launch_gemm_grouped(const int8_t* q, uint32_t rows, const int8_t* w, uint32_t n, uint32_t kpad,
+                                const EpilogueParams& epi, cudaStream_t stream) {
+    if (rows == 0 || n == 0) return cudaSuccess;
+    if (epi.mode != kEpiF32 || !epi.gscales || epi.group % 16 != 0 || !epi.groups) return cudaErrorInvalidValue;
+    constexpr int kMR = 4;
+    for (uint32_t r0 = 0; r0 < rows; r0 += 65535u * kMR) {
+        const uint32_t cnt = rows - r0 < 65535u * kMR ? rows - r0 : 65535u * kMR;
+        EpilogueParams e = epi;
+        e.row_scales = epi.row_scales + r0;
+        e.out = (uint8_t*)epi.out + (size_t)r0 * epi.ld * 4;
+        dim3 grid((n + 127) / 128, (cnt + kMR - 1) / kMR);
+        if (cnt == 1) gemm_grouped_kernel<1><<<dim3(grid.x, 1), 128, 0, stream>>>(q + (size_t)r0 * kpad, cnt, w, n, kpad, e);
+        else gemm_grouped_kernel<kMR><<<grid, 128, 0, stream>>>(q + (size_t)r0 * kpad, cnt, w, n, kpad, e);
+    }
+    return cudaGetLastError();
+}
 
 cudaError_t launch_gemv(const int8_t* q, uint32_t rows, const int8_t* w, uint32_t n, uint32_t kpad,
                         const EpilogueParams& epi, int sm_count, cudaStream_t stream) {
