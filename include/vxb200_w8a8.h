@@ -174,6 +174,25 @@ VXB_API int vxb_linear_i8_gather(VxbContext* ctx, const VxbWeight* w, const floa
                          float out_scale, int32_t out_zero, int8_t* y, uint32_t ldy,
                          void* const* peer_y, uint32_t n_peers);
 
+/* ---- boundary of a static W8A8 island (device pointers) --------------------------------
+ * QuantizeLinear, DequantizeLinear and RequantizeLinear with scalar (per-tensor) metadata,
+ * the arithmetic of the reference's CPU authority:
+ *   quantize    NaN -> zero point; f32(x / scale) + f32(zero), saturated, ties to even
+ *               (native/src/kernels/quantize_linear_ops.inc:155-170,230-254)
+ *   dequantize  f32((x - zero) * scale), rounded once (:9-16,95-122)
+ *   requantize  f32(f32(x - in_zero) * f32(in_scale / out_scale)) + f32(out_zero), NaN -> out_zero,
+ *               saturated, ties to even (portable_inference_kernels.inc:2437-2463)
+ * Dtypes are VXB_DTYPE_I8 / VXB_DTYPE_U8; scales must be positive and finite (the reference's
+ * dequantizer also takes other scales: those are declined here), zero points inside their
+ * dtype.  Declined (0) before anything is launched otherwise. */
+VXB_API int vxb_quantize_linear_device(VxbContext* ctx, const float* x, uint64_t elements, float scale,
+                               int32_t zero_point, uint32_t output_dtype, void* out);
+VXB_API int vxb_dequantize_linear_device(VxbContext* ctx, const void* x, uint64_t elements, float scale,
+                                 int32_t zero_point, uint32_t input_dtype, float* out);
+VXB_API int vxb_requantize_linear_device(VxbContext* ctx, const void* x, uint64_t elements, float input_scale,
+                                 int32_t input_zero_point, float output_scale, int32_t output_zero_point,
+                                 uint32_t input_dtype, uint32_t output_dtype, void* out);
+
 /* Prepared-activation form, the counterpart of the reference's prepared path
  * (x[4] prepared words / x[5] row scales, native/src/backends/cuda/host/
  * cuda_graph_llm_host.inc:15-107): the caller quantized the rows itself with
@@ -316,6 +335,21 @@ typedef struct VxbLLMOpArgs {
  * with per-channel-constant group scales; declines (0) everything else so the
  * reference's own routes keep serving W2/3/4 and A16/F32.  A window must cover
  * whole rows. */
+/* The same three operators with HOST pointers: the slots quantize_typed_f32_i8u8,
+ * dequantize_typed_i8u8_f32 and requantize_linear_i8u8 of VxW8A8Ops
+ * (native/src/backends/w8a8_device_ops.h:28-31,111-113), signatures of
+ * cuda_graph_quantize_typed_f32_i8u8 / cuda_graph_dequantize_typed_i8u8_f32 /
+ * cuda_graph_requantize_linear_i8u8 (native/src/backends/cuda_engine.h:627-644).
+ * 1 = handled, 0 = declined before the output was touched, -1 = failed after submission. */
+VXB_API int vxb_quantize_typed_f32_i8u8(const float* input, uint32_t elements, void* output, float output_scale,
+                                int32_t output_zero_point, uint32_t output_dtype);
+VXB_API int vxb_dequantize_typed_i8u8_f32(const void* input, uint32_t elements, float input_scale,
+                                  int32_t input_zero_point, uint32_t input_dtype, float* output);
+VXB_API int vxb_requantize_linear_i8u8(const void* input, uint32_t input_elements, void* output,
+                               uint32_t output_elements, float input_scale, int32_t input_zero_point,
+                               float output_scale, int32_t output_zero_point, uint32_t input_dtype,
+                               uint32_t output_dtype);
+
 VXB_API int vxb_cuda_graph_llm_f32(const VxbLLMOpArgs* args);
 
 /* Drop-in for the scalar decode entry cuda_graph_packed_linear_decode_f32

@@ -159,6 +159,29 @@ class Oracle:
             C.c_int(1 if out_unsigned else 0))
         return out if ok else None
 
+    def quantize_linear(self, x, scale, zero, out_unsigned=False):
+        x = _f32(x).reshape(-1)
+        out = np.zeros(x.size, np.uint8 if out_unsigned else np.int8)
+        ok = self.lib.vxo_quantize_linear(_p(x, C.c_float), C.c_uint64(x.size), C.c_float(scale), C.c_int32(zero),
+                                          C.c_int(1 if out_unsigned else 0), out.ctypes.data_as(C.c_void_p))
+        return out if ok else None
+
+    def dequantize_linear(self, x, scale, zero):
+        x = np.ascontiguousarray(x).reshape(-1)
+        out = np.zeros(x.size, np.float32)
+        self.lib.vxo_dequantize_linear(x.ctypes.data_as(C.c_void_p), C.c_uint64(x.size), C.c_float(scale),
+                                       C.c_int32(zero), C.c_int(1 if x.dtype == np.uint8 else 0), _p(out, C.c_float))
+        return out
+
+    def requantize_linear(self, x, in_scale, in_zero, out_scale, out_zero, out_unsigned=False):
+        x = np.ascontiguousarray(x).reshape(-1)
+        out = np.zeros(x.size, np.uint8 if out_unsigned else np.int8)
+        ok = self.lib.vxo_requantize_linear(x.ctypes.data_as(C.c_void_p), out.ctypes.data_as(C.c_void_p),
+                                            C.c_uint64(x.size), C.c_float(in_scale), C.c_int32(in_zero),
+                                            C.c_float(out_scale), C.c_int32(out_zero),
+                                            C.c_int(1 if x.dtype == np.uint8 else 0), C.c_int(1 if out_unsigned else 0))
+        return out if ok else None
+
     def w8a8_linear(self, x, w, ws, bias=None, bias_i32=None, out_scale=1.0, out_zero=0,
                     requant=False):
         """Whole op on the CPU (quantize -> int32 GEMM -> E1/E2)."""
@@ -298,6 +321,29 @@ class Ref:
             C.c_uint32(rows), C.c_uint32(k), C.c_uint32(n), C.c_float(in_scale),
             C.c_int32(in_zero), C.c_float(out_scale), C.c_int32(out_zero),
             C.c_uint32(self._dt(x)), C.c_uint32(self._dt(w)), C.c_uint32(self._dt(out)))
+        return out if ok else None
+
+    def quantize_linear(self, x, scale, zero, out_unsigned=False):
+        x = _f32(x).reshape(-1)
+        out = np.zeros(x.size, np.uint8 if out_unsigned else np.int8)
+        ok = self.lib.ref_quantize_linear(_p(x, C.c_float), C.c_uint32(x.size), C.c_float(scale), C.c_int32(zero),
+                                          C.c_uint32(self._dt(out)), out.ctypes.data_as(C.c_void_p))
+        return out if ok else None
+
+    def dequantize_linear(self, x, scale, zero):
+        x = np.ascontiguousarray(x).reshape(-1)
+        out = np.zeros(x.size, np.float32)
+        ok = self.lib.ref_dequantize_linear(x.ctypes.data_as(C.c_void_p), C.c_uint32(x.size), C.c_float(scale),
+                                            C.c_int32(zero), C.c_uint32(self._dt(x)), _p(out, C.c_float))
+        return out if ok else None
+
+    def requantize_linear(self, x, in_scale, in_zero, out_scale, out_zero, out_unsigned=False):
+        x = np.ascontiguousarray(x).reshape(-1)
+        out = np.zeros(x.size, np.uint8 if out_unsigned else np.int8)
+        ok = self.lib.ref_requantize_linear(x.ctypes.data_as(C.c_void_p), out.ctypes.data_as(C.c_void_p),
+                                            C.c_uint32(x.size), C.c_float(in_scale), C.c_int32(in_zero),
+                                            C.c_float(out_scale), C.c_int32(out_zero),
+                                            C.c_uint32(self._dt(x)), C.c_uint32(self._dt(out)))
         return out if ok else None
 
     def pack_q8(self, w):

@@ -121,3 +121,27 @@ REF_API void ref_threads_leave(void) {
 REF_API const char* ref_isa_name(void) {
     return vx_kernel_isa_name(vx_kernel_platform()->isa);
 }
+
+/* The F32 <-> integer boundary and the byte-to-byte bridge, as the reference computes them
+ * (kernels.c amalgamation: quantize_linear_ops.inc, portable_inference_kernels.inc). */
+int quantize_linear_typed(const float*, const float*, const void*, uint32_t, void*, uint32_t, uint32_t);
+int dequantize_linear_typed(const void*, int, const float*, const void*, int, float*, int);
+int requantize_linear_i8u8(const void*, void*, uint32_t, float, int32_t, float, int32_t, uint32_t, uint32_t);
+
+REF_API int ref_quantize_linear(const float* x, uint32_t elements, float scale, int32_t zero,
+                                uint32_t out_dtype, void* out) {
+    int8_t z8 = (int8_t)zero; uint8_t zu = (uint8_t)zero;
+    return quantize_linear_typed(x, &scale, out_dtype == VX_DTYPE_I8 ? (const void*)&z8 : (const void*)&zu,
+                                 out_dtype, out, out_dtype, elements);
+}
+REF_API int ref_dequantize_linear(const void* x, uint32_t elements, float scale, int32_t zero,
+                                  uint32_t in_dtype, float* out) {
+    int8_t z8 = (int8_t)zero; uint8_t zu = (uint8_t)zero;
+    return dequantize_linear_typed(x, (int)in_dtype, &scale,
+                                   in_dtype == VX_DTYPE_I8 ? (const void*)&z8 : (const void*)&zu,
+                                   (int)in_dtype, out, (int)elements);
+}
+REF_API int ref_requantize_linear(const void* x, void* out, uint32_t elements, float in_scale, int32_t in_zero,
+                                  float out_scale, int32_t out_zero, uint32_t in_dtype, uint32_t out_dtype) {
+    return requantize_linear_i8u8(x, out, elements, in_scale, in_zero, out_scale, out_zero, in_dtype, out_dtype);
+}

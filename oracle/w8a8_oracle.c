@@ -292,3 +292,67 @@ VXO_API uint64_t vxo_div_const_mismatches(float d, uint64_t count, uint64_t seed
     }
     return bad;
 }
+
+/* ---- the F32 <-> byte boundary and the byte-to-byte bridge ---------------------------------
+ * dtype: 0 = int8, 1 = uint8 (the callers translate the reference's VX_DTYPE codes). */
+static void vxo_byte_range(int is_unsigned, int32_t* lo, int32_t* hi) {
+    *lo = is_unsigned ? 0 : -128; *hi = is_unsigned ? 255 : 127;
+}
+
+/* native/src/kernels/quantize_linear_ops.inc:155-170,230-254 (quantize_linear_typed):
+ * NaN -> zero point; t = x / scale + (float)zero; saturate, ties to even. */
+VXO_API int vxo_quantize_linear(const float* x, uint64_t elements, float scale, int32_t zero,
+                                int out_unsigned, void* out) {
+    int32_t lo, hi;
+    vxo_byte_range(out_unsigned, &lo, &hi);
+    if (!vxo_finite(scale) || scale <= 0.0f || zero < lo || zero > hi) return 0;
+    for (uint64_t i = 0; i < elements; i++) {
+        int32_t q;
+        float v = x[i];
+        if (v != v) q = zero;
+        else {
+            volatile float quotient = v / scale;
+            volatile float t = quotient + (float)zero;
+            if (t <= (float)lo) q = lo;
+            else if (t >= (float)hi) q = hi;
+            else if (!vxo_finite(t)) q = t < 0.0f ? lo : hi;
+            else q = vxo_round_ties_even(t);
+        }
+        if (out_unsigned) ((uint8_t*)out)[i] = (uint8_t)q; else ((int8_t*)out)[i] = (int8_t)q;
+    }
+    return 1;
+}
+
+/* native/src/kernels/quantize_linear_ops.inc:9-16,95-122 (dequantize_linear_typed):
+ * (float)(((double)x - zero) * (double)scale). */
+VXO_API int vxo_dequantize_linear(const void* x, uint64_t elements, float scale, int32_t zero,
+                                  int in_unsigned, float* out) {
+    for (uint64_t i = 0; i < elements; i++) {
+        const double v = in_unsigned ? (double)((const uint8_t*)x)[i] : (double)((const int8_t*)x)[i];
+        out[i] = (float)((v - (double)zero) * (double)scale);
+    }
+    return 1;
+}
+
+/* native/src/kernels/portable_inference_kernels.inc:2437-2463 (requantize_linear_i8u8):
+ * multiplier = in_scale / out_scale (f32); f32(f32(x - in_zero) * multiplier) + f32(out_zero),
+ * then the canonical requantization (NaN -> out_zero, saturate, ties to even). */
+VXO_API int vxo_requantize_linear(const void* x, void* out, uint64_t elements, float in_scale, int32_t in_zero,
+                                  float out_scale, int32_t out_zero, int in_unsigned, int out_unsigned) {
+    int32_t ilo, ihi, lo, hi;
+    vxo_byte_range(in_unsigned, &ilo, &ihi);
+    vxo_byte_range(out_unsigned, &lo, &hi);
+    if (!elements || !vxo_finite(in_scale) || in_scale <= 0.0f || !vxo_finite(out_scale) || out_scale <= 0.0f ||
+        in_zero < ilo || in_zero > ihi || out_zero < lo || out_zero > hi) return 0;
+    volatile float multiplier = in_scale / out_scale;
+    if (!vxo_finite(multiplier) || multiplier <= 0.0f) return 0;
+    for (uint64_t i = 0; i < elements; i++) {
+        const int32_t v = in_unsigned ? (int32_t)((const uint8_t*)x)[i] : (int32_t)((const int8_t*)x)[i];
+        volatile float centered = (float)(v - in_zero);
+        volatile float scaled = centered * multiplier;
+        volatile float t = scaled + (float)out_zero;
+        const int32_t q = vxo_requantize(t, lo, hi, out_zero);
+        if (out_unsigned) ((uint8_t*)out)[i] = (uint8_t)q; else ((int8_t*)out)[i] = (int8_t)q;
+    }
+    return 1;
+}

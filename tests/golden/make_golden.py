@@ -162,6 +162,23 @@ def main():
         out[f"r2_sym_z{izp}_y"] = got
     out["r2_sym_x"], out["r2_sym_w"], out["r2_sym_ws"], out["r2_sym_bias"] = xin, wv, wsc, b
 
+    # 6. the F32 <-> byte boundary and the byte-to-byte bridge (quantize_linear_typed,
+    #    dequantize_linear_typed, requantize_linear_i8u8): ties, saturation, NaN, infinities
+    rng = np.random.default_rng(20261)
+    half = (np.arange(-300, 300, dtype=np.float32) + np.float32(0.5))
+    bx = np.concatenate([rng.standard_normal(700).astype(np.float32) * 40, half * np.float32(0.25), half * np.float32(0.1),
+                         np.array([np.nan, np.inf, -np.inf, 0.0, -0.0, 1e30, -1e30, 1e-40], np.float32)]).astype(np.float32)
+    out["bnd_x"] = bx
+    cases = [(0.25, 0, 0), (0.1, -7, 0), (0.0371, 127, 0), (0.25, 128, 1), (0.1, 3, 1), (3e-5, 255, 1)]
+    out["bnd_cases"] = np.array(cases, np.float64)   # scale, zero point, 1 = uint8
+    all_bytes = np.arange(256, dtype=np.uint8)
+    for i, (scale, zero, u) in enumerate(cases):
+        out[f"bnd_q{i}"] = ref.quantize_linear(bx, scale, zero, bool(u))
+        src = all_bytes if u else all_bytes.view(np.int8)
+        out[f"bnd_dq{i}"] = ref.dequantize_linear(src, scale, zero)
+        oscale, ozero, ou = cases[(i + 1) % len(cases)]
+        out[f"bnd_rq{i}"] = ref.requantize_linear(src, max(scale, 0.01), zero, max(oscale, 0.01), ozero, bool(ou))
+
     path = os.path.join(ROOT, "tests", "golden", "w8a8_golden.npz")
     np.savez_compressed(path, **out)
     print(f"wrote {path}: {len(out)} arrays, {os.path.getsize(path)} bytes; ref isa={ref.isa()}")

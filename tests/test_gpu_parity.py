@@ -444,3 +444,70 @@ def test_full_size_properties(torch, ctx, oracle):
     want = oracle.requant_rows(acc[:8], s.cpu().numpy()[:8], None, c["ws"], None, os_, 0)
     assert np.array_equal(y8.cpu().numpy()[:8], want)
     weight.close()
+
+
+# ---- boundary ops of a static W8A8 island --------------------------------------------------
+
+def _boundary_cases(golden):
+    cases = [(float(c[0]), int(c[1]), bool(c[2])) for c in golden["bnd_cases"]]
+    all_bytes = np.arange(256, dtype=np.uint8)
+    for i, (scale, zero, u) in enumerate(cases):
+        oscale, ozero, ou = cases[(i + 1) % len(cases)]
+        yield i, scale, zero, u, (all_bytes if u else all_bytes.view(np.int8)), max(scale, 0.01), max(oscale, 0.01), ozero, ou
+
+
+def test_boundary_ops_golden(torch, ctx, golden):
+    """Vectors produced by the reference's own quantize_linear_typed / dequantize_linear_typed /
+    requantize_linear_i8u8: ties, saturation, NaN, infinities, every byte value."""
+    x = dev(torch, golden["bnd_x"])
+    for i, scale, zero, u, src, rs, ros, ozero, ou in _boundary_cases(golden):
+        assert np.array_equal(ctx.quantize_linear(x, scale, zero, u).cpu().numpy(), golden[f"bnd_q{i}"])
+        got = ctx.dequantize_linear(dev(torch, src), scale, zero).cpu().numpy()
+        assert np.array_equal(got.view(np.uint32), golden[f"bnd_dq{i}"].view(np.uint32))
+        assert np.array_equal(ctx.requantize_linear(dev(torch, src), rs, zero, ros, ozero, ou).cpu().numpy(), golden[f"bnd_rq{i}"])
+
+
+@pytest.mark.parametrize("count", [1, 15, 16, 17, 4099, 1 << 20])
+def test_boundary_ops_vs_oracle(torch, ctx, oracle, count):
+    """Random tensors at sizes around the 16-element vector width, and an unaligned view."""
+    rng = np.random.default_rng(count)
+    for trial in range(4):
+        u, ou = bool(rng.integers(2)), bool(rng.integers(2))
+        scale = float(np.float32(10.0 ** rng.uniform(-3, 1)))
+        oscale = float(np.float32(10.0 ** rng.uniform(-3, 1)))
+        zero = int(rng.integers(0, 256)) if u else int(rng.integers(-128, 128))
+        ozero = int(rng.integers(0, 256)) if ou else int(rng.integers(-128, 128))
+        x = (rng.standard_normal(count + 3) * 10.0 ** rng.uniform(-2, 2)).astype(np.float32)
+        x[rng.integers(count + 3)] = np.nan
+        xd = dev(torch, x)[3:] if trial % 2 else dev(torch, x[3:])      # odd trials: 12-byte offset
+        assert np.array_equal(ctx.quantize_linear(xd, scale, zero, u).cpu().numpy(), oracle.quantize_linear(x[3:], scale, zero, u))
+        b = rng.integers(0, 256, size=count + 1).astype(np.uint8)
+        src = b if u else b.view(np.int8)
+        sd = dev(torch, src)[1:] if trial % 2 else dev(torch, src[1:])
+        assert np.array_equal(ctx.dequantize_linear(sd, scale, zero).cpu().numpy().view(np.uint32),
+                              oracle.dequantize_linear(src[1:], scale, zero).view(np.uint32))
+        assert np.array_equal(ctx.requantize_linear(sd, scale, zero, oscale, ozero, ou).cpu().numpy(),
+                              oracle.requantize_linear(src[1:], scale, zero, oscale, ozero, ou))
+
+
+def test_boundary_ops_host_entries(torch, oracle):
+    from volvoxai_b200 import w8a8
+    rng = np.random.default_rng(5)
+    x = (rng.standard_normal(3001) * 7).astype(np.float32)
+    q = np.full(3001, 9, np.uint8)
+    assert w8a8.quantize_typed_f32_i8u8(x, q, 0.11, 131) == 1
+    assert np.array_equal(q, oracle.quantize_linear(x, 0.11, 131, True))
+    f = np.zeros(3001, np.float32)
+    assert w8a8.dequantize_typed_i8u8_f32(q, 0.11, 131, f) == 1
+    assert np.array_equal(f.view(np.uint32), oracle.dequantize_linear(q, 0.11, 131).view(np.uint32))
+    r = np.zeros(3001, np.int8)
+    assert w8a8.requantize_linear_i8u8(q, r, 0.11, 131, 0.3, -5) == 1
+    assert np.array_equal(r, oracle.requantize_linear(q, 0.11, 131, 0.3, -5, False))
+    # declined before the output is touched: bad scale, zero point outside the dtype, size mismatch
+    keep = r.copy()
+    assert w8a8.requantize_linear_i8u8(q, r, 0.0, 131, 0.3, -5) == 0
+    assert w8a8.requantize_linear_i8u8(q, r, 0.11, 300, 0.3, -5) == 0
+    assert w8a8.requantize_linear_i8u8(q, r[:-1], 0.11, 131, 0.3, -5) == 0
+    assert w8a8.quantize_typed_f32_i8u8(x, q, float("nan"), 0) == 0
+    assert np.array_equal(r, keep)
+    w8a8.host_cache_clear()

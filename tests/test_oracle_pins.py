@@ -221,3 +221,42 @@ def test_constant_divisor_division_for_the_quantizer(oracle):
                 continue
             lo = int(np.floor(np.log2(float(d)))) - 20
             assert oracle.div_const_mismatches(d, 200000, seed=e * 7 + 1000, lo_exp=lo, hi_exp=lo + 28) == 0, d
+
+
+def _boundary_cases(golden):
+    cases = [(float(c[0]), int(c[1]), bool(c[2])) for c in golden["bnd_cases"]]
+    all_bytes = np.arange(256, dtype=np.uint8)
+    for i, (scale, zero, u) in enumerate(cases):
+        oscale, ozero, ou = cases[(i + 1) % len(cases)]
+        yield i, scale, zero, u, (all_bytes if u else all_bytes.view(np.int8)), max(scale, 0.01), max(oscale, 0.01), ozero, ou
+
+
+def test_boundary_ops_golden(oracle, golden):
+    """QuantizeLinear / DequantizeLinear / RequantizeLinear restatements against vectors produced
+    by the reference's own functions (ties, saturation, NaN, infinities, every byte value)."""
+    x = golden["bnd_x"]
+    for i, scale, zero, u, src, rs, ros, ozero, ou in _boundary_cases(golden):
+        assert np.array_equal(oracle.quantize_linear(x, scale, zero, u), golden[f"bnd_q{i}"])
+        assert np.array_equal(oracle.dequantize_linear(src, scale, zero).view(np.uint32), golden[f"bnd_dq{i}"].view(np.uint32))
+        assert np.array_equal(oracle.requantize_linear(src, rs, zero, ros, ozero, ou), golden[f"bnd_rq{i}"])
+
+
+def test_boundary_ops_fuzz_vs_ref(oracle, ref):
+    rng = np.random.default_rng(77)
+    for _ in range(40):
+        u, ou = bool(rng.integers(2)), bool(rng.integers(2))
+        scale = float(np.float32(10.0 ** rng.uniform(-4, 2)))
+        oscale = float(np.float32(10.0 ** rng.uniform(-3, 1)))
+        zero = int(rng.integers(0, 256)) if u else int(rng.integers(-128, 128))
+        ozero = int(rng.integers(0, 256)) if ou else int(rng.integers(-128, 128))
+        x = (rng.standard_normal(4096) * 10.0 ** rng.uniform(-3, 3)).astype(np.float32)
+        assert np.array_equal(oracle.quantize_linear(x, scale, zero, u), ref.quantize_linear(x, scale, zero, u))
+        b = rng.integers(0, 256, size=4096).astype(np.uint8)
+        src = b if u else b.view(np.int8)
+        assert np.array_equal(oracle.dequantize_linear(src, scale, zero).view(np.uint32),
+                              ref.dequantize_linear(src, scale, zero).view(np.uint32))
+        assert np.array_equal(oracle.requantize_linear(src, scale, zero, oscale, ozero, ou),
+                              ref.requantize_linear(src, scale, zero, oscale, ozero, ou))
+    # declined descriptors
+    assert oracle.quantize_linear(x, 0.0, 0) is None and ref.quantize_linear(x, 0.0, 0) is None
+    assert oracle.requantize_linear(src, 0.1, zero, float("inf"), 0) is None

@@ -607,6 +607,55 @@ int vxb_linear_i8_gather(VxbContext* ctx, const VxbWeight* w, const float* x, ui
     return run_gemm(ctx, w, (const int8_t*)ctx->q.ptr, rows, epi, VXB_ROUTE_TCGEN05, "k1+");
 }
 
+namespace {
+bool byte_dtype(uint32_t dt) { return dt == VXB_DTYPE_I8 || dt == VXB_DTYPE_U8; }
+bool zero_in_range(int32_t z, uint32_t dt) { return dt == VXB_DTYPE_I8 ? (z >= -128 && z <= 127) : (z >= 0 && z <= 255); }
+}
+
+int vxb_quantize_linear_device(VxbContext* ctx, const float* x, uint64_t elements, float scale, int32_t zero_point,
+                               uint32_t output_dtype, void* out) {
+    if (!ctx || !x || !out) return fail(0, "null argument");
+    if (!byte_dtype(output_dtype)) return fail(0, "output dtype %u is not I8/U8", output_dtype);
+    if (!valid_scale(scale)) return fail(0, "scale is not positive and finite");
+    if (!zero_in_range(zero_point, output_dtype)) return fail(0, "zero point %d outside the output dtype", zero_point);
+    if (!elements) return 1;
+    if (ensure_device(ctx) != 1) return -1;
+    CUDA_TRY(launch_quantize_linear(x, elements, scale, zero_point, output_dtype == VXB_DTYPE_U8, out, ctx->stream), -1);
+    count_launch();
+    return 1;
+}
+
+int vxb_dequantize_linear_device(VxbContext* ctx, const void* x, uint64_t elements, float scale, int32_t zero_point,
+                                 uint32_t input_dtype, float* out) {
+    if (!ctx || !x || !out) return fail(0, "null argument");
+    if (!byte_dtype(input_dtype)) return fail(0, "input dtype %u is not I8/U8", input_dtype);
+    if (!valid_scale(scale)) return fail(0, "scale is not positive and finite");
+    if (!zero_in_range(zero_point, input_dtype)) return fail(0, "zero point %d outside the input dtype", zero_point);
+    if (!elements) return 1;
+    if (ensure_device(ctx) != 1) return -1;
+    CUDA_TRY(launch_dequantize_linear(x, elements, scale, zero_point, input_dtype == VXB_DTYPE_U8, out, ctx->stream), -1);
+    count_launch();
+    return 1;
+}
+
+int vxb_requantize_linear_device(VxbContext* ctx, const void* x, uint64_t elements, float input_scale,
+                                 int32_t input_zero_point, float output_scale, int32_t output_zero_point,
+                                 uint32_t input_dtype, uint32_t output_dtype, void* out) {
+    if (!ctx || !x || !out) return fail(0, "null argument");
+    if (!elements) return fail(0, "empty tensor");
+    if (!byte_dtype(input_dtype) || !byte_dtype(output_dtype)) return fail(0, "dtypes must be I8/U8");
+    if (!valid_scale(input_scale) || !valid_scale(output_scale)) return fail(0, "scales must be positive and finite");
+    if (!zero_in_range(input_zero_point, input_dtype) || !zero_in_range(output_zero_point, output_dtype))
+        return fail(0, "zero point outside its dtype");
+    const volatile float multiplier = input_scale / output_scale;   // one fp32 division, as the reference
+    if (!valid_scale(multiplier)) return fail(0, "input_scale / output_scale is not positive and finite");
+    if (ensure_device(ctx) != 1) return -1;
+    CUDA_TRY(launch_requantize_linear(x, elements, multiplier, input_zero_point, input_dtype == VXB_DTYPE_U8,
+                                      output_zero_point, output_dtype == VXB_DTYPE_U8, out, ctx->stream), -1);
+    count_launch();
+    return 1;
+}
+
 uint32_t vxb_weight_row_bytes(const VxbWeight* w) { return w ? w->kpad : 0; }
 
 int vxb_linear_prepared(VxbContext* ctx, const VxbWeight* w, const int8_t* q, const float* row_scales,
@@ -889,6 +938,54 @@ int vxb_qlinear_i8u8(const void* input, const void* weight, const float* weight_
     if (rc != 1) return rc;
     CUDA_TRY(cudaMemcpyAsync(output, ctx->stage_out.ptr, out_bytes, cudaMemcpyDeviceToHost, ctx->stream), -1);
     return vxb_context_synchronize(ctx) == 1 ? 1 : -1;
+}
+
+extern "C++" {
+namespace {
+// host buffers through the context's staging buffers: upload, one device entry, download
+template <typename Fn>
+int host_elementwise(const void* input, size_t in_bytes, void* output, size_t out_bytes, Fn&& device_call) {
+    if (!input || !output) return fail(0, "null argument");
+    if (overlap(output, out_bytes, input, in_bytes)) return fail(0, "output overlaps the input");
+    std::lock_guard<std::mutex> lock(g_host_mutex);
+    VxbContext* ctx = nullptr;
+    int rc = host_context(&ctx);
+    if (rc != 1) return rc;
+    CUDA_TRY(ctx->stage_in.reserve(in_bytes), 0);
+    CUDA_TRY(ctx->stage_out.reserve(out_bytes), 0);
+    CUDA_TRY(cudaMemcpyAsync(ctx->stage_in.ptr, input, in_bytes, cudaMemcpyHostToDevice, ctx->stream), -1);
+    rc = device_call(ctx, ctx->stage_in.ptr, ctx->stage_out.ptr);
+    if (rc != 1) return rc;
+    CUDA_TRY(cudaMemcpyAsync(output, ctx->stage_out.ptr, out_bytes, cudaMemcpyDeviceToHost, ctx->stream), -1);
+    return vxb_context_synchronize(ctx) == 1 ? 1 : -1;
+}
+}  // namespace
+}  // extern "C++"
+
+int vxb_quantize_typed_f32_i8u8(const float* input, uint32_t elements, void* output, float output_scale,
+                                int32_t output_zero_point, uint32_t output_dtype) {
+    if (!elements) return fail(0, "empty tensor");
+    return host_elementwise(input, (size_t)elements * 4, output, elements, [&](VxbContext* ctx, void* in, void* out) {
+        return vxb_quantize_linear_device(ctx, (const float*)in, elements, output_scale, output_zero_point, output_dtype, out);
+    });
+}
+
+int vxb_dequantize_typed_i8u8_f32(const void* input, uint32_t elements, float input_scale, int32_t input_zero_point,
+                                  uint32_t input_dtype, float* output) {
+    if (!elements) return fail(0, "empty tensor");
+    return host_elementwise(input, elements, output, (size_t)elements * 4, [&](VxbContext* ctx, void* in, void* out) {
+        return vxb_dequantize_linear_device(ctx, in, elements, input_scale, input_zero_point, input_dtype, (float*)out);
+    });
+}
+
+int vxb_requantize_linear_i8u8(const void* input, uint32_t input_elements, void* output, uint32_t output_elements,
+                               float input_scale, int32_t input_zero_point, float output_scale,
+                               int32_t output_zero_point, uint32_t input_dtype, uint32_t output_dtype) {
+    if (!input_elements || input_elements != output_elements) return fail(0, "element counts differ or are zero");
+    return host_elementwise(input, input_elements, output, output_elements, [&](VxbContext* ctx, void* in, void* out) {
+        return vxb_requantize_linear_device(ctx, in, input_elements, input_scale, input_zero_point, output_scale,
+                                            output_zero_point, input_dtype, output_dtype, out);
+    });
 }
 
 int vxb_cuda_graph_llm_f32(const VxbLLMOpArgs* a) {

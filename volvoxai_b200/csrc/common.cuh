@@ -131,6 +131,15 @@ __device__ __forceinline__ void epi_store(const EpilogueParams& p, uint32_t row,
 
 // ---- launchers implemented in the .cu files -------------------------------
 
+// Boundary ops of a static W8A8 island (boundary_ops.cu): byte outputs are int8 or uint8.
+cudaError_t launch_quantize_linear(const float* x, unsigned long long n, float scale, int32_t zero, bool out_unsigned,
+                                   void* out, cudaStream_t stream);
+cudaError_t launch_dequantize_linear(const void* x, unsigned long long n, float scale, int32_t zero, bool in_unsigned,
+                                     float* out, cudaStream_t stream);
+cudaError_t launch_requantize_linear(const void* x, unsigned long long n, float multiplier, int32_t in_zero,
+                                     bool in_unsigned, int32_t out_zero, bool out_unsigned, void* out,
+                                     cudaStream_t stream);
+
 // Grouped weight scales (the reference's PackedLinear storage groups): one thread per output,
 // an exact integer dot per group, fp32 accumulation in ascending group order. fp32 output only.
 cudaError_t launch_gemm_grouped(const int8_t* q, uint32_t rows, const int8_t* w, uint32_t n, uint32_t kpad,

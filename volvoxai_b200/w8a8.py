@@ -25,7 +25,7 @@ from ._lib import (DT_I8, DT_U8, OP_PACKED_LINEAR, ROUTE_AUTO, ROUTE_DECODE, ROU
 
 __all__ = ["Context", "Weight", "W8A8Error", "qlinear_i8u8", "packed_linear",
            "packed_linear_decode", "host_cache_clear", "launch_count", "last_error",
-           "last_route", "ROUTE_AUTO", "ROUTE_GEMV", "ROUTE_TCGEN05", "ROUTE_SIMT", "ROUTE_DECODE", "ROUTE_DECODE_STREAMK", "ROUTE_TCGEN05_PAIR",
+           "quantize_typed_f32_i8u8", "dequantize_typed_i8u8_f32", "requantize_linear_i8u8", "last_route", "ROUTE_AUTO", "ROUTE_GEMV", "ROUTE_TCGEN05", "ROUTE_SIMT", "ROUTE_DECODE", "ROUTE_DECODE_STREAMK", "ROUTE_TCGEN05_PAIR",
            "DT_I8", "DT_U8"]
 
 
@@ -168,6 +168,31 @@ class Context:
                                            _ptr(out), out.stride(0), route))
         return out
 
+    # ---- boundary of a static W8A8 island (torch CUDA tensors) ----
+    def quantize_linear(self, x, scale: float, zero_point: int = 0, unsigned: bool = False):
+        import torch
+        out = torch.empty(x.shape, dtype=torch.uint8 if unsigned else torch.int8, device=x.device)
+        _check(self._L.vxb_quantize_linear_device(self.handle, _ptr(x), x.numel(), float(scale), int(zero_point),
+                                                  DT_U8 if unsigned else DT_I8, _ptr(out)))
+        return out
+
+    def dequantize_linear(self, x, scale: float, zero_point: int = 0):
+        import torch
+        out = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+        _check(self._L.vxb_dequantize_linear_device(self.handle, _ptr(x), x.numel(), float(scale), int(zero_point),
+                                                    DT_U8 if x.dtype == torch.uint8 else DT_I8, _ptr(out)))
+        return out
+
+    def requantize_linear(self, x, input_scale: float, input_zero_point: int, output_scale: float,
+                          output_zero_point: int, unsigned: bool = False):
+        import torch
+        out = torch.empty(x.shape, dtype=torch.uint8 if unsigned else torch.int8, device=x.device)
+        _check(self._L.vxb_requantize_linear_device(self.handle, _ptr(x), x.numel(), float(input_scale),
+                                                    int(input_zero_point), float(output_scale), int(output_zero_point),
+                                                    DT_U8 if x.dtype == torch.uint8 else DT_I8,
+                                                    DT_U8 if unsigned else DT_I8, _ptr(out)))
+        return out
+
     def qlinear_device(self, w: "Weight", x, input_scale, input_zero, output_scale, output_zero,
                        out_unsigned: bool = False, route: int = ROUTE_AUTO):
         import torch
@@ -255,6 +280,29 @@ def qlinear_i8u8(input, weight, weight_scales, weight_zero_points, bias, output,
                                   _ptr(output), rows, d_in, d_out, float(input_scale),
                                   int(input_zero_point), float(output_scale),
                                   int(output_zero_point), dt(input), dt(weight), dt(output)))
+
+
+def _np_dt(a):
+    return DT_U8 if a.dtype == np.uint8 else DT_I8
+
+
+def quantize_typed_f32_i8u8(input, output, output_scale, output_zero_point) -> int:
+    """``VxW8A8Ops.quantize_typed_f32_i8u8``: fp32 NumPy array -> int8/uint8 array in place."""
+    return int(_lib.load().vxb_quantize_typed_f32_i8u8(_ptr(input), input.size, _ptr(output), float(output_scale),
+                                                       int(output_zero_point), _np_dt(output)))
+
+
+def dequantize_typed_i8u8_f32(input, input_scale, input_zero_point, output) -> int:
+    """``VxW8A8Ops.dequantize_typed_i8u8_f32``: int8/uint8 NumPy array -> fp32 array in place."""
+    return int(_lib.load().vxb_dequantize_typed_i8u8_f32(_ptr(input), input.size, float(input_scale),
+                                                         int(input_zero_point), _np_dt(input), _ptr(output)))
+
+
+def requantize_linear_i8u8(input, output, input_scale, input_zero_point, output_scale, output_zero_point) -> int:
+    """``VxW8A8Ops.requantize_linear_i8u8``: byte array -> byte array of another quantized domain."""
+    return int(_lib.load().vxb_requantize_linear_i8u8(_ptr(input), input.size, _ptr(output), output.size,
+                                                      float(input_scale), int(input_zero_point), float(output_scale),
+                                                      int(output_zero_point), _np_dt(input), _np_dt(output)))
 
 
 def packed_linear(x, words, scales, bias, y, *, weight_bits=8, group_size=128,
