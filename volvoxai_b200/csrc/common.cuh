@@ -113,6 +113,21 @@ __device__ __forceinline__ int32_t epi_i8_v2(int32_t acc, float as, float ws, fl
     return moved != moved ? out_zero : q;
 }
 
+// E2 inside the fast-division guard with the byte range of the output type as the clamp: as,
+// ws and out_scale within 2^+-30 keep every intermediate finite (|acc| < 2^31, multiplier < 2^90),
+// so no NaN can appear, and round + saturate is one conversion instruction. Same result as
+// epi_i8 bit for bit there.
+template <bool UNSIGNED>
+__device__ __forceinline__ int32_t epi_i8_sat(int32_t acc, float as, float ws, float out_scale,
+                                              float out_rcp, float zero_f) {
+    const float mult = div_const(__fmul_rn(as, ws), out_scale, out_rcp);
+    const float moved = __fadd_rn(__fmul_rn(__int2float_rn(acc), mult), zero_f);
+    int32_t q;
+    if (UNSIGNED) asm("cvt.rni.sat.u8.f32 %0, %1;" : "=r"(q) : "f"(moved));
+    else asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q) : "f"(moved));
+    return q;
+}
+
 // One output element through the selected epilogue (scalar path).
 __device__ __forceinline__ void epi_store(const EpilogueParams& p, uint32_t row, uint32_t col,
                                           int32_t acc) {

@@ -103,6 +103,30 @@ __device__ __forceinline__ void umma_i8_pair(uint32_t d_tmem, uint64_t a_desc, u
         "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// The same with the descriptors given by their low words (start address >> 4 | leading offset): the
+// high word (stride, version, swizzle) is one constant for every tile of this kernel. Fewer
+// instructions in the issuing thread, whose time between two MMAs is exposed tensor-pipe idle time.
+constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t desc_lo(uint32_t smem_addr) { return ((smem_addr >> 4) & 0x3fffu) | (1u << 16); }
+__device__ __forceinline__ void umma_i8_pair_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.eq.b32 p, 0, 0;\n\t"
+        "mov.b64 da, {%1, %4};\n\t"
+        "mov.b64 db, {%2, %4};\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], da, db, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(kDescHi) : "memory");
+}
+__device__ __forceinline__ void umma_i8_pair_lo_first(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                                      uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 da, {%1, %4};\n\t"
+        "mov.b64 db, {%2, %4};\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], da, db, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(kDescHi), "r"(accumulate) : "memory");
+}
 // the barrier (any CTA of the cluster) gets one arrival once all MMAs issued so far have finished
 __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];"
@@ -193,25 +217,29 @@ gemm_i8_pair_kernel(const __grid_constant__ GemmTcgen05Args args) {
             constexpr uint32_t idesc = make_idesc(2 * kBM, kBN);
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
+            const uint32_t a_lo0 = desc_lo(sm.a(0));
+            const uint32_t peer_delta = in_cta(sm.empty(0), 1) - sm.empty(0);   // the same offset for every barrier
+            uint32_t full_s = sm.full(0), empty_s = sm.empty(0), a_lo = a_lo0;
             for (uint32_t t = pair; ok && t < total_tiles; t += pairs) {
                 if (!mbar_wait(sm.tmem_empty(acc), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * kAccCols;
                 for (uint32_t kb = 0; kb < num_kb; kb++) {
-                    if (!mbar_wait(sm.full(stage), phase, abort_flag)) { ok = false; break; }
+                    if (!mbar_try_wait(full_s, phase) && !mbar_wait(full_s, phase, abort_flag)) { ok = false; break; }
                     tc_fence_after();
-                    const uint64_t da = make_smem_desc(sm.a(stage)), db = make_smem_desc(sm.b(stage));
-#pragma unroll
-                    for (uint32_t k = 0; k < kBK / kUmmaK; k++)   // +32 bytes of K = +2 in the descriptor's address field
-                        umma_i8_pair(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0u);
+                    umma_i8_pair_lo_first(d_tmem, a_lo, a_lo + (kABytes >> 4), idesc, kb);
+                    umma_i8_pair_lo(d_tmem, a_lo + 2u, a_lo + (kABytes >> 4) + 2u, idesc);
+                    umma_i8_pair_lo(d_tmem, a_lo + 4u, a_lo + (kABytes >> 4) + 4u, idesc);
+                    umma_i8_pair_lo(d_tmem, a_lo + 6u, a_lo + (kABytes >> 4) + 6u, idesc);
                     // the stage is free again in both CTAs once these MMAs have read it
-                    umma_commit_pair(in_cta(sm.empty(stage), 0));
-                    umma_commit_pair(in_cta(sm.empty(stage), 1));
-                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                    umma_commit_pair(empty_s);
+                    umma_commit_pair(empty_s + peer_delta);
+                    full_s += 8; empty_s += 8; a_lo += kStageBytes >> 4;
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; full_s = sm.full(0); empty_s = sm.empty(0); a_lo = a_lo0; }
                 }
                 if (!ok) break;
-                umma_commit_pair(in_cta(sm.tmem_full(acc), 0));
-                umma_commit_pair(in_cta(sm.tmem_full(acc), 1));
+                umma_commit_pair(sm.tmem_full(acc));
+                umma_commit_pair(sm.tmem_full(acc) + peer_delta);
                 acc ^= 1u;
                 if (acc == 0) acc_phase ^= 1u;
             }
@@ -226,6 +254,7 @@ gemm_i8_pair_kernel(const __grid_constant__ GemmTcgen05Args args) {
         float* s_bias = sm.bias() + (warp - 2u) * kEpiCols;
         const float zero_f = __int2float_rn(ep.out_zero);
         const float lo_f = __int2float_rn(ep.out_lo), hi_f = __int2float_rn(ep.out_hi);
+        const bool sat_s8 = ep.out_lo == -128 && ep.out_hi == 127, sat_u8 = ep.out_lo == 0 && ep.out_hi == 255;
         uint32_t acc = 0, acc_phase = 0;
         bool ok = true;
         for (uint32_t t = pair; ok && t < total_tiles; t += pairs) {
@@ -264,7 +293,27 @@ gemm_i8_pair_kernel(const __grid_constant__ GemmTcgen05Args args) {
                 if (ep.mode == kEpiI8) {
                     int8_t* dst = (int8_t*)ep.out + (size_t)row * ep.ld + col;
                     uint32_t packed[8];
-                    if (fast) {
+                    if (fast && sat_s8) {
+#pragma unroll
+                        for (int j = 0; j < 8; j++) {
+                            const float4 wv = w4[j], bv = b4[j];
+                            const int32_t q0 = epi_i8_sat<false>((int32_t)r[4 * j + 0] + __float_as_int(bv.x), as, wv.x, ep.out_scale, ep.out_rcp, zero_f);
+                            const int32_t q1 = epi_i8_sat<false>((int32_t)r[4 * j + 1] + __float_as_int(bv.y), as, wv.y, ep.out_scale, ep.out_rcp, zero_f);
+                            const int32_t q2 = epi_i8_sat<false>((int32_t)r[4 * j + 2] + __float_as_int(bv.z), as, wv.z, ep.out_scale, ep.out_rcp, zero_f);
+                            const int32_t q3 = epi_i8_sat<false>((int32_t)r[4 * j + 3] + __float_as_int(bv.w), as, wv.w, ep.out_scale, ep.out_rcp, zero_f);
+                            packed[j] = __byte_perm(__byte_perm(q0, q1, 0x0040), __byte_perm(q2, q3, 0x0040), 0x5410);
+                        }
+                    } else if (fast && sat_u8) {
+#pragma unroll
+                        for (int j = 0; j < 8; j++) {
+                            const float4 wv = w4[j], bv = b4[j];
+                            const int32_t q0 = epi_i8_sat<true>((int32_t)r[4 * j + 0] + __float_as_int(bv.x), as, wv.x, ep.out_scale, ep.out_rcp, zero_f);
+                            const int32_t q1 = epi_i8_sat<true>((int32_t)r[4 * j + 1] + __float_as_int(bv.y), as, wv.y, ep.out_scale, ep.out_rcp, zero_f);
+                            const int32_t q2 = epi_i8_sat<true>((int32_t)r[4 * j + 2] + __float_as_int(bv.z), as, wv.z, ep.out_scale, ep.out_rcp, zero_f);
+                            const int32_t q3 = epi_i8_sat<true>((int32_t)r[4 * j + 3] + __float_as_int(bv.w), as, wv.w, ep.out_scale, ep.out_rcp, zero_f);
+                            packed[j] = __byte_perm(__byte_perm(q0, q1, 0x0040), __byte_perm(q2, q3, 0x0040), 0x5410);
+                        }
+                    } else if (fast) {
 #pragma unroll
                         for (int j = 0; j < 8; j++) {
                             const float4 wv = w4[j], bv = b4[j];
