@@ -106,8 +106,6 @@ __device__ __forceinline__ void umma_i8_pair(uint32_t d_tmem, uint64_t a_desc, u
 // The same with the descriptors given by their low words (start address >> 4 | leading offset): the
 // high word (stride, version, swizzle) is one constant for every tile of this kernel. Fewer
 // instructions in the issuing thread, whose time between two MMAs is exposed tensor-pipe idle time.
-constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
-__device__ __forceinline__ uint32_t desc_lo(uint32_t smem_addr) { return ((smem_addr >> 4) & 0x3fffu) | (1u << 16); }
 __device__ __forceinline__ void umma_i8_pair_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
@@ -115,7 +113,7 @@ __device__ __forceinline__ void umma_i8_pair_lo(uint32_t d_tmem, uint32_t a_lo, 
         "mov.b64 da, {%1, %4};\n\t"
         "mov.b64 db, {%2, %4};\n\t"
         "tcgen05.mma.cta_group::2.kind::i8 [%0], da, db, %3, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(kDescHi) : "memory");
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(kSmemDescHi) : "memory");
 }
 __device__ __forceinline__ void umma_i8_pair_lo_first(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
                                                       uint32_t accumulate) {
@@ -125,7 +123,7 @@ __device__ __forceinline__ void umma_i8_pair_lo_first(uint32_t d_tmem, uint32_t 
         "mov.b64 da, {%1, %4};\n\t"
         "mov.b64 db, {%2, %4};\n\t"
         "tcgen05.mma.cta_group::2.kind::i8 [%0], da, db, %3, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(kDescHi), "r"(accumulate) : "memory");
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(kSmemDescHi), "r"(accumulate) : "memory");
 }
 // the barrier (any CTA of the cluster) gets one arrival once all MMAs issued so far have finished
 __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster) {
@@ -217,7 +215,7 @@ gemm_i8_pair_kernel(const __grid_constant__ GemmTcgen05Args args) {
             constexpr uint32_t idesc = make_idesc(2 * kBM, kBN);
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
-            const uint32_t a_lo0 = desc_lo(sm.a(0));
+            const uint32_t a_lo0 = smem_desc_lo(sm.a(0));
             const uint32_t peer_delta = in_cta(sm.empty(0), 1) - sm.empty(0);   // the same offset for every barrier
             uint32_t full_s = sm.full(0), empty_s = sm.empty(0), a_lo = a_lo0;
             for (uint32_t t = pair; ok && t < total_tiles; t += pairs) {

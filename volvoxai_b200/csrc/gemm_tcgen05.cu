@@ -153,21 +153,23 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ GemmTcgen05Args args) {
             constexpr uint32_t idesc = make_idesc(kBM, kBN);
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
+            // barrier addresses and descriptor low words advance by constants from stage to stage
+            const uint32_t a_lo0 = smem_desc_lo(sm.a(0));
+            uint32_t full_s = sm.full(0), empty_s = sm.empty(0), a_lo = a_lo0;
             for (uint32_t t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
                 if (!mbar_wait(sm.tmem_empty(acc), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * kAccCols;
                 for (uint32_t kb = 0; kb < num_kb; kb++) {
-                    if (!mbar_wait(sm.full(stage), phase, abort_flag)) { ok = false; break; }
+                    if (!mbar_try_wait(full_s, phase) && !mbar_wait(full_s, phase, abort_flag)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t a_addr = sm.a(stage), b_addr = sm.b(stage);
-#pragma unroll
-                    for (uint32_t k = 0; k < kBK / kUmmaK; k++) {
-                        umma_i8(d_tmem, make_smem_desc(a_addr + k * kUmmaK),
-                                make_smem_desc(b_addr + k * kUmmaK), idesc, (kb | k) != 0u);
-                    }
-                    umma_commit(sm.empty(stage));
-                    if (++stage == nstages) { stage = 0; phase ^= 1u; }
+                    umma_i8_lo_first(d_tmem, a_lo, a_lo + (kABytes >> 4), idesc, kb);
+                    umma_i8_lo(d_tmem, a_lo + 2u, a_lo + (kABytes >> 4) + 2u, idesc);   // +32 bytes of K = +2
+                    umma_i8_lo(d_tmem, a_lo + 4u, a_lo + (kABytes >> 4) + 4u, idesc);
+                    umma_i8_lo(d_tmem, a_lo + 6u, a_lo + (kABytes >> 4) + 6u, idesc);
+                    umma_commit(empty_s);
+                    full_s += 8; empty_s += 8; a_lo += kStageBytes >> 4;
+                    if (++stage == nstages) { stage = 0; phase ^= 1u; full_s = sm.full(0); empty_s = sm.empty(0); a_lo = a_lo0; }
                 }
                 if (!ok) break;
                 umma_commit(sm.tmem_full(acc));
@@ -191,6 +193,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ GemmTcgen05Args args) {
         uint8_t* stage_tile = sm.base + kOffStages + (kStages - 1) * kStageBytes + (warp - 2u) * (32u * kEpiCols);
         const float zero_f = __int2float_rn(ep.out_zero);
         const float lo_f = __int2float_rn(ep.out_lo), hi_f = __int2float_rn(ep.out_hi);
+        const bool sat_s8 = ep.out_lo == -128 && ep.out_hi == 127, sat_u8 = ep.out_lo == 0 && ep.out_hi == 255;
         uint32_t acc = 0, acc_phase = 0;
         bool ok = true;
         for (uint32_t t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
@@ -230,7 +233,27 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ GemmTcgen05Args args) {
                 if (ep.mode == kEpiI8) {
                     int8_t* dst = (int8_t*)ep.out + (size_t)row * ep.ld + col;
                     uint32_t packed[8];
-                    if (fast) {
+                    if (fast && sat_s8) {
+#pragma unroll
+                        for (int j = 0; j < 8; j++) {
+                            const float4 wv = w4[j], bv = b4[j];
+                            const int32_t q0 = epi_i8_sat<false>((int32_t)r[4 * j + 0] + __float_as_int(bv.x), as, wv.x, ep.out_scale, ep.out_rcp, zero_f);
+                            const int32_t q1 = epi_i8_sat<false>((int32_t)r[4 * j + 1] + __float_as_int(bv.y), as, wv.y, ep.out_scale, ep.out_rcp, zero_f);
+                            const int32_t q2 = epi_i8_sat<false>((int32_t)r[4 * j + 2] + __float_as_int(bv.z), as, wv.z, ep.out_scale, ep.out_rcp, zero_f);
+                            const int32_t q3 = epi_i8_sat<false>((int32_t)r[4 * j + 3] + __float_as_int(bv.w), as, wv.w, ep.out_scale, ep.out_rcp, zero_f);
+                            packed[j] = __byte_perm(__byte_perm(q0, q1, 0x0040), __byte_perm(q2, q3, 0x0040), 0x5410);
+                        }
+                    } else if (fast && sat_u8) {
+#pragma unroll
+                        for (int j = 0; j < 8; j++) {
+                            const float4 wv = w4[j], bv = b4[j];
+                            const int32_t q0 = epi_i8_sat<true>((int32_t)r[4 * j + 0] + __float_as_int(bv.x), as, wv.x, ep.out_scale, ep.out_rcp, zero_f);
+                            const int32_t q1 = epi_i8_sat<true>((int32_t)r[4 * j + 1] + __float_as_int(bv.y), as, wv.y, ep.out_scale, ep.out_rcp, zero_f);
+                            const int32_t q2 = epi_i8_sat<true>((int32_t)r[4 * j + 2] + __float_as_int(bv.z), as, wv.z, ep.out_scale, ep.out_rcp, zero_f);
+                            const int32_t q3 = epi_i8_sat<true>((int32_t)r[4 * j + 3] + __float_as_int(bv.w), as, wv.w, ep.out_scale, ep.out_rcp, zero_f);
+                            packed[j] = __byte_perm(__byte_perm(q0, q1, 0x0040), __byte_perm(q2, q3, 0x0040), 0x5410);
+                        }
+                    } else if (fast) {
 #pragma unroll
                         for (int j = 0; j < 8; j++) {
                             const float4 wv = w4[j], bv = b4[j];

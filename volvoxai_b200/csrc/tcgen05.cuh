@@ -138,6 +138,34 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
     return d;
 }
 
+// The same descriptor split in words: the high word (stride, version, swizzle) is one constant
+// for every such tile, the low word carries the start address. An MMA-issuing thread that keeps
+// low words in registers spends fewer instructions between two MMAs, and that time is exposed
+// tensor-pipe idle time (the pipe does not run ahead of the issuing thread by more than one MMA).
+constexpr uint32_t kSmemDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t smem_addr) { return ((smem_addr >> 4) & 0x3fffu) | (1u << 16); }
+// D[tmem] += A * B (accumulate always), descriptors by low word
+__device__ __forceinline__ void umma_i8_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.eq.b32 p, 0, 0;\n\t"
+        "mov.b64 da, {%1, %4};\n\t"
+        "mov.b64 db, {%2, %4};\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(kSmemDescHi) : "memory");
+}
+// ... D = A * B when accumulate == 0
+__device__ __forceinline__ void umma_i8_lo_first(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                                 uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 da, {%1, %4};\n\t"
+        "mov.b64 db, {%2, %4};\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(kSmemDescHi), "r"(accumulate) : "memory");
+}
+
 // Instruction descriptor, kind::i8: D = S32 (bits 4-5 = 2), A and B signed
 // 8-bit (bits 7-9 and 10-12 = 1), both K-major (bits 15, 16 = 0), N>>3 at
 // bits 17-22, M>>4 at bits 24-28, dense, no saturation.
