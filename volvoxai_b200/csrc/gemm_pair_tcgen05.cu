@@ -8,14 +8,14 @@
 // stages are all the shared memory holds - barely one L2 round trip of cover. In a pair, CTA r
 // loads its own 128 activation rows and only HALF of the tile's 256 weight rows (channels
 // n0 + 128 r ...); the pair's MMA reads the other half from the partner's shared memory. Each SM
-// now pulls 32 KB per 128 bytes of K for the same MMA time, and six stages fit.
+// now pulls 32 KB per 128 bytes of K for the same MMA time; the ring holds 3 stages of 256 K bytes.
 //
 // Per CTA (same warp roles as the single-CTA kernel):
-//   warp 0      TMA producer, activation tile (128 rows x 128 B) of each stage
-//   warp 10     TMA producer, weight half-tile (128 channels x 128 B) of each stage
+//   warp 0      TMA producer, activation tiles (two of 128 rows x 128 B) of each stage
+//   warp 10     TMA producer, weight half-tiles (two of 128 channels x 128 B) of each stage
 //               both complete on the LEADER's (cluster rank 0) full barrier of the stage
 //   warp 1      allocates TMEM (cta_group::2); in the leader one lane issues
-//               tcgen05.mma.cta_group::2.kind::i8 (M256 x N256 x K32, 4 per stage) and commits
+//               tcgen05.mma.cta_group::2.kind::i8 (M256 x N256 x K32, 8 per stage) and commits
 //               to the stage's empty barrier and the accumulator's full barrier of BOTH CTAs
 //   warps 2-9   epilogue of this CTA's 128 rows x 256 columns (its own TMEM), then one arrive
 //               per warp on the leader's accumulator-empty barrier
@@ -35,10 +35,14 @@ using namespace tc;
 constexpr uint32_t kBM = 128;           // activation rows per CTA (256 per pair)
 constexpr uint32_t kBNHalf = 128;       // weight rows loaded per CTA
 constexpr uint32_t kBN = 256;           // output channels per tile
-constexpr uint32_t kBK = 128;           // K bytes per stage
-constexpr uint32_t kStages = 6;
-constexpr uint32_t kABytes = kBM * kBK;            // 16 KiB
-constexpr uint32_t kBBytes = kBNHalf * kBK;        // 16 KiB
+constexpr uint32_t kAtomK = 128;        // K bytes of one swizzle span (one TMA box, four MMAs)
+constexpr uint32_t kBK = 256;           // K bytes per stage: two spans, so that the issuing thread's
+                                        // per-stage work (barrier wait, commits) is paid once per 8 MMAs
+constexpr uint32_t kStages = 3;
+constexpr uint32_t kAAtomBytes = kBM * kAtomK;     // 16 KiB
+constexpr uint32_t kBAtomBytes = kBNHalf * kAtomK; // 16 KiB
+constexpr uint32_t kABytes = 2 * kAAtomBytes;
+constexpr uint32_t kBBytes = 2 * kBAtomBytes;
 constexpr uint32_t kStageBytes = kABytes + kBBytes;
 constexpr uint32_t kAccCols = kBN;
 constexpr uint32_t kTmemCols = 512;
@@ -157,7 +161,7 @@ gemm_i8_pair_kernel(const __grid_constant__ GemmTcgen05Args args) {
     const uint32_t tiles_m = (args.rows + 2 * kBM - 1) / (2 * kBM);
     const uint32_t tiles_n = (args.n + kBN - 1) / kBN;
     const uint32_t total_tiles = tiles_m * tiles_n;
-    const uint32_t num_kb = args.kpad / kBK;
+    const uint32_t num_kb = (args.kpad + kBK - 1) / kBK;   // a last half-empty stage is zero-filled by TMA
     volatile int* abort_flag = sm.abort_flag();
 
     if (threadIdx.x == 0) {
@@ -191,6 +195,7 @@ gemm_i8_pair_kernel(const __grid_constant__ GemmTcgen05Args args) {
                     // the leader's barrier collects the bytes of both CTAs' copies of the stage
                     if (rank == 0) mbar_expect_tx(sm.full(stage), 2 * kStageBytes);
                     tma_load_2d_pair(sm.a(stage), &args.tmap_a, in_cta(sm.full(stage), 0), (int32_t)(kb * kBK), m0);
+                    tma_load_2d_pair(sm.a(stage) + kAAtomBytes, &args.tmap_a, in_cta(sm.full(stage), 0), (int32_t)(kb * kBK + kAtomK), m0);
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -205,6 +210,7 @@ gemm_i8_pair_kernel(const __grid_constant__ GemmTcgen05Args args) {
                 for (uint32_t kb = 0; kb < num_kb; kb++) {
                     if (!mbar_wait(sm.empty(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
                     tma_load_2d_pair(sm.b(stage), &args.tmap_b, in_cta(sm.full(stage), 0), (int32_t)(kb * kBK), n0);
+                    tma_load_2d_pair(sm.b(stage) + kBAtomBytes, &args.tmap_b, in_cta(sm.full(stage), 0), (int32_t)(kb * kBK + kAtomK), n0);
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -225,10 +231,16 @@ gemm_i8_pair_kernel(const __grid_constant__ GemmTcgen05Args args) {
                 for (uint32_t kb = 0; kb < num_kb; kb++) {
                     if (!mbar_try_wait(full_s, phase) && !mbar_wait(full_s, phase, abort_flag)) { ok = false; break; }
                     tc_fence_after();
-                    umma_i8_pair_lo_first(d_tmem, a_lo, a_lo + (kABytes >> 4), idesc, kb);
-                    umma_i8_pair_lo(d_tmem, a_lo + 2u, a_lo + (kABytes >> 4) + 2u, idesc);
-                    umma_i8_pair_lo(d_tmem, a_lo + 4u, a_lo + (kABytes >> 4) + 4u, idesc);
-                    umma_i8_pair_lo(d_tmem, a_lo + 6u, a_lo + (kABytes >> 4) + 6u, idesc);
+                    const uint32_t b_lo = a_lo + (kABytes >> 4);
+                    umma_i8_pair_lo_first(d_tmem, a_lo, b_lo, idesc, kb);       // +32 bytes of K = +2
+                    umma_i8_pair_lo(d_tmem, a_lo + 2u, b_lo + 2u, idesc);
+                    umma_i8_pair_lo(d_tmem, a_lo + 4u, b_lo + 4u, idesc);
+                    umma_i8_pair_lo(d_tmem, a_lo + 6u, b_lo + 6u, idesc);
+                    constexpr uint32_t kA2 = kAAtomBytes >> 4, kB2 = kBAtomBytes >> 4;   // the second span's tiles
+                    umma_i8_pair_lo(d_tmem, a_lo + kA2, b_lo + kB2, idesc);
+                    umma_i8_pair_lo(d_tmem, a_lo + kA2 + 2u, b_lo + kB2 + 2u, idesc);
+                    umma_i8_pair_lo(d_tmem, a_lo + kA2 + 4u, b_lo + kB2 + 4u, idesc);
+                    umma_i8_pair_lo(d_tmem, a_lo + kA2 + 6u, b_lo + kB2 + 6u, idesc);
                     // the stage is free again in both CTAs once these MMAs have read it
                     umma_commit_pair(empty_s);
                     umma_commit_pair(empty_s + peer_delta);
