@@ -288,10 +288,13 @@ decode_rows_kernel(const __grid_constant__ DecodeRowsArgs args) {
                     if (!mbar_wait(fb, cphase, abort_flag)) { ok = false; break; }
                     tc_fence_after();
                     if ((t | kb) == 0) stamp(args.trace, 2);
-                    const uint64_t da = make_smem_desc(xa), db = make_smem_desc(wa);
-#pragma unroll
-                    for (uint32_t k = 0; k < kRK / kUmmaK; k++)   // +32 bytes of K = +2 in the descriptor's address field
-                        umma_i8(d_tmem, da + 2u * k, db + 2u * k, idesc, (first && k == 0u) ? 0u : 1u);
+                    // descriptors by their low words: the time this thread spends between two MMAs is
+                    // tensor-pipe idle time
+                    const uint32_t da = smem_desc_lo(xa), db = smem_desc_lo(wa);
+                    umma_i8_lo_first(d_tmem, da, db, idesc, first ? 0u : 1u);   // +32 bytes of K = +2
+                    umma_i8_lo(d_tmem, da + 2u, db + 2u, idesc);
+                    umma_i8_lo(d_tmem, da + 4u, db + 4u, idesc);
+                    umma_i8_lo(d_tmem, da + 6u, db + 6u, idesc);
                     first = 0;
                     umma_commit(eb);
                     wa += wstep; fb += 8 * I; eb += 8 * I; xa += xstep;

@@ -36,13 +36,14 @@ constexpr uint32_t kBM = 128;           // activation rows per CTA (256 per pair
 constexpr uint32_t kBNHalf = 128;       // weight rows loaded per CTA
 constexpr uint32_t kBN = 256;           // output channels per tile
 constexpr uint32_t kAtomK = 128;        // K bytes of one swizzle span (one TMA box, four MMAs)
-constexpr uint32_t kBK = 256;           // K bytes per stage: two spans, so that the issuing thread's
+constexpr uint32_t kAtoms = 2;
+constexpr uint32_t kBK = kAtoms * kAtomK;           // K bytes per stage: two spans, so that the issuing thread's
                                         // per-stage work (barrier wait, commits) is paid once per 8 MMAs
 constexpr uint32_t kStages = 3;
 constexpr uint32_t kAAtomBytes = kBM * kAtomK;     // 16 KiB
 constexpr uint32_t kBAtomBytes = kBNHalf * kAtomK; // 16 KiB
-constexpr uint32_t kABytes = 2 * kAAtomBytes;
-constexpr uint32_t kBBytes = 2 * kBAtomBytes;
+constexpr uint32_t kABytes = kAtoms * kAAtomBytes;
+constexpr uint32_t kBBytes = kAtoms * kBAtomBytes;
 constexpr uint32_t kStageBytes = kABytes + kBBytes;
 constexpr uint32_t kAccCols = kBN;
 constexpr uint32_t kTmemCols = 512;
@@ -194,8 +195,9 @@ gemm_i8_pair_kernel(const __grid_constant__ GemmTcgen05Args args) {
                     if (!mbar_wait(sm.empty(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
                     // the leader's barrier collects the bytes of both CTAs' copies of the stage
                     if (rank == 0) mbar_expect_tx(sm.full(stage), 2 * kStageBytes);
-                    tma_load_2d_pair(sm.a(stage), &args.tmap_a, in_cta(sm.full(stage), 0), (int32_t)(kb * kBK), m0);
-                    tma_load_2d_pair(sm.a(stage) + kAAtomBytes, &args.tmap_a, in_cta(sm.full(stage), 0), (int32_t)(kb * kBK + kAtomK), m0);
+#pragma unroll
+                    for (uint32_t a = 0; a < kAtoms; a++)
+                        tma_load_2d_pair(sm.a(stage) + a * kAAtomBytes, &args.tmap_a, in_cta(sm.full(stage), 0), (int32_t)(kb * kBK + a * kAtomK), m0);
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -209,8 +211,9 @@ gemm_i8_pair_kernel(const __grid_constant__ GemmTcgen05Args args) {
                 const int32_t n0 = (int32_t)((t / tiles_m) * kBN + rank * kBNHalf);
                 for (uint32_t kb = 0; kb < num_kb; kb++) {
                     if (!mbar_wait(sm.empty(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
-                    tma_load_2d_pair(sm.b(stage), &args.tmap_b, in_cta(sm.full(stage), 0), (int32_t)(kb * kBK), n0);
-                    tma_load_2d_pair(sm.b(stage) + kBAtomBytes, &args.tmap_b, in_cta(sm.full(stage), 0), (int32_t)(kb * kBK + kAtomK), n0);
+#pragma unroll
+                    for (uint32_t a = 0; a < kAtoms; a++)
+                        tma_load_2d_pair(sm.b(stage) + a * kBAtomBytes, &args.tmap_b, in_cta(sm.full(stage), 0), (int32_t)(kb * kBK + a * kAtomK), n0);
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -236,11 +239,14 @@ gemm_i8_pair_kernel(const __grid_constant__ GemmTcgen05Args args) {
                     umma_i8_pair_lo(d_tmem, a_lo + 2u, b_lo + 2u, idesc);
                     umma_i8_pair_lo(d_tmem, a_lo + 4u, b_lo + 4u, idesc);
                     umma_i8_pair_lo(d_tmem, a_lo + 6u, b_lo + 6u, idesc);
-                    constexpr uint32_t kA2 = kAAtomBytes >> 4, kB2 = kBAtomBytes >> 4;   // the second span's tiles
-                    umma_i8_pair_lo(d_tmem, a_lo + kA2, b_lo + kB2, idesc);
-                    umma_i8_pair_lo(d_tmem, a_lo + kA2 + 2u, b_lo + kB2 + 2u, idesc);
-                    umma_i8_pair_lo(d_tmem, a_lo + kA2 + 4u, b_lo + kB2 + 4u, idesc);
-                    umma_i8_pair_lo(d_tmem, a_lo + kA2 + 6u, b_lo + kB2 + 6u, idesc);
+#pragma unroll
+                    for (uint32_t a = 1; a < kAtoms; a++) {   // the other spans' tiles
+                        const uint32_t a2 = a_lo + a * (kAAtomBytes >> 4), b2 = b_lo + a * (kBAtomBytes >> 4);
+                        umma_i8_pair_lo(d_tmem, a2, b2, idesc);
+                        umma_i8_pair_lo(d_tmem, a2 + 2u, b2 + 2u, idesc);
+                        umma_i8_pair_lo(d_tmem, a2 + 4u, b2 + 4u, idesc);
+                        umma_i8_pair_lo(d_tmem, a2 + 6u, b2 + 6u, idesc);
+                    }
                     // the stage is free again in both CTAs once these MMAs have read it
                     umma_commit_pair(empty_s);
                     umma_commit_pair(empty_s + peer_delta);
