@@ -117,11 +117,14 @@ __device__ __forceinline__ int32_t epi_i8_v2(int32_t acc, float as, float ws, fl
 // ws and out_scale within 2^+-30 keep every intermediate finite (|acc| < 2^31, multiplier < 2^90),
 // so no NaN can appear, and round + saturate is one conversion instruction. Same result as
 // epi_i8 bit for bit there.
-template <bool UNSIGNED>
+template <bool UNSIGNED, bool ADD_ZERO = true>
 __device__ __forceinline__ int32_t epi_i8_sat(int32_t acc, float as, float ws, float out_scale,
                                               float out_rcp, float zero_f) {
     const float mult = div_const(__fmul_rn(as, ws), out_scale, out_rcp);
-    const float moved = __fadd_rn(__fmul_rn(__int2float_rn(acc), mult), zero_f);
+    // a zero point of 0 needs no addition (ADD_ZERO = false): x + 0 = x except -0 + 0 = +0, and
+    // both convert to 0
+    const float scaled = __fmul_rn(__int2float_rn(acc), mult);
+    const float moved = ADD_ZERO ? __fadd_rn(scaled, zero_f) : scaled;
     int32_t q;
     if (UNSIGNED) asm("cvt.rni.sat.u8.f32 %0, %1;" : "=r"(q) : "f"(moved));
     else asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q) : "f"(moved));
