@@ -412,28 +412,33 @@ def test_host_whole_op_entry_matches_device_entries(torch, ctx, rows):
 
 # ---- size-independent properties at benchmark sizes ---------------------------------------------
 
-def test_full_size_properties(torch, ctx, oracle):
-    """M2048 K4096 N14336 (too large for the scalar oracle in seconds): (a) a random sample of
-    512 outputs against exact NumPy int64 dots, (b) row permutation invariance - row r of a
+@pytest.mark.parametrize("rows,k,n", [(2048, 4096, 14336), (2048, 8192, 28672), (2048, 4096, 128256), (16384, 4096, 14336)])
+def test_full_size_properties(torch, ctx, oracle, rows, k, n):
+    """The compute-bound sweep's shapes (too large for the scalar oracle in seconds): (a) a random
+    sample of 512 outputs against exact int64 dots, (b) row permutation invariance - row r of a
     permuted input equals the permuted row of the output, bit for bit, (c) checksum of the int32
-    accumulators equals sum_k (sum_m q[m,k]) * (sum_n w[n,k])."""
+    accumulators equals sum_k (sum_m q[m,k]) * (sum_n w[n,k]). Reductions run on the device."""
     from volvoxai_b200 import w8a8
-    rows, k, n = 2048, 4096, 14336
     c = wl.gemm_case(rows, k, n, seed=1, weights_fast=True)
     weight = w8a8.Weight.from_i8(ctx, c["w"], c["ws"])
     xd = dev(torch, c["x"])
     acc, q, s = ctx.linear_acc_i32(weight, xd, want_q=True)
     ctx.synchronize()
-    acc, q = acc.cpu().numpy(), q.cpu().numpy()
     qo, so, _ = oracle.quantize_rows(c["x"][:64])
-    assert np.array_equal(q[:64], qo) and np.array_equal(s.cpu().numpy()[:64].view(np.uint32), so.view(np.uint32))
+    assert np.array_equal(q[:64].cpu().numpy(), qo) and np.array_equal(s[:64].cpu().numpy().view(np.uint32), so.view(np.uint32))
     rng = np.random.default_rng(0)
-    for _ in range(512):
-        m, j = int(rng.integers(rows)), int(rng.integers(n))
-        assert acc[m, j] == int(q[m].astype(np.int64) @ c["w"][j].astype(np.int64))
-    colsum_q = q.astype(np.int64).sum(axis=0)
-    colsum_w = c["w"].astype(np.int64).sum(axis=0)
-    assert int(acc.astype(np.int64).sum()) == int((colsum_q * colsum_w).sum())
+    ms = rng.integers(rows, size=512)
+    js = rng.integers(n, size=512)
+    got = acc[torch.from_numpy(ms).cuda(), torch.from_numpy(js).cuda()].cpu().numpy()
+    qs = q[torch.from_numpy(ms).cuda()].cpu().numpy().astype(np.int64)
+    want = (qs * c["w"][js].astype(np.int64)).sum(axis=1)
+    assert np.array_equal(got.astype(np.int64), want)
+    wd = dev(torch, c["w"])
+    colsum_q = q.to(torch.int64).sum(dim=0)
+    colsum_w = wd.to(torch.int64).sum(dim=0)
+    total = sum(int(part.to(torch.int64).sum().item()) for part in acc.split(1024))
+    assert total == int((colsum_q * colsum_w).sum().item())
+    del wd
     perm = rng.permutation(rows)
     os_ = 0.05
     y8 = ctx.linear_i8(weight, xd, os_, 0)
@@ -441,8 +446,28 @@ def test_full_size_properties(torch, ctx, oracle):
     ctx.synchronize()
     assert torch.equal(y8p, y8[torch.from_numpy(perm).cuda()])
     # spot-check E2 bytes of 8 rows against the oracle's requantizer on the exact accumulators
-    want = oracle.requant_rows(acc[:8], s.cpu().numpy()[:8], None, c["ws"], None, os_, 0)
-    assert np.array_equal(y8.cpu().numpy()[:8], want)
+    want8 = oracle.requant_rows(acc[:8].cpu().numpy(), s[:8].cpu().numpy(), None, c["ws"], None, os_, 0)
+    assert np.array_equal(y8[:8].cpu().numpy(), want8)
+    weight.close()
+
+
+@pytest.mark.parametrize("rows", [1, 8, 32])
+@pytest.mark.parametrize("k,n", [(4096, 4096), (4096, 14336), (14336, 4096)])
+def test_decode_sweep_shapes_exact(torch, ctx, rows, k, n):
+    """The memory-bound sweep's shapes through the automatic route: every accumulator against an
+    exact int64 matrix product on the device, fp32 outputs against the same product scaled."""
+    from volvoxai_b200 import w8a8
+    c = wl.gemv_case(rows, k, n, seed=rows + k)
+    weight = w8a8.Weight.from_i8(ctx, c["w"], c["ws"])
+    xd = dev(torch, c["x"])
+    acc, q, s = ctx.linear_acc_i32(weight, xd, want_q=True)
+    y = ctx.linear_f32(weight, xd)
+    ctx.synchronize()
+    assert "decode" in w8a8.last_route()
+    want = (q.to(torch.float64) @ dev(torch, c["w"]).to(torch.float64).T)      # exact: |sum| < 2^53
+    assert torch.equal(acc.to(torch.float64), want)
+    ref = (want.to(torch.float32) * (s[:, None] * dev(torch, c["ws"])[None, :]))
+    assert torch.equal(y, ref)
     weight.close()
 
 
