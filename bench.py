@@ -447,11 +447,11 @@ def gpu_arm(args):
                                  if quant_ms > 0 else None),
     }
     # DRAM traffic per launch, scaled from the ncu capture of a smaller launch of the same kernel
-    # (M 4096, K 4096, N 14336: dram read 75.64 MB = 1.002 x (M + N_local) x Kpad, dram write 27.3 MB =
-    # 0.466 x M x N_local; see profiles/gemm_i8_tcgen05_M4096_K4096_N14336.md). Reads grow with
+    # (M 4096, K 4096, N 14336: dram read 75.73 MB = 1.003 x (M + N_local) x Kpad, dram write 29.4 MB =
+    # 0.50 x M x N_local; see profiles/gemm_i8_pair_M4096_K4096_N14336.md). Reads grow with
     # (M + N) x K, writes with M x N.
     kpad = (k + 127) // 128 * 128
-    roofline["traffic"] = 1.002 * (m + n_local) * kpad + 0.466 * m * n_local
+    roofline["traffic"] = 1.003 * (m + n_local) * kpad + 0.50 * m * n_local
     roofline["traffic_source"] = "ncu dram__bytes_read+write of the M4096 launch, scaled by (M+N)K and MN"
     roofline["algorithmic_bytes"] = (m + n_local) * kpad + m * n_local
     if world > 1:
