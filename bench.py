@@ -312,6 +312,84 @@ def gemv_sweep(torch, ctx, w8a8, peaks, launches=24, replays=5):
     return out
 
 
+def model_linear_stacks(torch, ctx, w8a8, peaks, replays=5):
+    """The W8A8 linears of the two decoder configurations, all layers with their own weights, one
+    CUDA graph per pass (fp32 epilogue): the prefill batch of the SmolLM2-135M shape (8 x 512
+    tokens) and one decode step of the Qwen3-0.6B shape at batch 64.  Two ways of calling:
+    "per_linear" = seven vxb_linear_f32 calls per layer (quantizer + GEMM each); "shared" = what
+    the reference's fused decode patterns do with the same arithmetic: q/k/v and gate/up read
+    the same activations, so their weights are concatenated along the output channels and the
+    activations are quantized once (vxb_quantize_rows + vxb_linear_prepared): four quantizer and
+    four GEMM launches per layer.  Only the linears run here (no attention, norms or embedding),
+    so tokens/s is the rate the linear stack alone would allow."""
+    out = {}
+    for name, cfg in (("smollm2_135m_prefill_8x512", wl.SMOLLM2_135M), ("qwen3_0.6b_decode_b64", wl.QWEN3_0_6B)):
+        rows, layers, lin = cfg["rows"], cfg["layers"], cfg["linears"]
+        rng = np.random.default_rng(layers)
+        groups = [("q", "k", "v"), ("o",), ("gate", "up"), ("down",)]
+        per_linear, shared, ops, wbytes, iobytes = [], [], 0.0, 0, 0
+        for layer in range(layers):
+            raw = {}
+            for lname, (k, n) in lin.items():
+                raw[lname] = (rng.integers(-127, 128, size=(n, k), dtype=np.int8),
+                              rng.uniform(0.001, 0.02, size=n).astype(np.float32))
+                ops += 2.0 * rows * k * n
+                wbytes += k * n + 4 * n
+                iobytes += 4 * rows * n
+            iobytes += sum(4 * rows * lin[g[0]][0] for g in groups)     # each distinct input read once
+            per_linear.append({ln: w8a8.Weight.from_i8(ctx, *raw[ln]) for ln in lin})
+            shared.append([w8a8.Weight.from_i8(ctx, np.concatenate([raw[ln][0] for ln in g]),
+                                               np.concatenate([raw[ln][1] for ln in g])) for g in groups])
+        xs = {k: torch.randn(rows, k, device="cuda") for k in {kn[0] for kn in lin.values()}}
+        ys = {n: torch.empty(rows, n, device="cuda") for n in
+              {kn[1] for kn in lin.values()} | {sum(lin[ln][1] for ln in g) for g in groups}}
+
+        def pass_per_linear():
+            for row in per_linear:
+                for lname, (k, n) in lin.items():
+                    ctx.linear_f32(row[lname], xs[k], out=ys[n])
+
+        def pass_shared():
+            for row in shared:
+                for g, wt in zip(groups, row):
+                    q, sc = ctx.prepare(wt, xs[lin[g[0]][0]])
+                    ctx.linear_prepared(wt, q, sc, ys[wt.d_out], mode=1)
+
+        rec = {"rows": rows, "layers": layers, "weight_bytes": wbytes, "activation_bytes": iobytes}
+        for label, fn in (("per_linear", pass_per_linear), ("shared", pass_shared)):
+            fn()
+            route = w8a8.last_route()
+            torch.cuda.synchronize()
+            side = torch.cuda.Stream()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                ctx.use_torch_stream()
+                fn()
+            ctx.use_torch_stream()
+            g.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(replays):
+                g.replay()
+            e1.record()
+            e1.synchronize()
+            ms = e0.elapsed_time(e1) / replays
+            rec[label] = {"launches_per_layer": 14 if label == "per_linear" else 8, "ms_per_pass": ms,
+                          "tokens_per_s_linears_only": rows / (ms * 1e-3), "tops": ops / (ms * 1e-3) / 1e12,
+                          "gbs": (wbytes + iobytes) / (ms * 1e-3) / 1e9,
+                          "frac_of_measured_hbm": (wbytes + iobytes) / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                          "last_route": route}
+        out[name] = rec
+        for row in per_linear:
+            for wt in row.values():
+                wt.close()
+        for row in shared:
+            for wt in row:
+                wt.close()
+    return out
+
+
 def gpu_arm(args):
     import torch
     import torch.distributed as dist
@@ -508,7 +586,8 @@ def gpu_arm(args):
     elif rank == 0:
         line["cpu_baseline"] = None
     if rank == 0 and world == 1 and not args.no_extras:
-        line["extras"] = {"gemv_sweep": gemv_sweep(torch, ctx, w8a8, peaks)}
+        line["extras"] = {"gemv_sweep": gemv_sweep(torch, ctx, w8a8, peaks),
+                          "model_linear_stacks": model_linear_stacks(torch, ctx, w8a8, peaks)}
 
     weight.close()
     ctx.close()

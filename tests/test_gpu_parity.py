@@ -38,7 +38,7 @@ def rel_err(y, ref):
     return float(np.abs(y[ok].astype(np.float64) - ref[ok]).max() / max(rms, 1e-30)) if ok.any() else 0.0
 
 
-ROUTES = {"gemv": 1, "tcgen05": 2, "simt": 3, "decode": 4, "streamk": 5, "pair": 6}
+ROUTES = {"auto": 0, "gemv": 1, "tcgen05": 2, "simt": 3, "decode": 4, "streamk": 5, "pair": 6}
 
 
 def run_case(torch, ctx, oracle, case, routes, bias_i32=None, out_zero=0):
@@ -469,6 +469,21 @@ def test_decode_sweep_shapes_exact(torch, ctx, rows, k, n):
     ref = (want.to(torch.float32) * (s[:, None] * dev(torch, c["ws"])[None, :]))
     assert torch.equal(y, ref)
     weight.close()
+
+
+def _model_linear_cases():
+    for cfg, rows in ((wl.SMOLLM2_135M, 384), (wl.QWEN3_0_6B, 64)):
+        for name, (k, n) in sorted(set(cfg["linears"].items())):
+            yield pytest.param(rows, k, n, id=f"{cfg['layers']}l-{name}-{rows}x{k}x{n}")
+
+
+@pytest.mark.parametrize("rows,k,n", list(_model_linear_cases()))
+def test_decoder_configuration_linear_shapes(torch, ctx, oracle, rows, k, n):
+    """Every linear shape of the two decoder configurations (a 384-row slice of the prefill batch;
+    the decode batch of 64) through the automatic route, against the oracle: codes, scales,
+    accumulators and requantized bytes bit for bit, fp32 within the stated tolerance."""
+    c = wl.single_linear(rows=rows, k=k, n=n, seed=k + n)
+    run_case(torch, ctx, oracle, c, ["auto"], bias_i32=None, out_zero=0)
 
 
 # ---- boundary ops of a static W8A8 island --------------------------------------------------

@@ -28,6 +28,15 @@ QWEN3_LINEARS = {"q": (1024, 2048), "k": (1024, 1024), "v": (1024, 1024), "o": (
                  "gate": (1024, 3072), "up": (1024, 3072), "down": (3072, 1024)}
 
 
+# Linear layers of the two decoder configurations: name -> (K, N); every layer has one of each.
+SMOLLM2_135M = {"layers": 30, "rows": 8 * 512,
+                "linears": {"q": (576, 576), "k": (576, 192), "v": (576, 192), "o": (576, 576),
+                            "gate": (576, 1536), "up": (576, 1536), "down": (1536, 576)}}
+QWEN3_0_6B = {"layers": 28, "rows": 64,
+              "linears": {"q": (1024, 2048), "k": (1024, 1024), "v": (1024, 1024), "o": (2048, 1024),
+                          "gate": (1024, 3072), "up": (1024, 3072), "down": (3072, 1024)}}
+
+
 def quantize_weight_per_channel(wf: np.ndarray):
     """fp32 [N,K] -> (int8 [N,K], fp32 scales [N]) as the reference's PTQ packer does."""
     wf = np.asarray(wf, np.float32)
