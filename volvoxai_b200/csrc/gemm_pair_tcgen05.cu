@@ -55,7 +55,9 @@ constexpr uint32_t kEpiCols = kBN / 2;              // columns per epilogue warp
 constexpr uint32_t kOffStages = 0;
 constexpr uint32_t kOffWs = kStages * kStageBytes;                   // float[8 warps][128]
 constexpr uint32_t kOffBias = kOffWs + kEpiWarps * kEpiCols * 4;
-constexpr uint32_t kOffBars = kOffBias + kEpiWarps * kEpiCols * 4;
+constexpr uint32_t kOffStore = kOffBias + kEpiWarps * kEpiCols * 4;   // [8 warps][16 rows x 128 B] store staging
+constexpr uint32_t kStoreBytes = 16 * 128;
+constexpr uint32_t kOffBars = kOffStore + kEpiWarps * kStoreBytes;
 constexpr uint32_t kNumBars = 2 * kStages + 4;
 constexpr uint32_t kOffTmemPtr = kOffBars + kNumBars * 8;
 constexpr uint32_t kOffAbort = kOffTmemPtr + 4;
@@ -302,7 +304,9 @@ gemm_i8_pair_kernel(const __grid_constant__ GemmTcgen05Args args) {
                 tmem_ld32(taddr + c, r);
                 tmem_ld_wait();
                 const uint32_t col = n0 + c;
-                if (!row_ok || col >= args.n) continue;
+                if (col >= args.n) continue;                       // uniform over the warp
+                const bool wide = ep.mode != kEpiI8;                // 32-bit outputs go through the staging below
+                if (!row_ok && !wide) continue;
                 const bool full = col + 32 <= args.n;
                 const float4* w4 = reinterpret_cast<const float4*>(s_ws + c);
                 const float4* b4 = reinterpret_cast<const float4*>(s_bias + c);
@@ -385,15 +389,39 @@ gemm_i8_pair_kernel(const __grid_constant__ GemmTcgen05Args args) {
 #pragma unroll
                         for (int i = 0; i < 32; i++) o[i] = r[i];
                     }
-                    uint32_t* dst = (uint32_t*)ep.out + (size_t)row * ep.ld + col;
-                    if (full && (((uintptr_t)dst) & 15u) == 0) {
+                    // Each thread holds 128 contiguous bytes of its own row; stored directly, one store
+                    // instruction touches 32 different rows. Instead the warp passes 16 rows at a time
+                    // through shared memory (16-byte pieces XOR-swizzled by row: no bank conflicts either
+                    // way) and stores whole 128-byte row segments, four rows per instruction.
+                    uint8_t* stage = sm.base + kOffStore + (warp - 2u) * kStoreBytes;
 #pragma unroll
-                        for (int j = 0; j < 8; j++)
-                            reinterpret_cast<uint4*>(dst)[j] = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
-                    } else {
+                    for (uint32_t half16 = 0; half16 < 2; half16++) {
+                        __syncwarp();
+                        if ((lane >> 4) == half16) {
+                            uint8_t* mine = stage + (lane & 15u) * 128u;
 #pragma unroll
-                        for (int i = 0; i < 32; i++)
-                            if (col + i < args.n) dst[i] = o[i];
+                            for (uint32_t j = 0; j < 8; j++)
+                                *reinterpret_cast<uint4*>(mine + ((j ^ (lane & 7u)) << 4)) =
+                                    make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+                        }
+                        __syncwarp();
+                        const uint32_t piece = lane & 7u;
+#pragma unroll
+                        for (uint32_t i = 0; i < 4; i++) {
+                            const uint32_t rl = 4u * i + (lane >> 3);                 // row within the 16
+                            const uint4 v = *reinterpret_cast<const uint4*>(stage + rl * 128u + ((piece ^ (rl & 7u)) << 4));
+                            const uint32_t grow = m0 + quarter * 32u + half16 * 16u + rl, gcol = col + piece * 4u;
+                            if (grow >= args.rows || gcol >= args.n) continue;
+                            uint32_t* dst = (uint32_t*)ep.out + (size_t)grow * ep.ld + gcol;
+                            if (gcol + 4u <= args.n && (((uintptr_t)dst) & 15u) == 0) {
+                                *reinterpret_cast<uint4*>(dst) = v;
+                            } else {
+                                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                                for (uint32_t e = 0; e < 4; e++)
+                                    if (gcol + e < args.n) dst[e] = w[e];
+                            }
+                        }
                     }
                 }
             }
