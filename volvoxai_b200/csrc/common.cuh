@@ -131,6 +131,70 @@ __device__ __forceinline__ int32_t epi_i8_sat(int32_t acc, float as, float ws, f
     return q;
 }
 
+// The same two elements at a time with the packed fp32 instructions of sm_100 (mul/fma.rn.f32x2:
+// each half rounded to nearest like the scalar instruction, subnormals kept), which halves the
+// floating-point instruction count of the requantization. A pair lives in a 64-bit register.
+__device__ __forceinline__ uint64_t f32x2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ uint64_t mul_f32x2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+// Constants of one thread's requantization, each duplicated into both halves.
+struct RequantPair {
+    uint64_t as2, rcp2, neg_d2;
+    float zero;
+    __device__ __forceinline__ RequantPair(float as, float out_scale, float out_rcp, float zero_f)
+        : as2(f32x2(as, as)), rcp2(f32x2(out_rcp, out_rcp)), neg_d2(f32x2(-out_scale, -out_scale)),
+          zero(zero_f) {}
+};
+// epi_i8_sat for the accumulators (acc0, acc1) of two neighbouring channels with scales ws2.
+template <bool UNSIGNED, bool ADD_ZERO>
+__device__ __forceinline__ void epi_i8_sat2(int32_t acc0, int32_t acc1, uint64_t ws2, const RequantPair& c,
+                                            int32_t& q0, int32_t& q1) {
+    const uint64_t p = mul_f32x2(c.as2, ws2);
+    // div_const, both halves: a * rcp, then two corrections with exact residuals
+    const uint64_t d0 = mul_f32x2(p, c.rcp2);
+    const uint64_t r0 = fma_f32x2(c.neg_d2, d0, p);
+    const uint64_t d1 = fma_f32x2(r0, c.rcp2, d0);
+    const uint64_t r1 = fma_f32x2(c.neg_d2, d1, p);
+    const uint64_t mult = fma_f32x2(r1, c.rcp2, d1);
+    const uint64_t scaled = mul_f32x2(f32x2(__int2float_rn(acc0), __int2float_rn(acc1)), mult);
+    float m0, m1;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(m0), "=f"(m1) : "l"(scaled));
+    // the zero point is added with scalar instructions: a packed add right after the packed
+    // multiply came out as one fused multiply-add (33.4999962 instead of 33.5 in a tie case)
+    if (ADD_ZERO) { m0 = __fadd_rn(m0, c.zero); m1 = __fadd_rn(m1, c.zero); }
+    if (UNSIGNED) {
+        asm("cvt.rni.sat.u8.f32 %0, %1;" : "=r"(q0) : "f"(m0));
+        asm("cvt.rni.sat.u8.f32 %0, %1;" : "=r"(q1) : "f"(m1));
+    } else {
+        asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q0) : "f"(m0));
+        asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q1) : "f"(m1));
+    }
+}
+
+// E1 for two neighbouring channels: (f32(acc) * (as * ws)) + bias, each step rounded; the two
+// multiplications packed, the additions scalar (see epi_i8_sat2).
+__device__ __forceinline__ void epi_f32_2(int32_t acc0, int32_t acc1, uint64_t as2, uint64_t ws2, float bias0, float bias1,
+                                          uint32_t& y0, uint32_t& y1) {
+    const uint64_t combined = mul_f32x2(as2, ws2);
+    const uint64_t product = mul_f32x2(f32x2(__int2float_rn(acc0), __int2float_rn(acc1)), combined);
+    float p0, p1;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(p0), "=f"(p1) : "l"(product));
+    y0 = __float_as_uint(__fadd_rn(p0, bias0));
+    y1 = __float_as_uint(__fadd_rn(p1, bias1));
+}
+
 // One output element through the selected epilogue (scalar path).
 __device__ __forceinline__ void epi_store(const EpilogueParams& p, uint32_t row, uint32_t col,
                                           int32_t acc) {

@@ -314,35 +314,39 @@ gemm_i8_pair_kernel(const __grid_constant__ GemmTcgen05Args args) {
                     int8_t* dst = (int8_t*)ep.out + (size_t)row * ep.ld + col;
                     uint32_t packed[8];
                     if (fast && sat_s8 && !ep.bias_i32 && ep.out_zero == 0) {
-                        // no bias, zero point 0: two instructions fewer per element, and the epilogue's length is what the
-                        // MMA-issuing thread pays for while both run
+                        // no bias, zero point 0: fewest instructions per element, and the epilogue's length
+                        // is what the MMA-issuing thread pays for while both run
+                        const RequantPair rq(as, ep.out_scale, ep.out_rcp, zero_f);
 #pragma unroll
                         for (int j = 0; j < 8; j++) {
                             const float4 wv = w4[j];
-                            const int32_t q0 = epi_i8_sat<false, false>((int32_t)r[4 * j + 0], as, wv.x, ep.out_scale, ep.out_rcp, zero_f);
-                            const int32_t q1 = epi_i8_sat<false, false>((int32_t)r[4 * j + 1], as, wv.y, ep.out_scale, ep.out_rcp, zero_f);
-                            const int32_t q2 = epi_i8_sat<false, false>((int32_t)r[4 * j + 2], as, wv.z, ep.out_scale, ep.out_rcp, zero_f);
-                            const int32_t q3 = epi_i8_sat<false, false>((int32_t)r[4 * j + 3], as, wv.w, ep.out_scale, ep.out_rcp, zero_f);
+                            int32_t q0, q1, q2, q3;
+                            epi_i8_sat2<false, false>((int32_t)r[4 * j + 0], (int32_t)r[4 * j + 1], f32x2(wv.x, wv.y), rq, q0, q1);
+                            epi_i8_sat2<false, false>((int32_t)r[4 * j + 2], (int32_t)r[4 * j + 3], f32x2(wv.z, wv.w), rq, q2, q3);
                             packed[j] = __byte_perm(__byte_perm(q0, q1, 0x0040), __byte_perm(q2, q3, 0x0040), 0x5410);
                         }
                     } else if (fast && sat_s8) {
+                        const RequantPair rq(as, ep.out_scale, ep.out_rcp, zero_f);
 #pragma unroll
                         for (int j = 0; j < 8; j++) {
                             const float4 wv = w4[j], bv = b4[j];
-                            const int32_t q0 = epi_i8_sat<false>((int32_t)r[4 * j + 0] + __float_as_int(bv.x), as, wv.x, ep.out_scale, ep.out_rcp, zero_f);
-                            const int32_t q1 = epi_i8_sat<false>((int32_t)r[4 * j + 1] + __float_as_int(bv.y), as, wv.y, ep.out_scale, ep.out_rcp, zero_f);
-                            const int32_t q2 = epi_i8_sat<false>((int32_t)r[4 * j + 2] + __float_as_int(bv.z), as, wv.z, ep.out_scale, ep.out_rcp, zero_f);
-                            const int32_t q3 = epi_i8_sat<false>((int32_t)r[4 * j + 3] + __float_as_int(bv.w), as, wv.w, ep.out_scale, ep.out_rcp, zero_f);
+                            int32_t q0, q1, q2, q3;
+                            epi_i8_sat2<false, true>((int32_t)r[4 * j + 0] + __float_as_int(bv.x), (int32_t)r[4 * j + 1] + __float_as_int(bv.y),
+                                                     f32x2(wv.x, wv.y), rq, q0, q1);
+                            epi_i8_sat2<false, true>((int32_t)r[4 * j + 2] + __float_as_int(bv.z), (int32_t)r[4 * j + 3] + __float_as_int(bv.w),
+                                                     f32x2(wv.z, wv.w), rq, q2, q3);
                             packed[j] = __byte_perm(__byte_perm(q0, q1, 0x0040), __byte_perm(q2, q3, 0x0040), 0x5410);
                         }
                     } else if (fast && sat_u8) {
+                        const RequantPair rq(as, ep.out_scale, ep.out_rcp, zero_f);
 #pragma unroll
                         for (int j = 0; j < 8; j++) {
                             const float4 wv = w4[j], bv = b4[j];
-                            const int32_t q0 = epi_i8_sat<true>((int32_t)r[4 * j + 0] + __float_as_int(bv.x), as, wv.x, ep.out_scale, ep.out_rcp, zero_f);
-                            const int32_t q1 = epi_i8_sat<true>((int32_t)r[4 * j + 1] + __float_as_int(bv.y), as, wv.y, ep.out_scale, ep.out_rcp, zero_f);
-                            const int32_t q2 = epi_i8_sat<true>((int32_t)r[4 * j + 2] + __float_as_int(bv.z), as, wv.z, ep.out_scale, ep.out_rcp, zero_f);
-                            const int32_t q3 = epi_i8_sat<true>((int32_t)r[4 * j + 3] + __float_as_int(bv.w), as, wv.w, ep.out_scale, ep.out_rcp, zero_f);
+                            int32_t q0, q1, q2, q3;
+                            epi_i8_sat2<true, true>((int32_t)r[4 * j + 0] + __float_as_int(bv.x), (int32_t)r[4 * j + 1] + __float_as_int(bv.y),
+                                                    f32x2(wv.x, wv.y), rq, q0, q1);
+                            epi_i8_sat2<true, true>((int32_t)r[4 * j + 2] + __float_as_int(bv.z), (int32_t)r[4 * j + 3] + __float_as_int(bv.w),
+                                                    f32x2(wv.z, wv.w), rq, q2, q3);
                             packed[j] = __byte_perm(__byte_perm(q0, q1, 0x0040), __byte_perm(q2, q3, 0x0040), 0x5410);
                         }
                     } else if (fast) {
@@ -377,13 +381,12 @@ gemm_i8_pair_kernel(const __grid_constant__ GemmTcgen05Args args) {
                 } else {
                     uint32_t o[32];
                     if (ep.mode == kEpiF32) {
+                        const uint64_t as2 = f32x2(as, as);
 #pragma unroll
                         for (int j = 0; j < 8; j++) {
                             const float4 wv = w4[j], bv = b4[j];
-                            o[4 * j + 0] = __float_as_uint(epi_f32((int32_t)r[4 * j + 0], as, wv.x, bv.x));
-                            o[4 * j + 1] = __float_as_uint(epi_f32((int32_t)r[4 * j + 1], as, wv.y, bv.y));
-                            o[4 * j + 2] = __float_as_uint(epi_f32((int32_t)r[4 * j + 2], as, wv.z, bv.z));
-                            o[4 * j + 3] = __float_as_uint(epi_f32((int32_t)r[4 * j + 3], as, wv.w, bv.w));
+                            epi_f32_2((int32_t)r[4 * j + 0], (int32_t)r[4 * j + 1], as2, f32x2(wv.x, wv.y), bv.x, bv.y, o[4 * j + 0], o[4 * j + 1]);
+                            epi_f32_2((int32_t)r[4 * j + 2], (int32_t)r[4 * j + 3], as2, f32x2(wv.z, wv.w), bv.z, bv.w, o[4 * j + 2], o[4 * j + 3]);
                         }
                     } else {
 #pragma unroll
