@@ -50,10 +50,34 @@ __device__ __forceinline__ int32_t quant1(float v, const RowDivisor& d) {
     return __float2int_rn(r);
 }
 
+// x / scale for two elements with the packed fp32 instructions (div_const, each half rounded like
+// the scalar instruction), then round-to-nearest-even with saturation in one conversion: |x| <=
+// amax = 127 * scale up to rounding, so the quotient never reaches +-127.5 and the int8 saturation
+// bound of the instruction (-128) is never hit - the result is the clamp to +-127 of the contract.
+__device__ __forceinline__ void quant2_fast(float x0, float x1, uint64_t rcp2, uint64_t neg_d2, int32_t& q0, int32_t& q1) {
+    const uint64_t a = f32x2(x0, x1);
+    const uint64_t d0 = mul_f32x2(a, rcp2);
+    const uint64_t r0 = fma_f32x2(neg_d2, d0, a);
+    const uint64_t d1 = fma_f32x2(r0, rcp2, d0);
+    const uint64_t r1 = fma_f32x2(neg_d2, d1, a);
+    const uint64_t q = fma_f32x2(r1, rcp2, d1);
+    float f0, f1;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(f0), "=f"(f1) : "l"(q));
+    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q0) : "f"(f0));
+    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q1) : "f"(f1));
+}
+
 template <bool FAST>
 __device__ __forceinline__ uint32_t pack4t(float4 v, const RowDivisor& d) {
-    const int32_t a = quant1<FAST>(v.x, d), b = quant1<FAST>(v.y, d);
-    const int32_t c = quant1<FAST>(v.z, d), e = quant1<FAST>(v.w, d);
+    int32_t a, b, c, e;
+    if (FAST) {
+        const uint64_t rcp2 = f32x2(d.rcp, d.rcp), neg_d2 = f32x2(-d.scale, -d.scale);
+        quant2_fast(v.x, v.y, rcp2, neg_d2, a, b);
+        quant2_fast(v.z, v.w, rcp2, neg_d2, c, e);
+    } else {
+        a = quant1<false>(v.x, d); b = quant1<false>(v.y, d);
+        c = quant1<false>(v.z, d); e = quant1<false>(v.w, d);
+    }
     return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, e, 0x0040), 0x5410);
 }
 __device__ __forceinline__ uint32_t pack4(float4 v, const RowDivisor& d) {
