@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Generate tests/golden/w8a8_golden.npz from the reference itself.
 
-Run in a container that has the reference checkout (default /root/reference):
+Run where the reference checkout is present (its location: environment variable VX_REFERENCE):
 
     make -C oracle all && python tests/golden/make_golden.py
 
