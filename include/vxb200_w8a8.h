@@ -193,6 +193,21 @@ VXB_API int vxb_requantize_linear_device(VxbContext* ctx, const void* x, uint64_
                                  int32_t input_zero_point, float output_scale, int32_t output_zero_point,
                                  uint32_t input_dtype, uint32_t output_dtype, void* out);
 
+/* ---- fused decode patterns on the fp32 epilogue --------------------------------------------
+ * What the reference's fused GEMV kernels append to a PackedLinear
+ * (native/src/backends/cuda/kernels/cuda_forward_gemv_pair_kernels.inc:406-459 gate/up +
+ * SiLU * Mul, :670-713 projection + residual Add; recognised by
+ * native/src/runtime/incremental_runtime.c:1178-1232):
+ *   residual != NULL           y[m, n] = linear(x)[m, n] + residual[m, n]        (fp32 add, rounded once)
+ *   activation SILU_MUL        the weight's channels are interleaved (gate_0, up_0, gate_1, up_1, ...):
+ *                              y[m, j] = g * sigmoid(g) * u with g, u = linear(x)[m, 2j], [m, 2j+1];
+ *                              y is d_out / 2 wide; no residual in this form
+ * Automatic route only (decode kernel up to 128 rows, tensor-core GEMM above). q/k/v, or gate/up,
+ * share one activation quantization by concatenating their weights along the output channels. */
+enum { VXB_ACT_NONE = 0, VXB_ACT_SILU_MUL = 1 };
+VXB_API int vxb_linear_f32_fused(VxbContext* ctx, const VxbWeight* w, const float* x, uint32_t rows, float* y,
+                         uint32_t ldy, const float* residual, uint32_t ld_residual, int activation);
+
 /* Prepared-activation form, the counterpart of the reference's prepared path
  * (x[4] prepared words / x[5] row scales, native/src/backends/cuda/host/
  * cuda_graph_llm_host.inc:15-107): the caller quantized the rows itself with

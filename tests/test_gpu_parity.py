@@ -486,6 +486,37 @@ def test_decoder_configuration_linear_shapes(torch, ctx, oracle, rows, k, n):
     run_case(torch, ctx, oracle, c, ["auto"], bias_i32=None, out_zero=0)
 
 
+# ---- fused decode patterns on the fp32 epilogue ---------------------------------------------
+
+@pytest.mark.parametrize("rows,k,n", [(1, 256, 384), (3, 1024, 3072), (40, 256, 386), (100, 320, 1000),
+                                      (300, 256, 384), (1000, 576, 1536), (4096, 256, 2560)])
+def test_fused_residual_and_silu_mul(torch, ctx, oracle, rows, k, n):
+    """linear + residual equals the oracle's fp32 output plus the residual, bit for bit; silu(gate) *
+    up over interleaved channel pairs within the fp32 tolerance (the exponential is not part of the
+    bit-exact contract). Decode kernel (both epilogue forms), single-CTA and paired GEMM."""
+    from volvoxai_b200 import w8a8
+    c = wl.single_linear(rows=rows, k=k, n=n, seed=rows + n)
+    ref = oracle.w8a8_linear(c["x"], c["w"], c["ws"], bias=c["bias"])["out"]
+    weight = w8a8.Weight.from_i8(ctx, c["w"], c["ws"], bias_f32=c["bias"])
+    xd = dev(torch, c["x"])
+    rng = np.random.default_rng(rows)
+    res = rng.standard_normal((rows, n)).astype(np.float32)
+    y = ctx.linear_f32_fused(weight, xd, residual=dev(torch, res)).cpu().numpy()
+    plain = ctx.linear_f32(weight, xd).cpu().numpy()
+    assert np.array_equal(y.view(np.uint32), (plain + res).view(np.uint32))
+    assert rel_err(plain, ref) <= F32_TOL
+    s = ctx.linear_f32_fused(weight, xd, silu_mul=True).cpu().numpy()
+    assert s.shape == (rows, n // 2)
+    g, u = plain[:, 0::2].astype(np.float64), plain[:, 1::2].astype(np.float64)
+    want = g / (1.0 + np.exp(-g)) * u
+    assert rel_err(s, want.astype(np.float32)) <= F32_TOL
+    # declined: odd channel count, residual together with the activation
+    with pytest.raises(w8a8.W8A8Error) as e:
+        ctx.linear_f32_fused(weight, xd, residual=dev(torch, res), silu_mul=True)
+    assert e.value.code == 0
+    weight.close()
+
+
 # ---- boundary ops of a static W8A8 island --------------------------------------------------
 
 def _boundary_cases(golden):

@@ -517,6 +517,29 @@ int vxb_linear_f32(VxbContext* ctx, const VxbWeight* w, const float* x, uint32_t
     return run_gemm(ctx, w, (const int8_t*)ctx->q.ptr, rows, epi, route, "k1+");
 }
 
+int vxb_linear_f32_fused(VxbContext* ctx, const VxbWeight* w, const float* x, uint32_t rows, float* y,
+                         uint32_t ldy, const float* residual, uint32_t ld_residual, int activation) {
+    if (!ctx || !w || !x || !y) return fail(0, "null argument");
+    if (w->device != ctx->device) return fail(0, "weight lives on device %d, context on %d", w->device, ctx->device);
+    if (activation != VXB_ACT_NONE && activation != VXB_ACT_SILU_MUL) return fail(0, "unknown activation %d", activation);
+    if (w->group) return fail(0, "weights with grouped scales have no fused epilogue");
+    const uint32_t width = activation == VXB_ACT_SILU_MUL ? w->d_out / 2 : w->d_out;
+    if (activation == VXB_ACT_SILU_MUL && ((w->d_out & 1u) || residual))
+        return fail(0, "SiLU * up needs an even channel count and takes no residual");
+    if (ldy < width) return fail(0, "output row stride %u < output width %u", ldy, width);
+    if (residual && ld_residual < width) return fail(0, "residual row stride %u < output width %u", ld_residual, width);
+    if (!rows) return 1;
+    if (ensure_device(ctx) != 1) return -1;
+    int rc;
+    if ((rc = quantize_into_scratch(ctx, w, x, rows)) != 1) return rc;
+    EpilogueParams epi{};
+    epi.mode = kEpiF32; epi.row_scales = (const float*)ctx->row_scales.ptr; epi.ws = w->ws;
+    epi.bias_f32 = w->bias_f32; epi.out = y; epi.ld = ldy;
+    epi.residual = residual; epi.ld_res = ld_residual; epi.act = activation == VXB_ACT_SILU_MUL ? 1u : 0u;
+    // the decode kernel up to 128 rows, the tensor-core GEMM above: both carry the fused forms
+    return run_gemm(ctx, w, (const int8_t*)ctx->q.ptr, rows, epi, VXB_ROUTE_AUTO, "k1+");
+}
+
 int vxb_linear_i8(VxbContext* ctx, const VxbWeight* w, const float* x, uint32_t rows,
                   float out_scale, int32_t out_zero, int8_t* y, uint32_t ldy, int route) {
     int rc = check_common(ctx, w, x, y, ldy);

@@ -36,6 +36,11 @@ struct EpilogueParams {
     uint32_t group, groups;  // K bytes per group (32/64/128/256), groups per channel; 0 = per-channel scales
     uint32_t n_peers;
     void* peer_out[7];
+    // fused decode patterns on the fp32 epilogue (E1): y += residual[m, n], or, with the weight's
+    // channels interleaved as (gate_0, up_0, gate_1, up_1, ...), y[m, j] = silu(gate_j) * up_j
+    const float* residual;   // [rows, ld_res] or null
+    uint32_t ld_res;
+    uint32_t act;            // 0 none, 1 SiLU(gate) * up over channel pairs (output d_out / 2 wide)
 };
 
 // ---- programmatic dependent launch ------------------------------------------------------
@@ -193,6 +198,13 @@ __device__ __forceinline__ void epi_f32_2(int32_t acc0, int32_t acc1, uint64_t a
     asm("mov.b64 {%0, %1}, %2;" : "=f"(p0), "=f"(p1) : "l"(product));
     y0 = __float_as_uint(__fadd_rn(p0, bias0));
     y1 = __float_as_uint(__fadd_rn(p1, bias1));
+}
+
+// silu(g) * u as the reference's fused gate/up decode kernel computes it (g * sigmoid(g), then * u;
+// native/src/backends/cuda/kernels/cuda_forward_gemv_pair_kernels.inc:457-459), with an accurate exp.
+__device__ __forceinline__ float epi_silu_mul(float gate, float up) {
+    const float sig = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-gate)));
+    return __fmul_rn(__fmul_rn(gate, sig), up);
 }
 
 // One output element through the selected epilogue (scalar path).

@@ -119,6 +119,20 @@ __device__ __forceinline__ void finish_parked(const DecodeRowsArgs& args, const 
     const EpilogueParams& ep = args.epi;
     const float zero_f = __int2float_rn(ep.out_zero);
     const float lo_f = __int2float_rn(ep.out_lo), hi_f = __int2float_rn(ep.out_hi);
+    if (ep.mode == kEpiF32 && ep.act == 1u) {
+        // channel pairs (gate, up) -> one output column each
+        for (uint32_t o = col_thread; 2u * o + 1u < valid; o += 128) {
+            const float wg = s_ws[2 * o], wu = s_ws[2 * o + 1], bg = s_bias[2 * o], bu = s_bias[2 * o + 1];
+            const size_t at = (size_t)(c0 >> 1) + o;
+            for (uint32_t mm = first_row; mm < args.rows; mm += row_step) {
+                const float asv = s_as[mm];
+                const float g = epi_f32(parked[mm * pitch + 2 * o], asv, wg, bg);
+                const float u = epi_f32(parked[mm * pitch + 2 * o + 1], asv, wu, bu);
+                ((float*)ep.out)[(size_t)mm * ep.ld + at] = epi_silu_mul(g, u);
+            }
+        }
+        return;
+    }
     for (uint32_t col = col_thread; col < valid; col += 128) {
         const float wsv = s_ws[col];
         const float bf = s_bias[col];
@@ -129,7 +143,9 @@ __device__ __forceinline__ void finish_parked(const DecodeRowsArgs& args, const 
             const int32_t v = parked[mm * pitch + col];
             const float asv = s_as[mm];
             if (ep.mode == kEpiF32) {
-                ((float*)ep.out)[(size_t)mm * ep.ld + at] = epi_f32(v, asv, wsv, bf);
+                float y = epi_f32(v, asv, wsv, bf);
+                if (ep.residual) y = __fadd_rn(y, __ldg(ep.residual + (size_t)mm * ep.ld_res + at));
+                ((float*)ep.out)[(size_t)mm * ep.ld + at] = y;
             } else if (ep.mode == kEpiI8) {
                 const int32_t qv = (ep.fast_div != 0 && div_const_row_ok(asv))
                     ? epi_i8_v2<true>(v + bi, asv, wsv, ep.out_scale, ep.out_rcp, zero_f, lo_f, hi_f, ep.out_zero)
@@ -437,8 +453,17 @@ decode_rows_kernel(const __grid_constant__ DecodeRowsArgs args) {
                     for (uint32_t mm = row_group; mm < args.rows; mm += 4) {
                         const int32_t v = park[mm * kXposePitch + lane];
                         const float asv = s_as[mm];
-                        if (ep.mode == kEpiF32) {
-                            ((float*)ep.out)[(size_t)mm * ep.ld + at] = epi_f32(v, asv, wsv, bf);
+                        if (ep.mode == kEpiF32 && ep.act == 1u) {
+                            // channel pairs (gate, up): the even lane finishes both and writes one column
+                            if ((lane & 1u) == 0u && col + 1u < valid) {
+                                const float g = epi_f32(v, asv, wsv, bf);
+                                const float u = epi_f32(park[mm * kXposePitch + lane + 1], asv, s_ws[col + 1], s_bias[col + 1]);
+                                ((float*)ep.out)[(size_t)mm * ep.ld + (at >> 1)] = epi_silu_mul(g, u);
+                            }
+                        } else if (ep.mode == kEpiF32) {
+                            float y = epi_f32(v, asv, wsv, bf);
+                            if (ep.residual) y = __fadd_rn(y, __ldg(ep.residual + (size_t)mm * ep.ld_res + at));
+                            ((float*)ep.out)[(size_t)mm * ep.ld + at] = y;
                         } else if (ep.mode == kEpiI8) {
                             const int32_t qv = (ep.fast_div != 0 && div_const_row_ok(asv))
                                 ? epi_i8_v2<true>(v + bi, asv, wsv, ep.out_scale, ep.out_rcp, zero_f, lo_f, hi_f, ep.out_zero)
@@ -593,9 +618,11 @@ uint32_t decode_rows_token_slots(uint32_t rows) {
 void decode_rows_plan(uint32_t n, int sm_count, uint32_t* tile_rows, uint32_t* tiles_per_cta) {
     uint32_t per_cta = (n + (uint32_t)sm_count - 1) / (uint32_t)sm_count;
     if (per_cta < 8) per_cta = n < 8 ? n : 8;
+    if ((per_cta & 1u) && per_cta < n) per_cta++;   // even, so that (gate, up) channel pairs never straddle CTAs
     const uint32_t tiles = (per_cta + kMaxTile - 1) / kMaxTile;
     *tiles_per_cta = tiles;
     *tile_rows = (per_cta + tiles - 1) / tiles;
+    if ((*tile_rows & 1u) && tiles > 1) (*tile_rows)++;   // ... nor tiles
 }
 
 #define VXB_DECODE_DISPATCH(fn, ...)                                                          \

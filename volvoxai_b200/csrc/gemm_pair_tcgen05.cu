@@ -392,6 +392,35 @@ gemm_i8_pair_kernel(const __grid_constant__ GemmTcgen05Args args) {
 #pragma unroll
                         for (int i = 0; i < 32; i++) o[i] = r[i];
                     }
+                    if (ep.mode == kEpiF32 && ep.residual && row_ok) {
+                        // fused residual addition: y += residual[row, col ...]
+                        const float* res = ep.residual + (size_t)row * ep.ld_res + col;
+                        if (full && (((uintptr_t)res) & 15u) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 8; j++) {
+                                const float4 rv = __ldg(reinterpret_cast<const float4*>(res) + j);
+                                o[4 * j + 0] = __float_as_uint(__fadd_rn(__uint_as_float(o[4 * j + 0]), rv.x));
+                                o[4 * j + 1] = __float_as_uint(__fadd_rn(__uint_as_float(o[4 * j + 1]), rv.y));
+                                o[4 * j + 2] = __float_as_uint(__fadd_rn(__uint_as_float(o[4 * j + 2]), rv.z));
+                                o[4 * j + 3] = __float_as_uint(__fadd_rn(__uint_as_float(o[4 * j + 3]), rv.w));
+                            }
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; i++)
+                                if (col + i < args.n) o[i] = __float_as_uint(__fadd_rn(__uint_as_float(o[i]), __ldg(res + i)));
+                        }
+                    }
+                    if (ep.mode == kEpiF32 && ep.act == 1u) {
+                        // channel pairs (gate, up) -> silu(gate) * up, one output column per pair
+                        if (row_ok) {
+                            float* dst = (float*)ep.out + (size_t)row * ep.ld + (col >> 1);
+#pragma unroll
+                            for (int j = 0; j < 16; j++)
+                                if (col + 2 * j + 1 < args.n)
+                                    dst[j] = epi_silu_mul(__uint_as_float(o[2 * j]), __uint_as_float(o[2 * j + 1]));
+                        }
+                        continue;
+                    }
                     // Each thread holds 128 contiguous bytes of its own row; stored directly, one store
                     // instruction touches 32 different rows. Instead the warp passes 16 rows at a time
                     // through shared memory (16-byte pieces XOR-swizzled by row: no bank conflicts either

@@ -135,6 +135,20 @@ class Context:
                                       out.stride(0), route))
         return out
 
+    def linear_f32_fused(self, w: "Weight", x, residual=None, silu_mul: bool = False, out=None):
+        """fp32 linear with a fused tail: + residual, or silu(gate) * up over interleaved channel
+        pairs (output d_out / 2 wide)."""
+        import torch
+        rows = x.shape[0]
+        width = w.d_out // 2 if silu_mul else w.d_out
+        if out is None:
+            out = torch.empty((rows, width), dtype=torch.float32, device=x.device)
+        _check(self._L.vxb_linear_f32_fused(self.handle, w.handle, _ptr(x), rows, _ptr(out), out.stride(0),
+                                            _ptr(residual) if residual is not None else None,
+                                            residual.stride(0) if residual is not None else 0,
+                                            1 if silu_mul else 0))
+        return out
+
     def linear_i8(self, w: "Weight", x, out_scale: float, out_zero: int = 0, out=None,
                   route: int = ROUTE_AUTO):
         import torch
