@@ -113,6 +113,14 @@ VXB_API int vxb_weight_create_i8(VxbContext* ctx, const int8_t* weight, const fl
 VXB_API int vxb_weight_create_w8_words(VxbContext* ctx, const int32_t* words, const float* group_scales,
                                const float* bias_f32, uint32_t d_out, uint32_t d_in,
                                uint32_t group_size, VxbWeight** out);
+/* Same, from PackedLinear W4 storage with A8 arithmetic (the reference's W4/A8 mode,
+ * docs/quantization-benchmark-20261023.md:17): eight 4-bit codes per word, earlier K in lower bits,
+ * w = code - 8, padding codes 8 (tools/exporter/packed_linear.py:39-87).  The codes are unpacked to
+ * int8 once at load time and served by the same kernels as a W8 weight (the grouped-scale kernel
+ * when the group scales differ, which is the exporter's normal output). */
+VXB_API int vxb_weight_create_w4_words(VxbContext* ctx, const int32_t* words, const float* group_scales,
+                               const float* bias_f32, uint32_t d_out, uint32_t d_in,
+                               uint32_t group_size, VxbWeight** out);
 VXB_API void vxb_weight_destroy(VxbWeight* w);
 VXB_API uint32_t vxb_weight_d_in(const VxbWeight* w);
 VXB_API uint32_t vxb_weight_d_out(const VxbWeight* w);

@@ -52,6 +52,7 @@ class Oracle:
         L.vxo_requant_rows.restype = C.c_int
         L.vxo_qlinear_i8u8.restype = C.c_int
         L.vxo_packed_linear_w8_grouped.restype = C.c_int
+        L.vxo_packed_linear_w4_grouped.restype = C.c_int
         L.vxo_w8a8_linear.restype = C.c_int
         L.vxo_div_const_mismatches.restype = C.c_uint64
         L.vxo_div_const_mismatches.argtypes = [C.c_float, C.c_uint64, C.c_uint64, C.c_int, C.c_int]
@@ -133,6 +134,22 @@ class Oracle:
         b = _f32(bias) if bias is not None else None
         y = np.zeros((rows, n), np.float32)
         st = self.lib.vxo_packed_linear_w8_grouped(
+            _p(x, C.c_float), C.c_uint64(rows), C.c_uint32(k), C.c_uint32(n),
+            _p(words, C.c_uint32), _p(sc, C.c_float), C.c_uint32(group),
+            _p(b, C.c_float), _p(y, C.c_float))
+        if st != 0:
+            raise ValueError("oracle refused the packed linear")
+        return y
+
+    def packed_linear_w4_grouped(self, x, words, scales, group, bias):
+        x = _f32(x)
+        rows, k = x.shape
+        words = np.ascontiguousarray(words).view(np.uint32)
+        n = words.shape[0]
+        sc = _f32(scales)
+        b = _f32(bias) if bias is not None else None
+        y = np.zeros((rows, n), np.float32)
+        st = self.lib.vxo_packed_linear_w4_grouped(
             _p(x, C.c_float), C.c_uint64(rows), C.c_uint32(k), C.c_uint32(n),
             _p(words, C.c_uint32), _p(sc, C.c_float), C.c_uint32(group),
             _p(b, C.c_float), _p(y, C.c_float))

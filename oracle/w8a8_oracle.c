@@ -147,6 +147,39 @@ VXO_API int vxo_packed_linear_w8_grouped(const float* x, uint64_t rows, uint32_t
     return 0;
 }
 
+/* The same forward for W4 storage (A8 arithmetic): eight codes per word, earlier K in lower
+ * bits, w = code - 8 (docs/packed-linear-design.md:24-41; tools/exporter/packed_linear.py:39-87;
+ * dot over nibbles native/src/kernels/packed_linear_ops.inc:285-493 with bits = 4). */
+VXO_API int vxo_packed_linear_w4_grouped(const float* x, uint64_t rows, uint32_t k,
+                                         uint32_t n, const uint32_t* words,
+                                         const float* scales, uint32_t group,
+                                         const float* bias, float* y) {
+    if (group != 32 && group != 64 && group != 128 && group != 256) return -1;
+    if (!k || !n) return -1;
+    const uint32_t row_words = (k + 7u) / 8u, groups = (k + group - 1u) / group;
+    int8_t q[k];
+    for (uint64_t r = 0; r < rows; r++) {
+        float as; int32_t ok;
+        vxo_quantize_rows(x + r * (uint64_t)k, 1, k, q, k, &as, &ok);
+        for (uint32_t c = 0; c < n; c++) {
+            if (!ok) { y[r * n + c] = __builtin_nanf(""); continue; }
+            const uint32_t* wr = words + (uint64_t)c * row_words;
+            volatile float sum = 0.0f;
+            for (uint32_t g = 0; g < groups; g++) {
+                uint32_t begin = g * group, end = begin + group < k ? begin + group : k;
+                int32_t dot = 0;
+                for (uint32_t j = begin; j < end; j++)
+                    dot += (int32_t)q[j] * ((int32_t)((wr[j >> 3] >> (4u * (j & 7u))) & 0xFu) - 8);
+                volatile float combined = as * scales[(uint64_t)c * groups + g];
+                volatile float product = (float)dot * combined;
+                sum = sum + product;
+            }
+            y[r * n + c] = sum + (bias ? bias[c] : 0.0f);
+        }
+    }
+    return 0;
+}
+
 /* native/src/kernels/w8a8_affine.h:114-120 (ties to even through floor). */
 VXO_API int32_t vxo_round_ties_even(float value) {
     const int32_t lower = (int32_t)__builtin_floorf(value);

@@ -106,6 +106,23 @@ def main():
         out[tag + "_x"], out[tag + "_words"], out[tag + "_scales"] = x, words, scales
         out[tag + "_bias"], out[tag + "_y_c"], out[tag + "_y_numpy"] = bias, y_c, y_np
 
+    # 2b. R1 forward with W4 storage and A8 arithmetic (eight 4-bit codes per word, w = code - 8)
+    rng = np.random.default_rng(1704)
+    for (rows, k, n, g) in [(5, 257, 7, 128), (9, 320, 12, 32), (3, 1283, 6, 256)]:
+        wf = rng.standard_normal((n, k)).astype(np.float32)
+        words, scales = ex.pack_weight(wf, weight_bits=4, group_size=g)
+        x = rng.standard_normal((rows, k)).astype(np.float32)
+        if rows > 3:
+            x[1] = 0
+            x[2, k // 2] = np.nan
+        bias = rng.standard_normal(n).astype(np.float32)
+        y_np = ex.packed_linear_reference(x, words, scales, weight_bits=4, group_size=g,
+                                          activation_bits=8, bias=bias)
+        y_c = ref.packed_linear(x, words, scales, g, bias, bits=4)
+        tag = f"r1w4_{rows}x{k}x{n}_g{g}"
+        out[tag + "_x"], out[tag + "_words"], out[tag + "_scales"] = x, words, scales
+        out[tag + "_bias"], out[tag + "_y_c"], out[tag + "_y_numpy"] = bias, y_c, y_np
+
     # 3. configuration 1 (M64,K576,N1536): q, scales, exact accumulators, E1, E2
     c1 = wl.single_linear()
     x, w, ws, bias = c1["x"], c1["w"], c1["ws"], c1["bias"]

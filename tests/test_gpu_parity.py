@@ -287,6 +287,67 @@ def test_grouped_scales_vs_oracle(torch, ctx, oracle, group, rows, k, n):
     wg.close()
 
 
+@pytest.mark.parametrize("tag,group,k", [("r1w4_5x257x7_g128", 128, 257), ("r1w4_9x320x12_g32", 32, 320),
+                                         ("r1w4_3x1283x6_g256", 256, 1283)])
+def test_w4_words_golden(torch, ctx, golden, tag, group, k):
+    """W4 storage, A8 arithmetic: loader + forward against the reference's own outputs."""
+    from volvoxai_b200 import w8a8
+    wg = w8a8.Weight.from_w4_words(ctx, golden[tag + "_words"], golden[tag + "_scales"], k, group,
+                                   bias_f32=golden[tag + "_bias"])
+    y = ctx.linear_f32(wg, dev(torch, golden[tag + "_x"])).cpu().numpy()
+    want = golden[tag + "_y_c"]
+    assert np.array_equal(np.isnan(y), np.isnan(want))
+    assert np.array_equal(y[~np.isnan(want)].view(np.uint32), want[~np.isnan(want)].view(np.uint32))
+    wg.close()
+
+
+@pytest.mark.parametrize("group", [32, 128])
+@pytest.mark.parametrize("rows,k,n", [(1, 300, 50), (70, 1283, 130), (9, 4096, 520), (300, 1024, 384)])
+def test_w4_words_vs_oracle(torch, ctx, oracle, group, rows, k, n):
+    from volvoxai_b200 import w8a8
+    rng = np.random.default_rng(group + rows + k + n)
+    w = rng.integers(-8, 8, size=(n, k), dtype=np.int8)
+    words = wl.pack_w4_words(w)
+    groups = (k + group - 1) // group
+    gs = rng.uniform(0.01, 0.2, size=(n, groups)).astype(np.float32)
+    x = (rng.standard_normal((rows, k)) * 3).astype(np.float32)
+    bias = rng.standard_normal(n).astype(np.float32)
+    wg = w8a8.Weight.from_w4_words(ctx, words, gs, k, group, bias_f32=bias)
+    y = ctx.linear_f32(wg, dev(torch, x)).cpu().numpy()
+    want = oracle.packed_linear_w4_grouped(x, words, gs, group, bias)
+    assert np.array_equal(y.view(np.uint32), want.view(np.uint32))
+    wg.close()
+    # one scale per channel: the tensor-core routes serve it, within the fp32 tolerance of
+    # per-channel versus per-group summation
+    gs1 = np.repeat(gs[:, :1], groups, axis=1)
+    wc = w8a8.Weight.from_w4_words(ctx, words, gs1, k, group, bias_f32=bias)
+    y1 = ctx.linear_f32(wc, dev(torch, x)).cpu().numpy()
+    want1 = oracle.packed_linear_w4_grouped(x, words, gs1, group, bias)
+    rms = np.sqrt(np.mean(want1.astype(np.float64) ** 2))
+    assert np.abs(y1 - want1).max() <= 1e-5 * rms
+    wc.close()
+
+
+def test_w4_host_entry_and_declines(torch, golden):
+    """cuda_graph_llm_f32 with weight bits 4; a non-zero padding code and an unknown bit width decline."""
+    from volvoxai_b200 import _lib, w8a8
+    tag, k, group = "r1w4_5x257x7_g128", 257, 128
+    x, words, scales, bias = (golden[tag + s] for s in ("_x", "_words", "_scales", "_bias"))
+    y = np.zeros((x.shape[0], words.shape[0]), np.float32)
+    assert w8a8.packed_linear(x, words, scales, bias, y, weight_bits=4, group_size=group) == 1
+    want = golden[tag + "_y_c"]
+    assert np.array_equal(np.isnan(y), np.isnan(want))
+    assert np.array_equal(y[~np.isnan(want)].view(np.uint32), want[~np.isnan(want)].view(np.uint32))
+    assert w8a8.packed_linear(x, words, scales, bias, y, weight_bits=2, group_size=group) == 0
+    bad = words.copy().view(np.uint32)
+    bad[0, -1] = (bad[0, -1] & np.uint32(0x0FFFFFFF)) | np.uint32(0x30000000)   # last padding code 3
+    c = w8a8.Context(0)
+    with pytest.raises(Exception):
+        w8a8.Weight.from_w4_words(c, bad.view(np.int32), scales, k, group)
+    c.close()
+    w8a8.host_cache_clear()
+
+
 # ---- static-activation QLinear (R2) ---------------------------------------------------------
 
 @pytest.mark.parametrize("izp", [0, 11])

@@ -95,6 +95,31 @@ def test_r1_grouped_forward_golden(oracle, golden, tag, group):
         assert np.array_equal(y[m].view(np.uint32), want[m].view(np.uint32)), key
 
 
+@pytest.mark.parametrize("tag,group", [("r1w4_5x257x7_g128", 128), ("r1w4_9x320x12_g32", 32),
+                                       ("r1w4_3x1283x6_g256", 256)])
+def test_r1_w4_forward_golden(oracle, golden, tag, group):
+    """W4 storage with A8 arithmetic: the restatement against the reference's C forward and its
+    NumPy twin (tools/exporter/packed_linear.py packed_linear_reference)."""
+    y = oracle.packed_linear_w4_grouped(golden[tag + "_x"], golden[tag + "_words"],
+                                        golden[tag + "_scales"], group, golden[tag + "_bias"])
+    for key in ("_y_c", "_y_numpy"):
+        want = golden[tag + key]
+        assert np.array_equal(np.isnan(y), np.isnan(want))
+        m = ~np.isnan(want)
+        assert np.array_equal(y[m].view(np.uint32), want[m].view(np.uint32)), key
+
+
+def test_w4_word_packer_matches_exporter_layout(golden):
+    """workloads.pack_w4_words restates the exporter's layout: unpacking the golden words and
+    packing them again gives the same words."""
+    words = golden["r1w4_5x257x7_g128_words"].view(np.uint32)
+    k = 257
+    codes = ((words[:, :, None] >> (4 * np.arange(8, dtype=np.uint32))) & 0xF).reshape(words.shape[0], -1)
+    w = codes[:, :k].astype(np.int8) - 8
+    assert (codes[:, k:] == 8).all()
+    assert np.array_equal(wl.pack_w4_words(w).view(np.uint32), words)
+
+
 def test_config1_golden(oracle, golden):
     c1 = wl.single_linear()
     res = oracle.w8a8_linear(c1["x"], c1["w"], c1["ws"], bias=c1["bias"])

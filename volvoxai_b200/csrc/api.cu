@@ -477,6 +477,59 @@ int vxb_weight_create_w8_words(VxbContext* ctx, const int32_t* words, const floa
     return 1;
 }
 
+int vxb_weight_create_w4_words(VxbContext* ctx, const int32_t* words, const float* group_scales,
+                               const float* bias_f32, uint32_t d_out, uint32_t d_in,
+                               uint32_t group_size, VxbWeight** out) {
+    if (!ctx || !words || !group_scales || !out) return fail(0, "null argument");
+    *out = nullptr;
+    if (!d_out || !d_in) return fail(0, "empty weight");
+    if (group_size != 32 && group_size != 64 && group_size != 128 && group_size != 256)
+        return fail(0, "group size %u is not 32/64/128/256", group_size);
+    const uint32_t groups = (d_in + group_size - 1) / group_size, row_words = (d_in + 7) / 8;
+    std::vector<float> ws(d_out);
+    bool grouped = false;
+    for (uint32_t n = 0; n < d_out; n++) {
+        const float s = group_scales[(size_t)n * groups];
+        for (uint32_t g = 0; g < groups; g++) {
+            const float sg = group_scales[(size_t)n * groups + g];
+            if (!valid_scale(sg)) return fail(0, "scale of channel %u, group %u is not positive and finite", n, g);
+            if (memcmp(&sg, &s, 4) != 0) grouped = true;
+        }
+        ws[n] = s;
+    }
+    // unpack once: eight codes per word, earlier K in lower bits, w = code - 8; padding codes must be 8
+    std::vector<int8_t> dense((size_t)d_out * d_in);
+    for (uint32_t n = 0; n < d_out; n++) {
+        const uint32_t* wr = (const uint32_t*)words + (size_t)n * row_words;
+        for (uint32_t j = 0; j < row_words * 8; j++) {
+            const int32_t code = (int32_t)((wr[j >> 3] >> (4u * (j & 7u))) & 0xFu);
+            if (j < d_in) dense[(size_t)n * d_in + j] = (int8_t)(code - 8);
+            else if (code != 8) return fail(0, "channel %u: padding code %u is not the encoded zero", n, j);
+        }
+    }
+    if (ensure_device(ctx) != 1) return -1;
+    VxbWeight* w = new VxbWeight();
+    w->device = ctx->device; w->d_in = d_in; w->d_out = d_out;
+    Buffer staging;
+    int rc;
+    if (staging.reserve(dense.size()) != cudaSuccess) rc = fail(0, "staging allocation failed");
+    else if (cudaMemcpyAsync(staging.ptr, dense.data(), dense.size(), cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess)
+        rc = fail(-1, "weight upload failed");
+    else rc = finish_weight(ctx, w, (const uint8_t*)staging.ptr, d_in, 0u, ws.data(), bias_f32, nullptr);
+    if (rc == 1 && grouped) {
+        const size_t gbytes = (size_t)d_out * groups * 4;
+        if (cudaMalloc(&w->gscales, gbytes) != cudaSuccess) rc = fail(0, "group scale allocation failed");
+        else if (cudaMemcpyAsync(w->gscales, group_scales, gbytes, cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess)
+            rc = fail(-1, "group scale upload failed");
+        else { w->group = group_size; w->groups = groups; w->bytes += gbytes; }
+    }
+    cudaStreamSynchronize(ctx->stream);
+    staging.release();
+    if (rc != 1) { vxb_weight_destroy(w); return rc; }
+    *out = w;
+    return 1;
+}
+
 void vxb_weight_destroy(VxbWeight* w) {
     if (!w) return;
     cudaSetDevice(w->device);
@@ -1014,7 +1067,8 @@ int vxb_requantize_linear_i8u8(const void* input, uint32_t input_elements, void*
 int vxb_cuda_graph_llm_f32(const VxbLLMOpArgs* a) {
     if (!a) return fail(0, "null descriptor");
     if (a->kind != VXB_OP_PACKED_LINEAR) return fail(0, "operator %d is not PackedLinear", a->kind);
-    if (a->groups != 8 || a->normalize != 8) return fail(0, "only weight bits 8 / activation bits 8 are admitted");
+    if ((a->groups != 8 && a->groups != 4) || a->normalize != 8)
+        return fail(0, "only weight bits 8 or 4 with activation bits 8 are admitted");
     if (a->key_dim <= 0 || a->value_dim <= 0 || a->batch <= 0 || a->sequence <= 0) return fail(0, "bad shape");
     if (!a->x[0] || !a->x[1] || !a->x[2] || !a->y[0]) return fail(0, "null tensor");
     const uint32_t k = (uint32_t)a->key_dim, n = (uint32_t)a->value_dim;
@@ -1032,13 +1086,14 @@ int vxb_cuda_graph_llm_f32(const VxbLLMOpArgs* a) {
     VxbContext* ctx = nullptr;
     int rc = host_context(&ctx);
     if (rc != 1) return rc;
-    const HostKey key{a->x[1], a->x[2], a->x[3], k, n, 2u};
+    const HostKey key{a->x[1], a->x[2], a->x[3], k, n, a->groups == 4 ? 3u : 2u};
     VxbWeight* w = nullptr;
     auto it = g_host_weights.find(key);
     if (it != g_host_weights.end()) w = it->second;
     else {
-        rc = vxb_weight_create_w8_words(ctx, (const int32_t*)a->x[1], a->x[2], a->x[3], n, k,
-                                        (uint32_t)a->rate, &w);
+        rc = a->groups == 4
+            ? vxb_weight_create_w4_words(ctx, (const int32_t*)a->x[1], a->x[2], a->x[3], n, k, (uint32_t)a->rate, &w)
+            : vxb_weight_create_w8_words(ctx, (const int32_t*)a->x[1], a->x[2], a->x[3], n, k, (uint32_t)a->rate, &w);
         if (rc != 1) return rc;
         g_host_weights.emplace(key, w);
     }

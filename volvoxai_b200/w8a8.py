@@ -256,6 +256,19 @@ class Weight:
                                                  words.shape[0], d_in, group_size, C.byref(h)))
         return cls(ctx, h)
 
+    @classmethod
+    def from_w4_words(cls, ctx: Context, words: np.ndarray, group_scales: np.ndarray, d_in: int,
+                      group_size: int, bias_f32=None):
+        """PackedLinear W4 storage: I32 words [d_out,ceil(d_in/8)] of eight 4-bit codes
+        (weight = code - 8) + group scales; unpacked to int8 on load."""
+        words = np.ascontiguousarray(words).view(np.int32)
+        gs = np.ascontiguousarray(group_scales, np.float32)
+        bf = None if bias_f32 is None else np.ascontiguousarray(bias_f32, np.float32)
+        h = C.c_void_p(0)
+        _check(ctx._L.vxb_weight_create_w4_words(ctx.handle, _ptr(words), _ptr(gs), _ptr(bf),
+                                                 words.shape[0], d_in, group_size, C.byref(h)))
+        return cls(ctx, h)
+
     @property
     def device_bytes(self) -> int:
         return int(self._L.vxb_weight_device_bytes(self.handle))

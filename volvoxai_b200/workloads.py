@@ -63,6 +63,17 @@ def pack_w8_words(w: np.ndarray) -> np.ndarray:
     return codes.view("<u4").reshape(n, kw).copy()
 
 
+def pack_w4_words(w: np.ndarray) -> np.ndarray:
+    """int8 weights in [-8, 7] [N,K] -> PackedLinear W4 words [N, ceil(K/8)] (int32): eight codes per
+    word, earlier K in lower bits, code = w + 8, padding codes 8 (the encoded zero)."""
+    n, k = w.shape
+    kw = (k + 7) // 8
+    codes = np.full((n, kw * 8), 8, np.uint32)
+    codes[:, :k] = (w.astype(np.int32) + 8).astype(np.uint32)
+    shifts = (np.arange(8, dtype=np.uint32) * np.uint32(4))
+    return (codes.reshape(n, kw, 8) << shifts).sum(axis=2, dtype=np.uint32).view(np.int32)
+
+
 def group_scales(ws: np.ndarray, k: int, group: int) -> np.ndarray:
     """Per-channel scales expressed as PackedLinear group scales [N, ceil(K/G)]."""
     groups = (k + group - 1) // group
