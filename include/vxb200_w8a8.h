@@ -216,6 +216,30 @@ enum { VXB_ACT_NONE = 0, VXB_ACT_SILU_MUL = 1 };
 VXB_API int vxb_linear_f32_fused(VxbContext* ctx, const VxbWeight* w, const float* x, uint32_t rows, float* y,
                          uint32_t ldy, const float* residual, uint32_t ld_residual, int activation);
 
+/* RMSNorm folded into the quantizer: the head of the reference's fused decode patterns
+ * RMSNorm + {q,k,v} and RMSNorm + gate/up + SiLU*Mul
+ * (native/src/backends/cuda/kernels/cuda_forward_gemv_pair_kernels.inc:1133-1711, recognised at
+ * native/src/runtime/incremental_runtime.c:1178-1232), for any number of rows.  The residual
+ * stream x is read once; norm_out (fp32 [rows,k], may be NULL) receives the normalized rows for
+ * other consumers, as the reference's kernels persist them; q / row_scales / valid as
+ * vxb_quantize_rows.  Normalization arithmetic of the reference's CPU operator
+ * (native/src/kernels/softmax_rmsnorm.inc:3-16): mean of squares and 1/sqrt(mean + epsilon) in
+ * double, y = float((double(x) * inv) * double(norm_weight)); the double additions run as a tree, so
+ * a normalized value can differ from the sequential loop's by one fp32 unit in the last place in
+ * rare cases; the quantization of the normalized row is bit-exact.  epsilon > 0 and finite
+ * (native/src/runtime/engine_runtime_dispatch.inc:2912-2915). */
+VXB_API int vxb_rmsnorm_quantize_rows(VxbContext* ctx, const float* x, const float* norm_weight, float epsilon,
+                              uint32_t rows, uint32_t k, float* norm_out, int8_t* q, uint32_t ldq,
+                              float* row_scales, int32_t* valid);
+
+/* RMSNorm -> per-token quantization -> linear -> fp32 epilogue with the optional SiLU*Mul tail of
+ * vxb_linear_f32_fused, in two launches.  q/k/v (or gate/up, interleaved for SILU_MUL) are one
+ * weight concatenated along the output channels, so the three (two) projections share the
+ * normalization and the quantization.  norm_out may be NULL. */
+VXB_API int vxb_rmsnorm_linear_f32_fused(VxbContext* ctx, const VxbWeight* w, const float* x, const float* norm_weight,
+                                 float epsilon, float* norm_out, uint32_t rows, float* y, uint32_t ldy,
+                                 int activation);
+
 /* Prepared-activation form, the counterpart of the reference's prepared path
  * (x[4] prepared words / x[5] row scales, native/src/backends/cuda/host/
  * cuda_graph_llm_host.inc:15-107): the caller quantized the rows itself with

@@ -176,6 +176,14 @@ class Oracle:
             C.c_int(1 if out_unsigned else 0))
         return out if ok else None
 
+    def rmsnorm_rows(self, x, weight, eps):
+        x, weight = _f32(x), _f32(weight)
+        y = np.zeros_like(x)
+        self.lib.vxo_rmsnorm_rows.restype = None
+        self.lib.vxo_rmsnorm_rows(_p(x, C.c_float), _p(weight, C.c_float), _p(y, C.c_float), C.c_uint32(x.shape[0]),
+                                  C.c_uint32(x.shape[1]), C.c_double(float(np.float32(eps))))
+        return y
+
     def quantize_linear(self, x, scale, zero, out_unsigned=False):
         x = _f32(x).reshape(-1)
         out = np.zeros(x.size, np.uint8 if out_unsigned else np.int8)
@@ -339,6 +347,14 @@ class Ref:
             C.c_int32(in_zero), C.c_float(out_scale), C.c_int32(out_zero),
             C.c_uint32(self._dt(x)), C.c_uint32(self._dt(w)), C.c_uint32(self._dt(out)))
         return out if ok else None
+
+    def rmsnorm_rows(self, x, weight, eps):
+        x, weight = _f32(x), _f32(weight)
+        y = np.zeros_like(x)
+        self.lib.ref_rmsnorm_rows.restype = None
+        self.lib.ref_rmsnorm_rows(_p(x, C.c_float), _p(weight, C.c_float), _p(y, C.c_float), C.c_uint32(x.shape[0]),
+                                  C.c_uint32(x.shape[1]), C.c_double(float(np.float32(eps))))
+        return y
 
     def quantize_linear(self, x, scale, zero, out_unsigned=False):
         x = _f32(x).reshape(-1)

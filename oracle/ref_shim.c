@@ -128,6 +128,11 @@ int quantize_linear_typed(const float*, const float*, const void*, uint32_t, voi
 int dequantize_linear_typed(const void*, int, const float*, const void*, int, float*, int);
 int requantize_linear_i8u8(const void*, void*, uint32_t, float, int32_t, float, int32_t, uint32_t, uint32_t);
 
+void rmsnorm_f32(const float*, const float*, float*, int, int, double);
+REF_API void ref_rmsnorm_rows(const float* x, const float* weight, float* y, uint32_t rows, uint32_t k, double eps) {
+    rmsnorm_f32(x, weight, y, (int)rows, (int)k, eps);
+}
+
 REF_API int ref_quantize_linear(const float* x, uint32_t elements, float scale, int32_t zero,
                                 uint32_t out_dtype, void* out) {
     int8_t z8 = (int8_t)zero; uint8_t zu = (uint8_t)zero;

@@ -332,6 +332,21 @@ static void vxo_byte_range(int is_unsigned, int32_t* lo, int32_t* hi) {
     *lo = is_unsigned ? 0 : -128; *hi = is_unsigned ? 255 : 127;
 }
 
+
+/* RMSNorm over the last axis (native/src/kernels/softmax_rmsnorm.inc:3-16): squares and their
+ * mean accumulated left to right in double, inv = 1/sqrt(mean + eps) in double,
+ * y = float((double(x) * inv) * weight) with weight promoted to double. */
+VXO_API void vxo_rmsnorm_rows(const float* x, const float* weight, float* y, uint32_t rows, uint32_t k, double eps) {
+    for (uint32_t r = 0; r < rows; r++) {
+        const float* in = x + (size_t)r * k;
+        double var = 0.0;
+        for (uint32_t j = 0; j < k; j++) { const double v = in[j]; var += v * v; }
+        var /= (double)k;
+        const double inv = 1.0 / sqrt(var + eps);
+        for (uint32_t j = 0; j < k; j++) y[(size_t)r * k + j] = (float)((double)in[j] * inv * weight[j]);
+    }
+}
+
 /* native/src/kernels/quantize_linear_ops.inc:155-170,230-254 (quantize_linear_typed):
  * NaN -> zero point; t = x / scale + (float)zero; saturate, ties to even. */
 VXO_API int vxo_quantize_linear(const float* x, uint64_t elements, float scale, int32_t zero,

@@ -196,6 +196,18 @@ def main():
         oscale, ozero, ou = cases[(i + 1) % len(cases)]
         out[f"bnd_rq{i}"] = ref.requantize_linear(src, max(scale, 0.01), zero, max(oscale, 0.01), ozero, bool(ou))
 
+    # 7. RMSNorm (the head of the fused decode patterns): the reference's CPU operator
+    rng = np.random.default_rng(20262)
+    for (rows, k) in [(6, 257), (4, 576), (3, 4096)]:
+        x = (rng.standard_normal((rows, k)) * rng.uniform(0.01, 30.0, size=(rows, 1))).astype(np.float32)
+        x[0] = 0
+        if rows > 4:
+            x[1, k // 3] = np.nan
+        gamma = rng.uniform(0.2, 2.0, size=k).astype(np.float32)
+        tag = f"rms_{rows}x{k}"
+        out[tag + "_x"], out[tag + "_gamma"] = x, gamma
+        out[tag + "_y"] = ref.rmsnorm_rows(x, gamma, 1e-6)
+
     path = os.path.join(ROOT, "tests", "golden", "w8a8_golden.npz")
     np.savez_compressed(path, **out)
     print(f"wrote {path}: {len(out)} arrays, {os.path.getsize(path)} bytes; ref isa={ref.isa()}")

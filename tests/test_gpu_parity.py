@@ -578,6 +578,92 @@ def test_fused_residual_and_silu_mul(torch, ctx, oracle, rows, k, n):
     weight.close()
 
 
+# ---- RMSNorm folded into the quantizer ------------------------------------------------------
+
+def _ulp_distance(a, b):
+    """Units in the last place between finite fp32 arrays of equal sign structure."""
+    ia, ib = a.view(np.int32).astype(np.int64), b.view(np.int32).astype(np.int64)
+    ia = np.where(ia < 0, np.int64(-(2 ** 31)) - ia, ia)
+    ib = np.where(ib < 0, np.int64(-(2 ** 31)) - ib, ib)
+    return np.abs(ia - ib)
+
+
+def _check_norm(y, want):
+    assert np.array_equal(np.isnan(y), np.isnan(want))
+    ok = ~np.isnan(want)
+    d = _ulp_distance(y[ok], want[ok])
+    assert d.max(initial=0) <= 1                       # tree instead of sequential double additions
+    assert (d != 0).mean() <= 1e-4 if d.size else True
+
+
+@pytest.mark.parametrize("tag", ["rms_6x257", "rms_4x576", "rms_3x4096"])
+def test_rmsnorm_quantize_golden(torch, ctx, oracle, golden, tag):
+    """Normalized rows against the reference's CPU operator; codes and scales against the oracle's
+    quantizer applied to the rows this kernel produced (bit-exact)."""
+    x, gamma = golden[tag + "_x"], golden[tag + "_gamma"]
+    y, q, s, v = ctx.rmsnorm_quantize_rows(dev(torch, x), dev(torch, gamma), 1e-6)
+    y = y.cpu().numpy()
+    _check_norm(y, golden[tag + "_y"])
+    wq, ws_, wv = oracle.quantize_rows(y)
+    assert np.array_equal(v.cpu().numpy() != 0, wv != 0)
+    assert np.array_equal(q.cpu().numpy(), wq)
+    ok = wv != 0
+    assert np.array_equal(s.cpu().numpy()[ok].view(np.uint32), ws_[ok].view(np.uint32))
+
+
+@pytest.mark.parametrize("rows,k", [(1, 576), (7, 130), (40, 1024), (9, 4096), (300, 2048), (33, 8192),
+                                    (5, 12288), (2100, 576)])
+def test_rmsnorm_quantize_vs_oracle(torch, ctx, oracle, rows, k):
+    """Every launch shape: scalar rows (k % 4 != 0), 8..256 threads per row, the uncached form
+    (k > 8192); with and without the normalized rows written out; padded code rows."""
+    rng = np.random.default_rng(rows * 7 + k)
+    x = (rng.standard_normal((rows, k)) * rng.uniform(0.01, 50.0, size=(rows, 1))).astype(np.float32)
+    if rows > 2:
+        x[1] = 0
+        x[2, k // 2] = np.inf
+    gamma = rng.uniform(0.1, 3.0, size=k).astype(np.float32)
+    eps = 1e-5
+    xd, gd = dev(torch, x), dev(torch, gamma)
+    ldq = (k + 127) // 128 * 128
+    y, q, s, v = ctx.rmsnorm_quantize_rows(xd, gd, eps, ldq=ldq)
+    y = y.cpu().numpy()
+    _check_norm(y, oracle.rmsnorm_rows(x, gamma, eps))
+    wq, ws_, wv = oracle.quantize_rows(y)
+    q = q.cpu().numpy()
+    assert np.array_equal(q[:, :k], wq) and not q[:, k:].any()
+    ok = wv != 0
+    assert np.array_equal(v.cpu().numpy() != 0, ok)
+    assert np.array_equal(s.cpu().numpy()[ok].view(np.uint32), ws_[ok].view(np.uint32))
+    _, q2, s2, _ = ctx.rmsnorm_quantize_rows(xd, gd, eps, ldq=ldq, want_norm=False)
+    assert np.array_equal(q2.cpu().numpy(), q)
+    assert np.array_equal(s2.cpu().numpy()[ok].view(np.uint32), ws_[ok].view(np.uint32))
+    with pytest.raises(Exception):
+        ctx.rmsnorm_quantize_rows(xd, gd, 0.0)
+
+
+@pytest.mark.parametrize("rows,k,n", [(1, 576, 1536), (8, 1024, 3072), (100, 320, 1000), (600, 576, 1536)])
+def test_rmsnorm_linear_fused(torch, ctx, oracle, rows, k, n):
+    """RMSNorm -> quantize -> linear (-> SiLU * up): equal, bit for bit, to the unfused chain of this
+    library over the normalized rows the fused call wrote, and to the oracle within the fp32 contract."""
+    from volvoxai_b200 import w8a8
+    c = wl.single_linear(rows=rows, k=k, n=n, seed=rows + n + 1)
+    rng = np.random.default_rng(rows + k)
+    gamma = rng.uniform(0.1, 3.0, size=k).astype(np.float32)
+    weight = w8a8.Weight.from_i8(ctx, c["w"], c["ws"], bias_f32=c["bias"])
+    xd, gd = dev(torch, c["x"]), dev(torch, gamma)
+    norm = torch.empty_like(xd)
+    y = ctx.rmsnorm_linear_f32_fused(weight, xd, gd, 1e-6, norm_out=norm).cpu().numpy()
+    _check_norm(norm.cpu().numpy(), oracle.rmsnorm_rows(c["x"], gamma, 1e-6))
+    plain = ctx.linear_f32(weight, norm).cpu().numpy()
+    assert np.array_equal(y.view(np.uint32), plain.view(np.uint32))
+    ref = oracle.w8a8_linear(norm.cpu().numpy(), c["w"], c["ws"], bias=c["bias"])["out"]
+    assert rel_err(y, ref) <= F32_TOL
+    s = ctx.rmsnorm_linear_f32_fused(weight, xd, gd, 1e-6, silu_mul=True).cpu().numpy()
+    s2 = ctx.linear_f32_fused(weight, norm, silu_mul=True).cpu().numpy()
+    assert np.array_equal(s.view(np.uint32), s2.view(np.uint32))
+    weight.close()
+
+
 # ---- boundary ops of a static W8A8 island --------------------------------------------------
 
 def _boundary_cases(golden):

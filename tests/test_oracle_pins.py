@@ -120,6 +120,15 @@ def test_w4_word_packer_matches_exporter_layout(golden):
     assert np.array_equal(wl.pack_w4_words(w).view(np.uint32), words)
 
 
+@pytest.mark.parametrize("tag", ["rms_6x257", "rms_4x576", "rms_3x4096"])
+def test_rmsnorm_golden(oracle, golden, tag):
+    """The restated RMSNorm against the reference's CPU operator (softmax_rmsnorm.inc), bit for bit."""
+    y = oracle.rmsnorm_rows(golden[tag + "_x"], golden[tag + "_gamma"], 1e-6)
+    want = golden[tag + "_y"]
+    assert np.array_equal(np.isnan(y), np.isnan(want))
+    assert np.array_equal(y[~np.isnan(want)].view(np.uint32), want[~np.isnan(want)].view(np.uint32))
+
+
 def test_config1_golden(oracle, golden):
     c1 = wl.single_linear()
     res = oracle.w8a8_linear(c1["x"], c1["w"], c1["ws"], bias=c1["bias"])

@@ -24,7 +24,8 @@ EXPORTS = [
     "vxb_quantize_rows", "vxb_linear_f32", "vxb_linear_i8", "vxb_linear_acc_i32",
     "vxb_qlinear_device", "vxb_weight_row_bytes", "vxb_linear_prepared", "vxb_linear_host", "vxb_context_profile", "vxb_context_profile_read", "vxb_context_trace",
     "vxb_measure_i8_tensor_peak", "vxb_measure_mma_issue", "vxb_peer_alloc", "vxb_peer_open",
-    "vxb_peer_close", "vxb_peer_free", "vxb_linear_i8_gather", "vxb_linear_f32_fused", "vxb_weight_create_w4_words", "vxb_quantize_linear_device",
+    "vxb_peer_close", "vxb_peer_free", "vxb_linear_i8_gather", "vxb_linear_f32_fused", "vxb_weight_create_w4_words",
+    "vxb_rmsnorm_quantize_rows", "vxb_rmsnorm_linear_f32_fused", "vxb_quantize_linear_device",
     "vxb_dequantize_linear_device", "vxb_requantize_linear_device", "vxb_quantize_typed_f32_i8u8",
     "vxb_dequantize_typed_i8u8_f32", "vxb_requantize_linear_i8u8", "vxb_decode_linear_f32_noalloc", "vxb_qlinear_i8u8",
     "vxb_cuda_graph_llm_f32", "vxb_cuda_graph_packed_linear_decode_f32", "vxb_host_cache_clear",
@@ -101,6 +102,8 @@ def load() -> C.CDLL:
     L.vxb_dequantize_typed_i8u8_f32.argtypes = [vp, u32, f32, i32, u32, vp]
     L.vxb_requantize_linear_i8u8.argtypes = [vp, u32, vp, u32, f32, i32, f32, i32, u32, u32]
     L.vxb_linear_f32_fused.argtypes = [vp, vp, vp, u32, vp, u32, vp, u32, C.c_int]
+    L.vxb_rmsnorm_quantize_rows.argtypes = [vp, vp, vp, C.c_float, u32, u32, vp, vp, u32, vp, vp]
+    L.vxb_rmsnorm_linear_f32_fused.argtypes = [vp, vp, vp, vp, C.c_float, vp, u32, vp, u32, C.c_int]
     L.vxb_peer_alloc.argtypes = [C.c_size_t, C.POINTER(vp), C.c_char_p]
     L.vxb_peer_open.argtypes = [C.c_char_p, C.POINTER(vp)]
     L.vxb_peer_close.argtypes = [vp]

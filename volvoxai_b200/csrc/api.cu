@@ -317,13 +317,18 @@ int check_common(const VxbContext* ctx, const VxbWeight* w, const void* x, const
     return 1;
 }
 
-int quantize_into_scratch(VxbContext* ctx, const VxbWeight* w, const float* x, uint32_t rows) {
+int quantize_into_scratch(VxbContext* ctx, const VxbWeight* w, const float* x, uint32_t rows,
+                          const float* norm_weight = nullptr, float epsilon = 0.0f, float* norm_out = nullptr) {
     CUDA_TRY(ctx->q.reserve((size_t)rows * w->kpad), 0);
     CUDA_TRY(ctx->row_scales.reserve((size_t)rows * 4), 0);
     {
         ProfileScope scope(ctx, 0);
-        CUDA_TRY(launch_quantize_rows(x, rows, w->d_in, (int8_t*)ctx->q.ptr, w->kpad,
-                                      (float*)ctx->row_scales.ptr, nullptr, ctx->stream), -1);
+        if (norm_weight)
+            CUDA_TRY(launch_rmsnorm_quantize_rows(x, norm_weight, epsilon, rows, w->d_in, norm_out, (int8_t*)ctx->q.ptr,
+                                                  w->kpad, (float*)ctx->row_scales.ptr, nullptr, ctx->stream), -1);
+        else
+            CUDA_TRY(launch_quantize_rows(x, rows, w->d_in, (int8_t*)ctx->q.ptr, w->kpad,
+                                          (float*)ctx->row_scales.ptr, nullptr, ctx->stream), -1);
     }
     count_launch();
     return 1;
@@ -570,8 +575,9 @@ int vxb_linear_f32(VxbContext* ctx, const VxbWeight* w, const float* x, uint32_t
     return run_gemm(ctx, w, (const int8_t*)ctx->q.ptr, rows, epi, route, "k1+");
 }
 
-int vxb_linear_f32_fused(VxbContext* ctx, const VxbWeight* w, const float* x, uint32_t rows, float* y,
-                         uint32_t ldy, const float* residual, uint32_t ld_residual, int activation) {
+static int fused_linear(VxbContext* ctx, const VxbWeight* w, const float* x, uint32_t rows, float* y,
+                        uint32_t ldy, const float* residual, uint32_t ld_residual, int activation,
+                        const float* norm_weight, float epsilon, float* norm_out) {
     if (!ctx || !w || !x || !y) return fail(0, "null argument");
     if (w->device != ctx->device) return fail(0, "weight lives on device %d, context on %d", w->device, ctx->device);
     if (activation != VXB_ACT_NONE && activation != VXB_ACT_SILU_MUL) return fail(0, "unknown activation %d", activation);
@@ -584,13 +590,42 @@ int vxb_linear_f32_fused(VxbContext* ctx, const VxbWeight* w, const float* x, ui
     if (!rows) return 1;
     if (ensure_device(ctx) != 1) return -1;
     int rc;
-    if ((rc = quantize_into_scratch(ctx, w, x, rows)) != 1) return rc;
+    if ((rc = quantize_into_scratch(ctx, w, x, rows, norm_weight, epsilon, norm_out)) != 1) return rc;
     EpilogueParams epi{};
     epi.mode = kEpiF32; epi.row_scales = (const float*)ctx->row_scales.ptr; epi.ws = w->ws;
     epi.bias_f32 = w->bias_f32; epi.out = y; epi.ld = ldy;
     epi.residual = residual; epi.ld_res = ld_residual; epi.act = activation == VXB_ACT_SILU_MUL ? 1u : 0u;
     // the decode kernel up to 128 rows, the tensor-core GEMM above: both carry the fused forms
-    return run_gemm(ctx, w, (const int8_t*)ctx->q.ptr, rows, epi, VXB_ROUTE_AUTO, "k1+");
+    return run_gemm(ctx, w, (const int8_t*)ctx->q.ptr, rows, epi, VXB_ROUTE_AUTO, norm_weight ? "norm+k1+" : "k1+");
+}
+
+int vxb_linear_f32_fused(VxbContext* ctx, const VxbWeight* w, const float* x, uint32_t rows, float* y,
+                         uint32_t ldy, const float* residual, uint32_t ld_residual, int activation) {
+    return fused_linear(ctx, w, x, rows, y, ldy, residual, ld_residual, activation, nullptr, 0.0f, nullptr);
+}
+
+int vxb_rmsnorm_linear_f32_fused(VxbContext* ctx, const VxbWeight* w, const float* x, const float* norm_weight,
+                                 float epsilon, float* norm_out, uint32_t rows, float* y, uint32_t ldy,
+                                 int activation) {
+    if (!norm_weight) return fail(0, "null norm weight");
+    if (!(epsilon > 0.0f) || !std::isfinite(epsilon)) return fail(0, "epsilon is not positive and finite");
+    if (norm_out && x == norm_out) return fail(0, "the normalized rows cannot overwrite the input");
+    return fused_linear(ctx, w, x, rows, y, ldy, nullptr, 0, activation, norm_weight, epsilon, norm_out);
+}
+
+int vxb_rmsnorm_quantize_rows(VxbContext* ctx, const float* x, const float* norm_weight, float epsilon,
+                              uint32_t rows, uint32_t k, float* norm_out, int8_t* q, uint32_t ldq,
+                              float* row_scales, int32_t* valid) {
+    if (!ctx || !x || !norm_weight || !q || !row_scales) return fail(0, "null argument");
+    if (!k || ldq < k) return fail(0, "bad widths k=%u ldq=%u", k, ldq);
+    if (!(epsilon > 0.0f) || !std::isfinite(epsilon)) return fail(0, "epsilon is not positive and finite");
+    if (!rows) return 1;
+    if (ensure_device(ctx) != 1) return -1;
+    CUDA_TRY(launch_rmsnorm_quantize_rows(x, norm_weight, epsilon, rows, k, norm_out, q, ldq, row_scales, valid,
+                                          ctx->stream), -1);
+    count_launch();
+    snprintf(g_route, sizeof g_route, "norm+k1");
+    return 1;
 }
 
 int vxb_linear_i8(VxbContext* ctx, const VxbWeight* w, const float* x, uint32_t rows,

@@ -241,6 +241,9 @@ cudaError_t launch_gemm_grouped(const int8_t* q, uint32_t rows, const int8_t* w,
 
 // K1: per-token absmax + quantize. q rows have stride ldq (multiple of 16 when
 // the vector path is to be used); bytes [k, ldq) are zeroed.
+cudaError_t launch_rmsnorm_quantize_rows(const float* x, const float* gamma, float epsilon, uint32_t rows,
+                                         uint32_t k, float* norm_out, int8_t* q, uint32_t ldq,
+                                         float* row_scales, int32_t* valid, cudaStream_t stream);
 cudaError_t launch_quantize_rows(const float* x, uint32_t rows, uint32_t k, int8_t* q,
                                  uint32_t ldq, float* row_scales, int32_t* valid,
                                  cudaStream_t stream);

@@ -346,6 +346,188 @@ cudaError_t launch_vec(const float* x, uint32_t rows, uint32_t k, int8_t* q, uin
                       x, rows, k, q, ldq, row_scales, valid);
 }
 
+
+// ---- RMSNorm folded into the quantizer --------------------------------------------------------
+// The decode and prefill patterns RMSNorm -> {q,k,v} and RMSNorm -> {gate,up} read the residual
+// stream once: normalize, (optionally) persist the normalized row for other consumers, quantize.
+// Arithmetic of the normalization follows the reference's CPU operator
+// (native/src/kernels/softmax_rmsnorm.inc:3-16): squares and their mean in double,
+// inv = 1 / sqrt(mean + eps) in double, y = float((double(x) * inv) * double(gamma)).  The squares
+// are exact in double; only the order of the double additions differs from the sequential loop
+// (tree instead of left to right), which moves the mean by at most a few units of 2^-53.
+
+__device__ __forceinline__ float norm1(float x, double inv, float g) {
+    return __double2float_rn(__dmul_rn(__dmul_rn((double)x, inv), (double)g));
+}
+__device__ __forceinline__ float4 norm4(float4 c, double inv, float4 g) {
+    return make_float4(norm1(c.x, inv, g.x), norm1(c.y, inv, g.y), norm1(c.z, inv, g.z), norm1(c.w, inv, g.w));
+}
+__device__ __forceinline__ double square_sum4(float4 c, double acc) {
+    acc = __fma_rn((double)c.x, (double)c.x, acc);
+    acc = __fma_rn((double)c.y, (double)c.y, acc);
+    acc = __fma_rn((double)c.z, (double)c.z, acc);
+    return __fma_rn((double)c.w, (double)c.w, acc);
+}
+
+template <int THREADS_PER_ROW>
+__device__ __forceinline__ double row_sum(double v, double* smem_sum) {
+    constexpr int kWarpSpan = THREADS_PER_ROW < 32 ? THREADS_PER_ROW : 32;
+#pragma unroll
+    for (int off = kWarpSpan / 2; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    if constexpr (THREADS_PER_ROW > 32) {
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        if (lane == 0) smem_sum[warp] = v;
+        __syncthreads();
+        constexpr int kWarps = THREADS_PER_ROW / 32;
+        const int first = (threadIdx.x / THREADS_PER_ROW) * kWarps;
+        double s = 0.0;
+#pragma unroll
+        for (int i = 0; i < kWarps; i++) s += smem_sum[first + i];
+        v = s;
+    }
+    return v;
+}
+
+template <int THREADS_PER_ROW, bool CACHE>
+__global__ void __launch_bounds__(kThreads)
+rmsnorm_quantize_rows_vec(const float* __restrict__ x, const float* __restrict__ gamma, double eps,
+                          uint32_t rows, uint32_t k, float* __restrict__ norm_out, int8_t* __restrict__ q,
+                          uint32_t ldq, float* __restrict__ row_scales, int32_t* __restrict__ valid) {
+    __shared__ float smem_max[kThreads / 32];
+    __shared__ int smem_bad[kThreads / 32];
+    __shared__ double smem_sum[kThreads / 32];
+    pdl_release();
+    pdl_wait();
+    constexpr int kRowsPerCta = kThreads / THREADS_PER_ROW;
+    const uint32_t row = blockIdx.x * kRowsPerCta + threadIdx.x / THREADS_PER_ROW;
+    const int t = threadIdx.x % THREADS_PER_ROW;
+    const bool active = row < rows;
+    const uint32_t nvec = k / 4;
+    const float4* in = reinterpret_cast<const float4*>(x + (size_t)(active ? row : 0) * k);
+    const float4* g4 = reinterpret_cast<const float4*>(gamma);
+    float4* nout = norm_out ? reinterpret_cast<float4*>(norm_out + (size_t)(active ? row : 0) * k) : nullptr;
+
+    float4 cache[CACHE ? kMaxVecPerThread : 1];
+    double ss = 0.0;
+    if (active) {
+        if constexpr (CACHE) {
+#pragma unroll
+            for (int i = 0; i < kMaxVecPerThread; i++) {
+                const uint32_t v = t + i * THREADS_PER_ROW;
+                cache[i] = v < nvec ? __ldg(in + v) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int i = 0; i < kMaxVecPerThread; i++) ss = square_sum4(cache[i], ss);
+        } else {
+            for (uint32_t v = t; v < nvec; v += THREADS_PER_ROW) ss = square_sum4(__ldg(in + v), ss);
+        }
+    }
+    ss = row_sum<THREADS_PER_ROW>(ss, smem_sum);
+    const double inv = 1.0 / sqrt(ss / (double)k + eps);
+
+    float amax = 0.0f; int bad = 0;
+    if (active) {
+        if constexpr (CACHE) {
+#pragma unroll
+            for (int i = 0; i < kMaxVecPerThread; i++) {
+                const uint32_t v = t + i * THREADS_PER_ROW;
+                if (v < nvec) {
+                    const float4 c = norm4(cache[i], inv, __ldg(g4 + v));
+                    cache[i] = c;
+                    if (nout) nout[v] = c;
+                    bad |= nonfinite_bits(c.x) | nonfinite_bits(c.y) | nonfinite_bits(c.z) | nonfinite_bits(c.w);
+                    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(c.x), fabsf(c.y)), fmaxf(fabsf(c.z), fabsf(c.w))));
+                }
+            }
+        } else {
+            for (uint32_t v = t; v < nvec; v += THREADS_PER_ROW) {
+                const float4 c = norm4(__ldg(in + v), inv, __ldg(g4 + v));
+                if (nout) nout[v] = c;
+                bad |= nonfinite_bits(c.x) | nonfinite_bits(c.y) | nonfinite_bits(c.z) | nonfinite_bits(c.w);
+                amax = fmaxf(amax, fmaxf(fmaxf(fabsf(c.x), fabsf(c.y)), fmaxf(fabsf(c.z), fabsf(c.w))));
+            }
+        }
+    }
+    row_reduce<THREADS_PER_ROW>(amax, bad, smem_max, smem_bad);
+    if (!active) return;
+
+    float scale = amax == 0.0f ? 1.0f : __fdiv_rn(amax, 127.0f);
+    scale = fmaxf(scale, 1.1754943508222875e-38f);
+    if (t == 0) {
+        row_scales[row] = bad ? __int_as_float(0x7fc00000) : scale;
+        if (valid) valid[row] = bad ? 0 : 1;
+    }
+    uint32_t* out = reinterpret_cast<uint32_t*>(q + (size_t)row * ldq);
+    const uint32_t nwords = ldq / 4;
+    const RowDivisor div(scale);
+    if constexpr (CACHE) {
+        const bool fast = div.fast && !bad;
+#pragma unroll
+        for (int i = 0; i < kMaxVecPerThread; i++) {
+            const uint32_t v = t + i * THREADS_PER_ROW;
+            if (v < nwords)
+                out[v] = (v < nvec && !bad) ? (fast ? pack4t<true>(cache[i], div) : pack4t<false>(cache[i], div)) : 0u;
+        }
+        for (uint32_t v = t + kMaxVecPerThread * THREADS_PER_ROW; v < nwords; v += THREADS_PER_ROW) out[v] = 0u;
+    } else {
+        for (uint32_t v = t; v < nwords; v += THREADS_PER_ROW)
+            out[v] = (v < nvec && !bad) ? pack4(norm4(__ldg(in + v), inv, __ldg(g4 + v)), div) : 0u;
+    }
+}
+
+// Any k / alignment: one warp per row, scalar accesses, the row is read three times.
+__global__ void __launch_bounds__(kThreads)
+rmsnorm_quantize_rows_scalar(const float* __restrict__ x, const float* __restrict__ gamma, double eps,
+                             uint32_t rows, uint32_t k, float* __restrict__ norm_out, int8_t* __restrict__ q,
+                             uint32_t ldq, float* __restrict__ row_scales, int32_t* __restrict__ valid) {
+    pdl_release();
+    pdl_wait();
+    const uint32_t row = blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const float* in = x + (size_t)row * k;
+    double ss = 0.0;
+    for (uint32_t j = lane; j < k; j += 32) ss = __fma_rn((double)in[j], (double)in[j], ss);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+    const double inv = 1.0 / sqrt(ss / (double)k + eps);
+    float amax = 0.0f; int bad = 0;
+    for (uint32_t j = lane; j < k; j += 32) {
+        const float v = norm1(in[j], inv, gamma[j]);
+        if (norm_out) norm_out[(size_t)row * k + j] = v;
+        bad |= nonfinite_bits(v);
+        amax = fmaxf(amax, fabsf(v));
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+        bad |= __shfl_xor_sync(0xffffffffu, bad, off);
+    }
+    float scale = amax == 0.0f ? 1.0f : __fdiv_rn(amax, 127.0f);
+    scale = fmaxf(scale, 1.1754943508222875e-38f);
+    if (lane == 0) {
+        row_scales[row] = bad ? __int_as_float(0x7fc00000) : scale;
+        if (valid) valid[row] = bad ? 0 : 1;
+    }
+    int8_t* out = q + (size_t)row * ldq;
+    const RowDivisor div(scale);
+    for (uint32_t j = lane; j < ldq; j += 32)
+        out[j] = (j < k && !bad) ? (int8_t)quant1<false>(norm1(in[j], inv, gamma[j]), div) : (int8_t)0;
+}
+
+template <int TPR>
+cudaError_t launch_norm_vec(const float* x, const float* gamma, double eps, uint32_t rows, uint32_t k,
+                            float* norm_out, int8_t* q, uint32_t ldq, float* row_scales, int32_t* valid,
+                            cudaStream_t stream) {
+    constexpr int kRowsPerCta = kThreads / TPR;
+    const uint32_t grid = (rows + kRowsPerCta - 1) / kRowsPerCta;
+    if (k / 4 <= (uint32_t)TPR * kMaxVecPerThread)
+        return launch_pdl(rmsnorm_quantize_rows_vec<TPR, true>, dim3(grid), dim3(kThreads), 0, stream,
+                          x, gamma, eps, rows, k, norm_out, q, ldq, row_scales, valid);
+    return launch_pdl(rmsnorm_quantize_rows_vec<TPR, false>, dim3(grid), dim3(kThreads), 0, stream,
+                      x, gamma, eps, rows, k, norm_out, q, ldq, row_scales, valid);
+}
+
 }  // namespace
 
 cudaError_t launch_quantize_rows(const float* x, uint32_t rows, uint32_t k, int8_t* q, uint32_t ldq,
@@ -370,6 +552,25 @@ cudaError_t launch_quantize_rows(const float* x, uint32_t rows, uint32_t k, int8
     if (k <= 2048) return launch_vec<64>(x, rows, k, q, ldq, row_scales, valid, stream);
     if (k <= 4096) return launch_vec<128>(x, rows, k, q, ldq, row_scales, valid, stream);
     return launch_vec<256>(x, rows, k, q, ldq, row_scales, valid, stream);
+}
+
+cudaError_t launch_rmsnorm_quantize_rows(const float* x, const float* gamma, float epsilon, uint32_t rows,
+                                         uint32_t k, float* norm_out, int8_t* q, uint32_t ldq,
+                                         float* row_scales, int32_t* valid, cudaStream_t stream) {
+    if (rows == 0) return cudaSuccess;
+    const double eps = (double)epsilon;
+    const bool vec = (k % 4 == 0) && (ldq % 4 == 0) && ((uintptr_t)x % 16 == 0) && ((uintptr_t)gamma % 16 == 0) &&
+                     ((uintptr_t)norm_out % 16 == 0) && ((uintptr_t)q % 4 == 0);
+    if (!vec) {
+        const uint32_t grid = (rows + kThreads / 32 - 1) / (kThreads / 32);
+        return launch_pdl(rmsnorm_quantize_rows_scalar, dim3(grid), dim3(kThreads), 0, stream,
+                          x, gamma, eps, rows, k, norm_out, q, ldq, row_scales, valid);
+    }
+    if (k <= 256) return launch_norm_vec<8>(x, gamma, eps, rows, k, norm_out, q, ldq, row_scales, valid, stream);
+    if (k <= 1024) return launch_norm_vec<32>(x, gamma, eps, rows, k, norm_out, q, ldq, row_scales, valid, stream);
+    if (k <= 2048) return launch_norm_vec<64>(x, gamma, eps, rows, k, norm_out, q, ldq, row_scales, valid, stream);
+    if (k <= 4096) return launch_norm_vec<128>(x, gamma, eps, rows, k, norm_out, q, ldq, row_scales, valid, stream);
+    return launch_norm_vec<256>(x, gamma, eps, rows, k, norm_out, q, ldq, row_scales, valid, stream);
 }
 
 cudaError_t launch_fill_f32(float* dst, uint32_t count, float value, cudaStream_t stream) {

@@ -126,6 +126,33 @@ class Context:
         _check(self._L.vxb_quantize_rows(self.handle, _ptr(x), rows, k, _ptr(q), ldq, _ptr(s), _ptr(v)))
         return q, s, v
 
+    def rmsnorm_quantize_rows(self, x, norm_weight, epsilon: float, ldq: int | None = None,
+                              want_norm: bool = True):
+        """RMSNorm folded into the quantizer: -> (normalized fp32 rows or None, q, scales, valid)."""
+        import torch
+        rows, k = x.shape
+        ldq = ldq or k
+        q = torch.empty((rows, ldq), dtype=torch.int8, device=x.device)
+        s = torch.empty(rows, dtype=torch.float32, device=x.device)
+        v = torch.empty(rows, dtype=torch.int32, device=x.device)
+        y = torch.empty_like(x) if want_norm else None
+        _check(self._L.vxb_rmsnorm_quantize_rows(self.handle, _ptr(x), _ptr(norm_weight), float(epsilon), rows, k,
+                                                 _ptr(y) if want_norm else None, _ptr(q), ldq, _ptr(s), _ptr(v)))
+        return y, q, s, v
+
+    def rmsnorm_linear_f32_fused(self, w: "Weight", x, norm_weight, epsilon: float, silu_mul: bool = False,
+                                 norm_out=None, out=None):
+        """RMSNorm -> quantize -> linear (+ silu(gate) * up over interleaved channel pairs)."""
+        import torch
+        rows = x.shape[0]
+        width = w.d_out // 2 if silu_mul else w.d_out
+        if out is None:
+            out = torch.empty((rows, width), dtype=torch.float32, device=x.device)
+        _check(self._L.vxb_rmsnorm_linear_f32_fused(self.handle, w.handle, _ptr(x), _ptr(norm_weight), float(epsilon),
+                                                    _ptr(norm_out) if norm_out is not None else None, rows,
+                                                    _ptr(out), out.stride(0), 1 if silu_mul else 0))
+        return out
+
     def linear_f32(self, w: "Weight", x, out=None, route: int = ROUTE_AUTO):
         import torch
         rows = x.shape[0]
