@@ -51,9 +51,11 @@ __device__ __forceinline__ int32_t quant1(float v, const RowDivisor& d) {
 }
 
 // x / scale for two elements with the packed fp32 instructions (div_const, each half rounded like
-// the scalar instruction), then round-to-nearest-even with saturation in one conversion: |x| <=
-// amax = 127 * scale up to rounding, so the quotient never reaches +-127.5 and the int8 saturation
-// bound of the instruction (-128) is never hit - the result is the clamp to +-127 of the contract.
+// the scalar instruction), then round-to-nearest-even by adding 1.5 * 2^23: the sum's low mantissa
+// bits are the two's-complement integer, rounded by the addition itself (ties to even), so no
+// conversion instruction is needed.  |x| <= amax = 127 * scale up to rounding, so the quotient
+// never reaches +-127.5 and the code stays within +-127, the clamp of the contract.  The low
+// byte of each returned word is the int8 code.
 __device__ __forceinline__ void quant2_fast(float x0, float x1, uint64_t rcp2, uint64_t neg_d2, int32_t& q0, int32_t& q1) {
     const uint64_t a = f32x2(x0, x1);
     const uint64_t d0 = mul_f32x2(a, rcp2);
@@ -61,10 +63,9 @@ __device__ __forceinline__ void quant2_fast(float x0, float x1, uint64_t rcp2, u
     const uint64_t d1 = fma_f32x2(r0, rcp2, d0);
     const uint64_t r1 = fma_f32x2(neg_d2, d1, a);
     const uint64_t q = fma_f32x2(r1, rcp2, d1);
-    float f0, f1;
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(f0), "=f"(f1) : "l"(q));
-    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q0) : "f"(f0));
-    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q1) : "f"(f1));
+    uint64_t m;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(m) : "l"(q), "l"(f32x2(12582912.0f, 12582912.0f)));
+    asm("mov.b64 {%0, %1}, %2;" : "=r"(q0), "=r"(q1) : "l"(m));
 }
 
 template <bool FAST>
