@@ -287,6 +287,36 @@ def test_grouped_scales_vs_oracle(torch, ctx, oracle, group, rows, k, n):
     wg.close()
 
 
+@pytest.mark.parametrize("group", [32, 64, 128, 256])
+@pytest.mark.parametrize("rows,k,n", [(16, 300, 50), (130, 1283, 130), (300, 4096, 520), (1000, 576, 1000),
+                                      (257, 2048 + 128, 385)])
+def test_grouped_scales_tensor_core_kernel(torch, ctx, oracle, group, rows, k, n):
+    """From 16 rows up grouped scales run on the tensor cores with one accumulator drain per group:
+    bit-equal to the oracle's grouped forward and to the CUDA-core kernel; ragged tiles, a last group
+    shorter than the others, NaN and zero rows."""
+    from volvoxai_b200 import _lib, w8a8
+    rng = np.random.default_rng(group * 3 + rows + k + n)
+    c = wl.single_linear(rows=rows, k=k, n=n, seed=group + rows + 5)
+    words = wl.pack_w8_words(c["w"])
+    groups = (k + group - 1) // group
+    gs = (c["ws"][:, None] * rng.uniform(0.5, 2.0, size=(n, groups))).astype(np.float32)
+    x = c["x"].copy()
+    x[1] = 0
+    x[2, k // 2] = np.nan
+    wg = w8a8.Weight.from_w8_words(ctx, words, gs, k, group, bias_f32=c["bias"])
+    xd = dev(torch, x)
+    y = ctx.linear_f32(wg, xd).cpu().numpy()
+    assert "tcgen05-grouped-i8" in _lib.last_route()
+    want = oracle.packed_linear_w8_grouped(x, words, gs, group, c["bias"])
+    assert np.array_equal(np.isnan(y), np.isnan(want))
+    ok = ~np.isnan(want)
+    assert np.array_equal(y[ok].view(np.uint32), want[ok].view(np.uint32))
+    y2 = ctx.linear_f32(wg, xd, route=w8a8.ROUTE_SIMT).cpu().numpy()
+    assert "dp4a-grouped" in _lib.last_route()
+    assert np.array_equal(y2[ok].view(np.uint32), y[ok].view(np.uint32))
+    wg.close()
+
+
 @pytest.mark.parametrize("tag,group,k", [("r1w4_5x257x7_g128", 128, 257), ("r1w4_9x320x12_g32", 32, 320),
                                          ("r1w4_3x1283x6_g256", 256, 1283)])
 def test_w4_words_golden(torch, ctx, golden, tag, group, k):

@@ -104,6 +104,7 @@ struct VxbContext {
     int* status_host = nullptr;   // pinned mirror
     bool tcgen05_ready = false;
     bool pair_ready = false;
+    bool grouped_ready = false;
     // optional per-kernel timing (event pairs on the launching stream)
     // vxb_linear_host: upload / download streams and their events
     cudaStream_t copy_in = nullptr, copy_out = nullptr;
@@ -130,6 +131,8 @@ struct VxbWeight {
     // grouped scales (storage groups of the reference's PackedLinear): 0 = per-channel
     uint32_t group = 0, groups = 0;
     float* gscales = nullptr;  // [d_out, groups]
+    float* gscales_t = nullptr;  // [groups, n_pad], n_pad = round_up(d_out, 128), padding zero (tensor-core grouped kernel)
+    uint32_t n_pad = 0;
 };
 
 namespace {
@@ -206,6 +209,25 @@ void set_requant_divisor(EpilogueParams& epi, const VxbWeight* w, float out_scal
     epi.fast_div = (!all_ones && out_scale >= lo && out_scale <= hi && w->ws_min >= lo && w->ws_max <= hi) ? 1 : 0;
 }
 
+// Group scales that differ within a channel: keep them as given ([d_out, groups], CUDA-core
+// kernel) and transposed and padded ([groups, n_pad], tensor-core kernel).
+int upload_group_scales(VxbContext* ctx, VxbWeight* w, const float* group_scales, uint32_t d_out,
+                        uint32_t groups, uint32_t group_size) {
+    const size_t gbytes = (size_t)d_out * groups * 4;
+    const uint32_t n_pad = (d_out + 127u) / 128u * 128u;
+    std::vector<float> t((size_t)groups * n_pad, 0.0f);
+    for (uint32_t n = 0; n < d_out; n++)
+        for (uint32_t g = 0; g < groups; g++) t[(size_t)g * n_pad + n] = group_scales[(size_t)n * groups + g];
+    if (cudaMalloc(&w->gscales, gbytes) != cudaSuccess || cudaMalloc(&w->gscales_t, t.size() * 4) != cudaSuccess)
+        return fail(0, "group scale allocation failed");
+    if (cudaMemcpyAsync(w->gscales, group_scales, gbytes, cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess ||
+        cudaMemcpyAsync(w->gscales_t, t.data(), t.size() * 4, cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess)
+        return fail(-1, "group scale upload failed");
+    if (cudaStreamSynchronize(ctx->stream) != cudaSuccess) return fail(-1, "group scale upload failed");
+    w->group = group_size; w->groups = groups; w->n_pad = n_pad; w->bytes += gbytes + t.size() * 4;
+    return 1;
+}
+
 struct Plan {
     int route;
     const char* name;
@@ -233,10 +255,29 @@ int run_gemm(VxbContext* ctx, const VxbWeight* w, const int8_t* q, uint32_t rows
         // differing group scales: exact per-group arithmetic, fp32 output only
         if (!requested_auto && requested != VXB_ROUTE_SIMT) return fail(0, "weights with grouped scales take the automatic route only");
         if (epi.mode != kEpiF32) return fail(0, "weights with grouped scales produce fp32 output only");
-        EpilogueParams ge = epi;
-        ge.gscales = w->gscales; ge.group = w->group; ge.groups = w->groups;
-        CUDA_TRY(launch_gemm_grouped(q, rows, w->w, w->d_out, w->kpad, ge, ctx->stream), -1);
-        plan.name = "dp4a-grouped";
+        if (epi.residual || epi.act) return fail(0, "weights with grouped scales have no fused epilogue");
+        // tensor cores with one accumulator drain per group from 16 rows up; below that (and on the
+        // explicit CUDA-core route) one thread per channel
+        if (requested_auto && rows >= 16 && w->has_tmap && w->gscales_t) {
+            if (!ctx->grouped_ready) {
+                CUDA_TRY(gemm_grouped_tcgen05_prepare(), 0);
+                ctx->grouped_ready = true;
+            }
+            GemmGroupedArgs a;
+            if (!encode_i8_rows(&a.tmap_a, q, rows, w->kpad, 128)) return fail(0, "cuTensorMapEncodeTiled failed for activations");
+            a.tmap_b = w->tmap_w128;
+            a.rows = rows; a.n = w->d_out; a.kpad = w->kpad;
+            a.group = w->group; a.groups = w->groups; a.n_pad = w->n_pad; a.gscales_t = w->gscales_t;
+            a.row_scales = epi.row_scales; a.bias = epi.bias_f32; a.out = (float*)epi.out; a.ld = epi.ld;
+            a.status = ctx->status;
+            CUDA_TRY(launch_gemm_grouped_tcgen05(a, ctx->sm_count, ctx->stream), -1);
+            plan.name = "tcgen05-grouped-i8";
+        } else {
+            EpilogueParams ge = epi;
+            ge.gscales = w->gscales; ge.group = w->group; ge.groups = w->groups;
+            CUDA_TRY(launch_gemm_grouped(q, rows, w->w, w->d_out, w->kpad, ge, ctx->stream), -1);
+            plan.name = "dp4a-grouped";
+        }
     } else if (plan.route == VXB_ROUTE_GEMV) {
         if (rows > 32) return fail(0, "gemv route needs rows <= 32 (got %u)", rows);
         CUDA_TRY(launch_gemv(q, rows, w->w, w->d_out, w->kpad, epi, ctx->sm_count, ctx->stream), -1);
@@ -468,13 +509,7 @@ int vxb_weight_create_w8_words(VxbContext* ctx, const int32_t* words, const floa
     else if (cudaMemcpyAsync(staging.ptr, words, src_bytes, cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess)
         rc = fail(-1, "weight upload failed");
     else rc = finish_weight(ctx, w, (const uint8_t*)staging.ptr, row_words * 4, 0x80u, ws.data(), bias_f32, nullptr);
-    if (rc == 1 && grouped) {
-        const size_t gbytes = (size_t)d_out * groups * 4;
-        if (cudaMalloc(&w->gscales, gbytes) != cudaSuccess) rc = fail(0, "group scale allocation failed");
-        else if (cudaMemcpyAsync(w->gscales, group_scales, gbytes, cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess)
-            rc = fail(-1, "group scale upload failed");
-        else { w->group = group_size; w->groups = groups; w->bytes += gbytes; }
-    }
+    if (rc == 1 && grouped) rc = upload_group_scales(ctx, w, group_scales, d_out, groups, group_size);
     cudaStreamSynchronize(ctx->stream);
     staging.release();
     if (rc != 1) { vxb_weight_destroy(w); return rc; }
@@ -521,13 +556,7 @@ int vxb_weight_create_w4_words(VxbContext* ctx, const int32_t* words, const floa
     else if (cudaMemcpyAsync(staging.ptr, dense.data(), dense.size(), cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess)
         rc = fail(-1, "weight upload failed");
     else rc = finish_weight(ctx, w, (const uint8_t*)staging.ptr, d_in, 0u, ws.data(), bias_f32, nullptr);
-    if (rc == 1 && grouped) {
-        const size_t gbytes = (size_t)d_out * groups * 4;
-        if (cudaMalloc(&w->gscales, gbytes) != cudaSuccess) rc = fail(0, "group scale allocation failed");
-        else if (cudaMemcpyAsync(w->gscales, group_scales, gbytes, cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess)
-            rc = fail(-1, "group scale upload failed");
-        else { w->group = group_size; w->groups = groups; w->bytes += gbytes; }
-    }
+    if (rc == 1 && grouped) rc = upload_group_scales(ctx, w, group_scales, d_out, groups, group_size);
     cudaStreamSynchronize(ctx->stream);
     staging.release();
     if (rc != 1) { vxb_weight_destroy(w); return rc; }
@@ -544,6 +573,7 @@ void vxb_weight_destroy(VxbWeight* w) {
     if (w->bias_i32) cudaFree(w->bias_i32);
     if (w->wsum) cudaFree(w->wsum);
     if (w->gscales) cudaFree(w->gscales);
+    if (w->gscales_t) cudaFree(w->gscales_t);
     delete w;
 }
 uint32_t vxb_weight_d_in(const VxbWeight* w) { return w ? w->d_in : 0; }

@@ -290,6 +290,23 @@ cudaError_t gemm_pair_prepare();    // func attribute + how many pairs can be re
 int gemm_pair_clusters();           // 0: pairs cannot run on this device
 cudaError_t launch_gemm_pair(const GemmTcgen05Args& args, cudaStream_t stream);
 
+// K2g: the GEMM for weights with grouped scales on the tensor cores (fp32 output).  tmap_a and
+// tmap_b have boxes of 128 rows; gscales_t is the group-scale table transposed to
+// [groups][n_pad] (n_pad a multiple of 128, padding zero).
+struct GemmGroupedArgs {
+    CUtensorMap tmap_a, tmap_b;
+    uint32_t rows, n, kpad;
+    uint32_t group, groups, n_pad;
+    const float* gscales_t;
+    const float* row_scales;
+    const float* bias;
+    float* out;
+    uint32_t ld;
+    int* status;
+};
+cudaError_t gemm_grouped_tcgen05_prepare();
+cudaError_t launch_gemm_grouped_tcgen05(const GemmGroupedArgs& args, int sm_count, cudaStream_t stream);
+
 // K3: decode kernel in which every CTA owns whole output channels (rows <= 128).
 // tile_rows / tiles_per_cta come from decode_rows_plan(); tmap_w has a box of tile_rows rows,
 // tmap_x a box of decode_rows_token_slots(rows) rows.
