@@ -390,6 +390,50 @@ def model_linear_stacks(torch, ctx, w8a8, peaks, replays=5):
     return out
 
 
+def widened_rows(torch, ctx, w8a8, peaks, replays=10):
+    """Kernels of the rows next to the headline path, timed alone with CUDA events (inputs larger than
+    L2 or an L2 flush between launches is not applied here: these are secondary figures): the GEMM for
+    weights with grouped scales (G = 128, the exporter's default; also W4 storage, which is unpacked to
+    int8 at load and takes the same kernel) and RMSNorm folded into the quantizer."""
+    out = {}
+    rows, k, n, group = 4096, 4096, 4096, 128
+    rng = np.random.default_rng(77)
+    w = rng.integers(-127, 128, size=(n, k), dtype=np.int8)
+    gs = rng.uniform(0.001, 0.02, size=(n, k // group)).astype(np.float32)
+    x = torch.randn(rows, k, device="cuda")
+    y = torch.empty(rows, n, device="cuda")
+
+    def time_us(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(replays):
+            fn()
+        e1.record()
+        e1.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / replays
+
+    for label, weight in (("w8_g128", w8a8.Weight.from_w8_words(ctx, wl.pack_w8_words(w), gs, k, group)),
+                          ("w4_g128", w8a8.Weight.from_w4_words(ctx, wl.pack_w4_words((w >> 4).astype(np.int8)), gs, k, group))):
+        q, sc = ctx.prepare(weight, x)
+        us = time_us(lambda: ctx.linear_prepared(weight, q, sc, y, mode=1))
+        out["grouped_gemm_" + label] = {"rows": rows, "k": k, "n": n, "kernel_us": us,
+                                        "tops": 2.0 * rows * k * n / us / 1e6, "route": w8a8.last_route()}
+        weight.close()
+    rows = 8192
+    x = torch.randn(rows, k, device="cuda")
+    gamma = torch.rand(k, device="cuda") + 0.5
+    plain = time_us(lambda: ctx.quantize_rows(x))
+    fused = time_us(lambda: ctx.rmsnorm_quantize_rows(x, gamma, 1e-6, want_norm=False))
+    kept = time_us(lambda: ctx.rmsnorm_quantize_rows(x, gamma, 1e-6, want_norm=True))
+    out["rmsnorm_quantize"] = {"rows": rows, "k": k, "quantize_us": plain, "rmsnorm_quantize_us": fused,
+                               "rmsnorm_quantize_keep_rows_us": kept,
+                               "note": "times include the output allocation of the Python mirror"}
+    return out
+
+
 def gpu_arm(args):
     import torch
     import torch.distributed as dist
@@ -587,7 +631,8 @@ def gpu_arm(args):
         line["cpu_baseline"] = None
     if rank == 0 and world == 1 and not args.no_extras:
         line["extras"] = {"gemv_sweep": gemv_sweep(torch, ctx, w8a8, peaks),
-                          "model_linear_stacks": model_linear_stacks(torch, ctx, w8a8, peaks)}
+                          "model_linear_stacks": model_linear_stacks(torch, ctx, w8a8, peaks),
+                          "widened_rows": widened_rows(torch, ctx, w8a8, peaks)}
 
     weight.close()
     ctx.close()
@@ -667,9 +712,65 @@ def decode_arm(args):
     print(json.dumps(line), flush=True)
 
 
+def grouped_arm(args):
+    """`--workload grouped --rows M --k K --n N --group G`: the linear over PackedLinear storage whose
+    group scales differ within a channel (fp32 output), quantizer + grouped-scale GEMM per step on
+    device-resident activations. A secondary figure (one JSON line, tensor roofline of the
+    grouped kernel); the ncu summaries of that kernel were taken with this command."""
+    import torch
+    from volvoxai_b200 import w8a8
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device; there is no CPU fallback")
+    peaks = measured_peaks()
+    rows, k, n, group = args.rows, args.k, args.n, args.group
+    ctx = w8a8.Context(0)
+    ctx.use_torch_stream()
+    rng = np.random.default_rng(11)
+    w = rng.integers(-127, 128, size=(n, k), dtype=np.int8)
+    gs = rng.uniform(0.001, 0.02, size=(n, (k + group - 1) // group)).astype(np.float32)
+    weight = w8a8.Weight.from_w8_words(ctx, wl.pack_w8_words(w), gs, k, group)
+    x = torch.randn(rows, k, device="cuda")
+    y = torch.empty((rows, n), dtype=torch.float32, device="cuda")
+    q, sc = ctx.prepare(weight, x)
+
+    def timed(fn, count):
+        for _ in range(max(3, args.warmup)):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(count):
+            fn()
+        e1.record()
+        e1.synchronize()
+        return e0.elapsed_time(e1) / count
+
+    launches0 = w8a8.launch_count()
+    step_ms = timed(lambda: ctx.linear_f32(weight, x, out=y), args.steps)
+    launches = w8a8.launch_count() - launches0
+    route = w8a8.last_route()
+    kern_ms = timed(lambda: ctx.linear_prepared(weight, q, sc, y, mode=1), args.steps)
+    ops = 2.0 * rows * k * n
+    peak = 2.0 * peaks["bf16_tflops"]
+    line = {
+        "metric": "w8a8_grouped_linear_int8_tops", "value": ops / (step_ms * 1e-3) / 1e12, "unit": "TOPS",
+        "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": step_ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+        "config": {"workload": f"w8a8_linear_grouped_M{rows}_K{k}_N{n}_G{group}_f32", "rows": rows, "k": k, "n": n,
+                   "group": group, "route": route, "l2": "activations + weights + output exceed L2 at the default shape"},
+        "gpu_launches": int(launches),
+        "roofline": {"bound": "tensor", "achieved": ops / (kern_ms * 1e-3) / 1e12, "peak": peak, "unit": "TFLOP/s",
+                     "frac": ops / (kern_ms * 1e-3) / 1e12 / peak, "traffic": None,
+                     "kernel": "gemm_i8_grouped_tcgen05_kernel", "kernel_ms": kern_ms, "peak_source": peaks["_source"]},
+    }
+    weight.close()
+    ctx.close()
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="gemm", choices=["gemm", "decode"])
+    ap.add_argument("--workload", default="gemm", choices=["gemm", "decode", "grouped"])
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
@@ -677,17 +778,20 @@ def main():
     ap.add_argument("--rows", type=int, default=None)
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--n", type=int, default=14336)
+    ap.add_argument("--group", type=int, default=128, help="scale group size of --workload grouped")
     ap.add_argument("--cpu-rows", type=int, default=512, help="row sample for the CPU legs")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true")
     args = ap.parse_args()
     if args.rows is None:
-        args.rows = 8 if args.workload == "decode" else 8192
+        args.rows = 8 if args.workload == "decode" else 4096 if args.workload == "grouped" else 8192
     if args.impl == "reference":
         reference_arm(args)
     elif args.workload == "decode":
         decode_arm(args)
+    elif args.workload == "grouped":
+        grouped_arm(args)
     else:
         gpu_arm(args)
 

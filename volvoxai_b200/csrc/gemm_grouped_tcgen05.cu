@@ -11,15 +11,16 @@
 // them rotate), and the epilogue warps read it, convert, scale and add into fp32 running sums
 // that stay in registers for the whole K loop.
 //
-//   warp 0      TMA producer, activation tile (128 rows x 128 B per stage)
-//   warp 10     TMA producer, weight tile (128 channels x 128 B per stage)
+//   warp 0      TMA producers: lane 0 the activation tile (128 rows x 128 B per stage), lane 1
+//               the weight tile (128 channels x 128 B)
 //   warp 1      allocates TMEM; one lane issues tcgen05.mma.cta_group::1.kind::i8
 //               (M128 x N128 x K32), G/32 instructions per group
 //   warps 2-9   drain: two warps per TMEM lane quarter, 64 columns each (the drain is bound by
 //               fp32 issue: sixteen warps of 32 columns were no faster)
 //
 // int32 -> fp32 without a conversion instruction: |dot_g| <= 256 * 127 * 128 < 2^22, so
-// as_float(dot + 0x4B400000) - 1.5 * 2^23 is the exact value.
+// as_float(dot + 0x4B400000) - 1.5 * 2^23 is the exact value, and the addition of 0x4B400000 is
+// done by the tensor core (the accumulators start from that bit pattern instead of zero).
 // Every wait on an mbarrier is bounded; on expiry the kernel raises a status word, drains,
 // frees its TMEM and returns.
 #include "tcgen05.cuh"
@@ -35,8 +36,8 @@ constexpr uint32_t kStages = 6;
 constexpr uint32_t kABytes = kBM * kBK, kBBytes = kBN * kBK, kStageBytes = kABytes + kBBytes;
 constexpr uint32_t kAccBufs = 4, kAccCols = kBN, kTmemCols = 512;
 constexpr uint32_t kEpiWarps = 8, kEpiCols = kBN / 2;
-constexpr uint32_t kThreads = 64 + 32 * kEpiWarps + 32;
-constexpr uint32_t kBWarp = 2 + kEpiWarps;
+constexpr uint32_t kThreads = 64 + 32 * kEpiWarps;
+constexpr uint32_t kEndWarp = 2 + kEpiWarps;
 
 constexpr uint32_t kOffStages = 0;
 constexpr uint32_t kOffGs = kStages * kStageBytes;                  // float[8 warps][64] group scales
@@ -61,11 +62,29 @@ struct Smem {
     __device__ volatile int* abort_flag() const { return reinterpret_cast<volatile int*>(base + kOffAbort); }
 };
 
-// sum += f32(dot) * (as * gs), every operation rounded on its own; five fp32-pipe instructions
-// per element and no register shuffling (the packed f32x2 forms needed moves to pair their
-// operands and were slower here)
-__device__ __forceinline__ void drain1(uint32_t d, float as, float g, float& s) {
-    const float f = __fadd_rn(__uint_as_float(d + 0x4B400000u), -12582912.0f);
+// The accumulators are never zeroed: before every use the drain warps store the bit pattern of
+// 1.5 * 2^23 into them and the MMAs accumulate on top, so what comes back is 0x4B400000 + dot,
+// which read as fp32 is 12582912 + dot exactly (|dot| < 2^22).  One fp32 subtraction finishes the
+// int -> float conversion; no conversion instruction and no integer addition per element.
+constexpr uint32_t kBiasBits = 0x4B400000u;
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&c)[8]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+        ::"r"(taddr), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]), "r"(c[4]), "r"(c[5]), "r"(c[6]), "r"(c[7]) : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() {
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+// eight registers holding the bias serve all eight stores of a 64-column slice
+__device__ __forceinline__ void bias64(uint32_t taddr, const uint32_t (&c)[8]) {
+#pragma unroll
+    for (uint32_t i = 0; i < 8; i++) tmem_st8(taddr + 8u * i, c);
+}
+
+// sum += f32(dot) * (as * gs), every operation rounded on its own: four fp32-pipe instructions
+// per element (packed f32x2 forms of the same arithmetic were no faster here)
+__device__ __forceinline__ void drain1(uint32_t biased, float as, float g, float& s) {
+    const float f = __fadd_rn(__uint_as_float(biased), -12582912.0f);
     s = __fadd_rn(s, __fmul_rn(f, __fmul_rn(as, g)));
 }
 
@@ -104,42 +123,33 @@ gemm_i8_grouped_tcgen05_kernel(const __grid_constant__ GemmGroupedArgs args) {
     const uint32_t tmem_base = *sm.tmem_ptr();
 
     if (warp == 0) {
-        // ---------------- TMA producer, activation tiles ----------------
-        if (lane == 0) {
+        // ---------------- TMA producers: lane 0 the activation tile, lane 1 the weight tile ----------------
+        if (lane < 2) {
             uint32_t stage = 0, phase = 0, armed = 0, armed_parity = 0;
             bool ok = true;
             for (uint32_t t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
-                const int32_t m0 = (int32_t)((t % tiles_m) * kBM);
+                const int32_t m0 = (int32_t)((t % tiles_m) * kBM), n0 = (int32_t)((t / tiles_m) * kBN);
                 for (uint32_t kb = 0; kb < num_kb; kb++) {
                     if (!mbar_wait(sm.empty(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
-                    mbar_expect_tx(sm.full(stage), kStageBytes);
-                    tma_load_2d(sm.a(stage), &args.tmap_a, sm.full(stage), (int32_t)(kb * kBK), m0);
+                    if (lane == 0) {
+                        mbar_expect_tx(sm.full(stage), kStageBytes);
+                        tma_load_2d(sm.a(stage), &args.tmap_a, sm.full(stage), (int32_t)(kb * kBK), m0);
+                    } else {
+                        tma_load_2d(sm.b(stage), &args.tmap_b, sm.full(stage), (int32_t)(kb * kBK), n0);
+                    }
                     armed |= 1u << stage;
                     armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
             }
-            if (!ok) {
+            if (!ok && lane == 0) {
+                // drain: give this CTA's own copies in flight a bounded time to land
                 for (uint32_t s = 0; s < kStages; s++) {
                     if (!(armed & (1u << s))) continue;
                     for (uint32_t i = 0; i < 2000; i++) {
                         if (mbar_try_wait(sm.full(s), (armed_parity >> s) & 1u)) break;
                         __nanosleep(500);
                     }
-                }
-            }
-        }
-    } else if (warp == kBWarp) {
-        // ---------------- TMA producer, weight tiles ----------------
-        if (lane == 0) {
-            uint32_t stage = 0, phase = 0;
-            bool ok = true;
-            for (uint32_t t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
-                const int32_t n0 = (int32_t)((t / tiles_m) * kBN);
-                for (uint32_t kb = 0; kb < num_kb; kb++) {
-                    if (!mbar_wait(sm.empty(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
-                    tma_load_2d(sm.b(stage), &args.tmap_b, sm.full(stage), (int32_t)(kb * kBK), n0);
-                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
             }
         }
@@ -166,11 +176,12 @@ gemm_i8_grouped_tcgen05_kernel(const __grid_constant__ GemmGroupedArgs args) {
                         const bool first = MPG >= 8 ? (j == 0 && !(kb & 1u)) : (j % MPG == 0);
                         const bool last = MPG >= 8 ? (j == 3 && ((kb & 1u) || kb + 1 == num_kb)) : (j % MPG == MPG - 1);
                         if (first) {
-                            // a fresh accumulator for every group, once the drain of its previous use is over
-                            if (!mbar_try_wait(tempty, buf_phase ^ 1u) && !mbar_wait(tempty, buf_phase ^ 1u, abort_flag)) { ok = false; break; }
+                            // the next accumulator, once the drain warps have read its previous contents
+                            // and stored the conversion bias into it (phase 0: the fill at kernel start)
+                            if (!mbar_try_wait(tempty, buf_phase) && !mbar_wait(tempty, buf_phase, abort_flag)) { ok = false; break; }
                             tc_fence_after();
                         }
-                        umma_i8_lo_first(d_tmem, a_lo + 2u * j, a_lo + (kABytes >> 4) + 2u * j, idesc, first ? 0u : 1u);
+                        umma_i8_lo(d_tmem, a_lo + 2u * j, a_lo + (kABytes >> 4) + 2u * j, idesc);
                         if (last) {
                             umma_commit(tfull);
                             tfull += 8; tempty += 8; d_tmem += kAccCols;
@@ -184,7 +195,7 @@ gemm_i8_grouped_tcgen05_kernel(const __grid_constant__ GemmGroupedArgs args) {
                 }
             }
         }
-    } else if (warp < kBWarp) {
+    } else if (warp < kEndWarp) {
         // ---------------- drain and epilogue (warps 2..9) ----------------
         const uint32_t quarter = warp & 3u;              // TMEM lanes [32*quarter, +32)
         const uint32_t cbase = ((warp - 2u) >> 2) * kEpiCols;   // columns [cbase, +64) of the tile
@@ -193,6 +204,16 @@ gemm_i8_grouped_tcgen05_kernel(const __grid_constant__ GemmGroupedArgs args) {
         uint8_t* stage_store = sm.base + kOffStore + (warp - 2u) * kStoreBytes;
         uint32_t buf = 0, buf_phase = 0;
         bool ok = true;
+        // fill this warp's part of all four accumulators with the conversion bias
+        uint32_t bias_regs[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) asm volatile("mov.u32 %0, %1;" : "=r"(bias_regs[i]) : "n"(kBiasBits));   // opaque: one block of registers, not one per store
+        for (uint32_t b = 0; b < kAccBufs; b++) bias64(tmem_base + ((quarter * 32u) << 16) + b * kAccCols + cbase, bias_regs);
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0)
+            for (uint32_t b = 0; b < kAccBufs; b++) mbar_arrive(sm.tmem_empty(b));
         for (uint32_t t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
             const uint32_t m0 = (t % tiles_m) * kBM, n0 = (t / tiles_m) * kBN + cbase;
             const uint32_t row = m0 + quarter * 32 + lane;
@@ -235,7 +256,9 @@ gemm_i8_grouped_tcgen05_kernel(const __grid_constant__ GemmGroupedArgs args) {
                 }
                 tmem_ld32(taddr + 32u, r);
                 tmem_ld_wait();
-                // the accumulator is free again as soon as it is in registers
+                // the accumulator is free again as soon as it is in registers and holds the bias
+                bias64(taddr, bias_regs);
+                tmem_st_wait();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(sm.tmem_empty(buf));
