@@ -291,7 +291,7 @@ def test_grouped_scales_vs_oracle(torch, ctx, oracle, group, rows, k, n):
 @pytest.mark.parametrize("rows,k,n", [(16, 300, 50), (130, 1283, 130), (300, 4096, 520), (1000, 576, 1000),
                                       (257, 2048 + 128, 385)])
 def test_grouped_scales_tensor_core_kernel(torch, ctx, oracle, group, rows, k, n):
-    """From 16 rows up grouped scales run on the tensor cores with one accumulator drain per group:
+    """Grouped scales run on the tensor cores with one accumulator drain per group:
     bit-equal to the oracle's grouped forward and to the CUDA-core kernel; ragged tiles, a last group
     shorter than the others, NaN and zero rows."""
     from volvoxai_b200 import _lib, w8a8

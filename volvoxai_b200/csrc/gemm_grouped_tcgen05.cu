@@ -15,8 +15,8 @@
 //               the weight tile (128 channels x 128 B)
 //   warp 1      allocates TMEM; one lane issues tcgen05.mma.cta_group::1.kind::i8
 //               (M128 x N128 x K32), G/32 instructions per group
-//   warps 2-9   drain: two warps per TMEM lane quarter, 64 columns each (the drain is bound by
-//               fp32 issue: sixteen warps of 32 columns were no faster)
+//   warps 2-9   drain: two warps per TMEM lane quarter, 64 columns each (sixteen warps of 32
+//               columns were 1.6x slower: barrier, fence and bias-store overhead is per warp)
 //
 // int32 -> fp32 without a conversion instruction: |dot_g| <= 256 * 127 * 128 < 2^22, so
 // as_float(dot + 0x4B400000) - 1.5 * 2^23 is the exact value, and the addition of 0x4B400000 is
@@ -35,7 +35,8 @@ constexpr uint32_t kBM = 128, kBN = 128, kBK = 128;
 constexpr uint32_t kStages = 6;
 constexpr uint32_t kABytes = kBM * kBK, kBBytes = kBN * kBK, kStageBytes = kABytes + kBBytes;
 constexpr uint32_t kAccBufs = 4, kAccCols = kBN, kTmemCols = 512;
-constexpr uint32_t kEpiWarps = 8, kEpiCols = kBN / 2;
+constexpr uint32_t kEpiWarps = 8, kEpiCols = kBN * 4 / kEpiWarps;   // two warps per TMEM lane quarter (sixteen were 1.6x slower: the per-group barrier and store overhead is per warp)
+constexpr uint32_t kChunks = kEpiCols / 32, kGsLanes = kEpiCols / 4;
 constexpr uint32_t kThreads = 64 + 32 * kEpiWarps;
 constexpr uint32_t kEndWarp = 2 + kEpiWarps;
 
@@ -75,10 +76,10 @@ __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&c)[8])
 __device__ __forceinline__ void tmem_st_wait() {
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
-// eight registers holding the bias serve all eight stores of a 64-column slice
-__device__ __forceinline__ void bias64(uint32_t taddr, const uint32_t (&c)[8]) {
+// eight registers holding the bias serve all stores of a warp's column slice
+__device__ __forceinline__ void bias_slice(uint32_t taddr, const uint32_t (&c)[8]) {
 #pragma unroll
-    for (uint32_t i = 0; i < 8; i++) tmem_st8(taddr + 8u * i, c);
+    for (uint32_t i = 0; i < kEpiCols / 8u; i++) tmem_st8(taddr + 8u * i, c);
 }
 
 // sum += f32(dot) * (as * gs), every operation rounded on its own: four fp32-pipe instructions
@@ -208,7 +209,7 @@ gemm_i8_grouped_tcgen05_kernel(const __grid_constant__ GemmGroupedArgs args) {
         uint32_t bias_regs[8];
 #pragma unroll
         for (int i = 0; i < 8; i++) asm volatile("mov.u32 %0, %1;" : "=r"(bias_regs[i]) : "n"(kBiasBits));   // opaque: one block of registers, not one per store
-        for (uint32_t b = 0; b < kAccBufs; b++) bias64(tmem_base + ((quarter * 32u) << 16) + b * kAccCols + cbase, bias_regs);
+        for (uint32_t b = 0; b < kAccBufs; b++) bias_slice(tmem_base + ((quarter * 32u) << 16) + b * kAccCols + cbase, bias_regs);
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
@@ -230,46 +231,56 @@ gemm_i8_grouped_tcgen05_kernel(const __grid_constant__ GemmGroupedArgs args) {
             // this warp's 64 scales of a group are 256 contiguous bytes of the transposed table
             const float4* gs4 = reinterpret_cast<const float4*>(args.gscales_t + n0) + lane;
             const uint32_t gstride4 = args.n_pad / 4u;
+            const bool live = m0 + quarter * 32u < args.rows && n0 < args.n;
             float4 pre = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (lane < 16) pre = __ldg(gs4);
+            if (live && lane < kGsLanes) pre = __ldg(gs4);
 #pragma unroll 1
             for (uint32_t g = 0; g < args.groups; g++) {
+                const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + buf * kAccCols + cbase;
+                if (!live) {
+                    // none of this warp's 32 rows or 64 columns exists (few rows: decode): keep the
+                    // barrier protocol and the bias of its accumulator slice, skip the arithmetic
+                    ok = __all_sync(0xffffffffu, mbar_wait(sm.tmem_full(buf), buf_phase, abort_flag));
+                    if (!ok) break;
+                    tc_fence_after();
+                    bias_slice(taddr, bias_regs);
+                    tmem_st_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(sm.tmem_empty(buf));
+                    if (++buf == kAccBufs) { buf = 0; buf_phase ^= 1u; }
+                    continue;
+                }
                 __syncwarp();
-                if (lane < 16) reinterpret_cast<float4*>(s_gs)[lane] = pre;
+                if (lane < kGsLanes) reinterpret_cast<float4*>(s_gs)[lane] = pre;
                 __syncwarp();
-                if (lane < 16 && g + 1 < args.groups) pre = __ldg(gs4 + (size_t)(g + 1) * gstride4);
+                if (lane < kGsLanes && g + 1 < args.groups) pre = __ldg(gs4 + (size_t)(g + 1) * gstride4);
                 ok = __all_sync(0xffffffffu, mbar_wait(sm.tmem_full(buf), buf_phase, abort_flag));
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + buf * kAccCols + cbase;
                 const float4* g4 = reinterpret_cast<const float4*>(s_gs);
                 uint32_t r[32];
-                tmem_ld32(taddr, r);
-                tmem_ld_wait();
 #pragma unroll
-                for (int j = 0; j < 8; j++) {
-                    const float4 gv = g4[j];
-                    drain1(r[4 * j + 0], as, gv.x, sum[4 * j + 0]);
-                    drain1(r[4 * j + 1], as, gv.y, sum[4 * j + 1]);
-                    drain1(r[4 * j + 2], as, gv.z, sum[4 * j + 2]);
-                    drain1(r[4 * j + 3], as, gv.w, sum[4 * j + 3]);
-                }
-                tmem_ld32(taddr + 32u, r);
-                tmem_ld_wait();
-                // the accumulator is free again as soon as it is in registers and holds the bias
-                bias64(taddr, bias_regs);
-                tmem_st_wait();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(sm.tmem_empty(buf));
-                if (++buf == kAccBufs) { buf = 0; buf_phase ^= 1u; }
+                for (uint32_t ch = 0; ch < kChunks; ch++) {
+                    tmem_ld32(taddr + 32u * ch, r);
+                    tmem_ld_wait();
+                    if (ch == kChunks - 1) {
+                        // the accumulator is free again as soon as it is in registers and holds the bias
+                        bias_slice(taddr, bias_regs);
+                        tmem_st_wait();
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(sm.tmem_empty(buf));
+                        if (++buf == kAccBufs) { buf = 0; buf_phase ^= 1u; }
+                    }
 #pragma unroll
-                for (int j = 0; j < 8; j++) {
-                    const float4 gv = g4[8 + j];
-                    drain1(r[4 * j + 0], as, gv.x, sum[32 + 4 * j + 0]);
-                    drain1(r[4 * j + 1], as, gv.y, sum[32 + 4 * j + 1]);
-                    drain1(r[4 * j + 2], as, gv.z, sum[32 + 4 * j + 2]);
-                    drain1(r[4 * j + 3], as, gv.w, sum[32 + 4 * j + 3]);
+                    for (int j = 0; j < 8; j++) {
+                        const float4 gv = g4[8 * ch + j];
+                        drain1(r[4 * j + 0], as, gv.x, sum[32 * ch + 4 * j + 0]);
+                        drain1(r[4 * j + 1], as, gv.y, sum[32 * ch + 4 * j + 1]);
+                        drain1(r[4 * j + 2], as, gv.z, sum[32 * ch + 4 * j + 2]);
+                        drain1(r[4 * j + 3], as, gv.w, sum[32 * ch + 4 * j + 3]);
+                    }
                 }
             }
             if (!ok) break;
