@@ -288,6 +288,33 @@ def test_grouped_scales_vs_oracle(torch, ctx, oracle, group, rows, k, n):
 
 
 @pytest.mark.parametrize("group", [32, 64, 128, 256])
+@pytest.mark.parametrize("rows,k,n", [(1, 300, 50), (1, 4096, 1030), (2, 1283, 130), (3, 576, 192), (4, 2048 + 128, 385),
+                                      (4, 30000, 40), (1, 100000, 24)])
+def test_grouped_scales_decode_gemv(torch, ctx, oracle, group, rows, k, n):
+    """One to four rows against grouped scales (the reference's own decode mode): the warp-per-channel
+    kernel, bit-equal to the oracle's grouped forward; K not a multiple of the 512-byte step, K beyond
+    one shared-memory chunk, ragged channel counts, a NaN row."""
+    from volvoxai_b200 import _lib, w8a8
+    rng = np.random.default_rng(group * 5 + rows + k + n)
+    w = rng.integers(-127, 128, size=(n, k), dtype=np.int8)
+    words = wl.pack_w8_words(w)
+    groups = (k + group - 1) // group
+    gs = rng.uniform(0.001, 0.05, size=(n, groups)).astype(np.float32)
+    bias = rng.standard_normal(n).astype(np.float32)
+    x = (rng.standard_normal((rows, k)) * 2).astype(np.float32)
+    if rows > 2:
+        x[1, k // 3] = np.nan
+    wg = w8a8.Weight.from_w8_words(ctx, words, gs, k, group, bias_f32=bias)
+    y = ctx.linear_f32(wg, dev(torch, x)).cpu().numpy()
+    assert "gemv-grouped" in _lib.last_route()
+    want = oracle.packed_linear_w8_grouped(x, words, gs, group, bias)
+    assert np.array_equal(np.isnan(y), np.isnan(want))
+    ok = ~np.isnan(want)
+    assert np.array_equal(y[ok].view(np.uint32), want[ok].view(np.uint32))
+    wg.close()
+
+
+@pytest.mark.parametrize("group", [32, 64, 128, 256])
 @pytest.mark.parametrize("rows,k,n", [(16, 300, 50), (130, 1283, 130), (300, 4096, 520), (1000, 576, 1000),
                                       (257, 2048 + 128, 385)])
 def test_grouped_scales_tensor_core_kernel(torch, ctx, oracle, group, rows, k, n):

@@ -258,7 +258,15 @@ int run_gemm(VxbContext* ctx, const VxbWeight* w, const int8_t* q, uint32_t rows
         if (epi.residual || epi.act) return fail(0, "weights with grouped scales have no fused epilogue");
         // tensor cores with one accumulator drain per group (also for a single row: 34 us against
         // 42 us at K 4096, N 14336); the explicit CUDA-core route keeps one thread per channel
-        if (requested_auto && w->has_tmap && w->gscales_t) {
+        if (requested_auto && (rows <= 2 || (rows <= 4 && (uint64_t)w->kpad * w->d_out <= (32ull << 20)))) {
+            // decode: a warp per channel streams the weights once (the reference's own decode mode is
+            // one row against grouped scales): 14 us at K 4096, N 14336 for one row; from three rows
+            // on the tensor-core kernel is faster at large weights
+            EpilogueParams ge = epi;
+            ge.gscales = w->gscales; ge.group = w->group; ge.groups = w->groups;
+            CUDA_TRY(launch_gemv_grouped(q, rows, w->w, w->d_out, w->kpad, ge, ctx->sm_count, ctx->stream), -1);
+            plan.name = "gemv-grouped";
+        } else if (requested_auto && w->has_tmap && w->gscales_t) {
             if (!ctx->grouped_ready) {
                 CUDA_TRY(gemm_grouped_tcgen05_prepare(), 0);
                 ctx->grouped_ready = true;

@@ -236,6 +236,9 @@ cudaError_t launch_requantize_linear(const void* x, unsigned long long n, float 
 
 // Grouped weight scales (the reference's PackedLinear storage groups): one thread per output,
 // an exact integer dot per group, fp32 accumulation in ascending group order. fp32 output only.
+// Grouped scales, rows <= 4 (decode): warp-per-channel streaming kernel, fp32 output.
+cudaError_t launch_gemv_grouped(const int8_t* q, uint32_t rows, const int8_t* w, uint32_t n, uint32_t kpad,
+                                const EpilogueParams& epi, int sm_count, cudaStream_t stream);
 cudaError_t launch_gemm_grouped(const int8_t* q, uint32_t rows, const int8_t* w, uint32_t n, uint32_t kpad,
                                 const EpilogueParams& epi, cudaStream_t stream);
 

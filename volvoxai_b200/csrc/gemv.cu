@@ -195,6 +195,137 @@ gemm_grouped_kernel(const int8_t* __restrict__ q, uint32_t rows, const int8_t* _
         if (row0 + m < rows) ((float*)epi.out)[(size_t)(row0 + m) * epi.ld + col] = __fadd_rn(sum[m], bias);
 }
 
+
+// ---- grouped weight scales, few rows (decode) -------------------------------------------------
+// The reference's own decode mode: one row against PackedLinear storage with a scale per
+// G-element group.  Same streaming as gemv_dp4a_kernel (every warp reads CH weight rows with
+// 128-bit loads, each lane 16 bytes of every 512-byte step, activations staged in shared memory),
+// but the integer partials are reduced only within the G/16 lanes that share a group, and after
+// every step the 512/G group dots go through the reference's arithmetic in ascending order:
+//   sum = sum + f32(dot_g) * f32(as * ws[n,g])        (every operation rounded on its own)
+// All lanes carry the same chain, so no lane diverges; int -> fp32 by the exact 1.5 * 2^23 trick.
+template <int MR, int CH, int G>
+__global__ void __launch_bounds__(kGemvThreads)
+gemv_grouped_kernel(const int8_t* __restrict__ q, uint32_t rows, const int8_t* __restrict__ w,
+                    uint32_t n, uint32_t kpad, uint32_t kchunk, EpilogueParams epi) {
+    extern __shared__ __align__(16) uint8_t smem[];  // [MR][kchunk] activations
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr uint32_t kChannelsPerCta = kGemvWarps * CH;
+    constexpr int kLanesPerGroup = G / 16, kGroupsPerStep = 512 / G;
+    const uint32_t blocks = (n + kChannelsPerCta - 1) / kChannelsPerCta;
+    const bool single_chunk = kchunk >= kpad;
+    float as[MR];
+#pragma unroll
+    for (int m = 0; m < MR; m++) as[m] = (uint32_t)m < rows ? __ldg(epi.row_scales + m) : 0.0f;
+
+    for (uint32_t blk = blockIdx.x; blk < blocks; blk += gridDim.x) {
+        const uint32_t c0 = blk * kChannelsPerCta + warp * CH;
+        float sum[MR][CH];
+#pragma unroll
+        for (int m = 0; m < MR; m++)
+#pragma unroll
+            for (int c = 0; c < CH; c++) sum[m][c] = 0.0f;
+
+        for (uint32_t kb = 0; kb < kpad; kb += kchunk) {
+            const uint32_t klen = kpad - kb < kchunk ? kpad - kb : kchunk;
+            if (!(single_chunk && blk != blockIdx.x)) {
+                __syncthreads();
+                const uint32_t vec_per_row = klen / 16;
+                for (uint32_t i = threadIdx.x; i < MR * vec_per_row; i += kGemvThreads) {
+                    const uint32_t m = i / vec_per_row, v = i % vec_per_row;
+                    uint4 val = make_uint4(0, 0, 0, 0);
+                    if (m < rows) val = *reinterpret_cast<const uint4*>(q + (size_t)m * kpad + kb + v * 16);
+                    *reinterpret_cast<uint4*>(smem + (size_t)m * kchunk + v * 16) = val;
+                }
+                __syncthreads();
+            }
+            for (uint32_t ks = 0; ks < klen; ks += 512) {
+                const uint32_t k0 = ks + lane * 16;
+                const bool in = k0 < klen;
+                int part[MR][CH];
+                uint4 wv[CH];
+#pragma unroll
+                for (int c = 0; c < CH; c++) {
+                    const uint32_t ch = c0 + c;
+                    wv[c] = (in && ch < n) ? __ldcs(reinterpret_cast<const uint4*>(w + (size_t)ch * kpad + kb + k0))
+                                           : make_uint4(0, 0, 0, 0);
+                }
+#pragma unroll
+                for (int m = 0; m < MR; m++) {
+                    const uint4 a = in ? *reinterpret_cast<const uint4*>(smem + (size_t)m * kchunk + k0) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+                    for (int c = 0; c < CH; c++) {
+                        int s = dp4a_s8(a.x, wv[c].x, 0);
+                        s = dp4a_s8(a.y, wv[c].y, s);
+                        s = dp4a_s8(a.z, wv[c].z, s);
+                        s = dp4a_s8(a.w, wv[c].w, s);
+#pragma unroll
+                        for (int off = kLanesPerGroup / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+                        part[m][c] = s;
+                    }
+                }
+                const uint32_t g0 = (kb + ks) / G;
+#pragma unroll
+                for (int j = 0; j < kGroupsPerStep; j++) {
+                    if (g0 + j >= epi.groups) break;                       // uniform over the warp
+#pragma unroll
+                    for (int c = 0; c < CH; c++) {
+                        const uint32_t ch = c0 + c < n ? c0 + c : n - 1;
+                        const float gs = __ldg(epi.gscales + (size_t)ch * epi.groups + g0 + j);
+#pragma unroll
+                        for (int m = 0; m < MR; m++) {
+                            const int d = __shfl_sync(0xffffffffu, part[m][c], j * kLanesPerGroup);
+                            const float f = __fadd_rn(__int_as_float(d + 0x4B400000), -12582912.0f);
+                            sum[m][c] = __fadd_rn(sum[m][c], __fmul_rn(f, __fmul_rn(as[m], gs)));
+                        }
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int m = 0; m < MR; m++)
+#pragma unroll
+            for (int c = 0; c < CH; c++) {
+                if (lane == ((m * CH + c) & 31) && (uint32_t)m < rows && c0 + c < n) {
+                    const float bias = epi.bias_f32 ? __ldg(epi.bias_f32 + c0 + c) : 0.0f;
+                    ((float*)epi.out)[(size_t)m * epi.ld + c0 + c] = __fadd_rn(sum[m][c], bias);
+                }
+            }
+    }
+}
+
+template <int MR, int CH, int G>
+cudaError_t launch_gemv_grouped_t(const int8_t* q, uint32_t rows, const int8_t* w, uint32_t n, uint32_t kpad,
+                                  const EpilogueParams& epi, int sm_count, cudaStream_t stream) {
+    uint32_t kchunk = (kpad + 511u) / 512u * 512u;
+    if ((uint64_t)MR * kchunk > kGemvSmemBytes) kchunk = (kGemvSmemBytes / MR) / 512 * 512;
+    const uint32_t smem = MR * kchunk;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemv_grouped_kernel<MR, CH, G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)kGemvSmemBytes);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    constexpr uint32_t kChannelsPerCta = kGemvWarps * CH;
+    const uint32_t blocks = (n + kChannelsPerCta - 1) / kChannelsPerCta;
+    uint32_t per_sm = (200u * 1024u) / (smem + 1024u);
+    if (per_sm > 8) per_sm = 8;
+    if (per_sm < 1) per_sm = 1;
+    uint32_t grid = (uint32_t)sm_count * per_sm;
+    if (grid > blocks) grid = blocks;
+    gemv_grouped_kernel<MR, CH, G><<<grid, kGemvThreads, smem, stream>>>(q, rows, w, n, kpad, kchunk, epi);
+    return cudaGetLastError();
+}
+
+template <int G>
+cudaError_t launch_gemv_grouped_g(const int8_t* q, uint32_t rows, const int8_t* w, uint32_t n, uint32_t kpad,
+                                  const EpilogueParams& epi, int sm_count, cudaStream_t stream) {
+    if (rows <= 1) return launch_gemv_grouped_t<1, 4, G>(q, rows, w, n, kpad, epi, sm_count, stream);
+    if (rows <= 2) return launch_gemv_grouped_t<2, 4, G>(q, rows, w, n, kpad, epi, sm_count, stream);
+    return launch_gemv_grouped_t<4, 2, G>(q, rows, w, n, kpad, epi, sm_count, stream);
+}
+
 }  // namespace
 
 cudaError_t launch_gemm_grouped(const int8_t* q, uint32_t rows, const int8_t* w, uint32_t n, uint32_t kpad,
@@ -212,6 +343,19 @@ cudaError_t launch_gemm_grouped(const int8_t* q, uint32_t rows, const int8_t* w,
         else gemm_grouped_kernel<kMR><<<grid, 128, 0, stream>>>(q + (size_t)r0 * kpad, cnt, w, n, kpad, e);
     }
     return cudaGetLastError();
+}
+
+cudaError_t launch_gemv_grouped(const int8_t* q, uint32_t rows, const int8_t* w, uint32_t n, uint32_t kpad,
+                                const EpilogueParams& epi, int sm_count, cudaStream_t stream) {
+    if (rows == 0 || n == 0) return cudaSuccess;
+    if (rows > 4 || epi.mode != kEpiF32 || !epi.gscales || !epi.groups) return cudaErrorInvalidValue;
+    switch (epi.group) {
+        case 32: return launch_gemv_grouped_g<32>(q, rows, w, n, kpad, epi, sm_count, stream);
+        case 64: return launch_gemv_grouped_g<64>(q, rows, w, n, kpad, epi, sm_count, stream);
+        case 128: return launch_gemv_grouped_g<128>(q, rows, w, n, kpad, epi, sm_count, stream);
+        case 256: return launch_gemv_grouped_g<256>(q, rows, w, n, kpad, epi, sm_count, stream);
+        default: return cudaErrorInvalidValue;
+    }
 }
 
 cudaError_t launch_gemv(const int8_t* q, uint32_t rows, const int8_t* w, uint32_t n, uint32_t kpad,
