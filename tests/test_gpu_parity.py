@@ -358,6 +358,31 @@ def test_w4_words_golden(torch, ctx, golden, tag, group, k):
     wg.close()
 
 
+@pytest.mark.parametrize("group", [32, 64, 128, 256])
+@pytest.mark.parametrize("rows,k,n", [(1, 300, 50), (1, 4096, 1030), (2, 1283, 130), (2, 8192 + 64, 77), (1, 120000, 24)])
+def test_w4_decode_gemv(torch, ctx, oracle, group, rows, k, n):
+    """One and two rows against W4 storage: the decode kernel reads the 4-bit words themselves
+    (nibble unpack in registers), bit-equal to the oracle's W4 forward; a third row takes the
+    int8 copy and must agree as well."""
+    from volvoxai_b200 import _lib, w8a8
+    rng = np.random.default_rng(group * 7 + rows + k + n)
+    w = rng.integers(-8, 8, size=(n, k), dtype=np.int8)
+    words = wl.pack_w4_words(w)
+    groups = (k + group - 1) // group
+    gs = rng.uniform(0.01, 0.3, size=(n, groups)).astype(np.float32)
+    bias = rng.standard_normal(n).astype(np.float32)
+    x = (rng.standard_normal((3, k)) * 2).astype(np.float32)
+    wg = w8a8.Weight.from_w4_words(ctx, words, gs, k, group, bias_f32=bias)
+    y = ctx.linear_f32(wg, dev(torch, x[:rows])).cpu().numpy()
+    assert "gemv-w4-grouped" in _lib.last_route()
+    want = oracle.packed_linear_w4_grouped(x, words, gs, group, bias)
+    assert np.array_equal(y.view(np.uint32), want[:rows].view(np.uint32))
+    y3 = ctx.linear_f32(wg, dev(torch, x)).cpu().numpy()
+    assert "gemv-w4-grouped" not in _lib.last_route()
+    assert np.array_equal(y3.view(np.uint32), want.view(np.uint32))
+    wg.close()
+
+
 @pytest.mark.parametrize("group", [32, 128])
 @pytest.mark.parametrize("rows,k,n", [(1, 300, 50), (70, 1283, 130), (9, 4096, 520), (300, 1024, 384)])
 def test_w4_words_vs_oracle(torch, ctx, oracle, group, rows, k, n):

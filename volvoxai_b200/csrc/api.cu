@@ -133,6 +133,8 @@ struct VxbWeight {
     float* gscales = nullptr;  // [d_out, groups]
     float* gscales_t = nullptr;  // [groups, n_pad], n_pad = round_up(d_out, 128), padding zero (tensor-core grouped kernel)
     uint32_t n_pad = 0;
+    uint32_t* w4 = nullptr;      // W4 storage kept as words [d_out, w4_row_words] for the one/two-row decode kernel
+    uint32_t w4_row_words = 0;   // multiple of 4, * 8 >= kpad; codes past d_in are 8 (weight 0)
 };
 
 namespace {
@@ -258,7 +260,13 @@ int run_gemm(VxbContext* ctx, const VxbWeight* w, const int8_t* q, uint32_t rows
         if (epi.residual || epi.act) return fail(0, "weights with grouped scales have no fused epilogue");
         // tensor cores with one accumulator drain per group (also for a single row: 34 us against
         // 42 us at K 4096, N 14336); the explicit CUDA-core route keeps one thread per channel
-        if (requested_auto && (rows <= 2 || (rows <= 4 && (uint64_t)w->kpad * w->d_out <= (32ull << 20)))) {
+        if (requested_auto && rows <= 2 && w->w4) {
+            // W4 storage: the same decode kernel over the 4-bit words (half the bytes)
+            EpilogueParams ge = epi;
+            ge.gscales = w->gscales; ge.group = w->group; ge.groups = w->groups;
+            CUDA_TRY(launch_gemv_w4_grouped(q, rows, w->w4, w->w4_row_words, w->d_out, w->kpad, ge, ctx->sm_count, ctx->stream), -1);
+            plan.name = "gemv-w4-grouped";
+        } else if (requested_auto && (rows <= 2 || (rows <= 4 && (uint64_t)w->kpad * w->d_out <= (32ull << 20)))) {
             // decode: a warp per channel streams the weights once (the reference's own decode mode is
             // one row against grouped scales): 14 us at K 4096, N 14336 for one row; from three rows
             // on the tensor-core kernel is faster at large weights
@@ -565,6 +573,17 @@ int vxb_weight_create_w4_words(VxbContext* ctx, const int32_t* words, const floa
         rc = fail(-1, "weight upload failed");
     else rc = finish_weight(ctx, w, (const uint8_t*)staging.ptr, d_in, 0u, ws.data(), bias_f32, nullptr);
     if (rc == 1 && grouped) rc = upload_group_scales(ctx, w, group_scales, d_out, groups, group_size);
+    if (rc == 1 && grouped) {
+        // the words themselves, rows padded with the encoded zero to the padded K of the int8 copy
+        const uint32_t padded_words = w->kpad / 8u;
+        std::vector<uint32_t> padded((size_t)d_out * padded_words, 0x88888888u);
+        for (uint32_t n = 0; n < d_out; n++)
+            memcpy(&padded[(size_t)n * padded_words], (const uint32_t*)words + (size_t)n * row_words, (size_t)row_words * 4);
+        if (cudaMalloc(&w->w4, padded.size() * 4) != cudaSuccess) rc = fail(0, "W4 word allocation failed");
+        else if (cudaMemcpyAsync(w->w4, padded.data(), padded.size() * 4, cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess ||
+                 cudaStreamSynchronize(ctx->stream) != cudaSuccess) rc = fail(-1, "W4 word upload failed");
+        else { w->w4_row_words = padded_words; w->bytes += padded.size() * 4; }
+    }
     cudaStreamSynchronize(ctx->stream);
     staging.release();
     if (rc != 1) { vxb_weight_destroy(w); return rc; }
@@ -582,6 +601,7 @@ void vxb_weight_destroy(VxbWeight* w) {
     if (w->wsum) cudaFree(w->wsum);
     if (w->gscales) cudaFree(w->gscales);
     if (w->gscales_t) cudaFree(w->gscales_t);
+    if (w->w4) cudaFree(w->w4);
     delete w;
 }
 uint32_t vxb_weight_d_in(const VxbWeight* w) { return w ? w->d_in : 0; }

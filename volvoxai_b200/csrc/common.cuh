@@ -239,6 +239,10 @@ cudaError_t launch_requantize_linear(const void* x, unsigned long long n, float 
 // Grouped scales, rows <= 4 (decode): warp-per-channel streaming kernel, fp32 output.
 cudaError_t launch_gemv_grouped(const int8_t* q, uint32_t rows, const int8_t* w, uint32_t n, uint32_t kpad,
                                 const EpilogueParams& epi, int sm_count, cudaStream_t stream);
+// The same over the 4-bit words themselves (rows <= 2): w4 is [n][row_words] uint32, row_words a
+// multiple of 4 with row_words * 8 >= kpad, codes past the logical width 8 (= weight 0).
+cudaError_t launch_gemv_w4_grouped(const int8_t* q, uint32_t rows, const uint32_t* w4, uint32_t row_words, uint32_t n,
+                                   uint32_t kpad, const EpilogueParams& epi, int sm_count, cudaStream_t stream);
 cudaError_t launch_gemm_grouped(const int8_t* q, uint32_t rows, const int8_t* w, uint32_t n, uint32_t kpad,
                                 const EpilogueParams& epi, cudaStream_t stream);
 

@@ -326,6 +326,150 @@ cudaError_t launch_gemv_grouped_g(const int8_t* q, uint32_t rows, const int8_t* 
     return launch_gemv_grouped_t<4, 2, G>(q, rows, w, n, kpad, epi, sm_count, stream);
 }
 
+
+// ---- W4 storage, grouped scales, one or two rows ----------------------------------------------
+// The same decode kernel over the 4-bit words themselves (half the weight bytes of the int8
+// copy): eight codes per word, earlier K in lower bits, w = code - 8 (the reference's
+// vx_packed_cuda_unpack_w4_low/high, cuda_forward_llm_kernels.inc:152-165).  A word's low nibbles
+// are codes 0,2,4,6 and its high nibbles codes 1,3,5,7, so the activations are staged in shared
+// memory de-interleaved per 8 (even four, odd four) and a word costs two masks, a shift and two
+// dp4a; sum a * (c - 8) = sum a * c - 8 * sum a, with sum a taken once per row and step.
+// Each lane owns 16 bytes = 32 codes of every 1024-code step; G / 32 lanes share a group.
+template <int MR, int CH, int G>
+__global__ void __launch_bounds__(kGemvThreads)
+gemv_w4_grouped_kernel(const int8_t* __restrict__ q, uint32_t rows, const uint32_t* __restrict__ w4,
+                       uint32_t row_words, uint32_t n, uint32_t kpad, uint32_t kchunk, EpilogueParams epi) {
+    extern __shared__ __align__(16) uint8_t smem[];  // [MR][kchunk] de-interleaved activations
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr uint32_t kChannelsPerCta = kGemvWarps * CH;
+    constexpr int kLanesPerGroup = G / 32, kGroupsPerStep = 1024 / G;
+    const uint32_t blocks = (n + kChannelsPerCta - 1) / kChannelsPerCta;
+    const bool single_chunk = kchunk >= kpad;
+    float as[MR];
+#pragma unroll
+    for (int m = 0; m < MR; m++) as[m] = (uint32_t)m < rows ? __ldg(epi.row_scales + m) : 0.0f;
+
+    for (uint32_t blk = blockIdx.x; blk < blocks; blk += gridDim.x) {
+        const uint32_t c0 = blk * kChannelsPerCta + warp * CH;
+        float sum[MR][CH];
+#pragma unroll
+        for (int m = 0; m < MR; m++)
+#pragma unroll
+            for (int c = 0; c < CH; c++) sum[m][c] = 0.0f;
+
+        for (uint32_t kb = 0; kb < kpad; kb += kchunk) {
+            const uint32_t klen = kpad - kb < kchunk ? kpad - kb : kchunk;
+            if (!(single_chunk && blk != blockIdx.x)) {
+                __syncthreads();
+                const uint32_t vec_per_row = klen / 16;
+                for (uint32_t i = threadIdx.x; i < MR * vec_per_row; i += kGemvThreads) {
+                    const uint32_t m = i / vec_per_row, v = i % vec_per_row;
+                    uint4 val = make_uint4(0, 0, 0, 0);
+                    if (m < rows) val = *reinterpret_cast<const uint4*>(q + (size_t)m * kpad + kb + v * 16);
+                    const uint4 perm = make_uint4(__byte_perm(val.x, val.y, 0x6420), __byte_perm(val.x, val.y, 0x7531),
+                                                  __byte_perm(val.z, val.w, 0x6420), __byte_perm(val.z, val.w, 0x7531));
+                    *reinterpret_cast<uint4*>(smem + (size_t)m * kchunk + v * 16) = perm;
+                }
+                __syncthreads();
+            }
+            for (uint32_t ks = 0; ks < klen; ks += 1024) {
+                const uint32_t k0 = ks + lane * 32;                  // this lane's first code of the step
+                const bool in = k0 < klen;
+                uint4 wv[CH];
+#pragma unroll
+                for (int c = 0; c < CH; c++) {
+                    const uint32_t ch = c0 + c;
+                    wv[c] = (in && ch < n) ? __ldcs(reinterpret_cast<const uint4*>(w4 + (size_t)ch * row_words + (kb + k0) / 8))
+                                           : make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
+                }
+                int part[MR][CH];
+#pragma unroll
+                for (int m = 0; m < MR; m++) {
+                    uint4 a0 = make_uint4(0, 0, 0, 0), a1 = a0;
+                    if (in) {
+                        a0 = *reinterpret_cast<const uint4*>(smem + (size_t)m * kchunk + k0);
+                        a1 = *reinterpret_cast<const uint4*>(smem + (size_t)m * kchunk + k0 + 16);
+                    }
+                    const uint32_t av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};   // (even, odd) per word
+                    int asum = 0;
+#pragma unroll
+                    for (int i = 0; i < 8; i++) asum = dp4a_s8(av[i], 0x01010101u, asum);
+#pragma unroll
+                    for (int c = 0; c < CH; c++) {
+                        const uint32_t wd[4] = {wv[c].x, wv[c].y, wv[c].z, wv[c].w};
+                        int s = 0;
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            s = dp4a_s8(av[2 * i], wd[i] & 0x0F0F0F0Fu, s);
+                            s = dp4a_s8(av[2 * i + 1], (wd[i] >> 4) & 0x0F0F0F0Fu, s);
+                        }
+                        s -= 8 * asum;
+#pragma unroll
+                        for (int off = kLanesPerGroup / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+                        part[m][c] = s;
+                    }
+                }
+                const uint32_t g0 = (kb + ks) / G;
+#pragma unroll
+                for (int j = 0; j < kGroupsPerStep; j++) {
+                    if (g0 + j >= epi.groups) break;                       // uniform over the warp
+#pragma unroll
+                    for (int c = 0; c < CH; c++) {
+                        const uint32_t ch = c0 + c < n ? c0 + c : n - 1;
+                        const float gs = __ldg(epi.gscales + (size_t)ch * epi.groups + g0 + j);
+#pragma unroll
+                        for (int m = 0; m < MR; m++) {
+                            const int d = __shfl_sync(0xffffffffu, part[m][c], j * kLanesPerGroup);
+                            const float f = __fadd_rn(__int_as_float(d + 0x4B400000), -12582912.0f);
+                            sum[m][c] = __fadd_rn(sum[m][c], __fmul_rn(f, __fmul_rn(as[m], gs)));
+                        }
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int m = 0; m < MR; m++)
+#pragma unroll
+            for (int c = 0; c < CH; c++) {
+                if (lane == ((m * CH + c) & 31) && (uint32_t)m < rows && c0 + c < n) {
+                    const float bias = epi.bias_f32 ? __ldg(epi.bias_f32 + c0 + c) : 0.0f;
+                    ((float*)epi.out)[(size_t)m * epi.ld + c0 + c] = __fadd_rn(sum[m][c], bias);
+                }
+            }
+    }
+}
+
+template <int MR, int CH, int G>
+cudaError_t launch_gemv_w4_t(const int8_t* q, uint32_t rows, const uint32_t* w4, uint32_t row_words, uint32_t n,
+                             uint32_t kpad, const EpilogueParams& epi, int sm_count, cudaStream_t stream) {
+    uint32_t kchunk = (kpad + 1023u) / 1024u * 1024u;
+    if ((uint64_t)MR * kchunk > kGemvSmemBytes) kchunk = (kGemvSmemBytes / MR) / 1024 * 1024;
+    const uint32_t smem = MR * kchunk;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemv_w4_grouped_kernel<MR, CH, G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)kGemvSmemBytes);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    constexpr uint32_t kChannelsPerCta = kGemvWarps * CH;
+    const uint32_t blocks = (n + kChannelsPerCta - 1) / kChannelsPerCta;
+    uint32_t per_sm = (200u * 1024u) / (smem + 1024u);
+    if (per_sm > 8) per_sm = 8;
+    if (per_sm < 1) per_sm = 1;
+    uint32_t grid = (uint32_t)sm_count * per_sm;
+    if (grid > blocks) grid = blocks;
+    gemv_w4_grouped_kernel<MR, CH, G><<<grid, kGemvThreads, smem, stream>>>(q, rows, w4, row_words, n, kpad, kchunk, epi);
+    return cudaGetLastError();
+}
+
+template <int G>
+cudaError_t launch_gemv_w4_g(const int8_t* q, uint32_t rows, const uint32_t* w4, uint32_t row_words, uint32_t n,
+                             uint32_t kpad, const EpilogueParams& epi, int sm_count, cudaStream_t stream) {
+    if (rows <= 1) return launch_gemv_w4_t<1, 4, G>(q, rows, w4, row_words, n, kpad, epi, sm_count, stream);
+    return launch_gemv_w4_t<2, 4, G>(q, rows, w4, row_words, n, kpad, epi, sm_count, stream);
+}
+
 }  // namespace
 
 cudaError_t launch_gemm_grouped(const int8_t* q, uint32_t rows, const int8_t* w, uint32_t n, uint32_t kpad,
@@ -354,6 +498,20 @@ cudaError_t launch_gemv_grouped(const int8_t* q, uint32_t rows, const int8_t* w,
         case 64: return launch_gemv_grouped_g<64>(q, rows, w, n, kpad, epi, sm_count, stream);
         case 128: return launch_gemv_grouped_g<128>(q, rows, w, n, kpad, epi, sm_count, stream);
         case 256: return launch_gemv_grouped_g<256>(q, rows, w, n, kpad, epi, sm_count, stream);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+cudaError_t launch_gemv_w4_grouped(const int8_t* q, uint32_t rows, const uint32_t* w4, uint32_t row_words, uint32_t n,
+                                   uint32_t kpad, const EpilogueParams& epi, int sm_count, cudaStream_t stream) {
+    if (rows == 0 || n == 0) return cudaSuccess;
+    if (rows > 2 || epi.mode != kEpiF32 || !epi.gscales || !epi.groups || row_words % 4 != 0 || row_words * 8 < kpad)
+        return cudaErrorInvalidValue;
+    switch (epi.group) {
+        case 32: return launch_gemv_w4_g<32>(q, rows, w4, row_words, n, kpad, epi, sm_count, stream);
+        case 64: return launch_gemv_w4_g<64>(q, rows, w4, row_words, n, kpad, epi, sm_count, stream);
+        case 128: return launch_gemv_w4_g<128>(q, rows, w4, row_words, n, kpad, epi, sm_count, stream);
+        case 256: return launch_gemv_w4_g<256>(q, rows, w4, row_words, n, kpad, epi, sm_count, stream);
         default: return cudaErrorInvalidValue;
     }
 }
