@@ -239,16 +239,25 @@ gemv_grouped_kernel(const int8_t* __restrict__ q, uint32_t rows, const int8_t* _
                 }
                 __syncthreads();
             }
+            // the next step's weights are requested before this step's arithmetic: a warp's K loop is
+            // otherwise a chain of load -> use round trips of a microsecond each
+            uint4 wv[CH];
+#pragma unroll
+            for (int c = 0; c < CH; c++) {
+                const uint32_t ch = c0 + c;
+                wv[c] = (lane * 16u < klen && ch < n) ? __ldcs(reinterpret_cast<const uint4*>(w + (size_t)ch * kpad + kb + lane * 16))
+                                                      : make_uint4(0, 0, 0, 0);
+            }
             for (uint32_t ks = 0; ks < klen; ks += 512) {
                 const uint32_t k0 = ks + lane * 16;
                 const bool in = k0 < klen;
                 int part[MR][CH];
-                uint4 wv[CH];
+                uint4 wn[CH];
 #pragma unroll
                 for (int c = 0; c < CH; c++) {
                     const uint32_t ch = c0 + c;
-                    wv[c] = (in && ch < n) ? __ldcs(reinterpret_cast<const uint4*>(w + (size_t)ch * kpad + kb + k0))
-                                           : make_uint4(0, 0, 0, 0);
+                    wn[c] = (k0 + 512u < klen && ch < n) ? __ldcs(reinterpret_cast<const uint4*>(w + (size_t)ch * kpad + kb + k0 + 512u))
+                                                         : make_uint4(0, 0, 0, 0);
                 }
 #pragma unroll
                 for (int m = 0; m < MR; m++) {
@@ -280,6 +289,8 @@ gemv_grouped_kernel(const int8_t* __restrict__ q, uint32_t rows, const int8_t* _
                         }
                     }
                 }
+#pragma unroll
+                for (int c = 0; c < CH; c++) wv[c] = wn[c];
             }
         }
 #pragma unroll
@@ -372,15 +383,23 @@ gemv_w4_grouped_kernel(const int8_t* __restrict__ q, uint32_t rows, const uint32
                 }
                 __syncthreads();
             }
+            const uint4 kZero4 = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
+            uint4 wv[CH];
+#pragma unroll
+            for (int c = 0; c < CH; c++) {
+                const uint32_t ch = c0 + c;
+                wv[c] = (lane * 32u < klen && ch < n) ? __ldcs(reinterpret_cast<const uint4*>(w4 + (size_t)ch * row_words + (kb + lane * 32u) / 8))
+                                                      : kZero4;
+            }
             for (uint32_t ks = 0; ks < klen; ks += 1024) {
                 const uint32_t k0 = ks + lane * 32;                  // this lane's first code of the step
                 const bool in = k0 < klen;
-                uint4 wv[CH];
+                uint4 wn[CH];
 #pragma unroll
                 for (int c = 0; c < CH; c++) {
                     const uint32_t ch = c0 + c;
-                    wv[c] = (in && ch < n) ? __ldcs(reinterpret_cast<const uint4*>(w4 + (size_t)ch * row_words + (kb + k0) / 8))
-                                           : make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
+                    wn[c] = (k0 + 1024u < klen && ch < n) ? __ldcs(reinterpret_cast<const uint4*>(w4 + (size_t)ch * row_words + (kb + k0 + 1024u) / 8))
+                                                          : kZero4;
                 }
                 int part[MR][CH];
 #pragma unroll
@@ -425,6 +444,8 @@ gemv_w4_grouped_kernel(const int8_t* __restrict__ q, uint32_t rows, const uint32
                         }
                     }
                 }
+#pragma unroll
+                for (int c = 0; c < CH; c++) wv[c] = wn[c];
             }
         }
 #pragma unroll
