@@ -34,7 +34,7 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-from volvoxai_b200 import workloads as wl  # noqa: E402
+from tests import workloads as wl  # noqa: E402
 
 NOMINAL_I8_TOPS = 4500.0
 NOMINAL_HBM_GBS = 8000.0
@@ -153,7 +153,7 @@ def cpu_reference_run(rows, k, n, steps, warmup, budget_s=None, seed=0):
             assert ok is not None
         kind, isa = "reference", ref.isa()
         label = (f"vx_packed_prepare_i8 + vx_qlinear_i8u8_packed (isa {isa}) on rows 0..{rows - 1} "
-                 f"of the workload, K={k}, N={n}")
+                 f"of the workload (the row sample; times scale with the row count), K={k}, N={n}")
     else:
         orc = Oracle()
         threads = 1
@@ -231,9 +231,12 @@ def reference_arm(args):
     line = {
         "impl": "reference", "metric": "w8a8_linear_int8_tops", "value": r["tops"], "unit": "TOPS",
         "n_gpus": args.gpus, "steps": r["steps"], "warmup": args.warmup,
-        "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "strong",
+        # each timed step is the first `rows` rows of the workload (a bounded CPU sample): ms_per_step is
+        # that time scaled to the configuration's row count, so that value = 2MKN / ms_per_step holds
+        "ms_per_step": r["ms_per_step"] * (m / rows), "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "int8", "data": "synthetic",
         "config": workload_config(args, 1),
+        "sampled_rows": rows, "sample_ms_per_step": r["ms_per_step"],
         "cpu_baseline": {"value": r["tops"], "unit": "TOPS", "cores": r["cores"], "kind": r["kind"],
                          "sample": r["sample"]},
         "e2e": {"value": r["tops"], "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -464,13 +467,13 @@ def gpu_arm(args):
     x_host_np = wl.gemm_activations(m, k, seed=0)
     x_dev = torch.from_numpy(x_host_np).cuda()
 
-    # static output scale: 99.9th percentile |y| / 127 of the ORACLE's fp32 output on a sample
-    # (rows 0..15 x first 256 channels of rank 0's shard), broadcast to all ranks
+    # static output scale: 99.9th percentile |y| / 127 of this library's own fp32 output on a sample
+    # (rows 0..15 of rank 0's shard), broadcast to all ranks
     out_scale_t = torch.zeros(1, dtype=torch.float32, device="cuda")
     if rank == 0:
-        from oracle.bindings import Oracle
-        smp = Oracle().w8a8_linear(x_host_np[:16], w_local[:256], ws_local[:256])
-        out_scale_t[0] = float(wl.static_out_scale(smp["out"]))
+        smp = ctx.linear_f32(weight, x_dev[:16])
+        ctx.synchronize()
+        out_scale_t[0] = float(wl.static_out_scale(smp.cpu().numpy()))
     if world > 1:
         dist.broadcast(out_scale_t, 0)
     out_scale = float(out_scale_t.item())
@@ -540,6 +543,21 @@ def gpu_arm(args):
         nccl_ms = timed(step_nccl, args.steps) / args.steps
         y_rep = fused.forward(x_dev, out_scale)
         same_as_nccl = bool(torch.equal(y_rep, lin.forward(x_dev)))
+        # the gathered output against the CPU oracle (the checker, outside every timed region): rows
+        # 0..15 x the first 256 channels of EVERY rank's shard, as they arrived in rank 0's buffer
+        samples = [None] * world
+        dist.all_gather_object(samples, (lo, w_local[:256], ws_local[:256]))
+        matches_oracle = None
+        if rank == 0:
+            from oracle.bindings import Oracle
+            orc = Oracle()
+            got = y_rep[:16].cpu().numpy()
+            matches_oracle = True
+            for (lo_r, w_r, ws_r) in samples:
+                if len(ws_r) == 0:
+                    continue
+                want = orc.w8a8_linear(x_host_np[:16], w_r, ws_r, requant=True, out_scale=out_scale)["out"]
+                matches_oracle = matches_oracle and bool(np.array_equal(got[:, lo_r:lo_r + len(ws_r)], want))
         # lower bound of any exchange that replicates the int8 output: the bytes each GPU must
         # receive over NVLink at the measured peer-copy rate (770 GB/s per direction)
         recv_bytes = m * (n - n_local)
@@ -547,7 +565,9 @@ def gpu_arm(args):
                     "sharded_no_exchange_ms": nogather_ms,
                     "nvlink_recv_bytes_per_gpu": int(recv_bytes),
                     "nvlink_floor_ms": recv_bytes / 770e9 * 1e3,
-                    "fused_matches_nccl_path": same_as_nccl}
+                    "fused_matches_nccl_path": same_as_nccl, "matches_oracle": matches_oracle}
+        if rank == 0 and not (same_as_nccl and matches_oracle):
+            raise RuntimeError(f"multi-GPU output check failed: nccl path {same_as_nccl}, oracle {matches_oracle}")
 
     # roofline of the dominant kernel (the tcgen05 GEMM of this rank's shard)
     gemm_ms = prof["gemm_ms"] / max(1, prof["gemm_launches"])

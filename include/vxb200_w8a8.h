@@ -279,14 +279,6 @@ VXB_API int vxb_linear_host(VxbContext* ctx, const VxbWeight* w, const float* x_
  * vxb_context_profile(ctx, 1) clears and starts, (ctx, 0) clears and stops;
  * _read waits for the stream and returns summed milliseconds and launch counts. */
 VXB_API int vxb_context_profile(VxbContext* ctx, int enable);
-/* Diagnostic: while device_stamps is not NULL, every launch of the decode kernel (route
- * DECODE) writes 8 %globaltimer values (ns) per CTA into device_stamps[cta*8 + slot]:
- * 0 entry, 1 prologue done, 2 first weight tile landed, 3 last MMA issued, 4 accumulator
- * ready, 5 last output stored, 6 preceding kernel finished (programmatic dependency), 7 exit.
- * The buffer must hold 8 * ceil(d_out / channels-per-CTA) <= 8 * d_out values. The pointer is
- * read at launch (a captured launch keeps the pointer it was captured with). Counterpart of
- * the instrumented replay plan of the reference (docs/cuda.md:537-556). */
-VXB_API int vxb_context_trace(VxbContext* ctx, unsigned long long* device_stamps);
 VXB_API int vxb_context_profile_read(VxbContext* ctx, double* quantize_ms, uint64_t* quantize_launches,
                              double* gemm_ms, uint64_t* gemm_launches);
 
@@ -323,8 +315,14 @@ VXB_API int vxb_measure_i8_tensor_peak(VxbContext* ctx, uint32_t iters, double* 
  * do not depend on earlier calls, but two calls whose GPU work overlaps (different
  * streams, or graphs replayed concurrently) race on it - keep them ordered.
  * The work is enqueued on `stream` (a cudaStream_t); with wait != 0 the call also
- * waits for it and returns -1 if a bounded device wait expired.  error/error_bytes
- * name an optional buffer for a message. */
+ * waits for it and returns -1 if a bounded device wait expired.  A call with
+ * wait == 0 (the form to use under stream capture) only enqueues and so reports
+ * nothing by itself: if one of the kernel's bounded waits expires, the status
+ * word in the array stays raised - later calls do not clear it - and the next
+ * call made with wait != 0 returns -1 for it, whichever call raised it.  After a
+ * sequence of wait == 0 calls or graph replays, make one waited call (or check
+ * the outputs) before trusting the results.  error/error_bytes name an optional
+ * buffer for a message. */
 #define VXB_NOALLOC_MAX_ROWS 32u
 #define VXB_NOALLOC_MAX_CHANNELS 16384u
 VXB_API int vxb_decode_linear_f32_noalloc(const int8_t* q, const float* row_scales, uint32_t rows,
@@ -332,14 +330,6 @@ VXB_API int vxb_decode_linear_f32_noalloc(const int8_t* q, const float* row_scal
                                   const float* bias, uint32_t d_out, uint32_t row_bytes,
                                   float* y, uint32_t ldy, void* stream, int wait,
                                   char* error, size_t error_bytes);
-
-/* Measurement utility (no counterpart in the reference): on one SM, `iters` rounds of
- * `per_commit` kind::i8 MMAs of shape m x n x 32 cycling through `accs` TMEM accumulators,
- * one commit + wait per round; returns SM clocks per MMA.  Used to size the decode kernels
- * (how the tensor pipe's time per instruction depends on m and n, and whether MMAs into
- * one accumulator serialise). */
-VXB_API int vxb_measure_mma_issue(VxbContext* ctx, uint32_t m, uint32_t n, uint32_t accs, uint32_t per_commit,
-                          uint32_t iters, double* cycles_per_mma);
 
 /* ---- reference-facing entries (HOST pointers) ------------------------- */
 /* Drop-in for the VxW8A8Ops.qlinear_i8u8 slot
@@ -376,13 +366,7 @@ typedef struct VxbLLMOpArgs {
     uint64_t first_unit, unit_count;
 } VxbLLMOpArgs;
 
-/* Drop-in for cuda_graph_llm_f32 with kind == PackedLinear
- * (native/src/backends/cuda_engine.h:13-15; native/src/backends/cuda/host/
- * cuda_graph_llm_host.inc:714-783).  Admits weight bits 8 + activation bits 8
- * with per-channel-constant group scales; declines (0) everything else so the
- * reference's own routes keep serving W2/3/4 and A16/F32.  A window must cover
- * whole rows. */
-/* The same three operators with HOST pointers: the slots quantize_typed_f32_i8u8,
+/* The three boundary operators with HOST pointers: the slots quantize_typed_f32_i8u8,
  * dequantize_typed_i8u8_f32 and requantize_linear_i8u8 of VxW8A8Ops
  * (native/src/backends/w8a8_device_ops.h:28-31,111-113), signatures of
  * cuda_graph_quantize_typed_f32_i8u8 / cuda_graph_dequantize_typed_i8u8_f32 /
@@ -397,6 +381,17 @@ VXB_API int vxb_requantize_linear_i8u8(const void* input, uint32_t input_element
                                float output_scale, int32_t output_zero_point, uint32_t input_dtype,
                                uint32_t output_dtype);
 
+/* Drop-in for cuda_graph_llm_f32 with kind == PackedLinear
+ * (native/src/backends/cuda_engine.h:13-15; native/src/backends/cuda/host/
+ * cuda_graph_llm_host.inc:714-783).  Admits weight bits 8 or 4 with activation
+ * bits 8 and group size 32/64/128/256, with group scales that repeat the channel
+ * scale (served as a per-channel weight) or differ within a channel (served by the
+ * grouped-scale kernels, exact per-group arithmetic).  Declines (0) everything
+ * else - weight bits 2/3, activation bits 16/32, ragged windows, an output window
+ * that overlaps a source - before anything is touched, so that the reference's own
+ * routes keep serving those.  A window must cover whole rows.  Weights are keyed
+ * by their host addresses, shape, bit width and group size and repacked on first
+ * use. */
 VXB_API int vxb_cuda_graph_llm_f32(const VxbLLMOpArgs* args);
 
 /* Drop-in for the scalar decode entry cuda_graph_packed_linear_decode_f32

@@ -24,9 +24,15 @@ REF_SO = os.path.join(HERE, "_ref", "libvxref.so")
 DT_U8, DT_I8 = 5, 6
 
 
-def build(ref_root: str = "/root/reference") -> None:
+def reference_root() -> str:
+    """Where the reference checkout lies: $VX_REFERENCE, else a checkout named `reference`
+    beside this repository."""
+    return os.environ.get("VX_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
+def build(ref_root: str | None = None) -> None:
     """Compile liboracle.so and, when the reference checkout exists, _ref."""
-    subprocess.run(["make", "-s", "-C", HERE, f"REF={ref_root}", "all"], check=True)
+    subprocess.run(["make", "-s", "-C", HERE, f"REF={ref_root or reference_root()}", "all"], check=True)
 
 
 def _p(a, t):

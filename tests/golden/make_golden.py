@@ -27,9 +27,10 @@ import numpy as np
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 sys.path.insert(0, ROOT)
 from oracle.bindings import Ref  # noqa: E402
-from volvoxai_b200 import workloads as wl  # noqa: E402
+from tests import workloads as wl  # noqa: E402
 
-REF_ROOT = os.environ.get("VX_REFERENCE", "/root/reference")
+from oracle.bindings import reference_root  # noqa: E402
+REF_ROOT = reference_root()
 
 
 def load_exporter():

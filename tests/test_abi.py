@@ -8,23 +8,30 @@ import re
 import numpy as np
 
 from volvoxai_b200 import _lib, w8a8
-from volvoxai_b200 import workloads as wl
+from tests import workloads as wl
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def declared_symbols():
-    text = open(os.path.join(ROOT, "include", "vxb200_w8a8.h")).read()
-    return sorted(set(re.findall(r"VXB_API[^;(]*?\b(vxb_\w+)\s*\(", text)))
+def declared_symbols(*path):
+    text = open(os.path.join(ROOT, *path)).read()
+    return sorted(set(re.findall(r"VXB_(?:PLAN_)?API[^;(]*?\b(vxb_\w+)\s*\(", text)))
 
 
 def test_library_exports_every_declared_symbol():
+    """The boundary header, the planning header and the diagnostic header: every declared entry is
+    exported by the built library, and the ctypes mirror lists exactly those names."""
     L = _lib.load()
-    names = declared_symbols()
+    names = declared_symbols("include", "vxb200_w8a8.h")
     assert len(names) >= 20
-    for n in names:
+    plan = declared_symbols("include", "vxb200_plan.h")
+    diag = declared_symbols("volvoxai_b200", "csrc", "diag.h")
+    for n in names + plan + diag:
         assert hasattr(L, n), n
     assert sorted(_lib.EXPORTS) == names
+    assert sorted(_lib.PLAN_EXPORTS) == plan
+    assert sorted(_lib.DIAG_EXPORTS) == diag
+    assert not set(diag) & set(names), "diagnostics leaked into the boundary header"
     assert L.vxb_abi_version() == 1
 
 
@@ -43,16 +50,22 @@ def test_packed_linear_admission_declines_on_host():
     words = wl.pack_w8_words(w)
     scales = np.ones((4, 1), np.float32)
     y = np.full((2, 4), 7.0, np.float32)
-    # W4 / A16 / F32 arithmetic stay with the reference's own routes
-    assert w8a8.packed_linear(x, words, scales, None, y, weight_bits=4, group_size=64) == 0
+    # W2 / W3 storage and A16 / F32 arithmetic stay with the reference's own routes (W4 and W8 with
+    # A8 arithmetic are admitted); so does a group size outside 32..256
+    assert w8a8.packed_linear(x, words, scales, None, y, weight_bits=2, group_size=64) == 0
+    assert w8a8.packed_linear(x, words, scales, None, y, weight_bits=3, group_size=64) == 0
+    assert w8a8.packed_linear(x, words, scales, None, y, group_size=48) == 0
     assert w8a8.packed_linear(x, words, scales, None, y, activation_bits=16, group_size=64) == 0
     assert w8a8.packed_linear(x, words, scales, None, y, activation_bits=32, group_size=64) == 0
     # ragged window, window past the end, first_unit without a count
     assert w8a8.packed_linear(x, words, scales, None, y, group_size=64, first_unit=1, unit_count=4) == 0
     assert w8a8.packed_linear(x, words, scales, None, y, group_size=64, first_unit=4, unit_count=8) == 0
     assert w8a8.packed_linear(x, words, scales, None, y, group_size=64, first_unit=4, unit_count=0) == 0
+    # an output window that overlaps a source is declined as the reference's entry declines it
+    both = np.zeros(2 * 64 + 2 * 4, np.float32)
+    assert w8a8.packed_linear(both[:128].reshape(2, 64), words, scales, None, both[124:132].reshape(2, 4), group_size=64) == 0
+    assert "overlap" in w8a8.last_error()
     assert (y == 7.0).all()  # declined before touching the output
-    assert "admitted" in w8a8.last_error() or "window" in w8a8.last_error() or "first_unit" in w8a8.last_error()
 
 
 def test_qlinear_admission_declines_on_host():

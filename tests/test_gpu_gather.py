@@ -10,7 +10,7 @@ import socket
 import numpy as np
 import pytest
 
-from volvoxai_b200 import workloads as wl
+from tests import workloads as wl
 
 pytestmark = pytest.mark.gpu
 

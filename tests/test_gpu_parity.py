@@ -4,7 +4,7 @@ int8 outputs; fp32 outputs within 1e-5 (max-abs error normalised by output RMS).
 import numpy as np
 import pytest
 
-from volvoxai_b200 import workloads as wl
+from tests import workloads as wl
 
 pytestmark = pytest.mark.gpu
 
@@ -555,7 +555,8 @@ def test_host_whole_op_entry_matches_device_entries(torch, ctx, rows):
 
 # ---- size-independent properties at benchmark sizes ---------------------------------------------
 
-@pytest.mark.parametrize("rows,k,n", [(2048, 4096, 14336), (2048, 8192, 28672), (2048, 4096, 128256), (16384, 4096, 14336)])
+@pytest.mark.parametrize("rows", wl.GEMM_ROWS)
+@pytest.mark.parametrize("k,n", wl.GEMM_SHAPES)
 def test_full_size_properties(torch, ctx, oracle, rows, k, n):
     """The compute-bound sweep's shapes (too large for the scalar oracle in seconds): (a) a random
     sample of 512 outputs against exact int64 dots, (b) row permutation invariance - row r of a
@@ -594,8 +595,8 @@ def test_full_size_properties(torch, ctx, oracle, rows, k, n):
     weight.close()
 
 
-@pytest.mark.parametrize("rows", [1, 8, 32])
-@pytest.mark.parametrize("k,n", [(4096, 4096), (4096, 14336), (14336, 4096)])
+@pytest.mark.parametrize("rows", wl.GEMV_ROWS)
+@pytest.mark.parametrize("k,n", wl.GEMV_SHAPES)
 def test_decode_sweep_shapes_exact(torch, ctx, rows, k, n):
     """The memory-bound sweep's shapes through the automatic route: every accumulator against an
     exact int64 matrix product on the device, fp32 outputs against the same product scaled."""

@@ -5,7 +5,7 @@ in this container - a seeded fuzz against the reference's compiled CPU kernels."
 import numpy as np
 import pytest
 
-from volvoxai_b200 import workloads as wl
+from tests import workloads as wl
 
 
 def test_round_i8_ties_and_saturation(oracle):

@@ -11,7 +11,7 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 from volvoxai_b200 import sharded
-from volvoxai_b200 import workloads as wl
+from tests import workloads as wl
 
 
 def test_shard_bounds_cover_every_channel_once():

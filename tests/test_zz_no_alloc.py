@@ -17,7 +17,7 @@ import ctypes as C
 import numpy as np
 import pytest
 
-from volvoxai_b200 import workloads as wl
+from tests import workloads as wl
 
 pytestmark = pytest.mark.gpu
 
@@ -72,6 +72,47 @@ def test_noalloc_matches_ordinary_entry_twice(torch, rows, k, n):
         assert rc == 1, msg
         torch.cuda.synchronize()
         assert torch.equal(got.view(torch.int32), want.view(torch.int32)), f"call {attempt}"
+    weight.close()
+    ctx.close()
+
+
+def test_noalloc_enqueue_only_form_replays_from_a_graph(torch):
+    """wait = 0 only enqueues (the form a caller under stream capture uses): one ordinary call
+    first (the per-device set-up happens there), then the enqueue-only call is captured once and
+    replayed twice over different inputs; both results must equal the ordinary entry's bit for
+    bit, and a waited call afterwards must report no expired wait."""
+    from volvoxai_b200 import w8a8
+    rows, k, n = 8, 1024, 2048
+    ctx = w8a8.Context(0)
+    ctx.use_torch_stream()
+    rng = np.random.default_rng(5)
+    w = rng.integers(-127, 128, size=(n, k), dtype=np.int8)
+    ws = rng.uniform(0.001, 0.02, size=n).astype(np.float32)
+    weight = w8a8.Weight.from_i8(ctx, w, ws)
+    w_dev, ws_dev = torch.from_numpy(w).cuda(), torch.from_numpy(ws).cuda()
+    xs = [torch.from_numpy((rng.standard_normal((rows, k)) * s).astype(np.float32)).cuda() for s in (1.0, 7.0)]
+    prepared = [ctx.prepare(weight, x) for x in xs]
+    q_in, s_in = prepared[0][0].clone(), prepared[0][1].clone()
+    got = torch.zeros((rows, n), dtype=torch.float32, device="cuda")
+    rc, msg = call_noalloc(torch, q_in, s_in, w_dev, ws_dev, None, n, k, got)   # set-up + warm-up
+    assert rc == 1, msg
+    side = torch.cuda.Stream()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=side):
+        rc, msg = call_noalloc(torch, q_in, s_in, w_dev, ws_dev, None, n, k, got, wait=0)
+    assert rc == 1, msg
+    for q, s in prepared:
+        q_in.copy_(q)
+        s_in.copy_(s)
+        got.fill_(-1.0)
+        g.replay()
+        torch.cuda.synchronize()
+        want = torch.empty((rows, n), dtype=torch.float32, device="cuda")
+        ctx.linear_prepared(weight, q, s, want, mode=1, route=w8a8.ROUTE_DECODE_STREAMK)
+        ctx.synchronize()
+        assert torch.equal(got.view(torch.int32), want.view(torch.int32))
+    rc, msg = call_noalloc(torch, q_in, s_in, w_dev, ws_dev, None, n, k, got)   # a waited call reports
+    assert rc == 1, msg
     weight.close()
     ctx.close()
 

@@ -1,4 +1,6 @@
-"""Seeded synthetic inputs with the shapes and value distributions of the
+"""Benchmark and test input generators (not part of the product package).
+
+Seeded synthetic inputs with the shapes and value distributions of the
 benchmark configurations, plus the weight authoring arithmetic that produces
 W8A8 packages.  NumPy only; no dataset, checkpoint or reference file is read.
 
@@ -14,6 +16,8 @@ like a real package:
     scales [N, ceil(K/G)].
 """
 from __future__ import annotations
+
+import functools
 
 import numpy as np
 
@@ -109,6 +113,13 @@ def gemm_activations(rows, k, seed=0):
     return x
 
 
+@functools.lru_cache(maxsize=1)
+def gemm_weights_cached(n, k, seed=0):
+    """gemm_weights with the last result kept (read-only use): the multi-hundred-MB shapes take
+    seconds to draw and several tests share them."""
+    return gemm_weights(n, k, seed)
+
+
 def gemm_weights(n, k, seed=0):
     """Configuration 5 weights for n output channels, drawn directly as int8 codes with the
     distribution per-channel quantization of N(0,0.02) produces (|code| max pinned at 127,
@@ -133,7 +144,7 @@ def gemm_case(rows, k, n, seed=0, weights_fast=False):
     an fp32 master, for the multi-GB shapes."""
     x = gemm_activations(rows, k, seed)
     if weights_fast:
-        w, ws = gemm_weights(n, k, seed)
+        w, ws = gemm_weights_cached(n, k, seed)
     else:
         wf = (np.random.default_rng([seed, 0xC]).standard_normal((n, k), dtype=np.float32)
               * np.float32(0.02))

@@ -22,14 +22,50 @@ EXPORTS = [
     "vxb_context_synchronize", "vxb_weight_create_i8", "vxb_weight_create_w8_words",
     "vxb_weight_destroy", "vxb_weight_d_in", "vxb_weight_d_out", "vxb_weight_device_bytes",
     "vxb_quantize_rows", "vxb_linear_f32", "vxb_linear_i8", "vxb_linear_acc_i32",
-    "vxb_qlinear_device", "vxb_weight_row_bytes", "vxb_linear_prepared", "vxb_linear_host", "vxb_context_profile", "vxb_context_profile_read", "vxb_context_trace",
-    "vxb_measure_i8_tensor_peak", "vxb_measure_mma_issue", "vxb_peer_alloc", "vxb_peer_open",
+    "vxb_qlinear_device", "vxb_weight_row_bytes", "vxb_linear_prepared", "vxb_linear_host", "vxb_context_profile", "vxb_context_profile_read",
+    "vxb_measure_i8_tensor_peak", "vxb_peer_alloc", "vxb_peer_open",
     "vxb_peer_close", "vxb_peer_free", "vxb_linear_i8_gather", "vxb_linear_f32_fused", "vxb_weight_create_w4_words",
     "vxb_rmsnorm_quantize_rows", "vxb_rmsnorm_linear_f32_fused", "vxb_quantize_linear_device",
     "vxb_dequantize_linear_device", "vxb_requantize_linear_device", "vxb_quantize_typed_f32_i8u8",
     "vxb_dequantize_typed_i8u8_f32", "vxb_requantize_linear_i8u8", "vxb_decode_linear_f32_noalloc", "vxb_qlinear_i8u8",
     "vxb_cuda_graph_llm_f32", "vxb_cuda_graph_packed_linear_decode_f32", "vxb_host_cache_clear",
 ]
+
+
+# include/vxb200_plan.h: variant table, launch planning, registry rows (no GPU needed).
+PLAN_EXPORTS = ["vxb_variant_count", "vxb_variant_info", "vxb_plan", "vxb_registry_row"]
+# volvoxai_b200/csrc/diag.h: diagnostics and self-tests, not part of the drop-in boundary.
+DIAG_EXPORTS = ["vxb_context_trace", "vxb_measure_mma_issue", "vxb_context_set_wait_limit",
+                "vxb_selftest_wait_expiry", "vxb_selftest_div_const", "vxb_inject_failure", "vxb_tune"]
+
+EPI_ACC, EPI_F32, EPI_I8 = 1, 2, 4
+WEIGHT_PER_CHANNEL, WEIGHT_GROUPED, WEIGHT_W4_WORDS = 1, 2, 4
+VF_AUTO, VF_PEERS, VF_FUSED_TAIL, VF_VERIFY = 1, 2, 4, 8
+INJECT_LAUNCH, INJECT_ALLOCATION = 1, 2
+
+
+class Variant(C.Structure):
+    """VxbVariant of include/vxb200_plan.h."""
+    _fields_ = [("id", C.c_char_p), ("route", C.c_int32), ("route_label", C.c_char_p), ("kernel", C.c_char_p)] + [
+        (n, C.c_uint32) for n in ("tile_rows", "tile_columns", "tile_k", "threads", "cluster", "shared_bytes_max",
+                                  "min_rows", "max_rows", "epilogue_mask", "weight_mask", "group_size", "flags",
+                                  "priority")]
+
+
+class PlanQuery(C.Structure):
+    """VxbPlanQuery of include/vxb200_plan.h."""
+    _fields_ = [("rows", C.c_uint32), ("k", C.c_uint32), ("n", C.c_uint32), ("weight_kind", C.c_uint32),
+                ("group_size", C.c_uint32), ("epilogue", C.c_uint32), ("requested_route", C.c_int32),
+                ("n_peers", C.c_uint32), ("fused_tail", C.c_uint32), ("fp32_input", C.c_uint32),
+                ("sm_count", C.c_uint32), ("pair_clusters", C.c_uint32)]
+
+
+class LaunchPlan(C.Structure):
+    """VxbLaunchPlan of include/vxb200_plan.h."""
+    _fields_ = [("variant", C.c_int32), ("route", C.c_int32), ("tile_rows", C.c_uint32), ("tile_columns", C.c_uint32),
+                ("tile_k", C.c_uint32), ("grid", C.c_uint32), ("threads", C.c_uint32), ("cluster", C.c_uint32),
+                ("launches", C.c_uint32), ("quantizer", C.c_int32), ("quantizer_grid", C.c_uint32),
+                ("quantizer_cluster", C.c_uint32), ("workspace_bytes", C.c_uint64)]
 
 
 class LLMOpArgs(C.Structure):
@@ -91,6 +127,18 @@ def load() -> C.CDLL:
     L.vxb_linear_prepared.argtypes = [vp, vp, vp, vp, u32, C.c_int, f32, i32, vp, u32, C.c_int]
     L.vxb_linear_host.argtypes = [vp, vp, vp, u32, C.c_int, f32, i32, vp]
     L.vxb_context_trace.argtypes = [vp, vp]
+    L.vxb_context_set_wait_limit.argtypes = [vp, C.c_uint64]
+    L.vxb_selftest_wait_expiry.argtypes = [vp]
+    L.vxb_selftest_div_const.argtypes = [vp, C.c_int, u32, u32, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]
+    L.vxb_inject_failure.argtypes = [C.c_int, u32]
+    L.vxb_inject_failure.restype = None
+    L.vxb_tune.argtypes = [C.c_char_p, C.c_int64]
+    L.vxb_variant_count.restype = u32
+    L.vxb_variant_info.argtypes = [u32]
+    L.vxb_variant_info.restype = C.POINTER(Variant)
+    L.vxb_plan.argtypes = [C.POINTER(PlanQuery), C.POINTER(LaunchPlan), C.c_char_p, u32]
+    L.vxb_registry_row.argtypes = [u32, C.c_char_p, u32]
+    L.vxb_registry_row.restype = u32
     L.vxb_context_profile.argtypes = [vp, C.c_int]
     L.vxb_context_profile_read.argtypes = [vp, C.POINTER(C.c_double), C.POINTER(C.c_uint64),
                                            C.POINTER(C.c_double), C.POINTER(C.c_uint64)]

@@ -17,14 +17,14 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 ROOT = os.path.dirname(PKG)
 LIB = os.path.join(PKG, "libvxb200.so")
-SOURCES = ["api.cu", "quantize.cu", "gemv.cu", "gemm_tcgen05.cu", "gemm_pair_tcgen05.cu", "gemm_grouped_tcgen05.cu", "decode_tcgen05.cu", "decode_rows.cu", "boundary_ops.cu"]
-HEADERS = [os.path.join(CSRC, "common.cuh"), os.path.join(CSRC, "tcgen05.cuh"), os.path.join(ROOT, "include", "vxb200_w8a8.h")]
+SOURCES = ["api.cu", "plan.cu", "selftest.cu", "quantize.cu", "gemv.cu", "gemm_tcgen05.cu", "gemm_pair_tcgen05.cu", "gemm_grouped_tcgen05.cu", "decode_tcgen05.cu", "decode_rows.cu", "boundary_ops.cu"]
+HEADERS = [os.path.join(CSRC, "common.cuh"), os.path.join(CSRC, "tcgen05.cuh"), os.path.join(CSRC, "diag.h"), os.path.join(ROOT, "include", "vxb200_w8a8.h"), os.path.join(ROOT, "include", "vxb200_plan.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--fmad=false",            # every epilogue multiply/add is separately rounded
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
-    "-cudart", "static", "-shared",
+    "-cudart", "static", "-shared", "--threads", "0",
 ]
 
 

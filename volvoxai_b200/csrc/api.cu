@@ -1,6 +1,8 @@
 // C ABI of the W8A8 linear route (declarations and contracts: include/vxb200_w8a8.h).
 // Host-side orchestration only: validation, scratch, route choice, tensor maps.
 #include "../../include/vxb200_w8a8.h"
+#include "../../include/vxb200_plan.h"
+#include "diag.h"
 #include "common.cuh"
 
 #include <atomic>
@@ -77,10 +79,21 @@ bool encode_i8_kblocks(CUtensorMap* map, const void* base, uint32_t rows, uint32
               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Host-side failure injection (diag.h): countdowns to the launch / allocation that is refused.
+std::atomic<uint32_t> g_fail_launch{0}, g_fail_alloc{0};
+bool injected(std::atomic<uint32_t>& countdown) {
+    uint32_t c = countdown.load(std::memory_order_relaxed);
+    while (c != 0) {
+        if (countdown.compare_exchange_weak(c, c - 1, std::memory_order_relaxed)) return c == 1;
+    }
+    return false;
+}
+
 struct Buffer {
     void* ptr = nullptr; size_t bytes = 0;
     cudaError_t reserve(size_t need) {
         if (need <= bytes) return cudaSuccess;
+        if (injected(g_fail_alloc)) return cudaErrorMemoryAllocation;
         if (ptr) cudaFree(ptr);
         ptr = nullptr; bytes = 0;
         size_t grow = need + need / 4;
@@ -99,7 +112,7 @@ struct VxbContext {
     int sm_count = 0;
     Buffer q, row_scales, bias_eff, stage_in, stage_out;
     Buffer splitk_ws, splitk_counters;   // zero between calls (the decode kernel cleans up)
-    int* status = nullptr;        // device word raised by bounded waits
+    int* status = nullptr;        // device block: [0] raised by bounded waits, [1] wait limit in 1024-clock units (0 = default)
     unsigned long long* trace = nullptr;   // caller's device buffer for decode-kernel time stamps, or null
     int* status_host = nullptr;   // pinned mirror
     bool tcgen05_ready = false;
@@ -109,6 +122,7 @@ struct VxbContext {
     // vxb_linear_host: upload / download streams and their events
     cudaStream_t copy_in = nullptr, copy_out = nullptr;
     cudaEvent_t ev_in[2] = {}, ev_done[2] = {}, ev_out[2] = {}, ev_start = nullptr;
+    cudaEvent_t ev_switch = nullptr;   // orders the context's scratch across a stream change
     bool profiling = false;
     std::vector<cudaEvent_t> prof_events[2];   // [0] = K1 quantizer, [1] = GEMM / GEMV
 };
@@ -230,51 +244,56 @@ int upload_group_scales(VxbContext* ctx, VxbWeight* w, const float* group_scales
     return 1;
 }
 
-struct Plan {
-    int route;
-    const char* name;
-};
+// A refused launch (diag.h, vxb_inject_failure) looks like a launch the driver rejected.
+#define LAUNCH_TRY(expr)                                                                                  \
+    do { if (injected(g_fail_launch)) return fail(-1, "%s: launch refused (injected)", #expr);            \
+         CUDA_TRY((expr), -1); } while (0)
 
-Plan choose_route(const VxbContext* ctx, const VxbWeight* w, uint32_t rows, int requested) {
-    if (requested == VXB_ROUTE_GEMV) return {VXB_ROUTE_GEMV, "gemv-dp4a"};
-    if (requested == VXB_ROUTE_SIMT) return {VXB_ROUTE_SIMT, "simt-dp4a"};
-    if (requested == VXB_ROUTE_TCGEN05) return {VXB_ROUTE_TCGEN05, "tcgen05-i8"};
-    if (requested == VXB_ROUTE_TCGEN05_PAIR) return {VXB_ROUTE_TCGEN05_PAIR, "tcgen05-pair-i8"};
-    if (requested == VXB_ROUTE_DECODE) return {VXB_ROUTE_DECODE, "decode-rows-tcgen05-i8"};
-    if (requested == VXB_ROUTE_DECODE_STREAMK) return {VXB_ROUTE_DECODE_STREAMK, "decode-streamk-tcgen05-i8"};
-    (void)ctx; (void)w;
-    if (rows <= 128) return {VXB_ROUTE_DECODE, "decode-rows-tcgen05-i8"};
-    return {VXB_ROUTE_TCGEN05, "tcgen05-i8"};
+uint32_t weight_kind(const VxbWeight* w) {
+    return !w->group ? VXB_WEIGHT_PER_CHANNEL : w->w4 ? VXB_WEIGHT_W4_WORDS : VXB_WEIGHT_GROUPED;
 }
 
-// int32 GEMM + epilogue over already-quantized activations q [rows, kpad].
+// int32 GEMM + epilogue over already-quantized activations q [rows, kpad].  The kernel is the one
+// vxb_plan() names for this call: the same function tests call without a GPU.
 int run_gemm(VxbContext* ctx, const VxbWeight* w, const int8_t* q, uint32_t rows,
              const EpilogueParams& epi, int requested, const char* prefix) {
-    Plan plan = choose_route(ctx, w, rows, requested);
-    const bool requested_auto = requested == VXB_ROUTE_AUTO;
+    if (!ctx->tcgen05_ready) {
+        CUDA_TRY(gemm_tcgen05_prepare(), 0);
+        ctx->tcgen05_ready = true;
+    }
+    if (!ctx->pair_ready) {
+        CUDA_TRY(gemm_pair_prepare(), 0);
+        ctx->pair_ready = true;
+    }
+    VxbPlanQuery query{};
+    query.rows = rows; query.k = w->d_in; query.n = w->d_out;
+    query.weight_kind = weight_kind(w); query.group_size = w->group;
+    query.epilogue = epi.mode == kEpiAcc ? VXB_EPI_ACC : epi.mode == kEpiF32 ? VXB_EPI_F32 : VXB_EPI_I8;
+    query.requested_route = requested; query.n_peers = epi.n_peers;
+    query.fused_tail = (epi.residual || epi.act) ? 1u : 0u;
+    query.sm_count = (uint32_t)ctx->sm_count;
+    query.pair_clusters = (uint32_t)(gemm_pair_clusters() > 0 ? gemm_pair_clusters() : 0);
+    VxbLaunchPlan plan;
+    char why[160];
+    if (vxb_plan(&query, &plan, why, sizeof why) != 1) return fail(0, "%s", why);
+    const VxbVariant* variant = vxb_variant_info((uint32_t)plan.variant);
+    const bool tensor_map_route = plan.variant == VXB_VARIANT_DECODE_ROWS || plan.variant == VXB_VARIANT_DECODE_STREAMK ||
+                                  plan.variant == VXB_VARIANT_TCGEN05 || plan.variant == VXB_VARIANT_TCGEN05_PAIR ||
+                                  plan.variant == VXB_VARIANT_GROUPED_TCGEN05;
+    if (tensor_map_route && !w->has_tmap) return fail(0, "no tensor map for this weight (driver entry point missing)");
+    EpilogueParams ge = epi;
+    if (w->group) { ge.gscales = w->gscales; ge.group = w->group; ge.groups = w->groups; }
     ProfileScope scope(ctx, 1);
-    if (w->group) {
-        // differing group scales: exact per-group arithmetic, fp32 output only
-        if (!requested_auto && requested != VXB_ROUTE_SIMT) return fail(0, "weights with grouped scales take the automatic route only");
-        if (epi.mode != kEpiF32) return fail(0, "weights with grouped scales produce fp32 output only");
-        if (epi.residual || epi.act) return fail(0, "weights with grouped scales have no fused epilogue");
-        // tensor cores with one accumulator drain per group (also for a single row: 34 us against
-        // 42 us at K 4096, N 14336); the explicit CUDA-core route keeps one thread per channel
-        if (requested_auto && rows <= 2 && w->w4) {
-            // W4 storage: the same decode kernel over the 4-bit words (half the bytes)
-            EpilogueParams ge = epi;
-            ge.gscales = w->gscales; ge.group = w->group; ge.groups = w->groups;
-            CUDA_TRY(launch_gemv_w4_grouped(q, rows, w->w4, w->w4_row_words, w->d_out, w->kpad, ge, ctx->sm_count, ctx->stream), -1);
-            plan.name = "gemv-w4-grouped";
-        } else if (requested_auto && (rows <= 2 || (rows <= 4 && (uint64_t)w->kpad * w->d_out <= (32ull << 20)))) {
-            // decode: a warp per channel streams the weights once (the reference's own decode mode is
-            // one row against grouped scales): 14 us at K 4096, N 14336 for one row; from three rows
-            // on the tensor-core kernel is faster at large weights
-            EpilogueParams ge = epi;
-            ge.gscales = w->gscales; ge.group = w->group; ge.groups = w->groups;
-            CUDA_TRY(launch_gemv_grouped(q, rows, w->w, w->d_out, w->kpad, ge, ctx->sm_count, ctx->stream), -1);
-            plan.name = "gemv-grouped";
-        } else if (requested_auto && w->has_tmap && w->gscales_t) {
+    switch (plan.variant) {
+        case VXB_VARIANT_GEMV_W4_GROUPED:
+            // W4 storage: the decode kernel over the 4-bit words themselves (half the bytes)
+            LAUNCH_TRY(launch_gemv_w4_grouped(q, rows, w->w4, w->w4_row_words, w->d_out, w->kpad, ge, ctx->sm_count, ctx->stream));
+            break;
+        case VXB_VARIANT_GEMV_GROUPED:
+            LAUNCH_TRY(launch_gemv_grouped(q, rows, w->w, w->d_out, w->kpad, ge, ctx->sm_count, ctx->stream));
+            break;
+        case VXB_VARIANT_GROUPED_TCGEN05: {
+            if (!w->gscales_t) return fail(0, "no transposed group-scale table for this weight");
             if (!ctx->grouped_ready) {
                 CUDA_TRY(gemm_grouped_tcgen05_prepare(), 0);
                 ctx->grouped_ready = true;
@@ -286,84 +305,71 @@ int run_gemm(VxbContext* ctx, const VxbWeight* w, const int8_t* q, uint32_t rows
             a.group = w->group; a.groups = w->groups; a.n_pad = w->n_pad; a.gscales_t = w->gscales_t;
             a.row_scales = epi.row_scales; a.bias = epi.bias_f32; a.out = (float*)epi.out; a.ld = epi.ld;
             a.status = ctx->status;
-            CUDA_TRY(launch_gemm_grouped_tcgen05(a, ctx->sm_count, ctx->stream), -1);
-            plan.name = "tcgen05-grouped-i8";
-        } else {
-            EpilogueParams ge = epi;
-            ge.gscales = w->gscales; ge.group = w->group; ge.groups = w->groups;
-            CUDA_TRY(launch_gemm_grouped(q, rows, w->w, w->d_out, w->kpad, ge, ctx->stream), -1);
-            plan.name = "dp4a-grouped";
+            LAUNCH_TRY(launch_gemm_grouped_tcgen05(a, ctx->sm_count, ctx->stream));
+            break;
         }
-    } else if (plan.route == VXB_ROUTE_GEMV) {
-        if (rows > 32) return fail(0, "gemv route needs rows <= 32 (got %u)", rows);
-        CUDA_TRY(launch_gemv(q, rows, w->w, w->d_out, w->kpad, epi, ctx->sm_count, ctx->stream), -1);
-    } else if (plan.route == VXB_ROUTE_SIMT) {
-        CUDA_TRY(launch_gemm_simt(q, rows, w->w, w->d_out, w->kpad, epi, ctx->stream), -1);
-    } else if (plan.route == VXB_ROUTE_DECODE) {
-        if (rows > 128) return fail(0, "decode route needs rows <= 128 (got %u)", rows);
-        if (!w->has_tmap) return fail(0, "no tensor map for this weight (driver entry point missing)");
-        DecodeRowsArgs a;
-        a.tmap_w = w->tmap_rows;
-        a.rows = rows; a.n = w->d_out; a.kpad = w->kpad;
-        a.tile_rows = w->tile_rows; a.tiles_per_cta = w->tiles_per_cta;
-        a.w_stage_bytes = round_up(w->tile_rows * kKAlign, 1024u);
-        a.epi = epi; a.status = ctx->status; a.trace = ctx->trace;
-        if (!decode_rows_configure(a)) return fail(0, "no launch shape for the decode kernel (rows %u, d_out %u)", rows, w->d_out);
-        if (!encode_i8_kblocks(&a.tmap_x, q, rows, w->kpad, decode_rows_token_slots(rows), a.x_chunk_blocks))
-            return fail(0, "cuTensorMapEncodeTiled failed for activations");
-        CUDA_TRY(launch_decode_rows(a, ctx->stream), -1);
-    } else if (plan.route == VXB_ROUTE_DECODE_STREAMK) {
-        if (rows > 128) return fail(0, "decode route needs rows <= 128 (got %u)", rows);
-        if (!w->has_tmap) return fail(0, "no tensor map for this weight (driver entry point missing)");
-        // split-K scratch: int32 [rows, d_out] + one counter per 128-channel tile, kept zero
-        const size_t ws_bytes = (size_t)128 * w->d_out * 4, cnt_bytes = (size_t)((w->d_out + 127) / 128) * 4;
-        if (ctx->splitk_ws.bytes < ws_bytes) {
-            CUDA_TRY(ctx->splitk_ws.reserve(ws_bytes), 0);
-            CUDA_TRY(cudaMemsetAsync(ctx->splitk_ws.ptr, 0, ctx->splitk_ws.bytes, ctx->stream), -1);
+        case VXB_VARIANT_DP4A_GROUPED:
+            LAUNCH_TRY(launch_gemm_grouped(q, rows, w->w, w->d_out, w->kpad, ge, ctx->stream));
+            break;
+        case VXB_VARIANT_GEMV_DP4A:
+            LAUNCH_TRY(launch_gemv(q, rows, w->w, w->d_out, w->kpad, epi, ctx->sm_count, ctx->stream));
+            break;
+        case VXB_VARIANT_SIMT_DP4A:
+            LAUNCH_TRY(launch_gemm_simt(q, rows, w->w, w->d_out, w->kpad, epi, ctx->stream));
+            break;
+        case VXB_VARIANT_DECODE_ROWS: {
+            DecodeRowsArgs a;
+            a.tmap_w = w->tmap_rows;
+            a.rows = rows; a.n = w->d_out; a.kpad = w->kpad;
+            a.tile_rows = w->tile_rows; a.tiles_per_cta = w->tiles_per_cta;
+            a.w_stage_bytes = round_up(w->tile_rows * kKAlign, 1024u);
+            a.epi = epi; a.status = ctx->status; a.trace = ctx->trace;
+            if (!decode_rows_configure(a)) return fail(0, "no launch shape for the decode kernel (rows %u, d_out %u)", rows, w->d_out);
+            if (!encode_i8_kblocks(&a.tmap_x, q, rows, w->kpad, decode_rows_token_slots(rows), a.x_chunk_blocks))
+                return fail(0, "cuTensorMapEncodeTiled failed for activations");
+            LAUNCH_TRY(launch_decode_rows(a, ctx->stream));
+            break;
         }
-        if (ctx->splitk_counters.bytes < cnt_bytes) {
-            CUDA_TRY(ctx->splitk_counters.reserve(cnt_bytes), 0);
-            CUDA_TRY(cudaMemsetAsync(ctx->splitk_counters.ptr, 0, ctx->splitk_counters.bytes, ctx->stream), -1);
+        case VXB_VARIANT_DECODE_STREAMK: {
+            // split-K scratch: int32 [rows, d_out] + one counter per 128-channel tile, kept zero
+            const size_t ws_bytes = (size_t)128 * w->d_out * 4, cnt_bytes = (size_t)((w->d_out + 127) / 128) * 4;
+            if (ctx->splitk_ws.bytes < ws_bytes) {
+                CUDA_TRY(ctx->splitk_ws.reserve(ws_bytes), 0);
+                CUDA_TRY(cudaMemsetAsync(ctx->splitk_ws.ptr, 0, ctx->splitk_ws.bytes, ctx->stream), -1);
+            }
+            if (ctx->splitk_counters.bytes < cnt_bytes) {
+                CUDA_TRY(ctx->splitk_counters.reserve(cnt_bytes), 0);
+                CUDA_TRY(cudaMemsetAsync(ctx->splitk_counters.ptr, 0, ctx->splitk_counters.bytes, ctx->stream), -1);
+            }
+            DecodeTcgen05Args a;
+            if (!encode_i8_rows(&a.tmap_x, q, rows, w->kpad, decode_token_slots(rows)))
+                return fail(0, "cuTensorMapEncodeTiled failed for activations");
+            a.tmap_w = w->tmap_w128;
+            a.rows = rows; a.n = w->d_out; a.kpad = w->kpad; a.epi = epi;
+            a.workspace = (int32_t*)ctx->splitk_ws.ptr; a.counters = (uint32_t*)ctx->splitk_counters.ptr;
+            a.status = ctx->status;
+            LAUNCH_TRY(launch_decode_tcgen05(a, ctx->sm_count, ctx->stream));
+            break;
         }
-        DecodeTcgen05Args a;
-        if (!encode_i8_rows(&a.tmap_x, q, rows, w->kpad, decode_token_slots(rows)))
-            return fail(0, "cuTensorMapEncodeTiled failed for activations");
-        a.tmap_w = w->tmap_w128;
-        a.rows = rows; a.n = w->d_out; a.kpad = w->kpad; a.epi = epi;
-        a.workspace = (int32_t*)ctx->splitk_ws.ptr; a.counters = (uint32_t*)ctx->splitk_counters.ptr;
-        a.status = ctx->status;
-        CUDA_TRY(launch_decode_tcgen05(a, ctx->sm_count, ctx->stream), -1);
-    } else {
-        if (!w->has_tmap) return fail(0, "no tensor map for this weight (driver entry point missing)");
-        if (!ctx->tcgen05_ready) {
-            CUDA_TRY(gemm_tcgen05_prepare(), 0);
-            ctx->tcgen05_ready = true;
+        case VXB_VARIANT_TCGEN05: case VXB_VARIANT_TCGEN05_PAIR: {
+            GemmTcgen05Args a;
+            if (!encode_i8_rows(&a.tmap_a, q, rows, w->kpad, 128)) return fail(0, "cuTensorMapEncodeTiled failed for activations");
+            a.rows = rows; a.n = w->d_out; a.kpad = w->kpad; a.epi = epi; a.status = ctx->status;
+            if (plan.variant == VXB_VARIANT_TCGEN05_PAIR) {
+                a.tmap_b = w->tmap_w128;   // each CTA of a pair loads half of the tile's weight rows
+                LAUNCH_TRY(launch_gemm_pair(a, ctx->stream));
+            } else {
+                a.tmap_b = w->tmap_b;
+                LAUNCH_TRY(launch_gemm_tcgen05(a, ctx->sm_count, ctx->stream));
+            }
+            break;
         }
-        if (!ctx->pair_ready) {
-            CUDA_TRY(gemm_pair_prepare(), 0);
-            ctx->pair_ready = true;
-        }
-        GemmTcgen05Args a;
-        if (!encode_i8_rows(&a.tmap_a, q, rows, w->kpad, 128)) return fail(0, "cuTensorMapEncodeTiled failed for activations");
-        a.rows = rows; a.n = w->d_out; a.kpad = w->kpad; a.epi = epi; a.status = ctx->status;
-        // pairs of CTAs on 256 x 256 tiles once there are at least two waves of 128 x 256 tiles
-        const uint32_t tiles = ((rows + 127) / 128) * ((w->d_out + 255) / 256);
-        const bool pair = gemm_pair_clusters() > 0 && epi.n_peers == 0 &&
-                          (plan.route == VXB_ROUTE_TCGEN05_PAIR ||
-                           (requested_auto && tiles >= 2u * (uint32_t)ctx->sm_count));
-        if (plan.route == VXB_ROUTE_TCGEN05_PAIR && !pair) return fail(0, "no co-resident CTA pairs on this device");
-        if (pair) {
-            a.tmap_b = w->tmap_w128;   // each CTA of a pair loads half of the tile's weight rows
-            CUDA_TRY(launch_gemm_pair(a, ctx->stream), -1);
-            plan.name = "tcgen05-pair-i8";
-        } else {
-            a.tmap_b = w->tmap_b;
-            CUDA_TRY(launch_gemm_tcgen05(a, ctx->sm_count, ctx->stream), -1);
-        }
+        default:
+            return fail(0, "variant %d has no launcher", plan.variant);
     }
     count_launch();
     const char* tail = epi.mode == kEpiAcc ? "acc" : epi.mode == kEpiF32 ? "e1" : "e2";
-    snprintf(g_route, sizeof g_route, "%s%s+%s", prefix, plan.name, tail);
+    snprintf(g_route, sizeof g_route, "%s%s+%s", prefix, variant->route_label, tail);
     return 1;
 }
 
@@ -381,11 +387,11 @@ int quantize_into_scratch(VxbContext* ctx, const VxbWeight* w, const float* x, u
     {
         ProfileScope scope(ctx, 0);
         if (norm_weight)
-            CUDA_TRY(launch_rmsnorm_quantize_rows(x, norm_weight, epsilon, rows, w->d_in, norm_out, (int8_t*)ctx->q.ptr,
-                                                  w->kpad, (float*)ctx->row_scales.ptr, nullptr, ctx->stream), -1);
+            LAUNCH_TRY(launch_rmsnorm_quantize_rows(x, norm_weight, epsilon, rows, w->d_in, norm_out, (int8_t*)ctx->q.ptr,
+                                                    w->kpad, (float*)ctx->row_scales.ptr, nullptr, ctx->stream));
         else
-            CUDA_TRY(launch_quantize_rows(x, rows, w->d_in, (int8_t*)ctx->q.ptr, w->kpad,
-                                          (float*)ctx->row_scales.ptr, nullptr, ctx->stream), -1);
+            LAUNCH_TRY(launch_quantize_rows(x, rows, w->d_in, (int8_t*)ctx->q.ptr, w->kpad,
+                                            (float*)ctx->row_scales.ptr, nullptr, ctx->stream));
     }
     count_launch();
     return 1;
@@ -412,8 +418,8 @@ int vxb_context_create(int device, void* stream, VxbContext** out) {
     if (prop.major != 10) return fail(0, "device %d is sm_%d%d; this library is sm_100a only", device, prop.major, prop.minor);
     VxbContext* ctx = new VxbContext();
     ctx->device = device; ctx->stream = (cudaStream_t)stream; ctx->sm_count = prop.multiProcessorCount;
-    if (cudaMalloc(&ctx->status, sizeof(int)) != cudaSuccess ||
-        cudaMemset(ctx->status, 0, sizeof(int)) != cudaSuccess ||
+    if (cudaMalloc(&ctx->status, 2 * sizeof(int)) != cudaSuccess ||
+        cudaMemset(ctx->status, 0, 2 * sizeof(int)) != cudaSuccess ||
         cudaMallocHost(&ctx->status_host, sizeof(int)) != cudaSuccess) {
         delete ctx;
         return fail(0, "context allocation failed: %s", cudaGetErrorString(cudaGetLastError()));
@@ -435,6 +441,7 @@ void vxb_context_destroy(VxbContext* ctx) {
         for (int b = 0; b < 2; b++) { cudaEventDestroy(ctx->ev_in[b]); cudaEventDestroy(ctx->ev_done[b]); cudaEventDestroy(ctx->ev_out[b]); }
         cudaEventDestroy(ctx->ev_start);
     }
+    if (ctx->ev_switch) cudaEventDestroy(ctx->ev_switch);
     if (ctx->status) cudaFree(ctx->status);
     if (ctx->status_host) cudaFreeHost(ctx->status_host);
     delete ctx;
@@ -442,7 +449,23 @@ void vxb_context_destroy(VxbContext* ctx) {
 
 int vxb_context_set_stream(VxbContext* ctx, void* stream) {
     if (!ctx) return fail(0, "null context");
-    ctx->stream = (cudaStream_t)stream;
+    cudaStream_t next = (cudaStream_t)stream;
+    if (next == ctx->stream) return 1;
+    // The context's scratch (quantized rows, row scales, split-K workspace, status block) is shared
+    // by everything queued through it: work on the new stream must not overtake what is still
+    // queued on the old one.  Under stream capture the recording is skipped (an event of a stream
+    // that is not part of the capture cannot be waited on there); the caller orders the streams.
+    if (ensure_device(ctx) != 1) return -1;
+    cudaStreamCaptureStatus cap_old = cudaStreamCaptureStatusNone, cap_new = cudaStreamCaptureStatusNone;
+    const bool plain = cudaStreamIsCapturing(ctx->stream, &cap_old) == cudaSuccess && cap_old == cudaStreamCaptureStatusNone &&
+                       cudaStreamIsCapturing(next, &cap_new) == cudaSuccess && cap_new == cudaStreamCaptureStatusNone;
+    cudaGetLastError();
+    if (plain) {
+        if (!ctx->ev_switch) CUDA_TRY(cudaEventCreateWithFlags(&ctx->ev_switch, cudaEventDisableTiming), 0);
+        CUDA_TRY(cudaEventRecord(ctx->ev_switch, ctx->stream), -1);
+        CUDA_TRY(cudaStreamWaitEvent(next, ctx->ev_switch, 0), -1);
+    }
+    ctx->stream = next;
     return 1;
 }
 
@@ -888,6 +911,58 @@ int vxb_context_trace(VxbContext* ctx, unsigned long long* device_stamps) {
     return 1;
 }
 
+int vxb_context_set_wait_limit(VxbContext* ctx, uint64_t cycles) {
+    if (!ctx) return fail(0, "null context");
+    if (ensure_device(ctx) != 1) return -1;
+    uint64_t units = (cycles + 1023u) >> 10;
+    if (units > 0x7fffffffull) units = 0x7fffffffull;
+    const int value = (int)units;   // 0 = the default limit
+    CUDA_TRY(cudaMemcpyAsync(ctx->status + 1, &value, sizeof(int), cudaMemcpyHostToDevice, ctx->stream), -1);
+    CUDA_TRY(cudaStreamSynchronize(ctx->stream), -1);
+    return 1;
+}
+
+int vxb_selftest_wait_expiry(VxbContext* ctx) {
+    if (!ctx) return fail(0, "null context");
+    if (ensure_device(ctx) != 1) return -1;
+    LAUNCH_TRY(launch_wait_expiry(ctx->status, ctx->stream));
+    count_launch();
+    return 1;
+}
+
+int vxb_selftest_div_const(VxbContext* ctx, int divisor_exponent, uint32_t neighbours, uint32_t samples,
+                           uint64_t* mismatches, uint64_t* checked) {
+    if (!ctx || !mismatches || !checked) return fail(0, "null argument");
+    if (divisor_exponent < -100 || divisor_exponent > 100 || neighbours > 16) return fail(0, "argument out of range");
+    if (ensure_device(ctx) != 1) return -1;
+    unsigned long long* counts = nullptr;
+    CUDA_TRY(cudaMalloc(&counts, 2 * sizeof(unsigned long long)), 0);
+    cudaError_t err = cudaMemsetAsync(counts, 0, 2 * sizeof(unsigned long long), ctx->stream);
+    if (err == cudaSuccess)
+        err = launch_div_const_check(divisor_exponent, neighbours, samples, counts, counts + 1, ctx->sm_count, ctx->stream);
+    unsigned long long host[2] = {0, 0};
+    if (err == cudaSuccess) err = cudaMemcpyAsync(host, counts, sizeof host, cudaMemcpyDeviceToHost, ctx->stream);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(ctx->stream);
+    cudaFree(counts);
+    count_launch();
+    if (err != cudaSuccess) return fail(-1, "division self-test failed: %s", cudaGetErrorString(err));
+    *mismatches = host[0]; *checked = host[1];
+    return 1;
+}
+
+void vxb_inject_failure(int kind, uint32_t countdown) {
+    if (kind == VXB_INJECT_LAUNCH) g_fail_launch.store(countdown);
+    else if (kind == VXB_INJECT_ALLOCATION) g_fail_alloc.store(countdown);
+}
+
+int vxb_tune(const char* name, int64_t value) {
+    if (!name) return 0;
+    Tunables& t = tunables();
+    if (!strcmp(name, "decode.pair_share_bytes")) { t.decode_pair_share_bytes = (uint32_t)value; return 1; }
+    if (!strcmp(name, "decode.l2_prefetch")) { t.decode_l2_prefetch = value != 0; return 1; }
+    return 0;
+}
+
 int vxb_context_profile(VxbContext* ctx, int enable) {
     if (!ctx) return fail(0, "null context");
     if (ensure_device(ctx) != 1) return -1;
@@ -1026,10 +1101,10 @@ int vxb_measure_i8_tensor_peak(VxbContext* ctx, uint32_t iters, double* tops) {
 namespace {
 
 struct HostKey {
-    const void* weight; const void* scales; const void* bias; uint32_t d_in, d_out, kind;
+    const void* weight; const void* scales; const void* bias; uint32_t d_in, d_out, kind, group;
     bool operator==(const HostKey& o) const {
         return weight == o.weight && scales == o.scales && bias == o.bias && d_in == o.d_in &&
-               d_out == o.d_out && kind == o.kind;
+               d_out == o.d_out && kind == o.kind && group == o.group;
     }
 };
 struct HostKeyHash {
@@ -1037,7 +1112,7 @@ struct HostKeyHash {
         size_t h = (size_t)k.weight * 1315423911u;
         h ^= (size_t)k.scales + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2);
         h ^= (size_t)k.bias + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2);
-        h ^= ((size_t)k.d_in << 32) ^ k.d_out ^ ((size_t)k.kind << 60);
+        h ^= ((size_t)k.d_in << 32) ^ k.d_out ^ ((size_t)k.kind << 60) ^ ((size_t)k.group << 20);
         return h;
     }
 };
@@ -1089,7 +1164,7 @@ int vxb_qlinear_i8u8(const void* input, const void* weight, const float* weight_
     VxbContext* ctx = nullptr;
     int rc = host_context(&ctx);
     if (rc != 1) return rc;
-    const HostKey key{weight, weight_scales, bias, d_in, d_out, 1u};
+    const HostKey key{weight, weight_scales, bias, d_in, d_out, 1u, 0u};
     VxbWeight* w = nullptr;
     auto it = g_host_weights.find(key);
     if (it != g_host_weights.end()) w = it->second;
@@ -1174,12 +1249,25 @@ int vxb_cuda_graph_llm_f32(const VxbLLMOpArgs* a) {
     if (a->first_unit != 0 && a->unit_count == 0) return fail(0, "first_unit without unit_count");
     const uint32_t row0 = (uint32_t)(first / n), rows = (uint32_t)(units / n);
     if (!rows) return 1;
+    if (a->rate != 32 && a->rate != 64 && a->rate != 128 && a->rate != 256) return fail(0, "group size %d is not 32/64/128/256", a->rate);
+    {
+        // the output window must not overlap any source, as the reference's entry checks before it
+        // maps anything (ranges_overlap in native/src/backends/cuda/host/cuda_graph_llm_host.inc:111-186)
+        const uint32_t bits = (uint32_t)a->groups, groups = (k + (uint32_t)a->rate - 1) / (uint32_t)a->rate;
+        const size_t out_b = (size_t)rows * n * 4;
+        const float* out_p = a->y[0] + (size_t)row0 * n;
+        if (overlap(out_p, out_b, a->x[0], (size_t)rows64 * k * 4) ||
+            overlap(out_p, out_b, a->x[1], (size_t)n * ((k * bits + 31) / 32) * 4) ||
+            overlap(out_p, out_b, a->x[2], (size_t)n * groups * 4) ||
+            (a->x[3] && overlap(out_p, out_b, a->x[3], (size_t)n * 4)))
+            return fail(0, "output overlaps an input");
+    }
 
     std::lock_guard<std::mutex> lock(g_host_mutex);
     VxbContext* ctx = nullptr;
     int rc = host_context(&ctx);
     if (rc != 1) return rc;
-    const HostKey key{a->x[1], a->x[2], a->x[3], k, n, a->groups == 4 ? 3u : 2u};
+    const HostKey key{a->x[1], a->x[2], a->x[3], k, n, a->groups == 4 ? 3u : 2u, (uint32_t)a->rate};
     VxbWeight* w = nullptr;
     auto it = g_host_weights.find(key);
     if (it != g_host_weights.end()) w = it->second;

@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 #include <cuda.h>
 #include <stdint.h>
+#include <mutex>
 
 namespace vxb {
 
@@ -62,6 +63,26 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+// Raises a kernel's dynamic shared-memory limit to `bytes`, once per device and size: the
+// attribute belongs to the (function, device) pair, and contexts may live on several devices and
+// threads of one process.
+template <auto Kernel>
+inline cudaError_t ensure_dynamic_smem(uint32_t bytes) {
+    static std::mutex guard;
+    static uint32_t configured[64] = {};
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return e;
+    if (device < 0 || device >= 64) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(guard);
+    if (bytes > configured[device]) {
+        e = cudaFuncSetAttribute(Kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        if (e != cudaSuccess) return e;
+        configured[device] = bytes;
+    }
+    return cudaSuccess;
 }
 
 // ---- epilogue arithmetic (every operation separately rounded; no FMA) ----
@@ -272,6 +293,12 @@ cudaError_t launch_repack_weight(const uint8_t* src, uint32_t src_ld, uint32_t n
                                  uint32_t xor_mask, int8_t* dst, uint32_t kpad, int32_t* wsum,
                                  cudaStream_t stream);
 
+// Launch geometry of the three streaming GEMV kernels (256 threads, one warp per `ch` channels,
+// activations staged in a shared-memory chunk): kind 0 = per-channel scales (rows <= 32),
+// 1 = grouped scales (rows <= 4), 2 = grouped scales over 4-bit words (rows <= 2).
+struct GemvShape { uint32_t mr, ch, kchunk, smem, grid; };
+GemvShape gemv_shape(int kind, uint32_t rows, uint32_t n, uint32_t kpad, int sm_count);
+
 // K3: small-M (rows <= 32) bandwidth-bound GEMV, dp4a + warp-shuffle reduction.
 cudaError_t launch_gemv(const int8_t* q, uint32_t rows, const int8_t* w, uint32_t n,
                         uint32_t kpad, const EpilogueParams& epi, int sm_count,
@@ -325,6 +352,7 @@ struct DecodeRowsArgs {
     // filled in by decode_rows_configure
     uint32_t stages, umma_n, tmem_cols, acc_cols, issuers, producers, x_chunk_blocks, x_slots, pair;
     uint32_t w_stage_bytes;   // round_up(tile_rows * 128, 1024)
+    uint32_t l2_prefetch;     // 1: producers prefetch the tile one ring-depth ahead into L2
     EpilogueParams epi;
     int* status;
     unsigned long long* trace;   // optional [grid][kTraceSlots] of %globaltimer stamps, or null
@@ -334,6 +362,7 @@ constexpr uint32_t kTraceSlots = 8;   // 0 entry, 1 prologue done, 2 first weigh
 uint32_t decode_rows_token_slots(uint32_t rows);  // 8 / 16 / 32 / 64 / 128
 void decode_rows_plan(uint32_t n, int sm_count, uint32_t* tile_rows, uint32_t* tiles_per_cta);
 bool decode_rows_configure(DecodeRowsArgs& args);   // before the activation tensor map is encoded
+uint32_t decode_rows_threads(bool pair);             // threads per CTA of the two residency modes
 cudaError_t launch_decode_rows(const DecodeRowsArgs& args, cudaStream_t stream);
 
 // K3b: skinny stream-K tcgen05 kernel for rows <= 128 (weights are the UMMA M operand).
@@ -350,6 +379,18 @@ struct DecodeTcgen05Args {
 };
 uint32_t decode_token_slots(uint32_t rows);  // 32 / 64 / 128
 cudaError_t launch_decode_tcgen05(const DecodeTcgen05Args& args, int sm_count, cudaStream_t stream);
+
+// Device self-tests (selftest.cu): a wait that expires by design, and div_const against the IEEE divide.
+cudaError_t launch_wait_expiry(int* status, cudaStream_t stream);
+cudaError_t launch_div_const_check(int exponent, uint32_t neighbours, uint32_t samples, unsigned long long* mismatches,
+                                   unsigned long long* checked, int sm_count, cudaStream_t stream);
+
+// Internal tunables (defaults are what ships; changed through the diagnostic entry vxb_tune()).
+struct Tunables {
+    uint32_t decode_pair_share_bytes;   // largest per-CTA weight share the decode kernel runs as two CTAs per SM
+    bool decode_l2_prefetch;            // weight producers ask L2 for the tile one ring-depth ahead
+};
+Tunables& tunables();
 
 // tensor-pipe peak probe: issues `iters` rounds of kind::i8 MMAs on resident
 // shared-memory operands in every CTA; returns through `cycles` the SM clocks

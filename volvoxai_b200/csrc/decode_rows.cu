@@ -180,7 +180,7 @@ decode_rows_kernel(const __grid_constant__ DecodeRowsArgs args) {
     auto tmem_empty = [&](uint32_t b) { return smem_u32(base + lay.bars_off() + (2 * kMaxStages + 2 * kMaxXSlots + 2 + b) * 8); };
     uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(base + lay.misc_off());
     volatile int* abort_flag = reinterpret_cast<volatile int*>(base + lay.misc_off() + 4);
-    volatile int* epi_flag = reinterpret_cast<volatile int*>(base + lay.misc_off() + 8);
+    volatile int* epi_flag = reinterpret_cast<volatile int*>(base + lay.misc_off() + 12);
     float* s_as = reinterpret_cast<float*>(base + lay.misc_off() + 32);
     float* s_ws = reinterpret_cast<float*>(base + lay.consts_off());
     float* s_bias = s_ws + kMaxTile;
@@ -203,7 +203,7 @@ decode_rows_kernel(const __grid_constant__ DecodeRowsArgs args) {
         if (lane == 0) {
             mbar_init(tmem_full(0), args.issuers); mbar_init(tmem_full(1), 1);
             for (uint32_t b = 0; b < 2; b++) mbar_init(tmem_empty(b), 128);
-            *abort_flag = 0;
+            arm_abort(abort_flag, args.status);
             prefetch_tmap(&args.tmap_w);
             prefetch_tmap(&args.tmap_x);
         }
@@ -252,7 +252,14 @@ decode_rows_kernel(const __grid_constant__ DecodeRowsArgs args) {
             while (kb >= num_kb) { kb -= num_kb; channel += (int32_t)args.tile_rows; }
             uint32_t w_sm = w0, fb = f0, eb = e0, stage = 0, phase = 0;
             bool ok = true;
+            // block one ring-depth ahead of the one being copied (stages is a multiple of P, so this
+            // producer owns it too): optionally requested from L2 early, which keeps twice the ring in
+            // flight towards HBM without any shared memory
+            uint32_t pkb = kb + stages; int32_t pchannel = channel;
+            while (pkb >= num_kb) { pkb -= num_kb; pchannel += (int32_t)args.tile_rows; }
             for (uint32_t i = p, u = 0; i < total; i += P, u++) {
+                if (args.l2_prefetch && i + stages < total) tma_prefetch_l2_2d(&args.tmap_w, (int32_t)(pkb * kRK), pchannel);
+                pkb += P; while (pkb >= num_kb) { pkb -= num_kb; pchannel += (int32_t)args.tile_rows; }
                 if (u >= own && !mbar_wait(eb, phase ^ 1u, abort_flag)) { ok = false; break; }
                 mbar_expect_tx(fb, stage_tx);
                 tma_load_2d(w_sm, &args.tmap_w, fb, (int32_t)(kb * kRK), channel);
@@ -598,18 +605,21 @@ cudaError_t launch_t(const DecodeRowsArgs& args, cudaStream_t stream) {
     const RowsLayout lay{args.stages, args.w_stage_bytes, args.x_slots, args.x_chunk_blocks * Cfg::kXAtom,
                          Cfg::kUmmaM, args.umma_n, Cfg::xpose_bytes(args.rows, args.umma_n)};
     const uint32_t smem = lay.total();
-    static uint32_t configured = 0;
-    if (smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(decode_rows_kernel<MT, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-        configured = smem;
-    }
+    cudaError_t e = ensure_dynamic_smem<decode_rows_kernel<MT, PAIR>>(smem);
+    if (e != cudaSuccess) return e;
     const uint32_t per_cta = args.tiles_per_cta * args.tile_rows;
     const uint32_t grid = (args.n + per_cta - 1) / per_cta;
     return launch_pdl(decode_rows_kernel<MT, PAIR>, dim3(grid), dim3(Mode::kThreads), smem, stream, args);
 }
 
 }  // namespace
+
+Tunables& tunables() {
+    static Tunables t{kPairShareBytes, false};
+    return t;
+}
+
+uint32_t decode_rows_threads(bool pair) { return pair ? ModeCfg<true>::kThreads : ModeCfg<false>::kThreads; }
 
 uint32_t decode_rows_token_slots(uint32_t rows) {
     return rows <= 8 ? 8u : rows <= 16 ? 16u : rows <= 32 ? 32u : rows <= 64 ? 64u : 128u;
@@ -645,7 +655,8 @@ void decode_rows_plan(uint32_t n, int sm_count, uint32_t* tile_rows, uint32_t* t
 bool decode_rows_configure(DecodeRowsArgs& args) {
     if (args.rows == 0 || args.rows > 128 || args.n == 0 || args.tile_rows == 0 || args.tile_rows > kMaxTile) return false;
     // small weight shares: two CTAs per SM, so that successive launches overlap (see kPairSmemBytes)
-    const bool pair = (size_t)args.tiles_per_cta * args.tile_rows * args.kpad <= kPairShareBytes;
+    const bool pair = (size_t)args.tiles_per_cta * args.tile_rows * args.kpad <= tunables().decode_pair_share_bytes;
+    args.l2_prefetch = tunables().decode_l2_prefetch ? 1u : 0u;
     VXB_DECODE_DISPATCH(configure_t, args);
 }
 

@@ -48,7 +48,7 @@ template <uint32_t MT> struct DecodeCfg {
     static constexpr uint32_t kNumBars = 2 * kStages + 4;
     static constexpr uint32_t kOffTmemPtr = kOffBars + kNumBars * 8;
     static constexpr uint32_t kOffAbort = kOffTmemPtr + 4;
-    static constexpr uint32_t kOffFlag = kOffAbort + 4;       // epilogue-uniform decisions (4 ints)
+    static constexpr uint32_t kOffFlag = kOffAbort + 8;       // epilogue-uniform decisions (4 ints)
     static constexpr uint32_t kOffScales = kOffFlag + 16;     // float[MT] activation scales
     static constexpr uint32_t kSmemBytes = kOffScales + MT * 4 + 1024;
 };
@@ -97,7 +97,7 @@ decode_i8_tcgen05_kernel(const __grid_constant__ DecodeTcgen05Args args) {
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < Cfg::kStages; s++) { mbar_init(full(s), 1); mbar_init(empty(s), 1); }
         for (uint32_t b = 0; b < 2; b++) { mbar_init(tmem_full(b), 1); mbar_init(tmem_empty(b), 128); }
-        *abort_flag = 0;
+        arm_abort(abort_flag, args.status);
         fence_barrier_init();
         prefetch_tmap(&args.tmap_w);
         prefetch_tmap(&args.tmap_x);
@@ -326,13 +326,8 @@ decode_i8_tcgen05_kernel(const __grid_constant__ DecodeTcgen05Args args) {
 template <uint32_t MT>
 cudaError_t launch_t(const DecodeTcgen05Args& args, int sm_count, cudaStream_t stream) {
     using Cfg = DecodeCfg<MT>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(decode_i8_tcgen05_kernel<MT>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::kSmemBytes);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
+    cudaError_t e = ensure_dynamic_smem<decode_i8_tcgen05_kernel<MT>>(Cfg::kSmemBytes);
+    if (e != cudaSuccess) return e;
     const uint64_t units = (uint64_t)((args.n + kDM - 1) / kDM) * (args.kpad / kDK);
     const uint32_t grid = units < (uint64_t)sm_count ? (uint32_t)units : (uint32_t)sm_count;
     // This launch may begin (prologue, weight prefetch) while the kernel before it in the
@@ -479,9 +474,12 @@ extern "C" int vxb_decode_linear_f32_noalloc(const int8_t* q, const float* row_s
     cudaStream_t s = (cudaStream_t)stream;
 
     // The array keeps whatever the previous call left: counters and the part of the workspace
-    // this call will use must start at zero (a memset node, not an allocation).
-    const size_t used = kNoAllocStatusBytes + kNoAllocCounterBytes + (size_t)rows * d_out * 4;
-    e = cudaMemsetAsync(scratch, 0, used, s);
+    // this call will use must start at zero (a memset node, not an allocation). The status block
+    // in front of them is NOT cleared here: a word raised by an expired wait stays up until a
+    // call with wait != 0 has reported it, so that a call enqueued with wait == 0 (or a graph
+    // replay) cannot wipe the evidence of its predecessor's failure.
+    const size_t used = kNoAllocCounterBytes + (size_t)rows * d_out * 4;
+    e = cudaMemsetAsync(scratch + kNoAllocStatusBytes, 0, used, s);
     if (e != cudaSuccess) return noalloc_fail(-1, "cudaMemsetAsync(scratch)", e);
 
     vxb::DecodeTcgen05Args a;
@@ -503,7 +501,14 @@ extern "C" int vxb_decode_linear_f32_noalloc(const int8_t* q, const float* row_s
         e = cudaMemcpyAsync(&host_status, status, sizeof(int), cudaMemcpyDeviceToHost, s);
         if (e == cudaSuccess) e = cudaStreamSynchronize(s);
         if (e != cudaSuccess) return noalloc_fail(-1, "waiting for the result", e);
-        if (host_status != 0) return noalloc_fail(-1, "a bounded device wait expired; the output is invalid");
+        if (host_status != 0) {
+            // reported once: lower the word and clear everything an aborted launch may have left
+            cudaMemsetAsync(scratch, 0, sizeof(int), s);
+            cudaMemsetAsync(scratch + kNoAllocStatusBytes, 0, kNoAllocBytes - kNoAllocStatusBytes, s);
+            cudaStreamSynchronize(s);
+            return noalloc_fail(-1, "a bounded device wait expired in this call or in an earlier call made with "
+                                    "wait == 0; outputs since the last waited call are invalid");
+        }
     }
     return 1;
 }

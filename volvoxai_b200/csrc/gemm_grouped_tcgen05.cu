@@ -49,7 +49,7 @@ constexpr uint32_t kOffBars = kOffStore + kEpiWarps * kStoreBytes;
 constexpr uint32_t kNumBars = 2 * kStages + 2 * kAccBufs;
 constexpr uint32_t kOffTmemPtr = kOffBars + kNumBars * 8;
 constexpr uint32_t kOffAbort = kOffTmemPtr + 4;
-constexpr uint32_t kSmemBytes = kOffAbort + 4 + 1024;
+constexpr uint32_t kSmemBytes = kOffAbort + 8 + 1024;
 
 struct Smem {
     uint8_t* base;
@@ -109,7 +109,7 @@ gemm_i8_grouped_tcgen05_kernel(const __grid_constant__ GemmGroupedArgs args) {
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < kStages; s++) { mbar_init(sm.full(s), 1); mbar_init(sm.empty(s), 1); }
         for (uint32_t b = 0; b < kAccBufs; b++) { mbar_init(sm.tmem_full(b), 1); mbar_init(sm.tmem_empty(b), kEpiWarps); }
-        *abort_flag = 0;
+        arm_abort(abort_flag, args.status);
         fence_barrier_init();
         prefetch_tmap(&args.tmap_a);
         prefetch_tmap(&args.tmap_b);

@@ -61,7 +61,7 @@ constexpr uint32_t kOffBars = kOffStore + kEpiWarps * kStoreBytes;
 constexpr uint32_t kNumBars = 2 * kStages + 4;
 constexpr uint32_t kOffTmemPtr = kOffBars + kNumBars * 8;
 constexpr uint32_t kOffAbort = kOffTmemPtr + 4;
-constexpr uint32_t kSmemBytes = kOffAbort + 4 + 1024;
+constexpr uint32_t kSmemBytes = kOffAbort + 8 + 1024;
 
 // ---- cluster-scope PTX ----------------------------------------------------------------------
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -171,7 +171,7 @@ gemm_i8_pair_kernel(const __grid_constant__ GemmTcgen05Args args) {
         for (uint32_t s = 0; s < kStages; s++) { mbar_init(sm.full(s), 1); mbar_init(sm.empty(s), 1); }
         // accumulator-empty: one arrival per epilogue warp of both CTAs (only the leader's is waited on)
         for (uint32_t b = 0; b < 2; b++) { mbar_init(sm.tmem_full(b), 1); mbar_init(sm.tmem_empty(b), 2 * kEpiWarps); }
-        *abort_flag = 0;
+        arm_abort(abort_flag, args.status);
         fence_barrier_init();
         prefetch_tmap(&args.tmap_a);
         prefetch_tmap(&args.tmap_b);

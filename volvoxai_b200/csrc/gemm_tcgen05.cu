@@ -58,7 +58,7 @@ constexpr uint32_t kOffBars = kOffStore + kEpiWarps * kStoreBytes;   // 8-byte b
 constexpr uint32_t kNumBars = 2 * kStages + 4;
 constexpr uint32_t kOffTmemPtr = kOffBars + kNumBars * 8;
 constexpr uint32_t kOffAbort = kOffTmemPtr + 4;
-constexpr uint32_t kSmemBytes = kOffAbort + 4 + 1024;        // + alignment slack
+constexpr uint32_t kSmemBytes = kOffAbort + 8 + 1024;        // + alignment slack
 
 struct Smem {
     uint8_t* base;
@@ -94,7 +94,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ GemmTcgen05Args args) {
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < kStages; s++) { mbar_init(sm.full(s), 1); mbar_init(sm.empty(s), 1); }
         for (uint32_t b = 0; b < 2; b++) { mbar_init(sm.tmem_full(b), 1); mbar_init(sm.tmem_empty(b), kEpiThreads); }
-        *abort_flag = 0;
+        arm_abort(abort_flag, args.status);
         fence_barrier_init();
         prefetch_tmap(&args.tmap_a);
         prefetch_tmap(&args.tmap_b);
@@ -450,11 +450,11 @@ i8_peak_probe_kernel(uint32_t iters, long long* cycles, int* status, uint32_t id
     uint8_t* base = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     __shared__ uint64_t bar;
     __shared__ uint32_t tmem_ptr;
-    __shared__ int abort_flag;
+    __shared__ int abort_flag[2];
     const uint32_t warp = threadIdx.x >> 5;
     for (uint32_t i = threadIdx.x; i < kStageBytes / 4; i += blockDim.x)
         reinterpret_cast<uint32_t*>(base)[i] = 0x01010101u;
-    if (threadIdx.x == 0) { mbar_init(smem_u32(&bar), 1); abort_flag = 0; fence_barrier_init(); }
+    if (threadIdx.x == 0) { mbar_init(smem_u32(&bar), 1); arm_abort(abort_flag, status); fence_barrier_init(); }
     fence_proxy_async();
     if (warp == 0) { tmem_alloc(smem_u32(&tmem_ptr), kTmemCols); tmem_relinquish(); }
     tc_fence_before();
@@ -480,7 +480,7 @@ i8_peak_probe_kernel(uint32_t iters, long long* cycles, int* status, uint32_t id
                 umma_i8(my_tmem + (j & (accs - 1u)) * acc_stride, make_smem_desc(a_addr + (j & 3u) * kUmmaK),
                         make_smem_desc(b_addr + (j & 3u) * kUmmaK), idesc, 1u);
             umma_commit(my_bar);
-            ok = mbar_wait(my_bar, parity, &abort_flag);
+            ok = mbar_wait(my_bar, parity, abort_flag);
             parity ^= 1u;
         }
         if (warp == 0) cycles[blockIdx.x] = clock64() - t0;

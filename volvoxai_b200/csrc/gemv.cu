@@ -107,26 +107,11 @@ template <int MR, int CH>
 cudaError_t launch_gemv_t(const int8_t* q, uint32_t rows, const int8_t* w, uint32_t n,
                           uint32_t kpad, const EpilogueParams& epi, int sm_count,
                           cudaStream_t stream) {
-    // K chunk: whole K when MR*kpad fits the budget, else the largest multiple of 512 that does.
-    uint32_t kchunk = kpad;
-    if ((uint64_t)MR * kpad > kGemvSmemBytes) kchunk = (kGemvSmemBytes / MR) / 512 * 512;
-    const uint32_t smem = MR * kchunk;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_dp4a_kernel<MR, CH>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)kGemvSmemBytes);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
-    constexpr uint32_t kChannelsPerCta = kGemvWarps * CH;
-    const uint32_t blocks = (n + kChannelsPerCta - 1) / kChannelsPerCta;
-    uint32_t per_sm = smem ? (200u * 1024u) / (smem + 1024u) : 8u;
-    if (per_sm > 8) per_sm = 8;
-    if (per_sm < 1) per_sm = 1;
-    uint32_t grid = (uint32_t)sm_count * per_sm;
-    if (grid > blocks) grid = blocks;
-    gemv_dp4a_kernel<MR, CH><<<grid, kGemvThreads, smem, stream>>>(q, rows, w, n, kpad, kchunk, epi);
+    const GemvShape shape = gemv_shape(0, rows, n, kpad, sm_count);
+    if (shape.mr != (uint32_t)MR || shape.ch != (uint32_t)CH) return cudaErrorInvalidValue;
+    cudaError_t e = ensure_dynamic_smem<gemv_dp4a_kernel<MR, CH>>(kGemvSmemBytes);
+    if (e != cudaSuccess) return e;
+    gemv_dp4a_kernel<MR, CH><<<shape.grid, kGemvThreads, shape.smem, stream>>>(q, rows, w, n, kpad, shape.kchunk, epi);
     return cudaGetLastError();
 }
 
@@ -308,24 +293,11 @@ gemv_grouped_kernel(const int8_t* __restrict__ q, uint32_t rows, const int8_t* _
 template <int MR, int CH, int G>
 cudaError_t launch_gemv_grouped_t(const int8_t* q, uint32_t rows, const int8_t* w, uint32_t n, uint32_t kpad,
                                   const EpilogueParams& epi, int sm_count, cudaStream_t stream) {
-    uint32_t kchunk = (kpad + 511u) / 512u * 512u;
-    if ((uint64_t)MR * kchunk > kGemvSmemBytes) kchunk = (kGemvSmemBytes / MR) / 512 * 512;
-    const uint32_t smem = MR * kchunk;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_grouped_kernel<MR, CH, G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)kGemvSmemBytes);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
-    constexpr uint32_t kChannelsPerCta = kGemvWarps * CH;
-    const uint32_t blocks = (n + kChannelsPerCta - 1) / kChannelsPerCta;
-    uint32_t per_sm = (200u * 1024u) / (smem + 1024u);
-    if (per_sm > 8) per_sm = 8;
-    if (per_sm < 1) per_sm = 1;
-    uint32_t grid = (uint32_t)sm_count * per_sm;
-    if (grid > blocks) grid = blocks;
-    gemv_grouped_kernel<MR, CH, G><<<grid, kGemvThreads, smem, stream>>>(q, rows, w, n, kpad, kchunk, epi);
+    const GemvShape shape = gemv_shape(1, rows, n, kpad, sm_count);
+    if (shape.mr != (uint32_t)MR || shape.ch != (uint32_t)CH) return cudaErrorInvalidValue;
+    cudaError_t e = ensure_dynamic_smem<gemv_grouped_kernel<MR, CH, G>>(kGemvSmemBytes);
+    if (e != cudaSuccess) return e;
+    gemv_grouped_kernel<MR, CH, G><<<shape.grid, kGemvThreads, shape.smem, stream>>>(q, rows, w, n, kpad, shape.kchunk, epi);
     return cudaGetLastError();
 }
 
@@ -463,24 +435,11 @@ gemv_w4_grouped_kernel(const int8_t* __restrict__ q, uint32_t rows, const uint32
 template <int MR, int CH, int G>
 cudaError_t launch_gemv_w4_t(const int8_t* q, uint32_t rows, const uint32_t* w4, uint32_t row_words, uint32_t n,
                              uint32_t kpad, const EpilogueParams& epi, int sm_count, cudaStream_t stream) {
-    uint32_t kchunk = (kpad + 1023u) / 1024u * 1024u;
-    if ((uint64_t)MR * kchunk > kGemvSmemBytes) kchunk = (kGemvSmemBytes / MR) / 1024 * 1024;
-    const uint32_t smem = MR * kchunk;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_w4_grouped_kernel<MR, CH, G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)kGemvSmemBytes);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
-    constexpr uint32_t kChannelsPerCta = kGemvWarps * CH;
-    const uint32_t blocks = (n + kChannelsPerCta - 1) / kChannelsPerCta;
-    uint32_t per_sm = (200u * 1024u) / (smem + 1024u);
-    if (per_sm > 8) per_sm = 8;
-    if (per_sm < 1) per_sm = 1;
-    uint32_t grid = (uint32_t)sm_count * per_sm;
-    if (grid > blocks) grid = blocks;
-    gemv_w4_grouped_kernel<MR, CH, G><<<grid, kGemvThreads, smem, stream>>>(q, rows, w4, row_words, n, kpad, kchunk, epi);
+    const GemvShape shape = gemv_shape(2, rows, n, kpad, sm_count);
+    if (shape.mr != (uint32_t)MR || shape.ch != (uint32_t)CH) return cudaErrorInvalidValue;
+    cudaError_t e = ensure_dynamic_smem<gemv_w4_grouped_kernel<MR, CH, G>>(kGemvSmemBytes);
+    if (e != cudaSuccess) return e;
+    gemv_w4_grouped_kernel<MR, CH, G><<<shape.grid, kGemvThreads, shape.smem, stream>>>(q, rows, w4, row_words, n, kpad, shape.kchunk, epi);
     return cudaGetLastError();
 }
 
@@ -492,6 +451,35 @@ cudaError_t launch_gemv_w4_g(const int8_t* q, uint32_t rows, const uint32_t* w4,
 }
 
 }  // namespace
+
+GemvShape gemv_shape(int kind, uint32_t rows, uint32_t n, uint32_t kpad, int sm_count) {
+    GemvShape s{};
+    // rows per CTA pass (compile-time MR) and channels per warp (CH)
+    if (kind == 0) {
+        s.mr = rows <= 1 ? 1 : rows <= 2 ? 2 : rows <= 4 ? 4 : rows <= 8 ? 8 : rows <= 16 ? 16 : 32;
+        s.ch = s.mr <= 4 ? 4 : s.mr <= 16 ? 2 : 1;
+    } else if (kind == 1) {
+        s.mr = rows <= 1 ? 1 : rows <= 2 ? 2 : 4;
+        s.ch = s.mr <= 2 ? 4 : 2;
+    } else {
+        s.mr = rows <= 1 ? 1 : 2;
+        s.ch = 4;
+    }
+    // K chunk staged in shared memory: whole (rounded) K when mr * K fits the budget, else the
+    // largest multiple of the kernel's step that does
+    const uint32_t step = kind == 2 ? 1024u : 512u;
+    s.kchunk = kind == 0 ? kpad : (kpad + step - 1) / step * step;
+    if ((uint64_t)s.mr * s.kchunk > kGemvSmemBytes) s.kchunk = (kGemvSmemBytes / s.mr) / step * step;
+    s.smem = s.mr * s.kchunk;
+    const uint32_t per_cta = (uint32_t)kGemvWarps * s.ch;
+    const uint32_t blocks = (n + per_cta - 1) / per_cta;
+    uint32_t per_sm = s.smem ? (200u * 1024u) / (s.smem + 1024u) : 8u;
+    if (per_sm > 8) per_sm = 8;
+    if (per_sm < 1) per_sm = 1;
+    s.grid = (uint32_t)sm_count * per_sm;
+    if (s.grid > blocks) s.grid = blocks;
+    return s;
+}
 
 cudaError_t launch_gemm_grouped(const int8_t* q, uint32_t rows, const int8_t* w, uint32_t n, uint32_t kpad,
                                 const EpilogueParams& epi, cudaStream_t stream) {

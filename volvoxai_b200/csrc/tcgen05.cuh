@@ -8,7 +8,10 @@
 namespace vxb {
 namespace tc {
 
-constexpr long long kWaitLimitCycles = 4000000000LL;  // ~2 s at 1.9 GHz
+// Bounded waits: the shared-memory word after a kernel's abort flag holds the wait limit in units
+// of 1024 SM clocks; arm_abort() copies it from the second word of the context's status block
+// (0 there = the default, about 2 s at 1.9 GHz).
+constexpr int kDefaultWaitLimitKcycles = 3906250;
 constexpr uint32_t kUmmaK = 32;                       // K per kind::i8 instruction
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -32,6 +35,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
+// abort_flag[0] = 0 (nobody gave up yet), abort_flag[1] = this launch's wait limit. Called by one
+// thread before the barrier that publishes the kernel's shared-memory set-up. `status` is the
+// context's status block (word 0 raised on expiry, word 1 the configured limit) or null.
+__device__ __forceinline__ void arm_abort(volatile int* abort_flag, const int* status) {
+    abort_flag[0] = 0;
+    int limit = status ? status[1] : 0;
+    abort_flag[1] = limit > 0 ? limit : kDefaultWaitLimitKcycles;
+}
 // Bounded wait: false when the limit expired or another role already gave up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -39,8 +50,8 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
         if ((++spins & 63u) == 0u) {
-            if (*abort_flag) return false;
-            if (clock64() - t0 > kWaitLimitCycles) { *abort_flag = 1; return false; }
+            if (abort_flag[0]) return false;
+            if (clock64() - t0 > ((long long)abort_flag[1] << 10)) { abort_flag[0] = 1; return false; }
         }
     }
     return true;
@@ -64,6 +75,12 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
         "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes "
         "[%0], [%1, {%3, %4, %5}], [%2];"
         ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+// Ask L2 for a tile ahead of the copy that will bring it into shared memory (no barrier, no
+// shared-memory destination).
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* map, int32_t c0, int32_t c1) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
+                 ::"l"(map), "r"(c0), "r"(c1) : "memory");
 }
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");

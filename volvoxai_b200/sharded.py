@@ -120,7 +120,9 @@ class FusedGatherLinear:
     of all `world` buffers, with plain stores over NVLink while the MMAs of later tiles run.
     No NCCL collective moves data; a one-element all-reduce after the kernel is the only
     cross-GPU synchronisation (stream-ordered: when it has completed on a rank, every rank's
-    kernel, and with it every store into this rank's buffer, has completed).
+    kernel, and with it every store into this rank's buffer, has completed).  forward() therefore
+    moves the context onto torch's current stream of the device before it launches: the
+    all-reduce is queued there, and it only orders what runs on the same stream.
 
     Two buffers alternate between steps, so that a rank that is still reading step k's
     output is never overwritten by a faster peer's step k+1: a peer reaches step k+2, which
@@ -173,6 +175,9 @@ class FusedGatherLinear:
             raise ValueError("row count differs from the mapped buffers")
         b = self._step % self.DEPTH
         self._step += 1
+        # the kernel must run on the stream torch will queue the ordering all-reduce on, otherwise
+        # that barrier could complete before this rank's peer stores do
+        self.ctx.set_stream(torch.cuda.current_stream(self.ctx.device).cuda_stream)
         if self.hi > self.lo:
             off = self.lo
             peers = (C.c_void_p * max(1, len(self._peers[b])))(*[p + off for p in self._peers[b]])

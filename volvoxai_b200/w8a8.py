@@ -23,7 +23,7 @@ from ._lib import (DT_I8, DT_U8, OP_PACKED_LINEAR, ROUTE_AUTO, ROUTE_DECODE, ROU
                    ROUTE_GEMV, ROUTE_SIMT,
                    ROUTE_TCGEN05, LLMOpArgs, last_error, last_route)
 
-__all__ = ["Context", "Weight", "W8A8Error", "qlinear_i8u8", "packed_linear",
+__all__ = ["Context", "Weight", "W8A8Error", "variants", "plan", "registry_rows", "qlinear_i8u8", "packed_linear",
            "packed_linear_decode", "host_cache_clear", "launch_count", "last_error",
            "quantize_typed_f32_i8u8", "dequantize_typed_i8u8_f32", "requantize_linear_i8u8", "last_route", "ROUTE_AUTO", "ROUTE_GEMV", "ROUTE_TCGEN05", "ROUTE_SIMT", "ROUTE_DECODE", "ROUTE_DECODE_STREAMK", "ROUTE_TCGEN05_PAIR",
            "DT_I8", "DT_U8"]
@@ -54,6 +54,57 @@ def launch_count() -> int:
     return int(_lib.load().vxb_launch_count())
 
 
+def variants() -> list[dict]:
+    """The kernel variant table (include/vxb200_plan.h) as dictionaries."""
+    L = _lib.load()
+    out = []
+    for i in range(L.vxb_variant_count()):
+        v = L.vxb_variant_info(i).contents
+        row = {name: getattr(v, name) for name, _ in _lib.Variant._fields_}
+        for key in ("id", "route_label", "kernel"):
+            row[key] = row[key].decode()
+        out.append(row)
+    return out
+
+
+def plan(rows: int, k: int, n: int, *, weight_kind: int = _lib.WEIGHT_PER_CHANNEL, group_size: int = 0,
+         epilogue: int = _lib.EPI_F32, route: int = ROUTE_AUTO, n_peers: int = 0, fused_tail: bool = False,
+         fp32_input: bool = True, sm_count: int = 148, pair_clusters: int = 74):
+    """vxb_plan(): the launch plan of one call (a dict with the variant's id added) or
+    (None, reason) when it is refused.  Needs no GPU."""
+    L = _lib.load()
+    q = _lib.PlanQuery(rows, k, n, weight_kind, group_size, epilogue, route, n_peers, 1 if fused_tail else 0,
+                       1 if fp32_input else 0, sm_count, pair_clusters)
+    out = _lib.LaunchPlan()
+    why = C.create_string_buffer(200)
+    if L.vxb_plan(C.byref(q), C.byref(out), why, len(why)) != 1:
+        return None, why.value.decode()
+    d = {name: getattr(out, name) for name, _ in _lib.LaunchPlan._fields_}
+    d["id"] = L.vxb_variant_info(out.variant).contents.id.decode()
+    return d, ""
+
+
+def registry_rows() -> list[str]:
+    """One kernel-registry row per variant, in the reference's KernelVariant field order."""
+    L = _lib.load()
+    rows = []
+    for i in range(L.vxb_variant_count()):
+        buf = C.create_string_buffer(512)
+        if L.vxb_registry_row(i, buf, len(buf)):
+            rows.append(buf.value.decode())
+    return rows
+
+
+def inject_failure(kind: int, countdown: int) -> None:
+    """Host-side failure injection (diag.h): refuse the countdown-th launch (kind 1) or scratch
+    allocation (kind 2) from now; countdown 0 disarms."""
+    _lib.load().vxb_inject_failure(kind, countdown)
+
+
+def tune(name: str, value: int) -> bool:
+    return _lib.load().vxb_tune(name.encode(), int(value)) == 1
+
+
 class Context:
     """Device + stream + reusable scratch (one per thread of use)."""
 
@@ -73,6 +124,21 @@ class Context:
 
     def synchronize(self) -> None:
         _check(self._L.vxb_context_synchronize(self.handle))
+
+    def set_wait_limit(self, cycles: int) -> None:
+        """Limit of every bounded device wait, in SM clocks (0 = the default, about 2 s)."""
+        _check(self._L.vxb_context_set_wait_limit(self.handle, int(cycles)))
+
+    def selftest_wait_expiry(self) -> None:
+        """Launches the kernel whose only wait runs out by design (diag.h)."""
+        _check(self._L.vxb_selftest_wait_expiry(self.handle))
+
+    def selftest_div_const(self, exponent: int, neighbours: int = 2, samples: int = 64):
+        """(mismatches, divisions checked) of div_const against the IEEE divide over every divisor
+        significand at the given exponent."""
+        bad, done = C.c_uint64(0), C.c_uint64(0)
+        _check(self._L.vxb_selftest_div_const(self.handle, exponent, neighbours, samples, C.byref(bad), C.byref(done)))
+        return bad.value, done.value
 
     def measure_i8_tensor_peak(self, iters: int = 200) -> float:
         out = C.c_double(0.0)
