@@ -25,8 +25,10 @@ def test_library_exports_every_declared_symbol():
     names = declared_symbols("include", "vxb200_w8a8.h")
     assert len(names) >= 20
     plan = declared_symbols("include", "vxb200_plan.h")
+    package = declared_symbols("include", "vxb200_package.h")
+    assert sorted(_lib.PACKAGE_EXPORTS) == package
     diag = declared_symbols("volvoxai_b200", "csrc", "diag.h")
-    for n in names + plan + diag:
+    for n in names + plan + package + diag:
         assert hasattr(L, n), n
     assert sorted(_lib.EXPORTS) == names
     assert sorted(_lib.PLAN_EXPORTS) == plan

@@ -34,6 +34,12 @@ EXPORTS = [
 
 # include/vxb200_plan.h: variant table, launch planning, registry rows (no GPU needed).
 PLAN_EXPORTS = ["vxb_variant_count", "vxb_variant_info", "vxb_plan", "vxb_registry_row"]
+# include/vxb200_package.h: graph.json + SafeTensors loader and the device-resident forward pass.
+PACKAGE_EXPORTS = ["vxb_package_open", "vxb_package_close", "vxb_package_node_count", "vxb_package_node_op",
+                   "vxb_package_io_count", "vxb_package_io_name", "vxb_package_io_dtype", "vxb_package_io_rank",
+                   "vxb_package_io_dim", "vxb_package_io_bytes", "vxb_program_compile", "vxb_program_destroy",
+                   "vxb_program_device_bytes", "vxb_program_route_evidence", "vxb_program_execute"]
+DT_F32, DT_I32 = 18, 16
 # volvoxai_b200/csrc/diag.h: diagnostics and self-tests, not part of the drop-in boundary.
 DIAG_EXPORTS = ["vxb_context_trace", "vxb_measure_mma_issue", "vxb_context_set_wait_limit",
                 "vxb_selftest_wait_expiry", "vxb_selftest_div_const", "vxb_inject_failure", "vxb_tune"]
@@ -133,6 +139,32 @@ def load() -> C.CDLL:
     L.vxb_inject_failure.argtypes = [C.c_int, u32]
     L.vxb_inject_failure.restype = None
     L.vxb_tune.argtypes = [C.c_char_p, C.c_int64]
+    L.vxb_package_open.argtypes = [C.c_char_p, C.POINTER(C.c_char_p), C.c_size_t, C.POINTER(vp)]
+    L.vxb_package_close.argtypes = [vp]
+    L.vxb_package_close.restype = None
+    L.vxb_package_node_count.argtypes = [vp]
+    L.vxb_package_node_count.restype = u32
+    L.vxb_package_node_op.argtypes = [vp, u32]
+    L.vxb_package_node_op.restype = C.c_char_p
+    L.vxb_package_io_count.argtypes = [vp, C.c_int]
+    L.vxb_package_io_count.restype = u32
+    L.vxb_package_io_name.argtypes = [vp, C.c_int, u32]
+    L.vxb_package_io_name.restype = C.c_char_p
+    for name in ("vxb_package_io_dtype", "vxb_package_io_rank"):
+        getattr(L, name).argtypes = [vp, C.c_int, u32]
+        getattr(L, name).restype = u32
+    L.vxb_package_io_dim.argtypes = [vp, C.c_int, u32, u32]
+    L.vxb_package_io_dim.restype = C.c_int64
+    L.vxb_package_io_bytes.argtypes = [vp, C.c_int, u32]
+    L.vxb_package_io_bytes.restype = C.c_uint64
+    L.vxb_program_compile.argtypes = [vp, vp, C.POINTER(vp)]
+    L.vxb_program_destroy.argtypes = [vp]
+    L.vxb_program_destroy.restype = None
+    L.vxb_program_device_bytes.argtypes = [vp]
+    L.vxb_program_device_bytes.restype = C.c_uint64
+    L.vxb_program_route_evidence.argtypes = [vp]
+    L.vxb_program_route_evidence.restype = C.c_char_p
+    L.vxb_program_execute.argtypes = [vp, C.POINTER(vp), C.POINTER(C.c_size_t), u32, C.POINTER(vp), C.POINTER(C.c_size_t), u32]
     L.vxb_variant_count.restype = u32
     L.vxb_variant_info.argtypes = [u32]
     L.vxb_variant_info.restype = C.POINTER(Variant)

@@ -17,8 +17,8 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 ROOT = os.path.dirname(PKG)
 LIB = os.path.join(PKG, "libvxb200.so")
-SOURCES = ["api.cu", "plan.cu", "selftest.cu", "quantize.cu", "gemv.cu", "gemm_tcgen05.cu", "gemm_pair_tcgen05.cu", "gemm_grouped_tcgen05.cu", "decode_tcgen05.cu", "decode_rows.cu", "boundary_ops.cu"]
-HEADERS = [os.path.join(CSRC, "common.cuh"), os.path.join(CSRC, "tcgen05.cuh"), os.path.join(CSRC, "diag.h"), os.path.join(ROOT, "include", "vxb200_w8a8.h"), os.path.join(ROOT, "include", "vxb200_plan.h")]
+SOURCES = ["api.cu", "plan.cu", "package.cu", "selftest.cu", "quantize.cu", "gemv.cu", "gemm_tcgen05.cu", "gemm_pair_tcgen05.cu", "gemm_grouped_tcgen05.cu", "decode_tcgen05.cu", "decode_rows.cu", "boundary_ops.cu"]
+HEADERS = [os.path.join(CSRC, "common.cuh"), os.path.join(CSRC, "tcgen05.cuh"), os.path.join(CSRC, "diag.h"), os.path.join(ROOT, "include", "vxb200_w8a8.h"), os.path.join(ROOT, "include", "vxb200_plan.h"), os.path.join(ROOT, "include", "vxb200_package.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -56,6 +56,37 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+PROVIDER_LIB = os.path.join(PKG, "libvxb200_provider.so")
+PROVIDER_SRC = os.path.join(PKG, "provider", "vxb200_provider.c")
+
+
+def reference_include() -> str | None:
+    """Where the reference's public headers lie: $VX_REFERENCE/native/include, else a checkout named
+    `reference` beside this repository; None when neither exists."""
+    root = os.environ.get("VX_REFERENCE") or os.path.join(os.path.dirname(ROOT), "reference")
+    inc = os.path.join(root, "native", "include")
+    return inc if os.path.exists(os.path.join(inc, "volvoxai_backend.h")) else None
+
+
+def build_provider(force: bool = False) -> str | None:
+    """Builds libvxb200_provider.so (the VxBackendProvider of this route) against the reference's own
+    header.  Needs the reference checkout; returns None (and keeps any prebuilt library) without it."""
+    inc = reference_include()
+    if inc is None:
+        return PROVIDER_LIB if os.path.exists(PROVIDER_LIB) else None
+    deps = [PROVIDER_SRC, os.path.join(ROOT, "include", "vxb200_package.h"), os.path.join(inc, "volvoxai_backend.h")]
+    if not force and os.path.exists(PROVIDER_LIB) and all(os.path.getmtime(d) <= os.path.getmtime(PROVIDER_LIB) for d in deps):
+        return PROVIDER_LIB
+    cmd = ["gcc", "-std=gnu11", "-O2", "-fPIC", "-shared", "-fvisibility=hidden", "-I", inc, "-o", PROVIDER_LIB, PROVIDER_SRC,
+           "-L", PKG, "-l:libvxb200.so", "-Wl,-rpath,$ORIGIN"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        sys.stderr.write(res.stdout + res.stderr)
+        raise RuntimeError("gcc failed building libvxb200_provider.so")
+    return PROVIDER_LIB
+
+
 if __name__ == "__main__":
     build(force="--force" in sys.argv, verbose="-v" in sys.argv or "--force" in sys.argv)
     print(LIB)
+    print(build_provider(force="--force" in sys.argv))

@@ -28,6 +28,18 @@ int fail(int code, const char* fmt, ...) {
     va_end(ap);
     return code;
 }
+}  // namespace
+
+// Sets the calling thread's error text from another translation unit of the library.
+int vxb::set_error(int code, const char* fmt, ...) {
+    va_list ap; va_start(ap, fmt);
+    vsnprintf(g_error, sizeof g_error, fmt, ap);
+    va_end(ap);
+    return code;
+}
+void vxb::set_route(const char* text) { snprintf(g_route, sizeof g_route, "%s", text); }
+
+namespace {
 #define CUDA_TRY(expr, code)                                                              \
     do { cudaError_t e__ = (expr);                                                        \
          if (e__ != cudaSuccess) return fail((code), "%s: %s", #expr, cudaGetErrorString(e__)); \
@@ -150,6 +162,8 @@ struct VxbWeight {
     uint32_t* w4 = nullptr;      // W4 storage kept as words [d_out, w4_row_words] for the one/two-row decode kernel
     uint32_t w4_row_words = 0;   // multiple of 4, * 8 >= kpad; codes past d_in are 8 (weight 0)
 };
+
+cudaStream_t vxb::context_stream(const VxbContext* ctx) { return ctx->stream; }
 
 namespace {
 

@@ -244,6 +244,14 @@ __device__ __forceinline__ void epi_store(const EpilogueParams& p, uint32_t row,
     }
 }
 
+// Thread-local error / route text of the C ABI (defined beside vxb_last_error); returns `code`.
+int set_error(int code, const char* fmt, ...);
+void set_route(const char* text);
+}  // namespace vxb
+struct VxbContext;
+namespace vxb {
+cudaStream_t context_stream(const VxbContext* ctx);   // the stream a context queues its work on
+
 // ---- launchers implemented in the .cu files -------------------------------
 
 // Boundary ops of a static W8A8 island (boundary_ops.cu): byte outputs are int8 or uint8.
