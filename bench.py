@@ -437,6 +437,76 @@ def widened_rows(torch, ctx, w8a8, peaks, replays=10):
     return out
 
 
+def gemm_sweep(torch, ctx, w8a8, peaks, i8_probe, steps=5):
+    """All twelve shapes of the compute-bound sweep (M in 2048..16384 x three (K, N) pairs), requantizing
+    epilogue, one GPU: step time (quantizer + GEMM, inputs resident in HBM, CUDA events) and the GEMM
+    kernel's own time (event pairs inside the library), as TOPS and as fractions of the resident-operand
+    kind::i8 probe and of 2 x the measured bf16 rate.  Weights are drawn on the device (N(0, 30)-shaped
+    codes clamped to +-127): the timing does not depend on their values."""
+    out = []
+    peak2 = 2.0 * peaks["bf16_tflops"]
+    for (k, n) in wl.GEMM_SHAPES:
+        gen = torch.Generator(device="cuda").manual_seed(k + n)
+        codes = torch.randn((n, k), device="cuda", generator=gen).mul_(30.0).round_().clamp_(-127, 127).to(torch.int8)
+        ws = np.full(n, 0.02 * 4.2 / 127.0, np.float32)
+        weight = w8a8.Weight.from_i8(ctx, codes.cpu().numpy(), ws)
+        del codes
+        for m in wl.GEMM_ROWS:
+            x = torch.randn((m, k), device="cuda", generator=gen)
+            y = torch.empty((m, n), dtype=torch.int8, device="cuda")
+            for _ in range(3):
+                ctx.linear_i8(weight, x, 0.05, 0, out=y)
+            torch.cuda.synchronize()
+            ctx.profile(True)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                ctx.linear_i8(weight, x, 0.05, 0, out=y)
+            e1.record()
+            e1.synchronize()
+            prof = ctx.profile_read()
+            ctx.profile(False)
+            step_ms, kern_ms = e0.elapsed_time(e1) / steps, prof["gemm_ms"] / steps
+            ops = 2.0 * m * k * n
+            out.append({"rows": m, "k": k, "n": n, "route": w8a8.last_route(), "step_ms": step_ms, "kernel_ms": kern_ms,
+                        "step_tops": ops / step_ms / 1e9, "kernel_tops": ops / kern_ms / 1e9,
+                        "step_frac_of_nominal_4500": ops / step_ms / 1e9 / NOMINAL_I8_TOPS,
+                        "kernel_frac_of_i8_probe": ops / kern_ms / 1e9 / i8_probe,
+                        "kernel_frac_of_2x_bf16": ops / kern_ms / 1e9 / peak2})
+            del x, y
+        weight.close()
+    return out
+
+
+def sustained_run(torch, step, ops, device_index, seconds=2.5):
+    """Back-to-back steps for `seconds` with the clock sampler at 5 ms: the sustained rate under the power
+    cap next to the burst figure of the short timed loop (median SM clock, TOPS, and TOPS scaled to the
+    maximum SM clock)."""
+    sampler = ClockSampler(device_index, period_s=0.005)
+    for _ in range(5):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler.start()
+    t0 = time.perf_counter()
+    count = 0
+    e0.record()
+    while time.perf_counter() - t0 < seconds:
+        for _ in range(50):
+            step()
+        count += 50
+        torch.cuda.current_stream().synchronize() if count % 500 == 0 else None
+    e1.record()
+    e1.synchronize()
+    sampler.stop()
+    ms = e0.elapsed_time(e1) / count
+    clocks = sampler.summary()
+    tops = ops / ms / 1e9
+    mhz, top = clocks.get("sm_mhz"), clocks.get("sm_max_mhz")
+    return {"seconds": e0.elapsed_time(e1) / 1e3, "steps": count, "ms_per_step": ms, "tops": tops, "clocks": clocks,
+            "tops_at_max_clock": tops * top / mhz if mhz and top else None}
+
+
 def gpu_arm(args):
     import torch
     import torch.distributed as dist
@@ -570,8 +640,19 @@ def gpu_arm(args):
             raise RuntimeError(f"multi-GPU output check failed: nccl path {same_as_nccl}, oracle {matches_oracle}")
 
     # roofline of the dominant kernel (the tcgen05 GEMM of this rank's shard)
-    gemm_ms = prof["gemm_ms"] / max(1, prof["gemm_launches"])
-    quant_ms = prof["quantize_ms"] / max(1, prof["quantize_launches"])
+    # a large batch is cut in two (the quantizer of the later rows runs under the GEMM of the first ones):
+    # the GEMM's time per step is the sum over its launches of that step
+    gemm_ms = prof["gemm_ms"] / args.steps
+    # the quantizer alone over the whole batch, timed outside the step loop
+    for _ in range(3):
+        ctx.quantize_rows(x_dev, ldq=weight.row_bytes)
+    qe0, qe1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    qe0.record()
+    for _ in range(10):
+        ctx.quantize_rows(x_dev, ldq=weight.row_bytes)
+    qe1.record()
+    qe1.synchronize()
+    quant_ms = qe0.elapsed_time(qe1) / 10
     ops_local = 2.0 * m * k * n_local
     achieved = ops_local / (gemm_ms * 1e-3) / 1e12
     peak = 2.0 * peaks["bf16_tflops"]
@@ -580,10 +661,12 @@ def gpu_arm(args):
         "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
         "frac": achieved / peak, "traffic": None,
         "kernel": "gemm_i8_pair_kernel" if "pair" in step_route else "gemm_i8_tcgen05_kernel", "kernel_ms": gemm_ms,
+        "kernel_launches_per_step": prof["gemm_launches"] / args.steps, "route": step_route,
         "peak_source": f"2 x bf16_tflops (cuBLAS bf16 burst, {peaks['_source']}) as the dense int8 rate",
         "i8_probe_tops": i8_probe, "frac_of_i8_probe": achieved / i8_probe,
         "frac_of_nominal_4500": achieved / NOMINAL_I8_TOPS,
         "quantize_kernel_ms": quant_ms,
+        "quantize_note": "whole-batch quantizer timed alone (allocation of its outputs included); inside a step all but the first row chunk of it runs under the GEMM",
         "quantize_gbs": (5.0 * m * k + 4.0 * m) / (quant_ms * 1e-3) / 1e9 if quant_ms > 0 else None,
         "quantize_frac_of_hbm": ((5.0 * m * k + 4.0 * m) / (quant_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]
                                  if quant_ms > 0 else None),
@@ -607,15 +690,30 @@ def gpu_arm(args):
                              "kernel_ms": gemm_ms, "frac": max(t_mma, t_link) / gemm_ms}
 
     # end to end through the host-pointer entry: pinned host buffers, copies inside the region
-    x_pin = torch.from_numpy(x_host_np).pin_memory()
     y_pin = torch.empty((m, n_local), dtype=torch.int8).pin_memory()
     e2e_steps = max(3, min(args.steps, 20))
+    if world == 1:
+        x_pin = torch.from_numpy(x_host_np).pin_memory()
+        e2e_api = "vxb_linear_host"
+
+        def e2e_step():
+            ctx.linear_host(weight, x_pin, y_pin, requant=True, out_scale=out_scale)
+    else:
+        # every rank uploads M / N rows, quantizes them, all-gathers the int8 codes over NVLink and
+        # downloads its channel slab: host traffic per step does not grow with the number of GPUs
+        rows_local = m // world
+        x_pin = torch.from_numpy(x_host_np[rank * rows_local:(rank + 1) * rows_local]).pin_memory()
+        host_lin = sharded.RowShardedHostLinear(ctx, weight, m, k, world, rank)
+        e2e_api = "RowShardedHostLinear (vxb_quantize_rows + NCCL all-gather of int8 rows + vxb_linear_prepared)"
+
+        def e2e_step():
+            host_lin.forward(x_pin, y_pin, out_scale)
     for _ in range(2):
-        ctx.linear_host(weight, x_pin, y_pin, requant=True, out_scale=out_scale)
+        e2e_step()
     barrier()
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
-        ctx.linear_host(weight, x_pin, y_pin, requant=True, out_scale=out_scale)
+        e2e_step()
     barrier()
     e2e_s = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device="cuda")
     if world > 1:
@@ -625,7 +723,7 @@ def gpu_arm(args):
     same = bool(torch.equal(y_pin.cuda(), y_local))
     e2e = {"value": ops / (e2e_ms * 1e-3) / 1e12, "unit": "TOPS", "ms_per_step": e2e_ms,
            "steps": e2e_steps, "h2d_bytes_per_step": int(x_pin.numel() * 4) * world,
-           "d2h_bytes_per_step": int(y_pin.numel()) * world, "api": "vxb_linear_host",
+           "d2h_bytes_per_step": int(y_pin.numel()) * world, "api": e2e_api,
            "matches_device_result": same}
 
     line = {
@@ -650,7 +748,9 @@ def gpu_arm(args):
     elif rank == 0:
         line["cpu_baseline"] = None
     if rank == 0 and world == 1 and not args.no_extras:
-        line["extras"] = {"gemv_sweep": gemv_sweep(torch, ctx, w8a8, peaks),
+        line["extras"] = {"gemm_sweep": gemm_sweep(torch, ctx, w8a8, peaks, i8_probe),
+                          "sustained": sustained_run(torch, step, ops, local),
+                          "gemv_sweep": gemv_sweep(torch, ctx, w8a8, peaks),
                           "model_linear_stacks": model_linear_stacks(torch, ctx, w8a8, peaks),
                           "widened_rows": widened_rows(torch, ctx, w8a8, peaks)}
 

@@ -181,6 +181,15 @@ VXB_API int vxb_peer_free(void* ptr);
 VXB_API int vxb_linear_i8_gather(VxbContext* ctx, const VxbWeight* w, const float* x, uint32_t rows,
                          float out_scale, int32_t out_zero, int8_t* y, uint32_t ldy,
                          void* const* peer_y, uint32_t n_peers);
+/* Barrier between the GPUs of the N-sharded linear, enqueued on the context's stream like a kernel:
+ * when it has completed on a rank, every rank has reached the same point of its stream, and the
+ * peer stores each of them issued before that point are visible here.  my_flags is this GPU's flag
+ * array (uint32[8], zero at start, from vxb_peer_alloc), peer_flags[p] the peer-mapped address of
+ * peer p's array, peer_ranks[p] its rank; epoch counts the barriers (1, 2, 3, ... the same on every
+ * rank).  A few microseconds instead of a collective's tens; every wait in it is bounded: a rank
+ * that never arrives turns the next vxb_context_synchronize() into -1 instead of a hang. */
+VXB_API int vxb_peer_barrier(VxbContext* ctx, uint32_t* my_flags, void* const* peer_flags, const uint32_t* peer_ranks,
+                     uint32_t n_peers, uint32_t my_rank, uint32_t epoch);
 
 /* ---- boundary of a static W8A8 island (device pointers) --------------------------------
  * QuantizeLinear, DequantizeLinear and RequantizeLinear with scalar (per-tensor) metadata,

@@ -75,6 +75,47 @@ def test_world_of_one_uses_the_shared_allocation(torch, oracle):
     ctx.close()
 
 
+@pytest.mark.parametrize("rows,k,n", [(2048, 256, 1536), (2500, 576, 4096), (4096, 128, 20000)])
+def test_two_chunk_overlap_equals_the_serial_form(torch, oracle, rows, k, n):
+    """Batches of 2048 rows or more are cut in two (the quantizer of the later rows runs on a side
+    stream under the GEMM of the first rows): every output byte must equal the serial form's, for the
+    int8 and fp32 epilogues, the residual tail, and with extra store destinations."""
+    from volvoxai_b200 import _lib, w8a8
+    L = _lib.load()
+    ctx = w8a8.Context(0)
+    ctx.use_torch_stream()
+    rng = np.random.default_rng(rows + n)
+    w = rng.integers(-127, 128, size=(n, k), dtype=np.int8)
+    ws = rng.uniform(0.001, 0.02, size=n).astype(np.float32)
+    weight = w8a8.Weight.from_i8(ctx, w, ws, bias_f32=rng.standard_normal(n).astype(np.float32))
+    x = torch.from_numpy((rng.standard_normal((rows, k)) * rng.uniform(0.1, 5, size=(rows, 1))).astype(np.float32)).cuda()
+    x[rows - 3, 1] = float("nan")
+    res = torch.randn((rows, n), device="cuda")
+    ld = (n + 15) // 16 * 16
+    got = {}
+    for mode in (0, 1):
+        assert w8a8.tune("gemm.overlap_k1", mode)
+        y8 = ctx.linear_i8(weight, x, 0.05, 3)
+        route = w8a8.last_route()
+        yf = ctx.linear_f32(weight, x)
+        yr = ctx.linear_f32_fused(weight, x, residual=res)
+        bufs = [torch.zeros((rows, ld), dtype=torch.int8, device="cuda") for _ in range(2)]
+        peers = (C.c_void_p * 1)(bufs[1].data_ptr())
+        assert L.vxb_linear_i8_gather(ctx.handle, weight.handle, C.c_void_p(x.data_ptr()), rows, 0.05, 0,
+                                      C.c_void_p(bufs[0].data_ptr()), ld, peers, 1) == 1
+        ctx.synchronize()
+        assert ("2-chunk-overlap" in route) == bool(mode), route
+        got[mode] = (y8, yf.view(torch.int32), yr.view(torch.int32), bufs[0], bufs[1])
+    for a, b in zip(got[0], got[1]):
+        assert torch.equal(a, b)
+    assert torch.equal(got[1][3], got[1][4])
+    # ... and the serial form is the oracle's
+    ref = oracle.w8a8_linear(x[:64].cpu().numpy(), w, ws, requant=True, out_scale=0.05, out_zero=3)
+    assert np.array_equal(got[0][0][:64].cpu().numpy(), ref["out"])
+    weight.close()
+    ctx.close()
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
@@ -100,9 +141,18 @@ def _worker(rank, world, port, rows, k, n, ret):
         ok = True
         for _ in range(4):
             y = lin.forward(x, os_)
+            torch.cuda.synchronize()         # the flag barrier inside forward() is the only cross-GPU ordering
             ok = ok and np.array_equal(y.cpu().numpy(), want)
-            dist.barrier()
         lin.close()
+        # the host-fed form: every rank uploads its rows, the int8 codes are all-gathered over NCCL
+        if hi > lo and rows % world == 0:
+            host = sharded.RowShardedHostLinear(ctx, weight, rows, k, world, rank)
+            per = rows // world
+            x_pin = torch.from_numpy(case["x"][rank * per:(rank + 1) * per].copy()).pin_memory()
+            y_pin = torch.empty((rows, hi - lo), dtype=torch.int8).pin_memory()
+            for _ in range(2):
+                host.forward(x_pin, y_pin, os_)
+                ok = ok and np.array_equal(y_pin.numpy(), want[:, lo:hi])
         if weight is not None:
             weight.close()
         ctx.close()
@@ -111,7 +161,7 @@ def _worker(rank, world, port, rows, k, n, ret):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,rows,k,n", [(2, 1000, 512, 1300), (2, 64, 128, 100)])
+@pytest.mark.parametrize("world,rows,k,n", [(2, 1000, 512, 1300), (2, 64, 128, 100), (2, 2304, 512, 1300)])
 def test_two_gpus_every_rank_holds_the_whole_output(torch, world, rows, k, n):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")

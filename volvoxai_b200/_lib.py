@@ -24,7 +24,7 @@ EXPORTS = [
     "vxb_quantize_rows", "vxb_linear_f32", "vxb_linear_i8", "vxb_linear_acc_i32",
     "vxb_qlinear_device", "vxb_weight_row_bytes", "vxb_linear_prepared", "vxb_linear_host", "vxb_context_profile", "vxb_context_profile_read",
     "vxb_measure_i8_tensor_peak", "vxb_peer_alloc", "vxb_peer_open",
-    "vxb_peer_close", "vxb_peer_free", "vxb_linear_i8_gather", "vxb_linear_f32_fused", "vxb_weight_create_w4_words",
+    "vxb_peer_close", "vxb_peer_free", "vxb_linear_i8_gather", "vxb_peer_barrier", "vxb_linear_f32_fused", "vxb_weight_create_w4_words",
     "vxb_rmsnorm_quantize_rows", "vxb_rmsnorm_linear_f32_fused", "vxb_quantize_linear_device",
     "vxb_dequantize_linear_device", "vxb_requantize_linear_device", "vxb_quantize_typed_f32_i8u8",
     "vxb_dequantize_typed_i8u8_f32", "vxb_requantize_linear_i8u8", "vxb_decode_linear_f32_noalloc", "vxb_qlinear_i8u8",
@@ -189,6 +189,7 @@ def load() -> C.CDLL:
     L.vxb_peer_close.argtypes = [vp]
     L.vxb_peer_free.argtypes = [vp]
     L.vxb_linear_i8_gather.argtypes = [vp, vp, vp, u32, f32, i32, vp, u32, C.POINTER(vp), u32]
+    L.vxb_peer_barrier.argtypes = [vp, vp, C.POINTER(vp), C.POINTER(u32), u32, u32, u32]
     L.vxb_measure_mma_issue.argtypes = [vp, u32, u32, u32, u32, u32, C.POINTER(C.c_double)]
     L.vxb_measure_i8_tensor_peak.argtypes = [vp, u32, C.POINTER(C.c_double)]
     L.vxb_decode_linear_f32_noalloc.argtypes = [vp, vp, u32, vp, vp, vp, u32, u32, vp, u32, vp,

@@ -135,6 +135,9 @@ struct VxbContext {
     cudaStream_t copy_in = nullptr, copy_out = nullptr;
     cudaEvent_t ev_in[2] = {}, ev_done[2] = {}, ev_out[2] = {}, ev_start = nullptr;
     cudaEvent_t ev_switch = nullptr;   // orders the context's scratch across a stream change
+    // K1 / K2 overlap: the quantizer of the later rows runs on `side` under the GEMM of the first rows
+    cudaStream_t side = nullptr;
+    cudaEvent_t ev_first = nullptr, ev_rest = nullptr;
     bool profiling = false;
     std::vector<cudaEvent_t> prof_events[2];   // [0] = K1 quantizer, [1] = GEMM / GEMV
 };
@@ -411,6 +414,95 @@ int quantize_into_scratch(VxbContext* ctx, const VxbWeight* w, const float* x, u
     return 1;
 }
 
+// Rows of the first chunk when a large batch is cut in two so that the quantizer of the later rows
+// runs under the GEMM of the first ones (K1 is HBM-bound, K2 tensor-bound or link-bound): 0 = do
+// not split.  The first chunk is the smallest number of row tiles whose GEMM lasts at least as
+// long as the quantizer of the rest and that adds no wave of tiles to the launch pair.
+uint32_t overlap_first_rows(const VxbContext* ctx, const VxbWeight* w, uint32_t rows, const EpilogueParams& epi, int route) {
+    if (!tunables().overlap_k1 || w->group || rows < 2048) return 0;
+    if (route != VXB_ROUTE_AUTO && route != VXB_ROUTE_TCGEN05 && route != VXB_ROUTE_TCGEN05_PAIR) return 0;
+    const bool gather = epi.n_peers != 0;
+    const uint32_t tiles128 = ((rows + 127) / 128) * ((w->d_out + 255) / 256);
+    const bool pair = !gather && route != VXB_ROUTE_TCGEN05 && gemm_pair_clusters() > 0 &&
+                      (route == VXB_ROUTE_TCGEN05_PAIR || tiles128 >= 2u * (uint32_t)ctx->sm_count);
+    const uint32_t tile_rows = pair ? 256u : 128u;
+    const uint32_t slots = pair ? (uint32_t)gemm_pair_clusters() : (uint32_t)ctx->sm_count;
+    const uint32_t cols = (w->d_out + 255) / 256, row_tiles = (rows + tile_rows - 1) / tile_rows;
+    if (row_tiles < 4) return 0;
+    auto waves = [&](uint32_t r) { return (r * cols + slots - 1) / slots; };
+    // GEMM seconds per row ~ 2 K N / 3.3e15 (link-bound with peers: slower still), quantizer seconds per
+    // row ~ 5 K / 4.7e12: the first chunk needs rows_first / rows_rest >= 1755 / N
+    const double ratio = 1755.0 / (double)w->d_out;
+    uint32_t r_min = (uint32_t)((double)row_tiles * ratio / (1.0 + ratio)) + 1;
+    if (r_min >= row_tiles) return 0;
+    uint32_t best = 0;
+    if (!gather) {
+        for (uint32_t r = r_min; r < row_tiles && r <= 2 * r_min + 4; r++)
+            if (waves(r) + waves(row_tiles - r) == waves(row_tiles)) { best = r; break; }
+        if (!best) return 0;   // every cut here would idle part of a wave: keep the single launch
+    } else best = r_min;
+    return best * tile_rows;
+}
+
+// Quantizer + GEMM of one call; a large batch takes the overlapped form when the side stream exists
+// (it is created on first use outside stream capture).
+int quantize_then_gemm(VxbContext* ctx, const VxbWeight* w, const float* x, uint32_t rows, const EpilogueParams& epi,
+                       int route, const char* prefix, const float* norm_weight = nullptr, float epsilon = 0.0f,
+                       float* norm_out = nullptr) {
+    uint32_t first = norm_weight ? 0u : overlap_first_rows(ctx, w, rows, epi, route);
+    if (first) {
+        cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(ctx->stream, &capturing) != cudaSuccess) { cudaGetLastError(); capturing = cudaStreamCaptureStatusActive; }
+        if (!ctx->side && capturing == cudaStreamCaptureStatusNone) {
+            if (cudaStreamCreateWithFlags(&ctx->side, cudaStreamNonBlocking) != cudaSuccess ||
+                cudaEventCreateWithFlags(&ctx->ev_first, cudaEventDisableTiming) != cudaSuccess ||
+                cudaEventCreateWithFlags(&ctx->ev_rest, cudaEventDisableTiming) != cudaSuccess) {
+                cudaGetLastError(); ctx->side = nullptr;
+            }
+        }
+        if (!ctx->side) first = 0;
+    }
+    if (!first) {
+        int rc = quantize_into_scratch(ctx, w, x, rows, norm_weight, epsilon, norm_out);
+        if (rc != 1) return rc;
+        return run_gemm(ctx, w, (const int8_t*)ctx->q.ptr, rows, epi, route, prefix);
+    }
+    CUDA_TRY(ctx->q.reserve((size_t)rows * w->kpad), 0);
+    CUDA_TRY(ctx->row_scales.reserve((size_t)rows * 4), 0);
+    int8_t* q = (int8_t*)ctx->q.ptr; float* scales = (float*)ctx->row_scales.ptr;
+    const uint32_t rest = rows - first;
+    {
+        ProfileScope scope(ctx, 0);
+        LAUNCH_TRY(launch_quantize_rows(x, first, w->d_in, q, w->kpad, scales, nullptr, ctx->stream));
+    }
+    // the quantizer of the rest starts when the first chunk's has finished (two at once would only share
+    // the HBM bandwidth) and runs under the first chunk's GEMM
+    CUDA_TRY(cudaEventRecord(ctx->ev_first, ctx->stream), -1);
+    CUDA_TRY(cudaStreamWaitEvent(ctx->side, ctx->ev_first, 0), -1);
+    LAUNCH_TRY(launch_quantize_rows(x + (size_t)first * w->d_in, rest, w->d_in, q + (size_t)first * w->kpad, w->kpad,
+                                    scales + first, nullptr, ctx->side));
+    CUDA_TRY(cudaEventRecord(ctx->ev_rest, ctx->side), -1);
+    count_launch(2);
+    int rc = run_gemm(ctx, w, q, first, epi, route, prefix);
+    if (rc != 1) { cudaStreamWaitEvent(ctx->stream, ctx->ev_rest, 0); return rc; }   // 0: no output was touched
+    CUDA_TRY(cudaStreamWaitEvent(ctx->stream, ctx->ev_rest, 0), -1);
+    EpilogueParams tail = epi;
+    const size_t elem = epi.mode == kEpiI8 ? 1 : 4;
+    tail.row_scales = epi.row_scales + first;
+    tail.out = (uint8_t*)epi.out + (size_t)first * epi.ld * elem;
+    if (epi.residual) tail.residual = epi.residual + (size_t)first * epi.ld_res;
+    for (uint32_t p = 0; p < epi.n_peers; p++) tail.peer_out[p] = (uint8_t*)epi.peer_out[p] + (size_t)first * epi.ld * elem;
+    char overlapped[32];
+    snprintf(overlapped, sizeof overlapped, "%s", prefix);
+    rc = run_gemm(ctx, w, q + (size_t)first * w->kpad, rest, tail, route, overlapped);
+    if (rc == 1) {
+        char route_text[96];
+        snprintf(route_text, sizeof route_text, "%s", g_route);
+        snprintf(g_route, sizeof g_route, "%s|2-chunk-overlap", route_text);
+    }
+    return rc == 0 ? -1 : rc;
+}
+
 }  // namespace
 
 extern "C" {
@@ -456,6 +548,7 @@ void vxb_context_destroy(VxbContext* ctx) {
         cudaEventDestroy(ctx->ev_start);
     }
     if (ctx->ev_switch) cudaEventDestroy(ctx->ev_switch);
+    if (ctx->side) { cudaStreamDestroy(ctx->side); cudaEventDestroy(ctx->ev_first); cudaEventDestroy(ctx->ev_rest); }
     if (ctx->status) cudaFree(ctx->status);
     if (ctx->status_host) cudaFreeHost(ctx->status_host);
     delete ctx;
@@ -663,11 +756,11 @@ int vxb_linear_f32(VxbContext* ctx, const VxbWeight* w, const float* x, uint32_t
     if (rc != 1) return rc;
     if (!rows) return 1;
     if (ensure_device(ctx) != 1) return -1;
-    if ((rc = quantize_into_scratch(ctx, w, x, rows)) != 1) return rc;
+    CUDA_TRY(ctx->row_scales.reserve((size_t)rows * 4), 0);
     EpilogueParams epi{};
     epi.mode = kEpiF32; epi.row_scales = (const float*)ctx->row_scales.ptr; epi.ws = w->ws;
     epi.bias_f32 = w->bias_f32; epi.out = y; epi.ld = ldy;
-    return run_gemm(ctx, w, (const int8_t*)ctx->q.ptr, rows, epi, route, "k1+");
+    return quantize_then_gemm(ctx, w, x, rows, epi, route, "k1+");
 }
 
 static int fused_linear(VxbContext* ctx, const VxbWeight* w, const float* x, uint32_t rows, float* y,
@@ -684,14 +777,13 @@ static int fused_linear(VxbContext* ctx, const VxbWeight* w, const float* x, uin
     if (residual && ld_residual < width) return fail(0, "residual row stride %u < output width %u", ld_residual, width);
     if (!rows) return 1;
     if (ensure_device(ctx) != 1) return -1;
-    int rc;
-    if ((rc = quantize_into_scratch(ctx, w, x, rows, norm_weight, epsilon, norm_out)) != 1) return rc;
+    CUDA_TRY(ctx->row_scales.reserve((size_t)rows * 4), 0);
     EpilogueParams epi{};
     epi.mode = kEpiF32; epi.row_scales = (const float*)ctx->row_scales.ptr; epi.ws = w->ws;
     epi.bias_f32 = w->bias_f32; epi.out = y; epi.ld = ldy;
     epi.residual = residual; epi.ld_res = ld_residual; epi.act = activation == VXB_ACT_SILU_MUL ? 1u : 0u;
     // the decode kernel up to 128 rows, the tensor-core GEMM above: both carry the fused forms
-    return run_gemm(ctx, w, (const int8_t*)ctx->q.ptr, rows, epi, VXB_ROUTE_AUTO, norm_weight ? "norm+k1+" : "k1+");
+    return quantize_then_gemm(ctx, w, x, rows, epi, VXB_ROUTE_AUTO, norm_weight ? "norm+k1+" : "k1+", norm_weight, epsilon, norm_out);
 }
 
 int vxb_linear_f32_fused(VxbContext* ctx, const VxbWeight* w, const float* x, uint32_t rows, float* y,
@@ -731,12 +823,12 @@ int vxb_linear_i8(VxbContext* ctx, const VxbWeight* w, const float* x, uint32_t 
     if (out_zero < -128 || out_zero > 127) return fail(0, "output zero point %d outside int8", out_zero);
     if (!rows) return 1;
     if (ensure_device(ctx) != 1) return -1;
-    if ((rc = quantize_into_scratch(ctx, w, x, rows)) != 1) return rc;
+    CUDA_TRY(ctx->row_scales.reserve((size_t)rows * 4), 0);
     EpilogueParams epi{};
     epi.mode = kEpiI8; epi.row_scales = (const float*)ctx->row_scales.ptr; epi.ws = w->ws;
     epi.bias_i32 = w->bias_i32; set_requant_divisor(epi, w, out_scale); epi.out_zero = out_zero;
     epi.out_lo = -128; epi.out_hi = 127; epi.out = y; epi.ld = ldy;
-    return run_gemm(ctx, w, (const int8_t*)ctx->q.ptr, rows, epi, route, "k1+");
+    return quantize_then_gemm(ctx, w, x, rows, epi, route, "k1+");
 }
 
 int vxb_linear_acc_i32(VxbContext* ctx, const VxbWeight* w, const float* x, uint32_t rows,
@@ -802,7 +894,7 @@ int vxb_linear_i8_gather(VxbContext* ctx, const VxbWeight* w, const float* x, ui
     if (out_zero < -128 || out_zero > 127) return fail(0, "output zero point %d outside int8", out_zero);
     if (!rows) return 1;
     if (ensure_device(ctx) != 1) return -1;
-    if ((rc = quantize_into_scratch(ctx, w, x, rows)) != 1) return rc;
+    CUDA_TRY(ctx->row_scales.reserve((size_t)rows * 4), 0);
     EpilogueParams epi{};
     epi.mode = kEpiI8; epi.row_scales = (const float*)ctx->row_scales.ptr; epi.ws = w->ws;
     epi.bias_i32 = w->bias_i32; set_requant_divisor(epi, w, out_scale); epi.out_zero = out_zero;
@@ -810,7 +902,24 @@ int vxb_linear_i8_gather(VxbContext* ctx, const VxbWeight* w, const float* x, ui
     epi.n_peers = n_peers;
     for (uint32_t p = 0; p < n_peers; p++) epi.peer_out[p] = peer_y[p];
     // the peer stores live in the large-M kernel's epilogue
-    return run_gemm(ctx, w, (const int8_t*)ctx->q.ptr, rows, epi, VXB_ROUTE_TCGEN05, "k1+");
+    return quantize_then_gemm(ctx, w, x, rows, epi, VXB_ROUTE_TCGEN05, "k1+");
+}
+
+int vxb_peer_barrier(VxbContext* ctx, uint32_t* my_flags, void* const* peer_flags, const uint32_t* peer_ranks,
+                     uint32_t n_peers, uint32_t my_rank, uint32_t epoch) {
+    if (!ctx || !my_flags || (n_peers && (!peer_flags || !peer_ranks))) return fail(0, "null argument");
+    if (n_peers > 7 || my_rank > 7) return fail(0, "at most 8 ranks");
+    if (!n_peers) return 1;
+    PeerBarrierArgs a{};
+    for (uint32_t p = 0; p < n_peers; p++) {
+        if (!peer_flags[p] || peer_ranks[p] > 7 || peer_ranks[p] == my_rank) return fail(0, "bad peer %u", p);
+        a.peer_flags[p] = (uint32_t*)peer_flags[p]; a.peer_ranks[p] = peer_ranks[p];
+    }
+    a.n_peers = n_peers; a.my_rank = my_rank; a.epoch = epoch;
+    if (ensure_device(ctx) != 1) return -1;
+    LAUNCH_TRY(launch_peer_barrier(my_flags, a, ctx->status, ctx->stream));
+    count_launch();
+    return 1;
 }
 
 namespace {
@@ -974,6 +1083,7 @@ int vxb_tune(const char* name, int64_t value) {
     Tunables& t = tunables();
     if (!strcmp(name, "decode.pair_share_bytes")) { t.decode_pair_share_bytes = (uint32_t)value; return 1; }
     if (!strcmp(name, "decode.l2_prefetch")) { t.decode_l2_prefetch = value != 0; return 1; }
+    if (!strcmp(name, "gemm.overlap_k1")) { t.overlap_k1 = value != 0; return 1; }
     return 0;
 }
 

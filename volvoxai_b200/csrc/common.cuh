@@ -388,6 +388,14 @@ struct DecodeTcgen05Args {
 uint32_t decode_token_slots(uint32_t rows);  // 32 / 64 / 128
 cudaError_t launch_decode_tcgen05(const DecodeTcgen05Args& args, int sm_count, cudaStream_t stream);
 
+// Cross-GPU barrier (selftest.cu): flag arrays of uint32, one slot per rank, in peer-mapped memory.
+struct PeerBarrierArgs {
+    uint32_t* peer_flags[7];   // the peers' flag arrays (peer-mapped addresses)
+    uint32_t peer_ranks[7];    // rank of peer t (its slot in this GPU's own array)
+    uint32_t n_peers, my_rank, epoch;
+};
+cudaError_t launch_peer_barrier(uint32_t* my_flags, const PeerBarrierArgs& args, int* status, cudaStream_t stream);
+
 // Device self-tests (selftest.cu): a wait that expires by design, and div_const against the IEEE divide.
 cudaError_t launch_wait_expiry(int* status, cudaStream_t stream);
 cudaError_t launch_div_const_check(int exponent, uint32_t neighbours, uint32_t samples, unsigned long long* mismatches,
@@ -397,6 +405,7 @@ cudaError_t launch_div_const_check(int exponent, uint32_t neighbours, uint32_t s
 struct Tunables {
     uint32_t decode_pair_share_bytes;   // largest per-CTA weight share the decode kernel runs as two CTAs per SM
     bool decode_l2_prefetch;            // weight producers ask L2 for the tile one ring-depth ahead
+    bool overlap_k1;                    // large batches: quantize the later rows under the GEMM of the first ones
 };
 Tunables& tunables();
 

@@ -615,7 +615,7 @@ cudaError_t launch_t(const DecodeRowsArgs& args, cudaStream_t stream) {
 }  // namespace
 
 Tunables& tunables() {
-    static Tunables t{kPairShareBytes, false};
+    static Tunables t{kPairShareBytes, false, true};
     return t;
 }
 

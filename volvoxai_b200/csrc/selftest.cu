@@ -81,7 +81,41 @@ div_const_check_kernel(int exponent, uint32_t neighbours, uint32_t samples, unsi
     }
 }
 
+// Cross-GPU barrier of the N-sharded linear: thread t tells peer t that this rank has reached `epoch`
+// (a release store at system scope into the peer's flag array, after a system-scope fence that
+// orders this GPU's earlier peer stores before it) and then waits, with the launch's limit, until
+// peer t's flag in this GPU's own array has reached the epoch too.  Every rank runs this kernel
+// on its own GPU at the same point of its stream, so each waits only for kernels that are already
+// queued on other GPUs; a rank that never arrives makes the wait run out, which raises the
+// status word instead of hanging.
+__global__ void __launch_bounds__(32, 1)
+peer_barrier_kernel(uint32_t* my_flags, PeerBarrierArgs args, int* status) {
+    const uint32_t t = threadIdx.x;
+    if (t >= args.n_peers) return;
+    __threadfence_system();
+    uint32_t* remote = args.peer_flags[t] + args.my_rank;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(args.epoch) : "memory");
+    const uint32_t* mine = my_flags + args.peer_ranks[t];
+    int limit = status ? status[1] : 0;
+    if (limit <= 0) limit = kDefaultWaitLimitKcycles;
+    const long long t0 = clock64();
+    for (uint32_t spins = 0;; spins++) {
+        uint32_t seen;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+        if ((int32_t)(seen - args.epoch) >= 0) break;
+        if ((spins & 63u) == 63u && clock64() - t0 > ((long long)limit << 10)) {
+            if (status) atomicExch(status, 6);
+            break;
+        }
+    }
+}
+
 }  // namespace
+
+cudaError_t launch_peer_barrier(uint32_t* my_flags, const PeerBarrierArgs& args, int* status, cudaStream_t stream) {
+    peer_barrier_kernel<<<1, 32, 0, stream>>>(my_flags, args, status);
+    return cudaGetLastError();
+}
 
 cudaError_t launch_wait_expiry(int* status, cudaStream_t stream) {
     wait_expiry_kernel<<<1, 128, 0, stream>>>(status);

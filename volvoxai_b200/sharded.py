@@ -102,6 +102,52 @@ class NShardedLinear:
         return interleave(self.forward_gathered(x), self.n)
 
 
+class RowShardedHostLinear:
+    """The N-sharded linear fed from HOST memory at `world` GPUs without replicating the upload.
+
+    Rank r holds rows [r*M/g, (r+1)*M/g) of the fp32 activations in pinned host memory and the
+    channel range shard_bounds(n, world, r) of the weights.  One step: upload the rank's rows,
+    quantize them (K1 on M/g rows), all-gather the int8 codes and the row scales over NVLink (NCCL:
+    a quarter of the fp32 bytes), run the rank's channel slab from the prepared activations with
+    the requantizing epilogue, download the [M, n_local] int8 slab.  Host traffic per step is
+    4*M*K up and M*N down in total, whatever the number of GPUs."""
+
+    def __init__(self, ctx, weight, rows: int, k: int, world: int, rank: int, group=None):
+        if rows % world:
+            raise ValueError("the row count must divide by the number of GPUs")
+        self.ctx, self.weight, self.rows, self.k, self.world, self.rank, self.group = ctx, weight, rows, k, world, rank, group
+        self.local_rows = rows // world
+        dev = f"cuda:{ctx.device}"
+        kpad = weight.row_bytes
+        self.x_dev = torch.empty((self.local_rows, k), dtype=torch.float32, device=dev)
+        self.q_local = torch.empty((self.local_rows, kpad), dtype=torch.int8, device=dev)
+        self.s_local = torch.empty(self.local_rows, dtype=torch.float32, device=dev)
+        self.q_all = torch.empty((rows, kpad), dtype=torch.int8, device=dev)
+        self.s_all = torch.empty(rows, dtype=torch.float32, device=dev)
+        self.y_dev = torch.empty((rows, weight.d_out), dtype=torch.int8, device=dev)
+
+    def forward(self, x_pinned_local, y_pinned_slab, out_scale: float, out_zero: int = 0) -> None:
+        """x_pinned_local: this rank's [M/g, K] fp32 rows; y_pinned_slab: [M, n_local] int8 (both pinned)."""
+        import ctypes as C
+        ctx, L = self.ctx, self.ctx._L
+        ctx.set_stream(torch.cuda.current_stream(ctx.device).cuda_stream)
+        self.x_dev.copy_(x_pinned_local, non_blocking=True)
+        rc = L.vxb_quantize_rows(ctx.handle, C.c_void_p(self.x_dev.data_ptr()), self.local_rows, self.k,
+                                 C.c_void_p(self.q_local.data_ptr()), self.q_local.shape[1],
+                                 C.c_void_p(self.s_local.data_ptr()), None)
+        if rc != 1:
+            raise RuntimeError("vxb_quantize_rows failed")
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.q_all, self.q_local, group=self.group)
+            dist.all_gather_into_tensor(self.s_all, self.s_local, group=self.group)
+            q, s = self.q_all, self.s_all
+        else:
+            q, s = self.q_local, self.s_local
+        ctx.linear_prepared(self.weight, q, s, self.y_dev, mode=2, out_scale=out_scale, out_zero=out_zero)
+        y_pinned_slab.copy_(self.y_dev, non_blocking=True)
+        torch.cuda.current_stream(ctx.device).synchronize()
+
+
 class _RawCuda:
     """A raw device allocation exposed through __cuda_array_interface__ (uint8, 1-D)."""
 
@@ -118,11 +164,11 @@ class FusedGatherLinear:
     vxb_linear_i8_gather quantizes the replicated activations, runs the tcgen05 GEMM of the
     rank's channel range and stores every finished tile at the same [row, lo + col] position
     of all `world` buffers, with plain stores over NVLink while the MMAs of later tiles run.
-    No NCCL collective moves data; a one-element all-reduce after the kernel is the only
-    cross-GPU synchronisation (stream-ordered: when it has completed on a rank, every rank's
-    kernel, and with it every store into this rank's buffer, has completed).  forward() therefore
-    moves the context onto torch's current stream of the device before it launches: the
-    all-reduce is queued there, and it only orders what runs on the same stream.
+    No collective moves data; a one-CTA barrier kernel after the GEMM (vxb_peer_barrier: a flag per
+    rank in every peer's memory, bounded waits) is the only cross-GPU synchronisation: when it has
+    completed on a rank, every rank's kernel, and with it every store into this rank's buffer, has
+    completed.  forward() moves the context onto torch's current stream of the device before it
+    launches, so that later torch work on that stream is ordered after the barrier.
 
     Two buffers alternate between steps, so that a rank that is still reading step k's
     output is never overwritten by a faster peer's step k+1: a peer reaches step k+2, which
@@ -144,7 +190,6 @@ class FusedGatherLinear:
         self.ld = (n + 15) // 16 * 16            # 16-byte row pitch: vector stores on every rank
         nbytes = rows * self.ld
         self._own, self._peers, self.buffers = [], [], []
-        self._flag = torch.zeros(1, dtype=torch.int32, device=f"cuda:{ctx.device}")
         self._step = 0
         import ctypes as C
         for _ in range(self.DEPTH):
@@ -166,6 +211,27 @@ class FusedGatherLinear:
             self._peers.append(mapped)
             t = torch.as_tensor(_RawCuda(ptr.value, nbytes), device=f"cuda:{ctx.device}")
             self.buffers.append(t.view(rows, self.ld))
+        # flag arrays of the cross-GPU barrier (one uint32 slot per rank), zero before the first step
+        ptr, handle = C.c_void_p(), C.create_string_buffer(64)
+        if self._L.vxb_peer_alloc(256, C.byref(ptr), handle) != 1:
+            raise RuntimeError(_lib.last_error())
+        self._flags = ptr.value
+        torch.as_tensor(_RawCuda(ptr.value, 256), device=f"cuda:{ctx.device}").zero_()
+        torch.cuda.synchronize()
+        handles = [None] * world
+        if world > 1:
+            dist.all_gather_object(handles, handle.raw, group=group)
+        self._peer_flags, self._peer_ranks = [], []
+        for r in range(world):
+            if r == rank:
+                continue
+            p = C.c_void_p()
+            if self._L.vxb_peer_open(handles[r], C.byref(p)) != 1:
+                raise RuntimeError(_lib.last_error())
+            self._peer_flags.append(p.value)
+            self._peer_ranks.append(r)
+        if world > 1:
+            dist.barrier(group=group)   # every rank's flags are zero before anybody's first barrier kernel
 
     def forward(self, x, out_scale: float, out_zero: int = 0, sync: bool = True) -> torch.Tensor:
         """Returns this rank's replicated [rows, n] int8 output (a view of the step's buffer).
@@ -189,8 +255,20 @@ class FusedGatherLinear:
                 from . import _lib
                 raise RuntimeError(f"vxb_linear_i8_gather returned {rc}: {_lib.last_error()}")
         if sync and self.world > 1:
-            dist.all_reduce(self._flag, group=self.group)
+            self.barrier()
         return self.buffers[b][:, : self.n]
+
+    def barrier(self) -> None:
+        """Orders the GPUs on the context's stream: a one-CTA kernel per rank that raises this rank's
+        flag in every peer's array and waits (bounded) for theirs (vxb_peer_barrier)."""
+        import ctypes as C
+        k = len(self._peer_flags)
+        flags = (C.c_void_p * max(1, k))(*self._peer_flags)
+        ranks = (C.c_uint32 * max(1, k))(*self._peer_ranks)
+        rc = self._L.vxb_peer_barrier(self.ctx.handle, C.c_void_p(self._flags), flags, ranks, k, self.rank, self._step)
+        if rc != 1:
+            from . import _lib
+            raise RuntimeError(f"vxb_peer_barrier returned {rc}: {_lib.last_error()}")
 
     def close(self) -> None:
         """Collective: every rank unmaps its peers' buffers before any owner frees one."""
@@ -199,10 +277,12 @@ class FusedGatherLinear:
         for mapped in self._peers:
             for p in mapped:
                 self._L.vxb_peer_close(C.c_void_p(p))
-        self._peers = []
+        for p in self._peer_flags:
+            self._L.vxb_peer_close(C.c_void_p(p))
+        self._peers, self._peer_flags = [], []
         self.buffers = []
         if self.world > 1:
             dist.barrier(group=self.group)
-        for p in self._own:
+        for p in self._own + ([self._flags] if self._flags else []):
             self._L.vxb_peer_free(C.c_void_p(p))
-        self._own = []
+        self._own, self._flags = [], None
