@@ -832,6 +832,136 @@ def decode_arm(args):
     print(json.dumps(line), flush=True)
 
 
+def decoder_arm(args):
+    """`--workload decoder --model smollm2|qwen3 [--gpus N]`: the two model-shaped configurations end to
+    end.  smollm2: prefill of 8 x 512 tokens through the 30-layer SmolLM2-135M-shaped decoder (tokens/s);
+    qwen3: greedy decode at batch 64 from 256-token prompts for 128 new tokens through the 28-layer
+    Qwen3-0.6B-shaped decoder with the paged KV cache (block 16), the decode step replayed from a CUDA
+    graph (new tokens/s).  Random-initialised weights, uniform random token ids.  Every W8A8 linear runs
+    in this library (fused RMSNorm / SiLU*Mul / residual forms); embedding, rotary, attention, KV-cache
+    indexing and the fp32 lm_head are PyTorch glue, and the line says how much of the step the
+    library's kernels account for.  With N > 1 every GPU runs an independent replica (the path has no
+    exchange step at these layer sizes): value is the sum over replicas, scaling weak."""
+    import torch
+    import torch.distributed as dist
+    from tests import decoder_harness as dh
+    from volvoxai_b200 import w8a8
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device; there is no CPU fallback")
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    peaks = measured_peaks()
+    ctx = w8a8.Context(local)
+    ctx.use_torch_stream()
+    prefill = args.model == "smollm2"
+    cfg = dh.SMOLLM2_135M if prefill else dh.QWEN3_0_6B
+    model = dh.W8A8Decoder(cfg, ctx, w8a8, seed=rank)
+    gen = torch.Generator(device="cuda").manual_seed(100 + rank)
+    sampler = ClockSampler(local)
+
+    def sync_all():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    if prefill:
+        batch, seq, steps = 8, 512, max(3, min(args.steps, 20))
+        tokens = torch.randint(0, cfg["vocab"], (batch, seq), device="cuda", generator=gen)
+        model.allocate_cache(batch, seq)
+        for _ in range(max(3, args.warmup)):
+            model.prefill(tokens)
+        sync_all()
+        launches0 = w8a8.launch_count()
+        ctx.profile(True)
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            model.prefill(tokens)
+        e1.record()
+        sync_all()
+        sampler.sample_now(); sampler.stop()
+        prof = ctx.profile_read(); ctx.profile(False)
+        ms = e0.elapsed_time(e1) / steps
+        units = batch * seq
+        lib_ms = (prof["quantize_ms"] + prof["gemm_ms"]) / steps
+        workload = "smollm2_135m_shape_prefill_8x512"
+        metric, note = "w8a8_decoder_prefill_tokens_per_s", "eager PyTorch glue between the library's launches"
+    else:
+        batch, prompt, new = 64, 256, 128
+        steps = new
+        tokens = torch.randint(0, cfg["vocab"], (batch, prompt), device="cuda", generator=gen)
+        model.allocate_cache(batch, prompt + new, dtype=torch.bfloat16)
+        logits = model.prefill(tokens)
+        tok = logits.argmax(-1)
+        pos = torch.full((batch, 1), prompt, dtype=torch.int64, device="cuda")
+        model.decode_step(tok, pos)           # warm-up (writes position `prompt`; rewritten by the first timed step)
+        torch.cuda.synchronize()
+        side, graph = torch.cuda.Stream(), torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            ctx.use_torch_stream()
+            out = model.decode_step(tok, pos)
+            tok.copy_(out.argmax(-1))
+            pos.add_(1)
+        ctx.use_torch_stream()
+        pos.fill_(prompt)
+        for _ in range(3):
+            graph.replay()
+        pos.fill_(prompt)
+        sync_all()
+        launches0 = w8a8.launch_count()
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(new):
+            graph.replay()
+        e1.record()
+        sync_all()
+        sampler.sample_now(); sampler.stop()
+        ms = e0.elapsed_time(e1) / new
+        units = batch
+        # the library's share of one step: the same step eagerly with per-kernel event pairs
+        pos.fill_(prompt)
+        ctx.profile(True)
+        model.decode_step(tok, pos)
+        prof = ctx.profile_read(); ctx.profile(False)
+        lib_ms = prof["quantize_ms"] + prof["gemm_ms"]
+        workload = "qwen3_0.6b_shape_decode_b64_prompt256_new128_paged_kv16"
+        metric, note = "w8a8_decoder_decode_tokens_per_s", "decode step replayed from a CUDA graph; bf16 paged KV cache"
+    t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_max = float(t.item())
+    launches_per_step = 8 * cfg["layers"]
+    weight_bytes = model.weight_bytes
+    line = {
+        "metric": metric, "value": world * units / (ms_max * 1e-3), "unit": "tokens/s", "n_gpus": world,
+        "steps": steps, "warmup": max(3, args.warmup), "ms_per_step": ms_max, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+        "config": {"workload": workload, "layers": cfg["layers"], "hidden": cfg["hidden"], "parallelism": f"replicas{world}",
+                   "l2": "weights of all layers (> L2) stream once per step", "glue": note},
+        "clocks": sampler.summary(), "gpu_launches": int(w8a8.launch_count() - launches0),
+        "library": {"launches_per_step": launches_per_step, "kernels_ms_per_step": lib_ms, "share_of_step": lib_ms / ms_max,
+                    "weight_bytes": weight_bytes, "route": w8a8.last_route()},
+        "roofline": {"bound": "hbm", "achieved": weight_bytes / (lib_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": weight_bytes / (lib_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "traffic": None,
+                     "kernel": "W8A8 linear launches of one step (quantizers + decode / GEMM kernels)",
+                     "note": "weight bytes of all layers / time inside the library's kernels"},
+    }
+    model.close()
+    ctx.close()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def grouped_arm(args):
     """`--workload grouped --rows M --k K --n N --group G`: the linear over PackedLinear storage whose
     group scales differ within a channel (fp32 output), quantizer + grouped-scale GEMM per step on
@@ -890,7 +1020,8 @@ def grouped_arm(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="gemm", choices=["gemm", "decode", "grouped"])
+    ap.add_argument("--workload", default="gemm", choices=["gemm", "decode", "grouped", "decoder"])
+    ap.add_argument("--model", default="qwen3", choices=["smollm2", "qwen3"], help="architecture of --workload decoder")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
@@ -912,6 +1043,8 @@ def main():
         decode_arm(args)
     elif args.workload == "grouped":
         grouped_arm(args)
+    elif args.workload == "decoder":
+        decoder_arm(args)
     else:
         gpu_arm(args)
 

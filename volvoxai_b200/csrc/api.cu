@@ -432,7 +432,7 @@ uint32_t overlap_first_rows(const VxbContext* ctx, const VxbWeight* w, uint32_t 
     auto waves = [&](uint32_t r) { return (r * cols + slots - 1) / slots; };
     // GEMM seconds per row ~ 2 K N / 3.3e15 (link-bound with peers: slower still), quantizer seconds per
     // row ~ 5 K / 4.7e12: the first chunk needs rows_first / rows_rest >= 1755 / N
-    const double ratio = 1755.0 / (double)w->d_out;
+    const double ratio = (double)tunables().overlap_ratio / (double)w->d_out;
     uint32_t r_min = (uint32_t)((double)row_tiles * ratio / (1.0 + ratio)) + 1;
     if (r_min >= row_tiles) return 0;
     uint32_t best = 0;
@@ -1084,6 +1084,8 @@ int vxb_tune(const char* name, int64_t value) {
     if (!strcmp(name, "decode.pair_share_bytes")) { t.decode_pair_share_bytes = (uint32_t)value; return 1; }
     if (!strcmp(name, "decode.l2_prefetch")) { t.decode_l2_prefetch = value != 0; return 1; }
     if (!strcmp(name, "gemm.overlap_k1")) { t.overlap_k1 = value != 0; return 1; }
+    if (!strcmp(name, "gemm.lean_regs")) { t.gemm_lean_regs = value != 0; return 1; }
+    if (!strcmp(name, "gemm.overlap_ratio")) { t.overlap_ratio = (uint32_t)value; return 1; }
     return 0;
 }
 

@@ -406,6 +406,8 @@ struct Tunables {
     uint32_t decode_pair_share_bytes;   // largest per-CTA weight share the decode kernel runs as two CTAs per SM
     bool decode_l2_prefetch;            // weight producers ask L2 for the tile one ring-depth ahead
     bool overlap_k1;                    // large batches: quantize the later rows under the GEMM of the first ones
+    bool gemm_lean_regs;                // launch the 128-register forms of the GEMM kernels
+    uint32_t overlap_ratio;             // rows_first / rows_rest >= overlap_ratio / d_out when a batch is cut in two
 };
 Tunables& tunables();
 

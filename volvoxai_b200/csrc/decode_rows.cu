@@ -67,7 +67,7 @@ constexpr uint32_t kXposePitch = 33;       // ints per row of the epilogue trans
 template <uint32_t MT> struct RowsCfg {
     static constexpr uint32_t kXAtom = MT * kRK;   // one [MT x 128 B] activation tile (MT >= 8: whole swizzle atoms)
     static constexpr uint32_t kUmmaM = MT <= 64 ? 64 : 128;                  // rows the MMA spans
-    static constexpr bool kParkAll = MT <= 32;   // few token rows: the epilogue parks the whole tile at once
+    static constexpr bool kParkAll = MT <= 64;   // up to 64 token rows (M = 64 layout): the epilogue parks the whole tile at once
     // parking area of the epilogue: the whole [rows, umma_n] tile (pitch umma_n + 4 ints) for few
     // token rows, else two [MT][33] buffers for 32-channel chunks
     // whole 32-channel chunks per row, + 4 ints (pitch = 4 mod 32: 16-byte row stores hit distinct banks)
@@ -109,51 +109,46 @@ __device__ __forceinline__ void stamp(unsigned long long* trace, uint32_t slot) 
 
 __device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
-// Finishes a tile parked in shared memory as int32 [rows][pitch]: thread `col_thread` of 128 takes
-// the channels col_thread, col_thread + 128, ... and of each the token rows first_row,
-// first_row + row_step, ..., so that a store instruction covers consecutive channels of one row.
+// Finishes a tile parked in shared memory as int32 [rows][pitch].  The (row, channel) pairs of the
+// tile are dealt out flat over the `workers` participating threads (worker index `me`): consecutive
+// threads take consecutive channels of one row, so a store instruction covers a contiguous run of
+// a row whatever the tile's width, and narrow tiles still keep every thread busy.
 __device__ __forceinline__ void finish_parked(const DecodeRowsArgs& args, const int32_t* parked, uint32_t pitch,
                                               const float* s_ws, const float* s_bias, const float* s_as,
-                                              uint32_t c0, uint32_t valid, uint32_t col_thread,
-                                              uint32_t first_row, uint32_t row_step) {
+                                              uint32_t c0, uint32_t valid, uint32_t me, uint32_t workers) {
     const EpilogueParams& ep = args.epi;
     const float zero_f = __int2float_rn(ep.out_zero);
     const float lo_f = __int2float_rn(ep.out_lo), hi_f = __int2float_rn(ep.out_hi);
     if (ep.mode == kEpiF32 && ep.act == 1u) {
         // channel pairs (gate, up) -> one output column each
-        for (uint32_t o = col_thread; 2u * o + 1u < valid; o += 128) {
-            const float wg = s_ws[2 * o], wu = s_ws[2 * o + 1], bg = s_bias[2 * o], bu = s_bias[2 * o + 1];
-            const size_t at = (size_t)(c0 >> 1) + o;
-            for (uint32_t mm = first_row; mm < args.rows; mm += row_step) {
-                const float asv = s_as[mm];
-                const float g = epi_f32(parked[mm * pitch + 2 * o], asv, wg, bg);
-                const float u = epi_f32(parked[mm * pitch + 2 * o + 1], asv, wu, bu);
-                ((float*)ep.out)[(size_t)mm * ep.ld + at] = epi_silu_mul(g, u);
-            }
+        const uint32_t pairs = valid >> 1, total = pairs * args.rows;
+        for (uint32_t idx = me; idx < total; idx += workers) {
+            const uint32_t mm = idx / pairs, o = idx - mm * pairs;
+            const float asv = s_as[mm];
+            const float g = epi_f32(parked[mm * pitch + 2 * o], asv, s_ws[2 * o], s_bias[2 * o]);
+            const float u = epi_f32(parked[mm * pitch + 2 * o + 1], asv, s_ws[2 * o + 1], s_bias[2 * o + 1]);
+            ((float*)ep.out)[(size_t)mm * ep.ld + (c0 >> 1) + o] = epi_silu_mul(g, u);
         }
         return;
     }
-    for (uint32_t col = col_thread; col < valid; col += 128) {
-        const float wsv = s_ws[col];
-        const float bf = s_bias[col];
-        const int32_t bi = __float_as_int(bf);
+    const uint32_t total = valid * args.rows;
+    for (uint32_t idx = me; idx < total; idx += workers) {
+        const uint32_t mm = idx / valid, col = idx - mm * valid;
+        const int32_t v = parked[mm * pitch + col];
+        const float asv = s_as[mm], wsv = s_ws[col], bf = s_bias[col];
         const size_t at = (size_t)c0 + col;
-#pragma unroll 4
-        for (uint32_t mm = first_row; mm < args.rows; mm += row_step) {
-            const int32_t v = parked[mm * pitch + col];
-            const float asv = s_as[mm];
-            if (ep.mode == kEpiF32) {
-                float y = epi_f32(v, asv, wsv, bf);
-                if (ep.residual) y = __fadd_rn(y, __ldg(ep.residual + (size_t)mm * ep.ld_res + at));
-                ((float*)ep.out)[(size_t)mm * ep.ld + at] = y;
-            } else if (ep.mode == kEpiI8) {
-                const int32_t qv = (ep.fast_div != 0 && div_const_row_ok(asv))
-                    ? epi_i8_v2<true>(v + bi, asv, wsv, ep.out_scale, ep.out_rcp, zero_f, lo_f, hi_f, ep.out_zero)
-                    : epi_i8_v2<false>(v + bi, asv, wsv, ep.out_scale, ep.out_rcp, zero_f, lo_f, hi_f, ep.out_zero);
-                ((int8_t*)ep.out)[(size_t)mm * ep.ld + at] = (int8_t)qv;
-            } else {
-                ((int32_t*)ep.out)[(size_t)mm * ep.ld + at] = v;
-            }
+        if (ep.mode == kEpiF32) {
+            float y = epi_f32(v, asv, wsv, bf);
+            if (ep.residual) y = __fadd_rn(y, __ldg(ep.residual + (size_t)mm * ep.ld_res + at));
+            ((float*)ep.out)[(size_t)mm * ep.ld + at] = y;
+        } else if (ep.mode == kEpiI8) {
+            const int32_t bi = __float_as_int(bf);
+            const int32_t qv = (ep.fast_div != 0 && div_const_row_ok(asv))
+                ? epi_i8_v2<true>(v + bi, asv, wsv, ep.out_scale, ep.out_rcp, zero_f, lo_f, hi_f, ep.out_zero)
+                : epi_i8_v2<false>(v + bi, asv, wsv, ep.out_scale, ep.out_rcp, zero_f, lo_f, hi_f, ep.out_zero);
+            ((int8_t*)ep.out)[(size_t)mm * ep.ld + at] = (int8_t)qv;
+        } else {
+            ((int32_t*)ep.out)[(size_t)mm * ep.ld + at] = v;
         }
     }
 }
@@ -197,8 +192,31 @@ decode_rows_kernel(const __grid_constant__ DecodeRowsArgs args) {
     const bool double_buffered = tiles > 1;                       // else one accumulator, reused
     const uint32_t acc_stride = args.tmem_cols / 2;              // columns between the two accumulators
 
+    // Weight producer p owns the stages p, p+P, ... (the ring depth is a multiple of P): it initialises
+    // their barriers itself and requests its first ring-full of weights at once, before the CTA-wide
+    // set-up below (TMEM allocation, the other barriers) has finished - the weight stream is the
+    // critical path of the kernel and depends on nothing else.
+    struct ProducerState { uint32_t kb; int32_t channel; uint32_t w_sm, fb, eb, stage, phase, i, u; };
+    ProducerState prod{};
+    const bool is_producer = warp >= kXWarp && warp < kXWarp + kProducerWarps - 1 && lane == 0 && warp - kXWarp < args.producers;
+    if (is_producer) {
+        const uint32_t p = warp - kXWarp, P = args.producers;
+        const uint32_t total = tiles * num_kb, own = stages / P;
+        for (uint32_t st = p; st < stages; st += P) { mbar_init(full(st), 1); mbar_init(empty(st), 1); }
+        fence_barrier_init();
+        prod.kb = p; prod.channel = (int32_t)first_channel;
+        while (prod.kb >= num_kb) { prod.kb -= num_kb; prod.channel += (int32_t)args.tile_rows; }
+        prod.w_sm = w_addr(p); prod.fb = full(p); prod.eb = empty(p);
+        prod.i = p;
+        for (; prod.i < total && prod.u < own; prod.i += P, prod.u++) {
+            mbar_expect_tx(prod.fb, stage_tx);
+            tma_load_2d(prod.w_sm, &args.tmap_w, prod.fb, (int32_t)(prod.kb * kRK), prod.channel);
+            prod.kb += P; while (prod.kb >= num_kb) { prod.kb -= num_kb; prod.channel += (int32_t)args.tile_rows; }
+            prod.w_sm += lay.w_bytes * P; prod.fb += 8 * P; prod.eb += 8 * P;
+            if (++prod.stage == own) { prod.stage = 0; prod.phase ^= 1u; prod.w_sm = w_addr(p); prod.fb = full(p); prod.eb = empty(p); }
+        }
+    }
     if (warp == 1) {
-        for (uint32_t s = lane; s < stages; s += 32) { mbar_init(full(s), 1); mbar_init(empty(s), 1); }
         if (lane < x_slots) { mbar_init(xfull(lane), 1); mbar_init(xempty(lane), args.issuers); }
         if (lane == 0) {
             mbar_init(tmem_full(0), args.issuers); mbar_init(tmem_full(1), 1);
@@ -245,27 +263,25 @@ decode_rows_kernel(const __grid_constant__ DecodeRowsArgs args) {
         // Weights depend on nothing that runs before this kernel, so these threads never wait
         // for the preceding kernel: the ring is full before the activations may be read.
         const uint32_t p = warp - kXWarp, P = args.producers;
-        if (lane == 0 && p < P) {
+        if (is_producer) {
+            // the first ring-full was requested in the prologue; from here on a stage is re-armed as soon
+            // as the MMAs that read it have completed
             const uint32_t total = tiles * num_kb, own = stages / P;
             const uint32_t w0 = w_addr(p), f0 = full(p), e0 = empty(p), wstep = lay.w_bytes * P;
-            uint32_t kb = p; int32_t channel = (int32_t)first_channel;
-            while (kb >= num_kb) { kb -= num_kb; channel += (int32_t)args.tile_rows; }
-            uint32_t w_sm = w0, fb = f0, eb = e0, stage = 0, phase = 0;
-            bool ok = true;
             // block one ring-depth ahead of the one being copied (stages is a multiple of P, so this
-            // producer owns it too): optionally requested from L2 early, which keeps twice the ring in
-            // flight towards HBM without any shared memory
-            uint32_t pkb = kb + stages; int32_t pchannel = channel;
+            // producer owns it too): optionally requested from L2 early
+            uint32_t pkb = prod.kb + stages; int32_t pchannel = prod.channel;
             while (pkb >= num_kb) { pkb -= num_kb; pchannel += (int32_t)args.tile_rows; }
-            for (uint32_t i = p, u = 0; i < total; i += P, u++) {
-                if (args.l2_prefetch && i + stages < total) tma_prefetch_l2_2d(&args.tmap_w, (int32_t)(pkb * kRK), pchannel);
+            bool ok = true;
+            for (; prod.i < total; prod.i += P, prod.u++) {
+                if (args.l2_prefetch && prod.i + stages < total) tma_prefetch_l2_2d(&args.tmap_w, (int32_t)(pkb * kRK), pchannel);
                 pkb += P; while (pkb >= num_kb) { pkb -= num_kb; pchannel += (int32_t)args.tile_rows; }
-                if (u >= own && !mbar_wait(eb, phase ^ 1u, abort_flag)) { ok = false; break; }
-                mbar_expect_tx(fb, stage_tx);
-                tma_load_2d(w_sm, &args.tmap_w, fb, (int32_t)(kb * kRK), channel);
-                kb += P; while (kb >= num_kb) { kb -= num_kb; channel += (int32_t)args.tile_rows; }
-                w_sm += wstep; fb += 8 * P; eb += 8 * P;
-                if (++stage == own) { stage = 0; phase ^= 1u; w_sm = w0; fb = f0; eb = e0; }
+                if (!mbar_wait(prod.eb, prod.phase ^ 1u, abort_flag)) { ok = false; break; }
+                mbar_expect_tx(prod.fb, stage_tx);
+                tma_load_2d(prod.w_sm, &args.tmap_w, prod.fb, (int32_t)(prod.kb * kRK), prod.channel);
+                prod.kb += P; while (prod.kb >= num_kb) { prod.kb -= num_kb; prod.channel += (int32_t)args.tile_rows; }
+                prod.w_sm += wstep; prod.fb += 8 * P; prod.eb += 8 * P;
+                if (++prod.stage == own) { prod.stage = 0; prod.phase ^= 1u; prod.w_sm = w0; prod.fb = f0; prod.eb = e0; }
             }
             if (!ok) {
                 // drain: give this thread's own copies in flight a bounded time to land
@@ -371,6 +387,9 @@ decode_rows_kernel(const __grid_constant__ DecodeRowsArgs args) {
                 pdl_wait();
                 if (e < 128) s_as[e] = (e < args.rows && ep.mode != kEpiAcc) ? __ldg(ep.row_scales + e) : 0.0f;
             }
+            if constexpr (Cfg::kParkAll) {
+                if (tiles == 1) break;   // the single tile is drained by every warp of the CTA, below
+            }
             const bool waited = mbar_wait(tmem_full(acc), acc_phase, abort_flag);
             // make the give-up decision uniform across the four epilogue warps (the first
             // barrier also publishes the staged constants)
@@ -419,9 +438,8 @@ decode_rows_kernel(const __grid_constant__ DecodeRowsArgs args) {
                         }
                     }
                 }
-                if (tiles == 1) break;   // every thread of the CTA finishes the parked tile below
                 epi_bar();
-                finish_parked(args, s_xpose, pitch, s_ws, s_bias, s_as, c0, valid, e, 0u, 1u);
+                finish_parked(args, s_xpose, pitch, s_ws, s_bias, s_as, c0, valid, e, 128u);
             } else {
             // TMEM hands each thread one token row; the stores want one channel per lane. Each
             // 32-channel chunk is therefore transposed through shared memory: row threads park
@@ -494,20 +512,54 @@ decode_rows_kernel(const __grid_constant__ DecodeRowsArgs args) {
 
     if constexpr (Cfg::kParkAll) {
         if (tiles == 1) {
-            // The single tile is parked (or a wait gave up, and everybody skips). The loops above
-            // are over for every role, so the whole CTA finishes the tile: four times the threads
-            // of the epilogue warps alone, on what is pure latency at the end of the kernel.
+            // Every role's loop is over.  The accumulators of few token rows sit in one or two TMEM lane
+            // quarters, which only warps with the matching index (warp % 4) can read; a single warp
+            // reading all 32-channel chunks one after the other was a chain of dependent TMEM loads
+            // (over a microsecond at 97 channels).  All warps of the CTA that can read a quarter
+            // therefore share its chunks, park them in shared memory, and then the whole CTA finishes
+            // the tile: pure latency at the end of the kernel, spread over every thread.
             __syncwarp();
+            uint32_t ready = 1;
+            if (lane == 0) ready = mbar_wait(tmem_full(0), 0u, abort_flag) ? 1u : 0u;
+            ready = __shfl_sync(0xffffffffu, ready, 0);
+            tc_fence_after();
+            const uint32_t left = args.n > first_channel ? args.n - first_channel : 0u;
+            const uint32_t valid = left < args.tile_rows ? left : args.tile_rows;
+            const uint32_t pitch = Cfg::park_pitch(args.umma_n);
+            const uint32_t quarter = warp & 3u;
+            if (ready && quarter * 16u < args.rows) {
+                constexpr uint32_t kWarps = ModeCfg<PAIR>::kThreads / 32;
+                const uint32_t sharers = (kWarps - quarter + 3u) / 4u, mine = warp >> 2;
+                const uint32_t taddr = tmem_base + ((quarter * 32u) << 16);
+                const uint32_t m = quarter * 16u + lane;
+                const bool m_ok = lane < 16 && m < args.rows;
+                const uint32_t nchunks = (valid + 31u) >> 5;
+#pragma unroll 1
+                for (uint32_t ci = mine; ci < nchunks; ci += sharers) {
+                    const uint32_t c = ci << 5;
+                    uint32_t r[32];
+                    tmem_ld32(taddr + c, r);
+                    tmem_ld_wait();
+                    for (uint32_t a = 1; a < args.issuers; a++) {   // add the other issuers' accumulators
+                        uint32_t more[32];
+                        tmem_ld32(taddr + a * args.acc_cols + c, more);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; i++) r[i] += more[i];
+                    }
+                    if (m_ok) {
+                        uint4* dst = reinterpret_cast<uint4*>(s_xpose + m * pitch + c);
+#pragma unroll
+                        for (int j = 0; j < 8; j++) dst[j] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+                    }
+                }
+            }
+            if (threadIdx.x == kEpiBase) stamp(args.trace, 4);
+            tc_fence_before();
             __syncthreads();
             if (!*abort_flag) {
                 pdl_wait();
-                constexpr uint32_t kGroups = ModeCfg<PAIR>::kThreads / 128;
-                const uint32_t g = threadIdx.x >> 7;
-                const uint32_t left = args.n > first_channel ? args.n - first_channel : 0u;
-                const uint32_t valid = left < args.tile_rows ? left : args.tile_rows;
-                if (g < kGroups)
-                    finish_parked(args, s_xpose, Cfg::park_pitch(args.umma_n), s_ws, s_bias, s_as, first_channel, valid,
-                                  threadIdx.x & 127u, g, kGroups);
+                finish_parked(args, s_xpose, pitch, s_ws, s_bias, s_as, first_channel, valid, threadIdx.x, ModeCfg<PAIR>::kThreads);
                 if (threadIdx.x == kEpiBase) stamp(args.trace, 5);
             }
         }
@@ -615,7 +667,7 @@ cudaError_t launch_t(const DecodeRowsArgs& args, cudaStream_t stream) {
 }  // namespace
 
 Tunables& tunables() {
-    static Tunables t{kPairShareBytes, false, true};
+    static Tunables t{kPairShareBytes, false, true, false, 1755u};
     return t;
 }
 
