@@ -44,6 +44,7 @@ extern "C" {
 #define VXB_VF_PEERS 2u       /* epilogue can store to peer GPUs (fused all-gather) */
 #define VXB_VF_FUSED_TAIL 4u  /* carries the residual-Add / SiLU*Mul tails of the fp32 epilogue */
 #define VXB_VF_VERIFY 8u      /* verification kernel: explicit request only */
+#define VXB_VF_FUSED_K1 16u   /* quantizes the fp32 rows itself: one launch per linear, fp32 input only */
 
 /*
  * Variant rows.  Fields:
@@ -55,6 +56,7 @@ extern "C" {
  */
 #define VXB_VARIANTS(X) \
     X(DECODE_ROWS,      4, "decode-rows-tcgen05-i8",    "decode_rows_kernel",             0,   0, 128, 544, 1, 204800,   1, 128, 7u, 1u, 0, 1u | 4u,      700) \
+    X(DECODE_FUSED,     7, "decode-fused-tcgen05-i8",   "decode_rows_kernel",             0,   0, 128, 544, 1, 204800,   1,   8, 7u, 1u, 0, 1u | 4u | 16u, 720) \
     X(DECODE_STREAMK,   5, "decode-streamk-tcgen05-i8", "decode_i8_tcgen05_kernel",       0, 128, 128, 192, 1, 107520,   1, 128, 7u, 1u, 0, 0u,           300) \
     X(GEMV_DP4A,        1, "gemv-dp4a",                 "gemv_dp4a_kernel",               0,   0,   0, 256, 1,  65536,   1,  32, 7u, 1u, 0, 0u,           200) \
     X(SIMT_DP4A,        3, "simt-dp4a",                 "gemm_simt_kernel",               4, 128,   0, 128, 1,      0,   1,   0, 7u, 1u, 0, 8u,             1) \
@@ -122,8 +124,9 @@ VXB_PLAN_API const VxbVariant* vxb_variant_info(uint32_t index);
 /* Builds the launch plan of one call or refuses it.  Returns 1 and fills *out, or 0 with the
  * reason in `why` (optional buffer).  An explicit route is honoured or refused, never replaced;
  * the automatic route picks, among the admitted variants flagged VXB_VF_AUTO, by these rules:
- *   per-channel scales: rows <= 128 -> the decode kernel, else the tensor-core GEMM, by pairs
- *     of CTAs once there are two waves of 128 x 256 tiles;
+ *   per-channel scales: rows <= 128 -> the decode kernel (its single-launch form, which quantizes the
+ *     rows itself, for fp32 input of up to 8 rows with a padded K of at most 8192 and d_in a multiple
+ *     of 4), else the tensor-core GEMM, by pairs of CTAs once there are two waves of 128 x 256 tiles;
  *   grouped scales: 1-2 rows (3-4 with <= 32 MB of weights) -> the streaming GEMV (over the 4-bit
  *     words when kept), else the tensor-core kernel with a per-group accumulator drain. */
 VXB_PLAN_API int vxb_plan(const VxbPlanQuery* query, VxbLaunchPlan* out, char* why, uint32_t why_bytes);

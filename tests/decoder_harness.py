@@ -117,16 +117,20 @@ class W8A8Decoder:
         self.k_cache[li].index_copy_(0, rows, k.reshape(-1, nkv, hd).to(self.k_cache.dtype))
         self.v_cache[li].index_copy_(0, rows, v.reshape(-1, nkv, hd).to(self.v_cache.dtype))
         if decode:
-            # attend over the sequence's cache rows (gathered through its block table), masked beyond its position
+            # attend over the sequence's cache rows (gathered through its block table), masked beyond its
+            # position; the query heads of one KV head ride along as query positions, so K and V are
+            # neither expanded nor converted
             all_rows = (self.block_table[:, :, None] * KV_BLOCK + torch.arange(KV_BLOCK, device=x.device)).reshape(batch, -1)
-            kk = self.k_cache[li][all_rows].float().transpose(1, 2)      # [B, KV, L, hd]
-            vv = self.v_cache[li][all_rows].float().transpose(1, 2)
+            kk = self.k_cache[li][all_rows].permute(0, 2, 1, 3)          # [B, KV, L, hd]
+            vv = self.v_cache[li][all_rows].permute(0, 2, 1, 3)
+            qg = q.reshape(batch, nkv, nh // nkv, hd).to(kk.dtype)
             mask = (torch.arange(self.max_len, device=x.device)[None, :] <= positions[:, :1])[:, None, None, :]
-            attn = torch.nn.functional.scaled_dot_product_attention(q.transpose(1, 2), kk, vv, attn_mask=mask, enable_gqa=True)
+            attn = torch.nn.functional.scaled_dot_product_attention(qg, kk, vv, attn_mask=mask).float()
+            attn = attn.reshape(batch, nh * hd)                          # head h = kv * group + g, as the query heads were grouped
         else:
             attn = torch.nn.functional.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
                                                                     is_causal=True, enable_gqa=True)
-        attn = attn.transpose(1, 2).reshape(batch * t, nh * hd).contiguous()
+            attn = attn.transpose(1, 2).reshape(batch * t, nh * hd).contiguous()
         x = ctx.linear_f32_fused(layer["o"], attn, residual=x)
         hmid = ctx.rmsnorm_linear_f32_fused(layer["gate_up"], x, layer["norm2"], c["eps"], silu_mul=True)
         return ctx.linear_f32_fused(layer["down"], hmid, residual=x)

@@ -38,7 +38,7 @@ def rel_err(y, ref):
     return float(np.abs(y[ok].astype(np.float64) - ref[ok]).max() / max(rms, 1e-30)) if ok.any() else 0.0
 
 
-ROUTES = {"auto": 0, "gemv": 1, "tcgen05": 2, "simt": 3, "decode": 4, "streamk": 5, "pair": 6}
+ROUTES = {"auto": 0, "gemv": 1, "tcgen05": 2, "simt": 3, "decode": 4, "streamk": 5, "pair": 6, "fused": 7}
 
 
 def run_case(torch, ctx, oracle, case, routes, bias_i32=None, out_zero=0):
@@ -150,7 +150,10 @@ def test_small_m_routes(torch, ctx, oracle, rows, k, n):
     if rows > 4:
         case["x"][3, k // 3] = np.inf
     bias_i32 = rng.integers(-300, 300, size=n).astype(np.int32)
-    run_case(torch, ctx, oracle, case, ["gemv", "decode", "streamk", "tcgen05", "simt"], bias_i32=bias_i32, out_zero=-3)
+    routes = ["gemv", "decode", "streamk", "tcgen05", "simt"]
+    if rows <= 8 and k % 4 == 0:
+        routes += ["fused", "auto"]      # the single-launch decode form (the automatic route for these shapes)
+    run_case(torch, ctx, oracle, case, routes, bias_i32=bias_i32, out_zero=-3)
 
 
 @pytest.mark.parametrize("rows", [33, 48, 64, 65, 100, 127, 128])
@@ -593,6 +596,40 @@ def test_full_size_properties(torch, ctx, oracle, rows, k, n):
     want8 = oracle.requant_rows(acc[:8].cpu().numpy(), s[:8].cpu().numpy(), None, c["ws"], None, os_, 0)
     assert np.array_equal(y8[:8].cpu().numpy(), want8)
     weight.close()
+
+
+@pytest.mark.parametrize("rows,k,n", [(1, 8192, 1000), (8, 8192, 2048), (5, 7000, 333), (8, 128, 8), (3, 4, 5), (7, 2048, 37888)])
+def test_single_launch_decode_form(torch, ctx, oracle, rows, k, n):
+    """Up to 8 fp32 rows, padded K up to 8192: the decode kernel quantizes the rows itself.  Same codes
+    (through the accumulators), scales (through both epilogues) and bytes as the oracle, NaN rows
+    included; and the fused residual / SiLU*Mul tails agree bit for bit with the two-launch form."""
+    from volvoxai_b200 import w8a8
+    rng = np.random.default_rng(rows * 7 + k + n)
+    case = {"x": (rng.standard_normal((rows, k)) * rng.choice([1e-20, 1e-3, 1.0, 300.0], size=(rows, 1))).astype(np.float32),
+            "w": rng.integers(-128, 128, size=(n, k), dtype=np.int8),
+            "ws": rng.uniform(0.001, 0.02, size=n).astype(np.float32),
+            "bias": rng.standard_normal(n).astype(np.float32)}
+    if rows > 2:
+        case["x"][1] = 0
+        case["x"][2, k // 2] = np.nan
+    run_case(torch, ctx, oracle, case, ["fused", "auto", "decode"], bias_i32=rng.integers(-300, 300, size=n).astype(np.int32), out_zero=4)
+    assert w8a8.plan(rows, k, n)[0]["id"] == "DECODE_FUSED"
+    if n % 2 == 0:
+        weight = w8a8.Weight.from_i8(ctx, case["w"], case["ws"], bias_f32=case["bias"])
+        xd = dev(torch, case["x"])
+        res = torch.randn((rows, n), device="cuda")
+        got = {}
+        for flag in (1, 0):
+            w8a8.tune("decode.fused", flag)
+            a = ctx.linear_f32_fused(weight, xd, residual=res)
+            route = w8a8.last_route()
+            b = ctx.linear_f32_fused(weight, xd, silu_mul=True)
+            ctx.synchronize()
+            assert ("decode-fused" in route) == bool(flag), route
+            got[flag] = (a.view(torch.int32).clone(), b.view(torch.int32).clone())
+        w8a8.tune("decode.fused", 1)
+        assert torch.equal(got[0][0], got[1][0]) and torch.equal(got[0][1], got[1][1])
+        weight.close()
 
 
 @pytest.mark.parametrize("rows", wl.GEMV_ROWS)

@@ -40,7 +40,13 @@ def test_variant_table_is_well_formed():
 
 
 def test_automatic_route_boundaries_per_channel():
-    assert pick(1, 4096, 4096)["id"] == "DECODE_ROWS"
+    assert pick(1, 4096, 4096)["id"] == "DECODE_FUSED"                       # fp32 rows in: one launch
+    assert pick(8, 4096, 14336)["id"] == "DECODE_FUSED"
+    assert pick(8, 4096, 14336, fp32_input=False)["id"] == "DECODE_ROWS"      # prepared activations
+    assert pick(9, 4096, 14336)["id"] == "DECODE_ROWS"                       # more than 8 rows
+    assert pick(8, 14336, 4096)["id"] == "DECODE_ROWS"                       # padded K beyond 8192
+    assert pick(4, 4098, 512)["id"] == "DECODE_ROWS"                         # d_in not a multiple of 4
+    assert pick(8, 1024, 512, fused_tail=True)["id"] == "DECODE_FUSED"
     assert pick(128, 1024, 3072)["id"] == "DECODE_ROWS"
     assert pick(129, 1024, 3072)["id"] == "TCGEN05"
     # two waves of 128 x 256 tiles on 148 SMs = 296 tiles: 8192 x 14336 has 64 * 56 = 3584
@@ -81,6 +87,12 @@ def test_explicit_requests_are_honoured_or_refused_never_replaced():
                        (w8a8.ROUTE_DECODE, "DECODE_ROWS"), (w8a8.ROUTE_DECODE_STREAMK, "DECODE_STREAMK"),
                        (w8a8.ROUTE_TCGEN05_PAIR, "TCGEN05_PAIR")):
         assert pick(16, 1024, 512, route=route)["id"] == vid
+    assert pick(8, 1024, 512, route=w8a8.ROUTE_DECODE_FUSED)["id"] == "DECODE_FUSED"
+    for kw in (dict(rows=9), dict(fp32_input=False), dict(k=1026)):
+        args = dict(rows=8, k=1024, n=512, route=w8a8.ROUTE_DECODE_FUSED, fp32_input=True)
+        args.update(kw)
+        plan, why = w8a8.plan(args.pop("rows"), args.pop("k"), args.pop("n"), **args)
+        assert plan is None and why
     for route, rows in ((w8a8.ROUTE_GEMV, 33), (w8a8.ROUTE_DECODE, 129), (w8a8.ROUTE_DECODE_STREAMK, 129)):
         plan, why = w8a8.plan(rows, 1024, 512, route=route)
         assert plan is None and "rows" in why
@@ -91,7 +103,7 @@ def test_explicit_requests_are_honoured_or_refused_never_replaced():
     plan, why = w8a8.plan(1, 132105, 8)
     assert plan is None and "overflow" in why
     # fused epilogue tails exist on the decode kernel and both GEMM kernels only
-    assert pick(8, 1024, 512, fused_tail=True)["id"] == "DECODE_ROWS"
+    assert pick(16, 1024, 512, fused_tail=True)["id"] == "DECODE_ROWS"
     plan, why = w8a8.plan(8, 1024, 512, fused_tail=True, route=w8a8.ROUTE_GEMV)
     assert plan is None and "tail" in why
 
@@ -106,7 +118,9 @@ def test_exact_launch_geometry():
     # decode: every CTA owns ceil(N / 148) whole channels (even, so gate/up pairs never straddle CTAs)
     p = pick(8, 4096, 14336)
     assert (p["tile_columns"], p["grid"], p["threads"], p["tile_rows"]) == (98, 147, 544, 8)
-    assert (p["quantizer"], p["quantizer_cluster"], p["quantizer_grid"]) == (3, 4, 32)   # cluster quantizer, 4 CTAs per row
+    assert (p["launches"], p["quantizer"], p["workspace_bytes"]) == (1, 0, 0)           # single launch, no scratch
+    p = pick(16, 4096, 14336)
+    assert (p["launches"], p["quantizer"], p["quantizer_cluster"], p["quantizer_grid"]) == (2, 3, 4, 64)   # cluster quantizer, 4 CTAs per row
     p = pick(64, 1024, 3072)
     assert (p["tile_columns"], p["grid"], p["threads"], p["tile_rows"]) == (22, 140, 384, 64)   # small share: two CTAs per SM
     p = pick(8, 4096, 14336, fp32_input=False)

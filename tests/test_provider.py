@@ -37,17 +37,24 @@ def host():
     fake.fake_host_contract_marker.restype = C.c_uint64
     fake.fake_host_provider_struct_size.restype = C.c_size_t
     fake.fake_host_max_rank.restype = C.c_size_t
+    vp, sz = C.c_void_p, C.c_size_t
+    fake.fake_host_compile.argtypes = [C.c_char_p, vp, sz, vp, vp, vp, vp, sz, sz, C.c_int, C.c_char_p]
+    fake.fake_host_execute.argtypes = [vp, vp, vp, vp, vp, vp, sz, vp, vp, vp, vp, sz]
+    fake.fake_host_register.argtypes = [vp]
+    fake.fake_host_register_broken.argtypes = [vp, C.c_int]
+    fake.fake_host_context_create.argtypes = [C.c_int]
     return fake, prov
 
 
 def test_descriptor_passes_the_exact_contract_checks(host):
     fake, prov = host
     assert fake.fake_host_contract_marker() == 0x565850524F563032
-    assert fake.fake_host_register(prov.vxb200_provider_register) == OK
+    reg = C.cast(prov.vxb200_provider_register, C.c_void_p)
+    assert fake.fake_host_register(reg) == OK
     assert fake.fake_host_provider_name() == b"b200-w8a8"
-    assert fake.fake_host_register(prov.vxb200_provider_register) == INVALID      # duplicate name
+    assert fake.fake_host_register(reg) == INVALID      # duplicate name
     for variant in range(4):     # wrong struct size, wrong marker, reserved name, missing callback
-        assert fake.fake_host_register_broken(prov.vxb200_provider_descriptor, variant) == INVALID
+        assert fake.fake_host_register_broken(C.cast(prov.vxb200_provider_descriptor, C.c_void_p), variant) == INVALID
 
 
 def test_runtime_create_reports_unavailable_without_a_b200(host):
@@ -55,7 +62,7 @@ def test_runtime_create_reports_unavailable_without_a_b200(host):
     if torch.cuda.is_available():
         pytest.skip("this box has a CUDA device")
     fake, prov = host
-    fake.fake_host_register(prov.vxb200_provider_register)
+    fake.fake_host_register(C.cast(prov.vxb200_provider_register, C.c_void_p))
     assert fake.fake_host_runtime_create() == UNAVAILABLE
     assert fake.fake_host_message()
 
@@ -100,7 +107,7 @@ def test_provider_compiles_and_executes_the_fixture_packages(host):
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     fake, prov = host
-    fake.fake_host_register(prov.vxb200_provider_register)
+    fake.fake_host_register(C.cast(prov.vxb200_provider_register, C.c_void_p))
     assert fake.fake_host_runtime_create() == OK
     # static W8A8 island
     ins, outs = [("x", DT_F32, (6, 96))], [("y", DT_F32, (6, 24)), ("y_q", DT_I8, (6, 24))]

@@ -14,6 +14,7 @@ DT_U8, DT_I8 = 5, 6
 OP_PACKED_LINEAR = 1036
 ROUTE_AUTO, ROUTE_GEMV, ROUTE_TCGEN05, ROUTE_SIMT, ROUTE_DECODE, ROUTE_DECODE_STREAMK = 0, 1, 2, 3, 4, 5
 ROUTE_TCGEN05_PAIR = 6
+ROUTE_DECODE_FUSED = 7
 
 # Every symbol include/vxb200_w8a8.h declares.
 EXPORTS = [
@@ -46,7 +47,7 @@ DIAG_EXPORTS = ["vxb_context_trace", "vxb_measure_mma_issue", "vxb_context_set_w
 
 EPI_ACC, EPI_F32, EPI_I8 = 1, 2, 4
 WEIGHT_PER_CHANNEL, WEIGHT_GROUPED, WEIGHT_W4_WORDS = 1, 2, 4
-VF_AUTO, VF_PEERS, VF_FUSED_TAIL, VF_VERIFY = 1, 2, 4, 8
+VF_AUTO, VF_PEERS, VF_FUSED_TAIL, VF_VERIFY, VF_FUSED_K1 = 1, 2, 4, 8, 16
 INJECT_LAUNCH, INJECT_ALLOCATION = 1, 2
 
 

@@ -270,6 +270,39 @@ uint32_t weight_kind(const VxbWeight* w) {
     return !w->group ? VXB_WEIGHT_PER_CHANNEL : w->w4 ? VXB_WEIGHT_W4_WORDS : VXB_WEIGHT_GROUPED;
 }
 
+VxbPlanQuery plan_query(const VxbContext* ctx, const VxbWeight* w, uint32_t rows, const EpilogueParams& epi, int requested, bool fp32_input) {
+    VxbPlanQuery query{};
+    query.rows = rows; query.k = w->d_in; query.n = w->d_out;
+    query.weight_kind = weight_kind(w); query.group_size = w->group;
+    query.epilogue = epi.mode == kEpiAcc ? VXB_EPI_ACC : epi.mode == kEpiF32 ? VXB_EPI_F32 : VXB_EPI_I8;
+    query.requested_route = requested; query.n_peers = epi.n_peers;
+    query.fused_tail = (epi.residual || epi.act) ? 1u : 0u;
+    query.fp32_input = fp32_input ? 1u : 0u;
+    query.sm_count = (uint32_t)ctx->sm_count;
+    query.pair_clusters = (uint32_t)(gemm_pair_clusters() > 0 ? gemm_pair_clusters() : 0);
+    return query;
+}
+
+// The decode kernel's single-launch form: the CTAs quantize the fp32 rows themselves.
+int launch_decode_fused(VxbContext* ctx, const VxbWeight* w, const float* x, uint32_t rows, const EpilogueParams& epi) {
+    if (!w->has_tmap) return fail(0, "no tensor map for this weight (driver entry point missing)");
+    if ((uintptr_t)x & 15u) return fail(0, "the single-launch decode form needs 16-byte aligned activations");
+    DecodeRowsArgs a{};
+    a.tmap_w = w->tmap_rows;
+    a.rows = rows; a.n = w->d_out; a.kpad = w->kpad;
+    a.tile_rows = w->tile_rows; a.tiles_per_cta = w->tiles_per_cta;
+    a.w_stage_bytes = round_up(w->tile_rows * kKAlign, 1024u);
+    a.x_f32 = x; a.k = w->d_in;
+    a.epi = epi; a.status = ctx->status; a.trace = ctx->trace;
+    if (!decode_rows_configure(a)) return fail(0, "no launch shape for the single-launch decode form (rows %u, d_out %u)", rows, w->d_out);
+    ProfileScope scope(ctx, 1);
+    LAUNCH_TRY(launch_decode_rows(a, ctx->stream));
+    count_launch();
+    const char* tail = epi.mode == kEpiAcc ? "acc" : epi.mode == kEpiF32 ? "e1" : "e2";
+    snprintf(g_route, sizeof g_route, "%s+%s", vxb_variant_info(VXB_VARIANT_DECODE_FUSED)->route_label, tail);
+    return 1;
+}
+
 // int32 GEMM + epilogue over already-quantized activations q [rows, kpad].  The kernel is the one
 // vxb_plan() names for this call: the same function tests call without a GPU.
 int run_gemm(VxbContext* ctx, const VxbWeight* w, const int8_t* q, uint32_t rows,
@@ -282,14 +315,8 @@ int run_gemm(VxbContext* ctx, const VxbWeight* w, const int8_t* q, uint32_t rows
         CUDA_TRY(gemm_pair_prepare(), 0);
         ctx->pair_ready = true;
     }
-    VxbPlanQuery query{};
-    query.rows = rows; query.k = w->d_in; query.n = w->d_out;
-    query.weight_kind = weight_kind(w); query.group_size = w->group;
-    query.epilogue = epi.mode == kEpiAcc ? VXB_EPI_ACC : epi.mode == kEpiF32 ? VXB_EPI_F32 : VXB_EPI_I8;
-    query.requested_route = requested; query.n_peers = epi.n_peers;
-    query.fused_tail = (epi.residual || epi.act) ? 1u : 0u;
-    query.sm_count = (uint32_t)ctx->sm_count;
-    query.pair_clusters = (uint32_t)(gemm_pair_clusters() > 0 ? gemm_pair_clusters() : 0);
+    if (requested == VXB_ROUTE_DECODE_FUSED) return fail(0, "the single-launch decode form starts from fp32 rows");
+    const VxbPlanQuery query = plan_query(ctx, w, rows, epi, requested, false);
     VxbLaunchPlan plan;
     char why[160];
     if (vxb_plan(&query, &plan, why, sizeof why) != 1) return fail(0, "%s", why);
@@ -416,7 +443,11 @@ int quantize_into_scratch(VxbContext* ctx, const VxbWeight* w, const float* x, u
 
 // Rows of the first chunk when a large batch is cut in two so that the quantizer of the later rows
 // runs under the GEMM of the first ones (K1 is HBM-bound, K2 tensor-bound or link-bound): 0 = do
-// not split.  The first chunk is the smallest number of row tiles whose GEMM lasts at least as
+// not split.  Off unless the tunable "gemm.overlap_k1" is set: on the B200 the GEMM kernels hold 168
+// registers per thread, so no quantizer CTA fits beside them and the second quantizer simply queues
+// behind the first GEMM (325 -> 381 us per step at M 8192, K 4096, N 14336); with 128-register
+// builds of the GEMM kernels the quantizer did run underneath, and slowed the GEMM by as much as
+// it saved (361 -> 364 us).  The first chunk is the smallest number of row tiles whose GEMM lasts at least as
 // long as the quantizer of the rest and that adds no wave of tiles to the launch pair.
 uint32_t overlap_first_rows(const VxbContext* ctx, const VxbWeight* w, uint32_t rows, const EpilogueParams& epi, int route) {
     if (!tunables().overlap_k1 || w->group || rows < 2048) return 0;
@@ -449,6 +480,18 @@ uint32_t overlap_first_rows(const VxbContext* ctx, const VxbWeight* w, uint32_t 
 int quantize_then_gemm(VxbContext* ctx, const VxbWeight* w, const float* x, uint32_t rows, const EpilogueParams& epi,
                        int route, const char* prefix, const float* norm_weight = nullptr, float epsilon = 0.0f,
                        float* norm_out = nullptr) {
+    if (!norm_weight && (route == VXB_ROUTE_AUTO || route == VXB_ROUTE_DECODE_FUSED) && rows <= 8 && tunables().decode_fused) {
+        // up to 8 rows: one launch, the decode kernel quantizes the rows itself (when the plan admits it)
+        const VxbPlanQuery query = plan_query(ctx, w, rows, epi, route, true);
+        VxbLaunchPlan plan;
+        char why[160];
+        const int planned = vxb_plan(&query, &plan, why, sizeof why);
+        if (planned == 1 && plan.variant == VXB_VARIANT_DECODE_FUSED && ((uintptr_t)x & 15u) == 0)
+            return launch_decode_fused(ctx, w, x, rows, epi);
+        if (route == VXB_ROUTE_DECODE_FUSED) return fail(0, "%s", planned == 1 ? "activations are not 16-byte aligned" : why);
+    } else if (route == VXB_ROUTE_DECODE_FUSED) {
+        return fail(0, "the single-launch decode form serves up to 8 rows without a fused RMSNorm");
+    }
     uint32_t first = norm_weight ? 0u : overlap_first_rows(ctx, w, rows, epi, route);
     if (first) {
         cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
@@ -846,6 +889,14 @@ int vxb_linear_acc_i32(VxbContext* ctx, const VxbWeight* w, const float* x, uint
                                  cudaMemcpyDeviceToDevice, ctx->stream), -1);
     EpilogueParams epi{};
     epi.mode = kEpiAcc; epi.out = acc; epi.ld = w->d_out;
+    if (route == VXB_ROUTE_DECODE_FUSED) {
+        // q_out / scales_out came from the stand-alone quantizer above; the accumulators from the kernel's own quantization
+        const VxbPlanQuery query = plan_query(ctx, w, rows, epi, route, true);
+        VxbLaunchPlan plan;
+        char why[160];
+        if (vxb_plan(&query, &plan, why, sizeof why) != 1) return fail(0, "%s", why);
+        return launch_decode_fused(ctx, w, x, rows, epi);
+    }
     return run_gemm(ctx, w, (const int8_t*)ctx->q.ptr, rows, epi, route, "k1+");
 }
 
@@ -1083,8 +1134,8 @@ int vxb_tune(const char* name, int64_t value) {
     Tunables& t = tunables();
     if (!strcmp(name, "decode.pair_share_bytes")) { t.decode_pair_share_bytes = (uint32_t)value; return 1; }
     if (!strcmp(name, "decode.l2_prefetch")) { t.decode_l2_prefetch = value != 0; return 1; }
+    if (!strcmp(name, "decode.fused")) { t.decode_fused = value != 0; return 1; }
     if (!strcmp(name, "gemm.overlap_k1")) { t.overlap_k1 = value != 0; return 1; }
-    if (!strcmp(name, "gemm.lean_regs")) { t.gemm_lean_regs = value != 0; return 1; }
     if (!strcmp(name, "gemm.overlap_ratio")) { t.overlap_ratio = (uint32_t)value; return 1; }
     return 0;
 }

@@ -361,6 +361,10 @@ struct DecodeRowsArgs {
     uint32_t stages, umma_n, tmem_cols, acc_cols, issuers, producers, x_chunk_blocks, x_slots, pair;
     uint32_t w_stage_bytes;   // round_up(tile_rows * 128, 1024)
     uint32_t l2_prefetch;     // 1: producers prefetch the tile one ring-depth ahead into L2
+    // single-launch form (rows <= 8): the CTA quantizes the fp32 rows itself into shared memory, in
+    // the UMMA operand layout, while its weight ring fills; tmap_x and epi.row_scales are unused then
+    const float* x_f32;       // [rows, k] fp32 activations, or null (activations come prepared through tmap_x)
+    uint32_t k;               // logical width of x_f32 (a multiple of 4)
     EpilogueParams epi;
     int* status;
     unsigned long long* trace;   // optional [grid][kTraceSlots] of %globaltimer stamps, or null
@@ -405,9 +409,9 @@ cudaError_t launch_div_const_check(int exponent, uint32_t neighbours, uint32_t s
 struct Tunables {
     uint32_t decode_pair_share_bytes;   // largest per-CTA weight share the decode kernel runs as two CTAs per SM
     bool decode_l2_prefetch;            // weight producers ask L2 for the tile one ring-depth ahead
-    bool overlap_k1;                    // large batches: quantize the later rows under the GEMM of the first ones
-    bool gemm_lean_regs;                // launch the 128-register forms of the GEMM kernels
+    bool overlap_k1;                    // large batches: quantize the later rows under the GEMM of the first ones (off: measured slower)
     uint32_t overlap_ratio;             // rows_first / rows_rest >= overlap_ratio / d_out when a batch is cut in two
+    bool decode_fused;                  // up to 8 fp32 rows: the decode kernel quantizes them itself (one launch)
 };
 Tunables& tunables();
 

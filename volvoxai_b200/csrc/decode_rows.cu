@@ -29,6 +29,7 @@
 // All mbarrier waits are bounded; on expiry the kernel raises the status word, drains and
 // frees its TMEM.  No CTA waits for another CTA.
 #include "tcgen05.cuh"
+#include "quantize.cuh"
 
 namespace vxb {
 
@@ -78,6 +79,7 @@ template <uint32_t MT> struct RowsCfg {
 };
 
 constexpr uint32_t kMaxXSlots = 8;
+constexpr uint32_t kFusedMaxKpad = 8192;   // single-launch form: 8 rows x padded K of int8 stay in shared memory (64 KB at most)
 
 struct RowsLayout {       // dynamic shared memory, offsets from a 1024-byte aligned base
     uint32_t stages, w_bytes;           // weight ring: one [tile_rows x 128 B] tile per stage
@@ -153,6 +155,50 @@ __device__ __forceinline__ void finish_parked(const DecodeRowsArgs& args, const 
     }
 }
 
+// Single-launch form: every CTA quantizes the (at most 8) fp32 rows itself, with K1's arithmetic bit
+// for bit, straight into the shared-memory layout the MMA reads (one [8 x 128 B] swizzled atom per
+// 128-byte K block: the 16-byte piece c of row r sits at piece c ^ r).  The rows are read twice
+// from L2 (absmax, then quantize); rows * k * 4 bytes per CTA is far below what the weight stream
+// brings in meanwhile, so the work hides behind the filling weight ring.  The row scales go to s_as.
+// Warps are dealt out to rows, `wpr` warps per row, each over a contiguous part of the row.
+__device__ __forceinline__ void fused_quantize_rows(const float* __restrict__ x, uint32_t rows, uint32_t k, uint8_t* x_smem,
+                                                    float* s_as, float* part_max, int* part_bad, uint32_t warps) {
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t wpr = warps / rows;                      // >= 1: rows <= 8 <= warps
+    const uint32_t row = warp / wpr, part = warp - row * wpr;
+    const bool active = row < rows;
+    const uint32_t nvec = k >> 2, seg = (nvec + wpr - 1) / wpr;
+    const uint32_t v0 = part * seg, v1 = v0 + seg < nvec ? v0 + seg : nvec;
+    const float4* in = reinterpret_cast<const float4*>(x + (size_t)(active ? row : 0) * k);
+    float amax = 0.0f; int bad = 0;
+    if (active)
+        for (uint32_t v = v0 + lane; v < v1; v += 32) {
+            const float4 c = __ldg(in + v);
+            bad |= nonfinite_bits(c.x) | nonfinite_bits(c.y) | nonfinite_bits(c.z) | nonfinite_bits(c.w);
+            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(c.x), fabsf(c.y)), fmaxf(fabsf(c.z), fabsf(c.w))));
+        }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+        bad |= __shfl_xor_sync(0xffffffffu, bad, off);
+    }
+    if (lane == 0) { part_max[warp] = amax; part_bad[warp] = bad; }
+    __syncthreads();
+    if (!active) return;
+    amax = 0.0f; bad = 0;
+    for (uint32_t i = 0; i < wpr; i++) { amax = fmaxf(amax, part_max[row * wpr + i]); bad |= part_bad[row * wpr + i]; }
+    const float scale = row_scale_from_amax(amax);
+    if (part == 0 && lane == 0) s_as[row] = bad ? __int_as_float(0x7fc00000) : scale;
+    const RowDivisor div(scale);
+    const bool fast = div.fast && !bad;
+    for (uint32_t v = v0 + lane; v < v1; v += 32) {
+        const float4 c = __ldg(in + v);
+        const uint32_t word = bad ? 0u : (fast ? pack4t<true>(c, div) : pack4t<false>(c, div));
+        const uint32_t kbyte = v << 2, kb = kbyte >> 7, off = kbyte & 127u;
+        *reinterpret_cast<uint32_t*>(x_smem + (size_t)kb * (8u * kRK) + row * kRK + (((off >> 4) ^ row) << 4) + (off & 15u)) = word;
+    }
+}
+
 template <uint32_t MT, bool PAIR>
 __global__ void __launch_bounds__(ModeCfg<PAIR>::kThreads, ModeCfg<PAIR>::kCtasPerSm)
 decode_rows_kernel(const __grid_constant__ DecodeRowsArgs args) {
@@ -223,7 +269,7 @@ decode_rows_kernel(const __grid_constant__ DecodeRowsArgs args) {
             for (uint32_t b = 0; b < 2; b++) mbar_init(tmem_empty(b), 128);
             arm_abort(abort_flag, args.status);
             prefetch_tmap(&args.tmap_w);
-            prefetch_tmap(&args.tmap_x);
+            if (!args.x_f32) prefetch_tmap(&args.tmap_x);
         }
         fence_barrier_init();
     }
@@ -234,6 +280,22 @@ decode_rows_kernel(const __grid_constant__ DecodeRowsArgs args) {
     const uint32_t tmem_base = *tmem_ptr;
     if (threadIdx.x == 0) stamp(args.trace, 1);
 
+    const bool fused = args.x_f32 != nullptr;
+    if constexpr (MT == 8) {
+        if (fused) {
+            // the weight producers have their first ring-full in flight; the whole CTA now turns the fp32
+            // rows (the preceding kernel's output) into the MMA's activation operand
+            pdl_wait();
+            if (threadIdx.x == 0) stamp(args.trace, 6);
+            float* part_max = reinterpret_cast<float*>(s_xpose);          // the parking area is free until the epilogue
+            int* part_bad = reinterpret_cast<int*>(s_xpose) + 32;
+            fused_quantize_rows(args.x_f32, args.rows, args.k, base + lay.x_off(0), s_as, part_max, part_bad,
+                                ModeCfg<PAIR>::kThreads / 32);
+            fence_proxy_async();   // generic-proxy writes to shared memory -> visible to the tensor core's reads
+            __syncthreads();
+        }
+    }
+
     if (warp == kXWarp + kProducerWarps - 1) {
         // ---------------- activation producer ----------------
         // The activations are shared by every K block's MMAs and small: one copy brings KC
@@ -241,7 +303,7 @@ decode_rows_kernel(const __grid_constant__ DecodeRowsArgs args) {
         // their own, so a TMA start (some 200 ns of the issuing thread whatever the box size) is
         // paid once per KC blocks. Every issuer owns the same number of blocks in each chunk and
         // hands the slot back (tcgen05.commit -> xempty) after its last one.
-        if (lane == 0) {
+        if (lane == 0 && !fused) {
             const uint32_t nch = (num_kb + KC - 1) / KC, total = tiles * nch;
             const uint32_t chunk_tx = KC * Cfg::kXAtom;    // the whole box, zero-filled past the edges
             pdl_wait();   // the activations are the preceding kernel's output
@@ -321,7 +383,7 @@ decode_rows_kernel(const __grid_constant__ DecodeRowsArgs args) {
                 uint32_t first = 1, in_chunk = 0, xa = 0;
                 for (uint32_t kb = ii; kb < num_kb; kb += I) {
                     if (in_chunk == 0) {
-                        if (!mbar_wait(xfull(xslot), xphase, abort_flag)) { ok = false; break; }
+                        if (!fused && !mbar_wait(xfull(xslot), xphase, abort_flag)) { ok = false; break; }
                         xa = x_addr(xslot) + ii * Cfg::kXAtom;
                     }
                     if (!mbar_wait(fb, cphase, abort_flag)) { ok = false; break; }
@@ -385,7 +447,7 @@ decode_rows_kernel(const __grid_constant__ DecodeRowsArgs args) {
             if (t == 0) {
                 // from here on: reads of what the preceding kernel wrote, writes of what it may read
                 pdl_wait();
-                if (e < 128) s_as[e] = (e < args.rows && ep.mode != kEpiAcc) ? __ldg(ep.row_scales + e) : 0.0f;
+                if (e < 128 && !fused) s_as[e] = (e < args.rows && ep.mode != kEpiAcc) ? __ldg(ep.row_scales + e) : 0.0f;
             }
             if constexpr (Cfg::kParkAll) {
                 if (tiles == 1) break;   // the single tile is drained by every warp of the CTA, below
@@ -618,10 +680,12 @@ bool configure_t(DecodeRowsArgs& args) {
         if (per < 1) per = 1;
         const uint32_t most = (num_kb + issuers - 1) / issuers;
         if (per > most) per = most;
+        if (args.x_f32) per = most;   // single-launch form: every K block of the rows stays resident
         const uint32_t kc = issuers * per;
         const uint32_t nch = ((num_kb + kc - 1) / kc) * args.tiles_per_cta;
         uint32_t slots = kc * Cfg::kXAtom > 8192u ? 2u : 4u;
         if (slots > nch) slots = nch;
+        if (args.x_f32) slots = 1;
         auto fits = [&](uint32_t st) {
             const RowsLayout f{st, args.w_stage_bytes, slots, kc * Cfg::kXAtom, Cfg::kUmmaM, args.umma_n,
                                Cfg::xpose_bytes(args.rows, args.umma_n)};
@@ -667,7 +731,7 @@ cudaError_t launch_t(const DecodeRowsArgs& args, cudaStream_t stream) {
 }  // namespace
 
 Tunables& tunables() {
-    static Tunables t{kPairShareBytes, false, true, false, 1755u};
+    static Tunables t{kPairShareBytes, false, false, 1755u, true};
     return t;
 }
 
@@ -706,6 +770,8 @@ void decode_rows_plan(uint32_t n, int sm_count, uint32_t* tile_rows, uint32_t* t
 
 bool decode_rows_configure(DecodeRowsArgs& args) {
     if (args.rows == 0 || args.rows > 128 || args.n == 0 || args.tile_rows == 0 || args.tile_rows > kMaxTile) return false;
+    // the single-launch form holds the quantized rows of every K block in shared memory: 8 rows, one tile per CTA
+    if (args.x_f32 && (args.rows > 8 || args.tiles_per_cta != 1 || args.kpad > kFusedMaxKpad || (args.k & 3u) || args.k > args.kpad)) return false;
     // small weight shares: two CTAs per SM, so that successive launches overlap (see kPairSmemBytes)
     const bool pair = (size_t)args.tiles_per_cta * args.tile_rows * args.kpad <= tunables().decode_pair_share_bytes;
     args.l2_prefetch = tunables().decode_l2_prefetch ? 1u : 0u;
@@ -715,6 +781,7 @@ bool decode_rows_configure(DecodeRowsArgs& args) {
 cudaError_t launch_decode_rows(const DecodeRowsArgs& args, cudaStream_t stream) {
     if (args.rows == 0 || args.n == 0) return cudaSuccess;
     if (args.rows > 128 || args.stages == 0 || args.x_chunk_blocks == 0) return cudaErrorInvalidValue;
+    if (args.x_f32 && (args.rows > 8 || args.x_slots != 1 || ((uintptr_t)args.x_f32 & 15u))) return cudaErrorInvalidValue;
     const bool pair = args.pair != 0;
     VXB_DECODE_DISPATCH(launch_t, args, stream);
 }

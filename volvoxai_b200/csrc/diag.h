@@ -64,8 +64,10 @@ VXB_API void vxb_inject_failure(int kind, uint32_t countdown);
  *   "decode.pair_share_bytes"   largest per-CTA weight share run as two CTAs per SM
  *   "decode.l2_prefetch"        1: the decode kernel's weight producers ask L2 for the tile one
  *                               ring-depth ahead of the copy they issue
- *   "gemm.overlap_k1"           1 (default): batches of 2048 rows or more are cut in two so that the
- *                               quantizer of the later rows runs under the GEMM of the first ones
+ *   "decode.fused"              1 (default): up to 8 fp32 rows take the decode kernel's single-launch form
+ *   "gemm.overlap_ratio"        rows_first / rows_rest >= this / d_out when a batch is cut in two (1755)
+ *   "gemm.overlap_k1"           1: batches of 2048 rows or more are cut in two so that the quantizer of the
+ *                               later rows runs under the GEMM of the first ones (default 0: measured slower)
  * Returns 1, or 0 for an unknown name. */
 VXB_API int vxb_tune(const char* name, int64_t value);
 

@@ -485,20 +485,12 @@ __device__ __forceinline__ void gemm_i8_pair_body(const GemmTcgen05Args& args) {
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_i8_pair_kernel(const __grid_constant__ GemmTcgen05Args args) { gemm_i8_pair_body(args); }
 
-// The same kernel held to 128 registers per thread (45 K of the SM's 64 K), which leaves room for one
-// CTA of the row quantizer beside it: the form launched when the quantizer of later rows is to run
-// under this GEMM.
-__global__ void __maxnreg__(128)
-gemm_i8_pair_lean_kernel(const __grid_constant__ GemmTcgen05Args args) { gemm_i8_pair_body(args); }
-
 int g_pair_clusters = 0;   // co-resident clusters of two, queried once
 
 }  // namespace
 
 cudaError_t gemm_pair_prepare() {
     cudaError_t e = cudaFuncSetAttribute(gemm_i8_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
-    if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(gemm_i8_pair_lean_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
     if (e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = kSmemBytes;
@@ -526,7 +518,6 @@ cudaError_t launch_gemm_pair(const GemmTcgen05Args& args, cudaStream_t stream) {
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
-    if (tunables().gemm_lean_regs) return cudaLaunchKernelEx(&cfg, gemm_i8_pair_lean_kernel, args);
     return cudaLaunchKernelEx(&cfg, gemm_i8_pair_kernel, args);
 }
 

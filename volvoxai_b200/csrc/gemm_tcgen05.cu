@@ -441,10 +441,6 @@ __device__ __forceinline__ void gemm_i8_tcgen05_body(const GemmTcgen05Args& args
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_i8_tcgen05_kernel(const __grid_constant__ GemmTcgen05Args args) { gemm_i8_tcgen05_body(args); }
 
-// Held to 128 registers per thread so that one CTA of the row quantizer fits beside it (see the paired kernel).
-__global__ void __maxnreg__(128)
-gemm_i8_tcgen05_lean_kernel(const __grid_constant__ GemmTcgen05Args args) { gemm_i8_tcgen05_body(args); }
-
 // ---- tensor-pipe peak probe --------------------------------------------------
 // Every CTA issues back-to-back M128xN256xK32 kind::i8 MMAs on operands that
 // stay resident in shared memory (no TMA, no epilogue): the dense int8 rate the
@@ -504,8 +500,6 @@ cudaError_t gemm_tcgen05_prepare() {
     cudaError_t e = cudaFuncSetAttribute(gemm_i8_tcgen05_kernel,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
     if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(gemm_i8_tcgen05_lean_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
-    if (e != cudaSuccess) return e;
     return cudaFuncSetAttribute(i8_peak_probe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 (int)(kStageBytes + 1024));
 }
@@ -514,8 +508,7 @@ cudaError_t launch_gemm_tcgen05(const GemmTcgen05Args& args, int sm_count, cudaS
     if (args.rows == 0 || args.n == 0) return cudaSuccess;
     const uint32_t tiles = ((args.rows + kBM - 1) / kBM) * ((args.n + kBN - 1) / kBN);
     const uint32_t grid = tiles < (uint32_t)sm_count ? tiles : (uint32_t)sm_count;
-    if (tunables().gemm_lean_regs) gemm_i8_tcgen05_lean_kernel<<<grid, kThreads, kSmemBytes, stream>>>(args);
-    else gemm_i8_tcgen05_kernel<<<grid, kThreads, kSmemBytes, stream>>>(args);
+    gemm_i8_tcgen05_kernel<<<grid, kThreads, kSmemBytes, stream>>>(args);
     return cudaGetLastError();
 }
 

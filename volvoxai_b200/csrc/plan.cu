@@ -44,6 +44,13 @@ bool admitted(const VxbVariant& v, const VxbPlanQuery& q, char* why, uint32_t by
     if (q.n_peers && !(v.flags & VXB_VF_PEERS)) { refuse(why, bytes, "%s has no peer stores", v.id); return false; }
     if (q.fused_tail && !(v.flags & VXB_VF_FUSED_TAIL)) { refuse(why, bytes, "%s has no fused epilogue tail", v.id); return false; }
     if (v.cluster > 1 && q.pair_clusters == 0) { refuse(why, bytes, "no co-resident CTA pairs on this device"); return false; }
+    if (v.flags & VXB_VF_FUSED_K1) {
+        if (!q.fp32_input) { refuse(why, bytes, "%s starts from fp32 rows", v.id); return false; }
+        if ((q.k & 3u) || round_up(q.k, kKAlign) > 8192u || q.n > 256u * (q.sm_count ? q.sm_count : 148u)) {
+            refuse(why, bytes, "%s needs d_in %% 4 == 0, a padded K of at most 8192 and one channel tile per CTA", v.id);
+            return false;
+        }
+    }
     return true;
 }
 
@@ -55,9 +62,10 @@ bool geometry(VxbVariantId id, const VxbPlanQuery& q, VxbLaunchPlan* p) {
     p->tile_rows = v.tile_rows; p->tile_columns = v.tile_columns; p->tile_k = v.tile_k;
     p->threads = v.threads; p->cluster = v.cluster;
     switch (id) {
-        case VXB_VARIANT_DECODE_ROWS: {
+        case VXB_VARIANT_DECODE_ROWS: case VXB_VARIANT_DECODE_FUSED: {
             DecodeRowsArgs a{};
             a.rows = q.rows; a.n = q.n; a.kpad = kpad;
+            if (id == VXB_VARIANT_DECODE_FUSED) { a.x_f32 = reinterpret_cast<const float*>(uintptr_t(16)); a.k = q.k; }
             decode_rows_plan(q.n, (int)sms, &a.tile_rows, &a.tiles_per_cta);
             a.w_stage_bytes = round_up(a.tile_rows * kKAlign, 1024u);
             if (!decode_rows_configure(a)) return false;
@@ -170,7 +178,11 @@ int vxb_plan(const VxbPlanQuery* query, VxbLaunchPlan* out, char* why, uint32_t 
         if (!admitted(kVariants[chosen], q, why, why_bytes)) return 0;
     } else {
         if (q.n_peers) chosen = VXB_VARIANT_TCGEN05;   // the peer stores live in the single-CTA GEMM's epilogue
-        else if (q.rows <= 128) chosen = VXB_VARIANT_DECODE_ROWS;
+        else if (q.rows <= 128) {
+            chosen = VXB_VARIANT_DECODE_ROWS;
+            char unused[8];
+            if (q.fp32_input && admitted(kVariants[VXB_VARIANT_DECODE_FUSED], q, unused, sizeof unused)) chosen = VXB_VARIANT_DECODE_FUSED;
+        }
         else {
             // pairs of CTAs on 256 x 256 tiles once there are at least two waves of 128 x 256 tiles
             const uint32_t tiles = ceil_div(q.rows, 128) * ceil_div(q.n, 256);
@@ -180,7 +192,7 @@ int vxb_plan(const VxbPlanQuery* query, VxbLaunchPlan* out, char* why, uint32_t 
     }
     if (!geometry((VxbVariantId)chosen, q, out))
         return refuse(why, why_bytes, "no launch shape for %s (rows %u, d_out %u)", kVariants[chosen].id, q.rows, q.n);
-    if (q.fp32_input) plan_quantizer(q, out);
+    if (q.fp32_input && !(kVariants[chosen].flags & VXB_VF_FUSED_K1)) plan_quantizer(q, out);
     return 1;
 }
 

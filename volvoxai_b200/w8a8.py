@@ -19,13 +19,13 @@ import ctypes as C
 import numpy as np
 
 from . import _lib
-from ._lib import (DT_I8, DT_U8, OP_PACKED_LINEAR, ROUTE_AUTO, ROUTE_DECODE, ROUTE_DECODE_STREAMK, ROUTE_TCGEN05_PAIR,
+from ._lib import (DT_I8, DT_U8, OP_PACKED_LINEAR, ROUTE_AUTO, ROUTE_DECODE, ROUTE_DECODE_FUSED, ROUTE_DECODE_STREAMK, ROUTE_TCGEN05_PAIR,
                    ROUTE_GEMV, ROUTE_SIMT,
                    ROUTE_TCGEN05, LLMOpArgs, last_error, last_route)
 
 __all__ = ["Context", "Weight", "W8A8Error", "variants", "plan", "registry_rows", "qlinear_i8u8", "packed_linear",
            "packed_linear_decode", "host_cache_clear", "launch_count", "last_error",
-           "quantize_typed_f32_i8u8", "dequantize_typed_i8u8_f32", "requantize_linear_i8u8", "last_route", "ROUTE_AUTO", "ROUTE_GEMV", "ROUTE_TCGEN05", "ROUTE_SIMT", "ROUTE_DECODE", "ROUTE_DECODE_STREAMK", "ROUTE_TCGEN05_PAIR",
+           "quantize_typed_f32_i8u8", "dequantize_typed_i8u8_f32", "requantize_linear_i8u8", "last_route", "ROUTE_AUTO", "ROUTE_GEMV", "ROUTE_TCGEN05", "ROUTE_SIMT", "ROUTE_DECODE", "ROUTE_DECODE_STREAMK", "ROUTE_TCGEN05_PAIR", "ROUTE_DECODE_FUSED",
            "DT_I8", "DT_U8"]
 
 
