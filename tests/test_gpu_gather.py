@@ -94,7 +94,7 @@ def test_two_chunk_overlap_equals_the_serial_form(torch, oracle, rows, k, n):
     ld = (n + 15) // 16 * 16
     got = {}
     for mode in (0, 1):
-        assert w8a8.tune("gemm.overlap_k1", mode)
+        assert w8a8.tune("gemm.overlap_k1", mode) and w8a8.tune("gemm.overlap_gather", mode)
         y8 = ctx.linear_i8(weight, x, 0.05, 3)
         route = w8a8.last_route()
         yf = ctx.linear_f32(weight, x)
@@ -106,7 +106,8 @@ def test_two_chunk_overlap_equals_the_serial_form(torch, oracle, rows, k, n):
         ctx.synchronize()
         assert mode or "2-chunk-overlap" not in route, route
         got[mode] = (y8, yf.view(torch.int32), yr.view(torch.int32), bufs[0], bufs[1])
-    w8a8.tune("gemm.overlap_k1", 0)      # the library's default
+    w8a8.tune("gemm.overlap_k1", 0)      # the library's defaults: off for the plain GEMM, on for the fused all-gather
+    w8a8.tune("gemm.overlap_gather", 1)
     for a, b in zip(got[0], got[1]):
         assert torch.equal(a, b)
     if (rows, n) == (8192, 14336):

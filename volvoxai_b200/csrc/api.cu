@@ -362,7 +362,7 @@ int run_gemm(VxbContext* ctx, const VxbWeight* w, const int8_t* q, uint32_t rows
             LAUNCH_TRY(launch_gemm_simt(q, rows, w->w, w->d_out, w->kpad, epi, ctx->stream));
             break;
         case VXB_VARIANT_DECODE_ROWS: {
-            DecodeRowsArgs a;
+            DecodeRowsArgs a{};
             a.tmap_w = w->tmap_rows;
             a.rows = rows; a.n = w->d_out; a.kpad = w->kpad;
             a.tile_rows = w->tile_rows; a.tiles_per_cta = w->tiles_per_cta;
@@ -450,9 +450,11 @@ int quantize_into_scratch(VxbContext* ctx, const VxbWeight* w, const float* x, u
 // it saved (361 -> 364 us).  The first chunk is the smallest number of row tiles whose GEMM lasts at least as
 // long as the quantizer of the rest and that adds no wave of tiles to the launch pair.
 uint32_t overlap_first_rows(const VxbContext* ctx, const VxbWeight* w, uint32_t rows, const EpilogueParams& epi, int route) {
-    if (!tunables().overlap_k1 || w->group || rows < 2048) return 0;
-    if (route != VXB_ROUTE_AUTO && route != VXB_ROUTE_TCGEN05 && route != VXB_ROUTE_TCGEN05_PAIR) return 0;
     const bool gather = epi.n_peers != 0;
+    // on by default for the fused all-gather only (that launch is link-bound and is built with 128
+    // registers, so the quantizer fits beside it); elsewhere only when the tunable asks for it
+    if (!(gather ? tunables().overlap_gather : tunables().overlap_k1) || w->group || rows < 2048) return 0;
+    if (route != VXB_ROUTE_AUTO && route != VXB_ROUTE_TCGEN05 && route != VXB_ROUTE_TCGEN05_PAIR) return 0;
     const uint32_t tiles128 = ((rows + 127) / 128) * ((w->d_out + 255) / 256);
     const bool pair = !gather && route != VXB_ROUTE_TCGEN05 && gemm_pair_clusters() > 0 &&
                       (route == VXB_ROUTE_TCGEN05_PAIR || tiles128 >= 2u * (uint32_t)ctx->sm_count);
@@ -464,14 +466,14 @@ uint32_t overlap_first_rows(const VxbContext* ctx, const VxbWeight* w, uint32_t 
     // GEMM seconds per row ~ 2 K N / 3.3e15 (link-bound with peers: slower still), quantizer seconds per
     // row ~ 5 K / 4.7e12: the first chunk needs rows_first / rows_rest >= 1755 / N
     const double ratio = (double)tunables().overlap_ratio / (double)w->d_out;
-    uint32_t r_min = (uint32_t)((double)row_tiles * ratio / (1.0 + ratio)) + 1;
+    uint32_t r_min = gather ? 1u : (uint32_t)((double)row_tiles * ratio / (1.0 + ratio)) + 1;
     if (r_min >= row_tiles) return 0;
     uint32_t best = 0;
     if (!gather) {
         for (uint32_t r = r_min; r < row_tiles && r <= 2 * r_min + 4; r++)
             if (waves(r) + waves(row_tiles - r) == waves(row_tiles)) { best = r; break; }
         if (!best) return 0;   // every cut here would idle part of a wave: keep the single launch
-    } else best = r_min;
+    } else best = r_min < row_tiles / 4 ? row_tiles / 4 : r_min;   // link-bound launch: a quarter of the rows is plenty
     return best * tile_rows;
 }
 
@@ -1136,6 +1138,7 @@ int vxb_tune(const char* name, int64_t value) {
     if (!strcmp(name, "decode.l2_prefetch")) { t.decode_l2_prefetch = value != 0; return 1; }
     if (!strcmp(name, "decode.fused")) { t.decode_fused = value != 0; return 1; }
     if (!strcmp(name, "gemm.overlap_k1")) { t.overlap_k1 = value != 0; return 1; }
+    if (!strcmp(name, "gemm.overlap_gather")) { t.overlap_gather = value != 0; return 1; }
     if (!strcmp(name, "gemm.overlap_ratio")) { t.overlap_ratio = (uint32_t)value; return 1; }
     return 0;
 }

@@ -410,6 +410,7 @@ struct Tunables {
     uint32_t decode_pair_share_bytes;   // largest per-CTA weight share the decode kernel runs as two CTAs per SM
     bool decode_l2_prefetch;            // weight producers ask L2 for the tile one ring-depth ahead
     bool overlap_k1;                    // large batches: quantize the later rows under the GEMM of the first ones (off: measured slower)
+    bool overlap_gather;                // the same for the fused all-gather launch (on: link-bound, 128-register build)
     uint32_t overlap_ratio;             // rows_first / rows_rest >= overlap_ratio / d_out when a batch is cut in two
     bool decode_fused;                  // up to 8 fp32 rows: the decode kernel quantizes them itself (one launch)
 };

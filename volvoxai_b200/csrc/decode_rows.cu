@@ -731,7 +731,7 @@ cudaError_t launch_t(const DecodeRowsArgs& args, cudaStream_t stream) {
 }  // namespace
 
 Tunables& tunables() {
-    static Tunables t{kPairShareBytes, false, false, 1755u, true};
+    static Tunables t{kPairShareBytes, false, false, true, 1755u, true};
     return t;
 }
 

@@ -441,6 +441,13 @@ __device__ __forceinline__ void gemm_i8_tcgen05_body(const GemmTcgen05Args& args
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_i8_tcgen05_kernel(const __grid_constant__ GemmTcgen05Args args) { gemm_i8_tcgen05_body(args); }
 
+// The same kernel held to 128 registers per thread (45 K of the SM's 64 K registers), which leaves
+// room for one CTA of the row quantizer beside it.  Used for the fused all-gather only: that launch
+// is bound by the NVLink stores of its epilogue, not by instruction issue, so the quantizer of the
+// later rows can run underneath it at no cost to the GEMM.
+__global__ void __maxnreg__(128)
+gemm_i8_tcgen05_gather_kernel(const __grid_constant__ GemmTcgen05Args args) { gemm_i8_tcgen05_body(args); }
+
 // ---- tensor-pipe peak probe --------------------------------------------------
 // Every CTA issues back-to-back M128xN256xK32 kind::i8 MMAs on operands that
 // stay resident in shared memory (no TMA, no epilogue): the dense int8 rate the
@@ -500,6 +507,8 @@ cudaError_t gemm_tcgen05_prepare() {
     cudaError_t e = cudaFuncSetAttribute(gemm_i8_tcgen05_kernel,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
     if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(gemm_i8_tcgen05_gather_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+    if (e != cudaSuccess) return e;
     return cudaFuncSetAttribute(i8_peak_probe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 (int)(kStageBytes + 1024));
 }
@@ -508,7 +517,8 @@ cudaError_t launch_gemm_tcgen05(const GemmTcgen05Args& args, int sm_count, cudaS
     if (args.rows == 0 || args.n == 0) return cudaSuccess;
     const uint32_t tiles = ((args.rows + kBM - 1) / kBM) * ((args.n + kBN - 1) / kBN);
     const uint32_t grid = tiles < (uint32_t)sm_count ? tiles : (uint32_t)sm_count;
-    gemm_i8_tcgen05_kernel<<<grid, kThreads, kSmemBytes, stream>>>(args);
+    if (args.epi.n_peers != 0) gemm_i8_tcgen05_gather_kernel<<<grid, kThreads, kSmemBytes, stream>>>(args);
+    else gemm_i8_tcgen05_kernel<<<grid, kThreads, kSmemBytes, stream>>>(args);
     return cudaGetLastError();
 }
 
