@@ -125,8 +125,9 @@ VXB_PLAN_API const VxbVariant* vxb_variant_info(uint32_t index);
  * reason in `why` (optional buffer).  An explicit route is honoured or refused, never replaced;
  * the automatic route picks, among the admitted variants flagged VXB_VF_AUTO, by these rules:
  *   per-channel scales: rows <= 128 -> the decode kernel (its single-launch form, which quantizes the
- *     rows itself, for fp32 input of up to 8 rows with a padded K of at most 8192 and d_in a multiple
- *     of 4), else the tensor-core GEMM, by pairs of CTAs once there are two waves of 128 x 256 tiles;
+ *     rows itself, for fp32 input of one or two rows with a padded K of at most 8192 and d_in a
+ *     multiple of 4; an explicit request admits it up to 8 rows), else the tensor-core GEMM, by pairs
+ *     of CTAs once there are two waves of 128 x 256 tiles;
  *   grouped scales: 1-2 rows (3-4 with <= 32 MB of weights) -> the streaming GEMV (over the 4-bit
  *     words when kept), else the tensor-core kernel with a per-group accumulator drain. */
 VXB_PLAN_API int vxb_plan(const VxbPlanQuery* query, VxbLaunchPlan* out, char* why, uint32_t why_bytes);

@@ -44,7 +44,7 @@ def _case(torch, ctx, rows, k=576, n=1536):
     return c, weight, torch.from_numpy(c["x"]).cuda()
 
 
-@pytest.mark.parametrize("rows", [8, 300])
+@pytest.mark.parametrize("rows", [16, 300])
 def test_refused_allocation_declines_before_the_output_is_touched(torch, fresh, oracle, rows):
     from volvoxai_b200 import w8a8
     c, weight, x = _case(torch, fresh, rows)
@@ -68,10 +68,13 @@ def test_refused_allocation_declines_before_the_output_is_touched(torch, fresh, 
     weight.close()
 
 
-@pytest.mark.parametrize("rows", [8, 300])
+@pytest.mark.parametrize("rows", [8, 16, 300])
 @pytest.mark.parametrize("nth", [1, 2])
 def test_refused_nth_launch_fails_after_submission(torch, fresh, rows, nth):
-    """nth = 1: the quantizer is refused; nth = 2: the quantizer is queued and the GEMM refused."""
+    """nth = 1: the quantizer is refused; nth = 2: the quantizer is queued and the GEMM refused.  Up to 8
+    rows the call is a single launch (the decode kernel quantizes the rows itself): only nth = 1 exists."""
+    if rows <= 8 and nth == 2:
+        pytest.skip("single-launch form")
     from volvoxai_b200 import w8a8
     c, weight, x = _case(torch, fresh, rows)
     want = fresh.linear_i8(weight, x, 0.05, 0)
@@ -105,7 +108,7 @@ def test_injection_through_the_reference_facing_entry(torch):
     assert w8a8.packed_linear(x, words, scales, None, y) == 0
     assert (y == 7.0).all()
     w8a8.inject_failure(2, 0)
-    w8a8.inject_failure(1, 2)            # the quantizer is queued, then the GEMV is refused
+    w8a8.inject_failure(1, 1)            # the (single) launch of the 5-row call is refused
     assert w8a8.packed_linear(x, words, scales, None, y) == -1
     w8a8.inject_failure(1, 0)
     assert w8a8.packed_linear(x, words, scales, None, y) == 1

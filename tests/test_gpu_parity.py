@@ -152,7 +152,7 @@ def test_small_m_routes(torch, ctx, oracle, rows, k, n):
     bias_i32 = rng.integers(-300, 300, size=n).astype(np.int32)
     routes = ["gemv", "decode", "streamk", "tcgen05", "simt"]
     if rows <= 8 and k % 4 == 0:
-        routes += ["fused", "auto"]      # the single-launch decode form (the automatic route for these shapes)
+        routes += ["fused", "auto"]      # the single-launch decode form (the automatic route for one and two rows)
     run_case(torch, ctx, oracle, case, routes, bias_i32=bias_i32, out_zero=-3)
 
 
@@ -613,21 +613,22 @@ def test_single_launch_decode_form(torch, ctx, oracle, rows, k, n):
         case["x"][1] = 0
         case["x"][2, k // 2] = np.nan
     run_case(torch, ctx, oracle, case, ["fused", "auto", "decode"], bias_i32=rng.integers(-300, 300, size=n).astype(np.int32), out_zero=4)
-    assert w8a8.plan(rows, k, n)[0]["id"] == "DECODE_FUSED"
+    assert w8a8.plan(rows, k, n, route=w8a8.ROUTE_DECODE_FUSED)[0]["id"] == "DECODE_FUSED"
+    assert (w8a8.plan(rows, k, n)[0]["id"] == "DECODE_FUSED") == (rows <= 2)
     if n % 2 == 0:
         weight = w8a8.Weight.from_i8(ctx, case["w"], case["ws"], bias_f32=case["bias"])
         xd = dev(torch, case["x"])
         res = torch.randn((rows, n), device="cuda")
         got = {}
         for flag in (1, 0):
-            w8a8.tune("decode.fused", flag)
+            w8a8.tune("decode.fused_max_rows", 8 if flag else 0)
             a = ctx.linear_f32_fused(weight, xd, residual=res)
             route = w8a8.last_route()
             b = ctx.linear_f32_fused(weight, xd, silu_mul=True)
             ctx.synchronize()
             assert ("decode-fused" in route) == bool(flag), route
             got[flag] = (a.view(torch.int32).clone(), b.view(torch.int32).clone())
-        w8a8.tune("decode.fused", 1)
+        w8a8.tune("decode.fused_max_rows", 2)      # the library's default
         assert torch.equal(got[0][0], got[1][0]) and torch.equal(got[0][1], got[1][1])
         weight.close()
 

@@ -41,12 +41,12 @@ def test_variant_table_is_well_formed():
 
 def test_automatic_route_boundaries_per_channel():
     assert pick(1, 4096, 4096)["id"] == "DECODE_FUSED"                       # fp32 rows in: one launch
-    assert pick(8, 4096, 14336)["id"] == "DECODE_FUSED"
-    assert pick(8, 4096, 14336, fp32_input=False)["id"] == "DECODE_ROWS"      # prepared activations
-    assert pick(9, 4096, 14336)["id"] == "DECODE_ROWS"                       # more than 8 rows
-    assert pick(8, 14336, 4096)["id"] == "DECODE_ROWS"                       # padded K beyond 8192
-    assert pick(4, 4098, 512)["id"] == "DECODE_ROWS"                         # d_in not a multiple of 4
-    assert pick(8, 1024, 512, fused_tail=True)["id"] == "DECODE_FUSED"
+    assert pick(2, 4096, 14336)["id"] == "DECODE_FUSED"
+    assert pick(2, 4096, 14336, fp32_input=False)["id"] == "DECODE_ROWS"      # prepared activations
+    assert pick(3, 4096, 14336)["id"] == "DECODE_ROWS"                       # from three rows: quantizer + decode kernel
+    assert pick(2, 14336, 4096)["id"] == "DECODE_ROWS"                       # padded K beyond 8192
+    assert pick(2, 4098, 512)["id"] == "DECODE_ROWS"                         # d_in not a multiple of 4
+    assert pick(2, 1024, 512, fused_tail=True)["id"] == "DECODE_FUSED"
     assert pick(128, 1024, 3072)["id"] == "DECODE_ROWS"
     assert pick(129, 1024, 3072)["id"] == "TCGEN05"
     # two waves of 128 x 256 tiles on 148 SMs = 296 tiles: 8192 x 14336 has 64 * 56 = 3584
@@ -116,9 +116,11 @@ def test_exact_launch_geometry():
     p = pick(300, 576, 1536)
     assert (p["grid"], p["threads"], p["cluster"]) == (3 * 6, 352, 1)
     # decode: every CTA owns ceil(N / 148) whole channels (even, so gate/up pairs never straddle CTAs)
-    p = pick(8, 4096, 14336)
+    p = pick(1, 4096, 14336)
     assert (p["tile_columns"], p["grid"], p["threads"], p["tile_rows"]) == (98, 147, 544, 8)
     assert (p["launches"], p["quantizer"], p["workspace_bytes"]) == (1, 0, 0)           # single launch, no scratch
+    p = pick(8, 4096, 14336)
+    assert (p["id"], p["launches"], p["quantizer"], p["quantizer_grid"]) == ("DECODE_ROWS", 2, 3, 32)
     p = pick(16, 4096, 14336)
     assert (p["launches"], p["quantizer"], p["quantizer_cluster"], p["quantizer_grid"]) == (2, 3, 4, 64)   # cluster quantizer, 4 CTAs per row
     p = pick(64, 1024, 3072)

@@ -482,7 +482,7 @@ uint32_t overlap_first_rows(const VxbContext* ctx, const VxbWeight* w, uint32_t 
 int quantize_then_gemm(VxbContext* ctx, const VxbWeight* w, const float* x, uint32_t rows, const EpilogueParams& epi,
                        int route, const char* prefix, const float* norm_weight = nullptr, float epsilon = 0.0f,
                        float* norm_out = nullptr) {
-    if (!norm_weight && (route == VXB_ROUTE_AUTO || route == VXB_ROUTE_DECODE_FUSED) && rows <= 8 && tunables().decode_fused) {
+    if (!norm_weight && (route == VXB_ROUTE_AUTO || route == VXB_ROUTE_DECODE_FUSED) && rows <= 8) {
         // up to 8 rows: one launch, the decode kernel quantizes the rows itself (when the plan admits it)
         const VxbPlanQuery query = plan_query(ctx, w, rows, epi, route, true);
         VxbLaunchPlan plan;
@@ -1136,7 +1136,7 @@ int vxb_tune(const char* name, int64_t value) {
     Tunables& t = tunables();
     if (!strcmp(name, "decode.pair_share_bytes")) { t.decode_pair_share_bytes = (uint32_t)value; return 1; }
     if (!strcmp(name, "decode.l2_prefetch")) { t.decode_l2_prefetch = value != 0; return 1; }
-    if (!strcmp(name, "decode.fused")) { t.decode_fused = value != 0; return 1; }
+    if (!strcmp(name, "decode.fused_max_rows")) { t.decode_fused_max_rows = (uint32_t)value; return 1; }
     if (!strcmp(name, "gemm.overlap_k1")) { t.overlap_k1 = value != 0; return 1; }
     if (!strcmp(name, "gemm.overlap_gather")) { t.overlap_gather = value != 0; return 1; }
     if (!strcmp(name, "gemm.overlap_ratio")) { t.overlap_ratio = (uint32_t)value; return 1; }

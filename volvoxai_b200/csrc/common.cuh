@@ -412,7 +412,7 @@ struct Tunables {
     bool overlap_k1;                    // large batches: quantize the later rows under the GEMM of the first ones (off: measured slower)
     bool overlap_gather;                // the same for the fused all-gather launch (on: link-bound, 128-register build)
     uint32_t overlap_ratio;             // rows_first / rows_rest >= overlap_ratio / d_out when a batch is cut in two
-    bool decode_fused;                  // up to 8 fp32 rows: the decode kernel quantizes them itself (one launch)
+    uint32_t decode_fused_max_rows;     // fp32 rows up to which the automatic route takes the decode kernel's single-launch form
 };
 Tunables& tunables();
 

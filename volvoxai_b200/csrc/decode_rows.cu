@@ -170,12 +170,21 @@ __device__ __forceinline__ void fused_quantize_rows(const float* __restrict__ x,
     const uint32_t nvec = k >> 2, seg = (nvec + wpr - 1) / wpr;
     const uint32_t v0 = part * seg, v1 = v0 + seg < nvec ? v0 + seg : nvec;
     const float4* in = reinterpret_cast<const float4*>(x + (size_t)(active ? row : 0) * k);
+    // loads go out in batches of kBatch per lane before any of them is used: the loop is a chain of
+    // L2 round trips otherwise (one outstanding load per lane)
+    constexpr uint32_t kBatch = 8;
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
     float amax = 0.0f; int bad = 0;
     if (active)
-        for (uint32_t v = v0 + lane; v < v1; v += 32) {
-            const float4 c = __ldg(in + v);
-            bad |= nonfinite_bits(c.x) | nonfinite_bits(c.y) | nonfinite_bits(c.z) | nonfinite_bits(c.w);
-            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(c.x), fabsf(c.y)), fmaxf(fabsf(c.z), fabsf(c.w))));
+        for (uint32_t vb = v0 + lane; vb < v1; vb += 32 * kBatch) {
+            float4 c[kBatch];
+#pragma unroll
+            for (uint32_t j = 0; j < kBatch; j++) c[j] = vb + 32 * j < v1 ? __ldg(in + vb + 32 * j) : zero4;
+#pragma unroll
+            for (uint32_t j = 0; j < kBatch; j++) {
+                bad |= nonfinite_bits(c[j].x) | nonfinite_bits(c[j].y) | nonfinite_bits(c[j].z) | nonfinite_bits(c[j].w);
+                amax = fmaxf(amax, fmaxf(fmaxf(fabsf(c[j].x), fabsf(c[j].y)), fmaxf(fabsf(c[j].z), fabsf(c[j].w))));
+            }
         }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) {
@@ -191,11 +200,19 @@ __device__ __forceinline__ void fused_quantize_rows(const float* __restrict__ x,
     if (part == 0 && lane == 0) s_as[row] = bad ? __int_as_float(0x7fc00000) : scale;
     const RowDivisor div(scale);
     const bool fast = div.fast && !bad;
-    for (uint32_t v = v0 + lane; v < v1; v += 32) {
-        const float4 c = __ldg(in + v);
-        const uint32_t word = bad ? 0u : (fast ? pack4t<true>(c, div) : pack4t<false>(c, div));
-        const uint32_t kbyte = v << 2, kb = kbyte >> 7, off = kbyte & 127u;
-        *reinterpret_cast<uint32_t*>(x_smem + (size_t)kb * (8u * kRK) + row * kRK + (((off >> 4) ^ row) << 4) + (off & 15u)) = word;
+    uint8_t* row_base = x_smem + row * kRK;
+    for (uint32_t vb = v0 + lane; vb < v1; vb += 32 * kBatch) {
+        float4 c[kBatch];
+#pragma unroll
+        for (uint32_t j = 0; j < kBatch; j++) c[j] = vb + 32 * j < v1 ? __ldg(in + vb + 32 * j) : zero4;
+#pragma unroll
+        for (uint32_t j = 0; j < kBatch; j++) {
+            const uint32_t v = vb + 32 * j;
+            if (v >= v1) break;
+            const uint32_t word = bad ? 0u : (fast ? pack4t<true>(c[j], div) : pack4t<false>(c[j], div));
+            const uint32_t kbyte = v << 2, kb = kbyte >> 7, off = kbyte & 127u;
+            *reinterpret_cast<uint32_t*>(row_base + (size_t)kb * (8u * kRK) + (((off >> 4) ^ row) << 4) + (off & 15u)) = word;
+        }
     }
 }
 
@@ -731,7 +748,7 @@ cudaError_t launch_t(const DecodeRowsArgs& args, cudaStream_t stream) {
 }  // namespace
 
 Tunables& tunables() {
-    static Tunables t{kPairShareBytes, false, false, true, 1755u, true};
+    static Tunables t{kPairShareBytes, false, false, true, 1755u, 2u};
     return t;
 }
 

@@ -64,7 +64,8 @@ VXB_API void vxb_inject_failure(int kind, uint32_t countdown);
  *   "decode.pair_share_bytes"   largest per-CTA weight share run as two CTAs per SM
  *   "decode.l2_prefetch"        1: the decode kernel's weight producers ask L2 for the tile one
  *                               ring-depth ahead of the copy they issue
- *   "decode.fused"              1 (default): up to 8 fp32 rows take the decode kernel's single-launch form
+ *   "decode.fused_max_rows"     fp32 rows up to which the automatic route takes the decode kernel's single-launch
+ *                               form (default 2; the kernel serves up to 8)
  *   "gemm.overlap_ratio"        rows_first / rows_rest >= this / d_out when a batch is cut in two (1755)
  *   "gemm.overlap_k1"           1: batches of 2048 rows or more are cut in two so that the quantizer of the
  *                               later rows runs under the GEMM of the first ones (default 0: measured slower)

@@ -181,7 +181,11 @@ int vxb_plan(const VxbPlanQuery* query, VxbLaunchPlan* out, char* why, uint32_t 
         else if (q.rows <= 128) {
             chosen = VXB_VARIANT_DECODE_ROWS;
             char unused[8];
-            if (q.fp32_input && admitted(kVariants[VXB_VARIANT_DECODE_FUSED], q, unused, sizeof unused)) chosen = VXB_VARIANT_DECODE_FUSED;
+            // one or two fp32 rows: the single-launch form.  From three rows on every CTA repeating the
+            // quantization costs more than the separate cluster quantizer (17.1 against 15.5 us per
+            // step at 8 rows, K 4096, N 14336), so the two-launch form stays.
+            if (q.fp32_input && q.rows <= tunables().decode_fused_max_rows &&
+                admitted(kVariants[VXB_VARIANT_DECODE_FUSED], q, unused, sizeof unused)) chosen = VXB_VARIANT_DECODE_FUSED;
         }
         else {
             // pairs of CTAs on 256 x 256 tiles once there are at least two waves of 128 x 256 tiles
