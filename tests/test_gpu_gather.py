@@ -133,7 +133,9 @@ def _worker(rank, world, port, rows, k, n, ret):
     from volvoxai_b200 import sharded, w8a8
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    import datetime
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank),
+                            timeout=datetime.timedelta(seconds=90))   # a mismatched collective fails in seconds, not minutes
     try:
         case, os_, want = _case(Oracle(), rows, k, n, seed=13)
         lo, hi = sharded.shard_bounds(n, world, rank)
@@ -149,7 +151,8 @@ def _worker(rank, world, port, rows, k, n, ret):
             ok = ok and np.array_equal(y.cpu().numpy(), want)
         lin.close()
         # the host-fed form: every rank uploads its rows, the int8 codes are all-gathered over NCCL
-        if hi > lo and rows % world == 0:
+        every_shard_holds_channels = all(sharded.shard_bounds(n, world, r)[1] > sharded.shard_bounds(n, world, r)[0] for r in range(world))
+        if every_shard_holds_channels and rows % world == 0:      # a collective: the same decision on every rank
             host = sharded.RowShardedHostLinear(ctx, weight, rows, k, world, rank)
             per = rows // world
             x_pin = torch.from_numpy(case["x"][rank * per:(rank + 1) * per].copy()).pin_memory()

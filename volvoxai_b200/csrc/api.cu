@@ -451,9 +451,10 @@ int quantize_into_scratch(VxbContext* ctx, const VxbWeight* w, const float* x, u
 // long as the quantizer of the rest and that adds no wave of tiles to the launch pair.
 uint32_t overlap_first_rows(const VxbContext* ctx, const VxbWeight* w, uint32_t rows, const EpilogueParams& epi, int route) {
     const bool gather = epi.n_peers != 0;
-    // on by default for the fused all-gather only (that launch is link-bound and is built with 128
-    // registers, so the quantizer fits beside it); elsewhere only when the tunable asks for it
-    if (!(gather ? tunables().overlap_gather : tunables().overlap_k1) || w->group || rows < 2048) return 0;
+    // on by default for the fused all-gather when it is link-bound (that launch runs the 128-register
+    // build, so the quantizer fits beside it); elsewhere only when the tunable asks for it
+    const bool link_bound = gather_is_link_bound(epi.n_peers, w->kpad);
+    if (!(link_bound ? tunables().overlap_gather : tunables().overlap_k1) || w->group || rows < 2048) return 0;
     if (route != VXB_ROUTE_AUTO && route != VXB_ROUTE_TCGEN05 && route != VXB_ROUTE_TCGEN05_PAIR) return 0;
     const uint32_t tiles128 = ((rows + 127) / 128) * ((w->d_out + 255) / 256);
     const bool pair = !gather && route != VXB_ROUTE_TCGEN05 && gemm_pair_clusters() > 0 &&

@@ -326,6 +326,10 @@ struct GemmTcgen05Args {
     int* status;
 };
 cudaError_t launch_gemm_tcgen05(const GemmTcgen05Args& args, int sm_count, cudaStream_t stream);
+// Fused all-gather: the launch is bound by its NVLink stores rather than by the MMAs when every row sends
+// n_local * peers bytes at ~770 GB/s for longer than its 2 * K * n_local operations take at ~3.3 POPS,
+// i.e. when peers * 2140 > K (three GPUs and more at K = 4096; two GPUs stay MMA-bound).
+inline bool gather_is_link_bound(uint32_t n_peers, uint32_t kpad) { return n_peers != 0 && (uint64_t)n_peers * 2140u > kpad; }
 cudaError_t gemm_tcgen05_prepare();  // one-time func attribute set-up
 // The same GEMM by pairs of CTAs (cta_group::2) on 256 x 256 tiles; tmap_b has a box of 128 rows.
 cudaError_t gemm_pair_prepare();    // func attribute + how many pairs can be resident

@@ -517,7 +517,7 @@ cudaError_t launch_gemm_tcgen05(const GemmTcgen05Args& args, int sm_count, cudaS
     if (args.rows == 0 || args.n == 0) return cudaSuccess;
     const uint32_t tiles = ((args.rows + kBM - 1) / kBM) * ((args.n + kBN - 1) / kBN);
     const uint32_t grid = tiles < (uint32_t)sm_count ? tiles : (uint32_t)sm_count;
-    if (args.epi.n_peers != 0) gemm_i8_tcgen05_gather_kernel<<<grid, kThreads, kSmemBytes, stream>>>(args);
+    if (gather_is_link_bound(args.epi.n_peers, args.kpad)) gemm_i8_tcgen05_gather_kernel<<<grid, kThreads, kSmemBytes, stream>>>(args);
     else gemm_i8_tcgen05_kernel<<<grid, kThreads, kSmemBytes, stream>>>(args);
     return cudaGetLastError();
 }
