@@ -451,8 +451,7 @@ int quantize_into_scratch(VxbContext* ctx, const VxbWeight* w, const float* x, u
 // long as the quantizer of the rest and that adds no wave of tiles to the launch pair.
 uint32_t overlap_first_rows(const VxbContext* ctx, const VxbWeight* w, uint32_t rows, const EpilogueParams& epi, int route) {
     const bool gather = epi.n_peers != 0;
-    // on by default for the fused all-gather when it is link-bound (that launch runs the 128-register
-    // build, so the quantizer fits beside it); elsewhere only when the tunable asks for it
+    // only when a tunable asks for it (see overlap_first_rows' note and the gather kernel's)
     const bool link_bound = gather_is_link_bound(epi.n_peers, w->kpad);
     if (!(link_bound ? tunables().overlap_gather : tunables().overlap_k1) || w->group || rows < 2048) return 0;
     if (route != VXB_ROUTE_AUTO && route != VXB_ROUTE_TCGEN05 && route != VXB_ROUTE_TCGEN05_PAIR) return 0;

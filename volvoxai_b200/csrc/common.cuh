@@ -414,7 +414,7 @@ struct Tunables {
     uint32_t decode_pair_share_bytes;   // largest per-CTA weight share the decode kernel runs as two CTAs per SM
     bool decode_l2_prefetch;            // weight producers ask L2 for the tile one ring-depth ahead
     bool overlap_k1;                    // large batches: quantize the later rows under the GEMM of the first ones (off: measured slower)
-    bool overlap_gather;                // the same for the fused all-gather launch (on: link-bound, 128-register build)
+    bool overlap_gather;                // the same for a link-bound fused all-gather launch, with its 128-register build (off: measured slower)
     uint32_t overlap_ratio;             // rows_first / rows_rest >= overlap_ratio / d_out when a batch is cut in two
     uint32_t decode_fused_max_rows;     // fp32 rows up to which the automatic route takes the decode kernel's single-launch form
 };

@@ -69,7 +69,8 @@ VXB_API void vxb_inject_failure(int kind, uint32_t countdown);
  *   "gemm.overlap_ratio"        rows_first / rows_rest >= this / d_out when a batch is cut in two (1755)
  *   "gemm.overlap_k1"           1: batches of 2048 rows or more are cut in two so that the quantizer of the
  *                               later rows runs under the GEMM of the first ones (default 0: measured slower)
- *   "gemm.overlap_gather"       1 (default): the same split for the fused all-gather launch, which is link-bound
+ *   "gemm.overlap_gather"       1: the same split for a link-bound fused all-gather launch, with the 128-register
+ *                               build of its kernel (default 0: measured slower)
  * Returns 1, or 0 for an unknown name. */
 VXB_API int vxb_tune(const char* name, int64_t value);
 

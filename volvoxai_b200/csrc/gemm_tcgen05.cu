@@ -55,7 +55,7 @@ constexpr uint32_t kOffBias = kOffWs + kEpiWarps * kEpiCols * 4;     // float/in
 constexpr uint32_t kOffStore = kOffBias + kEpiWarps * kEpiCols * 4;  // [8 warps][16 rows x 128 B] store staging
 constexpr uint32_t kStoreBytes = 16 * 128;
 constexpr uint32_t kOffBars = kOffStore + kEpiWarps * kStoreBytes;   // 8-byte barriers
-constexpr uint32_t kNumBars = 2 * kStages + 4;
+constexpr uint32_t kNumBars = 2 * kStages + 4 + 8;   // ... + (staged, flushed) per pair of epilogue warps sharing a TMEM lane quarter
 constexpr uint32_t kOffTmemPtr = kOffBars + kNumBars * 8;
 constexpr uint32_t kOffAbort = kOffTmemPtr + 4;
 constexpr uint32_t kSmemBytes = kOffAbort + 8 + 1024;        // + alignment slack
@@ -68,6 +68,8 @@ struct Smem {
     __device__ uint32_t empty(uint32_t s) const { return smem_u32(base + kOffBars + (kStages + s) * 8); }
     __device__ uint32_t tmem_full(uint32_t b) const { return smem_u32(base + kOffBars + (2 * kStages + b) * 8); }
     __device__ uint32_t tmem_empty(uint32_t b) const { return smem_u32(base + kOffBars + (2 * kStages + 2 + b) * 8); }
+    __device__ uint32_t pair_staged(uint32_t q) const { return smem_u32(base + kOffBars + (2 * kStages + 4 + q) * 8); }
+    __device__ uint32_t pair_flushed(uint32_t q) const { return smem_u32(base + kOffBars + (2 * kStages + 8 + q) * 8); }
     __device__ uint32_t* tmem_ptr() const { return reinterpret_cast<uint32_t*>(base + kOffTmemPtr); }
     __device__ volatile int* abort_flag() const { return reinterpret_cast<volatile int*>(base + kOffAbort); }
     __device__ float* ws() const { return reinterpret_cast<float*>(base + kOffWs); }
@@ -93,6 +95,7 @@ __device__ __forceinline__ void gemm_i8_tcgen05_body(const GemmTcgen05Args& args
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < kStages; s++) { mbar_init(sm.full(s), 1); mbar_init(sm.empty(s), 1); }
         for (uint32_t b = 0; b < 2; b++) { mbar_init(sm.tmem_full(b), 1); mbar_init(sm.tmem_empty(b), kEpiThreads); }
+        for (uint32_t q = 0; q < 4; q++) { mbar_init(sm.pair_staged(q), 2); mbar_init(sm.pair_flushed(q), 2); }
         arm_abort(abort_flag, args.status);
         fence_barrier_init();
         prefetch_tmap(&args.tmap_a);
@@ -191,7 +194,13 @@ __device__ __forceinline__ void gemm_i8_tcgen05_body(const GemmTcgen05Args& args
         // never wait on one another
         float* s_ws = sm.ws() + (warp - 2u) * kEpiCols;
         float* s_bias = sm.bias() + (warp - 2u) * kEpiCols;
-        uint8_t* stage_tile = sm.base + kOffStages + (kStages - 1) * kStageBytes + (warp - 2u) * (32u * kEpiCols);
+        // fused all-gather: the two warps of a lane quarter (left and right half of the tile's columns)
+        // stage into ONE [32 rows x 256 B] tile, so that the flush can store whole 256-byte row
+        // segments - NVLink moves long contiguous runs far better than 128-byte ones; the pair meets on
+        // two mbarriers (bounded waits, like every wait here) instead of a bar.sync
+        uint8_t* stage_tile = sm.base + kOffStages + (kStages - 1) * kStageBytes + quarter * (32u * 2u * kEpiCols);
+        uint32_t pair_phase = 0;
+        bool first_gather_tile = true;
         const float zero_f = __int2float_rn(ep.out_zero);
         const float lo_f = __int2float_rn(ep.out_lo), hi_f = __int2float_rn(ep.out_hi);
         const bool sat_s8 = ep.out_lo == -128 && ep.out_hi == 127, sat_u8 = ep.out_lo == 0 && ep.out_hi == 255;
@@ -215,6 +224,11 @@ __device__ __forceinline__ void gemm_i8_tcgen05_body(const GemmTcgen05Args& args
             ok = __all_sync(0xffffffffu, mbar_wait(sm.tmem_full(acc), acc_phase, abort_flag));
             if (!ok) break;
             tc_fence_after();
+            if (gather && !first_gather_tile) {
+                // the partner must have finished flushing the previous tile out of the shared staging tile
+                ok = __all_sync(0xffffffffu, mbar_wait(sm.pair_flushed(quarter), pair_phase ^ 1u, abort_flag));
+                if (!ok) break;
+            }
 
             const uint32_t row = m0 + quarter * 32 + lane;
             const bool row_ok = row < args.rows;
@@ -294,10 +308,10 @@ __device__ __forceinline__ void gemm_i8_tcgen05_body(const GemmTcgen05Args& args
                         }
                     }
                     if (gather) {
-                        // row `lane` of this warp's [32 rows x 128 B] staging tile; 16-byte pieces
-                        // XOR-swizzled by row so that both the row-wise writes here and the
-                        // piece-wise reads of the flush are free of bank conflicts
-                        uint8_t* st = stage_tile + lane * kEpiCols;
+                        // this warp's half of row `lane` of the pair's [32 rows x 256 B] staging tile; 16-byte
+                        // pieces XOR-swizzled by row within the half so that both the row-wise writes here and
+                        // the piece-wise reads of the flush are free of bank conflicts
+                        uint8_t* st = stage_tile + lane * (2u * kEpiCols) + half * kEpiCols;
                         const uint32_t p0 = c >> 4;
                         *reinterpret_cast<uint4*>(st + (((p0) ^ (lane & 7u)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
                         *reinterpret_cast<uint4*>(st + (((p0 + 1u) ^ (lane & 7u)) << 4)) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
@@ -392,18 +406,23 @@ __device__ __forceinline__ void gemm_i8_tcgen05_body(const GemmTcgen05Args& args
             mbar_arrive(sm.tmem_empty(acc));
             acc ^= 1u;
             if (acc == 0) acc_phase ^= 1u;
+            if (!ok) break;
             if (gather) {
-                // flush the staged int8 tile: 8 lanes cover the 128 bytes of one row, 4 rows per
-                // pass, the same 16 bytes going to this GPU's buffer (destination 0) and to the
-                // same rows and columns of every peer's buffer - plain stores over NVLink, so the
+                // both halves staged -> this warp flushes 16 of the 32 rows: 16 lanes cover the 256 bytes of
+                // one row, 2 rows per pass, the same 16 bytes going to this GPU's buffer (destination 0) and
+                // to the same rows and columns of every peer's buffer - plain stores over NVLink, so the
                 // all-gather of the output is part of the epilogue and overlaps the next tile's MMAs
                 __syncwarp();
-                const uint32_t piece = lane & 7u;
+                if (lane == 0) mbar_arrive(sm.pair_staged(quarter));
+                ok = __all_sync(0xffffffffu, mbar_wait(sm.pair_staged(quarter), pair_phase, abort_flag));
+                if (!ok) break;
+                const uint32_t piece = lane & 15u, phalf = piece >> 3, p = piece & 7u;
+                const uint32_t tile_n0 = n0 - cbase;
 #pragma unroll 1
                 for (uint32_t i = 0; i < 8; i++) {
-                    const uint32_t rl = 4u * i + (lane >> 3);
-                    const uint4 v = *reinterpret_cast<const uint4*>(stage_tile + rl * kEpiCols + ((piece ^ (rl & 7u)) << 4));
-                    const uint32_t grow = m0 + quarter * 32 + rl, gcol = n0 + piece * 16;
+                    const uint32_t rl = half * 16u + 2u * i + (lane >> 4);
+                    const uint4 v = *reinterpret_cast<const uint4*>(stage_tile + rl * (2u * kEpiCols) + phalf * kEpiCols + ((p ^ (rl & 7u)) << 4));
+                    const uint32_t grow = m0 + quarter * 32 + rl, gcol = tile_n0 + piece * 16;
                     if (grow >= args.rows || gcol >= args.n) continue;
                     const bool whole = gcol + 16 <= args.n;
                     const size_t off = (size_t)grow * ep.ld + gcol;
@@ -420,6 +439,9 @@ __device__ __forceinline__ void gemm_i8_tcgen05_body(const GemmTcgen05Args& args
                     }
                 }
                 __syncwarp();
+                if (lane == 0) mbar_arrive(sm.pair_flushed(quarter));
+                pair_phase ^= 1u;
+                first_gather_tile = false;
             }
         }
     }
@@ -442,9 +464,10 @@ __global__ void __launch_bounds__(kThreads, 1)
 gemm_i8_tcgen05_kernel(const __grid_constant__ GemmTcgen05Args args) { gemm_i8_tcgen05_body(args); }
 
 // The same kernel held to 128 registers per thread (45 K of the SM's 64 K registers), which leaves
-// room for one CTA of the row quantizer beside it.  Used for the fused all-gather only: that launch
-// is bound by the NVLink stores of its epilogue, not by instruction issue, so the quantizer of the
-// later rows can run underneath it at no cost to the GEMM.
+// room for one CTA of the row quantizer beside it.  Launched for a link-bound fused all-gather when the
+// tunable "gemm.overlap_gather" is set (the quantizer of the later rows then runs underneath it).  Off
+// by default: measured on four GPUs the pair of launches took 207 us against 173 us for the single
+// launch of the full-register build after the whole-batch quantizer.
 __global__ void __maxnreg__(128)
 gemm_i8_tcgen05_gather_kernel(const __grid_constant__ GemmTcgen05Args args) { gemm_i8_tcgen05_body(args); }
 
@@ -517,7 +540,8 @@ cudaError_t launch_gemm_tcgen05(const GemmTcgen05Args& args, int sm_count, cudaS
     if (args.rows == 0 || args.n == 0) return cudaSuccess;
     const uint32_t tiles = ((args.rows + kBM - 1) / kBM) * ((args.n + kBN - 1) / kBN);
     const uint32_t grid = tiles < (uint32_t)sm_count ? tiles : (uint32_t)sm_count;
-    if (gather_is_link_bound(args.epi.n_peers, args.kpad)) gemm_i8_tcgen05_gather_kernel<<<grid, kThreads, kSmemBytes, stream>>>(args);
+    if (gather_is_link_bound(args.epi.n_peers, args.kpad) && tunables().overlap_gather)
+        gemm_i8_tcgen05_gather_kernel<<<grid, kThreads, kSmemBytes, stream>>>(args);
     else gemm_i8_tcgen05_kernel<<<grid, kThreads, kSmemBytes, stream>>>(args);
     return cudaGetLastError();
 }
