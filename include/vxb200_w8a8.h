@@ -413,7 +413,23 @@ VXB_API int vxb_cuda_graph_packed_linear_decode_f32(const float* input, const in
                                             uint32_t output_width, uint32_t weight_bits,
                                             uint32_t activation_bits);
 
-/* Drops every cached weight / context the reference-facing entries created
+/* Device residency behind the reference-facing entries, the counterpart of the reference backend's
+ * host-pointer -> device-slot table with dirty marking (graph_ensure_input_view / graph_mark_device,
+ * native/src/backends/cuda/host/cuda_graph_memory_host.inc:1302-1310).  Off (the default), every entry
+ * uploads its input, downloads its output and returns when the host buffer holds the result.  On, an
+ * entry's output stays in a device buffer keyed by its host address - the host copy is STALE until
+ * vxb_host_download(ptr) (NULL: every tensor) - and a later entry whose input is that tensor, or a row
+ * window inside it, reads it where it lies: a chain of nodes bound through these entries crosses PCIe
+ * once in and once out instead of twice per node.  Ownership rule: while residency is on, the host
+ * calls vxb_host_download before it reads such an output and vxb_host_invalidate(ptr) (NULL: all)
+ * after it writes into one by itself; inputs the library did not produce are uploaded on every call, so
+ * plain host inputs need no announcement.  Partial output windows are written to the host at once.
+ * Turning residency off downloads everything that is still device-dirty. */
+VXB_API int vxb_host_residency(int enable);
+VXB_API int vxb_host_download(const void* host_ptr);
+VXB_API int vxb_host_invalidate(const void* host_ptr);
+
+/* Drops every cached weight / context / resident tensor the reference-facing entries created
  * (the counterpart of freeing a compiled model). */
 VXB_API void vxb_host_cache_clear(void);
 

@@ -30,6 +30,7 @@ EXPORTS = [
     "vxb_dequantize_linear_device", "vxb_requantize_linear_device", "vxb_quantize_typed_f32_i8u8",
     "vxb_dequantize_typed_i8u8_f32", "vxb_requantize_linear_i8u8", "vxb_decode_linear_f32_noalloc", "vxb_qlinear_i8u8",
     "vxb_cuda_graph_llm_f32", "vxb_cuda_graph_packed_linear_decode_f32", "vxb_host_cache_clear",
+    "vxb_host_residency", "vxb_host_download", "vxb_host_invalidate",
 ]
 
 
@@ -200,6 +201,9 @@ def load() -> C.CDLL:
     L.vxb_cuda_graph_llm_f32.argtypes = [C.POINTER(LLMOpArgs)]
     L.vxb_cuda_graph_packed_linear_decode_f32.argtypes = [vp, vp, vp, vp, vp, u32, u32, u32, u32]
     L.vxb_host_cache_clear.restype = None
+    L.vxb_host_residency.argtypes = [C.c_int]
+    L.vxb_host_download.argtypes = [vp]
+    L.vxb_host_invalidate.argtypes = [vp]
     for name in EXPORTS:
         fn = getattr(L, name)
         if fn.restype is C.c_int and name.startswith("vxb_") and name not in (

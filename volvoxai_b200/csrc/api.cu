@@ -10,6 +10,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <map>
 #include <mutex>
 #include <unordered_map>
 #include <vector>
@@ -1321,6 +1322,90 @@ bool overlap(const void* a, size_t an, const void* b, size_t bn) {
     return x < y + bn && y < x + an;
 }
 
+// ---- device residency of host tensors (vxb_host_residency) -----------------------------------------
+// The reference's CUDA backend keeps a table from host pointers to device slots, uploads only inputs
+// whose host copy is newer and leaves outputs device-dirty until something on the host needs them
+// (graph_ensure_input_view / graph_mark_device, native/src/backends/cuda/host/
+// cuda_graph_memory_host.inc:1302-1310).  The same here, behind the host-pointer entries: with
+// residency on, an output stays in its device buffer (the host copy is stale until
+// vxb_host_download), and an input that is such a device-dirty tensor - or a window of one: row
+// windows are interior pointers - is consumed where it lies.  Inputs the library did not produce are
+// uploaded on every call: the host may have rewritten them.
+struct Resident { void* dev; size_t bytes; bool dirty; };
+std::map<uintptr_t, Resident> g_resident;   // keyed by host address; ranges never overlap
+bool g_residency = false;
+
+std::map<uintptr_t, Resident>::iterator resident_containing(const void* host, size_t bytes) {
+    auto it = g_resident.upper_bound((uintptr_t)host);
+    if (it == g_resident.begin()) return g_resident.end();
+    --it;
+    return ((uintptr_t)host + bytes <= it->first + it->second.bytes) ? it : g_resident.end();
+}
+
+// Makes the host copies of every resident tensor overlapping [host, host+bytes) current and drops the entries.
+int resident_evict(VxbContext* ctx, const void* host, size_t bytes) {
+    for (auto it = g_resident.begin(); it != g_resident.end();) {
+        if (overlap(host, bytes, (const void*)it->first, it->second.bytes)) {
+            if (it->second.dirty)
+                CUDA_TRY(cudaMemcpyAsync((void*)it->first, it->second.dev, it->second.bytes, cudaMemcpyDeviceToHost, ctx->stream), -1);
+            CUDA_TRY(cudaStreamSynchronize(ctx->stream), -1);
+            cudaFree(it->second.dev);
+            it = g_resident.erase(it);
+        } else ++it;
+    }
+    return 1;
+}
+
+// Device address of an input: a device-dirty resident tensor (or a window of one) in place, else an upload
+// into `staging`.
+int resident_input(VxbContext* ctx, const void* host, size_t bytes, Buffer& staging, const void** dev) {
+    if (g_residency) {
+        auto it = resident_containing(host, bytes);
+        if (it != g_resident.end() && it->second.dirty) {
+            *dev = (const uint8_t*)it->second.dev + ((uintptr_t)host - it->first);
+            return 1;
+        }
+        // an input that only straddles device-dirty tensors: their host copies are made current first
+        if (it == g_resident.end()) {
+            const int rc = resident_evict(ctx, host, bytes);
+            if (rc != 1) return rc;
+        }
+    }
+    CUDA_TRY(staging.reserve(bytes), 0);
+    CUDA_TRY(cudaMemcpyAsync(staging.ptr, host, bytes, cudaMemcpyHostToDevice, ctx->stream), -1);
+    *dev = staging.ptr;
+    return 1;
+}
+
+// Device address an output is computed into: with residency its own buffer (created on first use; any
+// other resident range it overlaps is written back and dropped first), else `staging`.
+int resident_output(VxbContext* ctx, void* host, size_t bytes, Buffer& staging, void** dev, bool* lazy) {
+    *lazy = false;
+    if (g_residency) {
+        auto it = g_resident.find((uintptr_t)host);
+        if (it == g_resident.end() || it->second.bytes != bytes) {
+            const int rc = resident_evict(ctx, host, bytes);
+            if (rc != 1) return rc;
+            void* d = nullptr;
+            if (injected(g_fail_alloc) || cudaMalloc(&d, bytes) != cudaSuccess) return fail(0, "device allocation of a resident output failed");
+            it = g_resident.emplace((uintptr_t)host, Resident{d, bytes, false}).first;
+        }
+        *dev = it->second.dev;
+        *lazy = true;
+        return 1;
+    }
+    CUDA_TRY(staging.reserve(bytes), 0);
+    *dev = staging.ptr;
+    return 1;
+}
+
+// After the kernels: the output is device-dirty (residency) or copied to the host now; then the stream is drained.
+int resident_finish(VxbContext* ctx, void* host, size_t bytes, const void* dev, bool lazy) {
+    if (lazy) g_resident[(uintptr_t)host].dirty = true;
+    else CUDA_TRY(cudaMemcpyAsync(host, dev, bytes, cudaMemcpyDeviceToHost, ctx->stream), -1);
+    return vxb_context_synchronize(ctx) == 1 ? 1 : -1;
+}
+
 }  // namespace
 
 extern "C" {
@@ -1353,15 +1438,13 @@ int vxb_qlinear_i8u8(const void* input, const void* weight, const float* weight_
         if (rc != 1) return rc;
         g_host_weights.emplace(key, w);
     }
-    CUDA_TRY(ctx->stage_in.reserve(in_bytes), 0);
-    CUDA_TRY(ctx->stage_out.reserve(out_bytes), 0);
-    CUDA_TRY(cudaMemcpyAsync(ctx->stage_in.ptr, input, in_bytes, cudaMemcpyHostToDevice, ctx->stream), -1);
-    rc = vxb_qlinear_device(ctx, w, ctx->stage_in.ptr, rows, input_scale, input_zero_point, output_scale,
-                            output_zero_point, input_dtype, output_dtype, ctx->stage_out.ptr, d_out,
-                            VXB_ROUTE_AUTO);
+    const void* din = nullptr; void* dout = nullptr; bool lazy = false;
+    if ((rc = resident_output(ctx, output, out_bytes, ctx->stage_out, &dout, &lazy)) != 1) return rc;
+    if ((rc = resident_input(ctx, input, in_bytes, ctx->stage_in, &din)) != 1) return rc;
+    rc = vxb_qlinear_device(ctx, w, din, rows, input_scale, input_zero_point, output_scale,
+                            output_zero_point, input_dtype, output_dtype, dout, d_out, VXB_ROUTE_AUTO);
     if (rc != 1) return rc;
-    CUDA_TRY(cudaMemcpyAsync(output, ctx->stage_out.ptr, out_bytes, cudaMemcpyDeviceToHost, ctx->stream), -1);
-    return vxb_context_synchronize(ctx) == 1 ? 1 : -1;
+    return resident_finish(ctx, output, out_bytes, dout, lazy);
 }
 
 extern "C++" {
@@ -1375,13 +1458,12 @@ int host_elementwise(const void* input, size_t in_bytes, void* output, size_t ou
     VxbContext* ctx = nullptr;
     int rc = host_context(&ctx);
     if (rc != 1) return rc;
-    CUDA_TRY(ctx->stage_in.reserve(in_bytes), 0);
-    CUDA_TRY(ctx->stage_out.reserve(out_bytes), 0);
-    CUDA_TRY(cudaMemcpyAsync(ctx->stage_in.ptr, input, in_bytes, cudaMemcpyHostToDevice, ctx->stream), -1);
-    rc = device_call(ctx, ctx->stage_in.ptr, ctx->stage_out.ptr);
+    const void* din = nullptr; void* dout = nullptr; bool lazy = false;
+    if ((rc = resident_output(ctx, output, out_bytes, ctx->stage_out, &dout, &lazy)) != 1) return rc;
+    if ((rc = resident_input(ctx, input, in_bytes, ctx->stage_in, &din)) != 1) return rc;
+    rc = device_call(ctx, const_cast<void*>(din), dout);
     if (rc != 1) return rc;
-    CUDA_TRY(cudaMemcpyAsync(output, ctx->stage_out.ptr, out_bytes, cudaMemcpyDeviceToHost, ctx->stream), -1);
-    return vxb_context_synchronize(ctx) == 1 ? 1 : -1;
+    return resident_finish(ctx, output, out_bytes, dout, lazy);
 }
 }  // namespace
 }  // extern "C++"
@@ -1459,13 +1541,19 @@ int vxb_cuda_graph_llm_f32(const VxbLLMOpArgs* a) {
         g_host_weights.emplace(key, w);
     }
     const size_t in_bytes = (size_t)rows * k * 4, out_bytes = (size_t)rows * n * 4;
-    CUDA_TRY(ctx->stage_in.reserve(in_bytes), 0);
-    CUDA_TRY(ctx->stage_out.reserve(out_bytes), 0);
-    CUDA_TRY(cudaMemcpyAsync(ctx->stage_in.ptr, a->x[0] + (size_t)row0 * k, in_bytes, cudaMemcpyHostToDevice, ctx->stream), -1);
-    rc = vxb_linear_f32(ctx, w, (const float*)ctx->stage_in.ptr, rows, (float*)ctx->stage_out.ptr, n, VXB_ROUTE_AUTO);
+    const void* din = nullptr; void* dout = nullptr; bool lazy = false;
+    float* y_host = a->y[0] + (size_t)row0 * n;
+    if (rows != rows64) {
+        // a partial window keeps the bytes outside it: computed through staging and written to the host at
+        // once; a resident copy of the tensor is brought home first so that both stay one tensor
+        if (g_residency && (rc = resident_evict(ctx, a->y[0], (size_t)rows64 * n * 4)) != 1) return rc;
+        CUDA_TRY(ctx->stage_out.reserve(out_bytes), 0);
+        dout = ctx->stage_out.ptr;
+    } else if ((rc = resident_output(ctx, y_host, out_bytes, ctx->stage_out, &dout, &lazy)) != 1) return rc;
+    if ((rc = resident_input(ctx, a->x[0] + (size_t)row0 * k, in_bytes, ctx->stage_in, &din)) != 1) return rc;
+    rc = vxb_linear_f32(ctx, w, (const float*)din, rows, (float*)dout, n, VXB_ROUTE_AUTO);
     if (rc != 1) return rc == 0 ? 0 : -1;
-    CUDA_TRY(cudaMemcpyAsync(a->y[0] + (size_t)row0 * n, ctx->stage_out.ptr, out_bytes, cudaMemcpyDeviceToHost, ctx->stream), -1);
-    return vxb_context_synchronize(ctx) == 1 ? 1 : -1;
+    return resident_finish(ctx, y_host, out_bytes, dout, lazy);
 }
 
 int vxb_cuda_graph_packed_linear_decode_f32(const float* input, const int32_t* packed_weights,
@@ -1483,10 +1571,51 @@ int vxb_cuda_graph_packed_linear_decode_f32(const float* input, const int32_t* p
     return vxb_cuda_graph_llm_f32(&a);
 }
 
+int vxb_host_residency(int enable) {
+    std::lock_guard<std::mutex> lock(g_host_mutex);
+    if (!enable && g_residency && g_host_ctx) {
+        // leaving the mode: every device-dirty tensor goes home first
+        for (auto& kv : g_resident)
+            if (kv.second.dirty) {
+                CUDA_TRY(cudaMemcpyAsync((void*)kv.first, kv.second.dev, kv.second.bytes, cudaMemcpyDeviceToHost, g_host_ctx->stream), -1);
+                kv.second.dirty = false;
+            }
+        CUDA_TRY(cudaStreamSynchronize(g_host_ctx->stream), -1);
+    }
+    g_residency = enable != 0;
+    return 1;
+}
+
+int vxb_host_download(const void* host) {
+    std::lock_guard<std::mutex> lock(g_host_mutex);
+    if (!g_host_ctx) return 1;
+    bool found = host == nullptr;
+    for (auto& kv : g_resident) {
+        if (host && !overlap(host, 1, (const void*)kv.first, kv.second.bytes)) continue;
+        found = true;
+        if (!kv.second.dirty) continue;
+        CUDA_TRY(cudaMemcpyAsync((void*)kv.first, kv.second.dev, kv.second.bytes, cudaMemcpyDeviceToHost, g_host_ctx->stream), -1);
+        kv.second.dirty = false;
+    }
+    CUDA_TRY(cudaStreamSynchronize(g_host_ctx->stream), -1);
+    return found ? 1 : fail(0, "no resident tensor at this host address");
+}
+
+int vxb_host_invalidate(const void* host) {
+    std::lock_guard<std::mutex> lock(g_host_mutex);
+    for (auto it = g_resident.begin(); it != g_resident.end();) {
+        if (!host || overlap(host, 1, (const void*)it->first, it->second.bytes)) { cudaFree(it->second.dev); it = g_resident.erase(it); }
+        else ++it;
+    }
+    return 1;
+}
+
 void vxb_host_cache_clear(void) {
     std::lock_guard<std::mutex> lock(g_host_mutex);
     for (auto& kv : g_host_weights) vxb_weight_destroy(kv.second);
     g_host_weights.clear();
+    for (auto& kv : g_resident) cudaFree(kv.second.dev);   // device copies are dropped, not written back
+    g_resident.clear();
     if (g_host_ctx) { vxb_context_destroy(g_host_ctx); g_host_ctx = nullptr; }
 }
 

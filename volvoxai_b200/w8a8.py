@@ -24,7 +24,7 @@ from ._lib import (DT_I8, DT_U8, OP_PACKED_LINEAR, ROUTE_AUTO, ROUTE_DECODE, ROU
                    ROUTE_TCGEN05, LLMOpArgs, last_error, last_route)
 
 __all__ = ["Context", "Weight", "W8A8Error", "variants", "plan", "registry_rows", "qlinear_i8u8", "packed_linear",
-           "packed_linear_decode", "host_cache_clear", "launch_count", "last_error",
+           "packed_linear_decode", "host_cache_clear", "host_residency", "host_download", "host_invalidate", "launch_count", "last_error",
            "quantize_typed_f32_i8u8", "dequantize_typed_i8u8_f32", "requantize_linear_i8u8", "last_route", "ROUTE_AUTO", "ROUTE_GEMV", "ROUTE_TCGEN05", "ROUTE_SIMT", "ROUTE_DECODE", "ROUTE_DECODE_STREAMK", "ROUTE_TCGEN05_PAIR", "ROUTE_DECODE_FUSED",
            "DT_I8", "DT_U8"]
 
@@ -462,3 +462,19 @@ def packed_linear_decode(x, words, scales, bias, y, *, weight_bits=8, activation
 
 def host_cache_clear() -> None:
     _lib.load().vxb_host_cache_clear()
+
+
+def host_residency(enable: bool) -> int:
+    """Outputs of the reference-facing entries stay on the device (host copies stale until
+    host_download) and feed later entries in place; see vxb_host_residency."""
+    return int(_lib.load().vxb_host_residency(1 if enable else 0))
+
+
+def host_download(array=None) -> int:
+    """Makes the host copy of a device-resident output current (None: every tensor)."""
+    return int(_lib.load().vxb_host_download(_ptr(array)))
+
+
+def host_invalidate(array=None) -> int:
+    """The host wrote this buffer itself: drop its device copy (None: all)."""
+    return int(_lib.load().vxb_host_invalidate(_ptr(array)))
