@@ -45,6 +45,8 @@ extern "C" {
 #define VXB_VF_FUSED_TAIL 4u  /* carries the residual-Add / SiLU*Mul tails of the fp32 epilogue */
 #define VXB_VF_VERIFY 8u      /* verification kernel: explicit request only */
 #define VXB_VF_FUSED_K1 16u   /* quantizes the fp32 rows itself: one launch per linear, fp32 input only */
+#define VXB_VF_TILE_STORE 32u /* 32-bit outputs leave as TMA tile stores: 16-byte aligned output base and row pitch, \
+                                 residual Add as the only fused tail */
 
 /*
  * Variant rows.  Fields:
@@ -62,6 +64,7 @@ extern "C" {
     X(SIMT_DP4A,        3, "simt-dp4a",                 "gemm_simt_kernel",               4, 128,   0, 128, 1,      0,   1,   0, 7u, 1u, 0, 8u,             1) \
     X(TCGEN05,          2, "tcgen05-i8",                "gemm_i8_tcgen05_kernel",       128, 256, 128, 352, 1, 223000,   1,   0, 7u, 1u, 0, 1u | 2u | 4u,  600) \
     X(TCGEN05_PAIR,     6, "tcgen05-pair-i8",           "gemm_i8_pair_kernel",          256, 256, 256, 352, 2, 223000,   1,   0, 7u, 1u, 0, 1u | 4u,       650) \
+    X(TCGEN05_WIDE,     8, "tcgen05-wide-i8",           "gemm_i8_wide_kernel",          128, 256, 128, 608, 1, 231000,   1,   0, 3u, 1u, 0, 1u | 4u | 32u, 640) \
     X(GROUPED_TCGEN05,  0, "tcgen05-grouped-i8",        "gemm_i8_grouped_tcgen05_kernel", 128, 128, 128, 320, 1, 223000,   1,   0, 2u, 6u, 0, 1u,           500) \
     X(GEMV_GROUPED,     0, "gemv-grouped",              "gemv_grouped_kernel",            0,   0,   0, 256, 1,  65536,   1,   4, 2u, 6u, 0, 1u,           550) \
     X(GEMV_W4_GROUPED,  0, "gemv-w4-grouped",           "gemv_w4_grouped_kernel",         0,   0,   0, 256, 1,  65536,   1,   2, 2u, 4u, 0, 1u,           560) \
@@ -92,10 +95,11 @@ typedef struct VxbPlanQuery {
     uint32_t epilogue;       /* one VXB_EPI_* bit */
     int32_t requested_route; /* VXB_ROUTE_AUTO or an explicit VXB_ROUTE_* */
     uint32_t n_peers;        /* > 0: fused all-gather into peer buffers */
-    uint32_t fused_tail;     /* residual Add or SiLU*Mul on the fp32 epilogue */
+    uint32_t fused_tail;     /* tails of the fp32 epilogue: bit 0 residual Add, bit 1 SiLU*Mul over channel pairs */
     uint32_t fp32_input;     /* the call starts from fp32 activations (a K1 quantizer is part of it) */
     uint32_t sm_count;       /* SMs of the device (148 on a B200) */
     uint32_t pair_clusters;  /* co-resident clusters of two the device grants the pair kernel (0: none) */
+    uint32_t out_store_aligned; /* the output base and row pitch are multiples of 16 bytes (TMA tile stores possible) */
 } VxbPlanQuery;
 
 /* Per-row quantizer (K1) chosen for calls that start from fp32 activations. */
@@ -117,6 +121,8 @@ typedef struct VxbLaunchPlan {
     uint64_t workspace_bytes; /* context scratch the call needs (quantized rows, scales, split-K partials) */
 } VxbLaunchPlan;
 
+#define VXB_WIDE_MAX_KPAD 1536u /* measured: equal at 2048, slower beyond (three pipeline stages) */
+
 VXB_PLAN_API uint32_t vxb_variant_count(void);
 /* NULL when index is out of range. */
 VXB_PLAN_API const VxbVariant* vxb_variant_info(uint32_t index);
@@ -127,7 +133,9 @@ VXB_PLAN_API const VxbVariant* vxb_variant_info(uint32_t index);
  *   per-channel scales: rows <= 128 -> the decode kernel (its single-launch form, which quantizes the
  *     rows itself, for fp32 input of one or two rows with a padded K of at most 8192 and d_in a
  *     multiple of 4; an explicit request admits it up to 8 rows), else the tensor-core GEMM, by pairs
- *     of CTAs once there are two waves of 128 x 256 tiles;
+ *     of CTAs once there are two waves of 128 x 256 tiles; 32-bit outputs with a padded K of at most
+ *     VXB_WIDE_MAX_KPAD (the output, not the tensor pipe, bounds those launches) take the kernel
+ *     built for them (sixteen epilogue warps, TMA tile stores) when the output is 16-byte aligned;
  *   grouped scales: 1-2 rows (3-4 with <= 32 MB of weights) -> the streaming GEMV (over the 4-bit
  *     words when kept), else the tensor-core kernel with a per-group accumulator drain. */
 VXB_PLAN_API int vxb_plan(const VxbPlanQuery* query, VxbLaunchPlan* out, char* why, uint32_t why_bytes);

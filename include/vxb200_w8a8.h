@@ -62,7 +62,8 @@ enum {
     VXB_ROUTE_DECODE = 4,   /* weight-streaming tcgen05 kernel, whole channels per CTA (rows <= 128) */
     VXB_ROUTE_DECODE_STREAMK = 5, /* weight-streaming stream-K tcgen05 kernel (rows <= 128) */
     VXB_ROUTE_TCGEN05_PAIR = 6, /* the tcgen05 GEMM by pairs of CTAs (cta_group::2) on 256 x 256 tiles */
-    VXB_ROUTE_DECODE_FUSED = 7  /* the decode kernel quantizing the fp32 rows itself: one launch (rows <= 8, fp32 input) */
+    VXB_ROUTE_DECODE_FUSED = 7, /* the decode kernel quantizing the fp32 rows itself: one launch (rows <= 8, fp32 input) */
+    VXB_ROUTE_TCGEN05_WIDE = 8  /* the GEMM for 32-bit outputs: sixteen epilogue warps, TMA tile stores (aligned output) */
 };
 
 VXB_API uint32_t vxb_abi_version(void);

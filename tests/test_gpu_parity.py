@@ -38,7 +38,7 @@ def rel_err(y, ref):
     return float(np.abs(y[ok].astype(np.float64) - ref[ok]).max() / max(rms, 1e-30)) if ok.any() else 0.0
 
 
-ROUTES = {"auto": 0, "gemv": 1, "tcgen05": 2, "simt": 3, "decode": 4, "streamk": 5, "pair": 6, "fused": 7}
+ROUTES = {"auto": 0, "gemv": 1, "tcgen05": 2, "simt": 3, "decode": 4, "streamk": 5, "pair": 6, "fused": 7, "wide": 8}
 
 
 def run_case(torch, ctx, oracle, case, routes, bias_i32=None, out_zero=0):
@@ -696,6 +696,53 @@ def test_fused_residual_and_silu_mul(torch, ctx, oracle, rows, k, n):
     with pytest.raises(w8a8.W8A8Error) as e:
         ctx.linear_f32_fused(weight, xd, residual=dev(torch, res), silu_mul=True)
     assert e.value.code == 0
+    weight.close()
+
+
+# ---- the wide-output GEMM (32-bit outputs, TMA tile stores) -------------------------------------
+
+@pytest.mark.parametrize("rows,k,n", [(129, 65, 8), (257, 576, 20), (300, 320, 1000), (4096, 576, 576),
+                                      (4096, 576, 3072), (1000, 1536, 576), (513, 2048, 260), (130, 4096, 516)])
+def test_wide_output_kernel(torch, ctx, oracle, rows, k, n):
+    """gemm_i8_wide_kernel (sixteen epilogue warps, TMA tile stores clipped at ragged edges): raw
+    accumulators exact, fp32 output within the tolerance and bit-identical to the general kernel's, with
+    bias and with the fused residual Add; chosen automatically for aligned 32-bit outputs up to a padded K
+    of 1536, refused for int8 outputs, unaligned outputs and the SiLU*Mul tail."""
+    from volvoxai_b200 import w8a8
+    c = wl.single_linear(rows=rows, k=k, n=n, seed=rows * 7 + n)
+    ref = oracle.w8a8_linear(c["x"], c["w"], c["ws"], bias=c["bias"])
+    weight = w8a8.Weight.from_i8(ctx, c["w"], c["ws"], bias_f32=c["bias"])
+    xd = dev(torch, c["x"])
+    acc = ctx.linear_acc_i32(weight, xd, route=w8a8.ROUTE_TCGEN05_WIDE).cpu().numpy()
+    assert "tcgen05-wide-i8+acc" in w8a8.last_route()
+    assert np.array_equal(acc, ref["acc"])
+    y = ctx.linear_f32(weight, xd, route=w8a8.ROUTE_TCGEN05_WIDE).cpu().numpy()
+    general = ctx.linear_f32(weight, xd, route=w8a8.ROUTE_TCGEN05).cpu().numpy()
+    assert np.array_equal(y.view(np.uint32), general.view(np.uint32))
+    assert rel_err(y, ref["out"]) <= F32_TOL
+    auto = ctx.linear_f32(weight, xd).cpu().numpy()
+    assert ("tcgen05-wide-i8" in w8a8.last_route()) == (k <= 1536)
+    assert np.array_equal(auto.view(np.uint32), y.view(np.uint32))
+    # an output buffer wider than the matrix (row pitch > n) and the bytes beside it stay untouched
+    wide = torch.full((rows, n + 12), -7.0, device="cuda")
+    ctx.linear_f32(weight, xd, out=wide[:, 4:4 + n], route=w8a8.ROUTE_TCGEN05_WIDE)
+    got = wide.cpu().numpy()
+    assert np.array_equal(got[:, 4:4 + n].view(np.uint32), y.view(np.uint32))
+    assert (got[:, :4] == -7.0).all() and (got[:, 4 + n:] == -7.0).all()
+    res = np.random.default_rng(rows).standard_normal((rows, n)).astype(np.float32)
+    fused = ctx.linear_f32_fused(weight, xd, residual=dev(torch, res)).cpu().numpy()
+    assert np.array_equal(fused.view(np.uint32), (y + res).view(np.uint32))
+    with pytest.raises(w8a8.W8A8Error) as e:
+        ctx.linear_i8(weight, xd, 0.05, route=w8a8.ROUTE_TCGEN05_WIDE)
+    assert e.value.code == 0
+    if n % 4 == 0:
+        odd = torch.empty(rows * n + 1, device="cuda")[1:].view(rows, n)      # base 4 bytes off a 16-byte boundary
+        with pytest.raises(w8a8.W8A8Error) as e:
+            ctx.linear_f32(weight, xd, out=odd, route=w8a8.ROUTE_TCGEN05_WIDE)
+        assert e.value.code == 0 and "aligned" in str(e.value)
+        ctx.linear_f32(weight, xd, out=odd)                                   # the automatic route falls back
+        assert "wide" not in w8a8.last_route()
+        assert np.array_equal(odd.cpu().numpy().view(np.uint32), y.view(np.uint32))
     weight.close()
 
 

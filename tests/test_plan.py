@@ -48,12 +48,20 @@ def test_automatic_route_boundaries_per_channel():
     assert pick(2, 4098, 512)["id"] == "DECODE_ROWS"                         # d_in not a multiple of 4
     assert pick(2, 1024, 512, fused_tail=True)["id"] == "DECODE_FUSED"
     assert pick(128, 1024, 3072)["id"] == "DECODE_ROWS"
-    assert pick(129, 1024, 3072)["id"] == "TCGEN05"
+    assert pick(129, 1024, 3072, epilogue=_lib.EPI_I8)["id"] == "TCGEN05"
+    # 32-bit outputs with a padded K of at most 1536: the wide-output kernel, when the output is 16-byte aligned
+    assert pick(129, 1024, 3072)["id"] == "TCGEN05_WIDE"
+    assert pick(4096, 576, 3072)["id"] == "TCGEN05_WIDE"                      # would be a pair launch otherwise
+    assert pick(4096, 1536, 3072, epilogue=_lib.EPI_ACC)["id"] == "TCGEN05_WIDE"
+    assert pick(4096, 1537, 3072)["id"] == "TCGEN05_PAIR"                     # padded K 1664
+    assert pick(129, 1024, 3072, out_store_aligned=False)["id"] == "TCGEN05"
+    assert pick(129, 1024, 3072, fused_tail=1)["id"] == "TCGEN05_WIDE"        # residual Add
+    assert pick(129, 1024, 3072, fused_tail=2)["id"] == "TCGEN05"             # SiLU*Mul stays in the general kernel
     # two waves of 128 x 256 tiles on 148 SMs = 296 tiles: 8192 x 14336 has 64 * 56 = 3584
     assert pick(8192, 4096, 14336, epilogue=_lib.EPI_I8)["id"] == "TCGEN05_PAIR"
     # 4096 x 576 -> 1536: 32 * 6 = 192 tiles, below two waves
-    assert pick(4096, 576, 1536)["id"] == "TCGEN05"
-    assert pick(4096, 576, 2560)["id"] == "TCGEN05_PAIR"     # 32 * 10 = 320 tiles
+    assert pick(4096, 576, 1536, epilogue=_lib.EPI_I8)["id"] == "TCGEN05"
+    assert pick(4096, 576, 2560, epilogue=_lib.EPI_I8)["id"] == "TCGEN05_PAIR"     # 32 * 10 = 320 tiles
     # no co-resident pairs on the device: the single-CTA kernel serves everything
     plan, _ = w8a8.plan(8192, 4096, 14336, sm_count=B200_SMS, pair_clusters=0)
     assert plan["id"] == "TCGEN05"
@@ -85,8 +93,11 @@ def test_automatic_route_grouped_scales():
 def test_explicit_requests_are_honoured_or_refused_never_replaced():
     for route, vid in ((w8a8.ROUTE_GEMV, "GEMV_DP4A"), (w8a8.ROUTE_TCGEN05, "TCGEN05"), (w8a8.ROUTE_SIMT, "SIMT_DP4A"),
                        (w8a8.ROUTE_DECODE, "DECODE_ROWS"), (w8a8.ROUTE_DECODE_STREAMK, "DECODE_STREAMK"),
-                       (w8a8.ROUTE_TCGEN05_PAIR, "TCGEN05_PAIR")):
+                       (w8a8.ROUTE_TCGEN05_PAIR, "TCGEN05_PAIR"), (w8a8.ROUTE_TCGEN05_WIDE, "TCGEN05_WIDE")):
         assert pick(16, 1024, 512, route=route)["id"] == vid
+    for kw in (dict(epilogue=_lib.EPI_I8), dict(out_store_aligned=False), dict(fused_tail=2), dict(n_peers=1)):
+        plan, why = w8a8.plan(300, 1024, 512, route=w8a8.ROUTE_TCGEN05_WIDE, **kw)
+        assert plan is None and why
     assert pick(8, 1024, 512, route=w8a8.ROUTE_DECODE_FUSED)["id"] == "DECODE_FUSED"
     for kw in (dict(rows=9), dict(fp32_input=False), dict(k=1026)):
         args = dict(rows=8, k=1024, n=512, route=w8a8.ROUTE_DECODE_FUSED, fp32_input=True)
@@ -113,8 +124,10 @@ def test_exact_launch_geometry():
     assert (p["grid"], p["threads"], p["cluster"]) == (2 * B200_PAIRS, 352, 2)
     assert (p["tile_rows"], p["tile_columns"], p["tile_k"]) == (256, 256, 256)
     assert (p["launches"], p["quantizer"], p["quantizer_grid"]) == (2, 2, 8192 // 2)   # vec quantizer, 128 threads per row
-    p = pick(300, 576, 1536)
+    p = pick(300, 576, 1536, epilogue=_lib.EPI_I8)
     assert (p["grid"], p["threads"], p["cluster"]) == (3 * 6, 352, 1)
+    p = pick(300, 576, 1536)
+    assert (p["id"], p["grid"], p["threads"], p["cluster"], p["tile_columns"]) == ("TCGEN05_WIDE", 3 * 6, 608, 1, 256)
     # decode: every CTA owns ceil(N / 148) whole channels (even, so gate/up pairs never straddle CTAs)
     p = pick(1, 4096, 14336)
     assert (p["tile_columns"], p["grid"], p["threads"], p["tile_rows"]) == (98, 147, 544, 8)

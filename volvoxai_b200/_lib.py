@@ -15,6 +15,7 @@ OP_PACKED_LINEAR = 1036
 ROUTE_AUTO, ROUTE_GEMV, ROUTE_TCGEN05, ROUTE_SIMT, ROUTE_DECODE, ROUTE_DECODE_STREAMK = 0, 1, 2, 3, 4, 5
 ROUTE_TCGEN05_PAIR = 6
 ROUTE_DECODE_FUSED = 7
+ROUTE_TCGEN05_WIDE = 8
 
 # Every symbol include/vxb200_w8a8.h declares.
 EXPORTS = [
@@ -65,7 +66,7 @@ class PlanQuery(C.Structure):
     _fields_ = [("rows", C.c_uint32), ("k", C.c_uint32), ("n", C.c_uint32), ("weight_kind", C.c_uint32),
                 ("group_size", C.c_uint32), ("epilogue", C.c_uint32), ("requested_route", C.c_int32),
                 ("n_peers", C.c_uint32), ("fused_tail", C.c_uint32), ("fp32_input", C.c_uint32),
-                ("sm_count", C.c_uint32), ("pair_clusters", C.c_uint32)]
+                ("sm_count", C.c_uint32), ("pair_clusters", C.c_uint32), ("out_store_aligned", C.c_uint32)]
 
 
 class LaunchPlan(C.Structure):

@@ -17,7 +17,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 ROOT = os.path.dirname(PKG)
 LIB = os.path.join(PKG, "libvxb200.so")
-SOURCES = ["api.cu", "plan.cu", "package.cu", "selftest.cu", "quantize.cu", "gemv.cu", "gemm_tcgen05.cu", "gemm_pair_tcgen05.cu", "gemm_grouped_tcgen05.cu", "decode_tcgen05.cu", "decode_rows.cu", "boundary_ops.cu"]
+SOURCES = ["api.cu", "plan.cu", "package.cu", "selftest.cu", "quantize.cu", "gemv.cu", "gemm_tcgen05.cu", "gemm_pair_tcgen05.cu", "gemm_wide_tcgen05.cu", "gemm_grouped_tcgen05.cu", "decode_tcgen05.cu", "decode_rows.cu", "boundary_ops.cu"]
 HEADERS = [os.path.join(CSRC, "common.cuh"), os.path.join(CSRC, "tcgen05.cuh"), os.path.join(CSRC, "diag.h"), os.path.join(ROOT, "include", "vxb200_w8a8.h"), os.path.join(ROOT, "include", "vxb200_plan.h"), os.path.join(ROOT, "include", "vxb200_package.h")]
 
 NVCC_FLAGS = [

@@ -79,6 +79,20 @@ bool encode_i8_rows(CUtensorMap* map, const void* base, uint32_t rows, uint32_t 
 
 // The same matrix seen as {128 B, rows, kpad / 128}: a box of (128 B x box_rows x box_blocks) lands as
 // box_blocks consecutive [box_rows x 128 B] swizzled tiles, one per 128-byte K block.
+// 32-bit matrix [rows, n] with row pitch ld (elements) -> 2-D tensor map with a (32 columns x 32 rows) box,
+// 128B swizzle: the wide-output GEMM's TMA tile stores
+bool encode_out32(CUtensorMap* map, const void* base, uint32_t rows, uint32_t n, uint32_t ld) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn || ((uintptr_t)base & 15u) || (ld & 3u)) return false;
+    cuuint64_t dims[2] = {n, rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 4u};
+    cuuint32_t box[2] = {32, 32};
+    cuuint32_t elem[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+              CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 bool encode_i8_kblocks(CUtensorMap* map, const void* base, uint32_t rows, uint32_t kpad, uint32_t box_rows,
                        uint32_t box_blocks) {
     EncodeTiledFn fn = encode_fn();
@@ -277,7 +291,8 @@ VxbPlanQuery plan_query(const VxbContext* ctx, const VxbWeight* w, uint32_t rows
     query.weight_kind = weight_kind(w); query.group_size = w->group;
     query.epilogue = epi.mode == kEpiAcc ? VXB_EPI_ACC : epi.mode == kEpiF32 ? VXB_EPI_F32 : VXB_EPI_I8;
     query.requested_route = requested; query.n_peers = epi.n_peers;
-    query.fused_tail = (epi.residual || epi.act) ? 1u : 0u;
+    query.fused_tail = (epi.residual ? 1u : 0u) | (epi.act ? 2u : 0u);
+    query.out_store_aligned = (epi.mode != kEpiI8 && !((uintptr_t)epi.out & 15u) && !(epi.ld & 3u)) ? 1u : 0u;
     query.fp32_input = fp32_input ? 1u : 0u;
     query.sm_count = (uint32_t)ctx->sm_count;
     query.pair_clusters = (uint32_t)(gemm_pair_clusters() > 0 ? gemm_pair_clusters() : 0);
@@ -396,13 +411,18 @@ int run_gemm(VxbContext* ctx, const VxbWeight* w, const int8_t* q, uint32_t rows
             LAUNCH_TRY(launch_decode_tcgen05(a, ctx->sm_count, ctx->stream));
             break;
         }
-        case VXB_VARIANT_TCGEN05: case VXB_VARIANT_TCGEN05_PAIR: {
+        case VXB_VARIANT_TCGEN05: case VXB_VARIANT_TCGEN05_PAIR: case VXB_VARIANT_TCGEN05_WIDE: {
             GemmTcgen05Args a;
             if (!encode_i8_rows(&a.tmap_a, q, rows, w->kpad, 128)) return fail(0, "cuTensorMapEncodeTiled failed for activations");
-            a.rows = rows; a.n = w->d_out; a.kpad = w->kpad; a.epi = epi; a.status = ctx->status;
+            a.rows = rows; a.n = w->d_out; a.kpad = w->kpad; a.epi = epi; a.status = ctx->status; a.trace = ctx->trace; a.tma_out = 0;
             if (plan.variant == VXB_VARIANT_TCGEN05_PAIR) {
                 a.tmap_b = w->tmap_w128;   // each CTA of a pair loads half of the tile's weight rows
                 LAUNCH_TRY(launch_gemm_pair(a, ctx->stream));
+            } else if (plan.variant == VXB_VARIANT_TCGEN05_WIDE) {
+                a.tmap_b = w->tmap_b;
+                if (!encode_out32(&a.tmap_out, epi.out, rows, w->d_out, epi.ld)) return fail(0, "cuTensorMapEncodeTiled failed for the output");
+                a.tma_out = 1;
+                LAUNCH_TRY(launch_gemm_wide(a, ctx->sm_count, ctx->stream));
             } else {
                 a.tmap_b = w->tmap_b;
                 LAUNCH_TRY(launch_gemm_tcgen05(a, ctx->sm_count, ctx->stream));

@@ -324,6 +324,11 @@ struct GemmTcgen05Args {
     uint32_t rows, n, kpad;
     EpilogueParams epi;
     int* status;
+    unsigned long long* trace;   // optional [grid][8] of %globaltimer stamps (single-CTA kernel), or null
+    // 32-bit outputs [rows, ld] as a tensor map with a (32 columns x 32 rows) box, 128B swizzle: the
+    // wide-output kernel's epilogue stores through it (16-byte aligned base and row pitch)
+    CUtensorMap tmap_out;
+    uint32_t tma_out;
 };
 cudaError_t launch_gemm_tcgen05(const GemmTcgen05Args& args, int sm_count, cudaStream_t stream);
 // Fused all-gather: the launch is bound by its NVLink stores rather than by the MMAs when every row sends
@@ -331,6 +336,9 @@ cudaError_t launch_gemm_tcgen05(const GemmTcgen05Args& args, int sm_count, cudaS
 // i.e. when peers * 2140 > K (three GPUs and more at K = 4096; two GPUs stay MMA-bound).
 inline bool gather_is_link_bound(uint32_t n_peers, uint32_t kpad) { return n_peers != 0 && (uint64_t)n_peers * 2140u > kpad; }
 cudaError_t gemm_tcgen05_prepare();  // one-time func attribute set-up
+// K2w: the GEMM for 32-bit outputs (fp32 / raw int32) with sixteen epilogue warps and TMA tile stores through
+// args.tmap_out (args.tma_out must be set)
+cudaError_t launch_gemm_wide(const GemmTcgen05Args& args, int sm_count, cudaStream_t stream);
 // The same GEMM by pairs of CTAs (cta_group::2) on 256 x 256 tiles; tmap_b has a box of 128 rows.
 cudaError_t gemm_pair_prepare();    // func attribute + how many pairs can be resident
 int gemm_pair_clusters();           // 0: pairs cannot run on this device

@@ -76,11 +76,21 @@ struct Smem {
     __device__ float* bias() const { return reinterpret_cast<float*>(base + kOffBias); }
 };
 
+// time stamps for the launch timeline (diagnostic; args.trace is null in ordinary runs)
+__device__ __forceinline__ void stamp(unsigned long long* trace, uint32_t slot) {
+    if (trace) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        trace[(size_t)blockIdx.x * 8 + slot] = t;
+    }
+}
+
 __device__ __forceinline__ void gemm_i8_tcgen05_body(const GemmTcgen05Args& args) {
     extern __shared__ uint8_t smem_raw[];
     Smem sm;
     sm.base = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) stamp(args.trace, 0);
 
     const uint32_t tiles_m = (args.rows + kBM - 1) / kBM;
     const uint32_t tiles_n = (args.n + kBN - 1) / kBN;
@@ -100,6 +110,7 @@ __device__ __forceinline__ void gemm_i8_tcgen05_body(const GemmTcgen05Args& args
         fence_barrier_init();
         prefetch_tmap(&args.tmap_a);
         prefetch_tmap(&args.tmap_b);
+        pdl_release();   // the next launch in the stream may begin its own prologue
     }
     if (warp == 1) {
         tmem_alloc(smem_u32(sm.tmem_ptr()), kTmemCols);
@@ -109,12 +120,14 @@ __device__ __forceinline__ void gemm_i8_tcgen05_body(const GemmTcgen05Args& args
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *sm.tmem_ptr();
+    if (threadIdx.x == 0) stamp(args.trace, 1);
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
             uint32_t stage = 0, phase = 0, armed = 0, armed_parity = 0;
             bool ok = true;
+            pdl_wait();   // the activations come from the launch before this one; the weight producer does not wait
             for (uint32_t t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
                 const int32_t m0 = (int32_t)((t % tiles_m) * kBM);
                 for (uint32_t kb = 0; kb < num_kb; kb++) {
@@ -167,6 +180,7 @@ __device__ __forceinline__ void gemm_i8_tcgen05_body(const GemmTcgen05Args& args
                 for (uint32_t kb = 0; kb < num_kb; kb++) {
                     if (!mbar_try_wait(full_s, phase) && !mbar_wait(full_s, phase, abort_flag)) { ok = false; break; }
                     tc_fence_after();
+                    if (t == blockIdx.x && kb == 0) stamp(args.trace, 2);
                     umma_i8_lo_first(d_tmem, a_lo, a_lo + (kABytes >> 4), idesc, kb);
                     umma_i8_lo(d_tmem, a_lo + 2u, a_lo + (kABytes >> 4) + 2u, idesc);   // +32 bytes of K = +2
                     umma_i8_lo(d_tmem, a_lo + 4u, a_lo + (kABytes >> 4) + 4u, idesc);
@@ -177,6 +191,7 @@ __device__ __forceinline__ void gemm_i8_tcgen05_body(const GemmTcgen05Args& args
                 }
                 if (!ok) break;
                 umma_commit(sm.tmem_full(acc));
+                if (t == blockIdx.x) stamp(args.trace, 3);
                 acc ^= 1u;
                 if (acc == 0) acc_phase ^= 1u;
             }
@@ -206,6 +221,7 @@ __device__ __forceinline__ void gemm_i8_tcgen05_body(const GemmTcgen05Args& args
         const bool sat_s8 = ep.out_lo == -128 && ep.out_hi == 127, sat_u8 = ep.out_lo == 0 && ep.out_hi == 255;
         uint32_t acc = 0, acc_phase = 0;
         bool ok = true;
+        pdl_wait();   // row scales and residual come from earlier launches, and the output may still be read by one
         for (uint32_t t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
             const uint32_t m0 = (t % tiles_m) * kBM, n0 = (t / tiles_m) * kBN + cbase;
             // stage this warp's per-channel vectors for the tile
@@ -224,6 +240,7 @@ __device__ __forceinline__ void gemm_i8_tcgen05_body(const GemmTcgen05Args& args
             ok = __all_sync(0xffffffffu, mbar_wait(sm.tmem_full(acc), acc_phase, abort_flag));
             if (!ok) break;
             tc_fence_after();
+            if (t == blockIdx.x && threadIdx.x == 64) stamp(args.trace, 4);
             if (gather && !first_gather_tile) {
                 // the partner must have finished flushing the previous tile out of the shared staging tile
                 ok = __all_sync(0xffffffffu, mbar_wait(sm.pair_flushed(quarter), pair_phase ^ 1u, abort_flag));
@@ -404,6 +421,7 @@ __device__ __forceinline__ void gemm_i8_tcgen05_body(const GemmTcgen05Args& args
             }
             tc_fence_before();
             mbar_arrive(sm.tmem_empty(acc));
+            if (threadIdx.x == 64) stamp(args.trace, t == blockIdx.x ? 5 : 6);
             acc ^= 1u;
             if (acc == 0) acc_phase ^= 1u;
             if (!ok) break;
@@ -458,6 +476,7 @@ __device__ __forceinline__ void gemm_i8_tcgen05_body(const GemmTcgen05Args& args
     }
     tc_fence_after();
     if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+    if (threadIdx.x == 0) stamp(args.trace, 7);
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -541,9 +560,8 @@ cudaError_t launch_gemm_tcgen05(const GemmTcgen05Args& args, int sm_count, cudaS
     const uint32_t tiles = ((args.rows + kBM - 1) / kBM) * ((args.n + kBN - 1) / kBN);
     const uint32_t grid = tiles < (uint32_t)sm_count ? tiles : (uint32_t)sm_count;
     if (gather_is_link_bound(args.epi.n_peers, args.kpad) && tunables().overlap_gather)
-        gemm_i8_tcgen05_gather_kernel<<<grid, kThreads, kSmemBytes, stream>>>(args);
-    else gemm_i8_tcgen05_kernel<<<grid, kThreads, kSmemBytes, stream>>>(args);
-    return cudaGetLastError();
+        return launch_pdl(gemm_i8_tcgen05_gather_kernel, dim3(grid), dim3(kThreads), kSmemBytes, stream, args);
+    return launch_pdl(gemm_i8_tcgen05_kernel, dim3(grid), dim3(kThreads), kSmemBytes, stream, args);
 }
 
 cudaError_t launch_i8_peak_probe(uint32_t iters, long long* cycles, int* status, int sm_count,

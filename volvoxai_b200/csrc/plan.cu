@@ -43,6 +43,10 @@ bool admitted(const VxbVariant& v, const VxbPlanQuery& q, char* why, uint32_t by
     if (v.group_size && v.group_size != q.group_size) { refuse(why, bytes, "%s needs group size %u", v.id, v.group_size); return false; }
     if (q.n_peers && !(v.flags & VXB_VF_PEERS)) { refuse(why, bytes, "%s has no peer stores", v.id); return false; }
     if (q.fused_tail && !(v.flags & VXB_VF_FUSED_TAIL)) { refuse(why, bytes, "%s has no fused epilogue tail", v.id); return false; }
+    if (v.flags & VXB_VF_TILE_STORE) {
+        if (!q.out_store_aligned) { refuse(why, bytes, "%s needs a 16-byte aligned output base and row pitch", v.id); return false; }
+        if (q.fused_tail & 2u) { refuse(why, bytes, "%s has no SiLU*Mul tail", v.id); return false; }
+    }
     if (v.cluster > 1 && q.pair_clusters == 0) { refuse(why, bytes, "no co-resident CTA pairs on this device"); return false; }
     if (v.flags & VXB_VF_FUSED_K1) {
         if (!q.fp32_input) { refuse(why, bytes, "%s starts from fp32 rows", v.id); return false; }
@@ -94,7 +98,7 @@ bool geometry(VxbVariantId id, const VxbPlanQuery& q, VxbLaunchPlan* p) {
         case VXB_VARIANT_DP4A_GROUPED:
             p->grid = ceil_div(q.n, 128) * (q.rows == 1 ? 1 : ceil_div(q.rows, 4));
             return true;
-        case VXB_VARIANT_TCGEN05: case VXB_VARIANT_GROUPED_TCGEN05: {
+        case VXB_VARIANT_TCGEN05: case VXB_VARIANT_TCGEN05_WIDE: case VXB_VARIANT_GROUPED_TCGEN05: {
             const uint32_t tiles = ceil_div(q.rows, v.tile_rows) * ceil_div(q.n, v.tile_columns);
             p->grid = tiles < sms ? tiles : sms;
             return true;
@@ -191,6 +195,10 @@ int vxb_plan(const VxbPlanQuery* query, VxbLaunchPlan* out, char* why, uint32_t 
             // pairs of CTAs on 256 x 256 tiles once there are at least two waves of 128 x 256 tiles
             const uint32_t tiles = ceil_div(q.rows, 128) * ceil_div(q.n, 256);
             chosen = (q.pair_clusters > 0 && tiles >= 2u * sms) ? VXB_VARIANT_TCGEN05_PAIR : VXB_VARIANT_TCGEN05;
+            // 32-bit outputs at short K are bound by the output, not by the tensor pipe
+            char unused[8];
+            if (q.epilogue != VXB_EPI_I8 && round_up(q.k, kKAlign) <= VXB_WIDE_MAX_KPAD &&
+                admitted(kVariants[VXB_VARIANT_TCGEN05_WIDE], q, unused, sizeof unused)) chosen = VXB_VARIANT_TCGEN05_WIDE;
         }
         if (!admitted(kVariants[chosen], q, why, why_bytes)) return 0;
     }

@@ -19,13 +19,13 @@ import ctypes as C
 import numpy as np
 
 from . import _lib
-from ._lib import (DT_I8, DT_U8, OP_PACKED_LINEAR, ROUTE_AUTO, ROUTE_DECODE, ROUTE_DECODE_FUSED, ROUTE_DECODE_STREAMK, ROUTE_TCGEN05_PAIR,
+from ._lib import (DT_I8, DT_U8, OP_PACKED_LINEAR, ROUTE_AUTO, ROUTE_DECODE, ROUTE_DECODE_FUSED, ROUTE_DECODE_STREAMK, ROUTE_TCGEN05_PAIR, ROUTE_TCGEN05_WIDE,
                    ROUTE_GEMV, ROUTE_SIMT,
                    ROUTE_TCGEN05, LLMOpArgs, last_error, last_route)
 
 __all__ = ["Context", "Weight", "W8A8Error", "variants", "plan", "registry_rows", "qlinear_i8u8", "packed_linear",
            "packed_linear_decode", "host_cache_clear", "host_residency", "host_download", "host_invalidate", "launch_count", "last_error",
-           "quantize_typed_f32_i8u8", "dequantize_typed_i8u8_f32", "requantize_linear_i8u8", "last_route", "ROUTE_AUTO", "ROUTE_GEMV", "ROUTE_TCGEN05", "ROUTE_SIMT", "ROUTE_DECODE", "ROUTE_DECODE_STREAMK", "ROUTE_TCGEN05_PAIR", "ROUTE_DECODE_FUSED",
+           "quantize_typed_f32_i8u8", "dequantize_typed_i8u8_f32", "requantize_linear_i8u8", "last_route", "ROUTE_AUTO", "ROUTE_GEMV", "ROUTE_TCGEN05", "ROUTE_SIMT", "ROUTE_DECODE", "ROUTE_DECODE_STREAMK", "ROUTE_TCGEN05_PAIR", "ROUTE_DECODE_FUSED", "ROUTE_TCGEN05_WIDE",
            "DT_I8", "DT_U8"]
 
 
@@ -68,13 +68,14 @@ def variants() -> list[dict]:
 
 
 def plan(rows: int, k: int, n: int, *, weight_kind: int = _lib.WEIGHT_PER_CHANNEL, group_size: int = 0,
-         epilogue: int = _lib.EPI_F32, route: int = ROUTE_AUTO, n_peers: int = 0, fused_tail: bool = False,
-         fp32_input: bool = True, sm_count: int = 148, pair_clusters: int = 74):
+         epilogue: int = _lib.EPI_F32, route: int = ROUTE_AUTO, n_peers: int = 0, fused_tail=False,
+         fp32_input: bool = True, sm_count: int = 148, pair_clusters: int = 74, out_store_aligned: bool = True):
     """vxb_plan(): the launch plan of one call (a dict with the variant's id added) or
     (None, reason) when it is refused.  Needs no GPU."""
     L = _lib.load()
-    q = _lib.PlanQuery(rows, k, n, weight_kind, group_size, epilogue, route, n_peers, 1 if fused_tail else 0,
-                       1 if fp32_input else 0, sm_count, pair_clusters)
+    # fused_tail: False / True (residual Add) or the bit mask itself (1 residual Add, 2 SiLU*Mul)
+    q = _lib.PlanQuery(rows, k, n, weight_kind, group_size, epilogue, route, n_peers, int(fused_tail),
+                       1 if fp32_input else 0, sm_count, pair_clusters, 1 if out_store_aligned else 0)
     out = _lib.LaunchPlan()
     why = C.create_string_buffer(200)
     if L.vxb_plan(C.byref(q), C.byref(out), why, len(why)) != 1:
