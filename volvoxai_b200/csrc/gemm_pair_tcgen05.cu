@@ -174,6 +174,7 @@ __device__ __forceinline__ void gemm_i8_pair_body(const GemmTcgen05Args& args) {
         fence_barrier_init();
         prefetch_tmap(&args.tmap_a);
         prefetch_tmap(&args.tmap_b);
+        pdl_release();   // the next launch in the stream may begin its own prologue
     }
     if (warp == 1) {
         tmem_alloc_pair(smem_u32(sm.tmem_ptr()), kTmemCols);
@@ -190,6 +191,7 @@ __device__ __forceinline__ void gemm_i8_pair_body(const GemmTcgen05Args& args) {
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
+            pdl_wait();   // the activations come from the launch before this one; the weight producer does not wait
             for (uint32_t t = pair; ok && t < total_tiles; t += pairs) {
                 const int32_t m0 = (int32_t)((t % tiles_m) * 2 * kBM + rank * kBM);
                 for (uint32_t kb = 0; kb < num_kb; kb++) {
@@ -274,6 +276,7 @@ __device__ __forceinline__ void gemm_i8_pair_body(const GemmTcgen05Args& args) {
         const bool sat_s8 = ep.out_lo == -128 && ep.out_hi == 127, sat_u8 = ep.out_lo == 0 && ep.out_hi == 255;
         uint32_t acc = 0, acc_phase = 0;
         bool ok = true;
+        pdl_wait();   // row scales and residual come from earlier launches, and one may still read the output
         for (uint32_t t = pair; ok && t < total_tiles; t += pairs) {
             const uint32_t m0 = (t % tiles_m) * 2 * kBM + rank * kBM, n0 = (t / tiles_m) * kBN + cbase;
             __syncwarp();
@@ -514,10 +517,12 @@ cudaError_t launch_gemm_pair(const GemmTcgen05Args& args, cudaStream_t stream) {
     const uint32_t pairs = tiles < (uint32_t)g_pair_clusters ? tiles : (uint32_t)g_pair_clusters;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * pairs); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = kSmemBytes; cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr; cfg.numAttrs = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // set-up and weight loads under the predecessor's tail
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 2;
     return cudaLaunchKernelEx(&cfg, gemm_i8_pair_kernel, args);
 }
 
