@@ -478,6 +478,55 @@ def gemm_sweep(torch, ctx, w8a8, peaks, i8_probe, steps=5):
     return out
 
 
+def sharded_wide_shapes(torch, dist, ctx, w8a8, sharded, world, rank, timed, steps=10):
+    """The two widest configured layers at M 8192, N-sharded over `world` GPUs: the step with the int8
+    output replicated by the fused peer-store all-gather and the step with outputs left sharded (what
+    a row-parallel consumer takes).  All ranks call this; the activations are rank 0's, broadcast."""
+    out = []
+    for (m, k, n) in ((8192, 8192, 28672), (8192, 4096, 128256)):
+        lo, hi = sharded.shard_bounds(n, world, rank)
+        n_local = hi - lo
+        w_local, ws_local = wl.gemm_weights(n_local, k, seed=2000 + rank)
+        weight = w8a8.Weight.from_i8(ctx, w_local, ws_local)
+        x = torch.empty((m, k), dtype=torch.float32, device="cuda")
+        if rank == 0:
+            x.copy_(torch.from_numpy(wl.gemm_activations(m, k, seed=3)))
+        dist.broadcast(x, 0)
+        scale_t = torch.zeros(1, dtype=torch.float32, device="cuda")
+        if rank == 0:
+            smp = ctx.linear_f32(weight, x[:16])
+            ctx.synchronize()
+            scale_t[0] = float(wl.static_out_scale(smp.cpu().numpy()))
+        dist.broadcast(scale_t, 0)
+        out_scale = float(scale_t.item())
+        lin = sharded.NShardedLinear(
+            n, world, rank, lambda xx, o, w=weight, s=out_scale: ctx.linear_i8(w, xx, s, 0, out=o), torch.int8, "cuda")
+        fused = sharded.FusedGatherLinear(ctx, weight, n, world, rank, rows=m)
+        for _ in range(3):
+            fused.forward(x, out_scale)
+            lin.forward_sharded(x)
+        fused_ms = timed(lambda: fused.forward(x, out_scale), steps) / steps
+        shard_ms = timed(lambda: lin.forward_sharded(x), steps) / steps
+        # the replicated result equals every rank's own slab where they overlap
+        y_rep = fused.forward(x, out_scale)
+        own_ok = bool(torch.equal(y_rep[:, lo:hi], lin.forward_sharded(x)))
+        flags = [None] * world
+        dist.all_gather_object(flags, own_ok)
+        ops = 2.0 * m * k * n
+        recv = m * (n - n_local)
+        out.append({"rows": m, "k": k, "n": n, "n_gpus": world,
+                    "fused_ms": fused_ms, "fused_tops": ops / (fused_ms * 1e-3) / 1e12,
+                    "sharded_ms": shard_ms, "sharded_tops": ops / (shard_ms * 1e-3) / 1e12,
+                    "nvlink_recv_bytes_per_gpu": int(recv), "nvlink_floor_ms": recv / 770e9 * 1e3,
+                    "mma_floor_ms": ops / world / (2.0 * measured_peaks()["bf16_tflops"] * 1e12) * 1e3,
+                    "replicated_equals_own_slab_on_every_rank": all(flags)})
+        fused.close()
+        weight.close()
+        del x, lin, y_rep
+        torch.cuda.empty_cache()
+    return out
+
+
 def sustained_run(torch, step, ops, device_index, seconds=2.5):
     """Back-to-back steps for `seconds` with the clock sampler at 5 ms: the sustained rate under the power
     cap next to the burst figure of the short timed loop (median SM clock, TOPS, and TOPS scaled to the
@@ -666,7 +715,7 @@ def gpu_arm(args):
         "i8_probe_tops": i8_probe, "frac_of_i8_probe": achieved / i8_probe,
         "frac_of_nominal_4500": achieved / NOMINAL_I8_TOPS,
         "quantize_kernel_ms": quant_ms,
-        "quantize_note": "whole-batch quantizer timed alone (allocation of its outputs included); inside a step all but the first row chunk of it runs under the GEMM",
+        "quantize_note": "whole-batch quantizer timed alone (allocation of its outputs included); inside a step it runs in front of the GEMM",
         "quantize_gbs": (5.0 * m * k + 4.0 * m) / (quant_ms * 1e-3) / 1e9 if quant_ms > 0 else None,
         "quantize_frac_of_hbm": ((5.0 * m * k + 4.0 * m) / (quant_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]
                                  if quant_ms > 0 else None),
@@ -753,6 +802,11 @@ def gpu_arm(args):
                           "gemv_sweep": gemv_sweep(torch, ctx, w8a8, peaks),
                           "model_linear_stacks": model_linear_stacks(torch, ctx, w8a8, peaks),
                           "widened_rows": widened_rows(torch, ctx, w8a8, peaks)}
+
+    if world > 1 and not args.no_extras:
+        wide = sharded_wide_shapes(torch, dist, ctx, w8a8, sharded, world, rank, timed)
+        if rank == 0:
+            line["extras"] = {"sharded_wide_shapes": wide}
 
     weight.close()
     ctx.close()

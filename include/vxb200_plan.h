@@ -45,7 +45,7 @@ extern "C" {
 #define VXB_VF_FUSED_TAIL 4u  /* carries the residual-Add / SiLU*Mul tails of the fp32 epilogue */
 #define VXB_VF_VERIFY 8u      /* verification kernel: explicit request only */
 #define VXB_VF_FUSED_K1 16u   /* quantizes the fp32 rows itself: one launch per linear, fp32 input only */
-#define VXB_VF_TILE_STORE 32u /* 32-bit outputs leave as TMA tile stores: 16-byte aligned output base and row pitch, \
+#define VXB_VF_TILE_STORE 32u /* 32-bit outputs leave as TMA tile stores: output base, row pitch and width multiples of 16 bytes, \
                                  residual Add as the only fused tail */
 
 /*
@@ -99,7 +99,7 @@ typedef struct VxbPlanQuery {
     uint32_t fp32_input;     /* the call starts from fp32 activations (a K1 quantizer is part of it) */
     uint32_t sm_count;       /* SMs of the device (148 on a B200) */
     uint32_t pair_clusters;  /* co-resident clusters of two the device grants the pair kernel (0: none) */
-    uint32_t out_store_aligned; /* the output base and row pitch are multiples of 16 bytes (TMA tile stores possible) */
+    uint32_t out_store_aligned; /* the output's base, row pitch and width are multiples of 16 bytes (TMA tile stores possible) */
 } VxbPlanQuery;
 
 /* Per-row quantizer (K1) chosen for calls that start from fp32 activations. */

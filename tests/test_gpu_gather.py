@@ -31,26 +31,34 @@ def _case(oracle, rows, k, n, seed):
     return case, os_, want
 
 
-@pytest.mark.parametrize("rows,k,n,ld", [(300, 256, 200, 208), (129, 384, 257, 259)])
-def test_extra_destinations_receive_every_tile(torch, oracle, rows, k, n, ld):
-    """Three destinations on one GPU: the local buffer and two more. Row pitch 208 takes the
-    vector stores, 259 the unaligned scalar tail; columns beyond n stay untouched."""
+@pytest.mark.parametrize("rows,k,n,ld", [(300, 256, 200, 208), (129, 384, 257, 259), (1000, 512, 1296, 1312),
+                                         (2304, 640, 656, 656), (300, 256, 208, 224)])
+@pytest.mark.parametrize("tile_stores", [1, 0])
+def test_extra_destinations_receive_every_tile(torch, oracle, rows, k, n, ld, tile_stores):
+    """Three destinations on one GPU: the local buffer and two more, through both forms of the flush: TMA
+    tile stores clipped by the destination's tensor map (row pitch and channel count multiples of 16) and
+    per-lane stores (200 channels, or row pitch 259 with its unaligned scalar tail, take them whatever is
+    asked for); columns beyond n and the rows below the batch stay untouched."""
     from volvoxai_b200 import _lib, w8a8
     L = _lib.load()
     ctx = w8a8.Context(0)
     case, os_, want = _case(oracle, rows, k, n, seed=11)
     weight = w8a8.Weight.from_i8(ctx, case["w"], case["ws"])
     x = torch.from_numpy(case["x"]).cuda()
-    bufs = [torch.full((rows, ld), 77, dtype=torch.int8, device="cuda") for _ in range(3)]
+    bufs = [torch.full((rows + 3, ld), 77, dtype=torch.int8, device="cuda") for _ in range(3)]
     peers = (C.c_void_p * 2)(bufs[1].data_ptr(), bufs[2].data_ptr())
-    rc = L.vxb_linear_i8_gather(ctx.handle, weight.handle, C.c_void_p(x.data_ptr()), rows, os_, 0,
-                                C.c_void_p(bufs[0].data_ptr()), ld, peers, 2)
-    assert rc == 1, _lib.last_error()
-    ctx.synchronize()
+    assert w8a8.tune("gemm.gather_tma", tile_stores) == 1
+    try:
+        rc = L.vxb_linear_i8_gather(ctx.handle, weight.handle, C.c_void_p(x.data_ptr()), rows, os_, 0,
+                                    C.c_void_p(bufs[0].data_ptr()), ld, peers, 2)
+        assert rc == 1, _lib.last_error()
+        ctx.synchronize()
+    finally:
+        w8a8.tune("gemm.gather_tma", 1)
     for b in bufs:
         got = b.cpu().numpy()
-        assert np.array_equal(got[:, :n], want)
-        assert (got[:, n:] == 77).all()
+        assert np.array_equal(got[:rows, :n], want)
+        assert (got[:rows, n:] == 77).all() and (got[rows:] == 77).all()
     # more than seven peers is declined before any launch
     many = (C.c_void_p * 8)(*[bufs[1].data_ptr()] * 8)
     assert L.vxb_linear_i8_gather(ctx.handle, weight.handle, C.c_void_p(x.data_ptr()), rows, os_, 0,

@@ -729,6 +729,14 @@ def test_wide_output_kernel(torch, ctx, oracle, rows, k, n):
     got = wide.cpu().numpy()
     assert np.array_equal(got[:, 4:4 + n].view(np.uint32), y.view(np.uint32))
     assert (got[:, :4] == -7.0).all() and (got[:, 4 + n:] == -7.0).all()
+    # a width that is not a multiple of four columns is not this kernel's: tile stores clip in 16-byte units
+    narrow = w8a8.Weight.from_i8(ctx, c["w"][:n - 1], c["ws"][:n - 1], bias_f32=c["bias"][:n - 1])
+    padded = torch.full((rows, n), -7.0, device="cuda")
+    ctx.linear_f32(narrow, xd, out=padded[:, :n - 1])
+    assert "wide" not in w8a8.last_route()
+    got = padded.cpu().numpy()
+    assert np.array_equal(got[:, :n - 1].view(np.uint32), y[:, :n - 1].view(np.uint32)) and (got[:, n - 1] == -7.0).all()
+    narrow.close()
     res = np.random.default_rng(rows).standard_normal((rows, n)).astype(np.float32)
     fused = ctx.linear_f32_fused(weight, xd, residual=dev(torch, res)).cpu().numpy()
     assert np.array_equal(fused.view(np.uint32), (y + res).view(np.uint32))

@@ -93,6 +93,20 @@ bool encode_out32(CUtensorMap* map, const void* base, uint32_t rows, uint32_t n,
               CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// int8 matrix [rows, n] with row pitch ld bytes -> 2-D tensor map with a (128 columns x 32 rows) box, 128B
+// swizzle: the destination of the fused all-gather's TMA tile stores
+bool encode_gather_i8(CUtensorMap* map, const void* base, uint32_t rows, uint32_t n, uint32_t ld) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn || ((uintptr_t)base & 15u) || (ld & 15u)) return false;
+    cuuint64_t dims[2] = {n, rows};
+    cuuint64_t strides[1] = {ld};
+    cuuint32_t box[2] = {128, 32};
+    cuuint32_t elem[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+              CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 bool encode_i8_kblocks(CUtensorMap* map, const void* base, uint32_t rows, uint32_t kpad, uint32_t box_rows,
                        uint32_t box_blocks) {
     EncodeTiledFn fn = encode_fn();
@@ -292,7 +306,8 @@ VxbPlanQuery plan_query(const VxbContext* ctx, const VxbWeight* w, uint32_t rows
     query.epilogue = epi.mode == kEpiAcc ? VXB_EPI_ACC : epi.mode == kEpiF32 ? VXB_EPI_F32 : VXB_EPI_I8;
     query.requested_route = requested; query.n_peers = epi.n_peers;
     query.fused_tail = (epi.residual ? 1u : 0u) | (epi.act ? 2u : 0u);
-    query.out_store_aligned = (epi.mode != kEpiI8 && !((uintptr_t)epi.out & 15u) && !(epi.ld & 3u)) ? 1u : 0u;
+    // TMA tile stores clip at the matrix edge in units of 16 bytes: the width must be a multiple of four 32-bit columns too
+    query.out_store_aligned = (epi.mode != kEpiI8 && !((uintptr_t)epi.out & 15u) && !(epi.ld & 3u) && !(w->d_out & 3u)) ? 1u : 0u;
     query.fp32_input = fp32_input ? 1u : 0u;
     query.sm_count = (uint32_t)ctx->sm_count;
     query.pair_clusters = (uint32_t)(gemm_pair_clusters() > 0 ? gemm_pair_clusters() : 0);
@@ -425,6 +440,14 @@ int run_gemm(VxbContext* ctx, const VxbWeight* w, const int8_t* q, uint32_t rows
                 LAUNCH_TRY(launch_gemm_wide(a, ctx->sm_count, ctx->stream));
             } else {
                 a.tmap_b = w->tmap_b;
+                a.gather_tma = 0;
+                // (a tile store clips at the shard's edge in units of 16 bytes: whole 16-channel groups only)
+                if (epi.n_peers && epi.mode == kEpiI8 && tunables().gather_tma && !(w->d_out & 15u)) {
+                    bool ok = encode_gather_i8(&a.tmap_gather[0], epi.out, rows, w->d_out, epi.ld);
+                    for (uint32_t p = 0; ok && p < epi.n_peers; p++)
+                        ok = encode_gather_i8(&a.tmap_gather[p + 1], epi.peer_out[p], rows, w->d_out, epi.ld);
+                    a.gather_tma = ok ? 1u : 0u;   // otherwise the per-lane stores serve (unaligned buffers)
+                }
                 LAUNCH_TRY(launch_gemm_tcgen05(a, ctx->sm_count, ctx->stream));
             }
             break;
@@ -1160,6 +1183,7 @@ int vxb_tune(const char* name, int64_t value) {
     if (!strcmp(name, "decode.fused_max_rows")) { t.decode_fused_max_rows = (uint32_t)value; return 1; }
     if (!strcmp(name, "gemm.overlap_k1")) { t.overlap_k1 = value != 0; return 1; }
     if (!strcmp(name, "gemm.overlap_gather")) { t.overlap_gather = value != 0; return 1; }
+    if (!strcmp(name, "gemm.gather_tma")) { t.gather_tma = value != 0; return 1; }
     if (!strcmp(name, "gemm.overlap_ratio")) { t.overlap_ratio = (uint32_t)value; return 1; }
     return 0;
 }

@@ -329,6 +329,11 @@ struct GemmTcgen05Args {
     // wide-output kernel's epilogue stores through it (16-byte aligned base and row pitch)
     CUtensorMap tmap_out;
     uint32_t tma_out;
+    // fused all-gather through TMA tile stores: this rank's channel range of its own output buffer
+    // (index 0) and of every peer's buffer, int8 [rows, n] with the buffers' row pitch, box 128 columns x
+    // 32 rows, 128B swizzle; used when gather_tma != 0 (16-byte aligned bases and pitch)
+    CUtensorMap tmap_gather[8];
+    uint32_t gather_tma;
 };
 cudaError_t launch_gemm_tcgen05(const GemmTcgen05Args& args, int sm_count, cudaStream_t stream);
 // Fused all-gather: the launch is bound by its NVLink stores rather than by the MMAs when every row sends
@@ -425,6 +430,7 @@ struct Tunables {
     bool overlap_gather;                // the same for a link-bound fused all-gather launch, with its 128-register build (off: measured slower)
     uint32_t overlap_ratio;             // rows_first / rows_rest >= overlap_ratio / d_out when a batch is cut in two
     uint32_t decode_fused_max_rows;     // fp32 rows up to which the automatic route takes the decode kernel's single-launch form
+    bool gather_tma;                    // fused all-gather: TMA tile stores to the peers instead of per-lane stores
 };
 Tunables& tunables();
 

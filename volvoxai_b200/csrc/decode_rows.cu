@@ -748,7 +748,7 @@ cudaError_t launch_t(const DecodeRowsArgs& args, cudaStream_t stream) {
 }  // namespace
 
 Tunables& tunables() {
-    static Tunables t{kPairShareBytes, false, false, false, 1755u, 2u};
+    static Tunables t{kPairShareBytes, false, false, false, 1755u, 2u, true};
     return t;
 }
 

@@ -71,6 +71,8 @@ VXB_API void vxb_inject_failure(int kind, uint32_t countdown);
  *                               later rows runs under the GEMM of the first ones (default 0: measured slower)
  *   "gemm.overlap_gather"       1: the same split for a link-bound fused all-gather launch, with the 128-register
  *                               build of its kernel (default 0: measured slower)
+ *   "gemm.gather_tma"           1 (default): the fused all-gather's flush is one TMA tile store per destination and
+ *                               warp; 0: per-lane 16-byte stores of 256-byte row segments
  * Returns 1, or 0 for an unknown name. */
 VXB_API int vxb_tune(const char* name, int64_t value);
 

@@ -100,6 +100,8 @@ __device__ __forceinline__ void gemm_i8_tcgen05_body(const GemmTcgen05Args& args
     // with peer destinations the last pipeline stage becomes the epilogue warps' staging area
     // for coalesced stores (the exchange, not the MMA pipeline, bounds that launch)
     const bool gather = args.epi.n_peers != 0;
+    // the flush of the fused all-gather as TMA tile stores (one per destination and warp) instead of lane stores
+    const bool gather_tma = gather && args.gather_tma != 0;
     const uint32_t nstages = gather ? kStages - 1 : kStages;
 
     if (threadIdx.x == 0) {
@@ -213,7 +215,9 @@ __device__ __forceinline__ void gemm_i8_tcgen05_body(const GemmTcgen05Args& args
         // stage into ONE [32 rows x 256 B] tile, so that the flush can store whole 256-byte row
         // segments - NVLink moves long contiguous runs far better than 128-byte ones; the pair meets on
         // two mbarriers (bounded waits, like every wait here) instead of a bar.sync
-        uint8_t* stage_tile = sm.base + kOffStages + (kStages - 1) * kStageBytes + quarter * (32u * 2u * kEpiCols);
+        // TMA form: every warp has a [32 rows x 128 B] tile of its own (128B-swizzled), no partner
+        uint8_t* stage_tile = sm.base + kOffStages + (kStages - 1) * kStageBytes +
+                              (gather_tma ? (warp - 2u) * (32u * kEpiCols) : quarter * (32u * 2u * kEpiCols));
         uint32_t pair_phase = 0;
         bool first_gather_tile = true;
         const float zero_f = __int2float_rn(ep.out_zero);
@@ -241,7 +245,10 @@ __device__ __forceinline__ void gemm_i8_tcgen05_body(const GemmTcgen05Args& args
             if (!ok) break;
             tc_fence_after();
             if (t == blockIdx.x && threadIdx.x == 64) stamp(args.trace, 4);
-            if (gather && !first_gather_tile) {
+            if (gather_tma) {
+                if (lane == 0) tma_store_wait_read();   // the previous tile's stores have left the staging tile
+                __syncwarp();
+            } else if (gather && !first_gather_tile) {
                 // the partner must have finished flushing the previous tile out of the shared staging tile
                 ok = __all_sync(0xffffffffu, mbar_wait(sm.pair_flushed(quarter), pair_phase ^ 1u, abort_flag));
                 if (!ok) break;
@@ -328,7 +335,8 @@ __device__ __forceinline__ void gemm_i8_tcgen05_body(const GemmTcgen05Args& args
                         // this warp's half of row `lane` of the pair's [32 rows x 256 B] staging tile; 16-byte
                         // pieces XOR-swizzled by row within the half so that both the row-wise writes here and
                         // the piece-wise reads of the flush are free of bank conflicts
-                        uint8_t* st = stage_tile + lane * (2u * kEpiCols) + half * kEpiCols;
+                        uint8_t* st = gather_tma ? stage_tile + lane * kEpiCols
+                                                 : stage_tile + lane * (2u * kEpiCols) + half * kEpiCols;
                         const uint32_t p0 = c >> 4;
                         *reinterpret_cast<uint4*>(st + (((p0) ^ (lane & 7u)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
                         *reinterpret_cast<uint4*>(st + (((p0 + 1u) ^ (lane & 7u)) << 4)) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
@@ -425,7 +433,19 @@ __device__ __forceinline__ void gemm_i8_tcgen05_body(const GemmTcgen05Args& args
             acc ^= 1u;
             if (acc == 0) acc_phase ^= 1u;
             if (!ok) break;
-            if (gather) {
+            if (gather_tma) {
+                // this warp's 32 rows x 128 columns leave as one TMA tile store per destination: this GPU's
+                // buffer (0) and every peer's, each map covering this rank's channel range of that buffer, so
+                // the tensor map clips the shard's ragged last tile and the rows beyond the batch.  Plain
+                // tile stores over NVLink: no multicast, nothing is loaded from a peer.
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0 && n0 < args.n) {
+                    for (uint32_t d = 0; d <= ep.n_peers; d++)
+                        tma_store_2d(&args.tmap_gather[d], smem_u32(stage_tile), (int32_t)n0, (int32_t)(m0 + quarter * 32u));
+                    tma_store_commit();
+                }
+            } else if (gather) {
                 // both halves staged -> this warp flushes 16 of the 32 rows: 16 lanes cover the 256 bytes of
                 // one row, 2 rows per pass, the same 16 bytes going to this GPU's buffer (destination 0) and
                 // to the same rows and columns of every peer's buffer - plain stores over NVLink, so the
@@ -462,6 +482,7 @@ __device__ __forceinline__ void gemm_i8_tcgen05_body(const GemmTcgen05Args& args
                 first_gather_tile = false;
             }
         }
+        if (gather_tma && lane == 0) tma_store_wait_all();   // the stores are complete before the kernel ends
     }
 
     // ---------------- teardown ----------------
