@@ -41,7 +41,8 @@ extern "C" {
 #define VXB_WEIGHT_W4_WORDS 4u    /* grouped, and the 4-bit words are kept for the nibble-streaming kernel */
 /* Variant flags. */
 #define VXB_VF_AUTO 1u        /* eligible for automatic selection */
-#define VXB_VF_PEERS 2u       /* epilogue can store to peer GPUs (fused all-gather) */
+#define VXB_VF_PEERS 2u       /* epilogue can store to peer GPUs (fused all-gather); clustered variants only as TMA \
+                                 tile stores, i.e. into buffers whose base, row pitch and width are multiples of 16 bytes */
 #define VXB_VF_FUSED_TAIL 4u  /* carries the residual-Add / SiLU*Mul tails of the fp32 epilogue */
 #define VXB_VF_VERIFY 8u      /* verification kernel: explicit request only */
 #define VXB_VF_FUSED_K1 16u   /* quantizes the fp32 rows itself: one launch per linear, fp32 input only */
@@ -63,7 +64,7 @@ extern "C" {
     X(GEMV_DP4A,        1, "gemv-dp4a",                 "gemv_dp4a_kernel",               0,   0,   0, 256, 1,  65536,   1,  32, 7u, 1u, 0, 0u,           200) \
     X(SIMT_DP4A,        3, "simt-dp4a",                 "gemm_simt_kernel",               4, 128,   0, 128, 1,      0,   1,   0, 7u, 1u, 0, 8u,             1) \
     X(TCGEN05,          2, "tcgen05-i8",                "gemm_i8_tcgen05_kernel",       128, 256, 128, 352, 1, 223000,   1,   0, 7u, 1u, 0, 1u | 2u | 4u,  600) \
-    X(TCGEN05_PAIR,     6, "tcgen05-pair-i8",           "gemm_i8_pair_kernel",          256, 256, 256, 352, 2, 223000,   1,   0, 7u, 1u, 0, 1u | 4u,       650) \
+    X(TCGEN05_PAIR,     6, "tcgen05-pair-i8",           "gemm_i8_pair_kernel",          256, 256, 256, 352, 2, 223000,   1,   0, 7u, 1u, 0, 1u | 2u | 4u,  650) \
     X(TCGEN05_WIDE,     8, "tcgen05-wide-i8",           "gemm_i8_wide_kernel",          128, 256, 128, 608, 1, 231000,   1,   0, 3u, 1u, 0, 1u | 4u | 32u, 640) \
     X(GROUPED_TCGEN05,  0, "tcgen05-grouped-i8",        "gemm_i8_grouped_tcgen05_kernel", 128, 128, 128, 320, 1, 223000,   1,   0, 2u, 6u, 0, 1u,           500) \
     X(GEMV_GROUPED,     0, "gemv-grouped",              "gemv_grouped_kernel",            0,   0,   0, 256, 1,  65536,   1,   4, 2u, 6u, 0, 1u,           550) \
@@ -99,7 +100,8 @@ typedef struct VxbPlanQuery {
     uint32_t fp32_input;     /* the call starts from fp32 activations (a K1 quantizer is part of it) */
     uint32_t sm_count;       /* SMs of the device (148 on a B200) */
     uint32_t pair_clusters;  /* co-resident clusters of two the device grants the pair kernel (0: none) */
-    uint32_t out_store_aligned; /* the output's base, row pitch and width are multiples of 16 bytes (TMA tile stores possible) */
+    uint32_t out_store_aligned; /* the output's (and every peer buffer's) base, row pitch and width are multiples of 16 bytes \
+                                   (TMA tile stores possible) */
 } VxbPlanQuery;
 
 /* Per-row quantizer (K1) chosen for calls that start from fp32 activations. */

@@ -67,6 +67,45 @@ def test_extra_destinations_receive_every_tile(torch, oracle, rows, k, n, ld, ti
     ctx.close()
 
 
+def test_mma_bound_gather_runs_on_pairs_of_ctas(torch, oracle):
+    """One peer and a padded K above 2140: the launch is MMA-bound, so the plan gives the fused all-gather to
+    the paired kernel (64-column TMA tile stores).  Its output equals the single-CTA kernel's per-lane-store
+    form byte for byte on both destinations, and the oracle on sampled rows."""
+    from volvoxai_b200 import _lib, w8a8
+    L = _lib.load()
+    ctx = w8a8.Context(0)
+    rows, k, n, ld = 2310, 2176, 4368, 4384        # 19 x 18 = 342 tiles of 128 x 256: above two waves
+    x_np = wl.gemm_activations(rows, k, seed=5)
+    w_np, ws_np = wl.gemm_weights(n, k, seed=6)
+    weight = w8a8.Weight.from_i8(ctx, w_np, ws_np)
+    x = torch.from_numpy(x_np).cuda()
+    sample = np.r_[0:40, rows - 40:rows]
+    ref = oracle.w8a8_linear(x_np[sample], w_np, ws_np)
+    os_ = float(wl.static_out_scale(ref["out"]))
+    want = oracle.requant_rows(ref["acc"], ref["row_scales"], ref["valid"], ws_np, None, os_, 0)
+    results = {}
+    for tile_stores in (1, 0):
+        bufs = [torch.full((rows + 2, ld), 77, dtype=torch.int8, device="cuda") for _ in range(2)]
+        peers = (C.c_void_p * 1)(bufs[1].data_ptr())
+        assert w8a8.tune("gemm.gather_tma", tile_stores) == 1
+        try:
+            rc = L.vxb_linear_i8_gather(ctx.handle, weight.handle, C.c_void_p(x.data_ptr()), rows, os_, 0,
+                                        C.c_void_p(bufs[0].data_ptr()), ld, peers, 1)
+            assert rc == 1, _lib.last_error()
+            ctx.synchronize()
+        finally:
+            w8a8.tune("gemm.gather_tma", 1)
+        assert ("tcgen05-pair-i8" in w8a8.last_route()) == bool(tile_stores), w8a8.last_route()
+        results[tile_stores] = [b.cpu().numpy() for b in bufs]
+    for got in results[1] + results[0]:
+        assert np.array_equal(got[sample, :n], want)
+        assert (got[:rows, n:] == 77).all() and (got[rows:] == 77).all()
+    for a, b in zip(results[1], results[0]):
+        assert np.array_equal(a, b)
+    weight.close()
+    ctx.close()
+
+
 def test_world_of_one_uses_the_shared_allocation(torch, oracle):
     from volvoxai_b200 import sharded, w8a8
     ctx = w8a8.Context(0)

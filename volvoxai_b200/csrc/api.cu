@@ -95,15 +95,15 @@ bool encode_out32(CUtensorMap* map, const void* base, uint32_t rows, uint32_t n,
 
 // int8 matrix [rows, n] with row pitch ld bytes -> 2-D tensor map with a (128 columns x 32 rows) box, 128B
 // swizzle: the destination of the fused all-gather's TMA tile stores
-bool encode_gather_i8(CUtensorMap* map, const void* base, uint32_t rows, uint32_t n, uint32_t ld) {
+bool encode_gather_i8(CUtensorMap* map, const void* base, uint32_t rows, uint32_t n, uint32_t ld, uint32_t box_columns = 128) {
     EncodeTiledFn fn = encode_fn();
     if (!fn || ((uintptr_t)base & 15u) || (ld & 15u)) return false;
     cuuint64_t dims[2] = {n, rows};
     cuuint64_t strides[1] = {ld};
-    cuuint32_t box[2] = {128, 32};
+    cuuint32_t box[2] = {box_columns, 32};   // 128 columns with the 128B swizzle, 64 with the 64B one
     cuuint32_t elem[2] = {1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, box_columns == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
               CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -308,6 +308,11 @@ VxbPlanQuery plan_query(const VxbContext* ctx, const VxbWeight* w, uint32_t rows
     query.fused_tail = (epi.residual ? 1u : 0u) | (epi.act ? 2u : 0u);
     // TMA tile stores clip at the matrix edge in units of 16 bytes: the width must be a multiple of four 32-bit columns too
     query.out_store_aligned = (epi.mode != kEpiI8 && !((uintptr_t)epi.out & 15u) && !(epi.ld & 3u) && !(w->d_out & 3u)) ? 1u : 0u;
+    if (epi.mode == kEpiI8 && epi.n_peers) {
+        bool aligned = !((uintptr_t)epi.out & 15u) && !(epi.ld & 15u) && !(w->d_out & 15u) && tunables().gather_tma;
+        for (uint32_t p = 0; p < epi.n_peers; p++) aligned = aligned && !((uintptr_t)epi.peer_out[p] & 15u);
+        query.out_store_aligned = aligned ? 1u : 0u;
+    }
     query.fp32_input = fp32_input ? 1u : 0u;
     query.sm_count = (uint32_t)ctx->sm_count;
     query.pair_clusters = (uint32_t)(gemm_pair_clusters() > 0 ? gemm_pair_clusters() : 0);
@@ -432,6 +437,14 @@ int run_gemm(VxbContext* ctx, const VxbWeight* w, const int8_t* q, uint32_t rows
             a.rows = rows; a.n = w->d_out; a.kpad = w->kpad; a.epi = epi; a.status = ctx->status; a.trace = ctx->trace; a.tma_out = 0;
             if (plan.variant == VXB_VARIANT_TCGEN05_PAIR) {
                 a.tmap_b = w->tmap_w128;   // each CTA of a pair loads half of the tile's weight rows
+                a.gather_tma = 0;
+                if (epi.n_peers) {
+                    bool ok = encode_gather_i8(&a.tmap_gather[0], epi.out, rows, w->d_out, epi.ld, 64);
+                    for (uint32_t p = 0; ok && p < epi.n_peers; p++)
+                        ok = encode_gather_i8(&a.tmap_gather[p + 1], epi.peer_out[p], rows, w->d_out, epi.ld, 64);
+                    if (!ok) return fail(0, "cuTensorMapEncodeTiled failed for a gather destination");
+                    a.gather_tma = 1;
+                }
                 LAUNCH_TRY(launch_gemm_pair(a, ctx->stream));
             } else if (plan.variant == VXB_VARIANT_TCGEN05_WIDE) {
                 a.tmap_b = w->tmap_b;
@@ -998,8 +1011,8 @@ int vxb_linear_i8_gather(VxbContext* ctx, const VxbWeight* w, const float* x, ui
     epi.out_lo = -128; epi.out_hi = 127; epi.out = y; epi.ld = ldy;
     epi.n_peers = n_peers;
     for (uint32_t p = 0; p < n_peers; p++) epi.peer_out[p] = peer_y[p];
-    // the peer stores live in the large-M kernel's epilogue
-    return quantize_then_gemm(ctx, w, x, rows, epi, VXB_ROUTE_TCGEN05, "k1+");
+    // with peers the plan picks between the two GEMM kernels that carry the peer stores
+    return quantize_then_gemm(ctx, w, x, rows, epi, n_peers ? VXB_ROUTE_AUTO : VXB_ROUTE_TCGEN05, "k1+");
 }
 
 int vxb_peer_barrier(VxbContext* ctx, uint32_t* my_flags, void* const* peer_flags, const uint32_t* peer_ranks,

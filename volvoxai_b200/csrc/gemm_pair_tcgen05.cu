@@ -276,6 +276,10 @@ __device__ __forceinline__ void gemm_i8_pair_body(const GemmTcgen05Args& args) {
         const bool sat_s8 = ep.out_lo == -128 && ep.out_hi == 127, sat_u8 = ep.out_lo == 0 && ep.out_hi == 255;
         uint32_t acc = 0, acc_phase = 0;
         bool ok = true;
+        // fused all-gather (int8 output, aligned buffers): 64 columns at a time leave through this warp's
+        // 2 KB staging tile ([32 rows x 64 B], 64B-swizzled) as one TMA tile store per destination
+        const bool gather = ep.n_peers != 0;
+        const uint32_t gbuf = smem_u32(sm.base + kOffStore + (warp - 2u) * kStoreBytes);
         pdl_wait();   // row scales and residual come from earlier launches, and one may still read the output
         for (uint32_t t = pair; ok && t < total_tiles; t += pairs) {
             const uint32_t m0 = (t % tiles_m) * 2 * kBM + rank * kBM, n0 = (t / tiles_m) * kBN + cbase;
@@ -306,9 +310,18 @@ __device__ __forceinline__ void gemm_i8_pair_body(const GemmTcgen05Args& args) {
                 tmem_ld32(taddr + c, r);
                 tmem_ld_wait();
                 const uint32_t col = n0 + c;
-                if (col >= args.n) continue;                       // uniform over the warp
                 const bool wide = ep.mode != kEpiI8;                // 32-bit outputs go through the staging below
-                if (!row_ok && !wide) continue;
+                if (gather) {
+                    // no early exit: the destination's tensor map clips rows beyond the batch and columns beyond
+                    // the shard.  A new group of 64 columns starts once the previous group's stores have left the tile.
+                    if ((c & 32u) == 0) {
+                        if (lane == 0) tma_store_wait_read();
+                        __syncwarp();
+                    }
+                } else {
+                    if (col >= args.n) continue;                   // uniform over the warp
+                    if (!row_ok && !wide) continue;
+                }
                 const bool full = col + 32 <= args.n;
                 const float4* w4 = reinterpret_cast<const float4*>(s_ws + c);
                 const float4* b4 = reinterpret_cast<const float4*>(s_bias + c);
@@ -372,7 +385,25 @@ __device__ __forceinline__ void gemm_i8_pair_body(const GemmTcgen05Args& args) {
                             packed[j] = __byte_perm(__byte_perm(q0, q1, 0x0040), __byte_perm(q2, q3, 0x0040), 0x5410);
                         }
                     }
-                    if (full && (((uintptr_t)dst) & 15u) == 0) {
+                    if (gather) {
+                        // this lane's 32 bytes of its row: 16-byte pieces 0,1 or 2,3 of the 64-byte row, XORed with
+                        // bits 1-2 of the row number (the 64B swizzle of the tensor map)
+                        const uint32_t piece = (c & 32u) >> 4, sw = (lane >> 1) & 3u, base = gbuf + lane * 64u;
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(base + ((piece ^ sw) << 4)),
+                                     "r"(packed[0]), "r"(packed[1]), "r"(packed[2]), "r"(packed[3]) : "memory");
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(base + (((piece + 1u) ^ sw) << 4)),
+                                     "r"(packed[4]), "r"(packed[5]), "r"(packed[6]), "r"(packed[7]) : "memory");
+                        if (c & 32u) {
+                            fence_proxy_async();
+                            __syncwarp();
+                            const uint32_t g0 = col - 32u;
+                            if (lane == 0 && g0 < args.n) {
+                                for (uint32_t d = 0; d <= ep.n_peers; d++)
+                                    tma_store_2d(&args.tmap_gather[d], gbuf, (int32_t)g0, (int32_t)(m0 + quarter * 32u));
+                                tma_store_commit();
+                            }
+                        }
+                    } else if (full && (((uintptr_t)dst) & 15u) == 0) {
                         reinterpret_cast<uint4*>(dst)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
                         reinterpret_cast<uint4*>(dst)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
                     } else {
@@ -466,6 +497,7 @@ __device__ __forceinline__ void gemm_i8_pair_body(const GemmTcgen05Args& args) {
             acc ^= 1u;
             if (acc == 0) acc_phase ^= 1u;
         }
+        if (gather && lane == 0) tma_store_wait_all();   // the stores are complete before the kernel ends
     }
 
     // ---------------- teardown ----------------
@@ -512,7 +544,7 @@ int gemm_pair_clusters() { return g_pair_clusters; }
 
 cudaError_t launch_gemm_pair(const GemmTcgen05Args& args, cudaStream_t stream) {
     if (args.rows == 0 || args.n == 0) return cudaSuccess;
-    if (g_pair_clusters <= 0 || args.epi.n_peers != 0) return cudaErrorInvalidValue;
+    if (g_pair_clusters <= 0 || (args.epi.n_peers != 0 && (!args.gather_tma || args.epi.mode != kEpiI8))) return cudaErrorInvalidValue;
     const uint32_t tiles = ((args.rows + 2 * kBM - 1) / (2 * kBM)) * ((args.n + kBN - 1) / kBN);
     const uint32_t pairs = tiles < (uint32_t)g_pair_clusters ? tiles : (uint32_t)g_pair_clusters;
     cudaLaunchConfig_t cfg = {};

@@ -42,6 +42,10 @@ bool admitted(const VxbVariant& v, const VxbPlanQuery& q, char* why, uint32_t by
     }
     if (v.group_size && v.group_size != q.group_size) { refuse(why, bytes, "%s needs group size %u", v.id, v.group_size); return false; }
     if (q.n_peers && !(v.flags & VXB_VF_PEERS)) { refuse(why, bytes, "%s has no peer stores", v.id); return false; }
+    if (q.n_peers && v.cluster > 1 && (!q.out_store_aligned || q.epilogue != VXB_EPI_I8)) {
+        refuse(why, bytes, "%s stores to peers as TMA tiles only: int8 output, 16-byte aligned buffers", v.id);
+        return false;
+    }
     if (q.fused_tail && !(v.flags & VXB_VF_FUSED_TAIL)) { refuse(why, bytes, "%s has no fused epilogue tail", v.id); return false; }
     if (v.flags & VXB_VF_TILE_STORE) {
         if (!q.out_store_aligned) { refuse(why, bytes, "%s needs a 16-byte aligned output base and row pitch", v.id); return false; }
@@ -181,7 +185,15 @@ int vxb_plan(const VxbPlanQuery* query, VxbLaunchPlan* out, char* why, uint32_t 
         else chosen = VXB_VARIANT_GROUPED_TCGEN05;
         if (!admitted(kVariants[chosen], q, why, why_bytes)) return 0;
     } else {
-        if (q.n_peers) chosen = VXB_VARIANT_TCGEN05;   // the peer stores live in the single-CTA GEMM's epilogue
+        if (q.n_peers) {
+            // fused all-gather: a link-bound launch (see gather_is_link_bound) takes the single-CTA kernel with its
+            // 128-byte store tiles; an MMA-bound one the pairs of CTAs, when their tile stores are possible
+            const uint32_t tiles = ceil_div(q.rows, 128) * ceil_div(q.n, 256);
+            char unused[8];
+            chosen = VXB_VARIANT_TCGEN05;
+            if (q.rows > 128 && tiles >= 2u * sms && !gather_is_link_bound(q.n_peers, round_up(q.k, kKAlign)) &&
+                admitted(kVariants[VXB_VARIANT_TCGEN05_PAIR], q, unused, sizeof unused)) chosen = VXB_VARIANT_TCGEN05_PAIR;
+        }
         else if (q.rows <= 128) {
             chosen = VXB_VARIANT_DECODE_ROWS;
             char unused[8];
