@@ -68,13 +68,13 @@ def test_extra_destinations_receive_every_tile(torch, oracle, rows, k, n, ld, ti
 
 
 def test_mma_bound_gather_runs_on_pairs_of_ctas(torch, oracle):
-    """One peer and a padded K above 2140: the launch is MMA-bound, so the plan gives the fused all-gather to
+    """One peer and a padded K of at least 3424: the launch is clearly MMA-bound, so the plan gives the fused all-gather to
     the paired kernel (64-column TMA tile stores).  Its output equals the single-CTA kernel's per-lane-store
     form byte for byte on both destinations, and the oracle on sampled rows."""
     from volvoxai_b200 import _lib, w8a8
     L = _lib.load()
     ctx = w8a8.Context(0)
-    rows, k, n, ld = 2310, 2176, 4368, 4384        # 19 x 18 = 342 tiles of 128 x 256: above two waves
+    rows, k, n, ld = 2310, 3456, 4368, 4384        # 19 x 18 = 342 tiles of 128 x 256: above two waves
     x_np = wl.gemm_activations(rows, k, seed=5)
     w_np, ws_np = wl.gemm_weights(n, k, seed=6)
     weight = w8a8.Weight.from_i8(ctx, w_np, ws_np)

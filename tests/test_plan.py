@@ -65,13 +65,14 @@ def test_automatic_route_boundaries_per_channel():
     # no co-resident pairs on the device: the single-CTA kernel serves everything
     plan, _ = w8a8.plan(8192, 4096, 14336, sm_count=B200_SMS, pair_clusters=0)
     assert plan["id"] == "TCGEN05"
-    # the fused all-gather: a link-bound launch (peers * 2140 > padded K) takes the single-CTA kernel, an
-    # MMA-bound one the pairs of CTAs when their TMA tile stores are possible (aligned buffers, int8 output)
+    # the fused all-gather: the single-CTA kernel, unless the launch is clearly MMA-bound (padded K >= 3424 per
+    # peer): then the pairs of CTAs when their TMA tile stores are possible (aligned buffers, int8 output)
     g = dict(epilogue=_lib.EPI_I8)
     assert pick(8192, 4096, 1792, n_peers=7, **g)["id"] == "TCGEN05"
     assert pick(8192, 4096, 3584, n_peers=3, **g)["id"] == "TCGEN05"
     assert pick(8192, 4096, 7168, n_peers=1, **g)["id"] == "TCGEN05_PAIR"
-    assert pick(8192, 8192, 7168, n_peers=3, **g)["id"] == "TCGEN05_PAIR"
+    assert pick(8192, 8192, 7168, n_peers=3, **g)["id"] == "TCGEN05"
+    assert pick(8192, 8192, 14336, n_peers=1, **g)["id"] == "TCGEN05_PAIR"
     assert pick(8192, 4096, 7168, n_peers=1, out_store_aligned=False, **g)["id"] == "TCGEN05"
     assert pick(1024, 4096, 7168, n_peers=1, **g)["id"] == "TCGEN05"          # 8 * 28 = 224 tiles: below two waves
     assert pick(8192, 4096, 1792, n_peers=7, route=w8a8.ROUTE_TCGEN05, **g)["id"] == "TCGEN05"

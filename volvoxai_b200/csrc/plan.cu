@@ -186,12 +186,15 @@ int vxb_plan(const VxbPlanQuery* query, VxbLaunchPlan* out, char* why, uint32_t 
         if (!admitted(kVariants[chosen], q, why, why_bytes)) return 0;
     } else {
         if (q.n_peers) {
-            // fused all-gather: a link-bound launch (see gather_is_link_bound) takes the single-CTA kernel with its
-            // 128-byte store tiles; an MMA-bound one the pairs of CTAs, when their tile stores are possible
+            // fused all-gather: the single-CTA kernel with its 128-byte store tiles, unless the launch is clearly
+            // MMA-bound (padded K of at least 3424 per peer, 1.6 times the break-even of gather_is_link_bound):
+            // then the pairs of CTAs, whose 64-byte store tiles use the links less well, when their tile stores
+            // are possible.  Measured: 2 GPUs, K 4096: 174 us paired against 190; 4 GPUs, K 8192 (1.28 times
+            // the break-even): 569 us paired against 508.
             const uint32_t tiles = ceil_div(q.rows, 128) * ceil_div(q.n, 256);
             char unused[8];
             chosen = VXB_VARIANT_TCGEN05;
-            if (q.rows > 128 && tiles >= 2u * sms && !gather_is_link_bound(q.n_peers, round_up(q.k, kKAlign)) &&
+            if (q.rows > 128 && tiles >= 2u * sms && (uint64_t)q.n_peers * 3424u <= round_up(q.k, kKAlign) &&
                 admitted(kVariants[VXB_VARIANT_TCGEN05_PAIR], q, unused, sizeof unused)) chosen = VXB_VARIANT_TCGEN05_PAIR;
         }
         else if (q.rows <= 128) {
