@@ -886,6 +886,76 @@ def decode_arm(args):
     print(json.dumps(line), flush=True)
 
 
+def prefill_arm(args):
+    """--workload prefill: one prefill-shaped linear with fp32 output (dequantization + bias) on one GPU,
+    the output-write-bound case of small models (default M 4096, K 576, N 14336).  A step is the quantizer
+    + the GEMM on device-resident fp32 activations; outputs rotate through buffers larger than L2.  Prints
+    one JSON line with the HBM roofline of the GEMM (prepared activations, CUDA-graph replay)."""
+    import torch
+    from volvoxai_b200 import w8a8
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device; there is no CPU fallback")
+    peaks = measured_peaks()
+    rows, k, n = args.rows, args.k, args.n
+    ctx = w8a8.Context(0)
+    ctx.use_torch_stream()
+    w_np, ws_np = wl.gemm_weights(n, k, seed=9)
+    bias = np.random.default_rng(9).standard_normal(n).astype(np.float32) * 0.01
+    weight = w8a8.Weight.from_i8(ctx, w_np, ws_np, bias_f32=bias)
+    x = torch.from_numpy(wl.gemm_activations(rows, k, seed=10)).cuda()
+    copies = max(2, int(np.ceil(300e6 / (4.0 * rows * n))))
+    ys = [torch.empty((rows, n), dtype=torch.float32, device="cuda") for _ in range(copies)]
+    q, sc = ctx.prepare(weight, x)
+    kpad = (k + 127) // 128 * 128
+    algo_bytes = rows * kpad + n * kpad + 8 * n + 4 * rows + 4 * rows * n
+    side = torch.cuda.Stream()
+
+    def replay_ms(fn, launches):
+        for i in range(max(3, args.warmup)):
+            fn(i)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            ctx.use_torch_stream()
+            for i in range(launches):
+                fn(i)
+        ctx.use_torch_stream()
+        g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        e1.synchronize()
+        return e0.elapsed_time(e1) / launches
+
+    launches0 = w8a8.launch_count()
+    step_ms = replay_ms(lambda i: ctx.linear_f32(weight, x, out=ys[i % copies]), args.steps)
+    launches = w8a8.launch_count() - launches0
+    route = w8a8.last_route()
+    kern_ms = replay_ms(lambda i: ctx.linear_prepared(weight, q, sc, ys[i % copies], mode=1), args.steps)
+    gbs = algo_bytes / (kern_ms * 1e-3) / 1e9
+    line = {
+        "metric": "w8a8_prefill_linear_f32_hbm_gbs", "value": (algo_bytes + 4.0 * rows * k) / (step_ms * 1e-3) / 1e9,
+        "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": step_ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+        "config": {"workload": f"w8a8_linear_prefill_M{rows}_K{k}_N{n}_f32", "rows": rows, "k": k, "n": n,
+                   "route": route, "l2": f"{copies} output buffers rotate (> 2x L2 with the operands)",
+                   "timing": "CUDA-graph replay of back-to-back launches between two events"},
+        "gpu_launches": int(launches),
+        "tops": 2.0 * rows * k * n / (step_ms * 1e-3) / 1e12,
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": gbs / peaks["hbm_gbs"], "traffic": None,
+                     "kernel": "gemm_i8_wide_kernel" if "wide" in route else "gemm_i8_pair_kernel" if "pair" in route else "gemm_i8_tcgen05_kernel",
+                     "kernel_us": kern_ms * 1e3, "algorithmic_bytes": algo_bytes,
+                     "output_write_gbs": 4.0 * rows * n / (kern_ms * 1e-3) / 1e9,
+                     "frac_of_nominal_8000": gbs / NOMINAL_HBM_GBS, "peak_source": peaks["_source"]},
+    }
+    weight.close()
+    ctx.close()
+    print(json.dumps(line), flush=True)
+
+
 def decoder_arm(args):
     """`--workload decoder --model smollm2|qwen3 [--gpus N]`: the two model-shaped configurations end to
     end.  smollm2: prefill of 8 x 512 tokens through the 30-layer SmolLM2-135M-shaped decoder (tokens/s);
@@ -1074,7 +1144,7 @@ def grouped_arm(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="gemm", choices=["gemm", "decode", "grouped", "decoder"])
+    ap.add_argument("--workload", default="gemm", choices=["gemm", "decode", "grouped", "decoder", "prefill"])
     ap.add_argument("--model", default="qwen3", choices=["smollm2", "qwen3"], help="architecture of --workload decoder")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
@@ -1090,7 +1160,9 @@ def main():
     ap.add_argument("--no-extras", action="store_true")
     args = ap.parse_args()
     if args.rows is None:
-        args.rows = 8 if args.workload == "decode" else 4096 if args.workload == "grouped" else 8192
+        args.rows = 8 if args.workload == "decode" else 4096 if args.workload in ("grouped", "prefill") else 8192
+    if args.workload == "prefill" and (args.k, args.n) == (4096, 14336):
+        args.k = 576
     if args.impl == "reference":
         reference_arm(args)
     elif args.workload == "decode":
@@ -1099,6 +1171,8 @@ def main():
         grouped_arm(args)
     elif args.workload == "decoder":
         decoder_arm(args)
+    elif args.workload == "prefill":
+        prefill_arm(args)
     else:
         gpu_arm(args)
 
