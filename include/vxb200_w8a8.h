@@ -244,7 +244,10 @@ VXB_API int vxb_rmsnorm_quantize_rows(VxbContext* ctx, const float* x, const flo
                               float* row_scales, int32_t* valid);
 
 /* RMSNorm -> per-token quantization -> linear -> fp32 epilogue with the optional SiLU*Mul tail of
- * vxb_linear_f32_fused, in two launches.  q/k/v (or gate/up, interleaved for SILU_MUL) are one
+ * vxb_linear_f32_fused: ONE launch for one and two rows (the decode kernel normalizes and quantizes the
+ * rows itself; the counterpart of the reference's fused decode kernels,
+ * native/src/backends/cuda/kernels/cuda_forward_gemv_pair_kernels.inc:1136-1424), two launches
+ * otherwise, with the same bits either way.  q/k/v (or gate/up, interleaved for SILU_MUL) are one
  * weight concatenated along the output channels, so the three (two) projections share the
  * normalization and the quantization.  norm_out may be NULL. */
 VXB_API int vxb_rmsnorm_linear_f32_fused(VxbContext* ctx, const VxbWeight* w, const float* x, const float* norm_weight,

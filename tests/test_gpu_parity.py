@@ -840,6 +840,44 @@ def test_rmsnorm_linear_fused(torch, ctx, oracle, rows, k, n):
     weight.close()
 
 
+@pytest.mark.parametrize("rows,k,n", [(1, 1024, 3072), (2, 4096, 14336), (5, 576, 1536), (8, 8192, 2048)])
+def test_rmsnorm_in_the_single_launch_decode_form(torch, ctx, oracle, rows, k, n):
+    """RMSNorm + quantization inside the decode kernel (one launch per pattern, as the reference's fused decode
+    kernels): the same output and the same persisted normalized rows as the two-launch form, the normalized
+    rows within the tolerance contract of the reference's CPU operator; automatic for one and two rows, up
+    to eight rows on request; with the SiLU * up tail."""
+    from volvoxai_b200 import w8a8
+    c = wl.single_linear(rows=rows, k=k, n=n, seed=rows * 3 + n)
+    rng = np.random.default_rng(rows + k + 1)
+    x = (c["x"] * rng.uniform(0.05, 20.0, size=(rows, 1))).astype(np.float32)
+    gamma = rng.uniform(0.1, 3.0, size=k).astype(np.float32)
+    weight = w8a8.Weight.from_i8(ctx, c["w"], c["ws"], bias_f32=c["bias"])
+    xd, gd = dev(torch, x), dev(torch, gamma)
+    try:
+        assert w8a8.tune("decode.fused_max_rows", 8)
+        norm1 = torch.zeros_like(xd)
+        y1 = ctx.rmsnorm_linear_f32_fused(weight, xd, gd, 1e-5, norm_out=norm1).cpu().numpy()
+        assert w8a8.last_route().startswith("norm+decode-fused-tcgen05-i8"), w8a8.last_route()
+        s1 = ctx.rmsnorm_linear_f32_fused(weight, xd, gd, 1e-5, silu_mul=True).cpu().numpy()
+        assert w8a8.tune("decode.fused_max_rows", 0)
+        norm2 = torch.zeros_like(xd)
+        y2 = ctx.rmsnorm_linear_f32_fused(weight, xd, gd, 1e-5, norm_out=norm2).cpu().numpy()
+        assert w8a8.last_route().startswith("norm+k1+decode-rows"), w8a8.last_route()
+        s2 = ctx.rmsnorm_linear_f32_fused(weight, xd, gd, 1e-5, silu_mul=True).cpu().numpy()
+        assert w8a8.tune("decode.fused_max_rows", 2)
+        ctx.rmsnorm_linear_f32_fused(weight, xd, gd, 1e-5)
+        assert w8a8.last_route().startswith("norm+decode-fused") == (rows <= 2)
+    finally:
+        w8a8.tune("decode.fused_max_rows", 2)
+    _check_norm(norm1.cpu().numpy(), oracle.rmsnorm_rows(x, gamma, 1e-5))
+    assert np.array_equal(norm1.cpu().numpy().view(np.uint32), norm2.cpu().numpy().view(np.uint32))
+    assert np.array_equal(y1.view(np.uint32), y2.view(np.uint32))
+    assert np.array_equal(s1.view(np.uint32), s2.view(np.uint32))
+    ref = oracle.w8a8_linear(norm1.cpu().numpy(), c["w"], c["ws"], bias=c["bias"])["out"]
+    assert rel_err(y1, ref) <= F32_TOL
+    weight.close()
+
+
 # ---- boundary ops of a static W8A8 island --------------------------------------------------
 
 def _boundary_cases(golden):

@@ -320,7 +320,8 @@ VxbPlanQuery plan_query(const VxbContext* ctx, const VxbWeight* w, uint32_t rows
 }
 
 // The decode kernel's single-launch form: the CTAs quantize the fp32 rows themselves.
-int launch_decode_fused(VxbContext* ctx, const VxbWeight* w, const float* x, uint32_t rows, const EpilogueParams& epi) {
+int launch_decode_fused(VxbContext* ctx, const VxbWeight* w, const float* x, uint32_t rows, const EpilogueParams& epi,
+                        const float* norm_weight = nullptr, float epsilon = 0.0f, float* norm_out = nullptr) {
     if (!w->has_tmap) return fail(0, "no tensor map for this weight (driver entry point missing)");
     if ((uintptr_t)x & 15u) return fail(0, "the single-launch decode form needs 16-byte aligned activations");
     DecodeRowsArgs a{};
@@ -329,13 +330,14 @@ int launch_decode_fused(VxbContext* ctx, const VxbWeight* w, const float* x, uin
     a.tile_rows = w->tile_rows; a.tiles_per_cta = w->tiles_per_cta;
     a.w_stage_bytes = round_up(w->tile_rows * kKAlign, 1024u);
     a.x_f32 = x; a.k = w->d_in;
+    a.norm_weight = norm_weight; a.norm_eps = (double)epsilon; a.norm_out = norm_out;
     a.epi = epi; a.status = ctx->status; a.trace = ctx->trace;
     if (!decode_rows_configure(a)) return fail(0, "no launch shape for the single-launch decode form (rows %u, d_out %u)", rows, w->d_out);
     ProfileScope scope(ctx, 1);
     LAUNCH_TRY(launch_decode_rows(a, ctx->stream));
     count_launch();
     const char* tail = epi.mode == kEpiAcc ? "acc" : epi.mode == kEpiF32 ? "e1" : "e2";
-    snprintf(g_route, sizeof g_route, "%s+%s", vxb_variant_info(VXB_VARIANT_DECODE_FUSED)->route_label, tail);
+    snprintf(g_route, sizeof g_route, "%s%s+%s", norm_weight ? "norm+" : "", vxb_variant_info(VXB_VARIANT_DECODE_FUSED)->route_label, tail);
     return 1;
 }
 
@@ -539,17 +541,19 @@ uint32_t overlap_first_rows(const VxbContext* ctx, const VxbWeight* w, uint32_t 
 int quantize_then_gemm(VxbContext* ctx, const VxbWeight* w, const float* x, uint32_t rows, const EpilogueParams& epi,
                        int route, const char* prefix, const float* norm_weight = nullptr, float epsilon = 0.0f,
                        float* norm_out = nullptr) {
-    if (!norm_weight && (route == VXB_ROUTE_AUTO || route == VXB_ROUTE_DECODE_FUSED) && rows <= 8) {
-        // up to 8 rows: one launch, the decode kernel quantizes the rows itself (when the plan admits it)
+    if ((route == VXB_ROUTE_AUTO || route == VXB_ROUTE_DECODE_FUSED) && rows <= 8) {
+        // up to 8 rows: one launch, the decode kernel normalizes (when asked to) and quantizes the rows itself
+        // (when the plan admits it)
         const VxbPlanQuery query = plan_query(ctx, w, rows, epi, route, true);
         VxbLaunchPlan plan;
         char why[160];
         const int planned = vxb_plan(&query, &plan, why, sizeof why);
-        if (planned == 1 && plan.variant == VXB_VARIANT_DECODE_FUSED && ((uintptr_t)x & 15u) == 0)
-            return launch_decode_fused(ctx, w, x, rows, epi);
+        const bool aligned = (((uintptr_t)x | (uintptr_t)norm_weight | (uintptr_t)norm_out) & 15u) == 0;
+        if (planned == 1 && plan.variant == VXB_VARIANT_DECODE_FUSED && aligned)
+            return launch_decode_fused(ctx, w, x, rows, epi, norm_weight, epsilon, norm_out);
         if (route == VXB_ROUTE_DECODE_FUSED) return fail(0, "%s", planned == 1 ? "activations are not 16-byte aligned" : why);
     } else if (route == VXB_ROUTE_DECODE_FUSED) {
-        return fail(0, "the single-launch decode form serves up to 8 rows without a fused RMSNorm");
+        return fail(0, "the single-launch decode form serves up to 8 rows");
     }
     uint32_t first = norm_weight ? 0u : overlap_first_rows(ctx, w, rows, epi, route);
     if (first) {

@@ -382,6 +382,9 @@ struct DecodeRowsArgs {
     // the UMMA operand layout, while its weight ring fills; tmap_x and epi.row_scales are unused then
     const float* x_f32;       // [rows, k] fp32 activations, or null (activations come prepared through tmap_x)
     uint32_t k;               // logical width of x_f32 (a multiple of 4)
+    const float* norm_weight; // single-launch form only: RMSNorm weight [k] applied to the rows before they are quantized, or null
+    double norm_eps;
+    float* norm_out;          // optional [rows, k]: the normalized rows, written by the first CTA
     EpilogueParams epi;
     int* status;
     unsigned long long* trace;   // optional [grid][kTraceSlots] of %globaltimer stamps, or null

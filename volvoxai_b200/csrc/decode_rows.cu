@@ -157,12 +157,17 @@ __device__ __forceinline__ void finish_parked(const DecodeRowsArgs& args, const 
 
 // Single-launch form: every CTA quantizes the (at most 8) fp32 rows itself, with K1's arithmetic bit
 // for bit, straight into the shared-memory layout the MMA reads (one [8 x 128 B] swizzled atom per
-// 128-byte K block: the 16-byte piece c of row r sits at piece c ^ r).  The rows are read twice
-// from L2 (absmax, then quantize); rows * k * 4 bytes per CTA is far below what the weight stream
+// 128-byte K block: the 16-byte piece c of row r sits at piece c ^ r).  The rows are read from L2 once
+// per pass (absmax, then quantize); rows * k * 4 bytes per CTA is far below what the weight stream
 // brings in meanwhile, so the work hides behind the filling weight ring.  The row scales go to s_as.
 // Warps are dealt out to rows, `wpr` warps per row, each over a contiguous part of the row.
+// With `gamma` the rows pass through an RMSNorm first (the arithmetic of the stand-alone fused quantizer,
+// quantize.cuh): one more pass for the sum of squares, the normalized values are recomputed in the absmax
+// and in the quantizing pass, and the first CTA persists them in `norm_out` when other consumers need them.
 __device__ __forceinline__ void fused_quantize_rows(const float* __restrict__ x, uint32_t rows, uint32_t k, uint8_t* x_smem,
-                                                    float* s_as, float* part_max, int* part_bad, uint32_t warps) {
+                                                    float* s_as, float* part_max, int* part_bad, uint32_t warps,
+                                                    const float* __restrict__ gamma, double eps, float* __restrict__ norm_out,
+                                                    double* part_ss) {
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t wpr = warps / rows;                      // >= 1: rows <= 8 <= warps
     const uint32_t row = warp / wpr, part = warp - row * wpr;
@@ -171,9 +176,39 @@ __device__ __forceinline__ void fused_quantize_rows(const float* __restrict__ x,
     const uint32_t v0 = part * seg, v1 = v0 + seg < nvec ? v0 + seg : nvec;
     const float4* in = reinterpret_cast<const float4*>(x + (size_t)(active ? row : 0) * k);
     // loads go out in batches of kBatch per lane before any of them is used: the loop is a chain of
-    // L2 round trips otherwise (one outstanding load per lane)
+    // L2 round trips otherwise (one outstanding load per lane).  Keeping a warp's part of the row in
+    // registers across the passes instead of reading it again was slower (the kernel's 96-register
+    // budget spilled: 15.8 against 14.2 us per launch for one row at K 4096, N 14336).
     constexpr uint32_t kBatch = 8;
     const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4* g4 = reinterpret_cast<const float4*>(gamma);
+    double inv = 0.0;
+    if (gamma) {
+        // the row's sum of squares: exact products, double additions; the partial sums of a row's warps are
+        // added in a fixed order, so every CTA arrives at the same bits
+        double ss = 0.0;
+        if (active)
+            for (uint32_t vb = v0 + lane; vb < v1; vb += 32 * kBatch) {
+                float4 c[kBatch];
+#pragma unroll
+                for (uint32_t j = 0; j < kBatch; j++) c[j] = vb + 32 * j < v1 ? __ldg(in + vb + 32 * j) : zero4;
+#pragma unroll
+                for (uint32_t j = 0; j < kBatch; j++) ss = square_sum4(c[j], ss);
+            }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+        if (lane == 0) part_ss[warp] = ss;
+        __syncthreads();
+        // one thread per row does the double-precision division and square root
+        if (threadIdx.x < rows) {
+            double t = 0.0;
+            for (uint32_t i = 0; i < wpr; i++) t += part_ss[threadIdx.x * wpr + i];
+            part_ss[32 + threadIdx.x] = 1.0 / sqrt(t / (double)k + eps);
+        }
+        __syncthreads();
+        if (active) inv = part_ss[32 + row];
+    }
+    float4* nout = (gamma && norm_out && blockIdx.x == 0 && active) ? reinterpret_cast<float4*>(norm_out + (size_t)row * k) : nullptr;
     float amax = 0.0f; int bad = 0;
     if (active)
         for (uint32_t vb = v0 + lane; vb < v1; vb += 32 * kBatch) {
@@ -182,6 +217,10 @@ __device__ __forceinline__ void fused_quantize_rows(const float* __restrict__ x,
             for (uint32_t j = 0; j < kBatch; j++) c[j] = vb + 32 * j < v1 ? __ldg(in + vb + 32 * j) : zero4;
 #pragma unroll
             for (uint32_t j = 0; j < kBatch; j++) {
+                if (gamma && vb + 32 * j < v1) {
+                    c[j] = norm4(c[j], inv, __ldg(g4 + vb + 32 * j));
+                    if (nout) nout[vb + 32 * j] = c[j];
+                }
                 bad |= nonfinite_bits(c[j].x) | nonfinite_bits(c[j].y) | nonfinite_bits(c[j].z) | nonfinite_bits(c[j].w);
                 amax = fmaxf(amax, fmaxf(fmaxf(fabsf(c[j].x), fabsf(c[j].y)), fmaxf(fabsf(c[j].z), fabsf(c[j].w))));
             }
@@ -209,6 +248,7 @@ __device__ __forceinline__ void fused_quantize_rows(const float* __restrict__ x,
         for (uint32_t j = 0; j < kBatch; j++) {
             const uint32_t v = vb + 32 * j;
             if (v >= v1) break;
+            if (gamma) c[j] = norm4(c[j], inv, __ldg(g4 + v));
             const uint32_t word = bad ? 0u : (fast ? pack4t<true>(c[j], div) : pack4t<false>(c[j], div));
             const uint32_t kbyte = v << 2, kb = kbyte >> 7, off = kbyte & 127u;
             *reinterpret_cast<uint32_t*>(row_base + (size_t)kb * (8u * kRK) + (((off >> 4) ^ row) << 4) + (off & 15u)) = word;
@@ -306,8 +346,9 @@ decode_rows_kernel(const __grid_constant__ DecodeRowsArgs args) {
             if (threadIdx.x == 0) stamp(args.trace, 6);
             float* part_max = reinterpret_cast<float*>(s_xpose);          // the parking area is free until the epilogue
             int* part_bad = reinterpret_cast<int*>(s_xpose) + 32;
+            double* part_ss = reinterpret_cast<double*>(s_xpose) + 32;    // bytes 256.. of the same area
             fused_quantize_rows(args.x_f32, args.rows, args.k, base + lay.x_off(0), s_as, part_max, part_bad,
-                                ModeCfg<PAIR>::kThreads / 32);
+                                ModeCfg<PAIR>::kThreads / 32, args.norm_weight, args.norm_eps, args.norm_out, part_ss);
             fence_proxy_async();   // generic-proxy writes to shared memory -> visible to the tensor core's reads
             __syncthreads();
         }

@@ -294,19 +294,6 @@ cudaError_t launch_vec(const float* x, uint32_t rows, uint32_t k, int8_t* q, uin
 // are exact in double; only the order of the double additions differs from the sequential loop
 // (tree instead of left to right), which moves the mean by at most a few units of 2^-53.
 
-__device__ __forceinline__ float norm1(float x, double inv, float g) {
-    return __double2float_rn(__dmul_rn(__dmul_rn((double)x, inv), (double)g));
-}
-__device__ __forceinline__ float4 norm4(float4 c, double inv, float4 g) {
-    return make_float4(norm1(c.x, inv, g.x), norm1(c.y, inv, g.y), norm1(c.z, inv, g.z), norm1(c.w, inv, g.w));
-}
-__device__ __forceinline__ double square_sum4(float4 c, double acc) {
-    acc = __fma_rn((double)c.x, (double)c.x, acc);
-    acc = __fma_rn((double)c.y, (double)c.y, acc);
-    acc = __fma_rn((double)c.z, (double)c.z, acc);
-    return __fma_rn((double)c.w, (double)c.w, acc);
-}
-
 template <int THREADS_PER_ROW>
 __device__ __forceinline__ double row_sum(double v, double* smem_sum) {
     constexpr int kWarpSpan = THREADS_PER_ROW < 32 ? THREADS_PER_ROW : 32;
@@ -361,7 +348,12 @@ rmsnorm_quantize_rows_vec(const float* __restrict__ x, const float* __restrict__
         }
     }
     ss = row_sum<THREADS_PER_ROW>(ss, smem_sum);
-    const double inv = 1.0 / sqrt(ss / (double)k + eps);
+    // one thread per row does the double-precision division and square root (slow, shared units); the others
+    // take the result from shared memory
+    __shared__ double smem_inv[kThreads / 8];
+    if (t == 0) smem_inv[threadIdx.x / THREADS_PER_ROW] = 1.0 / sqrt(ss / (double)k + eps);
+    if constexpr (THREADS_PER_ROW > 32) __syncthreads(); else __syncwarp();
+    const double inv = smem_inv[threadIdx.x / THREADS_PER_ROW];
 
     float amax = 0.0f; int bad = 0;
     if (active) {

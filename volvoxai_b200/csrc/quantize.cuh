@@ -78,4 +78,19 @@ __device__ __forceinline__ float row_scale_from_amax(float amax) {
     return fmaxf(scale, 1.1754943508222875e-38f);
 }
 
+// RMSNorm in front of the quantizer (the reference's CPU operator, native/src/kernels/softmax_rmsnorm.inc:3-16):
+// squares and their mean in double, inv = 1 / sqrt(mean + eps) in double, y = float((double(x) * inv) * double(gamma)).
+__device__ __forceinline__ float norm1(float x, double inv, float g) {
+    return __double2float_rn(__dmul_rn(__dmul_rn((double)x, inv), (double)g));
+}
+__device__ __forceinline__ float4 norm4(float4 c, double inv, float4 g) {
+    return make_float4(norm1(c.x, inv, g.x), norm1(c.y, inv, g.y), norm1(c.z, inv, g.z), norm1(c.w, inv, g.w));
+}
+__device__ __forceinline__ double square_sum4(float4 c, double acc) {
+    acc = __fma_rn((double)c.x, (double)c.x, acc);
+    acc = __fma_rn((double)c.y, (double)c.y, acc);
+    acc = __fma_rn((double)c.z, (double)c.z, acc);
+    return __fma_rn((double)c.w, (double)c.w, acc);
+}
+
 }  // namespace vxb
