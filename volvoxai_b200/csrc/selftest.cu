@@ -91,6 +91,11 @@ div_const_check_kernel(int exponent, uint32_t neighbours, uint32_t samples, unsi
 __global__ void __launch_bounds__(32, 1)
 peer_barrier_kernel(uint32_t* my_flags, PeerBarrierArgs args, int* status) {
     const uint32_t t = threadIdx.x;
+    // launched as a programmatic dependent: resident while the kernel before it still runs, and letting the
+    // launch after it become resident in turn; the wait returns when that kernel (the GEMM whose peer stores
+    // this barrier orders) has completed and its stores have been performed
+    pdl_release();
+    pdl_wait();
     if (t >= args.n_peers) return;
     __threadfence_system();
     uint32_t* remote = args.peer_flags[t] + args.my_rank;
@@ -113,8 +118,7 @@ peer_barrier_kernel(uint32_t* my_flags, PeerBarrierArgs args, int* status) {
 }  // namespace
 
 cudaError_t launch_peer_barrier(uint32_t* my_flags, const PeerBarrierArgs& args, int* status, cudaStream_t stream) {
-    peer_barrier_kernel<<<1, 32, 0, stream>>>(my_flags, args, status);
-    return cudaGetLastError();
+    return launch_pdl(peer_barrier_kernel, dim3(1), dim3(32), 0, stream, my_flags, args, status);
 }
 
 cudaError_t launch_wait_expiry(int* status, cudaStream_t stream) {
