@@ -823,12 +823,22 @@ def decode_arm(args):
     through more than 2x L2 of distinct copies. Prints one JSON line with the HBM roofline of the
     decode kernel (prepared activations, CUDA-graph replay of back-to-back launches)."""
     import torch
+    import torch.distributed as dist
     from volvoxai_b200 import w8a8
     if not torch.cuda.is_available():
         raise RuntimeError("bench.py needs a CUDA device; there is no CPU fallback")
+    # N > 1: every GPU serves its own sequences against its own copy of the layer ("replicas only": at
+    # decode sizes an N-shard would trade a 10 us weight stream for an exchange of the same order)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     peaks = measured_peaks()
     rows, k, n = args.rows, args.k, args.n
-    ctx = w8a8.Context(0)
+    ctx = w8a8.Context(local)
     ctx.use_torch_stream()
     rng = np.random.default_rng(7)
     copies = max(2, int(np.ceil(300e6 / (k * n))))
@@ -853,12 +863,18 @@ def decode_arm(args):
         ctx.use_torch_stream()
         g.replay()
         torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         g.replay()
         e1.record()
         e1.synchronize()
-        return e0.elapsed_time(e1) / launches
+        ms = torch.tensor([e0.elapsed_time(e1) / launches], dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)   # the slowest replica's time counts
+        return float(ms.item())
 
     launches0 = w8a8.launch_count()
     step_ms = replay_ms(lambda i: ctx.linear_f32(weights[i % copies], x, out=y), args.steps)
@@ -867,12 +883,14 @@ def decode_arm(args):
     kern_ms = replay_ms(lambda i: ctx.linear_prepared(weights[i % copies], q, sc, y, mode=1), args.steps)
     gbs = algo_bytes / (kern_ms * 1e-3) / 1e9
     line = {
-        "metric": "w8a8_decode_linear_hbm_gbs", "value": algo_bytes / (step_ms * 1e-3) / 1e9, "unit": "GB/s",
-        "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": step_ms,
+        "metric": "w8a8_decode_linear_hbm_gbs", "value": world * algo_bytes / (step_ms * 1e-3) / 1e9, "unit": "GB/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": step_ms,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
         "data": "synthetic",
         "config": {"workload": f"w8a8_linear_decode_M{rows}_K{k}_N{n}_f32", "rows": rows, "k": k, "n": n,
-                   "route": route, "l2": f"{copies} distinct weight copies rotate (> 2x L2)",
+                   "route": route, "parallelism": "replicas only" if world > 1 else "one GPU",
+                   "rows_per_s": world * rows / (step_ms * 1e-3),
+                   "l2": f"{copies} distinct weight copies rotate (> 2x L2)",
                    "timing": "CUDA-graph replay of back-to-back launches between two events"},
         "gpu_launches": int(launches),
         "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
@@ -883,7 +901,11 @@ def decode_arm(args):
     for wt in weights:
         wt.close()
     ctx.close()
-    print(json.dumps(line), flush=True)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 def prefill_arm(args):
