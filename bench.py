@@ -638,7 +638,10 @@ def gpu_arm(args):
 
     sampler = ClockSampler(local)
     launches0 = w8a8.launch_count()
-    ctx.profile(True)
+    # the GEMM is bracketed by events on every 8th step only: an event between two launches keeps the later
+    # one from starting as a programmatic dependent of the earlier, which costs 12 us per step at N = 2
+    prof_stride = 8 if args.steps >= 16 else 1
+    ctx.profile(prof_stride)
     sampler.start()
     total_ms = timed(step, args.steps)
     sampler.sample_now()
@@ -691,7 +694,8 @@ def gpu_arm(args):
     # roofline of the dominant kernel (the tcgen05 GEMM of this rank's shard)
     # a large batch is cut in two (the quantizer of the later rows runs under the GEMM of the first ones):
     # the GEMM's time per step is the sum over its launches of that step
-    gemm_ms = prof["gemm_ms"] / args.steps
+    launches_per_step = 1.0   # one GEMM launch per step (the two-chunk overlap form is off by default)
+    gemm_ms = prof["gemm_ms"] / max(1, prof["gemm_launches"]) * launches_per_step
     # the quantizer alone over the whole batch, timed outside the step loop
     for _ in range(3):
         ctx.quantize_rows(x_dev, ldq=weight.row_bytes)
@@ -710,7 +714,9 @@ def gpu_arm(args):
         "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
         "frac": achieved / peak, "traffic": None,
         "kernel": "gemm_i8_pair_kernel" if "pair" in step_route else "gemm_i8_tcgen05_kernel", "kernel_ms": gemm_ms,
-        "kernel_launches_per_step": prof["gemm_launches"] / args.steps, "route": step_route,
+        "kernel_launches_per_step": launches_per_step, "kernel_launches_timed": int(prof["gemm_launches"]),
+        "kernel_timing": f"CUDA event pairs around every {prof_stride}th step's launch inside the timed region",
+        "route": step_route,
         "peak_source": f"2 x bf16_tflops (cuBLAS bf16 burst, {peaks['_source']}) as the dense int8 rate",
         "i8_probe_tops": i8_probe, "frac_of_i8_probe": achieved / i8_probe,
         "frac_of_nominal_4500": achieved / NOMINAL_I8_TOPS,

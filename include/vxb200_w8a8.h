@@ -290,8 +290,10 @@ VXB_API int vxb_linear_host(VxbContext* ctx, const VxbWeight* w, const float* x_
  * replay plan (docs/cuda.md:537-556): while enabled, every quantizer launch and
  * every GEMM/GEMV launch of this context is bracketed by CUDA events on the
  * context's stream (at most 8192 launches of each kind are recorded).
- * vxb_context_profile(ctx, 1) clears and starts, (ctx, 0) clears and stops;
- * _read waits for the stream and returns summed milliseconds and launch counts. */
+ * vxb_context_profile(ctx, 1) clears and starts, (ctx, 0) clears and stops; (ctx, n) with n > 1
+ * brackets only every n-th launch of each kind (an event between two launches keeps the later one
+ * from starting as a programmatic dependent of the earlier, so dense sampling perturbs a chain).
+ * _read waits for the stream and returns summed milliseconds and counts of the RECORDED launches. */
 VXB_API int vxb_context_profile(VxbContext* ctx, int enable);
 VXB_API int vxb_context_profile_read(VxbContext* ctx, double* quantize_ms, uint64_t* quantize_launches,
                              double* gemm_ms, uint64_t* gemm_launches);

@@ -167,7 +167,8 @@ struct VxbContext {
     // K1 / K2 overlap: the quantizer of the later rows runs on `side` under the GEMM of the first rows
     cudaStream_t side = nullptr;
     cudaEvent_t ev_first = nullptr, ev_rest = nullptr;
-    bool profiling = false;
+    int profiling = 0;          // 0 off, n: every n-th launch of a kind is bracketed by events
+    uint32_t prof_seen[2] = {0, 0};
     std::vector<cudaEvent_t> prof_events[2];   // [0] = K1 quantizer, [1] = GEMM / GEMV
 };
 
@@ -211,7 +212,8 @@ void count_launch(int n = 1) { g_launches.fetch_add((uint64_t)n, std::memory_ord
 constexpr size_t kMaxProfiledLaunches = 8192;
 struct ProfileScope {
     VxbContext* ctx; int kind; bool on;
-    ProfileScope(VxbContext* c, int k) : ctx(c), kind(k), on(c->profiling && c->prof_events[k].size() < 2 * kMaxProfiledLaunches) {
+    ProfileScope(VxbContext* c, int k) : ctx(c), kind(k), on(false) {
+        on = c->profiling && (c->prof_seen[k]++ % (uint32_t)c->profiling) == 0 && c->prof_events[k].size() < 2 * kMaxProfiledLaunches;
         if (on) { cudaEvent_t e; cudaEventCreate(&e); cudaEventRecord(e, ctx->stream); ctx->prof_events[kind].push_back(e); }
     }
     ~ProfileScope() {
@@ -1209,7 +1211,8 @@ int vxb_context_profile(VxbContext* ctx, int enable) {
     if (!ctx) return fail(0, "null context");
     if (ensure_device(ctx) != 1) return -1;
     for (auto& v : ctx->prof_events) { for (cudaEvent_t e : v) cudaEventDestroy(e); v.clear(); }
-    ctx->profiling = enable != 0;
+    ctx->profiling = enable > 0 ? enable : 0;
+    ctx->prof_seen[0] = ctx->prof_seen[1] = 0;
     return 1;
 }
 

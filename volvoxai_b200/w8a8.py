@@ -150,9 +150,10 @@ class Context:
         """Decode-kernel time stamps into the int64 CUDA tensor `stamps` ([ctas, 8]); None stops."""
         _check(self._L.vxb_context_trace(self.handle, _ptr(stamps) if stamps is not None else None))
 
-    def profile(self, enable: bool) -> None:
-        """Start (True) or stop (False) per-kernel event timing; both clear the record."""
-        _check(self._L.vxb_context_profile(self.handle, 1 if enable else 0))
+    def profile(self, enable) -> None:
+        """Start (True, or an int n > 1 to bracket only every n-th launch of each kind) or stop (False)
+        per-kernel event timing; both clear the record."""
+        _check(self._L.vxb_context_profile(self.handle, int(enable)))
 
     def profile_read(self) -> dict:
         qms, qn, gms, gn = C.c_double(0), C.c_uint64(0), C.c_double(0), C.c_uint64(0)
