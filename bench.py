@@ -437,7 +437,7 @@ def widened_rows(torch, ctx, w8a8, peaks, replays=10):
     return out
 
 
-def gemm_sweep(torch, ctx, w8a8, peaks, i8_probe, steps=5):
+def gemm_sweep(torch, ctx, w8a8, peaks, i8_probe, steps=12):
     """All twelve shapes of the compute-bound sweep (M in 2048..16384 x three (K, N) pairs), requantizing
     epilogue, one GPU: step time (quantizer + GEMM, inputs resident in HBM, CUDA events) and the GEMM
     kernel's own time (event pairs inside the library), as TOPS and as fractions of the resident-operand
@@ -457,7 +457,7 @@ def gemm_sweep(torch, ctx, w8a8, peaks, i8_probe, steps=5):
             for _ in range(3):
                 ctx.linear_i8(weight, x, 0.05, 0, out=y)
             torch.cuda.synchronize()
-            ctx.profile(True)
+            ctx.profile(4)   # every fourth step's GEMM is bracketed by events (they break the launch chain)
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             for _ in range(steps):
@@ -466,7 +466,7 @@ def gemm_sweep(torch, ctx, w8a8, peaks, i8_probe, steps=5):
             e1.synchronize()
             prof = ctx.profile_read()
             ctx.profile(False)
-            step_ms, kern_ms = e0.elapsed_time(e1) / steps, prof["gemm_ms"] / steps
+            step_ms, kern_ms = e0.elapsed_time(e1) / steps, prof["gemm_ms"] / max(1, prof["gemm_launches"])
             ops = 2.0 * m * k * n
             out.append({"rows": m, "k": k, "n": n, "route": w8a8.last_route(), "step_ms": step_ms, "kernel_ms": kern_ms,
                         "step_tops": ops / step_ms / 1e9, "kernel_tops": ops / kern_ms / 1e9,
