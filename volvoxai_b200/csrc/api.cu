@@ -1244,14 +1244,27 @@ int vxb_linear_host(VxbContext* ctx, const VxbWeight* w, const float* x_host, ui
     const size_t in_row = (size_t)w->d_in * 4, out_row = (size_t)w->d_out * (requant ? 1 : 4);
     // Large batches go through in row chunks on three streams, so that the upload of chunk c+1,
     // the kernels of chunk c and the download of chunk c-1 overlap (PCIe is full duplex and is
-    // what bounds this entry). Two staging buffers each way.
-    uint32_t chunk = rows;
-    if (rows >= 1024) {
-        chunk = (rows + 7) / 8;
-        chunk = (chunk + 127) / 128 * 128;
-        if (chunk < 256) chunk = 256;
+    // what bounds this entry). Two staging buffers each way.  The chunks ramp up from 256 rows and
+    // down again to 256: nothing can be downloaded before the first chunk is up and computed, and
+    // nothing overlaps the download of the last one, so both are kept short, while the chunks in the
+    // middle (about a sixth of the batch each) keep the number of copies small.
+    std::vector<uint32_t> sizes;
+    if (rows < 1024) sizes.push_back(rows);
+    else {
+        uint32_t big = ((rows / 6) + 127) / 128 * 128;
+        if (big < 256) big = 256;
+        std::vector<uint32_t> ramp;
+        uint32_t ramp_rows = 0;
+        for (uint32_t sz = 256; sz < big && 2 * (ramp_rows + sz) <= rows / 2; sz *= 2) { ramp.push_back(sz); ramp_rows += sz; }
+        const uint32_t middle = rows - 2 * ramp_rows, count = (middle + big - 1) / big;
+        const uint32_t each = ((middle + count - 1) / count + 127) / 128 * 128;
+        sizes = ramp;
+        for (uint32_t left = middle; left;) { const uint32_t take = left < each ? left : each; sizes.push_back(take); left -= take; }
+        for (size_t i = ramp.size(); i-- > 0;) sizes.push_back(ramp[i]);
     }
-    const uint32_t chunks = (rows + chunk - 1) / chunk;
+    uint32_t chunk = 0;   // the largest chunk sizes the staging buffers
+    for (uint32_t sz : sizes) chunk = sz > chunk ? sz : chunk;
+    const uint32_t chunks = (uint32_t)sizes.size();
     CUDA_TRY(ctx->stage_in.reserve(2 * (size_t)chunk * in_row), 0);
     CUDA_TRY(ctx->stage_out.reserve(2 * (size_t)chunk * out_row), 0);
     if (!ctx->copy_in) {
@@ -1268,9 +1281,10 @@ int vxb_linear_host(VxbContext* ctx, const VxbWeight* w, const float* x_host, ui
     CUDA_TRY(cudaEventRecord(ctx->ev_start, ctx->stream), -1);
     CUDA_TRY(cudaStreamWaitEvent(ctx->copy_in, ctx->ev_start, 0), -1);
     CUDA_TRY(cudaStreamWaitEvent(ctx->copy_out, ctx->ev_start, 0), -1);
+    uint32_t r0 = 0;
     for (uint32_t c = 0; c < chunks; c++) {
         const int b = (int)(c & 1u);
-        const uint32_t r0 = c * chunk, cnt = rows - r0 < chunk ? rows - r0 : chunk;
+        const uint32_t cnt = sizes[c];
         uint8_t* din = (uint8_t*)ctx->stage_in.ptr + (size_t)b * chunk * in_row;
         uint8_t* dout = (uint8_t*)ctx->stage_out.ptr + (size_t)b * chunk * out_row;
         // upload: the buffer is free once the kernels of chunk c-2 are done with it
@@ -1291,6 +1305,7 @@ int vxb_linear_host(VxbContext* ctx, const VxbWeight* w, const float* x_host, ui
         CUDA_TRY(cudaMemcpyAsync((uint8_t*)y_host + (size_t)r0 * out_row, dout, (size_t)cnt * out_row,
                                  cudaMemcpyDeviceToHost, ctx->copy_out), -1);
         CUDA_TRY(cudaEventRecord(ctx->ev_out[b], ctx->copy_out), -1);
+        r0 += cnt;
     }
     // the context's stream joins the last download(s), then the caller waits on it
     for (int b = 0; b < 2; b++)
