@@ -534,10 +534,11 @@ def test_host_packed_linear_entry(torch, oracle):
     w8a8.host_cache_clear()
 
 
-@pytest.mark.parametrize("rows", [7, 1024, 3001])
+@pytest.mark.parametrize("rows", [7, 1023, 1024, 1500, 3001, 8193])
 def test_host_whole_op_entry_matches_device_entries(torch, ctx, rows):
-    """vxb_linear_host (chunked, three-stream pipeline for large batches) returns the same bytes
-    as the device-pointer entries, for both epilogues and a ragged last chunk."""
+    """vxb_linear_host (three-stream pipeline over row chunks that ramp from 256 rows up and down again for
+    large batches) returns the same bytes as the device-pointer entries, for both epilogues, with ragged
+    chunks in the middle of the schedule."""
     from volvoxai_b200 import w8a8
     c = wl.gemm_case(rows, 512, 384, seed=rows)
     weight = w8a8.Weight.from_i8(ctx, c["w"], c["ws"], bias_f32=np.linspace(-1, 1, 384).astype(np.float32))
