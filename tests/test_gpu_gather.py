@@ -200,13 +200,15 @@ def _worker(rank, world, port, rows, k, n, ret):
         # the host-fed form: every rank uploads its rows, the int8 codes are all-gathered over NCCL
         every_shard_holds_channels = all(sharded.shard_bounds(n, world, r)[1] > sharded.shard_bounds(n, world, r)[0] for r in range(world))
         if every_shard_holds_channels and rows % world == 0:      # a collective: the same decision on every rank
-            host = sharded.RowShardedHostLinear(ctx, weight, rows, k, world, rank)
             per = rows // world
             x_pin = torch.from_numpy(case["x"][rank * per:(rank + 1) * per].copy()).pin_memory()
-            y_pin = torch.empty((rows, hi - lo), dtype=torch.int8).pin_memory()
-            for _ in range(2):
-                host.forward(x_pin, y_pin, os_)
-                ok = ok and np.array_equal(y_pin.numpy(), want[:, lo:hi])
+            # the default number of row pieces, and two pieces where the rank's rows divide (pipelined copies)
+            for pieces in (None, 2 if per % 2 == 0 else 1):
+                host = sharded.RowShardedHostLinear(ctx, weight, rows, k, world, rank, pieces=pieces)
+                y_pin = torch.full((rows, hi - lo), 99, dtype=torch.int8).pin_memory()
+                for _ in range(2):
+                    host.forward(x_pin, y_pin, os_)
+                    ok = ok and np.array_equal(y_pin.numpy(), want[:, lo:hi])
         if weight is not None:
             weight.close()
         ctx.close()

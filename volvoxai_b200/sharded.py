@@ -106,46 +106,73 @@ class RowShardedHostLinear:
     """The N-sharded linear fed from HOST memory at `world` GPUs without replicating the upload.
 
     Rank r holds rows [r*M/g, (r+1)*M/g) of the fp32 activations in pinned host memory and the
-    channel range shard_bounds(n, world, r) of the weights.  One step: upload the rank's rows,
-    quantize them (K1 on M/g rows), all-gather the int8 codes and the row scales over NVLink (NCCL:
-    a quarter of the fp32 bytes), run the rank's channel slab from the prepared activations with
-    the requantizing epilogue, download the [M, n_local] int8 slab.  Host traffic per step is
-    4*M*K up and M*N down in total, whatever the number of GPUs."""
+    channel range shard_bounds(n, world, r) of the weights.  One step, in `pieces` row pieces that
+    overlap on three streams (PCIe is full duplex and bounds this form): upload a piece of the rank's
+    rows, quantize it (K1), all-gather its int8 codes and row scales over NVLink (NCCL: a quarter of
+    the fp32 bytes), run the rank's channel slab over the gathered piece from prepared activations
+    with the requantizing epilogue, download the piece's rows of the [M, n_local] int8 slab while the
+    next piece uploads.  Host traffic per step is 4*M*K up and M*N down in total, whatever the
+    number of GPUs."""
 
-    def __init__(self, ctx, weight, rows: int, k: int, world: int, rank: int, group=None):
+    def __init__(self, ctx, weight, rows: int, k: int, world: int, rank: int, group=None, pieces: int | None = None):
         if rows % world:
             raise ValueError("the row count must divide by the number of GPUs")
         self.ctx, self.weight, self.rows, self.k, self.world, self.rank, self.group = ctx, weight, rows, k, world, rank, group
         self.local_rows = rows // world
+        if pieces is None:
+            pieces = 4 if self.local_rows % 4 == 0 and self.local_rows >= 1024 else 2 if self.local_rows % 2 == 0 and self.local_rows >= 512 else 1
+        if pieces < 1 or self.local_rows % pieces:
+            raise ValueError("the rank's rows must divide by the number of pieces")
+        self.pieces, self.piece_rows = pieces, self.local_rows // pieces
         dev = f"cuda:{ctx.device}"
         kpad = weight.row_bytes
         self.x_dev = torch.empty((self.local_rows, k), dtype=torch.float32, device=dev)
         self.q_local = torch.empty((self.local_rows, kpad), dtype=torch.int8, device=dev)
         self.s_local = torch.empty(self.local_rows, dtype=torch.float32, device=dev)
-        self.q_all = torch.empty((rows, kpad), dtype=torch.int8, device=dev)
-        self.s_all = torch.empty(rows, dtype=torch.float32, device=dev)
-        self.y_dev = torch.empty((rows, weight.d_out), dtype=torch.int8, device=dev)
+        gathered = world * self.piece_rows
+        self.q_all = [torch.empty((gathered, kpad), dtype=torch.int8, device=dev) for _ in range(pieces)]
+        self.s_all = [torch.empty(gathered, dtype=torch.float32, device=dev) for _ in range(pieces)]
+        self.y_dev = [torch.empty((gathered, weight.d_out), dtype=torch.int8, device=dev) for _ in range(pieces)]
+        self.s_in, self.s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+        self.ev_in = [torch.cuda.Event() for _ in range(pieces)]
+        self.ev_done = [torch.cuda.Event() for _ in range(pieces)]
 
     def forward(self, x_pinned_local, y_pinned_slab, out_scale: float, out_zero: int = 0) -> None:
-        """x_pinned_local: this rank's [M/g, K] fp32 rows; y_pinned_slab: [M, n_local] int8 (both pinned)."""
+        """x_pinned_local: this rank's [M/g, K] fp32 rows; y_pinned_slab: [M, n_local] int8 (both pinned).
+        Returns when the slab is complete in host memory."""
         import ctypes as C
         ctx, L = self.ctx, self.ctx._L
-        ctx.set_stream(torch.cuda.current_stream(ctx.device).cuda_stream)
-        self.x_dev.copy_(x_pinned_local, non_blocking=True)
-        rc = L.vxb_quantize_rows(ctx.handle, C.c_void_p(self.x_dev.data_ptr()), self.local_rows, self.k,
-                                 C.c_void_p(self.q_local.data_ptr()), self.q_local.shape[1],
-                                 C.c_void_p(self.s_local.data_ptr()), None)
-        if rc != 1:
-            raise RuntimeError("vxb_quantize_rows failed")
-        if self.world > 1:
-            dist.all_gather_into_tensor(self.q_all, self.q_local, group=self.group)
-            dist.all_gather_into_tensor(self.s_all, self.s_local, group=self.group)
-            q, s = self.q_all, self.s_all
-        else:
-            q, s = self.q_local, self.s_local
-        ctx.linear_prepared(self.weight, q, s, self.y_dev, mode=2, out_scale=out_scale, out_zero=out_zero)
-        y_pinned_slab.copy_(self.y_dev, non_blocking=True)
-        torch.cuda.current_stream(ctx.device).synchronize()
+        main = torch.cuda.current_stream(ctx.device)
+        ctx.set_stream(main.cuda_stream)
+        p, lr = self.piece_rows, self.local_rows
+        self.s_in.wait_stream(main)
+        self.s_out.wait_stream(main)
+        with torch.cuda.stream(self.s_in):
+            for j in range(self.pieces):
+                self.x_dev[j * p:(j + 1) * p].copy_(x_pinned_local[j * p:(j + 1) * p], non_blocking=True)
+                self.ev_in[j].record(self.s_in)
+        for j in range(self.pieces):
+            main.wait_event(self.ev_in[j])
+            xj, qj, sj = self.x_dev[j * p:(j + 1) * p], self.q_local[j * p:(j + 1) * p], self.s_local[j * p:(j + 1) * p]
+            rc = L.vxb_quantize_rows(ctx.handle, C.c_void_p(xj.data_ptr()), p, self.k, C.c_void_p(qj.data_ptr()),
+                                     self.q_local.shape[1], C.c_void_p(sj.data_ptr()), None)
+            if rc != 1:
+                raise RuntimeError("vxb_quantize_rows failed")
+            if self.world > 1:
+                dist.all_gather_into_tensor(self.q_all[j], qj, group=self.group)
+                dist.all_gather_into_tensor(self.s_all[j], sj, group=self.group)
+                q, s = self.q_all[j], self.s_all[j]
+            else:
+                q, s = qj, sj
+            ctx.linear_prepared(self.weight, q, s, self.y_dev[j], mode=2, out_scale=out_scale, out_zero=out_zero)
+            self.ev_done[j].record(main)
+            # the gathered piece holds rank r's rows at [r*p, (r+1)*p): they belong at rows r*lr + j*p of the slab
+            with torch.cuda.stream(self.s_out):
+                self.s_out.wait_event(self.ev_done[j])
+                for r in range(self.world):
+                    y_pinned_slab[r * lr + j * p:r * lr + (j + 1) * p].copy_(self.y_dev[j][r * p:(r + 1) * p], non_blocking=True)
+        self.s_out.synchronize()
+        main.synchronize()
 
 
 class _RawCuda:
