@@ -235,7 +235,9 @@ def reference_arm(args):
         # that time scaled to the configuration's row count, so that value = 2MKN / ms_per_step holds
         "ms_per_step": r["ms_per_step"] * (m / rows), "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-        "config": workload_config(args, 1),
+        # the configuration this arm is compared on is the GPU arm's at the same N (the CPU route itself
+        # does not shard: it runs on rank 0's host cores)
+        "config": workload_config(args, int(os.environ.get("WORLD_SIZE", "1"))),
         "sampled_rows": rows, "sample_ms_per_step": r["ms_per_step"],
         "cpu_baseline": {"value": r["tops"], "unit": "TOPS", "cores": r["cores"], "kind": r["kind"],
                          "sample": r["sample"]},
